@@ -1,0 +1,154 @@
+/* C ABI of libmononn_b200.so: the B200 (sm_100a) backend for the MonoNN hot path
+ * "XLA HLO module in -> one persistent kernel -> one launch per inference".
+ *
+ * Conventions
+ *   - every function returns 0 on success and a negative MONONN_ERR_* code on failure;
+ *     nothing here aborts the process (the reference LOG(FATAL)s instead) and there is
+ *     no CPU fallback: without a usable sm_100 device the calls fail.
+ *   - pointers are borrowed for the duration of the call unless the parameter is `out`.
+ *   - different modules may be used from different threads; one module from one
+ *     thread at a time.
+ */
+#ifndef MONONN_B200_H_
+#define MONONN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  MONONN_OK = 0,
+  MONONN_ERR_INVALID_ARGUMENT = -1,
+  MONONN_ERR_PARSE = -2,           /* HLO text or spec JSON is malformed */
+  MONONN_ERR_UNSUPPORTED = -3,     /* op / dtype / layout / pattern outside the supported set */
+  MONONN_ERR_CUDA = -4,            /* a CUDA runtime or driver call failed */
+  MONONN_ERR_NO_DEVICE = -5,       /* no sm_100 device */
+  MONONN_ERR_BARRIER_TIMEOUT = -6, /* a bounded wait inside the kernel expired */
+  MONONN_ERR_CONSTANT = -7,        /* unknown constant name or wrong size */
+  MONONN_ERR_IO = -8,              /* spec / dump directory I/O */
+  MONONN_ERR_NOT_READY = -9,       /* launch before all constants were set */
+  MONONN_ERR_TOO_LARGE = -10       /* size beyond a documented maximum */
+};
+
+typedef struct mononn_module mononn_module; /* opaque; free with mononn_destroy */
+
+/* Replaces the environment + Config singleton of the reference
+ * (mononn_engine/config/config.h:19-53, EnvVars.md:4-16). NULL strings fall back to the
+ * environment variables TF_MONONN_DUMP_DIR / TF_MONONN_EXISTING_TUNING_SPEC_DIR /
+ * TF_MONONN_THREADPOOL_SIZE. */
+typedef struct {
+  int device;                   /* CUDA device ordinal (the reference hard-codes 0) */
+  const char* dump_dir;         /* where tune() writes specs and reports */
+  const char* spec_dir;         /* existing tuning spec to load instead of tuning */
+  int threadpool_size;          /* host threads for lowering candidates; 0 = all cores */
+  int tuning_level;             /* 0 heuristics only, 1 per-GEMM tile search, 2 + grid search */
+  unsigned barrier_timeout_us;  /* bound on every in-kernel wait; 0 = 2 000 000 */
+} mononn_options;
+
+typedef struct {
+  int index;        /* position in the kernel argument list */
+  size_t bytes;
+  int kind;         /* 0 parameter, 1 live-out, 2 temp */
+  int param_number; /* HLO parameter_number for kind 0, live-out ordinal for kind 1 */
+} mononn_arg_desc;
+
+/* Parse -> fuse -> (load spec | heuristics) -> stage table.
+ * Replaces IRParserFused::from_hlo_module_unique + OptimizationRunner::run_group_* +
+ * GraphCodegen::generate as driven by MonoNNModule::generate_code
+ * (mononn_engine/module/mononn_module.cc:39-159) and the spec-loading side of the
+ * TF_MONONN_EXISTING_TUNING_SPEC_DIR hook (README.md:145-149). */
+int mononn_compile_hlo_text(const char* hlo_text, size_t len, const char* kernel_name,
+                            const mononn_options* options, mononn_module** out);
+
+/* Standalone path: build the fused graph of an encoder family from a JSON configuration
+ * instead of an HLO dump, e.g. {"model":"bert","layers":12,"hidden":768,"heads":12,
+ * "ffn":3072,"vocab":30522,"max_pos":512,"types":2,"batch":1,"seq":128,"eps":1e-12,
+ * "act":"gelu_erf"}. The model definitions are those the reference exports in
+ * examples/utils/save_model.py:44-110; constants are named "embeddings.word",
+ * "layer<i>.attn.q.w", ... (mononn_constant_info lists them). */
+int mononn_compile_encoder_json(const char* config_json, const char* kernel_name,
+                                const mononn_options* options, mononn_module** out);
+
+/* Kernel argument list: parameters by parameter_number, live-outs, then temp
+ * (mononn_engine/module/mononn_module.cc:91-143, README.md:186-200). */
+int mononn_module_args(const mononn_module* m, const mononn_arg_desc** descs, int* n);
+
+/* grid_dim, block_dim, dynamic shared memory: GraphSpecification.cuda_context.
+ * cuda_runtime_context (mononn_engine/core/context/cuda_runtime_context.cc:32-55). */
+int mononn_module_launch_config(const mononn_module* m, unsigned grid[3], unsigned block[3],
+                                unsigned* smem_bytes);
+
+/* Non-scalar HLO constants (the frozen weights). Replaces the
+ * `__device__ uint8_t buffer_for_<name>[bytes]` module globals the TF side fills
+ * (mononn_engine/codegen/graph_codegen.cc:71-86). `host` is row-major in the HLO shape. */
+int mononn_set_constant(mononn_module* m, const char* hlo_constant_name, const void* host,
+                        size_t bytes);
+/* Number of constants and the i-th constant's name / byte size. */
+int mononn_constant_count(const mononn_module* m, int* n);
+int mononn_constant_info(const mononn_module* m, int i, const char** name, size_t* bytes);
+
+/* Exactly one kernel launch on `cuda_stream` (a cudaStream_t), asynchronous.
+ * Mirrors the launch sequence of mononn_engine/module/mononn_module_tuner.cc:99-150.
+ * device_args[i] follows mononn_module_args order. The first launch with a new set of
+ * argument pointers also uploads the re-bound stage table on the same stream. */
+int mononn_launch(mononn_module* m, void* const* device_args, int n, void* cuda_stream);
+
+/* Synchronises the device, then reports the kernel's status word: 0, or
+ * MONONN_ERR_BARRIER_TIMEOUT with the stage and CTA that gave up. */
+int mononn_last_status(mononn_module* m, int* stage, int* cta);
+
+/* Search tile shapes on the device (MonoNNModuleTuner::tune,
+ * mononn_engine/module/mononn_module_tuner.cc:620-991): per-GEMM candidates timed in
+ * isolation with the allow-list mechanism, best ones merged, end-to-end pick. Needs all
+ * constants set and a full argument list. Writes dump_dir/<cluster>/ when set. */
+int mononn_tune(mononn_module* m, void* const* device_args, int n, void* cuda_stream);
+
+/* Writes <dir>/<cluster_N>/best_tuning_spec.json (+ performance_report.csv when known):
+ * the layout of mononn_engine/module/mononn_module_tuner.cc:584-603. */
+int mononn_save_spec(const mononn_module* m, const char* dir);
+/* JSON of the current spec; the pointer stays valid until the next call on `m`. */
+int mononn_spec_json(mononn_module* m, const char** json);
+
+/* Per-stage device time of the last profiled launch (performance_report.csv,
+ * mononn_engine/module/mononn_module_tuner.cc:422-448): launches once with in-kernel
+ * %globaltimer stamps, synchronises, fills up to `cap` entries of microseconds and sets
+ * *n_stages. names[i] points into module storage. */
+int mononn_profile_stages(mononn_module* m, void* const* device_args, int n, void* cuda_stream,
+                          double* us, const char** names, int cap, int* n_stages);
+
+/* Inspection. mononn_plan_json: the lowered stage table (stages, operators with tiles,
+ * tensor placements, constant bindings) of a module; stands in for the `<context>_src/`
+ * dump of the reference (mononn_engine/module/mononn_module_tuner.cc:560-575), since the
+ * table is the artefact. mononn_describe lowers without touching a device (kind "hlo" or
+ * "encoder", optional spec JSON, SM count) and returns {"plan":..,"spec":..} in a string
+ * the caller frees with mononn_free_string. */
+int mononn_plan_json(mononn_module* m, const char** json);
+int mononn_describe(const char* kind, const char* text, size_t len, const char* spec_json,
+                    unsigned sm_count, char** out_json);
+void mononn_free_string(char* s);
+
+/* Runs only stages [stage_begin, stage_end) in one launch: the single-node isolation of
+ * the reference's codegen_allow_list (mononn_engine/tuning/tuning_space_generator.cc:405-414)
+ * used for per-stage timing and for checking intermediate tensors. */
+int mononn_launch_stages(mononn_module* m, void* const* device_args, int n, void* cuda_stream,
+                         unsigned stage_begin, unsigned stage_end);
+
+/* Algorithmic bytes and FLOPs of one inference (weights once + gathered rows + I/O). */
+int mononn_module_cost(const mononn_module* m, double* bytes, double* flops);
+
+void mononn_destroy(mononn_module* m);
+const char* mononn_strerror(int code);
+/* Message of the last failing call on this thread. */
+const char* mononn_last_error(void);
+
+/* TF_MONONN_ENABLED is truthy for "True", "true" or "1"
+ * (mononn_engine/helpers/env_variable.cc:20-26); the host shim does not call in otherwise. */
+int mononn_enabled(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MONONN_B200_H_ */

@@ -1,0 +1,6 @@
+"""mononn_b200: B200 (sm_100a) backend for the MonoNN hot path -- an XLA HLO module in,
+one persistent kernel launch per inference out.  The work is done by libmononn_b200.so
+(mononn_b200/csrc); this package is the thin host-side mirror of its C ABI."""
+from .capi import MononnError, Options  # noqa: F401
+from .module import Module, compile_encoder, compile_hlo  # noqa: F401
+from .models import EncoderConfig, bert_base, bert_tiny, make_inputs, make_weights  # noqa: F401

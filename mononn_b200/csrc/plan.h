@@ -1,0 +1,177 @@
+// Host-side intermediate forms between the HLO graph and the device stage table.
+//
+//   HLO text --parser--> HloModule --recogniser--> FGraph --scheduler--> Plan --runtime--> device
+//
+// FGraph is the graph after this build's fusion passes: each node is one of the
+// kernel's operator kinds with its fused prologue/epilogue.  It plays the part of
+// the reference's clustered core::graph::Graph after run_group_pre_impl_assignment
+// (mononn_engine/optimization/optimization_runner.cc:61-84).  Plan is the result
+// of implementation/buffer assignment (optimization_runner.cc:86-163) and of
+// GraphCodegen::generate (mononn_engine/codegen/graph_codegen.cc:637-842), as
+// tables rather than source text.
+#pragma once
+#include <stdint.h>
+
+#include <map>
+#include <string>
+#include <vector>
+
+#include "stage_table.h"
+
+namespace mononn {
+
+// ---------------------------------------------------------------- tuning spec
+struct GemmTileSpec {
+  uint32_t n_tile = 0;   // 0 = choose by heuristic
+  uint32_t k_split = 0;
+};
+
+struct TuningSpec {
+  uint32_t grid = 0;       // CTAs; 0 = one per SM
+  uint32_t block = kThreads;
+  uint32_t smem_bytes = 0; // filled by the scheduler
+  std::map<std::string, GemmTileSpec> gemm;  // per GEMM node
+  std::vector<std::string> allow_list;       // run only these nodes (single-node profiling)
+  std::vector<std::string> reject_list;
+};
+
+// ------------------------------------------------------------------- FGraph
+enum class TKind : uint32_t {
+  ActF16,   // f16 activation [rows, ld] living in the caller's temp buffer
+  ActF16T,  // per-batch transposed f16 activation [batches*cols, ldt] (V^T), temp buffer
+  AccF32,   // f32 [rows, cols] accumulator in module scratch, zero whenever it is not live
+  VecF32,   // f32 vector [rows] in module scratch (mask bias)
+  Const,    // HLO constant (weights, biases, tables)
+  Arg,      // kernel argument (parameter or live-out)
+};
+
+struct FTensor {
+  std::string name;
+  TKind kind = TKind::ActF16;
+  uint32_t rows = 0, cols = 0, ld = 0;
+  uint32_t batches = 1, seq = 0;  // ActF16T geometry
+  uint32_t elem_bytes = 2;
+  int arg_index = -1;             // Arg
+  std::string const_name;         // Const: HLO constant name
+  std::vector<uint32_t> const_dims;
+  bool const_transposed = false;  // Const weight given as [N, K] instead of [K, N]
+};
+
+struct FOp {
+  OpKind kind = OP_NONE;
+  std::string name;
+  uint32_t flags = 0;
+  ActKind act = ACT_NONE;
+  float alpha = 1.f, eps = 0.f;
+  // GEMM: a (ActF16 [M,K]), w (Const [K,N]), bias (Const [N]), resid (ActF16), out
+  int a = -1, w = -1, bias = -1, resid = -1, out = -1;
+  uint32_t M = 0, N = 0, K = 0;
+  // ATTENTION: q, k (ActF16 with column offsets), vt (ActF16T), mask (VecF32), out
+  int q = -1, k = -1, vt = -1, mask = -1;
+  uint32_t q_col = 0, k_col = 0, heads = 0, seq = 0, batches = 0, head_dim = 64;
+  // LAYERNORM: src (AccF32 | ActF16), resid, gamma, beta, out
+  int src = -1, gamma = -1, beta = -1;
+  // EMBED: ids, type_ids, mask_in (Arg), word/pos/type tables (Const), mask_out (VecF32)
+  int ids = -1, type_ids = -1, mask_in = -1, word = -1, pos = -1, type = -1, mask_out = -1;
+  uint32_t rows = 0, cols = 0, vocab = 0;
+  int stage = -1;  // filled by the scheduler
+};
+
+struct ArgDesc {
+  std::string name;
+  size_t bytes = 0;
+  int kind = 0;  // 0 parameter, 1 live-out, 2 temp
+  int param_number = -1;
+};
+
+struct FGraph {
+  std::string module_name;
+  std::vector<FTensor> tensors;
+  std::vector<FOp> ops;
+  std::vector<ArgDesc> args;  // parameters.., live-outs.. ; the scheduler appends temp
+  int add_tensor(const FTensor& t) {
+    tensors.push_back(t);
+    return static_cast<int>(tensors.size()) - 1;
+  }
+};
+
+// --------------------------------------------------------------------- Plan
+enum BufSpace : int32_t { SPACE_NONE = -1, SPACE_ARG = 0, SPACE_CONST = 1, SPACE_SCRATCH = 2 };
+
+struct BufRef {
+  int32_t space = SPACE_NONE;
+  int32_t index = 0;  // argument index for SPACE_ARG
+  uint64_t offset = 0;
+};
+
+struct TmapSpec {
+  BufRef base;
+  uint64_t dim0 = 0, dim1 = 0;  // elements; dim0 is contiguous
+  uint64_t stride1_bytes = 0;
+  uint32_t box0 = 0, box1 = 0;
+};
+
+struct PlanOp {
+  std::string name;
+  OpDesc d{};
+  BufRef p[8];
+  BufRef q[2];
+};
+
+// How one HLO constant lands in the constant arena.
+struct ConstBinding {
+  std::string const_name;
+  enum Kind { RAW, PACK_B } kind = RAW;
+  uint64_t offset = 0, bytes = 0;
+  // PACK_B: source is row-major [K, N] (or [N, K] when transposed) f16;
+  // destination is [n_tiles][K/64][n_tile][64] so every (n tile, k block) is one
+  // contiguous 128-byte-row tile a single TMA box can fetch.
+  uint32_t K = 0, N = 0, n_tile = 0;
+  bool transposed = false;
+  size_t src_bytes = 0;
+};
+
+// Where a graph tensor lives (for inspection and intermediate-tensor parity checks).
+struct TensorPlacement {
+  std::string name;
+  TKind kind = TKind::ActF16;
+  BufRef at;
+  uint32_t rows = 0, cols = 0, ld = 0, batches = 1, seq = 0;
+  int def_stage = -1, last_stage = -1;
+};
+
+struct Plan {
+  std::string module_name;
+  std::vector<TensorPlacement> tensors;
+  std::vector<PlanOp> ops;
+  std::vector<StageDesc> stages;
+  std::vector<std::string> stage_names;
+  std::vector<TmapSpec> tmaps;
+  std::vector<ArgDesc> args;
+  std::vector<ConstBinding> consts;
+  uint64_t const_bytes = 0;
+  uint64_t scratch_bytes = 0;  // module-owned, zero-initialised
+  uint64_t temp_bytes = 0;
+  uint32_t grid = 0, block = kThreads, smem_bytes = 0;
+  TuningSpec spec;             // the spec this plan realises (with heuristics filled in)
+  double algorithmic_bytes = 0, algorithmic_flops = 0;
+};
+
+// Scheduler: stage assignment by dependency depth, tile selection, buffer and
+// tensor-map assignment. Returns 0 or a negative mononn error code; `err` gets a message.
+int schedule(const FGraph& g, const TuningSpec& spec, uint32_t sm_count, Plan* plan,
+             std::string* err);
+
+// Default tile choice for one GEMM given how many CTAs it may occupy.
+GemmTileSpec default_gemm_tile(uint32_t M, uint32_t N, uint32_t K, bool can_split_k,
+                               uint32_t cta_budget);
+// Legal alternatives for the tuner.
+std::vector<GemmTileSpec> gemm_tile_candidates(uint32_t M, uint32_t N, uint32_t K,
+                                               bool can_split_k, uint32_t cta_budget);
+
+// Fixed head of the module scratch: barrier counter, status word, per-stage time stamps.
+constexpr uint64_t kScratchBarrierOff = 0, kScratchStatusOff = 256, kScratchStampsOff = 512;
+
+constexpr uint32_t kSmemBytes = (kASlots + kBSlots) * kSlotBytes + 1024 /*ctrl*/ + 1024 /*align*/;
+
+}  // namespace mononn

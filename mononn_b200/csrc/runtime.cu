@@ -1,0 +1,344 @@
+// Device-side life of a module (see runtime.h).
+#include "runtime.h"
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/mononn.h"
+
+namespace mononn {
+
+extern "C" __global__ void mononn_megakernel(const __grid_constant__ KernelParams P);
+
+static thread_local std::string g_last_error;
+void set_last_error(const std::string& msg) { g_last_error = msg; }
+const char* get_last_error() { return g_last_error.c_str(); }
+
+#define CUDA_TRY(expr)                                                                   \
+  do {                                                                                   \
+    cudaError_t e__ = (expr);                                                            \
+    if (e__ != cudaSuccess) {                                                            \
+      set_last_error(std::string(#expr) + ": " + cudaGetErrorString(e__));               \
+      return MONONN_ERR_CUDA;                                                            \
+    }                                                                                    \
+  } while (0)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+Runtime::~Runtime() { release(); }
+
+void Runtime::release() {
+  if (d_const_) cudaFree(d_const_);
+  if (d_scratch_) cudaFree(d_scratch_);
+  if (d_table_) cudaFree(d_table_);
+  d_const_ = d_scratch_ = d_table_ = nullptr;
+}
+
+int Runtime::init(int device) {
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0) {
+    set_last_error("no CUDA device is visible; this backend has no CPU path");
+    return MONONN_ERR_NO_DEVICE;
+  }
+  if (device < 0 || device >= count) {
+    set_last_error("device ordinal out of range");
+    return MONONN_ERR_INVALID_ARGUMENT;
+  }
+  CUDA_TRY(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10) {
+    set_last_error("device is sm_" + std::to_string(prop.major * 10 + prop.minor) +
+                   "; the kernel is built for sm_100a only");
+    return MONONN_ERR_NO_DEVICE;
+  }
+  int coop = 0;
+  CUDA_TRY(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device));
+  if (!coop) {
+    set_last_error("device does not support cooperative launches");
+    return MONONN_ERR_NO_DEVICE;
+  }
+  device_ = device;
+  sm_count_ = static_cast<uint32_t>(prop.multiProcessorCount);
+  cudaDriverEntryPointQueryResult qres;
+  CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &encode_fn_, cudaEnableDefault, &qres));
+  if (qres != cudaDriverEntryPointSuccess || encode_fn_ == nullptr) {
+    set_last_error("cuTensorMapEncodeTiled is not available from the driver");
+    return MONONN_ERR_CUDA;
+  }
+  CUDA_TRY(cudaFuncSetAttribute(mononn_megakernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                static_cast<int>(kSmemBytes)));
+  attr_set_ = true;
+  return MONONN_OK;
+}
+
+int Runtime::max_coresident_ctas() {
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, mononn_megakernel, kThreads,
+                                                    kSmemBytes) != cudaSuccess)
+    return 0;
+  return per_sm * static_cast<int>(sm_count_);
+}
+
+int Runtime::load_plan(const Plan& plan) {
+  CUDA_TRY(cudaSetDevice(device_));
+  const int cap = max_coresident_ctas();
+  if (static_cast<int>(plan.grid) > cap) {
+    set_last_error("grid of " + std::to_string(plan.grid) + " CTAs exceeds the " +
+                   std::to_string(cap) + " that can be co-resident; the grid barrier would hang");
+    return MONONN_ERR_INVALID_ARGUMENT;
+  }
+  CUDA_TRY(cudaDeviceSynchronize());
+  release();
+  plan_ = plan;
+  CUDA_TRY(cudaMalloc(&d_const_, plan_.const_bytes));
+  CUDA_TRY(cudaMemset(d_const_, 0, plan_.const_bytes));
+  CUDA_TRY(cudaMalloc(&d_scratch_, plan_.scratch_bytes));
+  CUDA_TRY(cudaMemset(d_scratch_, 0, plan_.scratch_bytes));
+  off_ops_ = plan_.stages.size() * sizeof(StageDesc);
+  off_ops_ = (off_ops_ + 127) / 128 * 128;
+  off_tmaps_ = off_ops_ + plan_.ops.size() * sizeof(OpDesc);
+  off_tmaps_ = (off_tmaps_ + 127) / 128 * 128;
+  table_bytes_ = off_tmaps_ + plan_.tmaps.size() * 128;
+  CUDA_TRY(cudaMalloc(&d_table_, table_bytes_ + 128));
+  h_table_.assign(table_bytes_, 0);
+  bound_ = false;
+  bound_args_.clear();
+  epoch_ = 0;
+  for (const auto& kv : host_consts_)
+    for (const ConstBinding& b : plan_.consts)
+      if (b.const_name == kv.first) {
+        int rc = upload_constant(b, kv.second);
+        if (rc) return rc;
+      }
+  return MONONN_OK;
+}
+
+int Runtime::upload_constant(const ConstBinding& b, const std::vector<uint8_t>& src) {
+  uint8_t* dst = static_cast<uint8_t*>(d_const_) + b.offset;
+  if (b.kind == ConstBinding::RAW) {
+    CUDA_TRY(cudaMemcpy(dst, src.data(), b.bytes, cudaMemcpyHostToDevice));
+    return MONONN_OK;
+  }
+  // PACK_B: [n_tiles][K/64][n_tile][64], zero padded in N
+  const uint32_t K = b.K, N = b.N, nt = b.n_tile, kb = K / 64;
+  const uint32_t n_tiles = (N + nt - 1) / nt;
+  std::vector<uint16_t> packed(static_cast<size_t>(n_tiles) * nt * K, 0);
+  const uint16_t* w = reinterpret_cast<const uint16_t*>(src.data());
+  for (uint32_t t = 0; t < n_tiles; ++t)
+    for (uint32_t k = 0; k < kb; ++k)
+      for (uint32_t r = 0; r < nt; ++r) {
+        const uint32_t n = t * nt + r;
+        if (n >= N) continue;
+        uint16_t* d = &packed[((static_cast<size_t>(t) * kb + k) * nt + r) * 64];
+        if (b.transposed) {
+          std::memcpy(d, w + static_cast<size_t>(n) * K + k * 64, 128);
+        } else {
+          const uint16_t* s = w + static_cast<size_t>(k) * 64 * N + n;
+          for (uint32_t c = 0; c < 64; ++c) d[c] = s[static_cast<size_t>(c) * N];
+        }
+      }
+  CUDA_TRY(cudaMemcpy(dst, packed.data(), packed.size() * 2, cudaMemcpyHostToDevice));
+  return MONONN_OK;
+}
+
+int Runtime::set_constant(const std::string& name, const void* host, size_t bytes) {
+  CUDA_TRY(cudaSetDevice(device_));
+  bool found = false;
+  for (const ConstBinding& b : plan_.consts)
+    if (b.const_name == name) {
+      found = true;
+      if (b.src_bytes != bytes) {
+        set_last_error("constant " + name + ": expected " + std::to_string(b.src_bytes) +
+                       " bytes, got " + std::to_string(bytes));
+        return MONONN_ERR_CONSTANT;
+      }
+    }
+  if (!found) {
+    set_last_error("unknown constant " + name);
+    return MONONN_ERR_CONSTANT;
+  }
+  std::vector<uint8_t>& copy = host_consts_[name];
+  copy.assign(static_cast<const uint8_t*>(host), static_cast<const uint8_t*>(host) + bytes);
+  for (const ConstBinding& b : plan_.consts)
+    if (b.const_name == name) {
+      int rc = upload_constant(b, copy);
+      if (rc) return rc;
+    }
+  return MONONN_OK;
+}
+
+bool Runtime::constants_ready(std::string* missing) const {
+  for (const ConstBinding& b : plan_.consts)
+    if (!host_consts_.count(b.const_name)) {
+      if (missing) *missing = b.const_name;
+      return false;
+    }
+  return true;
+}
+
+int Runtime::bind(void* const* args, int n, void* stream) {
+  if (n != static_cast<int>(plan_.args.size())) {
+    set_last_error("expected " + std::to_string(plan_.args.size()) + " kernel arguments, got " +
+                   std::to_string(n));
+    return MONONN_ERR_INVALID_ARGUMENT;
+  }
+  if (bound_ && bound_args_.size() == static_cast<size_t>(n) &&
+      std::memcmp(bound_args_.data(), args, sizeof(void*) * n) == 0)
+    return MONONN_OK;
+  auto resolve = [&](const BufRef& r) -> uint64_t {
+    switch (r.space) {
+      case SPACE_ARG:
+        return reinterpret_cast<uint64_t>(args[r.index]) + r.offset;
+      case SPACE_CONST:
+        return reinterpret_cast<uint64_t>(d_const_) + r.offset;
+      case SPACE_SCRATCH:
+        return reinterpret_cast<uint64_t>(d_scratch_) + r.offset;
+      default:
+        return 0;
+    }
+  };
+  std::memcpy(h_table_.data(), plan_.stages.data(), plan_.stages.size() * sizeof(StageDesc));
+  OpDesc* ops = reinterpret_cast<OpDesc*>(h_table_.data() + off_ops_);
+  for (size_t i = 0; i < plan_.ops.size(); ++i) {
+    ops[i] = plan_.ops[i].d;
+    for (int k = 0; k < 8; ++k) ops[i].p[k] = resolve(plan_.ops[i].p[k]);
+    for (int k = 0; k < 2; ++k) ops[i].q[k] = resolve(plan_.ops[i].q[k]);
+  }
+  EncodeTiledFn encode = reinterpret_cast<EncodeTiledFn>(encode_fn_);
+  for (size_t i = 0; i < plan_.tmaps.size(); ++i) {
+    const TmapSpec& t = plan_.tmaps[i];
+    CUtensorMap tm;
+    const cuuint64_t dims[2] = {t.dim0, t.dim1};
+    const cuuint64_t strides[1] = {t.stride1_bytes};
+    const cuuint32_t box[2] = {t.box0, t.box1};
+    const cuuint32_t estr[2] = {1, 1};
+    const uint64_t base = resolve(t.base);
+    if ((base & 15u) || (t.stride1_bytes & 15u)) {
+      set_last_error("tensor map " + std::to_string(i) + ": base or stride is not 16-byte aligned");
+      return MONONN_ERR_INVALID_ARGUMENT;
+    }
+    CUresult r = encode(&tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, reinterpret_cast<void*>(base), dims,
+                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+      set_last_error("cuTensorMapEncodeTiled failed for tensor map " + std::to_string(i) +
+                     " (CUresult " + std::to_string(static_cast<int>(r)) + ")");
+      return MONONN_ERR_CUDA;
+    }
+    std::memcpy(h_table_.data() + off_tmaps_ + i * 128, &tm, 128);
+  }
+  // the table base must be 128-byte aligned for the tensor maps (cudaMalloc gives 256)
+  CUDA_TRY(cudaMemcpyAsync(d_table_, h_table_.data(), table_bytes_, cudaMemcpyHostToDevice,
+                           static_cast<cudaStream_t>(stream)));
+  bound_args_.assign(args, args + n);
+  bound_ = true;
+  return MONONN_OK;
+}
+
+int Runtime::launch(void* const* args, int n, void* stream, uint32_t stage_begin,
+                    uint32_t stage_end, bool stamps) {
+  CUDA_TRY(cudaSetDevice(device_));
+  if (stage_end > plan_.stages.size() || stage_begin >= stage_end) {
+    set_last_error("stage range out of bounds");
+    return MONONN_ERR_INVALID_ARGUMENT;
+  }
+  std::string missing;
+  if (!constants_ready(&missing)) {
+    set_last_error("constant " + missing + " has not been set");
+    return MONONN_ERR_NOT_READY;
+  }
+  int rc = bind(args, n, stream);
+  if (rc) return rc;
+  KernelParams kp;
+  uint8_t* tab = static_cast<uint8_t*>(d_table_);
+  uint8_t* scr = static_cast<uint8_t*>(d_scratch_);
+  kp.stages = reinterpret_cast<const StageDesc*>(tab);
+  kp.ops = reinterpret_cast<const OpDesc*>(tab + off_ops_);
+  kp.tmaps = tab + off_tmaps_;
+  kp.barrier = reinterpret_cast<uint32_t*>(scr + kScratchBarrierOff);
+  kp.status = reinterpret_cast<KernelStatus*>(scr + kScratchStatusOff);
+  kp.stamps = stamps ? reinterpret_cast<uint64_t*>(scr + kScratchStampsOff) : nullptr;
+  kp.n_stages = static_cast<uint32_t>(plan_.stages.size());
+  kp.epoch_base = epoch_;
+  kp.timeout_us = timeout_us ? timeout_us : 2000000u;
+  kp.stage_begin = stage_begin;
+  kp.stage_end = stage_end;
+  void* kargs[1] = {&kp};
+  CUDA_TRY(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(mononn_megakernel),
+                                       dim3(plan_.grid), dim3(plan_.block), kargs, plan_.smem_bytes,
+                                       static_cast<cudaStream_t>(stream)));
+  epoch_ += (stage_end - stage_begin) * plan_.grid;
+  if (stamps) n_stamp_stages_ = stage_end - stage_begin;
+  return MONONN_OK;
+}
+
+int Runtime::check_status(int* stage, int* cta) {
+  CUDA_TRY(cudaSetDevice(device_));
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    set_last_error(std::string("kernel failed: ") + cudaGetErrorString(e));
+    return MONONN_ERR_CUDA;
+  }
+  KernelStatus st;
+  CUDA_TRY(cudaMemcpy(&st, static_cast<uint8_t*>(d_scratch_) + kScratchStatusOff, sizeof(st),
+                      cudaMemcpyDeviceToHost));
+  if (st.code == ST_OK) return MONONN_OK;
+  if (stage) *stage = static_cast<int>(st.stage);
+  if (cta) *cta = static_cast<int>(st.cta);
+  char buf[160];
+  std::snprintf(buf, sizeof(buf),
+                "bounded wait expired in the kernel: code %u, stage %u, CTA %u, wait site 0x%x",
+                st.code, st.stage, st.cta, st.where);
+  set_last_error(buf);
+  // restore the invariants the next launch relies on: counter, status, zeroed accumulators
+  CUDA_TRY(cudaMemset(d_scratch_, 0, plan_.scratch_bytes));
+  epoch_ = 0;
+  return MONONN_ERR_BARRIER_TIMEOUT;
+}
+
+int Runtime::read_stamps(std::vector<double>* us) {
+  std::vector<uint64_t> t(n_stamp_stages_ + 1);
+  CUDA_TRY(cudaMemcpy(t.data(), static_cast<uint8_t*>(d_scratch_) + kScratchStampsOff,
+                      t.size() * 8, cudaMemcpyDeviceToHost));
+  us->clear();
+  for (uint32_t i = 0; i < n_stamp_stages_; ++i)
+    us->push_back(static_cast<double>(t[i + 1] - t[i]) * 1e-3);
+  return MONONN_OK;
+}
+
+int Runtime::time_stages(void* const* args, int n, void* stream, uint32_t begin, uint32_t end,
+                         int warmup, int iters, double* us) {
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  for (int i = 0; i < warmup; ++i) {
+    int rc = launch(args, n, stream, begin, end, false);
+    if (rc) return rc;
+  }
+  cudaEvent_t e0, e1;
+  CUDA_TRY(cudaEventCreate(&e0));
+  CUDA_TRY(cudaEventCreate(&e1));
+  CUDA_TRY(cudaEventRecord(e0, s));
+  for (int i = 0; i < iters; ++i) {
+    int rc = launch(args, n, stream, begin, end, false);
+    if (rc) return rc;
+  }
+  CUDA_TRY(cudaEventRecord(e1, s));
+  CUDA_TRY(cudaEventSynchronize(e1));
+  float ms = 0;
+  CUDA_TRY(cudaEventElapsedTime(&ms, e0, e1));
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  *us = static_cast<double>(ms) * 1000.0 / iters;
+  int st = 0, cta = 0;
+  return check_status(&st, &cta);
+}
+
+}  // namespace mononn

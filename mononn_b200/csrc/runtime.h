@@ -1,0 +1,83 @@
+// Device-side life of a module: constant arena, scratch, bound stage table, launch.
+//
+// Stands where the (absent) TF side of the reference stood: it loads the kernel, sets the
+// dynamic shared-memory attribute and launches (grid, block, smem) with the argument list
+// (params.., live-outs.., temp) -- the sequence mirrored in
+// mononn_engine/module/mononn_module_tuner.cc:99-150 -- except that the "kernel" is the
+// pre-compiled table interpreter and the per-graph artefact is the table.
+#pragma once
+#include <map>
+#include <set>
+#include <string>
+#include <vector>
+
+#include "plan.h"
+
+namespace mononn {
+
+void set_last_error(const std::string& msg);
+const char* get_last_error();
+
+struct PerfRow {
+  std::string context;  // "<grid>_1_1__<block>_1_1"
+  std::string node;
+  double us;
+};
+
+class Runtime {
+ public:
+  Runtime() = default;
+  ~Runtime();
+  Runtime(const Runtime&) = delete;
+  Runtime& operator=(const Runtime&) = delete;
+
+  int init(int device);           // selects the device, checks sm_100, queries SM count
+  uint32_t sm_count() const { return sm_count_; }
+  int max_coresident_ctas();      // occupancy query for the cooperative launch
+
+  // (Re)builds device state for a plan. Constants already given are re-packed.
+  int load_plan(const Plan& plan);
+  const Plan& plan() const { return plan_; }
+
+  int set_constant(const std::string& name, const void* host, size_t bytes);
+  bool constants_ready(std::string* missing) const;
+
+  // One cooperative launch over stages [begin, end). stamps: record per-stage timers.
+  int launch(void* const* args, int n, void* stream, uint32_t stage_begin, uint32_t stage_end,
+             bool stamps);
+  int launch_all(void* const* args, int n, void* stream) {
+    return launch(args, n, stream, 0, static_cast<uint32_t>(plan_.stages.size()), false);
+  }
+  // cudaDeviceSynchronize + status word; resets barrier and accumulators after a failure.
+  int check_status(int* stage, int* cta);
+  int read_stamps(std::vector<double>* us);  // after a stamps launch + sync
+  // Mean device time (microseconds) of `iters` launches of stages [begin, end) after `warmup`.
+  int time_stages(void* const* args, int n, void* stream, uint32_t begin, uint32_t end, int warmup,
+                  int iters, double* us);
+
+  unsigned timeout_us = 2000000;
+  const std::map<std::string, std::vector<uint8_t>>& host_constants() const { return host_consts_; }
+
+ private:
+  int bind(void* const* args, int n, void* stream);
+  int upload_constant(const ConstBinding& b, const std::vector<uint8_t>& src);
+  void release();
+
+  int device_ = 0;
+  uint32_t sm_count_ = 0;
+  Plan plan_;
+  void* d_const_ = nullptr;
+  void* d_scratch_ = nullptr;
+  void* d_table_ = nullptr;
+  size_t table_bytes_ = 0, off_ops_ = 0, off_tmaps_ = 0;
+  std::vector<uint8_t> h_table_;
+  std::vector<void*> bound_args_;
+  bool bound_ = false;
+  uint32_t epoch_ = 0;
+  uint32_t n_stamp_stages_ = 0;
+  std::map<std::string, std::vector<uint8_t>> host_consts_;
+  void* encode_fn_ = nullptr;
+  bool attr_set_ = false;
+};
+
+}  // namespace mononn

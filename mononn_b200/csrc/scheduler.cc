@@ -1,0 +1,548 @@
+// FGraph -> Plan: barrier-depth stage assignment, tile selection, buffer and tensor-map
+// assignment, constant-arena layout.
+//
+// Counterparts in the reference:
+//   stage assignment  GlobalSynchronizationEliminationPass (BFS depth over Global edges,
+//                     mononn_engine/optimization/global_synchronization_elimination_pass.cc:98-147)
+//   horizontal merge  MergeIndependentPass (.../merge_independent_pass.cc:103-194): here all
+//                     operators of one depth share a stage and split the CTAs between them
+//   tile selection    ImplementationAssignmentPass (.../implementation_assignment_pass.cc:49-193)
+//   buffers           BufferAssignmentPass + XLA's BufferAssignment offsets
+//                     (mononn_engine/codegen/graph_codegen.cc:113-257); XLA is absent, so a
+//                     liveness-based first-fit allocator decides the temp-arena offsets
+#include <algorithm>
+#include <cstring>
+#include <set>
+
+#include "../../include/mononn.h"
+#include "plan.h"
+
+namespace mononn {
+
+static inline uint64_t align_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
+
+// ------------------------------------------------------------ tile selection
+static bool tile_legal(uint32_t N, uint32_t K, const GemmTileSpec& t, bool can_split_k) {
+  if (t.n_tile < 16 || t.n_tile > 256 || (t.n_tile % 16) != 0) return false;
+  if (t.k_split < 1) return false;
+  const uint32_t kb = (K + 63) / 64;
+  if (kb % t.k_split != 0) return false;
+  if (t.k_split > 1 && !can_split_k) return false;
+  (void)N;
+  return true;
+}
+
+// Bytes a CTA moves for one tile: the A slab (L2), the weight slab (HBM) and the
+// partial-sum reduction when K is split. A crude latency-free model; the tuner refines it.
+static double tile_cost(uint32_t M, uint32_t N, uint32_t K, const GemmTileSpec& t,
+                        uint32_t cta_budget) {
+  const uint32_t m_tiles = (M + 127) / 128, n_tiles = (N + t.n_tile - 1) / t.n_tile;
+  const uint32_t items = m_tiles * n_tiles * t.k_split;
+  const uint32_t waves = (items + cta_budget - 1) / cta_budget;
+  const double kchunk = static_cast<double>(K) / t.k_split;
+  double per_item = (128.0 * 0.5 + t.n_tile) * kchunk * 2.0;  // L2 reads weigh half of HBM reads
+  if (t.k_split > 1) per_item += 128.0 * t.n_tile * 4.0 * 2.0;  // f32 atomics
+  per_item += 2000.0;                                            // fixed pipeline fill
+  return per_item * waves;
+}
+
+std::vector<GemmTileSpec> gemm_tile_candidates(uint32_t M, uint32_t N, uint32_t K,
+                                               bool can_split_k, uint32_t cta_budget) {
+  std::vector<GemmTileSpec> out;
+  const uint32_t kb = (K + 63) / 64;
+  const uint32_t m_tiles = (M + 127) / 128;
+  for (uint32_t n_tile : {16u, 32u, 48u, 64u, 96u, 128u, 192u, 256u}) {
+    if (n_tile > std::max(16u, (N + 15) / 16 * 16)) continue;
+    for (uint32_t ks = 1; ks <= kb; ++ks) {
+      GemmTileSpec t;
+      t.n_tile = n_tile;
+      t.k_split = ks;
+      if (!tile_legal(N, K, t, can_split_k)) continue;
+      const uint32_t items = m_tiles * ((N + n_tile - 1) / n_tile) * ks;
+      // more than two waves of tiny tiles is never a good trade at these sizes
+      if (items > 2 * cta_budget && n_tile < 128) continue;
+      out.push_back(t);
+    }
+  }
+  return out;
+}
+
+GemmTileSpec default_gemm_tile(uint32_t M, uint32_t N, uint32_t K, bool can_split_k,
+                               uint32_t cta_budget) {
+  GemmTileSpec best;
+  best.n_tile = 16;
+  best.k_split = 1;
+  double best_cost = 1e300;
+  for (const GemmTileSpec& t : gemm_tile_candidates(M, N, K, can_split_k, cta_budget)) {
+    const double c = tile_cost(M, N, K, t, cta_budget);
+    if (c < best_cost) {
+      best_cost = c;
+      best = t;
+    }
+  }
+  return best;
+}
+
+// ---------------------------------------------------------- liveness arena
+namespace {
+struct Interval {
+  int tensor;
+  int def_stage, last_stage;
+  uint64_t bytes;
+  uint64_t offset;
+};
+
+// First-fit by address among intervals whose live ranges overlap. A buffer may be
+// reused by a tensor defined in a later stage than the previous owner's last use:
+// the grid barrier between the two stages orders the last read before the first write.
+uint64_t assign_offsets(std::vector<Interval>& iv, uint64_t base, uint64_t align) {
+  std::sort(iv.begin(), iv.end(), [](const Interval& a, const Interval& b) {
+    return a.def_stage != b.def_stage ? a.def_stage < b.def_stage : a.bytes > b.bytes;
+  });
+  uint64_t top = base;
+  std::vector<Interval*> placed;
+  for (Interval& x : iv) {
+    std::vector<std::pair<uint64_t, uint64_t>> busy;
+    for (Interval* y : placed)
+      if (!(y->last_stage < x.def_stage || x.last_stage < y->def_stage))
+        busy.push_back({y->offset, y->offset + y->bytes});
+    std::sort(busy.begin(), busy.end());
+    uint64_t off = base;
+    for (auto& b : busy) {
+      if (off + x.bytes <= b.first) break;
+      off = std::max(off, align_up(b.second, align));
+    }
+    x.offset = off;
+    top = std::max(top, off + x.bytes);
+    placed.push_back(&x);
+  }
+  return align_up(top, align);
+}
+}  // namespace
+
+static bool listed(const std::vector<std::string>& l, const std::string& n) {
+  return std::find(l.begin(), l.end(), n) != l.end();
+}
+
+int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan* plan,
+             std::string* err) {
+  Plan& P = *plan;
+  P = Plan();
+  P.module_name = g.module_name;
+  P.spec = spec_in;
+  P.grid = spec_in.grid ? spec_in.grid : sm_count;
+  P.block = kThreads;
+  P.smem_bytes = kSmemBytes;
+  P.spec.grid = P.grid;
+  P.spec.block = P.block;
+  P.spec.smem_bytes = P.smem_bytes;
+  P.args = g.args;
+  const int n_t = static_cast<int>(g.tensors.size());
+
+  // ---- inputs / outputs of every op
+  auto inputs_of = [](const FOp& o) {
+    std::vector<int> v;
+    for (int t : {o.a, o.w, o.bias, o.resid, o.q, o.k, o.vt, o.mask, o.src, o.gamma, o.beta, o.ids,
+                  o.type_ids, o.mask_in, o.word, o.pos, o.type})
+      if (t >= 0) v.push_back(t);
+    return v;
+  };
+  auto outputs_of = [](const FOp& o) {
+    std::vector<int> v;
+    for (int t : {o.out, o.mask_out})
+      if (t >= 0) v.push_back(t);
+    return v;
+  };
+
+  std::vector<FOp> ops;
+  for (const FOp& o : g.ops) {
+    if (!spec_in.allow_list.empty() && !listed(spec_in.allow_list, o.name)) continue;
+    if (listed(spec_in.reject_list, o.name)) continue;
+    ops.push_back(o);
+  }
+  if (ops.empty()) {
+    if (err) *err = "no operators left after allow/reject lists";
+    return MONONN_ERR_INVALID_ARGUMENT;
+  }
+
+  // ---- stage = dependency depth
+  std::vector<int> producer(n_t, -1);
+  int n_stages = 0;
+  for (size_t i = 0; i < ops.size(); ++i) {
+    int depth = 0;
+    for (int t : inputs_of(ops[i]))
+      if (producer[t] >= 0) depth = std::max(depth, ops[producer[t]].stage + 1);
+    // a tensor that is both read and written by the op (accumulator reuse) is an input too
+    ops[i].stage = depth;
+    n_stages = std::max(n_stages, depth + 1);
+    for (int t : outputs_of(ops[i])) producer[t] = static_cast<int>(i);
+  }
+
+  // ---- liveness
+  std::vector<int> def_stage(n_t, -1), last_stage(n_t, -1);
+  for (const FOp& o : ops) {
+    for (int t : outputs_of(o)) {
+      if (def_stage[t] < 0) def_stage[t] = o.stage;
+      last_stage[t] = std::max(last_stage[t], o.stage);
+    }
+    for (int t : inputs_of(o)) {
+      if (def_stage[t] < 0) def_stage[t] = 0;  // produced outside (or cut away by allow-list)
+      last_stage[t] = std::max(last_stage[t], o.stage);
+    }
+  }
+
+  // ---- scratch layout: barrier counter, status, stamps, then f32 tensors
+  uint64_t scratch = kScratchStampsOff + align_up(8ull * (n_stages + 2), 256);
+
+  std::vector<Interval> temp_iv, scratch_iv;
+  for (int t = 0; t < n_t; ++t) {
+    if (def_stage[t] < 0) continue;
+    const FTensor& T = g.tensors[t];
+    Interval iv{t, def_stage[t], last_stage[t], 0, 0};
+    switch (T.kind) {
+      case TKind::ActF16:
+        iv.bytes = align_up(static_cast<uint64_t>(T.rows) * T.ld * 2, 256);
+        temp_iv.push_back(iv);
+        break;
+      case TKind::ActF16T:
+        iv.bytes = align_up(static_cast<uint64_t>(T.batches) * T.cols * T.ld * 2, 256);
+        temp_iv.push_back(iv);
+        break;
+      case TKind::AccF32:
+        iv.bytes = align_up(static_cast<uint64_t>(T.rows) * T.cols * 4, 256);
+        scratch_iv.push_back(iv);
+        break;
+      case TKind::VecF32:
+        iv.bytes = align_up(static_cast<uint64_t>(T.rows) * 4, 256);
+        // the mask bias is produced once and read by every layer
+        scratch_iv.push_back(iv);
+        break;
+      default:
+        break;
+    }
+  }
+  P.temp_bytes = assign_offsets(temp_iv, 0, 256);
+  if (P.temp_bytes == 0) P.temp_bytes = 256;
+  P.scratch_bytes = assign_offsets(scratch_iv, scratch, 256);
+
+  std::vector<BufRef> where(n_t);
+  const int temp_arg = static_cast<int>(P.args.size());
+  {
+    ArgDesc a;
+    a.name = "temp_buffer";
+    a.bytes = P.temp_bytes;
+    a.kind = 2;
+    a.param_number = 0;
+    P.args.push_back(a);
+  }
+  for (const Interval& iv : temp_iv) where[iv.tensor] = BufRef{SPACE_ARG, temp_arg, iv.offset};
+  for (const Interval& iv : scratch_iv) where[iv.tensor] = BufRef{SPACE_SCRATCH, 0, iv.offset};
+  for (int t = 0; t < n_t; ++t)
+    if (g.tensors[t].kind == TKind::Arg) where[t] = BufRef{SPACE_ARG, g.tensors[t].arg_index, 0};
+
+  for (int t = 0; t < n_t; ++t) {
+    const FTensor& T = g.tensors[t];
+    if (def_stage[t] < 0 || T.kind == TKind::Const) continue;
+    TensorPlacement tp;
+    tp.name = T.name;
+    tp.kind = T.kind;
+    tp.at = where[t];
+    tp.rows = T.rows;
+    tp.cols = T.cols;
+    tp.ld = T.ld;
+    tp.batches = T.batches;
+    tp.seq = T.seq;
+    tp.def_stage = def_stage[t];
+    tp.last_stage = last_stage[t];
+    P.tensors.push_back(tp);
+  }
+
+  // ---- constants: RAW bindings are shared, PACK_B bindings are per (constant, n_tile)
+  uint64_t const_top = 0;
+  std::map<std::string, size_t> raw_binding;
+  std::map<std::pair<std::string, uint32_t>, size_t> packed_binding;
+  auto raw_const = [&](int t) -> BufRef {
+    const FTensor& T = g.tensors[t];
+    auto it = raw_binding.find(T.const_name);
+    if (it == raw_binding.end()) {
+      ConstBinding b;
+      b.const_name = T.const_name;
+      b.kind = ConstBinding::RAW;
+      b.bytes = static_cast<uint64_t>(T.rows) * T.cols * T.elem_bytes;
+      b.src_bytes = b.bytes;
+      b.offset = const_top;
+      const_top = align_up(const_top + b.bytes, 256);
+      P.consts.push_back(b);
+      it = raw_binding.emplace(T.const_name, P.consts.size() - 1).first;
+    }
+    return BufRef{SPACE_CONST, 0, P.consts[it->second].offset};
+  };
+
+  // ---- tensor maps
+  std::map<int, uint32_t> act_tmap;  // tensor -> tmap index (box 64 x 128)
+  auto tmap_for_act = [&](int t) -> uint32_t {
+    auto it = act_tmap.find(t);
+    if (it != act_tmap.end()) return it->second;
+    const FTensor& T = g.tensors[t];
+    TmapSpec s;
+    s.base = where[t];
+    s.dim0 = T.cols;
+    s.dim1 = T.rows;
+    s.stride1_bytes = static_cast<uint64_t>(T.ld) * 2;
+    s.box0 = 64;
+    s.box1 = 128;
+    P.tmaps.push_back(s);
+    return act_tmap[t] = static_cast<uint32_t>(P.tmaps.size() - 1);
+  };
+
+  // ---- per stage: count GEMMs to share the CTA budget
+  std::vector<uint32_t> gemms_in_stage(n_stages, 0);
+  for (const FOp& o : ops)
+    if (o.kind == OP_GEMM) gemms_in_stage[o.stage]++;
+
+  // ---- emit ops stage by stage
+  std::vector<std::vector<size_t>> by_stage(n_stages);
+  for (size_t i = 0; i < ops.size(); ++i) by_stage[ops[i].stage].push_back(i);
+
+  for (int s = 0; s < n_stages; ++s) {
+    StageDesc sd{};
+    sd.op_begin = static_cast<uint32_t>(P.ops.size());
+    std::string sname;
+    for (size_t oi : by_stage[s]) {
+      const FOp& o = ops[oi];
+      PlanOp po;
+      po.name = o.name;
+      OpDesc& d = po.d;
+      std::memset(&d, 0, sizeof(d));
+      d.kind = o.kind;
+      d.flags = o.flags;
+      d.act = o.act;
+      d.alpha = o.alpha;
+      d.eps = o.eps;
+      switch (o.kind) {
+        case OP_GEMM: {
+          const FTensor& A = g.tensors[o.a];
+          const FTensor& W = g.tensors[o.w];
+          const FTensor& O = g.tensors[o.out];
+          if (o.K % 64 != 0 || o.N % 16 != 0) {
+            if (err) *err = "GEMM " + o.name + ": K must be a multiple of 64 and N of 16";
+            return MONONN_ERR_UNSUPPORTED;
+          }
+          const bool can_split = (O.kind == TKind::AccF32) && o.act == ACT_NONE;
+          const uint32_t budget = std::max(1u, P.grid / std::max(1u, gemms_in_stage[s]));
+          GemmTileSpec ts;
+          auto it = spec_in.gemm.find(o.name);
+          if (it != spec_in.gemm.end()) ts = it->second;
+          if (ts.n_tile == 0 || ts.k_split == 0 || !tile_legal(o.N, o.K, ts, can_split))
+            ts = default_gemm_tile(o.M, o.N, o.K, can_split, budget);
+          P.spec.gemm[o.name] = ts;
+          d.M = o.M;
+          d.N = o.N;
+          d.K = o.K;
+          d.n_tile = ts.n_tile;
+          d.k_split = ts.k_split;
+          d.m_tiles = (o.M + 127) / 128;
+          d.n_tiles = (o.N + ts.n_tile - 1) / ts.n_tile;
+          const uint32_t kb = o.K / 64;
+          d.kb_per_split = kb / ts.k_split;
+          d.kb_per_bslot = std::max(1u, std::min(d.kb_per_split, kSlotBytes / (ts.n_tile * 128u)));
+          d.n_items = d.m_tiles * d.n_tiles * d.k_split;
+          d.tmap_a = tmap_for_act(o.a);
+          (void)A;
+          // weights: packed per (constant, n_tile)
+          auto key = std::make_pair(W.const_name, ts.n_tile);
+          auto pit = packed_binding.find(key);
+          if (pit == packed_binding.end()) {
+            ConstBinding b;
+            b.const_name = W.const_name;
+            b.kind = ConstBinding::PACK_B;
+            b.K = o.K;
+            b.N = o.N;
+            b.n_tile = ts.n_tile;
+            b.transposed = W.const_transposed;
+            b.src_bytes = static_cast<uint64_t>(o.K) * o.N * 2;
+            b.bytes = static_cast<uint64_t>(d.n_tiles) * ts.n_tile * o.K * 2;
+            b.offset = const_top;
+            const_top = align_up(const_top + b.bytes, 1024);
+            P.consts.push_back(b);
+            pit = packed_binding.emplace(key, P.consts.size() - 1).first;
+          }
+          {
+            const ConstBinding& b = P.consts[pit->second];
+            TmapSpec tm;
+            tm.base = BufRef{SPACE_CONST, 0, b.offset};
+            tm.dim0 = 64;
+            tm.dim1 = static_cast<uint64_t>(d.n_tiles) * kb * ts.n_tile;
+            tm.stride1_bytes = 128;
+            tm.box0 = 64;
+            tm.box1 = ts.n_tile * d.kb_per_bslot;
+            P.tmaps.push_back(tm);
+            d.tmap_b = static_cast<uint32_t>(P.tmaps.size() - 1);
+          }
+          po.p[0] = where[o.out];
+          if (o.bias >= 0) {
+            po.p[1] = raw_const(o.bias);
+            d.flags |= F_BIAS;
+          }
+          if (o.resid >= 0) {
+            po.p[2] = where[o.resid];
+            d.flags |= F_RESID;
+            d.ldr = g.tensors[o.resid].ld;
+            if (g.tensors[o.resid].kind == TKind::AccF32) {
+              d.flags |= F_RESID_F32;
+              d.ldr = g.tensors[o.resid].cols;
+            }
+          }
+          switch (O.kind) {
+            case TKind::ActF16:
+              d.out_mode = OUT_F16;
+              d.ldo = O.ld;
+              break;
+            case TKind::ActF16T:
+              d.out_mode = OUT_F16_T;
+              d.rows_per_batch = O.seq;
+              d.ldt = O.ld;
+              break;
+            case TKind::AccF32:
+              d.out_mode = OUT_F32_RED;
+              d.ldo = O.cols;
+              break;
+            case TKind::Arg:
+              d.out_mode = O.elem_bytes == 4 ? OUT_F32 : OUT_F16;
+              d.ldo = O.ld;
+              break;
+            default:
+              if (err) *err = "GEMM " + o.name + ": unsupported output tensor kind";
+              return MONONN_ERR_UNSUPPORTED;
+          }
+          P.algorithmic_flops += 2.0 * o.M * o.N * o.K;
+          break;
+        }
+        case OP_ATTENTION: {
+          if (o.head_dim != 64 || o.seq > 128) {
+            if (err) *err = "attention " + o.name + ": head_dim must be 64 and seq <= 128";
+            return MONONN_ERR_UNSUPPORTED;
+          }
+          d.heads = o.heads;
+          d.seq = o.seq;
+          d.batches = o.batches;
+          d.head_dim = o.head_dim;
+          d.q_col = o.q_col;
+          d.k_col = o.k_col;
+          d.tmap_a = tmap_for_act(o.q);
+          d.tmap_b = tmap_for_act(o.k);
+          {
+            const FTensor& VT = g.tensors[o.vt];
+            TmapSpec tm;
+            tm.base = where[o.vt];
+            tm.dim0 = VT.seq;
+            tm.dim1 = static_cast<uint64_t>(VT.batches) * VT.cols;
+            tm.stride1_bytes = static_cast<uint64_t>(VT.ld) * 2;
+            tm.box0 = 64;
+            tm.box1 = 64;
+            P.tmaps.push_back(tm);
+            d.tmap_vt = static_cast<uint32_t>(P.tmaps.size() - 1);
+          }
+          d.n_items = o.batches * o.heads * ((o.seq + 127) / 128);
+          d.ldo = g.tensors[o.out].ld;
+          po.p[0] = where[o.out];
+          if (o.mask >= 0) {
+            po.p[1] = where[o.mask];
+            d.flags |= F_MASK_BIAS;
+          }
+          P.algorithmic_flops += 2.0 * 2.0 * o.seq * o.seq * o.head_dim * o.heads * o.batches;
+          break;
+        }
+        case OP_LAYERNORM: {
+          const FTensor& S = g.tensors[o.src];
+          d.rows = o.rows;
+          d.cols = o.cols;
+          if (o.cols % 4 != 0 || o.cols > 2048) {
+            if (err) *err = "layernorm " + o.name + ": row length must be <= 2048 and a multiple of 4";
+            return MONONN_ERR_UNSUPPORTED;
+          }
+          d.n_items = (o.rows + 3) / 4;
+          po.p[0] = where[o.out];
+          d.ldo = g.tensors[o.out].ld;
+          po.p[1] = where[o.src];
+          if (S.kind == TKind::AccF32) {
+            d.flags |= F_SRC_F32;
+            d.lds = S.cols;
+          } else {
+            d.lds = S.ld;
+          }
+          po.p[2] = raw_const(o.gamma);
+          po.p[3] = raw_const(o.beta);
+          if (o.resid >= 0) {
+            po.p[4] = where[o.resid];
+            d.flags |= F_RESID;
+            d.ldr = g.tensors[o.resid].ld;
+          }
+          break;
+        }
+        case OP_EMBED: {
+          d.rows = o.rows;
+          d.cols = o.cols;
+          d.seq = o.seq;
+          d.vocab = o.vocab;
+          if (o.cols % 4 != 0 || o.cols > 2048) {
+            if (err) *err = "embed " + o.name + ": row length must be <= 2048 and a multiple of 4";
+            return MONONN_ERR_UNSUPPORTED;
+          }
+          d.n_items = (o.rows + 3) / 4;
+          po.p[0] = where[o.out];
+          d.ldo = g.tensors[o.out].ld;
+          po.p[1] = where[o.ids];
+          po.p[3] = raw_const(o.word);
+          po.p[4] = raw_const(o.pos);
+          if (o.type_ids >= 0 && o.type >= 0) {
+            po.p[2] = where[o.type_ids];
+            po.p[5] = raw_const(o.type);
+            d.flags |= F_TYPE_IDS;
+          }
+          po.p[6] = raw_const(o.gamma);
+          po.p[7] = raw_const(o.beta);
+          if (o.mask_in >= 0 && o.mask_out >= 0) {
+            po.q[0] = where[o.mask_in];
+            po.q[1] = where[o.mask_out];
+            d.flags |= F_MASK_BIAS;
+          }
+          break;
+        }
+        default:
+          if (err) *err = "operator " + o.name + ": unknown kind";
+          return MONONN_ERR_UNSUPPORTED;
+      }
+      sd.n_items += d.n_items;
+      if (!sname.empty()) sname += "+";
+      sname += o.name;
+      P.ops.push_back(po);
+    }
+    sd.op_count = static_cast<uint32_t>(P.ops.size()) - sd.op_begin;
+    P.stages.push_back(sd);
+    P.stage_names.push_back(sname);
+  }
+  P.const_bytes = std::max<uint64_t>(const_top, 256);
+
+  // ---- algorithmic bytes: every constant once, except gathered tables (rows touched only)
+  std::set<std::string> gathered;
+  for (const FOp& o : ops)
+    if (o.kind == OP_EMBED) {
+      for (int t : {o.word, o.pos, o.type})
+        if (t >= 0) gathered.insert(g.tensors[t].const_name);
+      P.algorithmic_bytes += 2.0 * o.rows * o.cols;                 // word rows
+      P.algorithmic_bytes += 2.0 * std::min(o.rows, o.seq) * o.cols;  // position rows
+      if (o.type >= 0) P.algorithmic_bytes += 2.0 * o.cols;           // one type row
+    }
+  std::set<std::string> counted;
+  for (const ConstBinding& b : P.consts) {
+    if (gathered.count(b.const_name) || counted.count(b.const_name)) continue;
+    counted.insert(b.const_name);
+    P.algorithmic_bytes += static_cast<double>(b.src_bytes);
+  }
+  for (const ArgDesc& a : P.args)
+    if (a.kind != 2) P.algorithmic_bytes += static_cast<double>(a.bytes);
+  return MONONN_OK;
+}
+
+}  // namespace mononn

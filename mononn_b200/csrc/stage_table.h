@@ -1,0 +1,129 @@
+// Stage table shared by the host lowering and the persistent sm_100a kernel.
+//
+// The reference emits one CUDA source per graph: per-node device functions in
+// wave-front order with a grid barrier at every depth boundary
+// (mononn_engine/codegen/graph_codegen.cc:768-800).  Here the same structure
+// is data: a list of stages (one per barrier depth), each holding a span of
+// operator descriptors whose work items are dealt round-robin to the CTAs of
+// one cooperative launch.
+#pragma once
+#include <stdint.h>
+
+namespace mononn {
+
+enum OpKind : uint32_t {
+  OP_NONE = 0,
+  OP_GEMM = 1,       // tcgen05 GEMM, 128-row tiles, fused epilogue
+  OP_ATTENTION = 2,  // per (batch, head, 128 query rows): QK^T -> softmax -> PV
+  OP_LAYERNORM = 3,  // row-wise LayerNorm over an f32 or f16 source
+  OP_EMBED = 4,      // row gather + position + type + LayerNorm, mask bias
+  OP_L2NORM_LOGITS = 5,
+};
+
+enum ActKind : uint32_t {
+  ACT_NONE = 0,
+  ACT_GELU_ERF = 1,
+  ACT_RELU = 2,
+  ACT_QUICK_GELU = 3,
+  ACT_GELU_TANH = 4,
+};
+
+enum OutMode : uint32_t {
+  OUT_F16 = 0,      // out[row*ldo + col] = half(v)
+  OUT_F16_T = 1,    // out[batch][col][row_in_batch] = half(v)  (V^T for attention)
+  OUT_F32_RED = 2,  // red.add into f32 out[row*ldo + col] (split-K partials)
+  OUT_F32 = 3,      // out[row*ldo + col] = v
+};
+
+enum OpFlags : uint32_t {
+  F_BIAS = 1u << 0,
+  F_RESID = 1u << 1,       // residual add (f16 source)
+  F_ZERO_SRC = 1u << 2,    // LayerNorm: clear the f32 source after reading it
+  F_CAUSAL = 1u << 3,      // attention: key index > query index is masked
+  F_MASK_BIAS = 1u << 4,   // attention: additive f32 bias per (batch, key)
+  F_SRC_F32 = 1u << 5,     // LayerNorm source is f32 (else f16)
+  F_TYPE_IDS = 1u << 6,    // embed: token-type table present
+  F_OUT2_F16 = 1u << 7,    // LayerNorm: also write the un-normalised sum as f16
+  F_RESID_F32 = 1u << 8,   // residual source is f32
+};
+
+// Pointer slots p[0..7]; meaning per kind:
+//  GEMM:      0 out, 1 bias(f16), 2 resid
+//  ATTENTION: 0 out ctx(f16), 1 mask bias(f32 [B,S])
+//  LAYERNORM: 0 out(f16), 1 src, 2 gamma(f16), 3 beta(f16), 4 resid(f16, optional), 5 out2
+//  EMBED:     0 out(f16), 1 ids(i32), 2 type ids(i32), 3 word table(f16), 4 pos table(f16),
+//             5 type table(f16), 6 gamma, 7 beta ; mask(i32) -> q[0], mask bias out(f32) -> q[1]
+struct alignas(16) OpDesc {
+  uint32_t kind;
+  uint32_t flags;
+  uint32_t n_items;  // work items of this op
+  uint32_t act;
+  // GEMM geometry
+  uint32_t tmap_a, tmap_b;  // tensor-map indices
+  uint32_t m_tiles, n_tiles, k_split, kb_per_split;  // kb = 64-element k block
+  uint32_t n_tile;          // UMMA N (multiple of 16, <= 256)
+  uint32_t kb_per_bslot;    // k blocks fetched per weight-ring slot
+  uint32_t M, N, K;         // valid extents
+  uint32_t out_mode;
+  uint32_t ldo, ldr;        // leading dims (elements) of out / resid
+  uint32_t rows_per_batch;  // OUT_F16_T: rows per batch (sequence length)
+  uint32_t ldt;             // OUT_F16_T: leading dim of the transposed output
+  float alpha;
+  float eps;
+  // attention geometry
+  uint32_t heads, seq, batches, head_dim;
+  uint32_t q_col, k_col;    // column offsets of Q and K inside the tmap_a tensor
+  uint32_t tmap_vt;         // tensor map over V^T [batches*heads*head_dim, seq]
+  uint32_t cols;            // row length for row-wise ops
+  uint32_t rows;            // row count for row-wise ops
+  uint32_t lds;             // leading dim of row-wise source
+  uint32_t vocab;           // embed: word-table rows (ids are not clamped, as in the reference)
+  uint32_t pad0;
+  uint64_t p[8];
+  uint64_t q[2];
+};
+
+struct alignas(16) StageDesc {
+  uint32_t op_begin;
+  uint32_t op_count;
+  uint32_t n_items;  // sum over the ops
+  uint32_t flags;
+};
+
+// Status word written by the kernel when a bounded wait expires.
+struct KernelStatus {
+  uint32_t code;   // 0 ok
+  uint32_t stage;
+  uint32_t cta;
+  uint32_t where;  // which wait gave up
+};
+
+enum StatusCode : uint32_t {
+  ST_OK = 0,
+  ST_GRID_BARRIER_TIMEOUT = 1,
+  ST_MBARRIER_TIMEOUT = 2,
+};
+
+// Shared-memory ring geometry (bytes).
+constexpr uint32_t kSlotBytes = 16384;  // one 128x64 f16 operand tile
+constexpr uint32_t kASlots = 6;
+constexpr uint32_t kBSlots = 7;
+constexpr uint32_t kThreads = 256;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kAccCols = 256;  // two accumulator buffers of 256 columns
+
+struct KernelParams {
+  const StageDesc* stages;
+  const OpDesc* ops;
+  const void* tmaps;     // CUtensorMap[]
+  uint32_t* barrier;     // monotonically increasing arrival counter
+  KernelStatus* status;
+  uint64_t* stamps;      // optional per-stage %globaltimer stamps (CTA 0), or null
+  uint32_t n_stages;
+  uint32_t epoch_base;   // counter value at kernel entry
+  uint32_t timeout_us;   // bound on every wait
+  uint32_t stage_begin;  // run stages [stage_begin, stage_end)
+  uint32_t stage_end;
+};
+
+}  // namespace mononn

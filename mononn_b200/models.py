@@ -1,0 +1,105 @@
+"""Model configurations and seeded synthetic weights / inputs.
+
+The reference exports its example graphs from HuggingFace checkpoints
+(examples/utils/save_model.py:44-110).  No checkpoint or dataset is reachable here, so
+every tensor is synthetic: weights ~ N(0, 0.02) as HF initialises them, inputs drawn
+from ``numpy.random.default_rng(seed)``.  The *stress* variant also randomises biases and
+LayerNorm scale/shift so every fused epilogue term is observable in a parity test.
+"""
+from __future__ import annotations
+
+import dataclasses
+import json
+
+import numpy as np
+
+
+@dataclasses.dataclass
+class EncoderConfig:
+    model: str = "bert"
+    name: str = "cluster_0"
+    layers: int = 12
+    hidden: int = 768
+    heads: int = 12
+    ffn: int = 3072
+    vocab: int = 30522
+    max_pos: int = 512
+    types: int = 2
+    batch: int = 1
+    seq: int = 128
+    eps: float = 1e-12
+    act: str = "gelu_erf"
+
+    def to_json(self) -> str:
+        return json.dumps(dataclasses.asdict(self))
+
+    @property
+    def tokens(self) -> int:
+        return self.batch * self.seq
+
+
+def bert_base(batch: int = 1, seq: int = 128) -> EncoderConfig:
+    """BERT-base encoder: the headline configuration (b1, s128)."""
+    return EncoderConfig(batch=batch, seq=seq)
+
+
+def bert_tiny(batch: int = 1, seq: int = 16, layers: int = 1, hidden: int = 64, ffn: int = 256,
+              vocab: int = 100, max_pos: int = 64) -> EncoderConfig:
+    """Small shape for element-wise parity checks (one layer, hidden 64)."""
+    return EncoderConfig(layers=layers, hidden=hidden, heads=hidden // 64, ffn=ffn, vocab=vocab,
+                         max_pos=max_pos, batch=batch, seq=seq)
+
+
+def bert_weight_shapes(cfg: EncoderConfig) -> dict[str, tuple[int, ...]]:
+    h, f = cfg.hidden, cfg.ffn
+    shapes: dict[str, tuple[int, ...]] = {
+        "embeddings.word": (cfg.vocab, h),
+        "embeddings.position": (cfg.max_pos, h),
+        "embeddings.token_type": (cfg.types, h),
+        "embeddings.ln.gamma": (h,),
+        "embeddings.ln.beta": (h,),
+    }
+    for l in range(cfg.layers):
+        p = f"layer{l}."
+        for n in ("q", "k", "v", "o"):
+            shapes[p + f"attn.{n}.w"] = (h, h)
+            shapes[p + f"attn.{n}.b"] = (h,)
+        shapes[p + "attn.ln.gamma"] = (h,)
+        shapes[p + "attn.ln.beta"] = (h,)
+        shapes[p + "ffn.up.w"] = (h, f)
+        shapes[p + "ffn.up.b"] = (f,)
+        shapes[p + "ffn.down.w"] = (f, h)
+        shapes[p + "ffn.down.b"] = (h,)
+        shapes[p + "ffn.ln.gamma"] = (h,)
+        shapes[p + "ffn.ln.beta"] = (h,)
+    return shapes
+
+
+def make_weights(cfg: EncoderConfig, seed: int = 1234, stress: bool = False) -> dict[str, np.ndarray]:
+    """fp32 weights, already rounded to fp16-representable values so that the fp16 device
+    copy and the fp32 CPU copy hold the same numbers.  Linear weights are [in, out]."""
+    rng = np.random.default_rng(seed)
+    out: dict[str, np.ndarray] = {}
+    for name, shape in bert_weight_shapes(cfg).items():
+        if name.endswith(".gamma"):
+            w = np.ones(shape, np.float32)
+            if stress:
+                w += rng.normal(0.0, 0.02, shape).astype(np.float32)
+        elif name.endswith(".beta") or name.endswith(".b"):
+            w = rng.normal(0.0, 0.02, shape).astype(np.float32) if stress else np.zeros(shape, np.float32)
+        else:
+            w = rng.normal(0.0, 0.02, shape).astype(np.float32)
+        out[name] = w.astype(np.float16).astype(np.float32)
+    return out
+
+
+def make_inputs(cfg: EncoderConfig, seed: int = 1234, pad_fraction: float = 0.0) -> dict[str, np.ndarray]:
+    """Token ids uniform over the vocabulary, type ids 0, mask all ones (or the trailing
+    `pad_fraction` of every sequence zeroed)."""
+    rng = np.random.default_rng(seed + 7919)
+    ids = rng.integers(0, cfg.vocab, (cfg.batch, cfg.seq), dtype=np.int32)
+    mask = np.ones((cfg.batch, cfg.seq), np.int32)
+    if pad_fraction > 0:
+        mask[:, cfg.seq - int(cfg.seq * pad_fraction):] = 0
+    types = np.zeros((cfg.batch, cfg.seq), np.int32)
+    return {"input_ids": ids, "attention_mask": mask, "token_type_ids": types}

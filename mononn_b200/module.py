@@ -1,0 +1,203 @@
+"""Host-side mirror of the reference's module interface on top of the C ABI.
+
+``Module`` corresponds to MonoNNModule (mononn_engine/module/mononn_module.h:31-87):
+arguments in the order (parameters.., live-outs.., temp), launch configuration from the
+tuning spec, one launch per inference.  PyTorch is used only as the owner of device
+memory and streams.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import json
+import os
+
+import numpy as np
+
+from . import capi
+from .capi import ArgDesc, Options, check, lib
+
+
+def _options(device=0, dump_dir=None, spec_dir=None, threadpool_size=0, tuning_level=0,
+             barrier_timeout_us=0) -> Options:
+    o = Options()
+    o.device = device
+    o.dump_dir = dump_dir.encode() if dump_dir else None
+    o.spec_dir = spec_dir.encode() if spec_dir else None
+    o.threadpool_size = threadpool_size
+    o.tuning_level = tuning_level
+    o.barrier_timeout_us = barrier_timeout_us
+    return o
+
+
+class Module:
+    def __init__(self, handle: C.c_void_p, device: int = 0):
+        self._h = handle
+        self.device = device
+        self._bufs = None
+        self._ptrs = None
+
+    # ------------------------------------------------------------------ metadata
+    def args(self) -> list[dict]:
+        descs = C.POINTER(ArgDesc)()
+        n = C.c_int()
+        check(lib().mononn_module_args(self._h, C.byref(descs), C.byref(n)))
+        return [dict(index=descs[i].index, bytes=descs[i].bytes, kind=descs[i].kind,
+                     param_number=descs[i].param_number) for i in range(n.value)]
+
+    def launch_config(self) -> dict:
+        g, b, s = (C.c_uint * 3)(), (C.c_uint * 3)(), C.c_uint()
+        check(lib().mononn_module_launch_config(self._h, C.byref(g), C.byref(b), C.byref(s)))
+        return dict(grid=tuple(g), block=tuple(b), smem_bytes=s.value)
+
+    def constants(self) -> dict[str, int]:
+        n = C.c_int()
+        check(lib().mononn_constant_count(self._h, C.byref(n)))
+        out = {}
+        for i in range(n.value):
+            name, size = C.c_char_p(), C.c_size_t()
+            check(lib().mononn_constant_info(self._h, i, C.byref(name), C.byref(size)))
+            out[name.value.decode()] = size.value
+        return out
+
+    def cost(self) -> tuple[float, float]:
+        b, f = C.c_double(), C.c_double()
+        check(lib().mononn_module_cost(self._h, C.byref(b), C.byref(f)))
+        return b.value, f.value
+
+    def spec(self) -> dict:
+        p = C.c_char_p()
+        check(lib().mononn_spec_json(self._h, C.byref(p)))
+        return json.loads(p.value.decode())
+
+    def plan(self) -> dict:
+        p = C.c_char_p()
+        check(lib().mononn_plan_json(self._h, C.byref(p)))
+        return json.loads(p.value.decode())
+
+    def launch_stages(self, begin: int, end: int, stream=None) -> None:
+        """Single-stage isolation: run stages [begin, end) in one launch."""
+        if self._ptrs is None:
+            self.allocate()
+        check(lib().mononn_launch_stages(self._h, self._ptrs, len(self._bufs), self._stream(stream), begin, end))
+
+    def save_spec(self, directory: str) -> None:
+        check(lib().mononn_save_spec(self._h, directory.encode()))
+
+    # ----------------------------------------------------------------- constants
+    def set_constant(self, name: str, array: np.ndarray) -> None:
+        a = np.ascontiguousarray(array)
+        check(lib().mononn_set_constant(self._h, name.encode(), a.ctypes.data_as(C.c_void_p), a.nbytes))
+
+    def set_weights(self, weights: dict[str, np.ndarray]) -> None:
+        """fp32 weight dict -> fp16 constants, by name."""
+        for name in self.constants():
+            self.set_constant(name, np.asarray(weights[name]).astype(np.float16))
+
+    # ------------------------------------------------------------------- buffers
+    def allocate(self):
+        """Device buffers for every kernel argument (torch owns the memory)."""
+        import torch
+        dev = torch.device("cuda", self.device)
+        self._bufs = [torch.zeros(max(a["bytes"], 16), dtype=torch.uint8, device=dev) for a in self.args()]
+        self._ptrs = (C.c_void_p * len(self._bufs))(*[b.data_ptr() for b in self._bufs])
+        return self._bufs
+
+    @property
+    def buffers(self):
+        if self._bufs is None:
+            self.allocate()
+        return self._bufs
+
+    def _stream(self, stream) -> C.c_void_p:
+        import torch
+        s = stream if stream is not None else torch.cuda.current_stream(self.device)
+        return C.c_void_p(s.cuda_stream)
+
+    def launch(self, stream=None) -> None:
+        """Exactly one kernel launch on `stream` (default: torch's current stream)."""
+        if self._ptrs is None:
+            self.allocate()
+        check(lib().mononn_launch(self._h, self._ptrs, len(self._bufs), self._stream(stream)))
+
+    def status(self) -> None:
+        st, cta = C.c_int(), C.c_int()
+        check(lib().mononn_last_status(self._h, C.byref(st), C.byref(cta)))
+
+    def tune(self, stream=None) -> None:
+        if self._ptrs is None:
+            self.allocate()
+        check(lib().mononn_tune(self._h, self._ptrs, len(self._bufs), self._stream(stream)))
+
+    def profile_stages(self, stream=None) -> list[tuple[str, float]]:
+        if self._ptrs is None:
+            self.allocate()
+        cap = 4096
+        us = (C.c_double * cap)()
+        names = (C.c_char_p * cap)()
+        n = C.c_int()
+        check(lib().mononn_profile_stages(self._h, self._ptrs, len(self._bufs), self._stream(stream),
+                                          us, names, cap, C.byref(n)))
+        return [(names[i].decode(), us[i]) for i in range(min(n.value, cap))]
+
+    # ---------------------------------------------------------------- inference
+    def run(self, inputs: list[np.ndarray]) -> list[np.ndarray]:
+        """Host arrays in (by parameter number) -> host arrays out (live-outs, raw bytes
+        viewed as fp16).  Copies are on torch's current stream around the single launch."""
+        import torch
+        bufs = self.buffers
+        descs = self.args()
+        params = [d for d in descs if d["kind"] == 0]
+        for d, x in zip(sorted(params, key=lambda d: d["param_number"]), inputs):
+            src = torch.from_numpy(np.ascontiguousarray(x)).view(torch.uint8).reshape(-1)
+            bufs[d["index"]][: src.numel()].copy_(src, non_blocking=True)
+        self.launch()
+        outs = [bufs[d["index"]].cpu().numpy().view(np.float16) for d in descs if d["kind"] == 1]
+        self.status()
+        return outs
+
+    def close(self) -> None:
+        if self._h:
+            lib().mononn_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def compile_encoder(cfg, kernel_name: str | None = None, **opts) -> Module:
+    """Standalone path: fused graph from an encoder configuration."""
+    h = C.c_void_p()
+    o = _options(**opts)
+    check(lib().mononn_compile_encoder_json(cfg.to_json().encode(), kernel_name.encode() if kernel_name else None,
+                                            C.byref(o), C.byref(h)))
+    return Module(h, o.device)
+
+
+def compile_hlo(hlo_text: str, kernel_name: str | None = None, **opts) -> Module:
+    """Hook path: post-optimisation XLA HLO text of a cluster -> module."""
+    h = C.c_void_p()
+    o = _options(**opts)
+    data = hlo_text.encode()
+    check(lib().mononn_compile_hlo_text(data, len(data), kernel_name.encode() if kernel_name else None,
+                                        C.byref(o), C.byref(h)))
+    return Module(h, o.device)
+
+
+def describe(kind: str, text: str, spec: dict | None = None, sm_count: int = 148) -> dict:
+    """Lower without a device: {"plan": ..., "spec": ...} for an HLO text or encoder JSON."""
+    out = C.c_void_p()
+    data = text.encode()
+    check(lib().mononn_describe(kind.encode(), data, len(data), json.dumps(spec).encode() if spec else None,
+                                sm_count, C.byref(out)))
+    try:
+        return json.loads(C.string_at(out).decode())
+    finally:
+        lib().mononn_free_string(out)
+
+
+def enabled() -> bool:
+    """TF_MONONN_ENABLED truthiness (True / true / 1)."""
+    return bool(lib().mononn_enabled())

@@ -1,0 +1,137 @@
+"""CPU fp32 restatement of the encoder graphs on the hot path.  TEST INFRASTRUCTURE ONLY:
+imported by tests/, by ``__graft_entry__.smoke()`` and by ``bench.py``'s CPU-baseline leg,
+never by the product path.
+
+Parity status: UNPINNED by the reference.  The reference holds no golden outputs, no
+known-answer tests and no weights for this path (its only fixture is the input file
+examples/data/bert_bs1.npy), and its TF-XLA CPU execution cannot run here (TensorFlow 2.9
+and both submodules are absent).  The restatement is instead pinned against the
+`transformers` PyTorch BertModel on identical weights (tests/golden/make_golden.py).
+
+What it follows:
+  * graph and I/O signature: examples/utils/save_model.py:44-54 (BERT: int32 input_ids,
+    attention_mask, token_type_ids of shape [B, S]); the output is the last hidden state.
+  * GEMM semantics alpha*op(A)*op(B): mononn_engine/core/op_impl/gemm_impl.cc:233-469.
+  * reduce semantics (one reduced dimension, row-wise): core/op/cluster_reduce.cc:72-84.
+  * gather without clamping: mononn_engine/core/context/index_tracer.cc:235-280.
+  * architecture math (public BERT definition): embeddings = word + position + type -> LN;
+    post-LN blocks; attention scale 1/sqrt(64) with additive mask (1 - m) * -10000;
+    exact-erf GELU; LayerNorm eps 1e-12 with biased variance.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+
+
+def _erf(x: np.ndarray) -> np.ndarray:
+    try:
+        from scipy.special import erf
+        return erf(x).astype(x.dtype)
+    except Exception:  # pragma: no cover - scipy is present in the image
+        return np.vectorize(math.erf)(x).astype(x.dtype)
+
+
+def layer_norm(x: np.ndarray, gamma: np.ndarray, beta: np.ndarray, eps: float) -> np.ndarray:
+    mean = x.mean(-1, keepdims=True, dtype=np.float64)
+    var = ((x - mean) ** 2).mean(-1, keepdims=True, dtype=np.float64)
+    return (((x - mean) / np.sqrt(var + eps)) * gamma + beta).astype(np.float32)
+
+
+def gelu_erf(x: np.ndarray) -> np.ndarray:
+    return (0.5 * x * (1.0 + _erf(x * np.float32(0.7071067811865476)))).astype(np.float32)
+
+
+def activation(x: np.ndarray, kind: str) -> np.ndarray:
+    if kind == "gelu_erf":
+        return gelu_erf(x)
+    if kind == "relu":
+        return np.maximum(x, 0)
+    if kind == "quick_gelu":
+        return (x / (1.0 + np.exp(-1.702 * x))).astype(np.float32)
+    if kind == "gelu_tanh":
+        return (0.5 * x * (1 + np.tanh(0.7978845608028654 * (x + 0.044715 * x ** 3)))).astype(np.float32)
+    if kind == "none":
+        return x
+    raise ValueError(kind)
+
+
+def softmax_rows(z: np.ndarray) -> np.ndarray:
+    z = z - z.max(-1, keepdims=True)
+    e = np.exp(z)
+    return (e / e.sum(-1, keepdims=True)).astype(np.float32)
+
+
+def attention(q, k, v, mask_bias, heads, causal=False):
+    """q, k, v: [B, S, H]; mask_bias: [B, S] additive or None.  Returns [B, S, H]."""
+    b, s, h = q.shape
+    d = h // heads
+    split = lambda t: t.reshape(b, s, heads, d).transpose(0, 2, 1, 3)
+    qh, kh, vh = split(q), split(k), split(v)
+    scores = np.matmul(qh, kh.transpose(0, 1, 3, 2)) * np.float32(1.0 / math.sqrt(d))
+    if mask_bias is not None:
+        scores = scores + mask_bias[:, None, None, :]
+    if causal:
+        scores = scores + np.triu(np.full((s, s), -1e30, np.float32), 1)
+    p = softmax_rows(scores)
+    ctx = np.matmul(p, vh)
+    return ctx.transpose(0, 2, 1, 3).reshape(b, s, h)
+
+
+def bert_embeddings(cfg, w, ids, types):
+    pos = np.arange(cfg.seq)
+    x = w["embeddings.word"][ids] + w["embeddings.position"][pos][None] + w["embeddings.token_type"][types]
+    return layer_norm(x.astype(np.float32), w["embeddings.ln.gamma"], w["embeddings.ln.beta"], cfg.eps)
+
+
+def bert_layer(cfg, w, x, mask_bias, l):
+    p = f"layer{l}."
+    lin = lambda t, n: t @ w[p + n + ".w"] + w[p + n + ".b"]
+    q, k, v = lin(x, "attn.q"), lin(x, "attn.k"), lin(x, "attn.v")
+    ctx = attention(q, k, v, mask_bias, cfg.heads)
+    x1 = layer_norm(lin(ctx, "attn.o") + x, w[p + "attn.ln.gamma"], w[p + "attn.ln.beta"], cfg.eps)
+    hmid = activation(lin(x1, "ffn.up"), cfg.act)
+    return layer_norm(lin(hmid, "ffn.down") + x1, w[p + "ffn.ln.gamma"], w[p + "ffn.ln.beta"], cfg.eps)
+
+
+def bert_encoder(cfg, w, inputs, return_all=False):
+    """fp32 forward.  Returns the last hidden state [B*S, H] (the live-out of the module)."""
+    ids, mask, types = inputs["input_ids"], inputs["attention_mask"], inputs["token_type_ids"]
+    mask_bias = (1.0 - mask.astype(np.float32)) * np.float32(-10000.0)
+    x = bert_embeddings(cfg, w, ids, types)
+    hidden = [x]
+    for l in range(cfg.layers):
+        x = bert_layer(cfg, w, x, mask_bias, l)
+        hidden.append(x)
+    out = x.reshape(cfg.batch * cfg.seq, cfg.hidden)
+    return (out, hidden) if return_all else out
+
+
+def bert_encoder_torch(cfg, w, inputs, threads=0):
+    """Same math through torch CPU ops (multi-threaded); the timed CPU baseline."""
+    import torch
+    import torch.nn.functional as F
+    if threads:
+        torch.set_num_threads(threads)
+    tw = {k: torch.from_numpy(v) for k, v in w.items()}
+    ids = torch.from_numpy(inputs["input_ids"]).long()
+    types = torch.from_numpy(inputs["token_type_ids"]).long()
+    mask = torch.from_numpy(inputs["attention_mask"]).float()
+    mask_bias = (1.0 - mask) * -10000.0
+    b, s, h, nh = cfg.batch, cfg.seq, cfg.hidden, cfg.heads
+    with torch.no_grad():
+        x = tw["embeddings.word"][ids] + tw["embeddings.position"][:s][None] + tw["embeddings.token_type"][types]
+        x = F.layer_norm(x, (h,), tw["embeddings.ln.gamma"], tw["embeddings.ln.beta"], cfg.eps)
+        for l in range(cfg.layers):
+            p = f"layer{l}."
+            lin = lambda t, n: t @ tw[p + n + ".w"] + tw[p + n + ".b"]
+            split = lambda t: t.view(b, s, nh, h // nh).transpose(1, 2)
+            q, k, v = split(lin(x, "attn.q")), split(lin(x, "attn.k")), split(lin(x, "attn.v"))
+            sc = q @ k.transpose(-1, -2) / math.sqrt(h // nh) + mask_bias[:, None, None, :]
+            ctx = (torch.softmax(sc, -1) @ v).transpose(1, 2).reshape(b, s, h)
+            x = F.layer_norm(lin(ctx, "attn.o") + x, (h,), tw[p + "attn.ln.gamma"], tw[p + "attn.ln.beta"], cfg.eps)
+            y = lin(x, "ffn.up")
+            y = F.gelu(y) if cfg.act == "gelu_erf" else torch.relu(y)
+            x = F.layer_norm(lin(y, "ffn.down") + x, (h,), tw[p + "ffn.ln.gamma"], tw[p + "ffn.ln.beta"], cfg.eps)
+    return x.reshape(b * s, h).numpy()
