@@ -136,6 +136,18 @@ void mononn_free_string(char* s);
 int mononn_launch_stages(mononn_module* m, void* const* device_args, int n, void* cuda_stream,
                          unsigned stage_begin, unsigned stage_end);
 
+/* Per-CTA event trace of one launch: out[(cta * n_stages + stage) * 16 + event] in
+ * nanoseconds since the earliest event (0 = event did not occur). Events: 0 epilogue warps
+ * passed the previous barrier, 1 finished the stage's items, 2 arrived at the barrier,
+ * 3 activation producer passed the barrier, 4 issued its last activation load, 5 MMA issuer
+ * saw its first operands, 6 committed its last MMA, 7 weight producer issued its last load,
+ * 8..15 finer marks inside the epilogue / row-wise code.
+ * This is how the barrier's share of kernel time is measured without a profiler
+ * (the reference's performance_report.csv isolates nodes instead,
+ * mononn_engine/module/mononn_module_tuner.cc:422-448). cap counts doubles. */
+int mononn_trace_stages(mononn_module* m, void* const* device_args, int n, void* cuda_stream,
+                        double* out, size_t cap, int* grid, int* n_stages);
+
 /* Algorithmic bytes and FLOPs of one inference (weights once + gathered rows + I/O). */
 int mononn_module_cost(const mononn_module* m, double* bytes, double* flops);
 

@@ -17,7 +17,7 @@ EXPORTS = [
     "mononn_constant_info", "mononn_launch", "mononn_last_status", "mononn_tune",
     "mononn_save_spec", "mononn_spec_json", "mononn_profile_stages", "mononn_module_cost",
     "mononn_destroy", "mononn_strerror", "mononn_last_error", "mononn_enabled",
-    "mononn_plan_json", "mononn_describe", "mononn_free_string", "mononn_launch_stages",
+    "mononn_trace_stages", "mononn_plan_json", "mononn_describe", "mononn_free_string", "mononn_launch_stages",
 ]
 
 
@@ -66,6 +66,7 @@ def lib() -> C.CDLL:
         l.mononn_profile_stages.argtypes = [vp, C.POINTER(vp), C.c_int, vp, C.POINTER(C.c_double),
                                             C.POINTER(cp), C.c_int, ip]
         l.mononn_module_cost.argtypes = [vp, C.POINTER(C.c_double), C.POINTER(C.c_double)]
+        l.mononn_trace_stages.argtypes = [vp, C.POINTER(vp), C.c_int, vp, C.POINTER(C.c_double), C.c_size_t, ip, ip]
         l.mononn_plan_json.argtypes = [vp, C.POINTER(cp)]
         l.mononn_describe.argtypes = [cp, cp, C.c_size_t, cp, C.c_uint, C.POINTER(vp)]
         l.mononn_free_string.argtypes = [vp]

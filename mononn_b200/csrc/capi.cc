@@ -273,6 +273,19 @@ int mononn_describe(const char* kind, const char* text, size_t len, const char* 
 
 void mononn_free_string(char* s) { std::free(s); }
 
+int mononn_trace_stages(mononn_module* m, void* const* device_args, int n, void* cuda_stream,
+                        double* out, size_t cap, int* grid, int* n_stages) {
+  if (!m || !device_args || !out) return fail(MONONN_ERR_INVALID_ARGUMENT, "null argument");
+  std::vector<double> t;
+  int rc = m->rt.trace_launch(device_args, n, cuda_stream, &t);
+  if (rc) return rc;
+  if (grid) *grid = static_cast<int>(m->rt.plan().grid);
+  if (n_stages) *n_stages = static_cast<int>(m->rt.plan().stages.size());
+  if (t.size() > cap) return fail(MONONN_ERR_TOO_LARGE, "trace buffer too small");
+  std::memcpy(out, t.data(), t.size() * sizeof(double));
+  return MONONN_OK;
+}
+
 int mononn_module_cost(const mononn_module* m, double* bytes, double* flops) {
   if (!m) return fail(MONONN_ERR_INVALID_ARGUMENT, "null argument");
   if (bytes) *bytes = m->rt.plan().algorithmic_bytes;

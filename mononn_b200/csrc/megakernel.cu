@@ -109,10 +109,34 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
-__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  __syncwarp();
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+// Polling uses relaxed loads: an acquire load in a spin loop would invalidate the SM's L1 on
+// every iteration, under the feet of the warps that are doing the stage's work. One acquire
+// fence after the poll succeeds gives the ordering.
+__device__ __forceinline__ uint32_t ld_relaxed_gpu(const uint32_t* p) {
   uint32_t v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
+}
+__device__ __forceinline__ void fence_acq_rel_gpu() {
+  asm volatile("fence.acq_rel.gpu;" ::: "memory");
 }
 __device__ __forceinline__ void red_release_gpu_add(uint32_t* p, uint32_t v) {
   asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -146,7 +170,11 @@ struct Ctrl {
   uint64_t group_bar;  // the four epilogue warps (128 arrivals per phase)
   uint32_t tmem_base;
   uint32_t abort_flag;
+  float bias_tile[2][256];  // bias of the current GEMM tile, double buffered across items
+  float mask_row[128];      // additive mask of the current attention tile
 };
+
+static_assert(sizeof(Ctrl) <= 4096, "control block exceeds its shared-memory reserve");
 
 struct Ctx {
   const KernelParams* P;
@@ -159,59 +187,105 @@ struct Ctx {
   uint64_t timeout_ns;
 };
 
-__device__ __noinline__ void report_failure(const Ctx& c, uint32_t code, uint32_t where) {
-  volatile uint32_t* af = &c.ctrl->abort_flag;
+__device__ __noinline__ void report_failure(const KernelParams* P, Ctrl* ctrl, uint32_t stage,
+                                            uint32_t code, uint32_t where) {
+  volatile uint32_t* af = &ctrl->abort_flag;
   *af = 1;
-  KernelStatus* st = c.P->status;
+  KernelStatus* st = P->status;
   if (atomicCAS(&st->code, 0u, code) == 0u) {
-    st->stage = c.stage;
+    st->stage = stage;
     st->cta = blockIdx.x;
     st->where = where;
     __threadfence();
   }
 }
 
-// Bounded wait on an mbarrier phase. Returns false when the kernel is aborting.
-__device__ __forceinline__ bool mbar_wait(const Ctx& c, uint64_t* bar, uint32_t parity,
-                                          uint32_t where) {
-  const uint32_t b = smem_u32(bar);
-  if (mbar_try_wait(b, parity)) return true;
+// Optional per-CTA event trace: trace[(cta * n_stages + stage) * 8 + event] = %globaltimer.
+enum TraceEvent : uint32_t {
+  TR_SIMT_READY = 0,   // epilogue warps passed the previous stage's grid barrier
+  TR_SIMT_DONE = 1,    // ... finished this stage's items
+  TR_SIMT_ARRIVED = 2, // ... arrived at this stage's grid barrier
+  TR_ACT_READY = 3,    // activation producer passed the grid barrier
+  TR_ACT_ISSUED = 4,   // ... issued its last activation tile load of the stage
+  TR_MMA_FIRST = 5,    // MMA issuer saw its first operands of the stage
+  TR_MMA_LAST = 6,     // ... committed its last MMA of the stage
+  TR_W_ISSUED = 7,     // weight producer issued its last tile load of the stage
+  TR_MARK0 = 8,        // 8..15: free marks inside the epilogue / row-wise code (thread 0 of the group)
+};
+__device__ __forceinline__ void trace(const KernelParams& P, uint32_t stage, uint32_t ev) {
+  if (P.trace != nullptr)
+    P.trace[(static_cast<size_t>(blockIdx.x) * (P.stage_end - P.stage_begin) +
+             (stage - P.stage_begin)) * kTraceEvents + ev] = globaltimer_ns();
+}
+// Pull the descriptors of the following stage into L1 while this stage runs.
+__device__ __forceinline__ void prefetch_next_stage(const KernelParams& P, uint32_t s,
+                                                    const StageDesc& st) {
+  if (s + 1 >= P.stage_end) return;
+  asm volatile("prefetch.global.L1 [%0];" ::"l"(P.stages + s + 1));
+  const uint8_t* o = reinterpret_cast<const uint8_t*>(P.ops + st.op_begin + st.op_count);
+#pragma unroll
+  for (int i = 0; i < 6; ++i) asm volatile("prefetch.global.L1 [%0];" ::"l"(o + 128 * i));
+}
+
+// Bounded wait on an mbarrier phase. Returns false when the kernel is aborting. The slow
+// path is out of line so that the many wait sites stay a few instructions each.
+__device__ __noinline__ bool mbar_wait_slow(const KernelParams* P, Ctrl* ctrl, uint32_t b,
+                                            uint32_t parity, uint32_t stage, uint32_t where) {
   const uint64_t t0 = globaltimer_ns();
+  const uint64_t limit = static_cast<uint64_t>(P->timeout_us) * 1000ull;
   uint32_t it = 0;
   for (;;) {
     if (mbar_try_wait(b, parity)) return true;
     if ((++it & 63u) == 0u) {
-      if (*reinterpret_cast<volatile uint32_t*>(&c.ctrl->abort_flag)) return false;
-      if (globaltimer_ns() - t0 > c.timeout_ns) {
-        report_failure(c, ST_MBARRIER_TIMEOUT, where);
+      if (*reinterpret_cast<volatile uint32_t*>(&ctrl->abort_flag)) return false;
+      if (globaltimer_ns() - t0 > limit) {
+        report_failure(P, ctrl, stage, ST_MBARRIER_TIMEOUT, where);
         return false;
       }
     }
   }
 }
+__device__ __forceinline__ bool mbar_wait(const Ctx& c, uint64_t* bar, uint32_t parity,
+                                          uint32_t where) {
+  const uint32_t b = smem_u32(bar);
+  if (mbar_try_wait(b, parity)) return true;
+  return mbar_wait_slow(c.P, c.ctrl, b, parity, c.stage, where);
+}
 
 // Bounded wait until every CTA has arrived for all stages before `stage`.
-__device__ __forceinline__ bool grid_wait(const Ctx& c, uint32_t stage, uint32_t where) {
-  const KernelParams& P = *c.P;
-  if (stage == P.stage_begin) return true;
-  const uint32_t target = P.epoch_base + (stage - P.stage_begin) * gridDim.x;
-  if (static_cast<int32_t>(ld_acquire_gpu(P.barrier) - target) >= 0) return true;
+__device__ __noinline__ bool grid_wait_slow(const KernelParams* P, Ctrl* ctrl, uint32_t target,
+                                            uint32_t stage, uint32_t where) {
   const uint64_t t0 = globaltimer_ns();
+  const uint64_t limit = static_cast<uint64_t>(P->timeout_us) * 1000ull;
   uint32_t it = 0;
   for (;;) {
-    if (static_cast<int32_t>(ld_acquire_gpu(P.barrier) - target) >= 0) return true;
+    if (static_cast<int32_t>(ld_relaxed_gpu(P->barrier) - target) >= 0) {
+      fence_acq_rel_gpu();
+      return true;
+    }
+    __nanosleep(32);
     if ((++it & 31u) == 0u) {
-      if (*reinterpret_cast<volatile uint32_t*>(&c.ctrl->abort_flag)) return false;
-      if (*reinterpret_cast<volatile uint32_t*>(&P.status->code) != 0u) {
-        *reinterpret_cast<volatile uint32_t*>(&c.ctrl->abort_flag) = 1;
+      if (*reinterpret_cast<volatile uint32_t*>(&ctrl->abort_flag)) return false;
+      if (*reinterpret_cast<volatile uint32_t*>(&P->status->code) != 0u) {
+        *reinterpret_cast<volatile uint32_t*>(&ctrl->abort_flag) = 1;
         return false;
       }
-      if (globaltimer_ns() - t0 > c.timeout_ns) {
-        report_failure(c, ST_GRID_BARRIER_TIMEOUT, where);
+      if (globaltimer_ns() - t0 > limit) {
+        report_failure(P, ctrl, stage, ST_GRID_BARRIER_TIMEOUT, where);
         return false;
       }
     }
   }
+}
+__device__ __forceinline__ bool grid_wait(const Ctx& c, uint32_t stage, uint32_t where) {
+  const KernelParams& P = *c.P;
+  if (stage == P.stage_begin) return true;
+  const uint32_t target = P.epoch_base + (stage - P.stage_begin) * gridDim.x;
+  if (static_cast<int32_t>(ld_relaxed_gpu(P.barrier) - target) >= 0) {
+    fence_acq_rel_gpu();
+    return true;
+  }
+  return grid_wait_slow(c.P, c.ctrl, target, stage, where);
 }
 
 // Warp-collective variants for the epilogue warps: every lane gets the same answer, so a
@@ -292,6 +366,7 @@ __device__ void role_weight_producer(Ctx c) {
   for (uint32_t s = P.stage_begin; s < P.stage_end; ++s) {
     c.stage = s;
     const StageDesc st = P.stages[s];
+    prefetch_next_stage(P, s, st);
     for (uint32_t item = blockIdx.x; item < st.n_items; item += gridDim.x) {
       const Item it = locate(P, st, item);
       const OpDesc& op = *it.op;
@@ -311,6 +386,7 @@ __device__ void role_weight_producer(Ctx c) {
                     full);
         ++b_cnt;
       }
+      trace(P, s, TR_W_ISSUED);
     }
   }
 }
@@ -325,6 +401,17 @@ __device__ void role_act_producer(Ctx c) {
   for (uint32_t s = P.stage_begin; s < P.stage_end; ++s) {
     c.stage = s;
     const StageDesc st = P.stages[s];
+    prefetch_next_stage(P, s, st);
+    if (blockIdx.x < st.n_items) {
+      const OpDesc& op0 = *locate(P, st, blockIdx.x).op;
+      if (op0.kind == OP_GEMM || op0.kind == OP_ATTENTION) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(tmaps + static_cast<size_t>(op0.tmap_a) * 128u));
+        if (op0.kind == OP_ATTENTION) {
+          asm volatile("prefetch.tensormap [%0];" ::"l"(tmaps + static_cast<size_t>(op0.tmap_b) * 128u));
+          asm volatile("prefetch.tensormap [%0];" ::"l"(tmaps + static_cast<size_t>(op0.tmap_vt) * 128u));
+        }
+      }
+    }
     bool waited = false;
     for (uint32_t item = blockIdx.x; item < st.n_items; item += gridDim.x) {
       const Item it = locate(P, st, item);
@@ -334,6 +421,7 @@ __device__ void role_act_producer(Ctx c) {
         WAIT_OR_RETURN(grid_wait(c, s, 0x200));
         fence_proxy_async_all();
         waited = true;
+        trace(P, s, TR_ACT_READY);
       }
       if (op.kind == OP_GEMM) {
         const GemmTile t = gemm_tile(op, it.local);
@@ -375,6 +463,7 @@ __device__ void role_act_producer(Ctx c) {
         }
         a_cnt += 2;  // the two P slots are filled by the softmax warps
       }
+      trace(P, s, TR_ACT_ISSUED);
     }
   }
 }
@@ -388,6 +477,7 @@ __device__ void role_mma(Ctx c, uint32_t tmem_base) {
   for (uint32_t s = P.stage_begin; s < P.stage_end; ++s) {
     c.stage = s;
     const StageDesc st = P.stages[s];
+    prefetch_next_stage(P, s, st);
     for (uint32_t item = blockIdx.x; item < st.n_items; item += gridDim.x) {
       const Item it = locate(P, st, item);
       const OpDesc& op = *it.op;
@@ -407,6 +497,7 @@ __device__ void role_mma(Ctx c, uint32_t tmem_base) {
           }
           const uint32_t a_slot = a_cnt % kASlots;
           WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->a_full[a_slot], (a_cnt / kASlots) & 1u, 0x302));
+          if (kb == 0) trace(P, s, TR_MMA_FIRST);
           tc_fence_after();
           const uint64_t ad = umma_desc_sw128(c.a_ring + a_slot * kSlotBytes);
           const uint64_t bd =
@@ -423,6 +514,7 @@ __device__ void role_mma(Ctx c, uint32_t tmem_base) {
         }
         tc_commit(smem_u32(&c.ctrl->acc_full[buf]));
         ++acc_cnt;
+        trace(P, s, TR_MMA_LAST);
       } else if (op.kind == OP_ATTENTION) {
         uint32_t slot[kAttnASlots], par[kAttnASlots];
         for (uint32_t j = 0; j < kAttnASlots; ++j) {
@@ -474,129 +566,132 @@ __device__ void role_mma(Ctx c, uint32_t tmem_base) {
 }
 
 // ----------------------------------------------------------------------------
-// Epilogue / SIMT math
+// Epilogue / SIMT math. Everything here runs once per stage on four warps, so the code
+// is kept compact (chunk loops are not unrolled, slow paths are out of line): the whole
+// kernel has to stay resident in the instruction cache across a layer's stages.
 // ----------------------------------------------------------------------------
-__device__ __forceinline__ float apply_act(float x, uint32_t act) {
-  switch (act) {
-    case ACT_GELU_ERF:
-      return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
-    case ACT_RELU:
-      return fmaxf(x, 0.0f);
-    case ACT_QUICK_GELU:
-      return x / (1.0f + __expf(-1.702f * x));
-    case ACT_GELU_TANH: {
-      const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-      return 0.5f * x * (1.0f + tanhf(u));
+__device__ __forceinline__ float gelu_erf_f(float x) {
+  // erf by the rational form 1 - (a1 t + .. + a5 t^5) exp(-z^2), t = 1/(1 + p z), whose
+  // absolute error (1.5e-7) is far below the f16 resolution of the stored result
+  const float z = fabsf(x) * 0.70710678118654752f;
+  const float t = __fdividef(1.0f, fmaf(0.3275911f, z, 1.0f));
+  float p = fmaf(t, 1.061405429f, -1.453152027f);
+  p = fmaf(t, p, 1.421413741f);
+  p = fmaf(t, p, -0.284496736f);
+  p = fmaf(t, p, 0.254829592f);
+  const float e = 1.0f - p * t * __expf(-z * z);
+  return 0.5f * x * (1.0f + copysignf(e, x));
+}
+
+__device__ __forceinline__ void apply_act16(float (&v)[16], uint32_t act) {
+  if (act == ACT_GELU_ERF) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = gelu_erf_f(v[i]);
+  } else if (act == ACT_RELU) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = fmaxf(v[i], 0.0f);
+  } else if (act == ACT_QUICK_GELU) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __fdividef(v[i], 1.0f + __expf(-1.702f * v[i]));
+  } else if (act == ACT_GELU_TANH) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float u = 0.7978845608028654f * fmaf(0.044715f * v[i] * v[i], v[i], v[i]);
+      // 0.5 (1 + tanh u) = 1 / (1 + exp(-2u))
+      v[i] = __fdividef(v[i], 1.0f + __expf(-2.0f * u));
     }
-    default:
-      return x;
   }
 }
 
-__device__ __forceinline__ void load_f16x16(const __half* p, float (&o)[16]) {
-  const uint4 u0 = __ldg(reinterpret_cast<const uint4*>(p));
-  const uint4 u1 = __ldg(reinterpret_cast<const uint4*>(p) + 1);
-  const uint32_t w[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-    o[2 * i] = f.x;
-    o[2 * i + 1] = f.y;
-  }
-}
-// Activations written earlier in this launch: plain (coherent) loads, never the read-only path.
-__device__ __forceinline__ void load_f16x16_coherent(const __half* p, float (&o)[16]) {
-  const uint4 u0 = __ldcg(reinterpret_cast<const uint4*>(p));
-  const uint4 u1 = __ldcg(reinterpret_cast<const uint4*>(p) + 1);
-  const uint32_t w[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-    o[2 * i] = f.x;
-    o[2 * i + 1] = f.y;
-  }
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
   const __half2 h = __floats2half2_rn(a, b);
   return *reinterpret_cast<const uint32_t*>(&h);
 }
+__device__ __forceinline__ float4 h4_to_f4(uint2 u) {
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void add4(float4& a, const float4 b) {
+  a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+}
 
-__device__ void gemm_epilogue(const Ctx& c, const OpDesc& op, uint32_t local, uint32_t tmem_acc,
-                              uint32_t quarter, uint32_t lane) {
+// Thread `row` of the 128 epilogue threads owns accumulator row `row` (TMEM lane = row).
+__device__ __noinline__ void gemm_epilogue(const OpDesc& op, uint32_t local, uint32_t tmem_acc,
+                                           uint32_t quarter, uint32_t lane, const float* bias_s) {
   const GemmTile t = gemm_tile(op, local);
-  const uint32_t row = quarter * 32u + lane;
-  const uint32_t grow = t.mt * 128u + row;
+  const uint32_t grow = t.mt * 128u + quarter * 32u + lane;
   const bool row_ok = grow < op.M;
   const bool lead = (t.ks == 0);
   const uint32_t n0 = t.nt * op.n_tile;
-  const __half* bias = reinterpret_cast<const __half*>(op.p[1]);
-  for (uint32_t c0 = 0; c0 < op.n_tile; c0 += 16) {
+  const uint32_t flags = op.flags, act = op.act, out_mode = op.out_mode, N = op.N;
+  const uint32_t ldo = op.ldo, ldr = op.ldr, n_tile = op.n_tile;
+  const float alpha = op.alpha;
+  const uint64_t pout = op.p[0], presid = op.p[2];
+  const bool bias_on = (flags & F_BIAS) && lead, resid_on = (flags & F_RESID) && lead;
+#pragma unroll 1
+  for (uint32_t c0 = 0; c0 < n_tile; c0 += 16) {
     float v[16];
     tc_ld16(tmem_acc + ((quarter * 32u) << 16) + c0, v);
     const uint32_t col = n0 + c0;
-    if (!row_ok || col >= op.N) continue;
+    if (!row_ok || col >= N) continue;
+    if (alpha != 1.0f) {
 #pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] *= op.alpha;
-    if ((op.flags & F_BIAS) && lead) {
-      float b[16];
-      load_f16x16(bias + col, b);
-#pragma unroll
-      for (int i = 0; i < 16; ++i) v[i] += b[i];
+      for (int i = 0; i < 16; ++i) v[i] *= alpha;
     }
-    if (op.act != ACT_NONE) {
+    if (bias_on) {
 #pragma unroll
-      for (int i = 0; i < 16; ++i) v[i] = apply_act(v[i], op.act);
+      for (int i = 0; i < 16; ++i) v[i] += bias_s[c0 + i];
     }
-    if ((op.flags & F_RESID) && lead) {
-      if (op.flags & F_RESID_F32) {
-        const float4* r = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(op.p[2]) +
-                                                          static_cast<size_t>(grow) * op.ldr + col);
+    apply_act16(v, act);
+    if (resid_on) {
+      if (flags & F_RESID_F32) {
+        const float4* r = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(presid) +
+                                                          static_cast<size_t>(grow) * ldr + col);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const float4 x = __ldcg(r + i);
           v[4 * i] += x.x; v[4 * i + 1] += x.y; v[4 * i + 2] += x.z; v[4 * i + 3] += x.w;
         }
       } else {
-        float r[16];
-        load_f16x16_coherent(
-            reinterpret_cast<const __half*>(op.p[2]) + static_cast<size_t>(grow) * op.ldr + col, r);
+        const uint2* r = reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(presid) +
+                                                        static_cast<size_t>(grow) * ldr + col);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) v[i] += r[i];
+        for (int i = 0; i < 4; ++i) {
+          const float4 x = h4_to_f4(__ldcg(r + i));
+          v[4 * i] += x.x; v[4 * i + 1] += x.y; v[4 * i + 2] += x.z; v[4 * i + 3] += x.w;
+        }
       }
     }
-    switch (op.out_mode) {
-      case OUT_F16: {
-        uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(op.p[0]) +
-                                            static_cast<size_t>(grow) * op.ldo + col);
-        o[0] = make_uint4(pack_h2(v[0], v[1]), pack_h2(v[2], v[3]), pack_h2(v[4], v[5]),
-                          pack_h2(v[6], v[7]));
-        o[1] = make_uint4(pack_h2(v[8], v[9]), pack_h2(v[10], v[11]), pack_h2(v[12], v[13]),
-                          pack_h2(v[14], v[15]));
-        break;
-      }
-      case OUT_F16_T: {
-        const uint32_t b = grow / op.rows_per_batch, rib = grow % op.rows_per_batch;
-        __half* o = reinterpret_cast<__half*>(op.p[0]) +
-                    (static_cast<size_t>(b) * op.N + col) * op.ldt + rib;
+    if (out_mode == OUT_F16) {
+      uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(pout) +
+                                          static_cast<size_t>(grow) * ldo + col);
+      o[0] = make_uint4(pack_h2(v[0], v[1]), pack_h2(v[2], v[3]), pack_h2(v[4], v[5]),
+                        pack_h2(v[6], v[7]));
+      o[1] = make_uint4(pack_h2(v[8], v[9]), pack_h2(v[10], v[11]), pack_h2(v[12], v[13]),
+                        pack_h2(v[14], v[15]));
+    } else if (out_mode == OUT_F32_RED) {
+      float* o = reinterpret_cast<float*>(pout) + static_cast<size_t>(grow) * ldo + col;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) o[static_cast<size_t>(i) * op.ldt] = __float2half_rn(v[i]);
-        break;
-      }
-      case OUT_F32_RED: {
-        float* o = reinterpret_cast<float*>(op.p[0]) + static_cast<size_t>(grow) * op.ldo + col;
+      for (int i = 0; i < 4; ++i)
+        red_add_f32x4(o + 4 * i, v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    } else if (out_mode == OUT_F16_T) {
+      const uint32_t b = grow / op.rows_per_batch, rib = grow % op.rows_per_batch;
+      const uint32_t ldt = op.ldt;
+      __half* o = reinterpret_cast<__half*>(pout) + (static_cast<size_t>(b) * N + col) * ldt + rib;
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
-          red_add_f32x4(o + 4 * i, v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-        break;
-      }
-      default: {
-        float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(op.p[0]) +
-                                              static_cast<size_t>(grow) * op.ldo + col);
+      for (int i = 0; i < 16; ++i) o[static_cast<size_t>(i) * ldt] = __float2half_rn(v[i]);
+    } else {
+      float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(pout) +
+                                            static_cast<size_t>(grow) * ldo + col);
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
-          o[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-        break;
-      }
+      for (int i = 0; i < 4; ++i)
+        o[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
     }
   }
 }
@@ -607,138 +702,173 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
-constexpr int kLnMaxVec = 16;  // float4 chunks per lane -> rows up to 2048 columns
-
-// One warp normalises one row held in registers.
-__device__ __forceinline__ void layernorm_row_store(float4 (&x)[kLnMaxVec], uint32_t nvec,
-                                                    uint32_t cols, uint32_t lane, float eps,
-                                                    const __half* gamma, const __half* beta,
-                                                    __half* out) {
-  float s = 0.f;
-#pragma unroll
-  for (int i = 0; i < kLnMaxVec; ++i)
-    if (i * 32u + lane < nvec) s += x[i].x + x[i].y + x[i].z + x[i].w;
-  const float mean = warp_sum(s) / static_cast<float>(cols);
-  float q = 0.f;
-#pragma unroll
-  for (int i = 0; i < kLnMaxVec; ++i)
-    if (i * 32u + lane < nvec) {
-      const float a = x[i].x - mean, b = x[i].y - mean, cc = x[i].z - mean, d = x[i].w - mean;
-      q += a * a + b * b + cc * cc + d * d;
-    }
-  const float rstd = rsqrtf(warp_sum(q) / static_cast<float>(cols) + eps);
-#pragma unroll
-  for (int i = 0; i < kLnMaxVec; ++i) {
-    const uint32_t vi = i * 32u + lane;
-    if (vi < nvec) {
-      const uint2 g = __ldg(reinterpret_cast<const uint2*>(gamma) + vi);
-      const uint2 b = __ldg(reinterpret_cast<const uint2*>(beta) + vi);
-      const float2 g0 = __half22float2(*reinterpret_cast<const __half2*>(&g.x));
-      const float2 g1 = __half22float2(*reinterpret_cast<const __half2*>(&g.y));
-      const float2 b0 = __half22float2(*reinterpret_cast<const __half2*>(&b.x));
-      const float2 b1 = __half22float2(*reinterpret_cast<const __half2*>(&b.y));
-      uint2 o;
-      o.x = pack_h2((x[i].x - mean) * rstd * g0.x + b0.x, (x[i].y - mean) * rstd * g0.y + b0.y);
-      o.y = pack_h2((x[i].z - mean) * rstd * g1.x + b1.x, (x[i].w - mean) * rstd * g1.y + b1.y);
-      reinterpret_cast<uint2*>(out)[vi] = o;
-    }
+// Sources of one row of a row-wise op (LayerNorm or embedding): up to three addends.
+struct RowSrc {
+  const float4* f32;   // f32 accumulator row (LayerNorm), cleared after reading when `zero`
+  const uint2* h0;     // f16 row: LayerNorm source, or the gathered word row
+  const uint2* h1;     // f16 row: residual, or the position row
+  const uint2* h2;     // f16 row: token-type row
+  bool zero;
+};
+// Loads only: the optional clearing of the f32 source is a separate step, because a store
+// between the loads would keep the compiler from issuing them back to back.
+__device__ __forceinline__ float4 row_chunk(const RowSrc& s, uint32_t vi) {
+  float4 a;
+  if (s.f32 != nullptr) {
+    a = __ldcg(s.f32 + vi);
+  } else {
+    a = h4_to_f4(__ldcg(s.h0 + vi));
+  }
+  if (s.h1 != nullptr) add4(a, h4_to_f4(__ldcg(s.h1 + vi)));
+  if (s.h2 != nullptr) add4(a, h4_to_f4(__ldcg(s.h2 + vi)));
+  return a;
+}
+__device__ __forceinline__ void row_emit(float4 a, float mean, float rstd, uint32_t vi,
+                                         uint2 gv, uint2 bv, uint2 b2v, uint2* out, float4* out2,
+                                         bool add_bias2) {
+  const float4 g = h4_to_f4(gv), b = h4_to_f4(bv);
+  float4 y;
+  y.x = (a.x - mean) * rstd * g.x + b.x;
+  y.y = (a.y - mean) * rstd * g.y + b.y;
+  y.z = (a.z - mean) * rstd * g.z + b.z;
+  y.w = (a.w - mean) * rstd * g.w + b.w;
+  uint2 o;
+  o.x = pack_h2(y.x, y.y);
+  o.y = pack_h2(y.z, y.w);
+  out[vi] = o;
+  if (out2 != nullptr) {
+    if (add_bias2) add4(y, h4_to_f4(b2v));
+    out2[vi] = y;
   }
 }
 
-__device__ __forceinline__ float4 h4_to_f4(uint2 u) {
-  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
-  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
-  return make_float4(a.x, a.y, b.x, b.y);
-}
-
-__device__ void layernorm_item(const OpDesc& op, uint32_t local, uint32_t warp_in_group,
-                               uint32_t lane) {
+// LayerNorm / embedding item: four rows, one warp each. Rows up to 1024 columns stay in
+// registers between the statistics and the normalisation; wider rows are re-read.
+__device__ __noinline__ void rowwise_item(const OpDesc& op, uint32_t local, uint32_t warp_in_group,
+                                          uint32_t lane, const KernelParams& P, uint32_t stage) {
   const uint32_t row = local * 4u + warp_in_group;
   if (row >= op.rows) return;
-  const uint32_t nvec = op.cols / 4u;
-  float4 x[kLnMaxVec];
-  if (op.flags & F_SRC_F32) {
-    float4* src = reinterpret_cast<float4*>(reinterpret_cast<float*>(op.p[1]) +
-                                            static_cast<size_t>(row) * op.lds);
-#pragma unroll
-    for (int i = 0; i < kLnMaxVec; ++i) {
-      const uint32_t vi = i * 32u + lane;
-      if (vi < nvec) {
-        x[i] = __ldcg(src + vi);
-        if (op.flags & F_ZERO_SRC) src[vi] = make_float4(0.f, 0.f, 0.f, 0.f);
-      }
+  const bool mark = (warp_in_group == 0 && lane == 0);
+  if (mark) trace(P, stage, TR_MARK0);
+  const uint32_t cols = op.cols, nvec = cols >> 2, flags = op.flags;
+  const bool embed = (op.kind == OP_EMBED);
+  RowSrc s{nullptr, nullptr, nullptr, nullptr, false};
+  if (embed) {
+    const int32_t id = reinterpret_cast<const int32_t*>(op.p[1])[row];
+    s.h0 = reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(op.p[3]) +
+                                          static_cast<int64_t>(id) * cols);
+    s.h1 = reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(op.p[4]) +
+                                          static_cast<size_t>(row % op.seq) * cols);
+    if (flags & F_TYPE_IDS) {
+      const int32_t ty = reinterpret_cast<const int32_t*>(op.p[2])[row];
+      s.h2 = reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(op.p[5]) +
+                                            static_cast<int64_t>(ty) * cols);
+    }
+    if ((flags & F_MASK_BIAS) && lane == 0) {
+      const int32_t m = reinterpret_cast<const int32_t*>(op.q[0])[row];
+      reinterpret_cast<float*>(op.q[1])[row] = (1.0f - static_cast<float>(m)) * -10000.0f;
     }
   } else {
-    const uint2* src = reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(op.p[1]) +
-                                                      static_cast<size_t>(row) * op.lds);
-#pragma unroll
-    for (int i = 0; i < kLnMaxVec; ++i) {
-      const uint32_t vi = i * 32u + lane;
-      if (vi < nvec) x[i] = h4_to_f4(__ldcg(src + vi));
+    if (flags & F_SRC_F32) {
+      s.f32 = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(op.p[1]) +
+                                              static_cast<size_t>(row) * op.lds);
+      s.zero = (flags & F_ZERO_SRC) != 0u;
+    } else {
+      s.h0 = reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(op.p[1]) +
+                                            static_cast<size_t>(row) * op.lds);
     }
+    if (flags & F_RESID)
+      s.h1 = reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(op.p[4]) +
+                                            static_cast<size_t>(row) * op.ldr);
   }
-  if (op.flags & F_RESID) {
-    const uint2* r = reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(op.p[4]) +
-                                                    static_cast<size_t>(row) * op.ldr);
-#pragma unroll
-    for (int i = 0; i < kLnMaxVec; ++i) {
-      const uint32_t vi = i * 32u + lane;
-      if (vi < nvec) {
-        const float4 f = h4_to_f4(__ldcg(r + vi));
-        x[i].x += f.x; x[i].y += f.y; x[i].z += f.z; x[i].w += f.w;
-      }
-    }
-  }
-  layernorm_row_store(x, nvec, op.cols, lane, op.eps, reinterpret_cast<const __half*>(op.p[2]),
-                      reinterpret_cast<const __half*>(op.p[3]),
-                      reinterpret_cast<__half*>(op.p[0]) + static_cast<size_t>(row) * op.ldo);
-}
+  const uint2* gamma = reinterpret_cast<const uint2*>(embed ? op.p[6] : op.p[2]);
+  const uint2* beta = reinterpret_cast<const uint2*>(embed ? op.p[7] : op.p[3]);
+  uint2* out = reinterpret_cast<uint2*>(reinterpret_cast<__half*>(op.p[0]) +
+                                        static_cast<size_t>(row) * op.ldo);
+  float4* out2 = op.q[2] ? reinterpret_cast<float4*>(reinterpret_cast<float*>(op.q[2]) +
+                                                     static_cast<size_t>(row) * cols)
+                         : nullptr;
+  const uint2* bias2 = reinterpret_cast<const uint2*>(op.q[3]);
+  const float inv_n = 1.0f / static_cast<float>(cols), eps = op.eps;
 
-__device__ void embed_item(const OpDesc& op, uint32_t local, uint32_t warp_in_group,
-                           uint32_t lane) {
-  const uint32_t row = local * 4u + warp_in_group;
-  if (row >= op.rows) return;
-  const uint32_t nvec = op.cols / 4u;
-  const int32_t id = reinterpret_cast<const int32_t*>(op.p[1])[row];
-  const uint32_t pos = row % op.seq;
-  const uint2* w = reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(op.p[3]) +
-                                                  static_cast<int64_t>(id) * op.cols);
-  const uint2* pe = reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(op.p[4]) +
-                                                   static_cast<size_t>(pos) * op.cols);
-  const uint2* te = nullptr;
-  if (op.flags & F_TYPE_IDS) {
-    const int32_t ty = reinterpret_cast<const int32_t*>(op.p[2])[row];
-    te = reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(op.p[5]) +
-                                        static_cast<int64_t>(ty) * op.cols);
-  }
-  float4 x[kLnMaxVec];
+  const bool add_bias2 = (out2 != nullptr) && (bias2 != nullptr);
+  if (mark && (reinterpret_cast<uint64_t>(out) + reinterpret_cast<uint64_t>(gamma) +
+               reinterpret_cast<uint64_t>(s.f32) + reinterpret_cast<uint64_t>(s.h0) + nvec) != 1ull)
+    trace(P, stage, TR_MARK0 + 3);
+  if (nvec <= 256u) {
+    // every global load of the row is issued before anything waits on one of them
+    float4 x[8];
+    uint2 gv[8], bv[8], b2v[8];
 #pragma unroll
-  for (int i = 0; i < kLnMaxVec; ++i) {
-    const uint32_t vi = i * 32u + lane;
-    if (vi < nvec) {
-      float4 a = h4_to_f4(__ldg(w + vi));
-      const float4 b = h4_to_f4(__ldg(pe + vi));
-      a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
-      if (te) {
-        const float4 t = h4_to_f4(__ldg(te + vi));
-        a.x += t.x; a.y += t.y; a.z += t.z; a.w += t.w;
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t vi = i * 32u + lane;
+      x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      gv[i] = bv[i] = b2v[i] = make_uint2(0u, 0u);
+      if (vi < nvec) {
+        x[i] = row_chunk(s, vi);
+        gv[i] = __ldg(gamma + vi);
+        bv[i] = __ldg(beta + vi);
+        if (add_bias2) b2v[i] = __ldg(bias2 + vi);
       }
-      x[i] = a;
+    }
+    if (s.zero) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (i * 32u + lane < nvec)
+          const_cast<float4*>(s.f32)[i * 32u + lane] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (mark && x[0].x != 1.2345e-30f) trace(P, stage, TR_MARK0 + 4);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sum += x[i].x + x[i].y + x[i].z + x[i].w;
+    if (mark) trace(P, stage, TR_MARK0 + 1);
+    const float mean = warp_sum(sum) * inv_n;
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (i * 32u + lane < nvec) {
+        const float a = x[i].x - mean, b = x[i].y - mean, c = x[i].z - mean, d = x[i].w - mean;
+        sq += a * a + b * b + c * c + d * d;
+      }
+    const float rstd = rsqrtf(warp_sum(sq) * inv_n + eps);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t vi = i * 32u + lane;
+      if (vi < nvec) row_emit(x[i], mean, rstd, vi, gv[i], bv[i], b2v[i], out, out2, add_bias2);
+    }
+  } else {
+    // wide rows: three passes over the (L2-resident) sources
+    float sum = 0.f;
+#pragma unroll 1
+    for (uint32_t vi = lane; vi < nvec; vi += 32u) {
+      const float4 a = row_chunk(s, vi);
+      sum += a.x + a.y + a.z + a.w;
+    }
+    const float mean = warp_sum(sum) * inv_n;
+    float sq = 0.f;
+#pragma unroll 1
+    for (uint32_t vi = lane; vi < nvec; vi += 32u) {
+      const float4 a = row_chunk(s, vi);
+      const float e = a.x - mean, f = a.y - mean, g = a.z - mean, h = a.w - mean;
+      sq += e * e + f * f + g * g + h * h;
+    }
+    const float rstd = rsqrtf(warp_sum(sq) * inv_n + eps);
+#pragma unroll 1
+    for (uint32_t vi = lane; vi < nvec; vi += 32u) {
+      const float4 a = row_chunk(s, vi);
+      if (s.zero) const_cast<float4*>(s.f32)[vi] = make_float4(0.f, 0.f, 0.f, 0.f);
+      row_emit(a, mean, rstd, vi, __ldg(gamma + vi), __ldg(beta + vi),
+               add_bias2 ? __ldg(bias2 + vi) : make_uint2(0u, 0u), out, out2, add_bias2);
     }
   }
-  layernorm_row_store(x, nvec, op.cols, lane, op.eps, reinterpret_cast<const __half*>(op.p[6]),
-                      reinterpret_cast<const __half*>(op.p[7]),
-                      reinterpret_cast<__half*>(op.p[0]) + static_cast<size_t>(row) * op.ldo);
-  if ((op.flags & F_MASK_BIAS) && lane == 0) {
-    const int32_t m = reinterpret_cast<const int32_t*>(op.q[0])[row];
-    reinterpret_cast<float*>(op.q[1])[row] = (1.0f - static_cast<float>(m)) * -10000.0f;
-  }
+  if (mark) trace(P, stage, TR_MARK0 + 2);
 }
 
 // Softmax + output of one attention tile; thread `row` owns query row `row`.
-__device__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t local, uint32_t tmem_base,
-                               uint32_t& a_cnt, uint32_t& acc_cnt, uint32_t quarter, uint32_t lane,
-                               uint32_t tid_in_group) {
+__device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t local,
+                                            uint32_t tmem_base, uint32_t& a_cnt, uint32_t& acc_cnt,
+                                            uint32_t quarter, uint32_t lane,
+                                            uint32_t tid_in_group) {
   const AttnTile t = attn_tile(op, local);
   const uint32_t row = quarter * 32u + lane;
   const uint32_t qrow = t.mt * 128u + row;  // query index inside the sequence
@@ -747,57 +877,69 @@ __device__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t local, uint32_
   a_cnt += kAttnASlots;
 
   uint32_t buf = acc_cnt & 1u;
+  const uint32_t seq = op.seq;
+  const uint32_t n_keys = seq < 128u ? seq : 128u;
+  const float alpha = op.alpha * 1.4426950408889634f;  // scores in log2 units: exp(x) = 2^(x log2 e)
+  // Stage the additive key mask of this batch row while Q, K load and QK^T runs; keys past
+  // the sequence end are masked out here so the loops below need no bound check.
+  float* mb = c.ctrl->mask_row;
+  {
+    float m = -1.0e30f;
+    if (tid_in_group < n_keys)
+      m = (op.flags & F_MASK_BIAS)
+              ? __ldcg(reinterpret_cast<const float*>(op.p[1]) + static_cast<size_t>(t.b) * seq +
+                       tid_in_group)
+              : 0.f;
+    mb[tid_in_group] = m * 1.4426950408889634f;
+    if (!group_sync(c, 0x415)) return false;
+  }
+  // causal: keys after the query are masked
+  const uint32_t key_limit = (op.flags & F_CAUSAL) ? qrow : 0xffffffffu;
   if (!mbar_wait_warp(c, &c.ctrl->acc_full[buf], (acc_cnt >> 1) & 1u, 0x410)) return false;
+  if (tid_in_group == 0) trace(*c.P, c.stage, TR_MARK0);
   tc_fence_after();
   const uint32_t tS = tmem_base + buf * kAccCols + ((quarter * 32u) << 16);
-  const float* mb = (op.flags & F_MASK_BIAS)
-                        ? reinterpret_cast<const float*>(op.p[1]) + static_cast<size_t>(t.b) * op.seq
-                        : nullptr;
-  const uint32_t n_keys = op.seq < 128u ? op.seq : 128u;
-  const bool causal = (op.flags & F_CAUSAL) != 0u;
-  // pass 1: row maximum of scale*s + bias over the valid keys
+  // pass 1: row maximum of scale*s + mask
   float mx = -3.0e38f;
-  for (uint32_t c0 = 0; c0 < 128u; c0 += 16) {
-    float v[16];
-    tc_ld16(tS + c0, v);
+#pragma unroll 1
+  for (uint32_t c0 = 0; c0 < 128u; c0 += 32) {
+    float v[32];
+    tc_ld32(tS + c0, v);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const uint32_t key = c0 + i;
-      if (key < n_keys && !(causal && key > qrow)) {
-        const float z = v[i] * op.alpha + (mb ? __ldcg(mb + key) : 0.f);
-        mx = fmaxf(mx, z);
-      }
+    for (int i = 0; i < 32; ++i) {
+      const float z = (c0 + i <= key_limit) ? fmaf(v[i], alpha, mb[c0 + i]) : -1.0e30f;
+      mx = fmaxf(mx, z);
     }
   }
+  if (tid_in_group == 0) trace(*c.P, c.stage, TR_MARK0 + 1);
   // the P slots must be free before they are overwritten
   if (!mbar_wait_warp(c, &c.ctrl->a_empty[slotP0], parP0 ^ 1u, 0x411)) return false;
   if (!mbar_wait_warp(c, &c.ctrl->a_empty[slotP1], parP1 ^ 1u, 0x412)) return false;
   // pass 2: p = exp(z - max), row sum, P tile in the swizzled K-major operand layout
-  float sum = 0.f;
-  for (uint32_t c0 = 0; c0 < 128u; c0 += 16) {
-    float v[16];
-    tc_ld16(tS + c0, v);
+  float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll 1
+  for (uint32_t c0 = 0; c0 < 128u; c0 += 32) {
+    float v[32];
+    tc_ld32(tS + c0, v);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const uint32_t key = c0 + i;
-      float p = 0.f;
-      if (key < n_keys && !(causal && key > qrow)) {
-        const float z = v[i] * op.alpha + (mb ? __ldcg(mb + key) : 0.f);
-        p = __expf(z - mx);
-      }
-      // sum what the tensor core will actually multiply (the f16-rounded value)
-      v[i] = __half2float(__float2half_rn(p));
-      sum += v[i];
+    for (int i = 0; i < 32; i += 2) {
+      const float z0 = (c0 + i <= key_limit) ? fmaf(v[i], alpha, mb[c0 + i]) : -1.0e30f;
+      const float z1 = (c0 + i + 1 <= key_limit) ? fmaf(v[i + 1], alpha, mb[c0 + i + 1]) : -1.0e30f;
+      v[i] = fast_exp2(z0 - mx);
+      v[i + 1] = fast_exp2(z1 - mx);
+      sum0 += v[i];
+      sum1 += v[i + 1];
     }
     uint8_t* tile = c.a_ring_ptr + ((c0 < 64u) ? slotP0 : slotP1) * kSlotBytes;
     const uint32_t chunk = (c0 & 63u) >> 3;  // 16-byte chunk index inside the 128-byte row
-    uint4* d0 = reinterpret_cast<uint4*>(tile + row * 128u + (((chunk) ^ (row & 7u)) << 4));
-    uint4* d1 = reinterpret_cast<uint4*>(tile + row * 128u + (((chunk + 1u) ^ (row & 7u)) << 4));
-    *d0 = make_uint4(pack_h2(v[0], v[1]), pack_h2(v[2], v[3]), pack_h2(v[4], v[5]),
-                     pack_h2(v[6], v[7]));
-    *d1 = make_uint4(pack_h2(v[8], v[9]), pack_h2(v[10], v[11]), pack_h2(v[12], v[13]),
-                     pack_h2(v[14], v[15]));
+#pragma unroll
+    for (uint32_t j = 0; j < 4; ++j) {
+      uint4* d = reinterpret_cast<uint4*>(tile + row * 128u + (((chunk + j) ^ (row & 7u)) << 4));
+      *d = make_uint4(pack_h2(v[8 * j], v[8 * j + 1]), pack_h2(v[8 * j + 2], v[8 * j + 3]),
+                      pack_h2(v[8 * j + 4], v[8 * j + 5]), pack_h2(v[8 * j + 6], v[8 * j + 7]));
+    }
   }
+  if (tid_in_group == 0) trace(*c.P, c.stage, TR_MARK0 + 2);
   fence_proxy_async_smem();
   tc_fence_before();
   if (!group_sync(c, 0x414)) return false;
@@ -811,21 +953,25 @@ __device__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t local, uint32_
   // O = P V
   buf = acc_cnt & 1u;
   if (!mbar_wait_warp(c, &c.ctrl->acc_full[buf], (acc_cnt >> 1) & 1u, 0x413)) return false;
+  if (tid_in_group == 0) trace(*c.P, c.stage, TR_MARK0 + 3);
   tc_fence_after();
   const uint32_t tO = tmem_base + buf * kAccCols + ((quarter * 32u) << 16);
-  const float inv = 1.0f / sum;
-  const bool row_ok = qrow < op.seq;
+  const float inv = 1.0f / (sum0 + sum1);
+  const bool row_ok = qrow < seq;
   __half* out = reinterpret_cast<__half*>(op.p[0]) +
-                (static_cast<size_t>(t.b) * op.seq + qrow) * op.ldo + t.h * 64u;
-  for (uint32_t c0 = 0; c0 < 64u; c0 += 16) {
-    float v[16];
-    tc_ld16(tO + c0, v);
+                (static_cast<size_t>(t.b) * seq + qrow) * op.ldo + t.h * 64u;
+#pragma unroll 1
+  for (uint32_t c0 = 0; c0 < 64u; c0 += 32) {
+    float v[32];
+    tc_ld32(tO + c0, v);
     if (row_ok) {
       uint4* o = reinterpret_cast<uint4*>(out + c0);
-      o[0] = make_uint4(pack_h2(v[0] * inv, v[1] * inv), pack_h2(v[2] * inv, v[3] * inv),
-                        pack_h2(v[4] * inv, v[5] * inv), pack_h2(v[6] * inv, v[7] * inv));
-      o[1] = make_uint4(pack_h2(v[8] * inv, v[9] * inv), pack_h2(v[10] * inv, v[11] * inv),
-                        pack_h2(v[12] * inv, v[13] * inv), pack_h2(v[14] * inv, v[15] * inv));
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        o[j] = make_uint4(pack_h2(v[8 * j] * inv, v[8 * j + 1] * inv),
+                          pack_h2(v[8 * j + 2] * inv, v[8 * j + 3] * inv),
+                          pack_h2(v[8 * j + 4] * inv, v[8 * j + 5] * inv),
+                          pack_h2(v[8 * j + 6] * inv, v[8 * j + 7] * inv));
     }
   }
   tc_fence_before();
@@ -846,7 +992,9 @@ __device__ void role_simt(Ctx c, uint32_t tmem_base, uint32_t tid_in_group) {
     const StageDesc st = P.stages[s];
     // All CTAs must have finished the previous stage before this CTA reads its
     // results or arrives for this stage.
+    prefetch_next_stage(P, s, st);
     WAIT_OR_RETURN(grid_wait_warp(c, s, 0x400));
+    if (tid_in_group == 0) trace(P, s, TR_SIMT_READY);
     if (P.stamps != nullptr && blockIdx.x == 0 && tid_in_group == 0)
       P.stamps[s - P.stage_begin] = globaltimer_ns();
     for (uint32_t item = blockIdx.x; item < st.n_items; item += gridDim.x) {
@@ -855,9 +1003,21 @@ __device__ void role_simt(Ctx c, uint32_t tmem_base, uint32_t tid_in_group) {
       switch (op.kind) {
         case OP_GEMM: {
           const uint32_t buf = acc_cnt & 1u;
+          float* bias_s = c.ctrl->bias_tile[buf];
+          if (op.flags & F_BIAS) {
+            // stage the tile's bias while the MMAs run
+            const uint32_t n0 = ((it.local / op.k_split) % op.n_tiles) * op.n_tile;
+            for (uint32_t i = tid_in_group; i < op.n_tile; i += 128u)
+              bias_s[i] = (n0 + i < op.N)
+                              ? __half2float(__ldg(reinterpret_cast<const __half*>(op.p[1]) + n0 + i))
+                              : 0.f;
+            WAIT_OR_RETURN(group_sync(c, 0x403));
+          }
+          if (tid_in_group == 0) trace(P, s, TR_MARK0);
           WAIT_OR_RETURN(mbar_wait_warp(c, &c.ctrl->acc_full[buf], (acc_cnt >> 1) & 1u, 0x401));
+          if (tid_in_group == 0) trace(P, s, TR_MARK0 + 1);
           tc_fence_after();
-          gemm_epilogue(c, op, it.local, tmem_base + buf * kAccCols, quarter, lane);
+          gemm_epilogue(op, it.local, tmem_base + buf * kAccCols, quarter, lane, bias_s);
           tc_fence_before();
           mbar_arrive(smem_u32(&c.ctrl->acc_empty[buf]));
           ++acc_cnt;
@@ -869,21 +1029,24 @@ __device__ void role_simt(Ctx c, uint32_t tmem_base, uint32_t tid_in_group) {
               attention_simt(c, op, it.local, tmem_base, a_cnt, acc_cnt, quarter, lane, tid_in_group));
           break;
         case OP_LAYERNORM:
-          layernorm_item(op, it.local, quarter, lane);
-          break;
         case OP_EMBED:
-          embed_item(op, it.local, quarter, lane);
+          rowwise_item(op, it.local, quarter, lane, P, s);
           break;
         default:
           break;
       }
     }
     // publish this CTA's stores of the stage, then arrive
-    fence_proxy_async_all();
-    WAIT_OR_RETURN(group_sync(c, 0x402));
+    if (tid_in_group == 0) trace(P, s, TR_SIMT_DONE);
+    if (blockIdx.x < st.n_items) {
+      // this CTA stored results that later stages read through TMA (async proxy)
+      fence_proxy_async_all();
+      WAIT_OR_RETURN(group_sync(c, 0x402));
+    }
     if (tid_in_group == 0) {
-      __threadfence();
+      // release at gpu scope is cumulative over the group's stores ordered by group_sync
       red_release_gpu_add(P.barrier, 1u);
+      trace(P, s, TR_SIMT_ARRIVED);
     }
   }
   if (P.stamps != nullptr && blockIdx.x == 0 && tid_in_group == 0)
@@ -930,6 +1093,12 @@ mononn_megakernel(const __grid_constant__ KernelParams P) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
+
+  // Biases and LayerNorm scale/shift of every layer sit in one small region; touching it now
+  // puts it in L2 (and its page in the TLBs) long before the row-wise stages ask for it.
+  for (uint64_t off = (static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x) * 128ull;
+       off < P.hot_const_bytes; off += static_cast<uint64_t>(gridDim.x) * kThreads * 128ull)
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(P.hot_consts + off));
 
   Ctx c;
   c.P = &P;

@@ -71,6 +71,8 @@ struct FOp {
   uint32_t q_col = 0, k_col = 0, heads = 0, seq = 0, batches = 0, head_dim = 64;
   // LAYERNORM: src (AccF32 | ActF16), resid, gamma, beta, out
   int src = -1, gamma = -1, beta = -1;
+  // LAYERNORM / EMBED: optional f32 copy of the result (+ bias2) into an accumulator
+  int out2 = -1, bias2 = -1;
   // EMBED: ids, type_ids, mask_in (Arg), word/pos/type tables (Const), mask_out (VecF32)
   int ids = -1, type_ids = -1, mask_in = -1, word = -1, pos = -1, type = -1, mask_out = -1;
   uint32_t rows = 0, cols = 0, vocab = 0;
@@ -115,7 +117,7 @@ struct PlanOp {
   std::string name;
   OpDesc d{};
   BufRef p[8];
-  BufRef q[2];
+  BufRef q[4];
 };
 
 // How one HLO constant lands in the constant arena.
@@ -150,6 +152,7 @@ struct Plan {
   std::vector<ArgDesc> args;
   std::vector<ConstBinding> consts;
   uint64_t const_bytes = 0;
+  uint64_t hot_const_bytes = 0;  // leading part of the constant arena holding the small constants
   uint64_t scratch_bytes = 0;  // module-owned, zero-initialised
   uint64_t temp_bytes = 0;
   uint32_t grid = 0, block = kThreads, smem_bytes = 0;
@@ -172,6 +175,6 @@ std::vector<GemmTileSpec> gemm_tile_candidates(uint32_t M, uint32_t N, uint32_t 
 // Fixed head of the module scratch: barrier counter, status word, per-stage time stamps.
 constexpr uint64_t kScratchBarrierOff = 0, kScratchStatusOff = 256, kScratchStampsOff = 512;
 
-constexpr uint32_t kSmemBytes = (kASlots + kBSlots) * kSlotBytes + 1024 /*ctrl*/ + 1024 /*align*/;
+constexpr uint32_t kSmemBytes = (kASlots + kBSlots) * kSlotBytes + 4096 /*ctrl*/ + 1024 /*align*/;
 
 }  // namespace mononn

@@ -38,7 +38,8 @@ void Runtime::release() {
   if (d_const_) cudaFree(d_const_);
   if (d_scratch_) cudaFree(d_scratch_);
   if (d_table_) cudaFree(d_table_);
-  d_const_ = d_scratch_ = d_table_ = nullptr;
+  if (d_trace_) cudaFree(d_trace_);
+  d_const_ = d_scratch_ = d_table_ = d_trace_ = nullptr;
 }
 
 int Runtime::init(int device) {
@@ -210,7 +211,7 @@ int Runtime::bind(void* const* args, int n, void* stream) {
   for (size_t i = 0; i < plan_.ops.size(); ++i) {
     ops[i] = plan_.ops[i].d;
     for (int k = 0; k < 8; ++k) ops[i].p[k] = resolve(plan_.ops[i].p[k]);
-    for (int k = 0; k < 2; ++k) ops[i].q[k] = resolve(plan_.ops[i].q[k]);
+    for (int k = 0; k < 4; ++k) ops[i].q[k] = resolve(plan_.ops[i].q[k]);
   }
   EncodeTiledFn encode = reinterpret_cast<EncodeTiledFn>(encode_fn_);
   for (size_t i = 0; i < plan_.tmaps.size(); ++i) {
@@ -267,6 +268,9 @@ int Runtime::launch(void* const* args, int n, void* stream, uint32_t stage_begin
   kp.barrier = reinterpret_cast<uint32_t*>(scr + kScratchBarrierOff);
   kp.status = reinterpret_cast<KernelStatus*>(scr + kScratchStatusOff);
   kp.stamps = stamps ? reinterpret_cast<uint64_t*>(scr + kScratchStampsOff) : nullptr;
+  kp.trace = trace_on_ ? static_cast<uint64_t*>(d_trace_) : nullptr;
+  kp.hot_consts = static_cast<const uint8_t*>(d_const_);
+  kp.hot_const_bytes = plan_.hot_const_bytes;
   kp.n_stages = static_cast<uint32_t>(plan_.stages.size());
   kp.epoch_base = epoch_;
   kp.timeout_us = timeout_us ? timeout_us : 2000000u;
@@ -312,6 +316,30 @@ int Runtime::read_stamps(std::vector<double>* us) {
   us->clear();
   for (uint32_t i = 0; i < n_stamp_stages_; ++i)
     us->push_back(static_cast<double>(t[i + 1] - t[i]) * 1e-3);
+  return MONONN_OK;
+}
+
+int Runtime::trace_launch(void* const* args, int n, void* stream, std::vector<double>* out) {
+  CUDA_TRY(cudaSetDevice(device_));
+  const size_t ns = plan_.stages.size();
+  const size_t words = static_cast<size_t>(plan_.grid) * ns * kTraceEvents;
+  if (!d_trace_) CUDA_TRY(cudaMalloc(&d_trace_, words * 8));
+  CUDA_TRY(cudaMemsetAsync(d_trace_, 0, words * 8, static_cast<cudaStream_t>(stream)));
+  trace_on_ = true;
+  int rc = launch(args, n, stream, 0, static_cast<uint32_t>(ns), false);
+  trace_on_ = false;
+  if (rc) return rc;
+  int st = 0, cta = 0;
+  rc = check_status(&st, &cta);
+  if (rc) return rc;
+  std::vector<uint64_t> raw(words);
+  CUDA_TRY(cudaMemcpy(raw.data(), d_trace_, words * 8, cudaMemcpyDeviceToHost));
+  uint64_t t0 = ~0ull;
+  for (uint64_t v : raw)
+    if (v && v < t0) t0 = v;
+  out->assign(words, 0.0);
+  for (size_t i = 0; i < words; ++i)
+    if (raw[i]) (*out)[i] = static_cast<double>(raw[i] - t0) + 1.0;
   return MONONN_OK;
 }
 

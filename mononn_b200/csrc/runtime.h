@@ -51,6 +51,9 @@ class Runtime {
   // cudaDeviceSynchronize + status word; resets barrier and accumulators after a failure.
   int check_status(int* stage, int* cta);
   int read_stamps(std::vector<double>* us);  // after a stamps launch + sync
+  // One launch of all stages with the per-CTA event trace on; out = [grid][stages][kTraceEvents]
+  // nanoseconds relative to the earliest event (0 where an event did not occur).
+  int trace_launch(void* const* args, int n, void* stream, std::vector<double>* out);
   // Mean device time (microseconds) of `iters` launches of stages [begin, end) after `warmup`.
   int time_stages(void* const* args, int n, void* stream, uint32_t begin, uint32_t end, int warmup,
                   int iters, double* us);
@@ -69,6 +72,8 @@ class Runtime {
   void* d_const_ = nullptr;
   void* d_scratch_ = nullptr;
   void* d_table_ = nullptr;
+  void* d_trace_ = nullptr;
+  bool trace_on_ = false;
   size_t table_bytes_ = 0, off_ops_ = 0, off_tmaps_ = 0;
   std::vector<uint8_t> h_table_;
   std::vector<void*> bound_args_;

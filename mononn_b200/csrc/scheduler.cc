@@ -143,13 +143,13 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
   auto inputs_of = [](const FOp& o) {
     std::vector<int> v;
     for (int t : {o.a, o.w, o.bias, o.resid, o.q, o.k, o.vt, o.mask, o.src, o.gamma, o.beta, o.ids,
-                  o.type_ids, o.mask_in, o.word, o.pos, o.type})
+                  o.type_ids, o.mask_in, o.word, o.pos, o.type, o.bias2})
       if (t >= 0) v.push_back(t);
     return v;
   };
   auto outputs_of = [](const FOp& o) {
     std::vector<int> v;
-    for (int t : {o.out, o.mask_out})
+    for (int t : {o.out, o.mask_out, o.out2})
       if (t >= 0) v.push_back(t);
     return v;
   };
@@ -165,6 +165,28 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
     return MONONN_ERR_INVALID_ARGUMENT;
   }
 
+  // ---- residual hoisting: a split-K GEMM that accumulates into an f32 buffer and adds a
+  // residual produced by a LayerNorm / embedding row op gets that residual (and its bias)
+  // pre-loaded into the accumulator by the producer, so its own epilogue is a bare
+  // reduction with no global loads on the critical path.
+  for (FOp& gop : ops) {
+    if (gop.kind != OP_GEMM || gop.resid < 0 || gop.out < 0) continue;
+    if (g.tensors[gop.out].kind != TKind::AccF32) continue;
+    if (g.tensors[gop.resid].kind != TKind::ActF16 && g.tensors[gop.resid].kind != TKind::Arg) continue;
+    for (FOp& pop : ops) {
+      if ((pop.kind != OP_LAYERNORM && pop.kind != OP_EMBED) || pop.out != gop.resid) continue;
+      if (pop.out2 >= 0 || pop.cols != gop.N) break;
+      pop.out2 = gop.out;
+      pop.bias2 = gop.bias;
+      gop.resid = -1;
+      gop.bias = -1;
+      // the accumulator is now fully overwritten before use: its reader need not clear it
+      for (FOp& rop : ops)
+        if (rop.kind == OP_LAYERNORM && rop.src == gop.out) rop.flags &= ~F_ZERO_SRC;
+      break;
+    }
+  }
+
   // ---- stage = dependency depth
   std::vector<int> producer(n_t, -1);
   int n_stages = 0;
@@ -172,7 +194,9 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
     int depth = 0;
     for (int t : inputs_of(ops[i]))
       if (producer[t] >= 0) depth = std::max(depth, ops[producer[t]].stage + 1);
-    // a tensor that is both read and written by the op (accumulator reuse) is an input too
+    // an op that accumulates into a tensor someone pre-loaded runs after that producer
+    for (int t : outputs_of(ops[i]))
+      if (producer[t] >= 0) depth = std::max(depth, ops[producer[t]].stage + 1);
     ops[i].stage = depth;
     n_stages = std::max(n_stages, depth + 1);
     for (int t : outputs_of(ops[i])) producer[t] = static_cast<int>(i);
@@ -277,6 +301,15 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
     }
     return BufRef{SPACE_CONST, 0, P.consts[it->second].offset};
   };
+
+  // Small constants first, contiguously: biases and LayerNorm scale/shift of all layers share
+  // a few pages, which the kernel prefetches to L2 when it starts.
+  for (const FOp& o : ops)
+    for (int t : {o.bias, o.gamma, o.beta, o.bias2})
+      if (t >= 0 && static_cast<uint64_t>(g.tensors[t].rows) * g.tensors[t].cols *
+                            g.tensors[t].elem_bytes <= 65536)
+        raw_const(t);
+  P.hot_const_bytes = const_top;
 
   // ---- tensor maps
   std::map<int, uint32_t> act_tmap;  // tensor -> tmap index (box 64 x 128)
@@ -478,6 +511,10 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
             d.flags |= F_RESID;
             d.ldr = g.tensors[o.resid].ld;
           }
+          if (o.out2 >= 0) {
+            po.q[2] = where[o.out2];
+            if (o.bias2 >= 0) po.q[3] = raw_const(o.bias2);
+          }
           break;
         }
         case OP_EMBED: {
@@ -506,6 +543,10 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
             po.q[0] = where[o.mask_in];
             po.q[1] = where[o.mask_out];
             d.flags |= F_MASK_BIAS;
+          }
+          if (o.out2 >= 0) {
+            po.q[2] = where[o.out2];
+            if (o.bias2 >= 0) po.q[3] = raw_const(o.bias2);
           }
           break;
         }

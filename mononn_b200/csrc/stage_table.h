@@ -53,6 +53,8 @@ enum OpFlags : uint32_t {
 //  LAYERNORM: 0 out(f16), 1 src, 2 gamma(f16), 3 beta(f16), 4 resid(f16, optional), 5 out2
 //  EMBED:     0 out(f16), 1 ids(i32), 2 type ids(i32), 3 word table(f16), 4 pos table(f16),
 //             5 type table(f16), 6 gamma, 7 beta ; mask(i32) -> q[0], mask bias out(f32) -> q[1]
+//  LAYERNORM and EMBED may also write q[2] = f32 copy of the result plus the f16 bias q[3]
+//  (residual + bias pre-loaded into the accumulator of the next split-K GEMM)
 struct alignas(16) OpDesc {
   uint32_t kind;
   uint32_t flags;
@@ -80,7 +82,7 @@ struct alignas(16) OpDesc {
   uint32_t vocab;           // embed: word-table rows (ids are not clamped, as in the reference)
   uint32_t pad0;
   uint64_t p[8];
-  uint64_t q[2];
+  uint64_t q[4];  // LAYERNORM / EMBED: q[2] second output (f32, + q[3] bias f16), see plan
 };
 
 struct alignas(16) StageDesc {
@@ -110,6 +112,7 @@ constexpr uint32_t kASlots = 6;
 constexpr uint32_t kBSlots = 7;
 constexpr uint32_t kThreads = 256;
 constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kTraceEvents = 16;  // per (CTA, stage) slots of the optional event trace
 constexpr uint32_t kAccCols = 256;  // two accumulator buffers of 256 columns
 
 struct KernelParams {
@@ -119,6 +122,9 @@ struct KernelParams {
   uint32_t* barrier;     // monotonically increasing arrival counter
   KernelStatus* status;
   uint64_t* stamps;      // optional per-stage %globaltimer stamps (CTA 0), or null
+  uint64_t* trace;       // optional [cta][stage][kTraceEvents] event times, or null
+  const uint8_t* hot_consts;  // small constants (biases, scale/shift), prefetched to L2 at start
+  uint64_t hot_const_bytes;
   uint32_t n_stages;
   uint32_t epoch_base;   // counter value at kernel entry
   uint32_t timeout_us;   // bound on every wait

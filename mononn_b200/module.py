@@ -139,6 +139,18 @@ class Module:
                                           us, names, cap, C.byref(n)))
         return [(names[i].decode(), us[i]) for i in range(min(n.value, cap))]
 
+    def trace(self, stream=None) -> np.ndarray:
+        """Per-CTA event trace of one launch: array [grid, stages, 16] in ns (0 = no event)."""
+        if self._ptrs is None:
+            self.allocate()
+        cfg = self.launch_config()
+        n_st = len(self.plan()["stages"])
+        out = np.zeros(cfg["grid"][0] * n_st * 16, np.float64)
+        g, s = C.c_int(), C.c_int()
+        check(lib().mononn_trace_stages(self._h, self._ptrs, len(self._bufs), self._stream(stream),
+                                        out.ctypes.data_as(C.POINTER(C.c_double)), out.size, C.byref(g), C.byref(s)))
+        return out.reshape(g.value, s.value, 16)
+
     # ---------------------------------------------------------------- inference
     def run(self, inputs: list[np.ndarray]) -> list[np.ndarray]:
         """Host arrays in (by parameter number) -> host arrays out (live-outs, raw bytes
