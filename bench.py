@@ -1,0 +1,315 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: BERT-base b1/s128, one persistent-kernel launch per inference.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one inference (batch 1, 128 tokens) on every participating GPU; the GPUs run
+independent replicas (the path does not shard beyond batch, so there is no collective on
+the data path -- torch.distributed is used only for the barrier and the max-over-ranks of
+the measured time).  Rank 0 prints one JSON line.
+
+  value      samples/s of the whole job, inputs resident in HBM, device time (CUDA events)
+  e2e        the same through the public API with pinned HOST buffers: H2D of the three id
+             tensors, the launch, D2H of the hidden state, per step, wall clock
+  roofline   algorithmic bytes of one inference / measured kernel time vs the measured HBM peak
+  cpu_baseline  the fp32 CPU restatement (oracle/) timed on this box's host cores
+
+`--impl reference` times the reference's CPU path.  The reference's own TF-XLA CPU execution
+cannot run here (no TensorFlow), so the arm runs the CPU restatement under oracle/ with all
+host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "bert_base_b1_s128_samples_per_s"
+UNIT = "samples/s"
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised
+# in profiles/ (None until a capture exists)
+NCU_TRAFFIC_BYTES = None
+
+
+def measured_hbm_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.proc = None
+        self.index = device_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": float(max(mx)) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def replica_throughput(n_gpus: int, steps: int, max_seconds: float) -> float:
+    """Whole-job samples/s of `n_gpus` replicas that each ran `steps` inferences."""
+    return n_gpus * steps / max_seconds if max_seconds > 0 else 0.0
+
+
+def time_cpu_restatement(cfg, weights, inputs, budget_s: float = 15.0, max_iters: int = 100,
+                         warmup: int = 3):
+    """Bounded timing of the fp32 CPU restatement with all host threads."""
+    import torch
+    from oracle import ref_encoder
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    for _ in range(warmup):
+        ref_encoder.bert_encoder_torch(cfg, weights, inputs)
+    t0 = time.perf_counter()
+    n = 0
+    while n < max_iters and time.perf_counter() - t0 < budget_s:
+        ref_encoder.bert_encoder_torch(cfg, weights, inputs)
+        n += 1
+    dt = time.perf_counter() - t0
+    return n / dt, cores, n, dt
+
+
+def run_reference(args):
+    """The reference's CPU path on the host cores: rank 0 only."""
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    from mononn_b200 import bert_base, make_inputs, make_weights
+    cfg = bert_base()
+    w = make_weights(cfg, 1234)
+    inp = make_inputs(cfg, 1234)
+    per_step = max(1, min(20, int(100 / max(1, args.steps))))  # inferences per step (bounded)
+    import torch
+    from oracle import ref_encoder
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    for _ in range(args.warmup):
+        ref_encoder.bert_encoder_torch(cfg, w, inp)
+    t0 = time.perf_counter()
+    for _ in range(args.steps * per_step):
+        ref_encoder.bert_encoder_torch(cfg, w, inp)
+    dt = time.perf_counter() - t0
+    value = args.steps * per_step / dt
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "BERT-base encoder b1 s128, random-init N(0,0.02), ids uniform",
+                   "note": "TF-XLA CPU is not installable here; this is the fp32 CPU restatement "
+                           "(torch CPU ops) of the same graph"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"{per_step} inferences per step x {args.steps} steps"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    rank, world, local = dist_env()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the backend has no CPU path")
+    torch.cuda.set_device(local)
+    use_dist = world > 1
+    if use_dist:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    from mononn_b200 import bert_base, compile_encoder, make_inputs, make_weights
+    from mononn_b200.hlo_builder import bert_hlo
+    from mononn_b200 import compile_hlo
+
+    cfg = bert_base()
+    w = make_weights(cfg, 1234)
+    inp = make_inputs(cfg, 1234 + rank)
+    if args.frontend == "hlo":
+        text, names = bert_hlo(cfg)
+        mod = compile_hlo(text, device=local)
+        mod.set_weights({names[k]: v for k, v in w.items()})
+    else:
+        mod = compile_encoder(cfg, device=local)
+        mod.set_weights(w)
+    if args.tune:
+        mod.tune()
+    bufs = mod.allocate()
+    descs = mod.args()
+    params = sorted([d for d in descs if d["kind"] == 0], key=lambda d: d["param_number"])
+    out_desc = [d for d in descs if d["kind"] == 1][0]
+    host_in = [torch.from_numpy(inp[k]).contiguous().view(torch.uint8).reshape(-1).pin_memory()
+               for k in ("input_ids", "attention_mask", "token_type_ids")]
+    host_out = torch.empty(out_desc["bytes"], dtype=torch.uint8).pin_memory()
+    for d, h in zip(params, host_in):
+        bufs[d["index"]][: h.numel()].copy_(h)
+    flush = None if args.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def barrier():
+        torch.cuda.synchronize()
+        if use_dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing: K steps, each bracketed by its own event pair so that the
+    # L2 flush between steps stays outside the measured time
+    for _ in range(max(args.warmup, 3)):
+        mod.launch()
+    mod.status()
+    sampler = ClockSampler(local)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+          for _ in range(args.steps)]
+    barrier()
+    if rank == 0:
+        sampler.start()
+    for e0, e1 in ev:
+        if flush is not None:
+            flush.zero_()
+        e0.record()
+        mod.launch()
+        e1.record()
+    barrier()
+    mod.status()
+    dev_s = sum(e0.elapsed_time(e1) for e0, e1 in ev) * 1e-3
+
+    # ---- end to end through the public API with host buffers
+    def e2e_step():
+        for d, h in zip(params, host_in):
+            bufs[d["index"]][: h.numel()].copy_(h, non_blocking=True)
+        mod.launch()
+        host_out.copy_(bufs[out_desc["index"]][: host_out.numel()], non_blocking=True)
+        torch.cuda.synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    e2e_s = time.perf_counter() - t0
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    mod.status()
+
+    times = torch.tensor([dev_s, e2e_s], dtype=torch.float64, device="cuda")
+    if use_dist:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    dev_s, e2e_s = times.tolist()
+
+    if rank == 0:
+        alg_bytes, alg_flops = mod.cost()
+        peak, peak_kind = measured_hbm_peak()
+        us = dev_s / args.steps * 1e6
+        achieved = alg_bytes / (us * 1e-6) / 1e9
+        cpu = None
+        if world == 1 and not args.no_cpu:
+            v, cores, n, dt = time_cpu_restatement(cfg, w, inp)
+            cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
+                   "sample": f"{n} inferences of the same workload in {dt:.1f} s (torch CPU fp32)"}
+        h2d = sum(h.numel() for h in host_in)
+        line = {
+            "metric": METRIC, "value": replica_throughput(world, args.steps, dev_s), "unit": UNIT,
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": dev_s / args.steps * 1e3, "latency_us": us,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+            "data": "synthetic",
+            "config": {"workload": "BERT-base encoder b1 s128 (12 layers, hidden 768, FFN 3072), "
+                                   "random-init N(0,0.02), ids uniform, one launch per inference",
+                       "parallelism": f"replicas x{world} (no collective on the data path)",
+                       "frontend": args.frontend,
+                       "l2": "256 MiB device write between timed steps" if flush is not None
+                             else "no flush; 170 MB of weights per step exceed the 126 MB L2",
+                       "grid": mod.launch_config()["grid"][0], "stages": len(mod.plan()["stages"])},
+            "e2e": {"value": replica_throughput(world, args.steps, e2e_s), "unit": UNIT,
+                    "latency_us": e2e_s / args.steps * 1e6,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": int(host_out.numel())},
+            "gpu_launches": 2 * args.steps + max(args.warmup, 3) + 3,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES,
+                         "peak_source": peak_kind, "algorithmic_bytes": alg_bytes,
+                         "kernel_us": us},
+            "cpu_baseline": cpu,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    mod.close()
+    if use_dist:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--frontend", default="hlo", choices=["hlo", "builder"],
+                    help="lower from authored HLO text (the hook path) or the config builder")
+    ap.add_argument("--tune", action="store_true", help="run the on-device tile search first")
+    ap.add_argument("--no-flush", action="store_true", help="do not flush L2 between timed steps")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -148,6 +148,12 @@ int mononn_launch_stages(mononn_module* m, void* const* device_args, int n, void
 int mononn_trace_stages(mononn_module* m, void* const* device_args, int n, void* cuda_stream,
                         double* out, size_t cap, int* grid, int* n_stages);
 
+/* Test aid (host-side fault injection, no GPU fault involved): the next launch waits for
+ * `missing_arrivals` grid-barrier arrivals that no CTA will make, so its first bounded wait
+ * expires after barrier_timeout_us; the kernel then drains, returns, and
+ * mononn_last_status reports MONONN_ERR_BARRIER_TIMEOUT and restores the module. */
+int mononn_debug_skew_barrier(mononn_module* m, unsigned missing_arrivals);
+
 /* Algorithmic bytes and FLOPs of one inference (weights once + gathered rows + I/O). */
 int mononn_module_cost(const mononn_module* m, double* bytes, double* flops);
 

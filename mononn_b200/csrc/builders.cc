@@ -122,6 +122,7 @@ int build_bert_encoder(const EncoderConfig& c, FGraph* out, std::string* err) {
     e.seq = c.seq;
     e.vocab = c.vocab;
     e.eps = c.eps;
+    e.alpha = -10000.0f;  // additive mask (1 - m) * -10000, the HF convention
     g.ops.push_back(e);
   }
   for (uint32_t l = 0; l < c.layers; ++l) {

@@ -286,6 +286,12 @@ int mononn_trace_stages(mononn_module* m, void* const* device_args, int n, void*
   return MONONN_OK;
 }
 
+int mononn_debug_skew_barrier(mononn_module* m, unsigned missing_arrivals) {
+  if (!m) return fail(MONONN_ERR_INVALID_ARGUMENT, "null argument");
+  m->rt.skew_epoch(missing_arrivals);
+  return MONONN_OK;
+}
+
 int mononn_module_cost(const mononn_module* m, double* bytes, double* flops) {
   if (!m) return fail(MONONN_ERR_INVALID_ARGUMENT, "null argument");
   if (bytes) *bytes = m->rt.plan().algorithmic_bytes;

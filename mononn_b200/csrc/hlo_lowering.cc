@@ -1,0 +1,855 @@
+// HLO module -> fused operator graph.
+//
+// Replaces, for the hot path, the reference's parser + clustering passes:
+//   IRParserFused::from_hlo_module_impl     mononn_engine/parser/ir_parser_fused.cc:319-385
+//   initialize_custom_call (__cublas$gemm)  ir_parser_fused.cc:740-826, op_impl/gemm_impl.cc:182-253
+//   kLoop / kInput fusion -> cluster        ir_parser_fused.cc:489-539
+//   MergeDependent / ElementWiseConcatenation (vertical fusion)
+//                                           optimization/merge_dependent_pass.cc:37-190
+// The reference never fuses across a GEMM custom-call (its epilogue is alpha*AB + beta*C,
+// gemm_impl.cc:72-90); here the elementwise / reduce fusion that follows a GEMM becomes that
+// GEMM's epilogue (bias, activation, residual) or a LayerNorm stage fed by its accumulator,
+// and scores-GEMM -> softmax fusion -> PV-GEMM collapses into one attention operator.
+//
+// A fused computation is classified by hypothesis + numeric check (hlo_interp.h), so the
+// same arithmetic printed in a different instruction order is still recognised, and anything
+// that matches no hypothesis is rejected (the reference LOG(FATAL)s on unsupported input,
+// e.g. ir_parser_fused.cc:95,311; here the caller gets MONONN_ERR_UNSUPPORTED).
+#include "hlo_lowering.h"
+
+#include <algorithm>
+#include <cmath>
+#include <functional>
+
+#include "../../include/mononn.h"
+#include "hlo_interp.h"
+#include "hlo_parser.h"
+#include "json.h"
+
+namespace mononn {
+
+namespace {
+
+struct Rng {
+  uint64_t s = 0x9E3779B97F4A7C15ull;
+  float uni(float lo, float hi) {
+    s = s * 6364136223846793005ull + 1442695040888963407ull;
+    const float u = static_cast<float>((s >> 40) & 0xFFFFFF) / 16777216.0f;
+    return lo + (hi - lo) * u;
+  }
+};
+
+HTensor rand_tensor(const std::vector<int64_t>& dims, Rng& rng, float lo, float hi) {
+  HTensor t = HTensor::zeros(dims);
+  for (float& x : t.v) x = rng.uni(lo, hi);
+  return t;
+}
+
+bool all_close(const std::vector<float>& a, const std::vector<float>& b, float atol, float rtol) {
+  if (a.size() != b.size()) return false;
+  for (size_t i = 0; i < a.size(); ++i) {
+    const float d = std::fabs(a[i] - b[i]);
+    if (!(d <= atol + rtol * std::fabs(b[i]))) return false;
+  }
+  return true;
+}
+
+float act_ref(float x, ActKind k) {
+  switch (k) {
+    case ACT_GELU_ERF: return 0.5f * x * (1.0f + std::erf(x * 0.70710678118654752f));
+    case ACT_RELU: return std::max(x, 0.0f);
+    case ACT_QUICK_GELU: return x / (1.0f + std::exp(-1.702f * x));
+    case ACT_GELU_TANH:
+      return 0.5f * x * (1.0f + std::tanh(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+    default: return x;
+  }
+}
+
+struct Val {
+  enum Kind { NONE, ARG, CONST, ACT, GEMM, HEADS, SCORES, PROBS, ATTN, MASK, EMBED_SUM } kind = NONE;
+  int tensor = -1;  // FGraph tensor (ARG, CONST-as-instr, ACT, HEADS, MASK)
+  int op = -1;      // producing FGraph op (ACT, GEMM, HEADS, ATTN)
+  int instr = -1;   // HLO instruction that defines the (unaliased) value
+  uint32_t rows = 0, cols = 0;        // logical 2-D shape of ACT / GEMM
+  uint32_t B = 0, heads = 0, S = 0, D = 0;  // head-shaped values
+  int q_tensor = -1, k_tensor = -1;   // SCORES / PROBS
+  float alpha = 1.f;
+  int mask_tensor = -1;               // PROBS
+  float mask_scale = 0.f;             // MASK
+  int mask_arg = -1;                  // MASK: the s32 argument it derives from
+  int ids = -1, types = -1, word = -1, pos = -1, type = -1;  // EMBED_SUM (FGraph tensors)
+  uint32_t vocab = 0;
+};
+
+class Lowering {
+ public:
+  Lowering(const HloModule& m, FGraph* g, std::string* err) : m_(m), e_(m.comps[m.entry]), g_(*g), err_(err) {}
+
+  int run() {
+    g_ = FGraph();
+    g_.module_name = m_.name;
+    vals_.assign(e_.instrs.size(), Val());
+    uses_.assign(e_.instrs.size(), 0);
+    for (const HloInstr& i : e_.instrs)
+      for (int o : i.operands) uses_[o]++;
+    // parameters first: argument order is by parameter_number (mononn_module.cc:91-143)
+    for (size_t k = 0; k < e_.params.size(); ++k) {
+      if (e_.params[k] < 0) return fail(MONONN_ERR_PARSE, "parameter " + std::to_string(k) + " is missing");
+      const HloInstr& p = e_.instrs[e_.params[k]];
+      if (p.shape.is_tuple()) return unsupported(p, "tuple parameters");
+      ArgDesc a;
+      a.name = p.name;
+      a.kind = 0;
+      a.param_number = static_cast<int>(k);
+      a.bytes = static_cast<size_t>(p.shape.elements()) * p.shape.elem_bytes();
+      g_.args.push_back(a);
+      FTensor t;
+      t.name = p.name;
+      t.kind = TKind::Arg;
+      t.cols = p.shape.dims.empty() ? 1 : static_cast<uint32_t>(p.shape.dims.back());
+      t.rows = static_cast<uint32_t>(p.shape.elements() / std::max<uint32_t>(1, t.cols));
+      t.ld = t.cols;
+      t.elem_bytes = static_cast<uint32_t>(p.shape.elem_bytes());
+      t.arg_index = static_cast<int>(k);
+      Val v;
+      v.kind = Val::ARG;
+      v.tensor = g_.add_tensor(t);
+      v.instr = e_.params[k];
+      vals_[e_.params[k]] = v;
+    }
+    for (size_t idx = 0; idx < e_.instrs.size(); ++idx) {
+      const HloInstr& ins = e_.instrs[idx];
+      int rc = MONONN_OK;
+      if (ins.opcode == "parameter") continue;
+      if (ins.opcode == "constant") {
+        Val v;
+        v.kind = Val::CONST;
+        v.instr = static_cast<int>(idx);
+        vals_[idx] = v;
+      } else if (ins.opcode == "custom-call") {
+        rc = lower_custom_call(static_cast<int>(idx));
+      } else if (ins.opcode == "fusion") {
+        rc = lower_fusion(static_cast<int>(idx));
+      } else if (ins.opcode == "bitcast" || ins.opcode == "reshape" || ins.opcode == "copy") {
+        if (ins.operands.size() != 1) return unsupported(ins, "expects one operand");
+        const Val& s = vals_[ins.operands[0]];
+        if (s.kind != Val::ACT && s.kind != Val::ARG && s.kind != Val::CONST)
+          return unsupported(ins, "reshape of this kind of value at the top level");
+        if (ins.shape.elements() != e_.instrs[ins.operands[0]].shape.elements())
+          return unsupported(ins, "element count changes");
+        vals_[idx] = s;  // same buffer, row-major in both shapes
+      } else if (ins.opcode == "tuple") {
+        if (static_cast<int>(idx) != e_.root) return unsupported(ins, "tuple that is not the entry root");
+      } else {
+        // the reference wraps bare top-level ops into one-node clusters
+        // (optimization/clustering_single_node_pass.cc:41-219); none occurs on this path
+        return unsupported(ins, "top-level instruction outside {parameter, constant, fusion, custom-call, bitcast, tuple}");
+      }
+      if (rc) return rc;
+    }
+    int rc = finish_outputs();
+    if (rc) return rc;
+    return attach_mask();
+  }
+
+ private:
+  // ------------------------------------------------------------------ errors
+  int fail(int code, const std::string& msg) {
+    if (err_) *err_ = msg;
+    return code;
+  }
+  int unsupported(const HloInstr& ins, const std::string& why) {
+    return fail(MONONN_ERR_UNSUPPORTED, "%" + ins.name + " (" + ins.opcode + ", HLO line " +
+                                            std::to_string(ins.line) + "): " + why);
+  }
+
+  // ----------------------------------------------------------------- tensors
+  int const_tensor(int instr, uint32_t rows, uint32_t cols, bool transposed = false) {
+    const HloInstr& c = e_.instrs[instr];
+    auto it = const_tensors_.find(instr);
+    if (it != const_tensors_.end()) return it->second;
+    FTensor t;
+    t.name = c.name;
+    t.kind = TKind::Const;
+    t.rows = rows;
+    t.cols = cols;
+    t.ld = cols;
+    t.elem_bytes = static_cast<uint32_t>(c.shape.elem_bytes());
+    t.const_name = c.name;
+    t.const_transposed = transposed;
+    for (int64_t d : c.shape.dims) t.const_dims.push_back(static_cast<uint32_t>(d));
+    return const_tensors_[instr] = g_.add_tensor(t);
+  }
+  int act_tensor(const std::string& name, uint32_t rows, uint32_t cols) {
+    FTensor t;
+    t.name = name;
+    t.kind = TKind::ActF16;
+    t.rows = rows;
+    t.cols = cols;
+    t.ld = cols;
+    return g_.add_tensor(t);
+  }
+  bool is_f16(const HloInstr& i) const { return i.shape.dtype == "f16"; }
+
+  // Runs a fused computation on probe inputs.
+  int probe(const HloComputation& c, const std::vector<HTensor>& params, HTensor* out) {
+    std::string e;
+    int rc = eval_computation(m_, c, params, out, &e);
+    if (rc) return fail(rc, "fused computation " + c.name + ": " + e);
+    return MONONN_OK;
+  }
+  // Probe tensors shaped like the fusion's parameters; `fill` decides the contents.
+  std::vector<HTensor> probe_inputs(const HloComputation& c,
+                                    const std::function<void(size_t, HTensor&)>& fill) {
+    std::vector<HTensor> ps(c.params.size());
+    for (size_t k = 0; k < c.params.size(); ++k) {
+      ps[k] = HTensor::zeros(c.instrs[c.params[k]].shape.dims);
+      fill(k, ps[k]);
+    }
+    return ps;
+  }
+
+  // ------------------------------------------------------------- custom-call
+  int lower_custom_call(int idx) {
+    const HloInstr& ins = e_.instrs[idx];
+    const std::string target = ins.attr("custom_call_target");
+    if (target != "__cublas$gemm")  // custom_call.cc:96-103 accepts this and __cudnn$convForward
+      return unsupported(ins, "custom-call target " + target + " (only __cublas$gemm is on this path)");
+    if (ins.operands.size() != 2) return unsupported(ins, "GEMM with a C operand (beta != 0)");
+    Json cfg;
+    std::string je;
+    if (!Json::parse(ins.attr("backend_config"), &cfg, &je))
+      return fail(MONONN_ERR_PARSE, "%" + ins.name + ": backend_config is not JSON: " + je);
+    const Json* dn = cfg.find("dot_dimension_numbers");
+    if (!dn) return fail(MONONN_ERR_PARSE, "%" + ins.name + ": backend_config lacks dot_dimension_numbers");
+    auto list = [&](const char* key) {
+      std::vector<int> v;
+      if (const Json* a = dn->find(key))
+        if (a->is_array())
+          for (const Json& x : a->arr) v.push_back(static_cast<int>(x.as_number()));
+      return v;
+    };
+    const auto lc = list("lhs_contracting_dimensions"), rc_ = list("rhs_contracting_dimensions");
+    const auto lb = list("lhs_batch_dimensions"), rb = list("rhs_batch_dimensions");
+    if (lc.size() != 1 || rc_.size() != 1) return unsupported(ins, "exactly one contracting dimension per side");
+    if (cfg.get_number("beta", 0) != 0 || cfg.get_number("alpha_imag", 0) != 0)
+      return unsupported(ins, "beta or imaginary alpha");
+    const float alpha = static_cast<float>(cfg.get_number("alpha_real", 1));
+    const HloInstr& lhs = e_.instrs[ins.operands[0]];
+    const HloInstr& rhs = e_.instrs[ins.operands[1]];
+    if (!is_f16(lhs) || !is_f16(rhs) || !is_f16(ins))
+      return unsupported(ins, "GEMM operand types other than f16 (accumulation is fp32)");
+    const Val& a = vals_[ins.operands[0]];
+    const Val& b = vals_[ins.operands[1]];
+
+    if (lb.empty() && rb.empty()) {
+      // ---- dense layer: activation [M,K] x constant weight
+      if (a.kind != Val::ACT) return unsupported(ins, "left operand is not a materialised activation");
+      if (b.kind != Val::CONST) return unsupported(ins, "right operand is not a constant weight");
+      if (lhs.shape.dims.size() != 2 || rhs.shape.dims.size() != 2 || lc[0] != 1)
+        return unsupported(ins, "left operand must be [M,K] contracting its last dimension");
+      const uint32_t M = static_cast<uint32_t>(lhs.shape.dims[0]), K = static_cast<uint32_t>(lhs.shape.dims[1]);
+      const bool transposed = (rc_[0] == 1);
+      const uint32_t Kw = static_cast<uint32_t>(rhs.shape.dims[transposed ? 1 : 0]);
+      const uint32_t N = static_cast<uint32_t>(rhs.shape.dims[transposed ? 0 : 1]);
+      if (Kw != K || a.rows != M || a.cols != K) return unsupported(ins, "operand shapes are inconsistent");
+      FOp o;
+      o.kind = OP_GEMM;
+      o.name = canonical_node_name(ins.name);
+      o.a = a.tensor;
+      o.w = const_tensor(b.instr, K, N, transposed);
+      o.M = M;
+      o.N = N;
+      o.K = K;
+      o.alpha = alpha;
+      g_.ops.push_back(o);
+      Val v;
+      v.kind = Val::GEMM;
+      v.op = static_cast<int>(g_.ops.size()) - 1;
+      v.instr = idx;
+      v.rows = M;
+      v.cols = N;
+      vals_[idx] = v;
+      return MONONN_OK;
+    }
+    // ---- batched over (batch, head): the two GEMMs of attention
+    if (lb != std::vector<int>{0, 1} || rb != std::vector<int>{0, 1} || lhs.shape.dims.size() != 4)
+      return unsupported(ins, "batched GEMM other than [B,heads,.,.] x [B,heads,.,.]");
+    if (a.kind == Val::HEADS && b.kind == Val::HEADS && lc[0] == 3 && rc_[0] == 3) {
+      Val v;
+      v.kind = Val::SCORES;
+      v.instr = idx;
+      v.q_tensor = a.tensor;
+      v.k_tensor = b.tensor;
+      v.alpha = alpha;
+      v.B = a.B; v.heads = a.heads; v.S = a.S; v.D = a.D;
+      if (b.B != a.B || b.heads != a.heads || b.S != a.S || b.D != a.D)
+        return unsupported(ins, "query and key shapes differ");
+      vals_[idx] = v;
+      return MONONN_OK;
+    }
+    if (a.kind == Val::PROBS && b.kind == Val::HEADS && lc[0] == 3 && rc_[0] == 2) {
+      if (alpha != 1.f) return unsupported(ins, "alpha on the probability x value GEMM");
+      if (uses_[b.instr] != 1) return unsupported(ins, "value tensor has other consumers");
+      FTensor& vt = g_.tensors[b.tensor];
+      vt.kind = TKind::ActF16T;  // the V projection writes its output transposed per batch
+      vt.batches = b.B;
+      vt.seq = b.S;
+      vt.ld = (b.S + 7) / 8 * 8;
+      FOp o;
+      o.kind = OP_ATTENTION;
+      o.name = canonical_node_name(ins.name);
+      o.q = a.q_tensor;
+      o.k = a.k_tensor;
+      o.vt = b.tensor;
+      o.mask = a.mask_tensor;
+      o.heads = a.heads;
+      o.seq = a.S;
+      o.batches = a.B;
+      o.head_dim = a.D;
+      o.alpha = a.alpha;
+      g_.ops.push_back(o);
+      Val v;
+      v.kind = Val::ATTN;
+      v.op = static_cast<int>(g_.ops.size()) - 1;
+      v.instr = idx;
+      v.B = a.B; v.heads = a.heads; v.S = a.S; v.D = a.D;
+      vals_[idx] = v;
+      return MONONN_OK;
+    }
+    return unsupported(ins, "batched GEMM that is neither Q.K^T nor P.V of an attention block");
+  }
+
+  // ------------------------------------------------------------------ fusion
+  int lower_fusion(int idx) {
+    const HloInstr& ins = e_.instrs[idx];
+    const HloComputation* c = m_.find(ins.attr("calls"));
+    if (!c) return fail(MONONN_ERR_PARSE, "%" + ins.name + ": fused computation " + ins.attr("calls") + " not found");
+    if (c->params.size() != ins.operands.size())
+      return fail(MONONN_ERR_PARSE, "%" + ins.name + ": operand count does not match " + c->name);
+    if (ins.shape.is_tuple()) return unsupported(ins, "multi-output fusion");
+    bool has_reduce = false, has_gather = false;
+    for (const HloInstr& i : c->instrs) {
+      has_reduce = has_reduce || i.opcode == "reduce";
+      has_gather = has_gather || i.opcode == "gather";
+    }
+    if (has_gather) return lower_embed_sum(idx, *c);
+    // the "main" operand: same element count as the result and not a constant
+    int main_k = -1;
+    for (size_t k = 0; k < ins.operands.size(); ++k) {
+      const Val& v = vals_[ins.operands[k]];
+      if (v.kind == Val::CONST || v.kind == Val::NONE || v.kind == Val::MASK) continue;
+      if (e_.instrs[ins.operands[k]].shape.elements() != ins.shape.elements()) continue;
+      if (main_k < 0 || v.kind == Val::GEMM) main_k = static_cast<int>(k);
+    }
+    if (main_k < 0) return unsupported(ins, "fusion without a tensor operand of the result's size");
+    const Val& mv = vals_[ins.operands[main_k]];
+    switch (mv.kind) {
+      case Val::GEMM:
+        return has_reduce ? lower_layernorm(idx, *c, main_k) : lower_epilogue(idx, *c, main_k);
+      case Val::ACT:
+      case Val::EMBED_SUM:
+        if (has_reduce) return lower_layernorm(idx, *c, main_k);
+        return unsupported(ins, "elementwise fusion that does not follow a GEMM");
+      case Val::SCORES:
+        return lower_softmax(idx, *c, main_k);
+      case Val::ATTN:
+        return lower_merge(idx, *c, main_k);
+      case Val::ARG:
+        return lower_mask(idx, *c, main_k);
+      default:
+        return unsupported(ins, "fusion over this kind of value");
+    }
+  }
+
+  // bias / activation / residual (/ head split) after a GEMM -> that GEMM's epilogue
+  int lower_epilogue(int idx, const HloComputation& c, int main_k) {
+    const HloInstr& ins = e_.instrs[idx];
+    Val gv = vals_[ins.operands[main_k]];
+    if (uses_[gv.instr] != 1) return unsupported(ins, "GEMM result with more than one consumer");
+    FOp& gop = g_.ops[gv.op];
+    const uint32_t M = gop.M, N = gop.N;
+    int bias_k = -1, resid_k = -1;
+    for (size_t k = 0; k < ins.operands.size(); ++k) {
+      if (static_cast<int>(k) == main_k) continue;
+      const Val& v = vals_[ins.operands[k]];
+      const HloInstr& oi = e_.instrs[ins.operands[k]];
+      if (v.kind == Val::CONST && oi.shape.elements() == N && bias_k < 0) bias_k = static_cast<int>(k);
+      else if (v.kind == Val::ACT && v.rows == M && v.cols == N && resid_k < 0) resid_k = static_cast<int>(k);
+      else return unsupported(ins, "operand %" + oi.name + " has no role in a GEMM epilogue");
+    }
+    // result layout: [M,N] row-major, or [B,heads,S,D] with B*S = M and heads*D = N
+    bool split = false;
+    uint32_t B = 0, H = 0, S = 0, D = 0;
+    const auto& od = ins.shape.dims;
+    if (od.size() == 4 && od[0] * od[2] == M && od[1] * od[3] == N) {
+      split = true;
+      B = static_cast<uint32_t>(od[0]); H = static_cast<uint32_t>(od[1]);
+      S = static_cast<uint32_t>(od[2]); D = static_cast<uint32_t>(od[3]);
+    } else if (ins.shape.elements() != static_cast<int64_t>(M) * N) {
+      return unsupported(ins, "result shape");
+    }
+    Rng rng;
+    std::vector<HTensor> ps = probe_inputs(c, [&](size_t k, HTensor& t) {
+      for (float& x : t.v) x = rng.uni(-2.f, 2.f);
+      (void)k;
+    });
+    HTensor got;
+    int rc = probe(c, ps, &got);
+    if (rc) return rc;
+    const HTensor& x = ps[main_k];
+    ActKind found = ACT_NONE;
+    bool ok = false;
+    for (ActKind act : {ACT_NONE, ACT_GELU_ERF, ACT_RELU, ACT_QUICK_GELU, ACT_GELU_TANH}) {
+      std::vector<float> want(static_cast<size_t>(M) * N);
+      for (uint32_t r = 0; r < M; ++r)
+        for (uint32_t col = 0; col < N; ++col) {
+          float y = x.v[static_cast<size_t>(r) * N + col];
+          if (bias_k >= 0) y += ps[bias_k].v[col];
+          y = act_ref(y, act);
+          if (resid_k >= 0) y += ps[resid_k].v[static_cast<size_t>(r) * N + col];
+          size_t dst = static_cast<size_t>(r) * N + col;
+          if (split) {
+            const uint32_t b = r / S, s = r % S, h = col / D, d = col % D;
+            dst = ((static_cast<size_t>(b) * H + h) * S + s) * D + d;
+          }
+          want[dst] = y;
+        }
+      if (all_close(got.v, want, 1e-4f, 1e-4f)) {
+        found = act;
+        ok = true;
+        break;
+      }
+    }
+    if (!ok) return unsupported(ins, "fused computation " + c.name + " matches no epilogue form act(x + bias) + residual");
+    if (bias_k >= 0) gop.bias = const_tensor(vals_[ins.operands[bias_k]].instr, 1, N);
+    if (resid_k >= 0) gop.resid = vals_[ins.operands[resid_k]].tensor;
+    gop.act = found;
+    gop.out = act_tensor(canonical_node_name(ins.name), M, N);
+    Val v;
+    v.instr = idx;
+    v.tensor = gop.out;
+    v.op = gv.op;
+    v.rows = M;
+    v.cols = N;
+    if (split) {
+      if (D != 64) return unsupported(ins, "head dimension other than 64");
+      v.kind = Val::HEADS;
+      v.B = B; v.heads = H; v.S = S; v.D = D;
+    } else {
+      v.kind = Val::ACT;
+    }
+    vals_[idx] = v;
+    return MONONN_OK;
+  }
+
+  // LayerNorm of (x [+ bias] [+ residual]) where x is a GEMM result, an activation or the
+  // embedding sum.
+  int lower_layernorm(int idx, const HloComputation& c, int main_k) {
+    const HloInstr& ins = e_.instrs[idx];
+    const Val mv = vals_[ins.operands[main_k]];
+    if (ins.shape.dims.empty()) return unsupported(ins, "scalar LayerNorm result");
+    const uint32_t cols = static_cast<uint32_t>(ins.shape.dims.back());
+    const uint32_t rows = static_cast<uint32_t>(ins.shape.elements() / cols);
+    std::vector<int> vec_k;
+    int resid_k = -1;
+    for (size_t k = 0; k < ins.operands.size(); ++k) {
+      if (static_cast<int>(k) == main_k) continue;
+      const Val& v = vals_[ins.operands[k]];
+      const HloInstr& oi = e_.instrs[ins.operands[k]];
+      if (v.kind == Val::CONST && oi.shape.elements() == cols) vec_k.push_back(static_cast<int>(k));
+      else if (v.kind == Val::ACT && v.rows == rows && v.cols == cols && resid_k < 0) resid_k = static_cast<int>(k);
+      else return unsupported(ins, "operand %" + oi.name + " has no role in a LayerNorm fusion");
+    }
+    if (vec_k.size() < 2 || vec_k.size() > 3) return unsupported(ins, "expected scale, shift and at most one bias vector");
+    std::vector<float> eps_cands;
+    for (const HloInstr& i : c.instrs)
+      if (i.opcode == "constant" && i.literal_is_scalar && i.literal > 0 && i.literal < 0.1)
+        eps_cands.push_back(static_cast<float>(i.literal));
+    if (eps_cands.empty()) eps_cands.push_back(0.f);
+    // Probe with small-magnitude rows (variance ~1e-4) so that the epsilon under the square
+    // root changes the result visibly; scale/shift stay O(1).
+    Rng rng;
+    std::vector<HTensor> ps = probe_inputs(c, [&](size_t k, HTensor& t) {
+      const bool is_vec = std::find(vec_k.begin(), vec_k.end(), static_cast<int>(k)) != vec_k.end();
+      for (float& x : t.v) x = is_vec ? rng.uni(0.5f, 1.5f) : rng.uni(-0.02f, 0.02f);
+    });
+    HTensor got;
+    int rc = probe(c, ps, &got);
+    if (rc) return rc;
+    // closed form for a given assignment of the vectors to (bias?, gamma, beta) and epsilon
+    std::vector<float> want(static_cast<size_t>(rows) * cols), sum(cols);
+    auto max_error = [&](int bk, int gk, int ek, float eps, uint32_t n_rows) {
+      float worst = 0.f;
+      for (uint32_t r = 0; r < n_rows; ++r) {
+        double mean = 0;
+        for (uint32_t j = 0; j < cols; ++j) {
+          float y = ps[main_k].v[static_cast<size_t>(r) * cols + j];
+          if (bk >= 0) y += ps[bk].v[j];
+          if (resid_k >= 0) y += ps[resid_k].v[static_cast<size_t>(r) * cols + j];
+          sum[j] = y;
+          mean += y;
+        }
+        mean /= cols;
+        double var = 0;
+        for (uint32_t j = 0; j < cols; ++j) var += (sum[j] - mean) * (sum[j] - mean);
+        var /= cols;
+        const double rstd = 1.0 / std::sqrt(var + eps);
+        for (uint32_t j = 0; j < cols; ++j) {
+          const float w = static_cast<float>((sum[j] - mean) * rstd) * ps[gk].v[j] + ps[ek].v[j];
+          worst = std::max(worst, std::fabs(w - got.v[static_cast<size_t>(r) * cols + j]));
+        }
+      }
+      return worst;
+    };
+    std::vector<int> perm = vec_k;
+    std::sort(perm.begin(), perm.end());
+    int bias_k = -1, gamma_k = -1, beta_k = -1;
+    float eps_found = 0.f, best = 1e30f;
+    do {
+      const int bk = perm.size() == 3 ? perm[0] : -1;
+      const int gk = perm[perm.size() - 2], ek = perm[perm.size() - 1];
+      for (float eps : eps_cands) {
+        const float e = max_error(bk, gk, ek, eps, std::min<uint32_t>(rows, 4));
+        if (e < best) {
+          best = e;
+          bias_k = bk; gamma_k = gk; beta_k = ek;
+          eps_found = eps;
+        }
+      }
+    } while (std::next_permutation(perm.begin(), perm.end()));
+    const bool ok = best < 1e-3f && max_error(bias_k, gamma_k, beta_k, eps_found, rows) < 1e-3f;
+    if (!ok) return unsupported(ins, "fused computation " + c.name + " matches no LayerNorm(x + bias + residual) form");
+
+    FOp n;
+    n.kind = OP_LAYERNORM;
+    n.name = canonical_node_name(ins.name);
+    n.rows = rows;
+    n.cols = cols;
+    n.eps = eps_found;
+    n.gamma = const_tensor(vals_[ins.operands[gamma_k]].instr, 1, cols);
+    n.beta = const_tensor(vals_[ins.operands[beta_k]].instr, 1, cols);
+    if (mv.kind == Val::GEMM) {
+      if (uses_[mv.instr] != 1) return unsupported(ins, "GEMM result with more than one consumer");
+      FOp& gop = g_.ops[mv.op];
+      if (gop.M != rows || gop.N != cols) return unsupported(ins, "GEMM and LayerNorm shapes differ");
+      if (bias_k >= 0) gop.bias = const_tensor(vals_[ins.operands[bias_k]].instr, 1, cols);
+      if (resid_k >= 0) gop.resid = vals_[ins.operands[resid_k]].tensor;
+      FTensor acc;
+      acc.name = gop.name + "_sum";
+      acc.kind = TKind::AccF32;
+      acc.rows = rows;
+      acc.cols = cols;
+      acc.ld = cols;
+      acc.elem_bytes = 4;
+      gop.out = g_.add_tensor(acc);
+      n.src = gop.out;
+      n.flags = F_ZERO_SRC;
+    } else if (mv.kind == Val::EMBED_SUM) {
+      if (bias_k >= 0 || resid_k >= 0) return unsupported(ins, "bias or residual on the embedding LayerNorm");
+      n.kind = OP_EMBED;
+      n.ids = mv.ids;
+      n.type_ids = mv.types;
+      n.word = mv.word;
+      n.pos = mv.pos;
+      n.type = mv.type;
+      n.seq = mv.S;
+      n.vocab = mv.vocab;
+      n.alpha = -10000.f;
+    } else {
+      if (bias_k >= 0) return unsupported(ins, "bias vector on a LayerNorm that does not follow a GEMM");
+      n.src = mv.tensor;
+      if (resid_k >= 0) n.resid = vals_[ins.operands[resid_k]].tensor;
+    }
+    n.out = act_tensor(n.name, rows, cols);
+    g_.ops.push_back(n);
+    Val v;
+    v.kind = Val::ACT;
+    v.instr = idx;
+    v.tensor = n.out;
+    v.op = static_cast<int>(g_.ops.size()) - 1;
+    v.rows = rows;
+    v.cols = cols;
+    vals_[idx] = v;
+    return MONONN_OK;
+  }
+
+  // softmax(scores + mask) over the keys
+  int lower_softmax(int idx, const HloComputation& c, int main_k) {
+    const HloInstr& ins = e_.instrs[idx];
+    const Val sv = vals_[ins.operands[main_k]];
+    if (uses_[sv.instr] != 1) return unsupported(ins, "attention scores with more than one consumer");
+    int mask_k = -1;
+    for (size_t k = 0; k < ins.operands.size(); ++k) {
+      if (static_cast<int>(k) == main_k) continue;
+      if (vals_[ins.operands[k]].kind == Val::MASK && mask_k < 0) mask_k = static_cast<int>(k);
+      else return unsupported(ins, "operand %" + e_.instrs[ins.operands[k]].name + " has no role in a softmax fusion");
+    }
+    const uint32_t B = sv.B, H = sv.heads, S = sv.S;
+    if (ins.shape.dims != std::vector<int64_t>{B, H, S, S}) return unsupported(ins, "result shape");
+    // probe on a reduced number of rows would need a different computation; scores are small
+    Rng rng;
+    std::vector<HTensor> ps = probe_inputs(c, [&](size_t k, HTensor& t) {
+      for (float& x : t.v) x = (static_cast<int>(k) == mask_k) ? (rng.uni(0.f, 1.f) < 0.25f ? -50.f : 0.f)
+                                                               : rng.uni(-4.f, 4.f);
+    });
+    HTensor got;
+    int rc = probe(c, ps, &got);
+    if (rc) return rc;
+    std::vector<float> want(got.v.size());
+    for (uint32_t b = 0; b < B; ++b)
+      for (uint32_t h = 0; h < H; ++h)
+        for (uint32_t q = 0; q < S; ++q) {
+          const size_t base = ((static_cast<size_t>(b) * H + h) * S + q) * S;
+          float mx = -INFINITY;
+          for (uint32_t k = 0; k < S; ++k) {
+            const float z = ps[main_k].v[base + k] + (mask_k >= 0 ? ps[mask_k].v[static_cast<size_t>(b) * S + k] : 0.f);
+            want[base + k] = z;
+            mx = std::max(mx, z);
+          }
+          double sum = 0;
+          for (uint32_t k = 0; k < S; ++k) {
+            want[base + k] = std::exp(want[base + k] - mx);
+            sum += want[base + k];
+          }
+          for (uint32_t k = 0; k < S; ++k) want[base + k] = static_cast<float>(want[base + k] / sum);
+        }
+    if (!all_close(got.v, want, 1e-5f, 1e-4f))
+      return unsupported(ins, "fused computation " + c.name + " is not softmax(scores + mask) over the last dimension");
+    Val v = sv;
+    v.kind = Val::PROBS;
+    v.instr = idx;
+    v.mask_tensor = mask_k >= 0 ? vals_[ins.operands[mask_k]].tensor : -1;
+    vals_[idx] = v;
+    return MONONN_OK;
+  }
+
+  // [B,heads,S,D] -> [B*S, heads*D]
+  int lower_merge(int idx, const HloComputation& c, int main_k) {
+    const HloInstr& ins = e_.instrs[idx];
+    const Val av = vals_[ins.operands[main_k]];
+    if (ins.operands.size() != 1) return unsupported(ins, "extra operands on a head-merge fusion");
+    if (uses_[av.instr] != 1) return unsupported(ins, "attention output with more than one consumer");
+    const uint32_t B = av.B, H = av.heads, S = av.S, D = av.D;
+    if (ins.shape.elements() != static_cast<int64_t>(B) * H * S * D) return unsupported(ins, "result shape");
+    Rng rng;
+    std::vector<HTensor> ps = probe_inputs(c, [&](size_t, HTensor& t) {
+      for (float& x : t.v) x = rng.uni(-1.f, 1.f);
+    });
+    HTensor got;
+    int rc = probe(c, ps, &got);
+    if (rc) return rc;
+    std::vector<float> want(got.v.size());
+    for (uint32_t b = 0; b < B; ++b)
+      for (uint32_t h = 0; h < H; ++h)
+        for (uint32_t s = 0; s < S; ++s)
+          for (uint32_t d = 0; d < D; ++d)
+            want[(static_cast<size_t>(b) * S + s) * H * D + h * D + d] =
+                ps[0].v[((static_cast<size_t>(b) * H + h) * S + s) * D + d];
+    if (!all_close(got.v, want, 0.f, 0.f))
+      return unsupported(ins, "fused computation " + c.name + " is not the head merge [B,h,S,d] -> [B*S, h*d]");
+    FOp& aop = g_.ops[av.op];
+    aop.out = act_tensor(canonical_node_name(ins.name), B * S, H * D);
+    Val v;
+    v.kind = Val::ACT;
+    v.instr = idx;
+    v.tensor = aop.out;
+    v.op = av.op;
+    v.rows = B * S;
+    v.cols = H * D;
+    vals_[idx] = v;
+    return MONONN_OK;
+  }
+
+  // additive attention mask (1 - m) * c from the integer mask argument
+  int lower_mask(int idx, const HloComputation& c, int main_k) {
+    const HloInstr& ins = e_.instrs[idx];
+    if (ins.operands.size() != 1) return unsupported(ins, "extra operands on a mask fusion");
+    const Val mv = vals_[ins.operands[main_k]];
+    const HloInstr& mi = e_.instrs[ins.operands[main_k]];
+    if (mi.shape.dtype != "s32" || ins.shape.dims.size() != 2) return unsupported(ins, "mask must be s32 [B,S]");
+    Rng rng;
+    std::vector<HTensor> zero = probe_inputs(c, [&](size_t, HTensor&) {});
+    HTensor z;
+    int rc = probe(c, zero, &z);
+    if (rc) return rc;
+    const float scale = z.v.empty() ? 0.f : z.v[0];
+    std::vector<HTensor> ps = probe_inputs(c, [&](size_t, HTensor& t) {
+      for (float& x : t.v) x = rng.uni(0.f, 1.f) < 0.5f ? 0.f : 1.f;
+    });
+    HTensor got;
+    rc = probe(c, ps, &got);
+    if (rc) return rc;
+    std::vector<float> want(got.v.size());
+    for (size_t i = 0; i < want.size(); ++i) want[i] = (1.0f - ps[0].v[i]) * scale;
+    if (!all_close(got.v, want, 1e-3f, 1e-5f))
+      return unsupported(ins, "fused computation " + c.name + " is not the additive mask (1 - m) * c");
+    FTensor t;
+    t.name = canonical_node_name(ins.name);
+    t.kind = TKind::VecF32;
+    t.rows = static_cast<uint32_t>(ins.shape.elements());
+    t.cols = 1;
+    t.elem_bytes = 4;
+    Val v;
+    v.kind = Val::MASK;
+    v.instr = idx;
+    v.tensor = g_.add_tensor(t);
+    v.mask_scale = scale;
+    v.mask_arg = mv.tensor;
+    vals_[idx] = v;
+    masks_.push_back(v);
+    return MONONN_OK;
+  }
+
+  // word[ids] + position[0:S] + type[type_ids]
+  int lower_embed_sum(int idx, const HloComputation& c) {
+    const HloInstr& ins = e_.instrs[idx];
+    // roles from the structure: gather(table param, index param), slice(position table param)
+    auto param_of = [&](int i) {
+      while (c.instrs[i].opcode != "parameter") {
+        const std::string& o = c.instrs[i].opcode;
+        if ((o == "convert" || o == "reshape" || o == "bitcast" || o == "copy") && c.instrs[i].operands.size() == 1)
+          i = c.instrs[i].operands[0];
+        else
+          return -1;
+      }
+      return static_cast<int>(c.instrs[i].param_number);
+    };
+    std::vector<std::pair<int, int>> gathers;  // (table param, index param)
+    int pos_param = -1;
+    for (const HloInstr& i : c.instrs) {
+      if (i.opcode == "gather" && i.operands.size() == 2)
+        gathers.push_back({param_of(i.operands[0]), param_of(i.operands[1])});
+      if (i.opcode == "slice" && i.operands.size() == 1) pos_param = param_of(i.operands[0]);
+    }
+    if (gathers.empty() || gathers.size() > 2 || pos_param < 0)
+      return unsupported(ins, "embedding fusion must be word gather + position slice (+ type gather)");
+    for (auto& gp : gathers)
+      if (gp.first < 0 || gp.second < 0) return unsupported(ins, "gather operands must come from fusion parameters");
+    if (ins.shape.dims.size() != 2) return unsupported(ins, "embedding sum must be [tokens, hidden]");
+    const uint32_t T = static_cast<uint32_t>(ins.shape.dims[0]), H = static_cast<uint32_t>(ins.shape.dims[1]);
+    const HloInstr& ids_i = e_.instrs[ins.operands[gathers[0].second]];
+    if (ids_i.shape.dims.size() != 2 || ids_i.shape.elements() != T) return unsupported(ins, "ids must be [B,S]");
+    const uint32_t B = static_cast<uint32_t>(ids_i.shape.dims[0]), S = static_cast<uint32_t>(ids_i.shape.dims[1]);
+    // numeric check
+    Rng rng;
+    std::vector<HTensor> ps = probe_inputs(c, [&](size_t k, HTensor& t) {
+      const HloInstr& pi = c.instrs[c.params[k]];
+      if (pi.shape.dtype == "s32") {
+        int64_t rows = 1;
+        for (auto& gp : gathers)
+          if (gp.second == static_cast<int>(k)) rows = c.instrs[c.params[gp.first]].shape.dims[0];
+        for (float& x : t.v) x = std::floor(rng.uni(0.f, static_cast<float>(rows) - 0.001f));
+      } else {
+        for (float& x : t.v) x = rng.uni(-1.f, 1.f);
+      }
+    });
+    HTensor got;
+    int rc = probe(c, ps, &got);
+    if (rc) return rc;
+    std::vector<float> want(static_cast<size_t>(T) * H);
+    for (uint32_t t = 0; t < T; ++t)
+      for (uint32_t j = 0; j < H; ++j) {
+        float y = ps[pos_param].v[static_cast<size_t>(t % S) * H + j];
+        for (auto& gp : gathers)
+          y += ps[gp.first].v[static_cast<size_t>(ps[gp.second].v[t]) * H + j];
+        want[static_cast<size_t>(t) * H + j] = y;
+      }
+    if (!all_close(got.v, want, 1e-5f, 1e-5f))
+      return unsupported(ins, "fused computation " + c.name + " is not word[ids] + position[0:S] + type[type_ids]");
+    if (uses_[idx] != 1) return unsupported(ins, "embedding sum with more than one consumer");
+    auto table = [&](int param) {
+      const int instr = vals_[ins.operands[param]].instr;
+      const HloInstr& ti = e_.instrs[instr];
+      return const_tensor(instr, static_cast<uint32_t>(ti.shape.dims[0]), static_cast<uint32_t>(ti.shape.dims[1]));
+    };
+    for (int p : {gathers[0].first, pos_param})
+      if (vals_[ins.operands[p]].kind != Val::CONST) return unsupported(ins, "embedding tables must be constants");
+    Val v;
+    v.kind = Val::EMBED_SUM;
+    v.instr = idx;
+    v.rows = T;
+    v.cols = H;
+    v.B = B;
+    v.S = S;
+    v.ids = vals_[ins.operands[gathers[0].second]].tensor;
+    v.word = table(gathers[0].first);
+    v.vocab = g_.tensors[v.word].rows;
+    v.pos = table(pos_param);
+    if (gathers.size() == 2) {
+      if (vals_[ins.operands[gathers[1].first]].kind != Val::CONST) return unsupported(ins, "type table must be a constant");
+      v.types = vals_[ins.operands[gathers[1].second]].tensor;
+      v.type = table(gathers[1].first);
+    }
+    vals_[idx] = v;
+    return MONONN_OK;
+  }
+
+  // ------------------------------------------------------------------ outputs
+  int finish_outputs() {
+    const HloInstr& root = e_.instrs[e_.root];
+    std::vector<int> outs;
+    if (root.opcode == "tuple") outs = root.operands;
+    else outs.push_back(e_.root);
+    const int n_params = static_cast<int>(e_.params.size());
+    int ordinal = 0;
+    for (int o : outs) {
+      const Val& v = vals_[o];
+      const HloInstr& oi = e_.instrs[o];
+      if (v.kind != Val::ACT || v.op < 0)
+        return unsupported(oi, "module output must be the result of a fused operator");
+      ArgDesc a;
+      a.name = oi.name;
+      a.kind = 1;
+      a.param_number = ordinal;
+      a.bytes = static_cast<size_t>(oi.shape.elements()) * oi.shape.elem_bytes();
+      g_.args.push_back(a);
+      // the producing operator writes straight into the live-out buffer
+      FTensor& t = g_.tensors[v.tensor];
+      t.kind = TKind::Arg;
+      t.arg_index = n_params + ordinal;
+      t.name = oi.name;
+      ++ordinal;
+    }
+    return MONONN_OK;
+  }
+
+  // The additive mask is computed by the embedding stage (same launch, stage 0).
+  int attach_mask() {
+    if (masks_.empty()) return MONONN_OK;
+    bool used = false;
+    for (const FOp& o : g_.ops)
+      if (o.kind == OP_ATTENTION && o.mask >= 0) used = true;
+    if (!used) return MONONN_OK;
+    if (masks_.size() > 1) return fail(MONONN_ERR_UNSUPPORTED, "more than one attention-mask fusion");
+    for (FOp& o : g_.ops)
+      if (o.kind == OP_EMBED) {
+        o.mask_in = masks_[0].mask_arg;
+        o.mask_out = masks_[0].tensor;
+        o.alpha = masks_[0].mask_scale;
+        return MONONN_OK;
+      }
+    return fail(MONONN_ERR_UNSUPPORTED, "attention mask without an embedding stage to compute it in");
+  }
+
+  const HloModule& m_;
+  const HloComputation& e_;
+  FGraph& g_;
+  std::string* err_;
+  std::vector<Val> vals_;
+  std::vector<int> uses_;
+  std::map<int, int> const_tensors_;
+  std::vector<Val> masks_;
+};
+
+}  // namespace
+
+int hlo_text_to_fgraph(const std::string& text, FGraph* graph, std::string* err) {
+  HloModule m;
+  int rc = parse_hlo_text(text, &m, err);
+  if (rc) return rc;
+  Lowering l(m, graph, err);
+  return l.run();
+}
+
+}  // namespace mononn

@@ -766,7 +766,7 @@ __device__ __noinline__ void rowwise_item(const OpDesc& op, uint32_t local, uint
     }
     if ((flags & F_MASK_BIAS) && lane == 0) {
       const int32_t m = reinterpret_cast<const int32_t*>(op.q[0])[row];
-      reinterpret_cast<float*>(op.q[1])[row] = (1.0f - static_cast<float>(m)) * -10000.0f;
+      reinterpret_cast<float*>(op.q[1])[row] = (1.0f - static_cast<float>(m)) * op.alpha;
     }
   } else {
     if (flags & F_SRC_F32) {

@@ -150,8 +150,20 @@ int Runtime::upload_constant(const ConstBinding& b, const std::vector<uint8_t>& 
   return MONONN_OK;
 }
 
-int Runtime::set_constant(const std::string& name, const void* host, size_t bytes) {
+// '.' and '-' are interchangeable with '_' in constant names, as in the reference's
+// canonical node names (mononn_engine/helpers/string_helpers.cc:22-32).
+static std::string canon(const std::string& n) {
+  std::string v = n;
+  for (char& c : v)
+    if (c == '.' || c == '-') c = '_';
+  return v;
+}
+
+int Runtime::set_constant(const std::string& given, const void* host, size_t bytes) {
   CUDA_TRY(cudaSetDevice(device_));
+  std::string name = given;
+  for (const ConstBinding& b : plan_.consts)
+    if (b.const_name != given && canon(b.const_name) == canon(given)) name = b.const_name;
   bool found = false;
   for (const ConstBinding& b : plan_.consts)
     if (b.const_name == name) {

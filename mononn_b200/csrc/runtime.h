@@ -58,6 +58,10 @@ class Runtime {
   int time_stages(void* const* args, int n, void* stream, uint32_t begin, uint32_t end, int warmup,
                   int iters, double* us);
 
+  // Host-side fault injection for tests: the next launch expects `n` arrivals that never come,
+  // so its first grid-barrier wait runs into the timeout and the kernel reports it.
+  void skew_epoch(uint32_t n) { epoch_ += n; }
+
   unsigned timeout_us = 2000000;
   const std::map<std::string, std::vector<uint8_t>>& host_constants() const { return host_consts_; }
 

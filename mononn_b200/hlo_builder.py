@@ -1,0 +1,304 @@
+"""Authors the XLA HLO text of the example encoder graphs.
+
+The reference receives a post-optimisation XLA-GPU module from TensorFlow: an ENTRY
+computation made of parameters, constants (the frozen weights), kLoop/kInput fusions and
+``__cublas$gemm`` custom-calls (mononn_engine/parser/ir_parser_fused.cc:319-385; example
+GEMM HLO in mononn_engine/core/op_impl/gemm_impl.cc:290-316).  No dump of the example models
+exists offline and TensorFlow is absent, so this module writes that text for the model
+definitions of examples/utils/save_model.py:44-110: same op vocabulary
+(mononn_engine/core/op/op_type.h:20-65, plus the newer ``erf`` opcode), same
+``backend_config`` JSON keys (gemm_impl.cc:182-231), f16 storage with f32 reductions as
+TensorFlow's auto_mixed_precision graph rewrite produces (examples/run_mononn.py:44).
+
+Large constants are written the way XLA prints them when literals are elided:
+``constant({...})``; their values are supplied separately through ``mononn_set_constant``.
+"""
+from __future__ import annotations
+
+import json
+
+from .models import EncoderConfig
+
+
+class _Emitter:
+    def __init__(self):
+        self.comps: list[str] = []
+        self.entry: list[str] = []
+        self._n = 0
+
+    def uid(self, stem: str) -> str:
+        self._n += 1
+        return f"{stem}.{self._n}"
+
+
+def _shape(dtype: str, dims) -> str:
+    dims = list(dims)
+    layout = ",".join(str(i) for i in reversed(range(len(dims))))
+    return f"{dtype}[{','.join(str(d) for d in dims)}]" + ("{" + layout + "}" if dims else "")
+
+
+def _gemm_config(alpha: float, lhs_c: int, rhs_c: int, batch_dims, batch_size: int, lhs_stride: int,
+                 rhs_stride: int) -> str:
+    cfg = {
+        "alpha_real": alpha, "alpha_imag": 0, "beta": 0,
+        "dot_dimension_numbers": {
+            "lhs_contracting_dimensions": [str(lhs_c)], "rhs_contracting_dimensions": [str(rhs_c)],
+            "lhs_batch_dimensions": [str(d) for d in batch_dims],
+            "rhs_batch_dimensions": [str(d) for d in batch_dims]},
+        "batch_size": str(batch_size), "lhs_stride": str(lhs_stride), "rhs_stride": str(rhs_stride),
+        "selected_algorithm": "-1",
+    }
+    return json.dumps(json.dumps(cfg, separators=(",", ":")))  # quoted + escaped, as XLA prints it
+
+
+_REGIONS = """%region_add (a: f32[], b: f32[]) -> f32[] {
+  %a = f32[] parameter(0)
+  %b = f32[] parameter(1)
+  ROOT %add = f32[] add(f32[] %a, f32[] %b)
+}
+
+%region_max (a: f32[], b: f32[]) -> f32[] {
+  %a = f32[] parameter(0)
+  %b = f32[] parameter(1)
+  ROOT %max = f32[] maximum(f32[] %a, f32[] %b)
+}
+"""
+
+
+def _activation_lines(kind: str, x: str, shp: str) -> tuple[list[str], str]:
+    """f32 elementwise activation on value `x` of printed shape `shp`."""
+    def c(name, v):
+        return [f"  %{name}_s = f32[] constant({v})",
+                f"  %{name} = {shp} broadcast(f32[] %{name}_s), dimensions={{}}"]
+    L: list[str] = []
+    if kind == "gelu_erf":
+        L += c("half", 0.5) + c("rsqrt2", 0.70710678118654752) + c("one", 1)
+        L += [f"  %g1 = {shp} multiply({shp} %{x}, {shp} %rsqrt2)",
+              f"  %g2 = {shp} erf({shp} %g1)",
+              f"  %g3 = {shp} add({shp} %g2, {shp} %one)",
+              f"  %g4 = {shp} multiply({shp} %{x}, {shp} %half)",
+              f"  %act = {shp} multiply({shp} %g4, {shp} %g3)"]
+    elif kind == "relu":
+        L += c("zero", 0)
+        L += [f"  %act = {shp} maximum({shp} %{x}, {shp} %zero)"]
+    elif kind == "quick_gelu":
+        L += c("k", -1.702) + c("one", 1)
+        L += [f"  %q1 = {shp} multiply({shp} %{x}, {shp} %k)",
+              f"  %q2 = {shp} exponential({shp} %q1)",
+              f"  %q3 = {shp} add({shp} %q2, {shp} %one)",
+              f"  %act = {shp} divide({shp} %{x}, {shp} %q3)"]
+    elif kind == "gelu_tanh":
+        L += c("half", 0.5) + c("one", 1) + c("c0", 0.7978845608028654) + c("c1", 0.044715)
+        L += [f"  %t1 = {shp} multiply({shp} %{x}, {shp} %{x})",
+              f"  %t2 = {shp} multiply({shp} %t1, {shp} %{x})",
+              f"  %t3 = {shp} multiply({shp} %t2, {shp} %c1)",
+              f"  %t4 = {shp} add({shp} %{x}, {shp} %t3)",
+              f"  %t5 = {shp} multiply({shp} %t4, {shp} %c0)",
+              f"  %t6 = {shp} tanh({shp} %t5)",
+              f"  %t7 = {shp} add({shp} %t6, {shp} %one)",
+              f"  %t8 = {shp} multiply({shp} %{x}, {shp} %half)",
+              f"  %act = {shp} multiply({shp} %t8, {shp} %t7)"]
+    else:
+        raise ValueError(kind)
+    return L, "act"
+
+
+def _ln_body(rows: int, cols: int, eps: float, x32: str) -> list[str]:
+    """LayerNorm over the last dim of f32 value `x32` [rows, cols]; result in %ln (f16)."""
+    s2, s1 = _shape("f32", [rows, cols]), _shape("f32", [rows])
+    h2, hv, fv = _shape("f16", [rows, cols]), _shape("f16", [cols]), _shape("f32", [cols])
+    return [
+        f"  %zero = f32[] constant(0)",
+        f"  %inv_n_s = f32[] constant({1.0 / cols!r})",
+        f"  %inv_n = {s1} broadcast(f32[] %inv_n_s), dimensions={{}}",
+        f"  %eps_s = f32[] constant({eps!r})",
+        f"  %eps = {s1} broadcast(f32[] %eps_s), dimensions={{}}",
+        f"  %sum = {s1} reduce({s2} %{x32}, f32[] %zero), dimensions={{1}}, to_apply=%region_add",
+        f"  %mean = {s1} multiply({s1} %sum, {s1} %inv_n)",
+        f"  %mean_b = {s2} broadcast({s1} %mean), dimensions={{0}}",
+        f"  %cent = {s2} subtract({s2} %{x32}, {s2} %mean_b)",
+        f"  %sq = {s2} multiply({s2} %cent, {s2} %cent)",
+        f"  %sqsum = {s1} reduce({s2} %sq, f32[] %zero), dimensions={{1}}, to_apply=%region_add",
+        f"  %var = {s1} multiply({s1} %sqsum, {s1} %inv_n)",
+        f"  %var_eps = {s1} add({s1} %var, {s1} %eps)",
+        f"  %rstd = {s1} rsqrt({s1} %var_eps)",
+        f"  %rstd_b = {s2} broadcast({s1} %rstd), dimensions={{0}}",
+        f"  %norm = {s2} multiply({s2} %cent, {s2} %rstd_b)",
+        f"  %gamma32 = {fv} convert({hv} %gamma)",
+        f"  %beta32 = {fv} convert({hv} %beta)",
+        f"  %gamma_b = {s2} broadcast({fv} %gamma32), dimensions={{1}}",
+        f"  %beta_b = {s2} broadcast({fv} %beta32), dimensions={{1}}",
+        f"  %scaled = {s2} multiply({s2} %norm, {s2} %gamma_b)",
+        f"  %shifted = {s2} add({s2} %scaled, {s2} %beta_b)",
+        f"  ROOT %ln = {h2} convert({s2} %shifted)",
+    ]
+
+
+def bert_hlo(cfg: EncoderConfig) -> tuple[str, dict[str, str]]:
+    """HLO text of the BERT encoder of `cfg` and the map weight name -> HLO constant name."""
+    B, S, H, F, NH = cfg.batch, cfg.seq, cfg.hidden, cfg.ffn, cfg.heads
+    D = H // NH
+    T = B * S
+    em = _Emitter()
+    comps: list[str] = [_REGIONS]
+    entry: list[str] = []
+    names: dict[str, str] = {}
+
+    def const(name: str, dims) -> str:
+        names[name] = name
+        entry.append(f"  %{name} = {_shape('f16', dims)} constant({{...}})")
+        return name
+
+    h_TH, h_H = _shape("f16", [T, H]), _shape("f16", [H])
+    f_TH = _shape("f32", [T, H])
+    i_BS, i_T = _shape("s32", [B, S]), _shape("s32", [T])
+
+    entry.append(f"  %input_ids = {i_BS} parameter(0)")
+    entry.append(f"  %attention_mask = {i_BS} parameter(1)")
+    entry.append(f"  %token_type_ids = {i_BS} parameter(2)")
+
+    # ---- embeddings: gather + position + type, then LayerNorm
+    word = const("embeddings.word", [cfg.vocab, H])
+    pos = const("embeddings.position", [cfg.max_pos, H])
+    typ = const("embeddings.token_type", [cfg.types, H])
+    g0 = const("embeddings.ln.gamma", [H])
+    b0 = const("embeddings.ln.beta", [H])
+    h_SH, h_BSH = _shape("f16", [S, H]), _shape("f16", [B, S, H])
+    comps.append(f"""%fused_embed (p0: {i_BS}, p1: {i_BS}, p2: {_shape('f16', [cfg.vocab, H])}, p3: {_shape('f16', [cfg.max_pos, H])}, p4: {_shape('f16', [cfg.types, H])}) -> {h_TH} {{
+  %ids = {i_BS} parameter(0)
+  %types = {i_BS} parameter(1)
+  %word = {_shape('f16', [cfg.vocab, H])} parameter(2)
+  %pos = {_shape('f16', [cfg.max_pos, H])} parameter(3)
+  %type = {_shape('f16', [cfg.types, H])} parameter(4)
+  %gw = {h_BSH} gather({_shape('f16', [cfg.vocab, H])} %word, {i_BS} %ids), offset_dims={{2}}, collapsed_slice_dims={{0}}, start_index_map={{0}}, index_vector_dim=2, slice_sizes={{1,{H}}}
+  %gt = {h_BSH} gather({_shape('f16', [cfg.types, H])} %type, {i_BS} %types), offset_dims={{2}}, collapsed_slice_dims={{0}}, start_index_map={{0}}, index_vector_dim=2, slice_sizes={{1,{H}}}
+  %pos_s = {h_SH} slice({_shape('f16', [cfg.max_pos, H])} %pos), slice={{[0:{S}], [0:{H}]}}
+  %pos_b = {h_BSH} broadcast({h_SH} %pos_s), dimensions={{1,2}}
+  %e1 = {h_BSH} add({h_BSH} %gw, {h_BSH} %pos_b)
+  %e2 = {h_BSH} add({h_BSH} %e1, {h_BSH} %gt)
+  ROOT %e3 = {h_TH} reshape({h_BSH} %e2)
+}}
+""")
+    entry.append(f"  %fusion.embed = {h_TH} fusion({i_BS} %input_ids, {i_BS} %token_type_ids, "
+                 f"{_shape('f16', [cfg.vocab, H])} %{word}, {_shape('f16', [cfg.max_pos, H])} %{pos}, "
+                 f"{_shape('f16', [cfg.types, H])} %{typ}), kind=kLoop, calls=%fused_embed")
+    comps.append(f"%fused_ln (p0: {h_TH}, p1: {h_H}, p2: {h_H}) -> {h_TH} {{\n"
+                 f"  %x = {h_TH} parameter(0)\n  %gamma = {h_H} parameter(1)\n  %beta = {h_H} parameter(2)\n"
+                 f"  %x32 = {f_TH} convert({h_TH} %x)\n" + "\n".join(_ln_body(T, H, cfg.eps, "x32")) + "\n}\n")
+    entry.append(f"  %fusion.embed_ln = {h_TH} fusion({h_TH} %fusion.embed, {h_H} %{g0}, {h_H} %{b0}), "
+                 f"kind=kInput, calls=%fused_ln")
+    # ---- additive attention mask (1 - m) * -10000, f32 [B, S]
+    f_BS = _shape("f32", [B, S])
+    comps.append(f"""%fused_mask (p0: {i_BS}) -> {f_BS} {{
+  %m = {i_BS} parameter(0)
+  %mf = {f_BS} convert({i_BS} %m)
+  %one_s = f32[] constant(1)
+  %one = {f_BS} broadcast(f32[] %one_s), dimensions={{}}
+  %neg_s = f32[] constant(-10000)
+  %neg = {f_BS} broadcast(f32[] %neg_s), dimensions={{}}
+  %inv = {f_BS} subtract({f_BS} %one, {f_BS} %mf)
+  ROOT %bias = {f_BS} multiply({f_BS} %inv, {f_BS} %neg)
+}}
+""")
+    entry.append(f"  %fusion.mask = {f_BS} fusion({i_BS} %attention_mask), kind=kLoop, calls=%fused_mask")
+
+    # ---- shared fused computations of the layers
+    h_heads, h_BShd = _shape("f16", [B, NH, S, D]), _shape("f16", [B, S, NH, D])
+    comps.append(f"""%fused_bias_split (p0: {h_TH}, p1: {h_H}) -> {h_heads} {{
+  %x = {h_TH} parameter(0)
+  %b = {h_H} parameter(1)
+  %bb = {h_TH} broadcast({h_H} %b), dimensions={{1}}
+  %y = {h_TH} add({h_TH} %x, {h_TH} %bb)
+  %r = {h_BShd} reshape({h_TH} %y)
+  ROOT %t = {h_heads} transpose({h_BShd} %r), dimensions={{0,2,1,3}}
+}}
+""")
+    h_sc, f_sc, f_row = _shape("f16", [B, NH, S, S]), _shape("f32", [B, NH, S, S]), _shape("f32", [B, NH, S])
+    comps.append(f"""%fused_softmax (p0: {h_sc}, p1: {f_BS}) -> {h_sc} {{
+  %s = {h_sc} parameter(0)
+  %mask = {f_BS} parameter(1)
+  %s32 = {f_sc} convert({h_sc} %s)
+  %mask_b = {f_sc} broadcast({f_BS} %mask), dimensions={{0,3}}
+  %z = {f_sc} add({f_sc} %s32, {f_sc} %mask_b)
+  %ninf = f32[] constant(-inf)
+  %zmax = {f_row} reduce({f_sc} %z, f32[] %ninf), dimensions={{3}}, to_apply=%region_max
+  %zmax_b = {f_sc} broadcast({f_row} %zmax), dimensions={{0,1,2}}
+  %zc = {f_sc} subtract({f_sc} %z, {f_sc} %zmax_b)
+  %e = {f_sc} exponential({f_sc} %zc)
+  %zero = f32[] constant(0)
+  %esum = {f_row} reduce({f_sc} %e, f32[] %zero), dimensions={{3}}, to_apply=%region_add
+  %esum_b = {f_sc} broadcast({f_row} %esum), dimensions={{0,1,2}}
+  %p = {f_sc} divide({f_sc} %e, {f_sc} %esum_b)
+  ROOT %p16 = {h_sc} convert({f_sc} %p)
+}}
+""")
+    comps.append(f"""%fused_merge (p0: {h_heads}) -> {h_TH} {{
+  %x = {h_heads} parameter(0)
+  %t = {h_BShd} transpose({h_heads} %x), dimensions={{0,2,1,3}}
+  ROOT %r = {h_TH} reshape({h_BShd} %t)
+}}
+""")
+    comps.append(f"%fused_bias_resid_ln (p0: {h_TH}, p1: {h_H}, p2: {h_TH}, p3: {h_H}, p4: {h_H}) -> {h_TH} {{\n"
+                 f"  %x = {h_TH} parameter(0)\n  %b = {h_H} parameter(1)\n  %res = {h_TH} parameter(2)\n"
+                 f"  %gamma = {h_H} parameter(3)\n  %beta = {h_H} parameter(4)\n"
+                 f"  %bb = {h_TH} broadcast({h_H} %b), dimensions={{1}}\n"
+                 f"  %y = {h_TH} add({h_TH} %x, {h_TH} %bb)\n"
+                 f"  %yr = {h_TH} add({h_TH} %y, {h_TH} %res)\n"
+                 f"  %x32 = {f_TH} convert({h_TH} %yr)\n" + "\n".join(_ln_body(T, H, cfg.eps, "x32")) + "\n}\n")
+    h_TF, h_F, f_TF = _shape("f16", [T, F]), _shape("f16", [F]), _shape("f32", [T, F])
+    act_lines, act_name = _activation_lines(cfg.act, "y32", f_TF)
+    comps.append(f"%fused_bias_act (p0: {h_TF}, p1: {h_F}) -> {h_TF} {{\n"
+                 f"  %x = {h_TF} parameter(0)\n  %b = {h_F} parameter(1)\n"
+                 f"  %bb = {h_TF} broadcast({h_F} %b), dimensions={{1}}\n"
+                 f"  %y = {h_TF} add({h_TF} %x, {h_TF} %bb)\n"
+                 f"  %y32 = {f_TF} convert({h_TF} %y)\n" + "\n".join(act_lines) + "\n"
+                 f"  ROOT %out = {h_TF} convert({f_TF} %{act_name})\n}}\n")
+
+    def gemm(name: str, a: str, a_shape, w: str, w_shape, out_shape, alpha=1.0, lhs_c=1, rhs_c=0,
+             batch_dims=(), batch=1, ls=0, rs=0) -> str:
+        entry.append(f"  %{name} = {_shape('f16', out_shape)} custom-call({_shape('f16', a_shape)} %{a}, "
+                     f"{_shape('f16', w_shape)} %{w}), custom_call_target=\"__cublas$gemm\", "
+                     f"backend_config={_gemm_config(alpha, lhs_c, rhs_c, batch_dims, batch, ls, rs)}")
+        return name
+
+    x = "fusion.embed_ln"
+    for l in range(cfg.layers):
+        p = f"layer{l}."
+        heads = {}
+        for n in ("q", "k", "v"):
+            w = const(p + f"attn.{n}.w", [H, H])
+            b = const(p + f"attn.{n}.b", [H])
+            gname = gemm(f"gemm.{n}.{l}", x, [T, H], w, [H, H], [T, H], ls=T * H, rs=H * H)
+            entry.append(f"  %fusion.{n}.{l} = {h_heads} fusion({h_TH} %{gname}, {h_H} %{b}), kind=kLoop, "
+                         f"calls=%fused_bias_split")
+            heads[n] = f"fusion.{n}.{l}"
+        sc = gemm(f"gemm.scores.{l}", heads["q"], [B, NH, S, D], heads["k"], [B, NH, S, D], [B, NH, S, S],
+                  alpha=1.0 / (D ** 0.5), lhs_c=3, rhs_c=3, batch_dims=(0, 1), batch=B * NH, ls=S * D, rs=S * D)
+        entry.append(f"  %fusion.softmax.{l} = {h_sc} fusion({h_sc} %{sc}, {f_BS} %fusion.mask), kind=kInput, "
+                     f"calls=%fused_softmax")
+        pv = gemm(f"gemm.pv.{l}", f"fusion.softmax.{l}", [B, NH, S, S], heads["v"], [B, NH, S, D],
+                  [B, NH, S, D], lhs_c=3, rhs_c=2, batch_dims=(0, 1), batch=B * NH, ls=S * S, rs=S * D)
+        entry.append(f"  %fusion.ctx.{l} = {h_TH} fusion({h_heads} %{pv}), kind=kLoop, calls=%fused_merge")
+        wo, bo = const(p + "attn.o.w", [H, H]), const(p + "attn.o.b", [H])
+        g1, be1 = const(p + "attn.ln.gamma", [H]), const(p + "attn.ln.beta", [H])
+        go = gemm(f"gemm.o.{l}", f"fusion.ctx.{l}", [T, H], wo, [H, H], [T, H], ls=T * H, rs=H * H)
+        entry.append(f"  %fusion.attn_ln.{l} = {h_TH} fusion({h_TH} %{go}, {h_H} %{bo}, {h_TH} %{x}, {h_H} %{g1}, "
+                     f"{h_H} %{be1}), kind=kInput, calls=%fused_bias_resid_ln")
+        x1 = f"fusion.attn_ln.{l}"
+        w1, b1 = const(p + "ffn.up.w", [H, F]), const(p + "ffn.up.b", [F])
+        gu = gemm(f"gemm.up.{l}", x1, [T, H], w1, [H, F], [T, F], ls=T * H, rs=H * F)
+        entry.append(f"  %fusion.act.{l} = {h_TF} fusion({h_TF} %{gu}, {h_F} %{b1}), kind=kLoop, calls=%fused_bias_act")
+        w2, b2 = const(p + "ffn.down.w", [F, H]), const(p + "ffn.down.b", [H])
+        g2, be2 = const(p + "ffn.ln.gamma", [H]), const(p + "ffn.ln.beta", [H])
+        gd = gemm(f"gemm.down.{l}", f"fusion.act.{l}", [T, F], w2, [F, H], [T, H], ls=T * F, rs=F * H)
+        entry.append(f"  %fusion.ffn_ln.{l} = {h_TH} fusion({h_TH} %{gd}, {h_H} %{b2}, {h_TH} %{x1}, {h_H} %{g2}, "
+                     f"{h_H} %{be2}), kind=kInput, calls=%fused_bias_resid_ln")
+        x = f"fusion.ffn_ln.{l}"
+    out_shape = _shape("f16", [B, S, H])
+    entry.append(f"  ROOT %last_hidden_state = {out_shape} bitcast({h_TH} %{x})")
+
+    text = (f"HloModule {cfg.name}, entry_computation_layout={{({i_BS}, {i_BS}, {i_BS})->{out_shape}}}\n\n"
+            + "\n".join(comps)
+            + f"\nENTRY %{cfg.name}_main (input_ids: {i_BS}, attention_mask: {i_BS}, token_type_ids: {i_BS}) "
+              f"-> {out_shape} {{\n" + "\n".join(entry) + "\n}\n")
+    return text, names

@@ -47,7 +47,7 @@ def bert_tiny(batch: int = 1, seq: int = 16, layers: int = 1, hidden: int = 64, 
               vocab: int = 100, max_pos: int = 64) -> EncoderConfig:
     """Small shape for element-wise parity checks (one layer, hidden 64)."""
     return EncoderConfig(layers=layers, hidden=hidden, heads=hidden // 64, ffn=ffn, vocab=vocab,
-                         max_pos=max_pos, batch=batch, seq=seq)
+                         max_pos=max(max_pos, seq), batch=batch, seq=seq)
 
 
 def bert_weight_shapes(cfg: EncoderConfig) -> dict[str, tuple[int, ...]]:

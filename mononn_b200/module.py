@@ -80,6 +80,9 @@ class Module:
             self.allocate()
         check(lib().mononn_launch_stages(self._h, self._ptrs, len(self._bufs), self._stream(stream), begin, end))
 
+    def debug_skew_barrier(self, missing_arrivals: int) -> None:
+        check(lib().mononn_debug_skew_barrier(self._h, missing_arrivals))
+
     def save_spec(self, directory: str) -> None:
         check(lib().mononn_save_spec(self._h, directory.encode()))
 

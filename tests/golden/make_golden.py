@@ -1,0 +1,81 @@
+"""Generates tests/golden/*.npz.  Run from the repository root:
+
+    python tests/golden/make_golden.py
+
+The reference holds no expected outputs for this path (its only fixture is the input file
+examples/data/bert_bs1.npy), so the golden outputs come from an independent implementation
+of the same public model definition: `transformers`' PyTorch BertModel, built offline from a
+config and loaded with the seeded synthetic weights of mononn_b200.models.  The CPU
+restatement in oracle/ is pinned against these files.
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+from mononn_b200.models import EncoderConfig, make_inputs, make_weights  # noqa: E402
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def hf_bert_forward(cfg: EncoderConfig, w: dict, inputs: dict) -> np.ndarray:
+    from transformers import BertConfig, BertModel
+    hc = BertConfig(vocab_size=cfg.vocab, hidden_size=cfg.hidden, num_hidden_layers=cfg.layers,
+                    num_attention_heads=cfg.heads, intermediate_size=cfg.ffn, hidden_act="gelu",
+                    max_position_embeddings=cfg.max_pos, type_vocab_size=cfg.types,
+                    layer_norm_eps=cfg.eps, hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
+    model = BertModel(hc, add_pooling_layer=False).eval()
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a))
+    sd = {
+        "embeddings.word_embeddings.weight": t(w["embeddings.word"]),
+        "embeddings.position_embeddings.weight": t(w["embeddings.position"]),
+        "embeddings.token_type_embeddings.weight": t(w["embeddings.token_type"]),
+        "embeddings.LayerNorm.weight": t(w["embeddings.ln.gamma"]),
+        "embeddings.LayerNorm.bias": t(w["embeddings.ln.beta"]),
+    }
+    for l in range(cfg.layers):
+        p, q = f"layer{l}.", f"encoder.layer.{l}."
+        for ours, theirs in (("attn.q", "attention.self.query"), ("attn.k", "attention.self.key"),
+                             ("attn.v", "attention.self.value"), ("attn.o", "attention.output.dense"),
+                             ("ffn.up", "intermediate.dense"), ("ffn.down", "output.dense")):
+            sd[q + theirs + ".weight"] = t(w[p + ours + ".w"].T)  # torch Linear stores [out, in]
+            sd[q + theirs + ".bias"] = t(w[p + ours + ".b"])
+        sd[q + "attention.output.LayerNorm.weight"] = t(w[p + "attn.ln.gamma"])
+        sd[q + "attention.output.LayerNorm.bias"] = t(w[p + "attn.ln.beta"])
+        sd[q + "output.LayerNorm.weight"] = t(w[p + "ffn.ln.gamma"])
+        sd[q + "output.LayerNorm.bias"] = t(w[p + "ffn.ln.beta"])
+    missing, unexpected = model.load_state_dict(sd, strict=False)
+    missing = [m for m in missing if "position_ids" not in m]
+    assert not missing and not unexpected, (missing, unexpected)
+    with torch.no_grad():
+        out = model(input_ids=torch.from_numpy(inputs["input_ids"]).long(),
+                    attention_mask=torch.from_numpy(inputs["attention_mask"]).long(),
+                    token_type_ids=torch.from_numpy(inputs["token_type_ids"]).long()).last_hidden_state
+    return out.reshape(cfg.batch * cfg.seq, cfg.hidden).numpy()
+
+
+CASES = {
+    # name: (config, weight seed, stress, pad_fraction)
+    "bert_tiny_b1_s16": (EncoderConfig(layers=2, hidden=64, heads=1, ffn=256, vocab=100, max_pos=64,
+                                       batch=1, seq=16), 11, True, 0.0),
+    "bert_small_b2_s24_pad": (EncoderConfig(layers=2, hidden=128, heads=2, ffn=512, vocab=300, max_pos=64,
+                                            batch=2, seq=24), 12, True, 0.25),
+}
+
+
+def main():
+    for name, (cfg, seed, stress, pad) in CASES.items():
+        w = make_weights(cfg, seed, stress=stress)
+        inp = make_inputs(cfg, seed, pad_fraction=pad)
+        out = hf_bert_forward(cfg, w, inp)
+        # keep the file small: the inputs are regenerated from the seed, only the output is stored
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), last_hidden_state=out.astype(np.float32),
+                            seed=np.int64(seed), stress=np.bool_(stress), pad=np.float64(pad))
+        print(name, out.shape, float(np.abs(out).mean()))
+
+
+if __name__ == "__main__":
+    main()

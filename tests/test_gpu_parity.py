@@ -1,0 +1,124 @@
+"""Parity of the CUDA path with the CPU oracle, through the C ABI (-m gpu)."""
+import numpy as np
+import pytest
+
+from mononn_b200 import bert_base, bert_tiny, compile_encoder, compile_hlo, make_inputs, make_weights
+from mononn_b200.hlo_builder import bert_hlo
+from mononn_b200.models import EncoderConfig
+from oracle import ref_encoder as R
+from tests.helpers import assert_parity, golden_cases, load_golden, reference_fixture_inputs
+
+pytestmark = pytest.mark.gpu
+
+
+def run_module(mod, cfg, inp):
+    out = mod.run([inp["input_ids"], inp["attention_mask"], inp["token_type_ids"]])[0]
+    return out[: cfg.tokens * cfg.hidden].reshape(cfg.tokens, cfg.hidden).astype(np.float32)
+
+
+def build(cfg, w, frontend):
+    if frontend == "hlo":
+        text, names = bert_hlo(cfg)
+        mod = compile_hlo(text, barrier_timeout_us=500000)
+        mod.set_weights({names[k]: v for k, v in w.items()})
+    else:
+        mod = compile_encoder(cfg, barrier_timeout_us=500000)
+        mod.set_weights(w)
+    return mod
+
+
+@pytest.mark.parametrize("name", sorted(golden_cases()))
+@pytest.mark.parametrize("frontend", ["hlo", "builder"])
+def test_golden_vectors(name, frontend):
+    cfg, seed, stress, pad = golden_cases()[name]
+    w = make_weights(cfg, seed, stress=stress)
+    inp = make_inputs(cfg, seed, pad_fraction=pad)
+    mod = build(cfg, w, frontend)
+    got = run_module(mod, cfg, inp)
+    mod.close()
+    assert_parity(got, load_golden(name)["last_hidden_state"], name)
+
+
+@pytest.mark.parametrize("cfg", [
+    bert_tiny(),                                                   # one 16-row tile, hidden 64
+    bert_tiny(batch=3, seq=20, layers=2, hidden=128, ffn=512),     # ragged: 60 rows, 2 heads
+    bert_tiny(batch=1, seq=128, layers=1, hidden=192, ffn=768),    # full 128-row tile, 3 heads
+    bert_tiny(batch=2, seq=128, layers=1, hidden=128, ffn=512),    # two 128-row tiles
+    bert_tiny(batch=5, seq=33, layers=1, hidden=64, ffn=256),      # rows straddle tile boundaries
+], ids=lambda c: f"b{c.batch}s{c.seq}h{c.hidden}l{c.layers}")
+def test_shapes_against_oracle(cfg):
+    w = make_weights(cfg, 21, stress=True)
+    inp = make_inputs(cfg, 21, pad_fraction=0.25)
+    mod = build(cfg, w, "hlo")
+    got = run_module(mod, cfg, inp)
+    mod.close()
+    assert_parity(got, R.bert_encoder(cfg, w, inp), "shape case")
+
+
+@pytest.mark.parametrize("act", ["gelu_erf", "relu", "quick_gelu", "gelu_tanh"])
+def test_activations(act):
+    cfg = bert_tiny(seq=32, hidden=128, ffn=512)
+    cfg.act = act
+    w = make_weights(cfg, 5, stress=True)
+    inp = make_inputs(cfg, 5)
+    mod = build(cfg, w, "hlo")
+    got = run_module(mod, cfg, inp)
+    mod.close()
+    assert_parity(got, R.bert_encoder(cfg, w, inp), act)
+
+
+@pytest.fixture(scope="module")
+def base():
+    cfg = bert_base()
+    w = make_weights(cfg, 1234, stress=True)
+    text, names = bert_hlo(cfg)
+    mod = compile_hlo(text, barrier_timeout_us=500000)
+    mod.set_weights({names[k]: v for k, v in w.items()})
+    yield cfg, w, mod
+    mod.close()
+
+
+def test_bert_base_full_size(base):
+    cfg, w, mod = base
+    inp = make_inputs(cfg, 1234)
+    assert_parity(run_module(mod, cfg, inp), R.bert_encoder(cfg, w, inp), "BERT-base b1 s128")
+
+
+def test_bert_base_reference_fixture_inputs(base):
+    cfg, w, mod = base
+    inp = reference_fixture_inputs()
+    assert_parity(run_module(mod, cfg, inp), R.bert_encoder(cfg, w, inp), "bert_bs1 fixture inputs")
+
+
+def test_bert_base_padding_mask(base):
+    cfg, w, mod = base
+    inp = make_inputs(cfg, 77, pad_fraction=0.25)
+    got = run_module(mod, cfg, inp)
+    assert_parity(got, R.bert_encoder(cfg, w, inp), "padding mask")
+    # size-independent property: ids under the mask do not influence unmasked positions
+    inp2 = {k: v.copy() for k, v in inp.items()}
+    inp2["input_ids"][0, -5:] = 0
+    got2 = run_module(mod, cfg, inp2)
+    keep = inp["attention_mask"].reshape(-1) == 1
+    assert np.abs(got[keep] - got2[keep]).max() <= 2e-2
+
+
+def test_bert_base_relaunch_is_stable(base):
+    """The f32 accumulators and the barrier epoch carry over between launches: the same
+    inputs must give the same answer again (split-K sums are atomic, so allow rounding)."""
+    cfg, w, mod = base
+    inp = make_inputs(cfg, 3)
+    a = run_module(mod, cfg, inp)
+    for _ in range(3):
+        mod.launch()
+    b = run_module(mod, cfg, inp)
+    assert np.abs(a - b).max() <= 4e-3
+
+
+def test_layernorm_output_statistics(base):
+    # with gamma = 1 + small, beta small: every output row is close to zero mean, unit variance
+    cfg, w, mod = base
+    got = run_module(mod, cfg, make_inputs(cfg, 9))
+    g, b = w[f"layer{cfg.layers - 1}.ffn.ln.gamma"], w[f"layer{cfg.layers - 1}.ffn.ln.beta"]
+    z = (got - b) / g
+    assert np.abs(z.mean(1)).max() < 2e-2 and np.abs(z.var(1) - 1).max() < 5e-2

@@ -1,0 +1,138 @@
+"""Runtime behaviour on the device (-m gpu): launch geometry, one launch per inference,
+status reporting when a bounded wait expires, per-stage profile, spec dump and reload."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from mononn_b200 import bert_tiny, capi, compile_encoder, compile_hlo, make_inputs, make_weights
+from mononn_b200.hlo_builder import bert_hlo
+from oracle import ref_encoder as R
+from tests.helpers import assert_parity
+
+pytestmark = pytest.mark.gpu
+
+
+def small():
+    cfg = bert_tiny(batch=2, seq=24, layers=2, hidden=128, ffn=512)
+    w = make_weights(cfg, 4, stress=True)
+    inp = make_inputs(cfg, 4)
+    return cfg, w, inp
+
+
+def run(mod, cfg, inp):
+    out = mod.run([inp["input_ids"], inp["attention_mask"], inp["token_type_ids"]])[0]
+    return out[: cfg.tokens * cfg.hidden].reshape(cfg.tokens, cfg.hidden).astype(np.float32)
+
+
+def test_launch_configuration_and_arguments():
+    cfg, w, inp = small()
+    mod = compile_encoder(cfg)
+    lc = mod.launch_config()
+    import torch
+    assert lc["grid"][0] == torch.cuda.get_device_properties(0).multi_processor_count
+    assert lc["block"] == (256, 1, 1) and lc["smem_bytes"] <= 232448
+    kinds = [a["kind"] for a in mod.args()]
+    assert kinds == [0, 0, 0, 1, 2]
+    mod.close()
+
+
+def test_launch_before_constants_is_an_error():
+    cfg, w, inp = small()
+    mod = compile_encoder(cfg)
+    with pytest.raises(capi.MononnError) as e:
+        mod.launch()
+    assert e.value.code == -9
+    with pytest.raises(capi.MononnError) as e:
+        mod.set_constant("no.such.constant", np.zeros(4, np.float16))
+    assert e.value.code == -7
+    with pytest.raises(capi.MononnError) as e:
+        mod.set_constant("embeddings.ln.gamma", np.zeros(3, np.float16))
+    assert e.value.code == -7
+    mod.close()
+
+
+def test_expired_wait_is_reported_and_the_module_recovers():
+    """Host-side fault injection: the launch is told to wait for arrivals nobody makes. The
+    kernel's bounded wait gives up after the (short) timeout, the status word says where, and
+    the next launch on the same module works."""
+    cfg, w, inp = small()
+    mod = compile_encoder(cfg, barrier_timeout_us=20000)
+    mod.set_weights(w)
+    want = R.bert_encoder(cfg, w, inp)
+    assert_parity(run(mod, cfg, inp), want, "before")
+    mod.debug_skew_barrier(7)
+    mod.launch()
+    with pytest.raises(capi.MononnError) as e:
+        mod.status()
+    assert e.value.code == -6 and "stage" in str(e.value)
+    assert_parity(run(mod, cfg, inp), want, "after recovery")
+    mod.close()
+
+
+def test_stage_profile_and_trace():
+    cfg, w, inp = small()
+    mod = compile_encoder(cfg)
+    mod.set_weights(w)
+    run(mod, cfg, inp)
+    prof = mod.profile_stages()
+    assert len(prof) == len(mod.plan()["stages"]) and all(t > 0 for _, t in prof)
+    tr = mod.trace()
+    assert tr.shape[1] == len(prof) and tr.shape[2] == 16
+    # every CTA arrives at every stage's barrier (event 2)
+    assert (tr[:, :, 2] > 0).all()
+    mod.close()
+
+
+def test_single_stage_isolation_matches_full_run():
+    cfg, w, inp = small()
+    mod = compile_encoder(cfg)
+    mod.set_weights(w)
+    full = run(mod, cfg, inp)
+    n = len(mod.plan()["stages"])
+    for s in range(n):
+        mod.launch_stages(s, s + 1)
+    mod.status()
+    descs = mod.args()
+    out_idx = [d["index"] for d in descs if d["kind"] == 1][0]
+    step = mod.buffers[out_idx].cpu().numpy().view(np.float16)[: full.size].reshape(full.shape).astype(np.float32)
+    assert np.abs(step - full).max() <= 4e-3
+    mod.close()
+
+
+def test_spec_dump_and_reload(tmp_path):
+    cfg, w, inp = small()
+    text, names = bert_hlo(cfg)
+    mod = compile_hlo(text)
+    mod.set_weights({names[k]: v for k, v in w.items()})
+    run(mod, cfg, inp)
+    mod.profile_stages()
+    mod.save_spec(str(tmp_path))
+    cdir = tmp_path / "cluster_0"
+    assert (cdir / "best_tuning_spec.json").exists() and (cdir / "performance_report.csv").exists()
+    spec = json.loads((cdir / "best_tuning_spec.json").read_text())
+    grid = spec["cuda_context"]["cuda_runtime_context"]["grid_dim"]["x"]
+    assert (cdir / f"{grid}_1_1__256_1_1.json").exists()
+    rows = (cdir / "performance_report.csv").read_text().strip().splitlines()
+    assert len(rows) == len(mod.plan()["stages"]) and rows[0].split(",")[0] == f"{grid}_1_1__256_1_1"
+    # change a tile in the saved spec, reload through TF_MONONN_EXISTING_TUNING_SPEC_DIR semantics
+    spec["gemm_spec_list"]["gemm_down_0"]["sm100_config"].update(mma_n=32, k_split=2)
+    (cdir / "best_tuning_spec.json").write_text(json.dumps(spec))
+    mod2 = compile_hlo(text, spec_dir=str(tmp_path))
+    mod2.set_weights({names[k]: v for k, v in w.items()})
+    ops = {o["name"]: o for s in mod2.plan()["stages"] for o in s["ops"]}
+    assert ops["gemm_down_0"]["n_tile"] == 32 and ops["gemm_down_0"]["k_split"] == 2
+    assert_parity(run(mod2, cfg, inp), R.bert_encoder(cfg, w, inp), "reloaded spec")
+    mod.close()
+    mod2.close()
+
+
+def test_tuner_keeps_parity(tmp_path):
+    cfg, w, inp = small()
+    mod = compile_encoder(cfg, tuning_level=1, dump_dir=str(tmp_path))
+    mod.set_weights(w)
+    mod.tune()
+    assert_parity(run(mod, cfg, inp), R.bert_encoder(cfg, w, inp), "after tuning")
+    assert (tmp_path / "cluster_0" / "tuning_log.log").exists()
+    mod.close()

@@ -1,0 +1,143 @@
+"""Host-side lowering (no GPU): stage structure, tile choice, buffer assignment, spec I/O."""
+import json
+import os
+
+import pytest
+
+from mononn_b200 import bert_base, bert_tiny, capi
+from mononn_b200.hlo_builder import bert_hlo
+from mononn_b200.module import describe
+
+
+@pytest.fixture(scope="module")
+def base_plan(lib_built):
+    return describe("encoder", bert_base().to_json())
+
+
+def test_bert_base_stage_structure(base_plan):
+    p = base_plan["plan"]
+    assert p["grid"] == 148 and p["block"] == 256
+    assert p["smem_bytes"] <= 232448
+    stages = p["stages"]
+    assert len(stages) == 1 + 12 * 7
+    kinds = [tuple(o["kind"] for o in s["ops"]) for s in stages[:8]]
+    assert kinds == [("embed",), ("gemm", "gemm", "gemm"), ("attention",), ("gemm",), ("layernorm",),
+                     ("gemm",), ("gemm",), ("layernorm",)]
+    # every stage fits one wave of the 148 CTAs at b1/s128
+    assert all(s["n_items"] <= 148 for s in stages)
+
+
+def test_algorithmic_cost_matches_the_model(base_plan):
+    p = base_plan["plan"]
+    # 85 054 464 encoder parameters in f16 + gathered rows + ids + output
+    assert abs(p["algorithmic_bytes"] - 170.70e6) < 0.05e6
+    assert abs(p["algorithmic_flops"] - 22.35e9) < 0.02e9
+
+
+def test_residual_and_bias_are_preloaded_by_the_row_stage(base_plan):
+    """The split-K GEMMs accumulate into an f32 buffer that the preceding LayerNorm /
+    embedding stage fills with residual + bias, so their epilogue flags are empty."""
+    ops = {o["name"]: o for s in base_plan["plan"]["stages"] for o in s["ops"]}
+    for name in ("layer0.attn.o", "layer3.ffn.down"):
+        assert ops[name]["flags"] & 0x3 == 0 and ops[name]["out_mode"] == 2
+    assert ops["layer0.ffn.up"]["flags"] & 0x1 and ops["layer0.ffn.up"]["act"] == 1
+
+
+def _live_ranges_do_not_overlap(plan):
+    tensors = [t for t in plan["tensors"] if t["kind"] in ("act_f16", "act_f16_t", "acc_f32", "vec_f32")]
+
+    def size(t):
+        if t["kind"] == "act_f16":
+            return t["rows"] * t["ld"] * 2
+        if t["kind"] == "act_f16_t":
+            return t["batches"] * t["cols"] * t["ld"] * 2
+        if t["kind"] == "acc_f32":
+            return t["rows"] * t["cols"] * 4
+        return t["rows"] * 4
+    for i, a in enumerate(tensors):
+        for b in tensors[i + 1:]:
+            if a["at"]["space"] != b["at"]["space"] or a["at"]["index"] != b["at"]["index"]:
+                continue
+            live = not (a["last_stage"] < b["def_stage"] or b["last_stage"] < a["def_stage"])
+            mem = not (a["at"]["offset"] + size(a) <= b["at"]["offset"] or
+                       b["at"]["offset"] + size(b) <= a["at"]["offset"])
+            assert not (live and mem), (a["name"], b["name"])
+    for t in tensors:
+        if t["at"]["space"] == "arg":
+            assert t["at"]["offset"] + size(t) <= plan["temp_bytes"]
+        assert t["at"]["offset"] % 256 == 0
+
+
+def test_buffers_with_overlapping_lifetimes_never_share_memory(base_plan):
+    _live_ranges_do_not_overlap(base_plan["plan"])
+    _live_ranges_do_not_overlap(describe("encoder", bert_tiny(batch=3, seq=20, layers=3).to_json())["plan"])
+
+
+def test_temp_arena_reuses_memory_across_layers(base_plan):
+    # 12 layers of activations fit in the footprint of about one layer
+    assert base_plan["plan"]["temp_bytes"] < 2 * (128 * 3072 * 2 + 4 * 128 * 768 * 2)
+
+
+def test_tensor_maps_obey_the_tma_rules(base_plan):
+    for tm in base_plan["plan"]["tensor_maps"]:
+        assert tm["stride1_bytes"] % 16 == 0
+        assert tm["box0"] * 2 % 16 == 0 and tm["box0"] * 2 <= 128  # 128-byte swizzle span
+        assert 1 <= tm["box1"] <= 256
+        assert tm["base"]["offset"] % 16 == 0
+
+
+def test_spec_controls_the_tiles_and_round_trips(lib_built, tmp_path):
+    cfg = bert_tiny(layers=1, hidden=128, ffn=512, seq=32)
+    d = describe("encoder", cfg.to_json())
+    spec = d["spec"]
+    assert set(spec) >= {"cuda_context", "gemm_spec_list", "cluster_elewise_spec", "cluster_reduce_spec",
+                         "conv_spec_list", "codegen_allow_list", "codegen_reject_list"}
+    rt = spec["cuda_context"]["cuda_runtime_context"]
+    assert rt["grid_dim"] == {"x": 148, "y": 1, "z": 1} and rt["block_dim"]["x"] == 256
+    spec["gemm_spec_list"]["layer0.ffn.down"]["sm100_config"].update(mma_n=64, k_split=2)
+    d2 = describe("encoder", cfg.to_json(), spec=spec)
+    ops = {o["name"]: o for s in d2["plan"]["stages"] for o in s["ops"]}
+    assert ops["layer0.ffn.down"]["n_tile"] == 64 and ops["layer0.ffn.down"]["k_split"] == 2
+    # an illegal request (K split on a GEMM whose activation needs the full sum) falls back
+    spec["gemm_spec_list"]["layer0.ffn.up"]["sm100_config"].update(mma_n=32, k_split=2)
+    d3 = describe("encoder", cfg.to_json(), spec=spec)
+    ops = {o["name"]: o for s in d3["plan"]["stages"] for o in s["ops"]}
+    assert ops["layer0.ffn.up"]["k_split"] == 1
+    # a spec in the reference's layout (cutlass_config only) parses and is ignored
+    ref_style = {"cuda_context": spec["cuda_context"],
+                 "gemm_spec_list": {"layer0.ffn.down": {"cutlass_config": {"ThreadBlockShape": {"m": 128, "n": 64, "k": 32}}}}}
+    describe("encoder", cfg.to_json(), spec=ref_style)
+
+
+def test_allow_list_isolates_one_node(lib_built):
+    cfg = bert_tiny(layers=1)
+    spec = describe("encoder", cfg.to_json())["spec"]
+    spec["codegen_allow_list"] = ["layer0.ffn.up"]
+    d = describe("encoder", cfg.to_json(), spec=spec)
+    assert [s["name"] for s in d["plan"]["stages"]] == ["layer0.ffn.up"]
+
+
+def test_malformed_inputs_give_error_codes_not_aborts(lib_built):
+    with pytest.raises(capi.MononnError) as e:
+        describe("encoder", "{not json")
+    assert e.value.code == -2
+    with pytest.raises(capi.MononnError) as e:
+        describe("encoder", json.dumps({"model": "bert", "hidden": 100, "heads": 2}))
+    assert e.value.code == -3
+    with pytest.raises(capi.MononnError) as e:
+        describe("encoder", bert_tiny().to_json(), spec={"gemm_spec_list": 3})
+    assert e.value.code == -2
+
+
+def test_hlo_and_builder_paths_agree(lib_built):
+    for cfg in (bert_tiny(), bert_tiny(batch=2, seq=24, layers=2, hidden=128, ffn=512)):
+        text, _ = bert_hlo(cfg)
+        a = describe("hlo", text)["plan"]
+        b = describe("encoder", cfg.to_json())["plan"]
+        assert len(a["stages"]) == len(b["stages"])
+        for sa, sb in zip(a["stages"], b["stages"]):
+            ka = [(o["kind"], o.get("M"), o.get("N"), o.get("K"), o.get("n_tile"), o.get("k_split"), o["flags"], o["act"]) for o in sa["ops"]]
+            kb = [(o["kind"], o.get("M"), o.get("N"), o.get("K"), o.get("n_tile"), o.get("k_split"), o["flags"], o["act"]) for o in sb["ops"]]
+            assert ka == kb
+        assert a["temp_bytes"] == b["temp_bytes"] and a["algorithmic_bytes"] == b["algorithmic_bytes"]
+        assert [x["kind"] for x in a["args"]] == [0, 0, 0, 1, 2]

@@ -1,0 +1,65 @@
+"""The CPU restatement (oracle/) against the golden vectors and against itself."""
+import numpy as np
+import pytest
+
+from mononn_b200.models import EncoderConfig, bert_tiny, make_inputs, make_weights
+from oracle import ref_encoder as R
+from tests.helpers import golden_cases, load_golden
+
+
+@pytest.mark.parametrize("name", sorted(golden_cases()))
+def test_oracle_matches_golden_vectors(name):
+    cfg, seed, stress, pad = golden_cases()[name]
+    g = load_golden(name)
+    w = make_weights(cfg, seed, stress=stress)
+    inp = make_inputs(cfg, seed, pad_fraction=pad)
+    out = R.bert_encoder(cfg, w, inp)
+    ref = g["last_hidden_state"]
+    assert out.shape == ref.shape
+    # two fp32 implementations of the same definition: agreement to rounding
+    assert np.abs(out - ref).max() < 2e-4
+
+
+def test_numpy_and_torch_restatements_agree():
+    cfg = bert_tiny(batch=2, seq=24, layers=2, hidden=128, ffn=512)
+    w = make_weights(cfg, 5, stress=True)
+    inp = make_inputs(cfg, 5, pad_fraction=0.25)
+    a = R.bert_encoder(cfg, w, inp)
+    b = R.bert_encoder_torch(cfg, w, inp, threads=1)
+    assert np.abs(a - b).max() < 2e-4
+
+
+def test_mask_changes_only_through_masked_keys():
+    cfg = bert_tiny(seq=16)
+    w = make_weights(cfg, 3, stress=True)
+    inp = make_inputs(cfg, 3, pad_fraction=0.25)
+    base = R.bert_encoder(cfg, w, inp)
+    # changing a masked-out token id must not change any unmasked position
+    inp2 = {k: v.copy() for k, v in inp.items()}
+    inp2["input_ids"][0, -1] = (inp2["input_ids"][0, -1] + 1) % cfg.vocab
+    other = R.bert_encoder(cfg, w, inp2)
+    keep = inp["attention_mask"].reshape(-1) == 1
+    assert np.abs(base[keep] - other[keep]).max() < 1e-5
+
+
+def test_layer_norm_eps_and_biased_variance():
+    x = np.array([[1.0, 2.0, 3.0, 6.0]], np.float32)
+    y = R.layer_norm(x, np.ones(4, np.float32), np.zeros(4, np.float32), 1e-12)
+    assert abs(float(y.mean())) < 1e-6
+    assert abs(float((y ** 2).mean()) - 1.0) < 1e-5  # biased variance -> unit second moment
+
+
+def test_gelu_is_the_exact_erf_form():
+    x = np.linspace(-4, 4, 33, dtype=np.float32)
+    import math
+    want = np.array([0.5 * v * (1 + math.erf(v / math.sqrt(2))) for v in x], np.float32)
+    assert np.abs(R.gelu_erf(x) - want).max() < 1e-6
+
+
+def test_weights_are_f16_representable_and_seeded():
+    cfg = bert_tiny()
+    a, b = make_weights(cfg, 9), make_weights(cfg, 9)
+    for k in a:
+        assert np.array_equal(a[k], b[k])
+        assert np.array_equal(a[k].astype(np.float16).astype(np.float32), a[k])
+    assert not np.array_equal(make_weights(cfg, 10)["embeddings.word"], a["embeddings.word"])
