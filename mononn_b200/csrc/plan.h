@@ -165,6 +165,10 @@ struct Plan {
 int schedule(const FGraph& g, const TuningSpec& spec, uint32_t sm_count, Plan* plan,
              std::string* err);
 
+// Host-side check of every invariant the kernel assumes (ring-slot sizes, TMA boxes, tile
+// coverage, buffer presence). schedule() ends with it; the runtime repeats it before loading.
+int validate_plan(const Plan& plan, std::string* err);
+
 // Default tile choice for one GEMM given how many CTAs it may occupy.
 GemmTileSpec default_gemm_tile(uint32_t M, uint32_t N, uint32_t K, bool can_split_k,
                                uint32_t cta_budget);

@@ -96,6 +96,14 @@ int Runtime::load_plan(const Plan& plan) {
                    std::to_string(cap) + " that can be co-resident; the grid barrier would hang");
     return MONONN_ERR_INVALID_ARGUMENT;
   }
+  {
+    std::string verr;
+    int vrc = validate_plan(plan, &verr);
+    if (vrc) {
+      set_last_error(verr);
+      return vrc;
+    }
+  }
   CUDA_TRY(cudaDeviceSynchronize());
   release();
   plan_ = plan;

@@ -23,7 +23,10 @@ static inline uint64_t align_up(uint64_t v, uint64_t a) { return (v + a - 1) / a
 
 // ------------------------------------------------------------ tile selection
 static bool tile_legal(uint32_t N, uint32_t K, const GemmTileSpec& t, bool can_split_k) {
+  // UMMA N is a multiple of 16 up to 256, and one k-block of the tile (n_tile rows of 128
+  // bytes) has to fit a weight-ring slot
   if (t.n_tile < 16 || t.n_tile > 256 || (t.n_tile % 16) != 0) return false;
+  if (t.n_tile * 128u > kSlotBytes) return false;
   if (t.k_split < 1) return false;
   const uint32_t kb = (K + 63) / 64;
   if (kb % t.k_split != 0) return false;
@@ -51,7 +54,7 @@ std::vector<GemmTileSpec> gemm_tile_candidates(uint32_t M, uint32_t N, uint32_t 
   std::vector<GemmTileSpec> out;
   const uint32_t kb = (K + 63) / 64;
   const uint32_t m_tiles = (M + 127) / 128;
-  for (uint32_t n_tile : {16u, 32u, 48u, 64u, 96u, 128u, 192u, 256u}) {
+  for (uint32_t n_tile : {16u, 32u, 48u, 64u, 96u, 128u}) {
     if (n_tile > std::max(16u, (N + 15) / 16 * 16)) continue;
     for (uint32_t ks = 1; ks <= kb; ++ks) {
       GemmTileSpec t;
@@ -119,6 +122,75 @@ uint64_t assign_offsets(std::vector<Interval>& iv, uint64_t base, uint64_t align
   return align_up(top, align);
 }
 }  // namespace
+
+// Checks every invariant the kernel relies on without checking it itself. A plan that fails
+// here would read or write outside its shared-memory rings, TMEM columns or buffers.
+int validate_plan(const Plan& P, std::string* err) {
+  auto bad = [&](const std::string& m) {
+    if (err) *err = "plan validation: " + m;
+    return MONONN_ERR_INVALID_ARGUMENT;
+  };
+  if (P.block != kThreads) return bad("block size");
+  if (P.smem_bytes != kSmemBytes) return bad("shared memory size");
+  for (size_t s = 0; s < P.stages.size(); ++s) {
+    const StageDesc& sd = P.stages[s];
+    if (sd.op_begin + sd.op_count > P.ops.size() || sd.op_count == 0) return bad("stage op range");
+    uint32_t items = 0;
+    for (uint32_t i = 0; i < sd.op_count; ++i) items += P.ops[sd.op_begin + i].d.n_items;
+    if (items != sd.n_items) return bad("stage item count");
+  }
+  for (const PlanOp& op : P.ops) {
+    const OpDesc& d = op.d;
+    const std::string n = op.name + ": ";
+    switch (d.kind) {
+      case OP_GEMM: {
+        if (d.n_tile < 16 || d.n_tile > 256 || d.n_tile % 16) return bad(n + "n_tile");
+        if (d.n_tile > kAccCols) return bad(n + "n_tile exceeds an accumulator buffer");
+        if (d.kb_per_bslot == 0 || d.n_tile * d.kb_per_bslot * 128u > kSlotBytes)
+          return bad(n + "weight tile exceeds a ring slot");
+        if (d.n_tile * d.kb_per_bslot > 256) return bad(n + "TMA box taller than 256 rows");
+        if (d.k_split == 0 || d.kb_per_split == 0 || d.k_split * d.kb_per_split * 64u != d.K)
+          return bad(n + "K split does not cover K");
+        if (d.n_tiles * d.n_tile < d.N || d.m_tiles * 128u < d.M) return bad(n + "tiles do not cover the output");
+        if (d.n_items != d.m_tiles * d.n_tiles * d.k_split) return bad(n + "item count");
+        if (d.N % 16) return bad(n + "N must be a multiple of 16");
+        if (d.tmap_a >= P.tmaps.size() || d.tmap_b >= P.tmaps.size()) return bad(n + "tensor map index");
+        if (P.tmaps[d.tmap_b].box1 != d.n_tile * d.kb_per_bslot || P.tmaps[d.tmap_b].box0 != 64)
+          return bad(n + "weight tensor-map box");
+        if (P.tmaps[d.tmap_a].box0 != 64 || P.tmaps[d.tmap_a].box1 != 128) return bad(n + "activation box");
+        if (d.k_split > 1 && (d.out_mode != OUT_F32_RED || d.act != ACT_NONE))
+          return bad(n + "K split needs an accumulating output without activation");
+        if (op.p[0].space == SPACE_NONE) return bad(n + "no output buffer");
+        if ((d.flags & F_BIAS) && op.p[1].space == SPACE_NONE) return bad(n + "no bias buffer");
+        if ((d.flags & F_RESID) && op.p[2].space == SPACE_NONE) return bad(n + "no residual buffer");
+        if (d.out_mode == OUT_F16_T && (d.rows_per_batch == 0 || d.ldt == 0)) return bad(n + "transposed output geometry");
+        break;
+      }
+      case OP_ATTENTION:
+        if (d.head_dim != 64 || d.seq == 0 || d.seq > 128) return bad(n + "attention geometry");
+        if (d.tmap_a >= P.tmaps.size() || d.tmap_b >= P.tmaps.size() || d.tmap_vt >= P.tmaps.size())
+          return bad(n + "tensor map index");
+        if (P.tmaps[d.tmap_vt].box0 != 64 || P.tmaps[d.tmap_vt].box1 != 64) return bad(n + "V^T box");
+        if (d.n_items != d.batches * d.heads * ((d.seq + 127) / 128)) return bad(n + "item count");
+        if (op.p[0].space == SPACE_NONE) return bad(n + "no output buffer");
+        break;
+      case OP_LAYERNORM:
+      case OP_EMBED:
+        if (d.cols == 0 || d.cols % 4 || d.cols > 2048) return bad(n + "row length");
+        if (d.n_items != (d.rows + 3) / 4) return bad(n + "item count");
+        if (op.p[0].space == SPACE_NONE) return bad(n + "no output buffer");
+        break;
+      default:
+        return bad(n + "unknown operator kind");
+    }
+  }
+  for (const TmapSpec& t : P.tmaps) {
+    if (t.box0 * 2u > 128u || (t.box0 * 2u) % 16u) return bad("tensor-map inner box must be 16..128 bytes");
+    if (t.box1 == 0 || t.box1 > 256) return bad("tensor-map box rows");
+    if (t.stride1_bytes % 16) return bad("tensor-map stride");
+  }
+  return MONONN_OK;
+}
 
 static bool listed(const std::vector<std::string>& l, const std::string& n) {
   return std::find(l.begin(), l.end(), n) != l.end();
@@ -583,7 +655,7 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
   }
   for (const ArgDesc& a : P.args)
     if (a.kind != 2) P.algorithmic_bytes += static_cast<double>(a.bytes);
-  return MONONN_OK;
+  return validate_plan(P, err);
 }
 
 }  // namespace mononn
