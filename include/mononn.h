@@ -157,6 +157,33 @@ int mononn_debug_skew_barrier(mononn_module* m, unsigned missing_arrivals);
 /* Algorithmic bytes and FLOPs of one inference (weights once + gathered rows + I/O). */
 int mononn_module_cost(const mononn_module* m, double* bytes, double* flops);
 
+/* Allocation-free attention (no counterpart in the reference, which leaves every buffer to
+ * XLA's allocator and never allocates on its own).
+ *
+ * For hosts where this library must not call cudaMalloc: under TensorFlow/XLA the framework's
+ * allocator normally owns the whole GPU, so an allocation made by a plug-in can fail or
+ * fragment the pool, and serving threads avoid cudaMalloc because it synchronises the device.
+ * The call runs one attention stage of the persistent kernel,
+ *     out[b, s, h*64:(h+1)*64] = softmax(scale * Q_h K_h^T + (1 - mask) * mask_scale) V_h,
+ * on caller-owned f16 buffers and keeps everything else the kernel needs (stage table, tensor
+ * maps, barrier counter, status word, the f32 additive mask) in a static device array of
+ * 2 KB + 4 * MONONN_NOALLOC_MAX_TOKENS bytes that every GPU loading the library holds until exit.
+ *   q, k   f16 [batches*seq, ld_qk], head h in columns h*64 .. h*64+63
+ *   v_t    f16 [batches*heads*64, ld_vt]: V transposed per batch (row = b*heads*64 + h*64 + d,
+ *          column = key position)
+ *   mask   int32 [batches, seq] or NULL;  out  f16 [batches*seq, ld_out]
+ * Limits: seq <= 128, head dimension 64, batches*seq <= MONONN_NOALLOC_MAX_TOKENS (larger
+ * sizes return MONONN_ERR_TOO_LARGE); base addresses and row pitches multiples of 16 bytes.
+ * The call is asynchronous on `cuda_stream` and allocates nothing. All calls on a device
+ * share the static array and rewrite it: calls that overlap on the GPU (other streams or
+ * threads) race, so serialise them. The first call on a device does the one-time set-up
+ * (device address of the array, kernel attributes) and should come before any stream capture. */
+#define MONONN_NOALLOC_MAX_TOKENS 16384
+int mononn_attention_noalloc(const void* q, const void* k, const void* v_t, const int32_t* mask,
+                             void* out, unsigned batches, unsigned heads, unsigned seq,
+                             unsigned ld_qk, unsigned ld_vt, unsigned ld_out, float scale,
+                             float mask_scale, int causal, void* cuda_stream);
+
 void mononn_destroy(mononn_module* m);
 const char* mononn_strerror(int code);
 /* Message of the last failing call on this thread. */

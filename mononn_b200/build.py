@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libmononn_b200.so")
-SOURCES = ["megakernel.cu", "runtime.cu", "scheduler.cc", "builders.cc", "spec.cc", "tuner.cc",
+SOURCES = ["megakernel.cu", "runtime.cu", "noalloc.cu", "scheduler.cc", "builders.cc", "spec.cc", "tuner.cc",
            "capi.cc", "hlo_parser.cc", "hlo_interp.cc", "hlo_lowering.cc"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared",
          "-Xcompiler", "-fPIC"]

@@ -17,7 +17,7 @@ EXPORTS = [
     "mononn_constant_info", "mononn_launch", "mononn_last_status", "mononn_tune",
     "mononn_save_spec", "mononn_spec_json", "mononn_profile_stages", "mononn_module_cost",
     "mononn_destroy", "mononn_strerror", "mononn_last_error", "mononn_enabled",
-    "mononn_trace_stages", "mononn_plan_json", "mononn_describe", "mononn_free_string", "mononn_launch_stages", "mononn_debug_skew_barrier",
+    "mononn_trace_stages", "mononn_plan_json", "mononn_describe", "mononn_free_string", "mononn_launch_stages", "mononn_debug_skew_barrier", "mononn_attention_noalloc",
 ]
 
 
@@ -73,6 +73,8 @@ def lib() -> C.CDLL:
         l.mononn_free_string.restype = None
         l.mononn_launch_stages.argtypes = [vp, C.POINTER(vp), C.c_int, vp, C.c_uint, C.c_uint]
         l.mononn_debug_skew_barrier.argtypes = [vp, C.c_uint]
+        l.mononn_attention_noalloc.argtypes = [vp, vp, vp, vp, vp, C.c_uint, C.c_uint, C.c_uint, C.c_uint,
+                                               C.c_uint, C.c_uint, C.c_float, C.c_float, C.c_int, vp]
         l.mononn_destroy.argtypes = [vp]
         l.mononn_destroy.restype = None
         l.mononn_strerror.argtypes = [C.c_int]

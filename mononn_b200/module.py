@@ -213,6 +213,20 @@ def describe(kind: str, text: str, spec: dict | None = None, sm_count: int = 148
         lib().mononn_free_string(out)
 
 
+def attention_noalloc(q_ptr: int, k_ptr: int, vt_ptr: int, mask_ptr: int | None, out_ptr: int, batches: int,
+                      heads: int, seq: int, ld_qk: int, ld_vt: int, ld_out: int, scale: float,
+                      mask_scale: float = -10000.0, causal: bool = False, stream=None) -> None:
+    """Allocation-free attention on caller-owned device buffers (raw device pointers): for
+    hosts whose allocator owns the GPU and where this library must not cudaMalloc.  Calls on
+    one device share a static scratch array and must not overlap on the GPU."""
+    import torch
+    st = stream if stream is not None else torch.cuda.current_stream()
+    check(lib().mononn_attention_noalloc(C.c_void_p(q_ptr), C.c_void_p(k_ptr), C.c_void_p(vt_ptr),
+                                         C.c_void_p(mask_ptr) if mask_ptr else None, C.c_void_p(out_ptr),
+                                         batches, heads, seq, ld_qk, ld_vt, ld_out, scale, mask_scale,
+                                         1 if causal else 0, C.c_void_p(st.cuda_stream)))
+
+
 def enabled() -> bool:
     """TF_MONONN_ENABLED truthiness (True / true / 1)."""
     return bool(lib().mononn_enabled())

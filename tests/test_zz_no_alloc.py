@@ -1,0 +1,74 @@
+"""The allocation-free attention entry point (-m gpu), collected last on purpose.
+
+Some hosts cannot let this library allocate device memory (a framework allocator that owns
+the whole GPU, or a serving thread that must not hit cudaMalloc's device synchronisation).
+`mononn_attention_noalloc` runs the persistent kernel's attention stage with all of its
+internal state in a static device array.  Here it is called through the C ABI on the Q, K,
+V^T tensors a regular module produced, twice in a row, and must reproduce the regular entry
+point's attention output.
+"""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _tensor(plan, name):
+    return next(t for t in plan["tensors"] if t["name"] == name)
+
+
+def test_noalloc_attention_matches_the_module_path_twice():
+    import torch
+    from mononn_b200 import bert_tiny, capi, compile_encoder, make_inputs, make_weights
+    from mononn_b200.module import attention_noalloc
+
+    cfg = bert_tiny(batch=3, seq=40, layers=1, hidden=128, ffn=256)
+    w = make_weights(cfg, 31, stress=True)
+    inp = make_inputs(cfg, 31, pad_fraction=0.25)
+    mod = compile_encoder(cfg)
+    mod.set_weights(w)
+    bufs = mod.allocate()
+    descs = mod.args()
+    for d, key in zip(descs[:3], ("input_ids", "attention_mask", "token_type_ids")):
+        src = torch.from_numpy(inp[key]).view(torch.uint8).reshape(-1)
+        bufs[d["index"]][: src.numel()].copy_(src)
+    plan = mod.plan()
+    names = [s["name"] for s in plan["stages"]]
+    att_stage = next(i for i, s in enumerate(plan["stages"]) if s["ops"][0]["kind"] == "attention")
+    assert names[att_stage] == "layer0.attn.core"
+    # existing entry point: embeddings, Q/K/V projections, then the attention stage
+    mod.launch_stages(0, att_stage + 1)
+    mod.status()
+    temp = bufs[[d["index"] for d in descs if d["kind"] == 2][0]]
+    q, k, vt, ctx = (_tensor(plan, "layer0." + n) for n in ("q", "k", "v_t", "ctx"))
+    T, H = cfg.tokens, cfg.hidden
+
+    def view(t):
+        raw = temp.cpu().numpy()[t["at"]["offset"]: t["at"]["offset"] + T * H * 2]
+        return raw.view(np.float16).reshape(T, H).astype(np.float32)
+
+    want = view(ctx)
+    assert np.isfinite(want).all() and np.abs(want).max() > 0
+    base = temp.data_ptr()
+    mask_dev = bufs[descs[1]["index"]]
+    out = torch.zeros(T * H, dtype=torch.float16, device="cuda")
+    free_before = torch.cuda.mem_get_info()[0]
+    for call in range(2):  # the static scratch keeps the previous call's contents
+        out.zero_()
+        attention_noalloc(base + q["at"]["offset"], base + k["at"]["offset"], base + vt["at"]["offset"],
+                          mask_dev.data_ptr(), out.data_ptr(), cfg.batch, cfg.heads, cfg.seq,
+                          q["ld"], vt["ld"], H, 1.0 / 8.0)
+        torch.cuda.synchronize()
+        got = out.cpu().numpy().reshape(T, H).astype(np.float32)
+        # same kernel code on the same inputs: the two paths agree to f16 rounding
+        assert np.abs(got - want).max() <= 1e-3, f"call {call}: {np.abs(got - want).max()}"
+    assert torch.cuda.mem_get_info()[0] >= free_before  # nothing was allocated on the device
+
+    # sizes beyond the static array are refused with a clear error
+    with pytest.raises(capi.MononnError) as e:
+        attention_noalloc(base, base, base, None, out.data_ptr(), 1024, 2, 128, 128, 128, 128, 0.125)
+    assert e.value.code == -10 and "16384" in str(e.value)
+    with pytest.raises(capi.MononnError) as e:
+        attention_noalloc(base, base, base, None, out.data_ptr(), 1, 2, 200, 128, 200, 128, 0.125)
+    assert e.value.code == -10
+    mod.close()
