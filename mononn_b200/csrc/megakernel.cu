@@ -172,9 +172,14 @@ struct Ctrl {
   uint32_t abort_flag;
   float bias_tile[2][256];  // bias of the current GEMM tile, double buffered across items
   float mask_row[128];      // additive mask of the current attention tile
+  // Shared-memory copies of the operator descriptor each role is working on: slot 0 weight
+  // producer, 1 activation producer, 2 MMA issuer, 3..6 the four epilogue warps.
+  uint4 desc[7][16];
 };
 
-static_assert(sizeof(Ctrl) <= 4096, "control block exceeds its shared-memory reserve");
+static_assert(sizeof(Ctrl) <= 8192, "control block exceeds its shared-memory reserve");
+static_assert(sizeof(OpDesc) % 16 == 0 && sizeof(OpDesc) <= 256, "descriptor slot size");
+static_assert(sizeof(StageDesc) == 48, "stage descriptor is read as three 16-byte words");
 
 struct Ctx {
   const KernelParams* P;
@@ -217,16 +222,6 @@ __device__ __forceinline__ void trace(const KernelParams& P, uint32_t stage, uin
     P.trace[(static_cast<size_t>(blockIdx.x) * (P.stage_end - P.stage_begin) +
              (stage - P.stage_begin)) * kTraceEvents + ev] = globaltimer_ns();
 }
-// Pull the descriptors of the following stage into L1 while this stage runs.
-__device__ __forceinline__ void prefetch_next_stage(const KernelParams& P, uint32_t s,
-                                                    const StageDesc& st) {
-  if (s + 1 >= P.stage_end) return;
-  asm volatile("prefetch.global.L1 [%0];" ::"l"(P.stages + s + 1));
-  const uint8_t* o = reinterpret_cast<const uint8_t*>(P.ops + st.op_begin + st.op_count);
-#pragma unroll
-  for (int i = 0; i < 6; ++i) asm volatile("prefetch.global.L1 [%0];" ::"l"(o + 128 * i));
-}
-
 // Bounded wait on an mbarrier phase. Returns false when the kernel is aborting. The slow
 // path is out of line so that the many wait sites stay a few instructions each.
 __device__ __noinline__ bool mbar_wait_slow(const KernelParams* P, Ctrl* ctrl, uint32_t b,
@@ -319,14 +314,46 @@ struct Item {
   uint32_t local;  // item index inside the op
 };
 
-__device__ __forceinline__ Item locate(const KernelParams& P, const StageDesc& st, uint32_t item) {
-  const OpDesc* op = P.ops + st.op_begin;
-  uint32_t i = item;
-  for (uint32_t k = 0; k + 1 < st.op_count && i >= op->n_items; ++k) {
-    i -= op->n_items;
-    ++op;
+// Descriptors are read with straight-line code (no branch between two loads, which would
+// serialise them) into registers / shared memory, and the first item's descriptor of a stage
+// is fetched before the role waits for the previous stage's barrier.
+__device__ __forceinline__ StageDesc load_stage(const KernelParams& P, uint32_t s) {
+  StageDesc st;
+  const uint4* g = reinterpret_cast<const uint4*>(P.stages + s);
+  uint4* d = reinterpret_cast<uint4*>(&st);
+  d[0] = __ldg(g);
+  d[1] = __ldg(g + 1);
+  d[2] = __ldg(g + 2);
+  return st;
+}
+
+// Copies the descriptor of the operator that owns work item `item` of the stage into `slot`
+// and returns it with the item's index inside that operator. WARP: all 32 lanes call it and
+// share the slot; otherwise one thread does the copy.
+template <bool WARP>
+__device__ __forceinline__ Item fetch_item(const KernelParams& P, const StageDesc& st, uint32_t item,
+                                           uint4* slot, uint32_t lane) {
+  uint32_t k = 0, base = 0;
+#pragma unroll
+  for (int j = 0; j < 7; ++j) {  // unused entries of item_end are 0xffffffff
+    const bool past = item >= st.item_end[j];
+    k += past ? 1u : 0u;
+    base = past ? st.item_end[j] : base;
   }
-  return Item{op, i};
+  const uint4* g = reinterpret_cast<const uint4*>(P.ops + st.op_begin + k);
+  constexpr int kWords = sizeof(OpDesc) / 16;
+  if (WARP) {
+    __syncwarp();
+    if (lane < kWords) slot[lane] = __ldg(g + lane);
+    __syncwarp();
+  } else {
+    uint4 r[kWords];
+#pragma unroll
+    for (int i = 0; i < kWords; ++i) r[i] = __ldg(g + i);
+#pragma unroll
+    for (int i = 0; i < kWords; ++i) slot[i] = r[i];
+  }
+  return Item{reinterpret_cast<const OpDesc*>(slot), item - base};
 }
 
 struct GemmTile {
@@ -356,6 +383,15 @@ __device__ __forceinline__ AttnTile attn_tile(const OpDesc& op, uint32_t local) 
 
 constexpr uint32_t kAttnASlots = 5;  // Q, K, V^T, P(2)
 
+// The CTAs of a GEMM stage all walk the same K range of the A operand. Starting each CTA at
+// a different k-block group (and wrapping around) spreads their simultaneous tile requests
+// over the whole operand instead of hammering the L2 lines of one tile in lock-step. The
+// rotation is in units of weight-ring groups and only used when the groups are all full, so
+// that the MMA issuer's pairing of A slots with weight sub-tiles is unchanged.
+__device__ __forceinline__ uint32_t k_rotation(uint32_t nkb, uint32_t kbps) {
+  return (nkb % kbps == 0u) ? blockIdx.x % (nkb / kbps) : 0u;
+}
+
 // ----------------------------------------------------------------------------
 // Role: weight producer (warp 0, one lane)
 // ----------------------------------------------------------------------------
@@ -365,10 +401,9 @@ __device__ void role_weight_producer(Ctx c) {
   uint32_t b_cnt = 0;
   for (uint32_t s = P.stage_begin; s < P.stage_end; ++s) {
     c.stage = s;
-    const StageDesc st = P.stages[s];
-    prefetch_next_stage(P, s, st);
+    const StageDesc st = load_stage(P, s);
     for (uint32_t item = blockIdx.x; item < st.n_items; item += gridDim.x) {
-      const Item it = locate(P, st, item);
+      const Item it = fetch_item<false>(P, st, item, c.ctrl->desc[0], 0);
       const OpDesc& op = *it.op;
       if (op.kind != OP_GEMM) continue;
       const GemmTile t = gemm_tile(op, it.local);
@@ -377,7 +412,9 @@ __device__ void role_weight_producer(Ctx c) {
       const uint32_t row0 = (t.nt * kb_total + t.ks * nkb) * op.n_tile;
       const uint32_t bytes = op.n_tile * kbps * 128u;
       const void* tm = tmaps + static_cast<size_t>(op.tmap_b) * 128u;
-      for (uint32_t kb = 0; kb < nkb; kb += kbps) {
+      const uint32_t groups = (nkb + kbps - 1) / kbps, rot = k_rotation(nkb, kbps);
+      for (uint32_t gi = 0; gi < groups; ++gi) {
+        const uint32_t kb = ((gi + rot) % groups) * kbps;
         const uint32_t slot = b_cnt % kBSlots, use = b_cnt / kBSlots;
         WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->b_empty[slot], (use & 1u) ^ 1u, 0x100));
         const uint32_t full = smem_u32(&c.ctrl->b_full[slot]);
@@ -400,10 +437,11 @@ __device__ void role_act_producer(Ctx c) {
   uint32_t a_cnt = 0;
   for (uint32_t s = P.stage_begin; s < P.stage_end; ++s) {
     c.stage = s;
-    const StageDesc st = P.stages[s];
-    prefetch_next_stage(P, s, st);
+    const StageDesc st = load_stage(P, s);
+    Item first{nullptr, 0};
     if (blockIdx.x < st.n_items) {
-      const OpDesc& op0 = *locate(P, st, blockIdx.x).op;
+      first = fetch_item<false>(P, st, blockIdx.x, c.ctrl->desc[1], 0);
+      const OpDesc& op0 = *first.op;
       if (op0.kind == OP_GEMM || op0.kind == OP_ATTENTION) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(tmaps + static_cast<size_t>(op0.tmap_a) * 128u));
         if (op0.kind == OP_ATTENTION) {
@@ -414,7 +452,7 @@ __device__ void role_act_producer(Ctx c) {
     }
     bool waited = false;
     for (uint32_t item = blockIdx.x; item < st.n_items; item += gridDim.x) {
-      const Item it = locate(P, st, item);
+      const Item it = (item == blockIdx.x) ? first : fetch_item<false>(P, st, item, c.ctrl->desc[1], 0);
       const OpDesc& op = *it.op;
       if (op.kind != OP_GEMM && op.kind != OP_ATTENTION) continue;
       if (!waited) {
@@ -426,8 +464,10 @@ __device__ void role_act_producer(Ctx c) {
       if (op.kind == OP_GEMM) {
         const GemmTile t = gemm_tile(op, it.local);
         const void* tm = tmaps + static_cast<size_t>(op.tmap_a) * 128u;
-        const uint32_t nkb = op.kb_per_split;
-        for (uint32_t kb = 0; kb < nkb; ++kb) {
+        const uint32_t nkb = op.kb_per_split, kbps = op.kb_per_bslot;
+        const uint32_t groups = (nkb + kbps - 1) / kbps, rot = k_rotation(nkb, kbps);
+        for (uint32_t j = 0; j < nkb; ++j) {
+          const uint32_t kb = ((j / kbps + rot) % groups) * kbps + j % kbps;
           const uint32_t slot = a_cnt % kASlots, use = a_cnt / kASlots;
           WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->a_empty[slot], (use & 1u) ^ 1u, 0x201));
           const uint32_t full = smem_u32(&c.ctrl->a_full[slot]);
@@ -476,10 +516,9 @@ __device__ void role_mma(Ctx c, uint32_t tmem_base) {
   uint32_t a_cnt = 0, b_cnt = 0, acc_cnt = 0;
   for (uint32_t s = P.stage_begin; s < P.stage_end; ++s) {
     c.stage = s;
-    const StageDesc st = P.stages[s];
-    prefetch_next_stage(P, s, st);
+    const StageDesc st = load_stage(P, s);
     for (uint32_t item = blockIdx.x; item < st.n_items; item += gridDim.x) {
-      const Item it = locate(P, st, item);
+      const Item it = fetch_item<false>(P, st, item, c.ctrl->desc[2], 0);
       const OpDesc& op = *it.op;
       if (op.kind == OP_GEMM) {
         const uint32_t nkb = op.kb_per_split, kbps = op.kb_per_bslot;
@@ -792,24 +831,51 @@ __device__ __noinline__ void rowwise_item(const OpDesc& op, uint32_t local, uint
   const float inv_n = 1.0f / static_cast<float>(cols), eps = op.eps;
 
   const bool add_bias2 = (out2 != nullptr) && (bias2 != nullptr);
-  if (mark && (reinterpret_cast<uint64_t>(out) + reinterpret_cast<uint64_t>(gamma) +
-               reinterpret_cast<uint64_t>(s.f32) + reinterpret_cast<uint64_t>(s.h0) + nvec) != 1ull)
-    trace(P, stage, TR_MARK0 + 3);
   if (nvec <= 256u) {
-    // every global load of the row is issued before anything waits on one of them
+    // Every global load of the row is issued before anything waits on one of them. The
+    // loops are straight-line code (source kind decided outside, out-of-range chunks read
+    // chunk 0 and are zeroed afterwards): a branch between two loads would make the
+    // hardware wait for the first before issuing the second.
     float4 x[8];
     uint2 gv[8], bv[8], b2v[8];
+    uint32_t vj[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) vj[i] = (i * 32u + lane < nvec) ? i * 32u + lane : 0u;
+    if (s.f32 != nullptr) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] = __ldcg(s.f32 + vj[i]);
+    } else {
+      uint2 h[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) h[i] = __ldcg(s.h0 + vj[i]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] = h4_to_f4(h[i]);
+    }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const uint32_t vi = i * 32u + lane;
-      x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-      gv[i] = bv[i] = b2v[i] = make_uint2(0u, 0u);
-      if (vi < nvec) {
-        x[i] = row_chunk(s, vi);
-        gv[i] = __ldg(gamma + vi);
-        bv[i] = __ldg(beta + vi);
-        if (add_bias2) b2v[i] = __ldg(bias2 + vi);
-      }
+      gv[i] = __ldg(gamma + vj[i]);
+      bv[i] = __ldg(beta + vj[i]);
+    }
+    if (add_bias2) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) b2v[i] = __ldg(bias2 + vj[i]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) b2v[i] = make_uint2(0u, 0u);
+    }
+    if (s.h1 != nullptr) {
+      uint2 h[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) h[i] = __ldcg(s.h1 + vj[i]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) add4(x[i], h4_to_f4(h[i]));
+    }
+    if (s.h2 != nullptr) {
+      uint2 h[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) h[i] = __ldcg(s.h2 + vj[i]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) add4(x[i], h4_to_f4(h[i]));
     }
     if (s.zero) {
 #pragma unroll
@@ -817,10 +883,12 @@ __device__ __noinline__ void rowwise_item(const OpDesc& op, uint32_t local, uint
         if (i * 32u + lane < nvec)
           const_cast<float4*>(s.f32)[i * 32u + lane] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    if (mark && x[0].x != 1.2345e-30f) trace(P, stage, TR_MARK0 + 4);
     float sum = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) sum += x[i].x + x[i].y + x[i].z + x[i].w;
+    for (int i = 0; i < 8; ++i) {
+      if (i * 32u + lane >= nvec) x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      sum += x[i].x + x[i].y + x[i].z + x[i].w;
+    }
     if (mark) trace(P, stage, TR_MARK0 + 1);
     const float mean = warp_sum(sum) * inv_n;
     float sq = 0.f;
@@ -989,16 +1057,18 @@ __device__ void role_simt(Ctx c, uint32_t tmem_base, uint32_t tid_in_group) {
   uint32_t a_cnt = 0, acc_cnt = 0;
   for (uint32_t s = P.stage_begin; s < P.stage_end; ++s) {
     c.stage = s;
-    const StageDesc st = P.stages[s];
+    const StageDesc st = load_stage(P, s);
+    uint4* slot = c.ctrl->desc[3 + quarter];
+    Item first{nullptr, 0};
+    if (blockIdx.x < st.n_items) first = fetch_item<true>(P, st, blockIdx.x, slot, lane);
     // All CTAs must have finished the previous stage before this CTA reads its
     // results or arrives for this stage.
-    prefetch_next_stage(P, s, st);
     WAIT_OR_RETURN(grid_wait_warp(c, s, 0x400));
     if (tid_in_group == 0) trace(P, s, TR_SIMT_READY);
     if (P.stamps != nullptr && blockIdx.x == 0 && tid_in_group == 0)
       P.stamps[s - P.stage_begin] = globaltimer_ns();
     for (uint32_t item = blockIdx.x; item < st.n_items; item += gridDim.x) {
-      const Item it = locate(P, st, item);
+      const Item it = (item == blockIdx.x) ? first : fetch_item<true>(P, st, item, slot, lane);
       const OpDesc& op = *it.op;
       switch (op.kind) {
         case OP_GEMM: {

@@ -178,6 +178,8 @@ extern "C" int mononn_attention_noalloc(const void* q, const void* k, const void
   od.p[0] = reinterpret_cast<uint64_t>(out);
   od.p[1] = mask ? reinterpret_cast<uint64_t>(s + kOffMask) : 0;
   sd.n_items = od.n_items;
+  for (uint32_t i = 0; i < kMaxStageOps; ++i) sd.item_end[i] = 0xffffffffu;
+  sd.item_end[0] = od.n_items;
   std::memcpy(img + kOffStage, &sd, sizeof(sd));
   std::memcpy(img + kOffOp, &od, sizeof(od));
   CUtensorMap tm;

@@ -134,7 +134,15 @@ int validate_plan(const Plan& P, std::string* err) {
   if (P.smem_bytes != kSmemBytes) return bad("shared memory size");
   for (size_t s = 0; s < P.stages.size(); ++s) {
     const StageDesc& sd = P.stages[s];
-    if (sd.op_begin + sd.op_count > P.ops.size() || sd.op_count == 0) return bad("stage op range");
+    if (sd.op_begin + sd.op_count > P.ops.size() || sd.op_count == 0 || sd.op_count > kMaxStageOps)
+      return bad("stage op range");
+    {
+      uint32_t run = 0;
+      for (uint32_t k = 0; k < kMaxStageOps; ++k) {
+        if (k < sd.op_count) run += P.ops[sd.op_begin + k].d.n_items;
+        if (sd.item_end[k] != ((k < sd.op_count) ? run : 0xffffffffu)) return bad("stage item prefix sums");
+      }
+    }
     uint32_t items = 0;
     for (uint32_t i = 0; i < sd.op_count; ++i) items += P.ops[sd.op_begin + i].d.n_items;
     if (items != sd.n_items) return bad("stage item count");
@@ -632,6 +640,17 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
       P.ops.push_back(po);
     }
     sd.op_count = static_cast<uint32_t>(P.ops.size()) - sd.op_begin;
+    if (sd.op_count > kMaxStageOps) {
+      if (err) *err = "more than " + std::to_string(kMaxStageOps) + " independent operators at one depth";
+      return MONONN_ERR_UNSUPPORTED;
+    }
+    {
+      uint32_t run = 0;
+      for (uint32_t k = 0; k < kMaxStageOps; ++k) {
+        if (k < sd.op_count) run += P.ops[sd.op_begin + k].d.n_items;
+        sd.item_end[k] = (k < sd.op_count) ? run : 0xffffffffu;
+      }
+    }
     P.stages.push_back(sd);
     P.stage_names.push_back(sname);
   }

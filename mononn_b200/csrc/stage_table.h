@@ -85,11 +85,16 @@ struct alignas(16) OpDesc {
   uint64_t q[4];  // LAYERNORM / EMBED: q[2] second output (f32, + q[3] bias f16), see plan
 };
 
+constexpr uint32_t kMaxStageOps = 8;
+
 struct alignas(16) StageDesc {
   uint32_t op_begin;
-  uint32_t op_count;
-  uint32_t n_items;  // sum over the ops
+  uint32_t op_count;  // at most kMaxStageOps
+  uint32_t n_items;   // sum over the ops
   uint32_t flags;
+  // item_end[k] = work items of ops 0..k; entries past the last op are 0xffffffff, so the
+  // owner of an item is found by comparisons alone
+  uint32_t item_end[kMaxStageOps];
 };
 
 // Status word written by the kernel when a bounded wait expires.
