@@ -171,7 +171,7 @@ struct Ctrl {
   uint32_t tmem_base;
   uint32_t abort_flag;
   float bias_tile[2][256];  // bias of the current GEMM tile, double buffered across items
-  float mask_row[128];      // additive mask of the current attention tile
+  float mask_row[384];      // additive key mask of the current attention tile (log2 units)
   // Shared-memory copies of the operator descriptor each role is working on: slot 0 weight
   // producer, 1 activation producer, 2 MMA issuer, 3..6 the four epilogue warps.
   uint4 desc[7][16];
@@ -381,7 +381,14 @@ __device__ __forceinline__ AttnTile attn_tile(const OpDesc& op, uint32_t local) 
   return t;
 }
 
-constexpr uint32_t kAttnASlots = 5;  // Q, K, V^T, P(2)
+// Attention work item: 128 query rows of one (batch, head) against all keys, in chunks of
+// 128 keys. All score chunks stay in TMEM (columns 0 .. 128*chunks) next to the output
+// (columns kAttnOutCol..+63), so sequences up to 384 need no rescaling pass. Activation-ring
+// slots of an item, in allocation order: Q, K_0..K_{n-1}, then per chunk V^T_j, P_j (two
+// slots, written by the softmax warps).
+constexpr uint32_t kAttnOutCol = 448;
+__device__ __forceinline__ uint32_t attn_chunks(const OpDesc& op) { return (op.seq + 127u) / 128u; }
+__device__ __forceinline__ uint32_t attn_slots(const OpDesc& op) { return 1u + 4u * attn_chunks(op); }
 
 // The CTAs of a GEMM stage all walk the same K range of the A operand. Starting each CTA at
 // a different k-block group (and wrapping around) spreads their simultaneous tile requests
@@ -482,7 +489,10 @@ __device__ void role_act_producer(Ctx c) {
         const void* tm = tmaps + static_cast<size_t>(op.tmap_a) * 128u;
         const void* tmk = tmaps + static_cast<size_t>(op.tmap_b) * 128u;
         const void* tmv = tmaps + static_cast<size_t>(op.tmap_vt) * 128u;
-        for (uint32_t j = 0; j < 3; ++j) {
+        const uint32_t nc = attn_chunks(op);
+        // Q, K_0 .. K_{nc-1}, then V^T_j for every chunk (the P slots in between are skipped)
+        for (uint32_t j = 0; j < 1u + 2u * nc; ++j) {
+          if (j > nc) a_cnt += (j == nc + 1u) ? 0u : 2u;  // step over the previous chunk's P slots
           const uint32_t slot = a_cnt % kASlots, use = a_cnt / kASlots;
           WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->a_empty[slot], (use & 1u) ^ 1u, 0x202));
           const uint32_t full = smem_u32(&c.ctrl->a_full[slot]);
@@ -491,17 +501,18 @@ __device__ void role_act_producer(Ctx c) {
           if (j == 0) {
             tma_load_2d(dst, tm, static_cast<int32_t>(op.q_col + t.h * 64u),
                         static_cast<int32_t>(t.b * op.seq + t.mt * 128u), full);
-          } else if (j == 1) {
+          } else if (j <= nc) {
             tma_load_2d(dst, tmk, static_cast<int32_t>(op.k_col + t.h * 64u),
-                        static_cast<int32_t>(t.b * op.seq), full);
+                        static_cast<int32_t>(t.b * op.seq + (j - 1u) * 128u), full);
           } else {
+            const int32_t x = static_cast<int32_t>((j - nc - 1u) * 128u);
             const int32_t y = static_cast<int32_t>((t.b * op.heads + t.h) * 64u);
-            tma_load_2d(dst, tmv, 0, y, full);
-            tma_load_2d(dst + 8192u, tmv, 64, y, full);
+            tma_load_2d(dst, tmv, x, y, full);
+            tma_load_2d(dst + 8192u, tmv, x + 64, y, full);
           }
           ++a_cnt;
         }
-        a_cnt += 2;  // the two P slots are filled by the softmax warps
+        a_cnt += 2;  // the last chunk's P slots
       }
       trace(P, s, TR_ACT_ISSUED);
     }
@@ -555,50 +566,50 @@ __device__ void role_mma(Ctx c, uint32_t tmem_base) {
         ++acc_cnt;
         trace(P, s, TR_MMA_LAST);
       } else if (op.kind == OP_ATTENTION) {
-        uint32_t slot[kAttnASlots], par[kAttnASlots];
-        for (uint32_t j = 0; j < kAttnASlots; ++j) {
-          slot[j] = (a_cnt + j) % kASlots;
-          par[j] = ((a_cnt + j) / kASlots) & 1u;
-        }
-        a_cnt += kAttnASlots;
-        // S = Q K^T  (128 x 128, K = 64)
-        uint32_t buf = acc_cnt & 1u;
-        WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->acc_empty[buf], ((acc_cnt >> 1) & 1u) ^ 1u, 0x310));
-        WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->a_full[slot[0]], par[0], 0x311));
-        WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->a_full[slot[1]], par[1], 0x312));
-        tc_fence_after();
-        {
-          const uint64_t ad = umma_desc_sw128(c.a_ring + slot[0] * kSlotBytes);
-          const uint64_t bd = umma_desc_sw128(c.a_ring + slot[1] * kSlotBytes);
+        const uint32_t nc = attn_chunks(op), base = a_cnt;
+        a_cnt += attn_slots(op);
+        auto slot_of = [](uint32_t cnt) { return cnt % kASlots; };
+        auto par_of = [](uint32_t cnt) { return (cnt / kASlots) & 1u; };
+        // the scores may span both accumulator buffers: both must have been drained
+        const uint32_t phS = acc_cnt, phO = acc_cnt + 1u;
+        WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->acc_empty[phS & 1u], ((phS >> 1) & 1u) ^ 1u, 0x310));
+        WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->acc_empty[phO & 1u], ((phO >> 1) & 1u) ^ 1u, 0x313));
+        // S_j = Q K_j^T  (128 x 128, K = 64) into columns j*128
+        WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->a_full[slot_of(base)], par_of(base), 0x311));
+        for (uint32_t j = 0; j < nc; ++j) {
+          const uint32_t kc = base + 1u + j;
+          WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->a_full[slot_of(kc)], par_of(kc), 0x312));
+          tc_fence_after();
+          const uint64_t ad = umma_desc_sw128(c.a_ring + slot_of(base) * kSlotBytes);
+          const uint64_t bd = umma_desc_sw128(c.a_ring + slot_of(kc) * kSlotBytes);
           const uint32_t idesc = umma_idesc_m128(128);
 #pragma unroll
           for (uint32_t k = 0; k < 4; ++k)
-            tc_mma_f16(tmem_base + buf * kAccCols, ad + 2u * k, bd + 2u * k, idesc, k != 0u);
+            tc_mma_f16(tmem_base + j * 128u, ad + 2u * k, bd + 2u * k, idesc, k != 0u);
+          tc_commit(smem_u32(&c.ctrl->a_empty[slot_of(kc)]));
         }
-        tc_commit(smem_u32(&c.ctrl->acc_full[buf]));
-        ++acc_cnt;
-        // O = P V  (128 x 64, K = 128)
-        buf = acc_cnt & 1u;
-        WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->acc_empty[buf], ((acc_cnt >> 1) & 1u) ^ 1u, 0x313));
-        WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->a_full[slot[2]], par[2], 0x314));
-        WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->a_full[slot[3]], par[3], 0x315));
-        WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->a_full[slot[4]], par[4], 0x316));
-        tc_fence_after();
-        {
+        tc_commit(smem_u32(&c.ctrl->a_empty[slot_of(base)]));
+        tc_commit(smem_u32(&c.ctrl->acc_full[phS & 1u]));
+        // O += P_j V_j  (128 x 64, K = 128 per chunk) into columns kAttnOutCol..
+        for (uint32_t j = 0; j < nc; ++j) {
+          const uint32_t vc = base + 1u + nc + 3u * j;
+          WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->a_full[slot_of(vc)], par_of(vc), 0x314));
+          WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->a_full[slot_of(vc + 1u)], par_of(vc + 1u), 0x315));
+          WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->a_full[slot_of(vc + 2u)], par_of(vc + 2u), 0x316));
+          tc_fence_after();
           const uint32_t idesc = umma_idesc_m128(64);
 #pragma unroll
           for (uint32_t kb = 0; kb < 2; ++kb) {
-            const uint64_t ad = umma_desc_sw128(c.a_ring + slot[3 + kb] * kSlotBytes);
-            const uint64_t bd = umma_desc_sw128(c.a_ring + slot[2] * kSlotBytes + kb * 8192u);
+            const uint64_t ad = umma_desc_sw128(c.a_ring + slot_of(vc + 1u + kb) * kSlotBytes);
+            const uint64_t bd = umma_desc_sw128(c.a_ring + slot_of(vc) * kSlotBytes + kb * 8192u);
 #pragma unroll
             for (uint32_t k = 0; k < 4; ++k)
-              tc_mma_f16(tmem_base + buf * kAccCols, ad + 2u * k, bd + 2u * k, idesc,
-                         (kb | k) != 0u);
+              tc_mma_f16(tmem_base + kAttnOutCol, ad + 2u * k, bd + 2u * k, idesc, (j | kb | k) != 0u);
           }
+          for (uint32_t q = 0; q < 3; ++q) tc_commit(smem_u32(&c.ctrl->a_empty[slot_of(vc + q)]));
         }
-        for (uint32_t j = 0; j < kAttnASlots; ++j) tc_commit(smem_u32(&c.ctrl->a_empty[slot[j]]));
-        tc_commit(smem_u32(&c.ctrl->acc_full[buf]));
-        ++acc_cnt;
+        tc_commit(smem_u32(&c.ctrl->acc_full[phO & 1u]));
+        acc_cnt += 2;
       }
     }
   }
@@ -940,90 +951,97 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
   const AttnTile t = attn_tile(op, local);
   const uint32_t row = quarter * 32u + lane;
   const uint32_t qrow = t.mt * 128u + row;  // query index inside the sequence
-  const uint32_t slotP0 = (a_cnt + 3) % kASlots, slotP1 = (a_cnt + 4) % kASlots;
-  const uint32_t parP0 = ((a_cnt + 3) / kASlots) & 1u, parP1 = ((a_cnt + 4) / kASlots) & 1u;
-  a_cnt += kAttnASlots;
-
-  uint32_t buf = acc_cnt & 1u;
-  const uint32_t seq = op.seq;
-  const uint32_t n_keys = seq < 128u ? seq : 128u;
+  const uint32_t nc = attn_chunks(op), base = a_cnt;
+  a_cnt += attn_slots(op);
+  const uint32_t phS = acc_cnt, phO = acc_cnt + 1u;
+  acc_cnt += 2;
+  const uint32_t seq = op.seq, n_cols = nc * 128u;
   const float alpha = op.alpha * 1.4426950408889634f;  // scores in log2 units: exp(x) = 2^(x log2 e)
   // Stage the additive key mask of this batch row while Q, K load and QK^T runs; keys past
   // the sequence end are masked out here so the loops below need no bound check.
   float* mb = c.ctrl->mask_row;
   {
-    float m = -1.0e30f;
-    if (tid_in_group < n_keys)
-      m = (op.flags & F_MASK_BIAS)
-              ? __ldcg(reinterpret_cast<const float*>(op.p[1]) + static_cast<size_t>(t.b) * seq +
-                       tid_in_group)
-              : 0.f;
-    mb[tid_in_group] = m * 1.4426950408889634f;
+    const bool has_mask = (op.flags & F_MASK_BIAS) != 0u;
+    const float* gm = reinterpret_cast<const float*>(op.p[1]) + static_cast<size_t>(t.b) * seq;
+    for (uint32_t i = tid_in_group; i < n_cols; i += 128u) {
+      float m = -1.0e30f;
+      if (i < seq) m = has_mask ? __ldcg(gm + i) : 0.f;
+      mb[i] = m * 1.4426950408889634f;
+    }
     if (!group_sync(c, 0x415)) return false;
   }
   // causal: keys after the query are masked
   const uint32_t key_limit = (op.flags & F_CAUSAL) ? qrow : 0xffffffffu;
-  if (!mbar_wait_warp(c, &c.ctrl->acc_full[buf], (acc_cnt >> 1) & 1u, 0x410)) return false;
+  if (!mbar_wait_warp(c, &c.ctrl->acc_full[phS & 1u], (phS >> 1) & 1u, 0x410)) return false;
   if (tid_in_group == 0) trace(*c.P, c.stage, TR_MARK0);
   tc_fence_after();
-  const uint32_t tS = tmem_base + buf * kAccCols + ((quarter * 32u) << 16);
-  // pass 1: row maximum of scale*s + mask
-  float mx = -3.0e38f;
+  const uint32_t tS = tmem_base + ((quarter * 32u) << 16);
+  // pass 1: row maximum of scale*s + mask (four independent chains: one warp per scheduler
+  // has nothing else to hide the dependent-issue latency with)
+  float m0 = -3.0e38f, m1 = -3.0e38f, m2 = -3.0e38f, m3 = -3.0e38f;
 #pragma unroll 1
-  for (uint32_t c0 = 0; c0 < 128u; c0 += 32) {
+  for (uint32_t c0 = 0; c0 < n_cols; c0 += 32) {
     float v[32];
     tc_ld32(tS + c0, v);
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const float z = (c0 + i <= key_limit) ? fmaf(v[i], alpha, mb[c0 + i]) : -1.0e30f;
-      mx = fmaxf(mx, z);
+    for (int i = 0; i < 32; i += 4) {
+      m0 = fmaxf(m0, (c0 + i <= key_limit) ? fmaf(v[i], alpha, mb[c0 + i]) : -1.0e30f);
+      m1 = fmaxf(m1, (c0 + i + 1 <= key_limit) ? fmaf(v[i + 1], alpha, mb[c0 + i + 1]) : -1.0e30f);
+      m2 = fmaxf(m2, (c0 + i + 2 <= key_limit) ? fmaf(v[i + 2], alpha, mb[c0 + i + 2]) : -1.0e30f);
+      m3 = fmaxf(m3, (c0 + i + 3 <= key_limit) ? fmaf(v[i + 3], alpha, mb[c0 + i + 3]) : -1.0e30f);
     }
   }
+  const float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
   if (tid_in_group == 0) trace(*c.P, c.stage, TR_MARK0 + 1);
-  // the P slots must be free before they are overwritten
-  if (!mbar_wait_warp(c, &c.ctrl->a_empty[slotP0], parP0 ^ 1u, 0x411)) return false;
-  if (!mbar_wait_warp(c, &c.ctrl->a_empty[slotP1], parP1 ^ 1u, 0x412)) return false;
-  // pass 2: p = exp(z - max), row sum, P tile in the swizzled K-major operand layout
+  // pass 2: p = exp(z - max), row sum, P tiles in the swizzled K-major operand layout
   float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll 1
-  for (uint32_t c0 = 0; c0 < 128u; c0 += 32) {
-    float v[32];
-    tc_ld32(tS + c0, v);
+  for (uint32_t j = 0; j < nc; ++j) {
+    const uint32_t cP = base + 2u + nc + 3u * j;  // first of the chunk's two P slots
+    const uint32_t slotP0 = cP % kASlots, slotP1 = (cP + 1u) % kASlots;
+    // the P slots must be free before they are overwritten
+    if (!mbar_wait_warp(c, &c.ctrl->a_empty[slotP0], ((cP / kASlots) & 1u) ^ 1u, 0x411)) return false;
+    if (!mbar_wait_warp(c, &c.ctrl->a_empty[slotP1], (((cP + 1u) / kASlots) & 1u) ^ 1u, 0x412))
+      return false;
+#pragma unroll 1
+    for (uint32_t c0 = 0; c0 < 128u; c0 += 32) {
+      const uint32_t cc = j * 128u + c0;
+      float v[32];
+      tc_ld32(tS + cc, v);
 #pragma unroll
-    for (int i = 0; i < 32; i += 2) {
-      const float z0 = (c0 + i <= key_limit) ? fmaf(v[i], alpha, mb[c0 + i]) : -1.0e30f;
-      const float z1 = (c0 + i + 1 <= key_limit) ? fmaf(v[i + 1], alpha, mb[c0 + i + 1]) : -1.0e30f;
-      v[i] = fast_exp2(z0 - mx);
-      v[i + 1] = fast_exp2(z1 - mx);
-      sum0 += v[i];
-      sum1 += v[i + 1];
+      for (int i = 0; i < 32; i += 2) {
+        const float z0 = (cc + i <= key_limit) ? fmaf(v[i], alpha, mb[cc + i]) : -1.0e30f;
+        const float z1 = (cc + i + 1 <= key_limit) ? fmaf(v[i + 1], alpha, mb[cc + i + 1]) : -1.0e30f;
+        v[i] = fast_exp2(z0 - mx);
+        v[i + 1] = fast_exp2(z1 - mx);
+        sum0 += v[i];
+        sum1 += v[i + 1];
+      }
+      uint8_t* tile = c.a_ring_ptr + ((c0 < 64u) ? slotP0 : slotP1) * kSlotBytes;
+      const uint32_t chunk = (c0 & 63u) >> 3;  // 16-byte chunk index inside the 128-byte row
+#pragma unroll
+      for (uint32_t q = 0; q < 4; ++q) {
+        uint4* d = reinterpret_cast<uint4*>(tile + row * 128u + (((chunk + q) ^ (row & 7u)) << 4));
+        *d = make_uint4(pack_h2(v[8 * q], v[8 * q + 1]), pack_h2(v[8 * q + 2], v[8 * q + 3]),
+                        pack_h2(v[8 * q + 4], v[8 * q + 5]), pack_h2(v[8 * q + 6], v[8 * q + 7]));
+      }
     }
-    uint8_t* tile = c.a_ring_ptr + ((c0 < 64u) ? slotP0 : slotP1) * kSlotBytes;
-    const uint32_t chunk = (c0 & 63u) >> 3;  // 16-byte chunk index inside the 128-byte row
-#pragma unroll
-    for (uint32_t j = 0; j < 4; ++j) {
-      uint4* d = reinterpret_cast<uint4*>(tile + row * 128u + (((chunk + j) ^ (row & 7u)) << 4));
-      *d = make_uint4(pack_h2(v[8 * j], v[8 * j + 1]), pack_h2(v[8 * j + 2], v[8 * j + 3]),
-                      pack_h2(v[8 * j + 4], v[8 * j + 5]), pack_h2(v[8 * j + 6], v[8 * j + 7]));
+    fence_proxy_async_smem();
+    if (!group_sync(c, 0x414)) return false;
+    if (tid_in_group == 0) {
+      mbar_arrive(smem_u32(&c.ctrl->a_full[slotP0]));
+      mbar_arrive(smem_u32(&c.ctrl->a_full[slotP1]));
     }
   }
   if (tid_in_group == 0) trace(*c.P, c.stage, TR_MARK0 + 2);
-  fence_proxy_async_smem();
   tc_fence_before();
-  if (!group_sync(c, 0x414)) return false;
-  if (tid_in_group == 0) {
-    mbar_arrive(smem_u32(&c.ctrl->a_full[slotP0]));
-    mbar_arrive(smem_u32(&c.ctrl->a_full[slotP1]));
-  }
-  mbar_arrive(smem_u32(&c.ctrl->acc_empty[buf]));
-  ++acc_cnt;
+  mbar_arrive(smem_u32(&c.ctrl->acc_empty[phS & 1u]));
 
-  // O = P V
-  buf = acc_cnt & 1u;
-  if (!mbar_wait_warp(c, &c.ctrl->acc_full[buf], (acc_cnt >> 1) & 1u, 0x413)) return false;
+  // O = sum_j P_j V_j
+  if (!mbar_wait_warp(c, &c.ctrl->acc_full[phO & 1u], (phO >> 1) & 1u, 0x413)) return false;
   if (tid_in_group == 0) trace(*c.P, c.stage, TR_MARK0 + 3);
   tc_fence_after();
-  const uint32_t tO = tmem_base + buf * kAccCols + ((quarter * 32u) << 16);
+  const uint32_t tO = tmem_base + kAttnOutCol + ((quarter * 32u) << 16);
   const float inv = 1.0f / (sum0 + sum1);
   const bool row_ok = qrow < seq;
   __half* out = reinterpret_cast<__half*>(op.p[0]) +
@@ -1035,16 +1053,15 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
     if (row_ok) {
       uint4* o = reinterpret_cast<uint4*>(out + c0);
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-        o[j] = make_uint4(pack_h2(v[8 * j] * inv, v[8 * j + 1] * inv),
-                          pack_h2(v[8 * j + 2] * inv, v[8 * j + 3] * inv),
-                          pack_h2(v[8 * j + 4] * inv, v[8 * j + 5] * inv),
-                          pack_h2(v[8 * j + 6] * inv, v[8 * j + 7] * inv));
+      for (int q = 0; q < 4; ++q)
+        o[q] = make_uint4(pack_h2(v[8 * q] * inv, v[8 * q + 1] * inv),
+                          pack_h2(v[8 * q + 2] * inv, v[8 * q + 3] * inv),
+                          pack_h2(v[8 * q + 4] * inv, v[8 * q + 5] * inv),
+                          pack_h2(v[8 * q + 6] * inv, v[8 * q + 7] * inv));
     }
   }
   tc_fence_before();
-  mbar_arrive(smem_u32(&c.ctrl->acc_empty[buf]));
-  ++acc_cnt;
+  mbar_arrive(smem_u32(&c.ctrl->acc_empty[phO & 1u]));
   return true;
 }
 

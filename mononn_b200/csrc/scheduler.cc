@@ -175,7 +175,7 @@ int validate_plan(const Plan& P, std::string* err) {
         break;
       }
       case OP_ATTENTION:
-        if (d.head_dim != 64 || d.seq == 0 || d.seq > 128) return bad(n + "attention geometry");
+        if (d.head_dim != 64 || d.seq == 0 || d.seq > 384) return bad(n + "attention geometry");
         if (d.tmap_a >= P.tmaps.size() || d.tmap_b >= P.tmaps.size() || d.tmap_vt >= P.tmaps.size())
           return bad(n + "tensor map index");
         if (P.tmaps[d.tmap_vt].box0 != 64 || P.tmaps[d.tmap_vt].box1 != 64) return bad(n + "V^T box");
@@ -532,8 +532,8 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
           break;
         }
         case OP_ATTENTION: {
-          if (o.head_dim != 64 || o.seq > 128) {
-            if (err) *err = "attention " + o.name + ": head_dim must be 64 and seq <= 128";
+          if (o.head_dim != 64 || o.seq > 384) {
+            if (err) *err = "attention " + o.name + ": head_dim must be 64 and seq <= 384";
             return MONONN_ERR_UNSUPPORTED;
           }
           d.heads = o.heads;

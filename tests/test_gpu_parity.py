@@ -45,6 +45,9 @@ def test_golden_vectors(name, frontend):
     bert_tiny(batch=1, seq=128, layers=1, hidden=192, ffn=768),    # full 128-row tile, 3 heads
     bert_tiny(batch=2, seq=128, layers=1, hidden=128, ffn=512),    # two 128-row tiles
     bert_tiny(batch=5, seq=33, layers=1, hidden=64, ffn=256),      # rows straddle tile boundaries
+    bert_tiny(batch=2, seq=200, layers=1, hidden=128, ffn=256),    # two key chunks, ragged second
+    bert_tiny(batch=1, seq=384, layers=2, hidden=128, ffn=256),    # three key chunks, three row tiles
+    bert_tiny(batch=3, seq=257, layers=1, hidden=64, ffn=256),     # third chunk holds a single key
 ], ids=lambda c: f"b{c.batch}s{c.seq}h{c.hidden}l{c.layers}")
 def test_shapes_against_oracle(cfg):
     w = make_weights(cfg, 21, stress=True)
@@ -113,6 +116,28 @@ def test_bert_base_relaunch_is_stable(base):
         mod.launch()
     b = run_module(mod, cfg, inp)
     assert np.abs(a - b).max() <= 4e-3
+
+
+def test_bert_large_shape_two_layers_batch16():
+    """BERT-large geometry (hidden 1024, 16 heads, FFN 4096, seq 384) at batch 16 = 6144 rows
+    (48 row tiles), last quarter of every sequence padded; two layers keep the oracle quick."""
+    cfg = EncoderConfig(layers=2, hidden=1024, heads=16, ffn=4096, batch=16, seq=384)
+    w = make_weights(cfg, 1235, stress=True)
+    inp = make_inputs(cfg, 1235, pad_fraction=0.25)
+    mod = build(cfg, w, "hlo")
+    got = run_module(mod, cfg, inp)
+    mod.close()
+    assert_parity(got, R.bert_encoder_torch(cfg, w, inp), "BERT-large geometry b16 s384")
+
+
+def test_bert_large_full_depth_batch1():
+    cfg = EncoderConfig(layers=24, hidden=1024, heads=16, ffn=4096, batch=1, seq=384)
+    w = make_weights(cfg, 1235)
+    inp = make_inputs(cfg, 1235, pad_fraction=0.25)
+    mod = build(cfg, w, "builder")
+    got = run_module(mod, cfg, inp)
+    mod.close()
+    assert_parity(got, R.bert_encoder_torch(cfg, w, inp), "BERT-large b1 s384")
 
 
 def test_layernorm_output_statistics(base):

@@ -109,6 +109,32 @@ def test_spec_controls_the_tiles_and_round_trips(lib_built, tmp_path):
     describe("encoder", cfg.to_json(), spec=ref_style)
 
 
+def test_tiles_wider_than_a_ring_slot_are_never_planned(lib_built):
+    # a 16-CTA grid once made the heuristic pick a 192-column tile (24 KB for a 16 KB slot)
+    cfg = bert_base()
+    spec = describe("encoder", cfg.to_json())["spec"]
+    spec["cuda_context"]["cuda_runtime_context"]["grid_dim"]["x"] = 16
+    spec["gemm_spec_list"] = {"layer0.ffn.up": {"sm100_config": {"mma_n": 192, "k_split": 1}}}
+    p = describe("encoder", cfg.to_json(), spec=spec)["plan"]
+    for st in p["stages"]:
+        for o in st["ops"]:
+            if o["kind"] == "gemm":
+                assert o["n_tile"] * o["kb_per_bslot"] * 128 <= 16384
+
+
+def test_long_sequences_and_large_batches_lower(lib_built):
+    from mononn_b200.models import EncoderConfig
+    cfg = EncoderConfig(layers=2, hidden=1024, heads=16, ffn=4096, batch=16, seq=384)
+    p = describe("encoder", cfg.to_json())["plan"]
+    att = [o for s in p["stages"] for o in s["ops"] if o["kind"] == "attention"][0]
+    assert att["n_items"] == 16 * 16 * 3
+    _live_ranges_do_not_overlap(p)
+    cfg.seq, cfg.max_pos = 512, 512
+    with pytest.raises(capi.MononnError) as e:
+        describe("encoder", cfg.to_json())
+    assert e.value.code == -3 and "384" in str(e.value)
+
+
 def test_allow_list_isolates_one_node(lib_built):
     cfg = bert_tiny(layers=1)
     spec = describe("encoder", cfg.to_json())["spec"]
