@@ -149,6 +149,29 @@ int eval_computation(const HloModule& m, const HloComputation& comp,
         if (row < 0 || row >= table.dims[0]) return unsupported(err, ins, "probe index out of range");
         std::copy(table.v.begin() + row * h, table.v.begin() + (row + 1) * h, r.v.begin() + t * h);
       }
+    } else if (op == "concatenate") {
+      const auto cd = ins.int_list("dimensions");
+      if (cd.size() != 1 || cd[0] < 0 || cd[0] >= static_cast<int64_t>(r.dims.size()))
+        return unsupported(err, ins, "bad concatenate dimension");
+      const int64_t d = cd[0];
+      const auto os = strides_of(r.dims);
+      r.v.resize(static_cast<size_t>(n));
+      int64_t offset = 0;
+      for (size_t k = 0; k < ins.operands.size(); ++k) {
+        const HTensor& a = A(static_cast<int>(k));
+        if (a.dims.size() != r.dims.size()) return unsupported(err, ins, "operand rank differs");
+        const auto as = strides_of(a.dims);
+        for (int64_t i = 0; i < a.size(); ++i) {
+          int64_t dst = 0;
+          for (size_t q = 0; q < a.dims.size(); ++q) {
+            const int64_t c = (i / as[q]) % a.dims[q];
+            dst += (static_cast<int64_t>(q) == d ? c + offset : c) * os[q];
+          }
+          r.v[dst] = a.v[i];
+        }
+        offset += a.dims[d];
+      }
+      if (offset != r.dims[d]) return unsupported(err, ins, "concatenated extent mismatch");
     } else if (op == "iota") {
       const auto d = ins.int_list("iota_dimension");
       if (d.size() != 1 || d[0] < 0 || d[0] >= static_cast<int64_t>(r.dims.size()))

@@ -66,7 +66,10 @@ float act_ref(float x, ActKind k) {
 }
 
 struct Val {
-  enum Kind { NONE, ARG, CONST, ACT, GEMM, HEADS, SCORES, PROBS, ATTN, MASK, EMBED_SUM } kind = NONE;
+  // STREAM: the f32 residual stream of a pre-LN model (an accumulator that GEMMs add into);
+  // IMAGE: NCHW f32 image argument seen through its NHWC/f16 layout fusion; CONVOUT: result
+  // tuple of a patch convolution (its element 0 is a pending GEMM)
+  enum Kind { NONE, ARG, CONST, ACT, GEMM, HEADS, SCORES, PROBS, ATTN, MASK, EMBED_SUM, STREAM, IMAGE, CONVOUT } kind = NONE;
   int tensor = -1;  // FGraph tensor (ARG, CONST-as-instr, ACT, HEADS, MASK)
   int op = -1;      // producing FGraph op (ACT, GEMM, HEADS, ATTN)
   int instr = -1;   // HLO instruction that defines the (unaliased) value
@@ -138,6 +141,16 @@ class Lowering {
         if (ins.shape.elements() != e_.instrs[ins.operands[0]].shape.elements())
           return unsupported(ins, "element count changes");
         vals_[idx] = s;  // same buffer, row-major in both shapes
+      } else if (ins.opcode == "get-tuple-element") {
+        if (ins.operands.size() != 1) return unsupported(ins, "expects one operand");
+        const Val& s = vals_[ins.operands[0]];
+        const auto gi = ins.int_list("index");
+        if (s.kind != Val::CONVOUT || gi.size() != 1 || gi[0] != 0)
+          return unsupported(ins, "get-tuple-element of anything but element 0 of a convolution result");
+        Val v = s;  // element 0 of the cuDNN result tuple is the output (ir_parser_fused.cc:803-823)
+        v.kind = Val::GEMM;
+        v.instr = static_cast<int>(idx);
+        vals_[idx] = v;
       } else if (ins.opcode == "tuple") {
         if (static_cast<int>(idx) != e_.root) return unsupported(ins, "tuple that is not the entry root");
       } else {
@@ -213,8 +226,9 @@ class Lowering {
   int lower_custom_call(int idx) {
     const HloInstr& ins = e_.instrs[idx];
     const std::string target = ins.attr("custom_call_target");
-    if (target != "__cublas$gemm")  // custom_call.cc:96-103 accepts this and __cudnn$convForward
-      return unsupported(ins, "custom-call target " + target + " (only __cublas$gemm is on this path)");
+    if (target == "__cudnn$convForward") return lower_conv(idx);  // custom_call.cc:96-103
+    if (target != "__cublas$gemm")
+      return unsupported(ins, "custom-call target " + target);
     if (ins.operands.size() != 2) return unsupported(ins, "GEMM with a C operand (beta != 0)");
     Json cfg;
     std::string je;
@@ -333,7 +347,14 @@ class Lowering {
       has_reduce = has_reduce || i.opcode == "reduce";
       has_gather = has_gather || i.opcode == "gather";
     }
+    bool has_concat = false;
+    for (const HloInstr& i : c->instrs) has_concat = has_concat || i.opcode == "concatenate";
     if (has_gather) return lower_embed_sum(idx, *c);
+    if (has_concat) {  // token assembly: the result has more rows than the patch GEMM
+      for (size_t k = 0; k < ins.operands.size(); ++k)
+        if (vals_[ins.operands[k]].kind == Val::GEMM) return lower_tokens(idx, *c, static_cast<int>(k));
+      return unsupported(ins, "concatenating fusion that does not follow a patch convolution");
+    }
     // the "main" operand: same element count as the result and not a constant
     int main_k = -1;
     for (size_t k = 0; k < ins.operands.size(); ++k) {
@@ -342,12 +363,16 @@ class Lowering {
       if (e_.instrs[ins.operands[k]].shape.elements() != ins.shape.elements()) continue;
       if (main_k < 0 || v.kind == Val::GEMM) main_k = static_cast<int>(k);
     }
+    if (main_k < 0 && ins.operands.size() == 1 && vals_[ins.operands[0]].kind == Val::ARG &&
+        e_.instrs[ins.operands[0]].shape.dims.size() == 4)
+      return lower_image_layout(idx, *c);
     if (main_k < 0) return unsupported(ins, "fusion without a tensor operand of the result's size");
     const Val& mv = vals_[ins.operands[main_k]];
     switch (mv.kind) {
       case Val::GEMM:
         return has_reduce ? lower_layernorm(idx, *c, main_k) : lower_epilogue(idx, *c, main_k);
       case Val::ACT:
+      case Val::STREAM:
       case Val::EMBED_SUM:
         if (has_reduce) return lower_layernorm(idx, *c, main_k);
         return unsupported(ins, "elementwise fusion that does not follow a GEMM");
@@ -356,6 +381,7 @@ class Lowering {
       case Val::ATTN:
         return lower_merge(idx, *c, main_k);
       case Val::ARG:
+        if (e_.instrs[ins.operands[main_k]].shape.dims.size() == 4) return lower_image_layout(idx, *c);
         return lower_mask(idx, *c, main_k);
       default:
         return unsupported(ins, "fusion over this kind of value");
@@ -375,7 +401,8 @@ class Lowering {
       const Val& v = vals_[ins.operands[k]];
       const HloInstr& oi = e_.instrs[ins.operands[k]];
       if (v.kind == Val::CONST && oi.shape.elements() == N && bias_k < 0) bias_k = static_cast<int>(k);
-      else if (v.kind == Val::ACT && v.rows == M && v.cols == N && resid_k < 0) resid_k = static_cast<int>(k);
+      else if ((v.kind == Val::ACT || v.kind == Val::STREAM) && v.rows == M && v.cols == N && resid_k < 0)
+        resid_k = static_cast<int>(k);
       else return unsupported(ins, "operand %" + oi.name + " has no role in a GEMM epilogue");
     }
     // result layout: [M,N] row-major, or [B,heads,S,D] with B*S = M and heads*D = N
@@ -423,6 +450,18 @@ class Lowering {
     }
     if (!ok) return unsupported(ins, "fused computation " + c.name + " matches no epilogue form act(x + bias) + residual");
     if (bias_k >= 0) gop.bias = const_tensor(vals_[ins.operands[bias_k]].instr, 1, N);
+    if (resid_k >= 0 && vals_[ins.operands[resid_k]].kind == Val::STREAM) {
+      // pre-LN residual: x <- x + (A W + b). The stream is an f32 accumulator the GEMM adds
+      // its (split-K) partial sums into; nothing is copied.
+      if (found != ACT_NONE || split) return unsupported(ins, "activation or head split on a residual update");
+      gop.act = ACT_NONE;
+      gop.out = vals_[ins.operands[resid_k]].tensor;
+      Val sv = vals_[ins.operands[resid_k]];
+      sv.instr = idx;
+      sv.op = gv.op;
+      vals_[idx] = sv;
+      return MONONN_OK;
+    }
     if (resid_k >= 0) gop.resid = vals_[ins.operands[resid_k]].tensor;
     gop.act = found;
     gop.out = act_tensor(canonical_node_name(ins.name), M, N);
@@ -460,6 +499,9 @@ class Lowering {
       if (v.kind == Val::CONST && oi.shape.elements() == cols) vec_k.push_back(static_cast<int>(k));
       else if (v.kind == Val::ACT && v.rows == rows && v.cols == cols && resid_k < 0) resid_k = static_cast<int>(k);
       else return unsupported(ins, "operand %" + oi.name + " has no role in a LayerNorm fusion");
+    }
+    if (mv.kind == Val::STREAM && (mv.rows != rows || mv.cols != cols)) {
+      return unsupported(ins, "LayerNorm shape differs from the residual stream");
     }
     if (vec_k.size() < 2 || vec_k.size() > 3) return unsupported(ins, "expected scale, shift and at most one bias vector");
     std::vector<float> eps_cands;
@@ -558,7 +600,7 @@ class Lowering {
       n.alpha = -10000.f;
     } else {
       if (bias_k >= 0) return unsupported(ins, "bias vector on a LayerNorm that does not follow a GEMM");
-      n.src = mv.tensor;
+      n.src = mv.tensor;  // f16 activation, or the f32 residual stream (read, not cleared)
       if (resid_k >= 0) n.resid = vals_[ins.operands[resid_k]].tensor;
     }
     n.out = act_tensor(n.name, rows, cols);
@@ -657,6 +699,198 @@ class Lowering {
     v.op = av.op;
     v.rows = B * S;
     v.cols = H * D;
+    vals_[idx] = v;
+    return MONONN_OK;
+  }
+
+  // NCHW f32 image argument -> NHWC f16 (the layout XLA gives cuDNN)
+  int lower_image_layout(int idx, const HloComputation& c) {
+    const HloInstr& ins = e_.instrs[idx];
+    const HloInstr& src = e_.instrs[ins.operands[0]];
+    const auto& sd = src.shape.dims;
+    if (src.shape.dtype != "f32" || sd.size() != 4 || ins.shape.dims.size() != 4)
+      return unsupported(ins, "image layout fusion must map f32 [B,C,H,W] to [B,H,W,C]");
+    const int64_t B = sd[0], C = sd[1], H = sd[2], W = sd[3];
+    if (ins.shape.dims != std::vector<int64_t>{B, H, W, C}) return unsupported(ins, "result is not [B,H,W,C]");
+    Rng rng;
+    std::vector<HTensor> ps = probe_inputs(c, [&](size_t, HTensor& t) {
+      for (float& x : t.v) x = rng.uni(-1.f, 1.f);
+    });
+    HTensor got;
+    int rc = probe(c, ps, &got);
+    if (rc) return rc;
+    std::vector<float> want(got.v.size());
+    for (int64_t b = 0; b < B; ++b)
+      for (int64_t ch = 0; ch < C; ++ch)
+        for (int64_t y = 0; y < H; ++y)
+          for (int64_t x = 0; x < W; ++x)
+            want[((b * H + y) * W + x) * C + ch] = ps[0].v[((b * C + ch) * H + y) * W + x];
+    if (!all_close(got.v, want, 0.f, 0.f))
+      return unsupported(ins, "fused computation " + c.name + " is not the NCHW -> NHWC layout change");
+    Val v;
+    v.kind = Val::IMAGE;
+    v.instr = idx;
+    v.tensor = vals_[ins.operands[0]].tensor;
+    v.B = static_cast<uint32_t>(B);
+    v.heads = static_cast<uint32_t>(C);
+    v.S = static_cast<uint32_t>(H);
+    v.D = static_cast<uint32_t>(W);
+    vals_[idx] = v;
+    return MONONN_OK;
+  }
+
+  // __cudnn$convForward whose stride equals its window and that has no padding: every output
+  // position sees its own patch, so the convolution is a GEMM over patch rows
+  // (NHWC input, KRSC filter, cross-correlation: ir_parser_fused.cc:749-800).
+  int lower_conv(int idx) {
+    const HloInstr& ins = e_.instrs[idx];
+    if (ins.operands.size() != 2) return unsupported(ins, "convolution with a side input");
+    const Val& img = vals_[ins.operands[0]];
+    const Val& wv = vals_[ins.operands[1]];
+    if (img.kind != Val::IMAGE || wv.kind != Val::CONST)
+      return unsupported(ins, "convolution operands must be the image and a constant filter");
+    if (ins.attr("dim_labels") != "b01f_o01i->b01f") return unsupported(ins, "dim_labels other than b01f_o01i->b01f");
+    const std::string win = ins.attr("window");
+    auto pair_after = [&](const std::string& key, int64_t* a, int64_t* b) {
+      const size_t p = win.find(key + "=");
+      if (p == std::string::npos) return false;
+      char* e = nullptr;
+      *a = std::strtoll(win.c_str() + p + key.size() + 1, &e, 10);
+      if (!e || *e != 'x') return false;
+      *b = std::strtoll(e + 1, nullptr, 10);
+      return true;
+    };
+    int64_t kh = 0, kw = 0, sh = 1, sw = 1;
+    if (!pair_after("size", &kh, &kw)) return unsupported(ins, "window without a size");
+    pair_after("stride", &sh, &sw);
+    if (win.find("pad") != std::string::npos || win.find("dilation") != std::string::npos)
+      return unsupported(ins, "padded or dilated convolution");
+    if (sh != kh || sw != kw) return unsupported(ins, "convolution whose stride differs from its window");
+    const HloInstr& wi = e_.instrs[ins.operands[1]];
+    if (!ins.shape.is_tuple() || ins.shape.elems.empty() || ins.shape.elems[0].dims.size() != 4 ||
+        wi.shape.dims.size() != 4)
+      return unsupported(ins, "convolution result must be a tuple whose element 0 is [B,P,Q,K]");
+    const auto& od = ins.shape.elems[0].dims;
+    const uint32_t O = static_cast<uint32_t>(wi.shape.dims[0]);
+    if (wi.shape.dims[1] != kh || wi.shape.dims[2] != kw || wi.shape.dims[3] != img.heads ||
+        od[0] != img.B || od[1] * kh != img.S || od[2] * kw != img.D || od[3] != O)
+      return unsupported(ins, "convolution shapes are inconsistent");
+    const uint32_t gh = static_cast<uint32_t>(od[1]), gw = static_cast<uint32_t>(od[2]);
+    const uint32_t M = img.B * gh * gw, K = static_cast<uint32_t>(kh * kw) * img.heads;
+    FOp pt;
+    pt.kind = OP_PATCHIFY;
+    pt.name = canonical_node_name(ins.name) + "_patches";
+    pt.src = img.tensor;
+    pt.out = act_tensor(pt.name, M, K);
+    pt.rows = M;
+    pt.cols = K;
+    pt.heads = img.heads;
+    pt.seq = img.S;
+    pt.batches = img.D;
+    pt.head_dim = static_cast<uint32_t>(kh);
+    pt.q_col = static_cast<uint32_t>(kw);
+    pt.k_col = gw;
+    pt.vocab = gh * gw;
+    g_.ops.push_back(pt);
+    FOp o;
+    o.kind = OP_GEMM;
+    o.name = canonical_node_name(ins.name);
+    o.a = pt.out;
+    o.w = const_tensor(wv.instr, K, O, /*transposed=*/true);  // filter [O, kh*kw*C] is [N, K]
+    o.M = M;
+    o.N = O;
+    o.K = K;
+    g_.ops.push_back(o);
+    Val v;
+    v.kind = Val::CONVOUT;
+    v.op = static_cast<int>(g_.ops.size()) - 1;
+    v.instr = idx;
+    v.rows = M;
+    v.cols = O;
+    v.B = img.B;
+    vals_[idx] = v;
+    return MONONN_OK;
+  }
+
+  // tokens = concat(class rows, patches + bias) + positions  -> the f32 residual stream
+  int lower_tokens(int idx, const HloComputation& c, int main_k) {
+    const HloInstr& ins = e_.instrs[idx];
+    const Val gv = vals_[ins.operands[main_k]];
+    if (uses_[gv.instr] != 1) return unsupported(ins, "patch embedding with more than one consumer");
+    FOp& gop = g_.ops[gv.op];
+    const uint32_t M = gop.M, O = gop.N, B = gv.B;
+    if (ins.shape.dims.size() != 2 || ins.shape.dims[1] != O || B == 0 || ins.shape.dims[0] % B)
+      return unsupported(ins, "token tensor must be [B*tokens, width]");
+    const uint32_t T = static_cast<uint32_t>(ins.shape.dims[0]), S = T / B, P = M / B;
+    if (S <= P) return unsupported(ins, "no prefix rows in a concatenating fusion");
+    const uint32_t prefix = S - P;
+    std::vector<int> small;  // operands of O or prefix*O elements: bias and prefix rows
+    int pos_k = -1;
+    for (size_t k = 0; k < ins.operands.size(); ++k) {
+      if (static_cast<int>(k) == main_k) continue;
+      const HloInstr& oi = e_.instrs[ins.operands[k]];
+      if (vals_[ins.operands[k]].kind != Val::CONST) return unsupported(ins, "operand %" + oi.name + " must be a constant");
+      if (oi.shape.elements() == static_cast<int64_t>(S) * O && pos_k < 0) pos_k = static_cast<int>(k);
+      else small.push_back(static_cast<int>(k));
+    }
+    if (pos_k < 0 || small.size() != 2) return unsupported(ins, "expected bias, prefix rows and position rows");
+    Rng rng;
+    std::vector<HTensor> ps = probe_inputs(c, [&](size_t, HTensor& t) {
+      for (float& x : t.v) x = rng.uni(-1.f, 1.f);
+    });
+    HTensor got;
+    int rc = probe(c, ps, &got);
+    if (rc) return rc;
+    int bias_k = -1, cls_k = -1;
+    for (int trial = 0; trial < 2 && bias_k < 0; ++trial) {
+      const int bk = small[trial], ck = small[1 - trial];
+      if (e_.instrs[ins.operands[bk]].shape.elements() != O ||
+          e_.instrs[ins.operands[ck]].shape.elements() != static_cast<int64_t>(prefix) * O)
+        continue;
+      std::vector<float> want(static_cast<size_t>(T) * O);
+      for (uint32_t b = 0; b < B; ++b)
+        for (uint32_t t = 0; t < S; ++t)
+          for (uint32_t j = 0; j < O; ++j) {
+            float y = ps[pos_k].v[static_cast<size_t>(t) * O + j];
+            if (t < prefix) y += ps[ck].v[static_cast<size_t>(t) * O + j];
+            else y += ps[main_k].v[(static_cast<size_t>(b) * P + (t - prefix)) * O + j] + ps[bk].v[j];
+            want[(static_cast<size_t>(b) * S + t) * O + j] = y;
+          }
+      if (all_close(got.v, want, 1e-5f, 1e-5f)) {
+        bias_k = bk;
+        cls_k = ck;
+      }
+    }
+    if (bias_k < 0)
+      return unsupported(ins, "fused computation " + c.name + " is not concat(prefix, patches + bias) + positions");
+    gop.out = act_tensor(gop.name + "_out", M, O);
+    FTensor st;
+    st.name = canonical_node_name(ins.name);
+    st.kind = TKind::AccF32;
+    st.rows = T;
+    st.cols = O;
+    st.ld = O;
+    st.elem_bytes = 4;
+    FOp a;
+    a.kind = OP_ASSEMBLE;
+    a.name = canonical_node_name(ins.name);
+    a.a = gop.out;
+    a.bias = const_tensor(vals_[ins.operands[bias_k]].instr, 1, O);
+    a.word = const_tensor(vals_[ins.operands[cls_k]].instr, prefix, O);
+    a.pos = const_tensor(vals_[ins.operands[pos_k]].instr, S, O);
+    a.out2 = g_.add_tensor(st);
+    a.rows = T;
+    a.cols = O;
+    a.seq = S;
+    a.k_col = prefix;
+    g_.ops.push_back(a);
+    Val v;
+    v.kind = Val::STREAM;
+    v.instr = idx;
+    v.tensor = a.out2;
+    v.op = static_cast<int>(g_.ops.size()) - 1;
+    v.rows = T;
+    v.cols = O;
     vals_[idx] = v;
     return MONONN_OK;
   }

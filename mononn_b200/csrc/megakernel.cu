@@ -775,17 +775,21 @@ __device__ __forceinline__ float4 row_chunk(const RowSrc& s, uint32_t vi) {
 }
 __device__ __forceinline__ void row_emit(float4 a, float mean, float rstd, uint32_t vi,
                                          uint2 gv, uint2 bv, uint2 b2v, uint2* out, float4* out2,
-                                         bool add_bias2) {
+                                         bool add_bias2, bool no_norm) {
   const float4 g = h4_to_f4(gv), b = h4_to_f4(bv);
-  float4 y;
-  y.x = (a.x - mean) * rstd * g.x + b.x;
-  y.y = (a.y - mean) * rstd * g.y + b.y;
-  y.z = (a.z - mean) * rstd * g.z + b.z;
-  y.w = (a.w - mean) * rstd * g.w + b.w;
-  uint2 o;
-  o.x = pack_h2(y.x, y.y);
-  o.y = pack_h2(y.z, y.w);
-  out[vi] = o;
+  float4 y = a;
+  if (!no_norm) {
+    y.x = (a.x - mean) * rstd * g.x + b.x;
+    y.y = (a.y - mean) * rstd * g.y + b.y;
+    y.z = (a.z - mean) * rstd * g.z + b.z;
+    y.w = (a.w - mean) * rstd * g.w + b.w;
+  }
+  if (out != nullptr) {
+    uint2 o;
+    o.x = pack_h2(y.x, y.y);
+    o.y = pack_h2(y.z, y.w);
+    out[vi] = o;
+  }
   if (out2 != nullptr) {
     if (add_bias2) add4(y, h4_to_f4(b2v));
     out2[vi] = y;
@@ -801,14 +805,30 @@ __device__ __noinline__ void rowwise_item(const OpDesc& op, uint32_t local, uint
   const bool mark = (warp_in_group == 0 && lane == 0);
   if (mark) trace(P, stage, TR_MARK0);
   const uint32_t cols = op.cols, nvec = cols >> 2, flags = op.flags;
-  const bool embed = (op.kind == OP_EMBED);
+  const bool embed = (op.kind == OP_EMBED), assemble = (op.kind == OP_ASSEMBLE);
+  const bool no_norm = (flags & F_NO_NORM) != 0u;
   RowSrc s{nullptr, nullptr, nullptr, nullptr, false};
-  if (embed) {
+  if (assemble) {
+    // token row t of batch b: the first k_col rows come from a constant table (class token),
+    // the others from the patch GEMM's output plus its bias; every row adds its position row
+    const uint32_t t = row % op.seq, b = row / op.seq, prefix = op.k_col;
+    if (t < prefix) {
+      s.h0 = reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(op.p[3]) +
+                                            static_cast<size_t>(t) * cols);
+    } else {
+      s.h0 = reinterpret_cast<const uint2*>(
+          reinterpret_cast<const __half*>(op.p[1]) +
+          (static_cast<size_t>(b) * (op.seq - prefix) + (t - prefix)) * op.lds);
+      if (flags & F_BIAS) s.h2 = reinterpret_cast<const uint2*>(op.p[5]);
+    }
+    s.h1 = reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(op.p[4]) +
+                                          static_cast<size_t>(t) * cols);
+  } else if (embed) {
     const int32_t id = reinterpret_cast<const int32_t*>(op.p[1])[row];
     s.h0 = reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(op.p[3]) +
                                           static_cast<int64_t>(id) * cols);
     s.h1 = reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(op.p[4]) +
-                                          static_cast<size_t>(row % op.seq) * cols);
+                                          static_cast<size_t>(row % op.seq + op.q_col) * cols);
     if (flags & F_TYPE_IDS) {
       const int32_t ty = reinterpret_cast<const int32_t*>(op.p[2])[row];
       s.h2 = reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(op.p[5]) +
@@ -831,10 +851,13 @@ __device__ __noinline__ void rowwise_item(const OpDesc& op, uint32_t local, uint
       s.h1 = reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(op.p[4]) +
                                             static_cast<size_t>(row) * op.ldr);
   }
-  const uint2* gamma = reinterpret_cast<const uint2*>(embed ? op.p[6] : op.p[2]);
-  const uint2* beta = reinterpret_cast<const uint2*>(embed ? op.p[7] : op.p[3]);
-  uint2* out = reinterpret_cast<uint2*>(reinterpret_cast<__half*>(op.p[0]) +
-                                        static_cast<size_t>(row) * op.ldo);
+  // (row ops without normalisation still get valid scale/shift pointers from the host, so
+  // that the loads below stay unconditional)
+  const uint2* gamma = reinterpret_cast<const uint2*>((embed || assemble) ? op.p[6] : op.p[2]);
+  const uint2* beta = reinterpret_cast<const uint2*>((embed || assemble) ? op.p[7] : op.p[3]);
+  uint2* out = op.p[0] ? reinterpret_cast<uint2*>(reinterpret_cast<__half*>(op.p[0]) +
+                                                  static_cast<size_t>(row) * op.ldo)
+                       : nullptr;
   float4* out2 = op.q[2] ? reinterpret_cast<float4*>(reinterpret_cast<float*>(op.q[2]) +
                                                      static_cast<size_t>(row) * cols)
                          : nullptr;
@@ -913,7 +936,7 @@ __device__ __noinline__ void rowwise_item(const OpDesc& op, uint32_t local, uint
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const uint32_t vi = i * 32u + lane;
-      if (vi < nvec) row_emit(x[i], mean, rstd, vi, gv[i], bv[i], b2v[i], out, out2, add_bias2);
+      if (vi < nvec) row_emit(x[i], mean, rstd, vi, gv[i], bv[i], b2v[i], out, out2, add_bias2, no_norm);
     }
   } else {
     // wide rows: three passes over the (L2-resident) sources
@@ -937,10 +960,32 @@ __device__ __noinline__ void rowwise_item(const OpDesc& op, uint32_t local, uint
       const float4 a = row_chunk(s, vi);
       if (s.zero) const_cast<float4*>(s.f32)[vi] = make_float4(0.f, 0.f, 0.f, 0.f);
       row_emit(a, mean, rstd, vi, __ldg(gamma + vi), __ldg(beta + vi),
-               add_bias2 ? __ldg(bias2 + vi) : make_uint2(0u, 0u), out, out2, add_bias2);
+               add_bias2 ? __ldg(bias2 + vi) : make_uint2(0u, 0u), out, out2, add_bias2, no_norm);
     }
   }
   if (mark) trace(P, stage, TR_MARK0 + 2);
+}
+
+// Patch extraction for a convolution whose stride equals its window (ViT / CLIP patch
+// embedding): row (b, py, px) of the f16 output holds the window's pixels in (ky, kx, c)
+// order, read from the NCHW f32 image. With that operand the convolution is a plain GEMM
+// against the [out_channels, ky*kx*c] filter. The reference runs these through CUTLASS
+// implicit-GEMM fprop (mononn_engine/core/op_impl/conv_impl.cc:36-106).
+__device__ __noinline__ void patchify_item(const OpDesc& op, uint32_t local, uint32_t warp_in_group,
+                                           uint32_t lane) {
+  const uint32_t row = local * 4u + warp_in_group;
+  if (row >= op.rows) return;
+  const uint32_t C = op.heads, Himg = op.seq, Wimg = op.batches, kh = op.head_dim, kw = op.q_col;
+  const uint32_t gw = op.k_col, per_img = op.vocab;  // patches per image row / per image
+  const uint32_t b = row / per_img, pr = row % per_img, py = pr / gw, px = pr % gw;
+  const float* src = reinterpret_cast<const float*>(op.p[1]);
+  __half* dst = reinterpret_cast<__half*>(op.p[0]) + static_cast<size_t>(row) * op.ldo;
+#pragma unroll 4
+  for (uint32_t j = lane; j < op.cols; j += 32u) {
+    const uint32_t c = j % C, kx = (j / C) % kw, ky = j / (C * kw);
+    dst[j] = __float2half_rn(
+        src[((static_cast<size_t>(b) * C + c) * Himg + py * kh + ky) * Wimg + px * kw + kx]);
+  }
 }
 
 // Softmax + output of one attention tile; thread `row` owns query row `row`.
@@ -1117,7 +1162,11 @@ __device__ void role_simt(Ctx c, uint32_t tmem_base, uint32_t tid_in_group) {
           break;
         case OP_LAYERNORM:
         case OP_EMBED:
+        case OP_ASSEMBLE:
           rowwise_item(op, it.local, quarter, lane, P, s);
+          break;
+        case OP_PATCHIFY:
+          patchify_item(op, it.local, quarter, lane);
           break;
         default:
           break;

@@ -185,9 +185,18 @@ int validate_plan(const Plan& P, std::string* err) {
         break;
       case OP_LAYERNORM:
       case OP_EMBED:
+      case OP_ASSEMBLE:
         if (d.cols == 0 || d.cols % 4 || d.cols > 2048) return bad(n + "row length");
         if (d.n_items != (d.rows + 3) / 4) return bad(n + "item count");
-        if (op.p[0].space == SPACE_NONE) return bad(n + "no output buffer");
+        if (op.p[0].space == SPACE_NONE && op.q[2].space == SPACE_NONE) return bad(n + "no output buffer");
+        if (op.p[6].space == SPACE_NONE && d.kind != OP_LAYERNORM) return bad(n + "no scale pointer");
+        if (d.kind == OP_ASSEMBLE && (d.seq == 0 || d.k_col >= d.seq)) return bad(n + "token geometry");
+        break;
+      case OP_PATCHIFY:
+        if (d.cols != d.heads * d.head_dim * d.q_col || d.vocab == 0 || d.k_col == 0)
+          return bad(n + "patch geometry");
+        if (d.n_items != (d.rows + 3) / 4) return bad(n + "item count");
+        if (op.p[0].space == SPACE_NONE || op.p[1].space == SPACE_NONE) return bad(n + "buffers");
         break;
       default:
         return bad(n + "unknown operator kind");
@@ -269,17 +278,22 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
   }
 
   // ---- stage = dependency depth
-  std::vector<int> producer(n_t, -1);
+  std::vector<int> producer(n_t, -1), last_reader(n_t, -1);
   int n_stages = 0;
   for (size_t i = 0; i < ops.size(); ++i) {
     int depth = 0;
     for (int t : inputs_of(ops[i]))
       if (producer[t] >= 0) depth = std::max(depth, ops[producer[t]].stage + 1);
+    // an op that adds into a live tensor (the f32 residual stream of pre-LN models) also
+    // runs after every earlier reader of the old value
+    for (int t : outputs_of(ops[i]))
+      if (producer[t] >= 0) depth = std::max(depth, last_reader[t] + 1);
     // an op that accumulates into a tensor someone pre-loaded runs after that producer
     for (int t : outputs_of(ops[i]))
       if (producer[t] >= 0) depth = std::max(depth, ops[producer[t]].stage + 1);
     ops[i].stage = depth;
     n_stages = std::max(n_stages, depth + 1);
+    for (int t : inputs_of(ops[i])) last_reader[t] = std::max(last_reader[t], depth);
     for (int t : outputs_of(ops[i])) producer[t] = static_cast<int>(i);
   }
 
@@ -598,6 +612,50 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
           }
           break;
         }
+        case OP_PATCHIFY: {
+          d.rows = o.rows;
+          d.cols = o.cols;
+          d.heads = o.heads;
+          d.seq = o.seq;
+          d.batches = o.batches;
+          d.head_dim = o.head_dim;
+          d.q_col = o.q_col;
+          d.k_col = o.k_col;
+          d.vocab = o.vocab;
+          d.n_items = (o.rows + 3) / 4;
+          po.p[0] = where[o.out];
+          d.ldo = g.tensors[o.out].ld;
+          po.p[1] = where[o.src];
+          break;
+        }
+        case OP_ASSEMBLE: {
+          d.rows = o.rows;
+          d.cols = o.cols;
+          d.seq = o.seq;
+          d.k_col = o.k_col;
+          if (o.cols % 4 != 0 || o.cols > 2048) {
+            if (err) *err = "assemble " + o.name + ": row length must be <= 2048 and a multiple of 4";
+            return MONONN_ERR_UNSUPPORTED;
+          }
+          d.n_items = (o.rows + 3) / 4;
+          d.flags |= F_NO_NORM;
+          if (o.out >= 0) {
+            po.p[0] = where[o.out];
+            d.ldo = g.tensors[o.out].ld;
+          }
+          po.p[1] = where[o.a];
+          d.lds = g.tensors[o.a].ld;
+          po.p[3] = raw_const(o.word);
+          po.p[4] = raw_const(o.pos);
+          if (o.bias >= 0) {
+            po.p[5] = raw_const(o.bias);
+            d.flags |= F_BIAS;
+          }
+          po.p[6] = po.p[4];
+          po.p[7] = po.p[4];
+          if (o.out2 >= 0) po.q[2] = where[o.out2];
+          break;
+        }
         case OP_EMBED: {
           d.rows = o.rows;
           d.cols = o.cols;
@@ -608,8 +666,11 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
             return MONONN_ERR_UNSUPPORTED;
           }
           d.n_items = (o.rows + 3) / 4;
-          po.p[0] = where[o.out];
-          d.ldo = g.tensors[o.out].ld;
+          d.q_col = o.q_col;  // offset of the position index
+          if (o.out >= 0) {
+            po.p[0] = where[o.out];
+            d.ldo = g.tensors[o.out].ld;
+          }
           po.p[1] = where[o.ids];
           po.p[3] = raw_const(o.word);
           po.p[4] = raw_const(o.pos);
@@ -618,8 +679,14 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
             po.p[5] = raw_const(o.type);
             d.flags |= F_TYPE_IDS;
           }
-          po.p[6] = raw_const(o.gamma);
-          po.p[7] = raw_const(o.beta);
+          if (o.gamma >= 0 && o.beta >= 0) {
+            po.p[6] = raw_const(o.gamma);
+            po.p[7] = raw_const(o.beta);
+          } else {  // no embedding LayerNorm: the row sum is the result
+            d.flags |= F_NO_NORM;
+            po.p[6] = po.p[4];
+            po.p[7] = po.p[4];
+          }
           if (o.mask_in >= 0 && o.mask_out >= 0) {
             po.q[0] = where[o.mask_in];
             po.q[1] = where[o.mask_out];

@@ -121,6 +121,8 @@ static const char* kind_name(uint32_t k) {
     case OP_ATTENTION: return "attention";
     case OP_LAYERNORM: return "layernorm";
     case OP_EMBED: return "embed";
+    case OP_ASSEMBLE: return "assemble";
+    case OP_PATCHIFY: return "patchify";
     default: return "none";
   }
 }

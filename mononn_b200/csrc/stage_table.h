@@ -18,6 +18,8 @@ enum OpKind : uint32_t {
   OP_LAYERNORM = 3,  // row-wise LayerNorm over an f32 or f16 source
   OP_EMBED = 4,      // row gather + position + type + LayerNorm, mask bias
   OP_L2NORM_LOGITS = 5,
+  OP_ASSEMBLE = 6,   // token rows = [constant prefix rows | GEMM rows + bias] + position rows -> f32
+  OP_PATCHIFY = 7,   // NCHW f32 image -> f16 patch rows (operand of the patch-embedding GEMM)
 };
 
 enum ActKind : uint32_t {
@@ -45,6 +47,7 @@ enum OpFlags : uint32_t {
   F_TYPE_IDS = 1u << 6,    // embed: token-type table present
   F_OUT2_F16 = 1u << 7,    // LayerNorm: also write the un-normalised sum as f16
   F_RESID_F32 = 1u << 8,   // residual source is f32
+  F_NO_NORM = 1u << 9,     // row op: no LayerNorm, the row sum is the result
 };
 
 // Pointer slots p[0..7]; meaning per kind:
@@ -53,6 +56,11 @@ enum OpFlags : uint32_t {
 //  LAYERNORM: 0 out(f16), 1 src, 2 gamma(f16), 3 beta(f16), 4 resid(f16, optional), 5 out2
 //  EMBED:     0 out(f16), 1 ids(i32), 2 type ids(i32), 3 word table(f16), 4 pos table(f16),
 //             5 type table(f16), 6 gamma, 7 beta ; mask(i32) -> q[0], mask bias out(f32) -> q[1]
+//  ASSEMBLE:  0 out(f16, optional), 1 GEMM rows(f16), 3 prefix rows(f16), 4 position rows(f16),
+//             5 bias(f16), 6/7 valid dummies; seq = tokens per batch, k_col = prefix rows
+//  PATCHIFY:  0 out(f16 [rows, cols]), 1 image(f32 NCHW); heads = C, seq = H, batches = W,
+//             head_dim = kh, q_col = kw, k_col = patches per image row, vocab = patches per image
+//  EMBED: q_col = offset added to the position index
 //  LAYERNORM and EMBED may also write q[2] = f32 copy of the result plus the f16 bias q[3]
 //  (residual + bias pre-loaded into the accumulator of the next split-K GEMM)
 struct alignas(16) OpDesc {

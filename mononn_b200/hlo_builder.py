@@ -302,3 +302,166 @@ def bert_hlo(cfg: EncoderConfig) -> tuple[str, dict[str, str]]:
             + f"\nENTRY %{cfg.name}_main (input_ids: {i_BS}, attention_mask: {i_BS}, token_type_ids: {i_BS}) "
               f"-> {out_shape} {{\n" + "\n".join(entry) + "\n}\n")
     return text, names
+
+
+def vit_hlo(cfg: EncoderConfig) -> tuple[str, dict[str, str]]:
+    """HLO text of the pre-LN vision encoder (ViT) of `cfg`: NCHW f32 pixels, patch embedding as
+    a ``__cudnn$convForward`` custom-call on the NHWC f16 image (window = stride = patch;
+    mononn_engine/parser/ir_parser_fused.cc:749-823), class token + learned positions, pre-LN
+    blocks, final LayerNorm (model of examples/utils/save_model.py:76-82)."""
+    B, S, H, F, NH = cfg.batch, cfg.seq, cfg.hidden, cfg.ffn, cfg.heads
+    D, T, C, IMG, PS = H // NH, cfg.batch * cfg.seq, cfg.channels, cfg.image, cfg.patch
+    G = IMG // PS
+    P = G * G
+    assert S == P + 1
+    comps: list[str] = [_REGIONS]
+    entry: list[str] = []
+    names: dict[str, str] = {}
+
+    def const(name: str, dims) -> str:
+        names[name] = name
+        entry.append(f"  %{name} = {_shape('f16', dims)} constant({{...}})")
+        return name
+
+    h_TH, h_H, f_TH = _shape("f16", [T, H]), _shape("f16", [H]), _shape("f32", [T, H])
+    px_s, nhwc_s = _shape("f32", [B, C, IMG, IMG]), _shape("f16", [B, IMG, IMG, C])
+    entry.append(f"  %pixel_values = {px_s} parameter(0)")
+    comps.append(f"""%fused_nhwc (p0: {px_s}) -> {nhwc_s} {{
+  %x = {px_s} parameter(0)
+  %t = {_shape('f32', [B, IMG, IMG, C])} transpose({px_s} %x), dimensions={{0,2,3,1}}
+  ROOT %c = {nhwc_s} convert({_shape('f32', [B, IMG, IMG, C])} %t)
+}}
+""")
+    entry.append(f"  %fusion.nhwc = {nhwc_s} fusion({px_s} %pixel_values), kind=kLoop, calls=%fused_nhwc")
+    wp = const("embeddings.patch.w", [H, PS, PS, C])
+    bp = const("embeddings.patch.b", [H])
+    cls = const("embeddings.cls", [1, H])
+    pos = const("embeddings.position", [S, H])
+    conv_s = _shape("f16", [B, G, G, H])
+    conv_cfg = json.dumps(json.dumps({"conv_result_scale": 1, "side_input_scale": 0, "activation_mode": "0",
+                                      "tensor_ops_enabled": True}, separators=(",", ":")))
+    entry.append(f"  %conv.patch = ({conv_s}, u8[0]{{0}}) custom-call({nhwc_s} %fusion.nhwc, "
+                 f"{_shape('f16', [H, PS, PS, C])} %{wp}), window={{size={PS}x{PS} stride={PS}x{PS}}}, "
+                 f"dim_labels=b01f_o01i->b01f, custom_call_target=\"__cudnn$convForward\", backend_config={conv_cfg}")
+    entry.append(f"  %gte.patch = {conv_s} get-tuple-element(({conv_s}, u8[0]{{0}}) %conv.patch), index=0")
+    h_BPH, h_BSH, h_B1H, h_SH = (_shape("f16", [B, P, H]), _shape("f16", [B, S, H]), _shape("f16", [B, 1, H]),
+                                 _shape("f16", [S, H]))
+    comps.append(f"""%fused_tokens (p0: {conv_s}, p1: {h_H}, p2: {_shape('f16', [1, H])}, p3: {h_SH}) -> {h_TH} {{
+  %y = {conv_s} parameter(0)
+  %b = {h_H} parameter(1)
+  %cls = {_shape('f16', [1, H])} parameter(2)
+  %pos = {h_SH} parameter(3)
+  %yr = {h_BPH} reshape({conv_s} %y)
+  %bb = {h_BPH} broadcast({h_H} %b), dimensions={{2}}
+  %yb = {h_BPH} add({h_BPH} %yr, {h_BPH} %bb)
+  %cls_b = {h_B1H} broadcast({_shape('f16', [1, H])} %cls), dimensions={{1,2}}
+  %cat = {h_BSH} concatenate({h_B1H} %cls_b, {h_BPH} %yb), dimensions={{1}}
+  %pos_b = {h_BSH} broadcast({h_SH} %pos), dimensions={{1,2}}
+  %tok = {h_BSH} add({h_BSH} %cat, {h_BSH} %pos_b)
+  ROOT %r = {h_TH} reshape({h_BSH} %tok)
+}}
+""")
+    entry.append(f"  %fusion.tokens = {h_TH} fusion({conv_s} %gte.patch, {h_H} %{bp}, {_shape('f16', [1, H])} %{cls}, "
+                 f"{h_SH} %{pos}), kind=kLoop, calls=%fused_tokens")
+
+    comps.append(f"%fused_ln (p0: {h_TH}, p1: {h_H}, p2: {h_H}) -> {h_TH} {{\n"
+                 f"  %x = {h_TH} parameter(0)\n  %gamma = {h_H} parameter(1)\n  %beta = {h_H} parameter(2)\n"
+                 f"  %x32 = {f_TH} convert({h_TH} %x)\n" + "\n".join(_ln_body(T, H, cfg.eps, "x32")) + "\n}\n")
+    h_heads, h_BShd = _shape("f16", [B, NH, S, D]), _shape("f16", [B, S, NH, D])
+    comps.append(f"""%fused_bias_split (p0: {h_TH}, p1: {h_H}) -> {h_heads} {{
+  %x = {h_TH} parameter(0)
+  %b = {h_H} parameter(1)
+  %bb = {h_TH} broadcast({h_H} %b), dimensions={{1}}
+  %y = {h_TH} add({h_TH} %x, {h_TH} %bb)
+  %r = {h_BShd} reshape({h_TH} %y)
+  ROOT %t = {h_heads} transpose({h_BShd} %r), dimensions={{0,2,1,3}}
+}}
+""")
+    h_sc, f_sc, f_row = _shape("f16", [B, NH, S, S]), _shape("f32", [B, NH, S, S]), _shape("f32", [B, NH, S])
+    comps.append(f"""%fused_softmax (p0: {h_sc}) -> {h_sc} {{
+  %s = {h_sc} parameter(0)
+  %z = {f_sc} convert({h_sc} %s)
+  %ninf = f32[] constant(-inf)
+  %zmax = {f_row} reduce({f_sc} %z, f32[] %ninf), dimensions={{3}}, to_apply=%region_max
+  %zmax_b = {f_sc} broadcast({f_row} %zmax), dimensions={{0,1,2}}
+  %zc = {f_sc} subtract({f_sc} %z, {f_sc} %zmax_b)
+  %e = {f_sc} exponential({f_sc} %zc)
+  %zero = f32[] constant(0)
+  %esum = {f_row} reduce({f_sc} %e, f32[] %zero), dimensions={{3}}, to_apply=%region_add
+  %esum_b = {f_sc} broadcast({f_row} %esum), dimensions={{0,1,2}}
+  %p = {f_sc} divide({f_sc} %e, {f_sc} %esum_b)
+  ROOT %p16 = {h_sc} convert({f_sc} %p)
+}}
+""")
+    comps.append(f"""%fused_merge (p0: {h_heads}) -> {h_TH} {{
+  %x = {h_heads} parameter(0)
+  %t = {h_BShd} transpose({h_heads} %x), dimensions={{0,2,1,3}}
+  ROOT %r = {h_TH} reshape({h_BShd} %t)
+}}
+""")
+    comps.append(f"""%fused_bias_resid (p0: {h_TH}, p1: {h_H}, p2: {h_TH}) -> {h_TH} {{
+  %x = {h_TH} parameter(0)
+  %b = {h_H} parameter(1)
+  %res = {h_TH} parameter(2)
+  %bb = {h_TH} broadcast({h_H} %b), dimensions={{1}}
+  %y = {h_TH} add({h_TH} %x, {h_TH} %bb)
+  ROOT %yr = {h_TH} add({h_TH} %y, {h_TH} %res)
+}}
+""")
+    h_TF, h_F, f_TF = _shape("f16", [T, F]), _shape("f16", [F]), _shape("f32", [T, F])
+    act_lines, act_name = _activation_lines(cfg.act, "y32", f_TF)
+    comps.append(f"%fused_bias_act (p0: {h_TF}, p1: {h_F}) -> {h_TF} {{\n"
+                 f"  %x = {h_TF} parameter(0)\n  %b = {h_F} parameter(1)\n"
+                 f"  %bb = {h_TF} broadcast({h_F} %b), dimensions={{1}}\n"
+                 f"  %y = {h_TF} add({h_TF} %x, {h_TF} %bb)\n"
+                 f"  %y32 = {f_TF} convert({h_TF} %y)\n" + "\n".join(act_lines) + "\n"
+                 f"  ROOT %out = {h_TF} convert({f_TF} %{act_name})\n}}\n")
+
+    def gemm(name, a, a_shape, w, w_shape, out_shape, alpha=1.0, lhs_c=1, rhs_c=0, batch_dims=(), batch=1,
+             ls=0, rs=0):
+        entry.append(f"  %{name} = {_shape('f16', out_shape)} custom-call({_shape('f16', a_shape)} %{a}, "
+                     f"{_shape('f16', w_shape)} %{w}), custom_call_target=\"__cublas$gemm\", "
+                     f"backend_config={_gemm_config(alpha, lhs_c, rhs_c, batch_dims, batch, ls, rs)}")
+        return name
+
+    x = "fusion.tokens"
+    for l in range(cfg.layers):
+        p = f"layer{l}."
+        g1, b1 = const(p + "ln1.gamma", [H]), const(p + "ln1.beta", [H])
+        entry.append(f"  %fusion.ln1.{l} = {h_TH} fusion({h_TH} %{x}, {h_H} %{g1}, {h_H} %{b1}), kind=kInput, calls=%fused_ln")
+        heads = {}
+        for n in ("q", "k", "v"):
+            w = const(p + f"attn.{n}.w", [H, H])
+            b = const(p + f"attn.{n}.b", [H])
+            gname = gemm(f"gemm.{n}.{l}", f"fusion.ln1.{l}", [T, H], w, [H, H], [T, H], ls=T * H, rs=H * H)
+            entry.append(f"  %fusion.{n}.{l} = {h_heads} fusion({h_TH} %{gname}, {h_H} %{b}), kind=kLoop, "
+                         f"calls=%fused_bias_split")
+            heads[n] = f"fusion.{n}.{l}"
+        sc = gemm(f"gemm.scores.{l}", heads["q"], [B, NH, S, D], heads["k"], [B, NH, S, D], [B, NH, S, S],
+                  alpha=1.0 / (D ** 0.5), lhs_c=3, rhs_c=3, batch_dims=(0, 1), batch=B * NH, ls=S * D, rs=S * D)
+        entry.append(f"  %fusion.softmax.{l} = {h_sc} fusion({h_sc} %{sc}), kind=kInput, calls=%fused_softmax")
+        pv = gemm(f"gemm.pv.{l}", f"fusion.softmax.{l}", [B, NH, S, S], heads["v"], [B, NH, S, D], [B, NH, S, D],
+                  lhs_c=3, rhs_c=2, batch_dims=(0, 1), batch=B * NH, ls=S * S, rs=S * D)
+        entry.append(f"  %fusion.ctx.{l} = {h_TH} fusion({h_heads} %{pv}), kind=kLoop, calls=%fused_merge")
+        wo, bo = const(p + "attn.o.w", [H, H]), const(p + "attn.o.b", [H])
+        go = gemm(f"gemm.o.{l}", f"fusion.ctx.{l}", [T, H], wo, [H, H], [T, H], ls=T * H, rs=H * H)
+        entry.append(f"  %fusion.res1.{l} = {h_TH} fusion({h_TH} %{go}, {h_H} %{bo}, {h_TH} %{x}), kind=kLoop, "
+                     f"calls=%fused_bias_resid")
+        x = f"fusion.res1.{l}"
+        g2, b2 = const(p + "ln2.gamma", [H]), const(p + "ln2.beta", [H])
+        entry.append(f"  %fusion.ln2.{l} = {h_TH} fusion({h_TH} %{x}, {h_H} %{g2}, {h_H} %{b2}), kind=kInput, calls=%fused_ln")
+        w1, bb1 = const(p + "ffn.up.w", [H, F]), const(p + "ffn.up.b", [F])
+        gu = gemm(f"gemm.up.{l}", f"fusion.ln2.{l}", [T, H], w1, [H, F], [T, F], ls=T * H, rs=H * F)
+        entry.append(f"  %fusion.act.{l} = {h_TF} fusion({h_TF} %{gu}, {h_F} %{bb1}), kind=kLoop, calls=%fused_bias_act")
+        w2, bb2 = const(p + "ffn.down.w", [F, H]), const(p + "ffn.down.b", [H])
+        gd = gemm(f"gemm.down.{l}", f"fusion.act.{l}", [T, F], w2, [F, H], [T, H], ls=T * F, rs=F * H)
+        entry.append(f"  %fusion.res2.{l} = {h_TH} fusion({h_TH} %{gd}, {h_H} %{bb2}, {h_TH} %{x}), kind=kLoop, "
+                     f"calls=%fused_bias_resid")
+        x = f"fusion.res2.{l}"
+    gf, bf = const("ln.gamma", [H]), const("ln.beta", [H])
+    entry.append(f"  %fusion.lnf = {h_TH} fusion({h_TH} %{x}, {h_H} %{gf}, {h_H} %{bf}), kind=kInput, calls=%fused_ln")
+    out_shape = _shape("f16", [B, S, H])
+    entry.append(f"  ROOT %last_hidden_state = {out_shape} bitcast({h_TH} %fusion.lnf)")
+    text = (f"HloModule {cfg.name}, entry_computation_layout={{({px_s})->{out_shape}}}\n\n" + "\n".join(comps)
+            + f"\nENTRY %{cfg.name}_main (pixel_values: {px_s}) -> {out_shape} {{\n" + "\n".join(entry) + "\n}\n")
+    return text, names

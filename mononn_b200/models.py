@@ -29,6 +29,10 @@ class EncoderConfig:
     seq: int = 128
     eps: float = 1e-12
     act: str = "gelu_erf"
+    # vision models: square image / patch size and channels (seq = patches + 1 class token)
+    image: int = 0
+    patch: int = 0
+    channels: int = 3
 
     def to_json(self) -> str:
         return json.dumps(dataclasses.asdict(self))
@@ -80,7 +84,8 @@ def make_weights(cfg: EncoderConfig, seed: int = 1234, stress: bool = False) -> 
     copy and the fp32 CPU copy hold the same numbers.  Linear weights are [in, out]."""
     rng = np.random.default_rng(seed)
     out: dict[str, np.ndarray] = {}
-    for name, shape in bert_weight_shapes(cfg).items():
+    shapes = vit_weight_shapes(cfg) if cfg.model == "vit" else bert_weight_shapes(cfg)
+    for name, shape in shapes.items():
         if name.endswith(".gamma"):
             w = np.ones(shape, np.float32)
             if stress:
@@ -103,3 +108,50 @@ def make_inputs(cfg: EncoderConfig, seed: int = 1234, pad_fraction: float = 0.0)
         mask[:, cfg.seq - int(cfg.seq * pad_fraction):] = 0
     types = np.zeros((cfg.batch, cfg.seq), np.int32)
     return {"input_ids": ids, "attention_mask": mask, "token_type_ids": types}
+
+
+def vit_base(batch: int = 1) -> EncoderConfig:
+    """ViT-B/16: 224x224x3 image, 16x16 patches (196 + class token = 197 tokens), pre-LN."""
+    return EncoderConfig(model="vit", layers=12, hidden=768, heads=12, ffn=3072, batch=batch, seq=197,
+                         image=224, patch=16, channels=3, max_pos=197, vocab=0, types=0)
+
+
+def vit_tiny(batch: int = 1, image: int = 32, patch: int = 16, layers: int = 1, hidden: int = 64,
+             ffn: int = 256) -> EncoderConfig:
+    n = (image // patch) ** 2 + 1
+    return EncoderConfig(model="vit", layers=layers, hidden=hidden, heads=hidden // 64, ffn=ffn, batch=batch,
+                         seq=n, image=image, patch=patch, channels=3, max_pos=n, vocab=0, types=0)
+
+
+def vit_weight_shapes(cfg: EncoderConfig) -> dict[str, tuple[int, ...]]:
+    h, f = cfg.hidden, cfg.ffn
+    shapes: dict[str, tuple[int, ...]] = {
+        "embeddings.patch.w": (h, cfg.patch, cfg.patch, cfg.channels),  # [out, ky, kx, in]
+        "embeddings.patch.b": (h,),
+        "embeddings.cls": (1, h),
+        "embeddings.position": (cfg.seq, h),
+    }
+    for l in range(cfg.layers):
+        p = f"layer{l}."
+        shapes[p + "ln1.gamma"] = (h,)
+        shapes[p + "ln1.beta"] = (h,)
+        for n in ("q", "k", "v", "o"):
+            shapes[p + f"attn.{n}.w"] = (h, h)
+            shapes[p + f"attn.{n}.b"] = (h,)
+        shapes[p + "ln2.gamma"] = (h,)
+        shapes[p + "ln2.beta"] = (h,)
+        shapes[p + "ffn.up.w"] = (h, f)
+        shapes[p + "ffn.up.b"] = (f,)
+        shapes[p + "ffn.down.w"] = (f, h)
+        shapes[p + "ffn.down.b"] = (h,)
+    shapes["ln.gamma"] = (h,)
+    shapes["ln.beta"] = (h,)
+    return shapes
+
+
+def make_vit_inputs(cfg: EncoderConfig, seed: int = 1234) -> dict[str, np.ndarray]:
+    """Pixels uniform in [-1, 1], NCHW f32 as the reference's exported graph takes them
+    (examples/utils/save_model.py:76-82)."""
+    rng = np.random.default_rng(seed + 7919)
+    px = rng.uniform(-1.0, 1.0, (cfg.batch, cfg.channels, cfg.image, cfg.image)).astype(np.float32)
+    return {"pixel_values": px}

@@ -135,3 +135,38 @@ def bert_encoder_torch(cfg, w, inputs, threads=0):
             y = F.gelu(y) if cfg.act == "gelu_erf" else torch.relu(y)
             x = F.layer_norm(lin(y, "ffn.down") + x, (h,), tw[p + "ffn.ln.gamma"], tw[p + "ffn.ln.beta"], cfg.eps)
     return x.reshape(b * s, h).numpy()
+
+
+def vit_patches(cfg, pixels):
+    """[B, C, H, W] -> [B * patches, ky * kx * C]: the operand of the patch-embedding
+    convolution (stride = window, cross-correlation, NHWC/KRSC as the reference's conv,
+    mononn_engine/core/op_impl/conv_impl.cc:252-345) written as a matrix product."""
+    b, c, hh, ww = pixels.shape
+    p = cfg.patch
+    g = hh // p
+    x = pixels.reshape(b, c, g, p, g, p).transpose(0, 2, 4, 3, 5, 1)  # b, gy, gx, ky, kx, c
+    return x.reshape(b * g * g, p * p * c)
+
+
+def vit_encoder(cfg, w, inputs, return_all=False):
+    """fp32 forward of the pre-LN vision encoder (patch embedding, class token, learned
+    positions, pre-LN blocks with exact GELU, final LayerNorm). Returns [B*tokens, H]."""
+    px = inputs["pixel_values"].astype(np.float32)
+    b, h = cfg.batch, cfg.hidden
+    pat = vit_patches(cfg, px) @ w["embeddings.patch.w"].reshape(h, -1).T + w["embeddings.patch.b"]
+    pat = pat.reshape(b, cfg.seq - 1, h)
+    cls = np.broadcast_to(w["embeddings.cls"].reshape(1, 1, h), (b, 1, h))
+    x = np.concatenate([cls, pat], 1) + w["embeddings.position"][None]
+    x = x.astype(np.float32)
+    hidden = [x]
+    for l in range(cfg.layers):
+        p = f"layer{l}."
+        lin = lambda t, n: t @ w[p + n + ".w"] + w[p + n + ".b"]
+        y = layer_norm(x, w[p + "ln1.gamma"], w[p + "ln1.beta"], cfg.eps)
+        ctx = attention(lin(y, "attn.q"), lin(y, "attn.k"), lin(y, "attn.v"), None, cfg.heads)
+        x = x + lin(ctx, "attn.o")
+        y = layer_norm(x, w[p + "ln2.gamma"], w[p + "ln2.beta"], cfg.eps)
+        x = x + lin(activation(lin(y, "ffn.up"), cfg.act), "ffn.down")
+        hidden.append(x)
+    out = layer_norm(x, w["ln.gamma"], w["ln.beta"], cfg.eps).reshape(b * cfg.seq, h)
+    return (out, hidden) if return_all else out

@@ -16,7 +16,7 @@ import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 sys.path.insert(0, ROOT)
-from mononn_b200.models import EncoderConfig, make_inputs, make_weights  # noqa: E402
+from mononn_b200.models import EncoderConfig, make_inputs, make_vit_inputs, make_weights  # noqa: E402
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
@@ -57,20 +57,61 @@ def hf_bert_forward(cfg: EncoderConfig, w: dict, inputs: dict) -> np.ndarray:
     return out.reshape(cfg.batch * cfg.seq, cfg.hidden).numpy()
 
 
+def hf_vit_forward(cfg: EncoderConfig, w: dict, inputs: dict) -> np.ndarray:
+    from transformers import ViTConfig, ViTModel
+    hc = ViTConfig(hidden_size=cfg.hidden, num_hidden_layers=cfg.layers, num_attention_heads=cfg.heads,
+                   intermediate_size=cfg.ffn, hidden_act="gelu", image_size=cfg.image, patch_size=cfg.patch,
+                   num_channels=cfg.channels, layer_norm_eps=cfg.eps, hidden_dropout_prob=0.0,
+                   attention_probs_dropout_prob=0.0, qkv_bias=True)
+    model = ViTModel(hc, add_pooling_layer=False).eval()
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a))
+    sd = {
+        "embeddings.cls_token": t(w["embeddings.cls"].reshape(1, 1, -1)),
+        "embeddings.position_embeddings": t(w["embeddings.position"][None]),
+        # ours is [out, ky, kx, in]; torch Conv2d wants [out, in, ky, kx]
+        "embeddings.patch_embeddings.projection.weight": t(w["embeddings.patch.w"].transpose(0, 3, 1, 2)),
+        "embeddings.patch_embeddings.projection.bias": t(w["embeddings.patch.b"]),
+        "layernorm.weight": t(w["ln.gamma"]), "layernorm.bias": t(w["ln.beta"]),
+    }
+    for l in range(cfg.layers):
+        p, q = f"layer{l}.", f"encoder.layer.{l}."
+        for ours, theirs in (("attn.q", "attention.attention.query"), ("attn.k", "attention.attention.key"),
+                             ("attn.v", "attention.attention.value"), ("attn.o", "attention.output.dense"),
+                             ("ffn.up", "intermediate.dense"), ("ffn.down", "output.dense")):
+            sd[q + theirs + ".weight"] = t(w[p + ours + ".w"].T)
+            sd[q + theirs + ".bias"] = t(w[p + ours + ".b"])
+        sd[q + "layernorm_before.weight"] = t(w[p + "ln1.gamma"])
+        sd[q + "layernorm_before.bias"] = t(w[p + "ln1.beta"])
+        sd[q + "layernorm_after.weight"] = t(w[p + "ln2.gamma"])
+        sd[q + "layernorm_after.bias"] = t(w[p + "ln2.beta"])
+    missing, unexpected = model.load_state_dict(sd, strict=False)
+    assert not missing and not unexpected, (missing, unexpected)
+    with torch.no_grad():
+        out = model(pixel_values=torch.from_numpy(inputs["pixel_values"])).last_hidden_state
+    return out.reshape(cfg.batch * cfg.seq, cfg.hidden).numpy()
+
+
 CASES = {
     # name: (config, weight seed, stress, pad_fraction)
     "bert_tiny_b1_s16": (EncoderConfig(layers=2, hidden=64, heads=1, ffn=256, vocab=100, max_pos=64,
                                        batch=1, seq=16), 11, True, 0.0),
     "bert_small_b2_s24_pad": (EncoderConfig(layers=2, hidden=128, heads=2, ffn=512, vocab=300, max_pos=64,
                                             batch=2, seq=24), 12, True, 0.25),
+    "vit_tiny_b2_img48": (EncoderConfig(model="vit", layers=2, hidden=128, heads=2, ffn=256, batch=2, seq=10,
+                                        image=48, patch=16, channels=3, max_pos=10, vocab=0, types=0),
+                          13, True, 0.0),
 }
 
 
 def main():
     for name, (cfg, seed, stress, pad) in CASES.items():
         w = make_weights(cfg, seed, stress=stress)
-        inp = make_inputs(cfg, seed, pad_fraction=pad)
-        out = hf_bert_forward(cfg, w, inp)
+        if cfg.model == "vit":
+            inp = make_vit_inputs(cfg, seed)
+            out = hf_vit_forward(cfg, w, inp)
+        else:
+            inp = make_inputs(cfg, seed, pad_fraction=pad)
+            out = hf_bert_forward(cfg, w, inp)
         # keep the file small: the inputs are regenerated from the seed, only the output is stored
         np.savez_compressed(os.path.join(HERE, name + ".npz"), last_hidden_state=out.astype(np.float32),
                             seed=np.int64(seed), stress=np.bool_(stress), pad=np.float64(pad))

@@ -2,8 +2,9 @@
 import numpy as np
 import pytest
 
-from mononn_b200 import bert_base, bert_tiny, compile_encoder, compile_hlo, make_inputs, make_weights
-from mononn_b200.hlo_builder import bert_hlo
+from mononn_b200 import (bert_base, bert_tiny, compile_encoder, compile_hlo, make_inputs, make_vit_inputs,
+                         make_weights, vit_base, vit_tiny)
+from mononn_b200.hlo_builder import bert_hlo, vit_hlo
 from mononn_b200.models import EncoderConfig
 from oracle import ref_encoder as R
 from tests.helpers import assert_parity, golden_cases, load_golden, reference_fixture_inputs
@@ -32,11 +33,45 @@ def build(cfg, w, frontend):
 def test_golden_vectors(name, frontend):
     cfg, seed, stress, pad = golden_cases()[name]
     w = make_weights(cfg, seed, stress=stress)
-    inp = make_inputs(cfg, seed, pad_fraction=pad)
-    mod = build(cfg, w, frontend)
-    got = run_module(mod, cfg, inp)
-    mod.close()
+    if cfg.model == "vit":
+        if frontend == "builder":
+            pytest.skip("the config builder covers the BERT family only")
+        got = run_vit(cfg, w, make_vit_inputs(cfg, seed))
+    else:
+        inp = make_inputs(cfg, seed, pad_fraction=pad)
+        mod = build(cfg, w, frontend)
+        got = run_module(mod, cfg, inp)
+        mod.close()
     assert_parity(got, load_golden(name)["last_hidden_state"], name)
+
+
+def run_vit(cfg, w, inp):
+    text, names = vit_hlo(cfg)
+    mod = compile_hlo(text, barrier_timeout_us=500000)
+    mod.set_weights({names[k]: v for k, v in w.items()})
+    out = mod.run([inp["pixel_values"]])[0]
+    mod.close()
+    return out[: cfg.tokens * cfg.hidden].reshape(cfg.tokens, cfg.hidden).astype(np.float32)
+
+
+@pytest.mark.parametrize("cfg", [
+    vit_tiny(),                                           # 4 patches + class token, one layer
+    vit_tiny(batch=3, image=64, layers=2, hidden=128),    # 17 tokens, ragged rows
+    vit_tiny(batch=2, image=224, layers=1, hidden=128),   # 197 tokens: two key chunks
+], ids=lambda c: f"b{c.batch}img{c.image}h{c.hidden}l{c.layers}")
+def test_vit_shapes_against_oracle(cfg):
+    """Pre-LN vision encoder: patch convolution as patchify + GEMM, class token and positions
+    assembled into the f32 residual stream, GEMMs accumulating into the stream."""
+    w = make_weights(cfg, 41, stress=True)
+    inp = make_vit_inputs(cfg, 41)
+    assert_parity(run_vit(cfg, w, inp), R.vit_encoder(cfg, w, inp), "ViT shape case")
+
+
+def test_vit_base_full_size():
+    cfg = vit_base()
+    w = make_weights(cfg, 1236, stress=True)
+    inp = make_vit_inputs(cfg, 1236)
+    assert_parity(run_vit(cfg, w, inp), R.vit_encoder(cfg, w, inp), "ViT-B/16 b1")
 
 
 @pytest.mark.parametrize("cfg", [

@@ -2,7 +2,7 @@
 import numpy as np
 import pytest
 
-from mononn_b200.models import EncoderConfig, bert_tiny, make_inputs, make_weights
+from mononn_b200.models import EncoderConfig, bert_tiny, make_inputs, make_vit_inputs, make_weights
 from oracle import ref_encoder as R
 from tests.helpers import golden_cases, load_golden
 
@@ -12,8 +12,10 @@ def test_oracle_matches_golden_vectors(name):
     cfg, seed, stress, pad = golden_cases()[name]
     g = load_golden(name)
     w = make_weights(cfg, seed, stress=stress)
-    inp = make_inputs(cfg, seed, pad_fraction=pad)
-    out = R.bert_encoder(cfg, w, inp)
+    if cfg.model == "vit":
+        out = R.vit_encoder(cfg, w, make_vit_inputs(cfg, seed))
+    else:
+        out = R.bert_encoder(cfg, w, make_inputs(cfg, seed, pad_fraction=pad))
     ref = g["last_hidden_state"]
     assert out.shape == ref.shape
     # two fp32 implementations of the same definition: agreement to rounding
