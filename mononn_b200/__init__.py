@@ -4,4 +4,4 @@ one persistent kernel launch per inference out.  The work is done by libmononn_b
 from .capi import MononnError, Options  # noqa: F401
 from .module import Module, compile_encoder, compile_hlo  # noqa: F401
 from .models import (EncoderConfig, bert_base, bert_tiny, make_inputs, make_vit_inputs,  # noqa: F401
-                     make_weights, vit_base, vit_tiny)
+                     make_weights, opt_1p3b, opt_tiny, vit_base, vit_tiny)

@@ -4,6 +4,7 @@
 #include <algorithm>
 #include <cmath>
 #include <functional>
+#include <map>
 
 #include "../../include/mononn.h"
 
@@ -38,11 +39,90 @@ float round_to_dtype(float x, const std::string& dtype) {
   return x;  // f16 / f32: the evaluator works in fp32 throughout
 }
 
+// A reduction's to_apply computation compiled to a straight-line program over scalars, for
+// combiners that are more than one operator (the (value, index) comparator of an arg-max:
+// codegen/reduction_functor_generator.cc:296-441 supports add/max/min/and/select/compare/
+// tuple/get-tuple-element there).
+struct ScalarProgram {
+  enum Code { PARAM, CONST, ADD, SUB, MUL, MAX, MIN, AND, OR, NOT, SELECT, EQ, NE, LT, LE, GT, GE, COPY };
+  struct Step { Code code; int a, b, c; float k; };
+  std::vector<Step> steps;
+  std::vector<int> results;  // step index of each result element
+  mutable std::vector<float> reg;
+
+  static bool compile(const HloComputation& f, ScalarProgram* p, std::string* why) {
+    p->steps.clear();
+    p->results.clear();
+    for (const HloInstr& i : f.instrs) {
+      Step st{COPY, i.operands.size() > 0 ? i.operands[0] : -1, i.operands.size() > 1 ? i.operands[1] : -1,
+              i.operands.size() > 2 ? i.operands[2] : -1, 0.f};
+      const std::string& o = i.opcode;
+      if (o == "parameter") { st.code = PARAM; st.a = static_cast<int>(i.param_number); }
+      else if (o == "constant" && i.literal_is_scalar) { st.code = CONST; st.k = static_cast<float>(i.literal); }
+      else if (o == "add") st.code = ADD;
+      else if (o == "subtract") st.code = SUB;
+      else if (o == "multiply") st.code = MUL;
+      else if (o == "maximum") st.code = MAX;
+      else if (o == "minimum") st.code = MIN;
+      else if (o == "and") st.code = AND;
+      else if (o == "or") st.code = OR;
+      else if (o == "not") st.code = NOT;
+      else if (o == "select") st.code = SELECT;
+      else if (o == "convert" || o == "copy" || o == "bitcast") st.code = COPY;
+      else if (o == "compare") {
+        const std::string d = i.attr("direction");
+        if (d == "EQ") st.code = EQ; else if (d == "NE") st.code = NE; else if (d == "LT") st.code = LT;
+        else if (d == "LE") st.code = LE; else if (d == "GT") st.code = GT; else if (d == "GE") st.code = GE;
+        else { *why = "comparison direction " + d; return false; }
+      } else if (o == "tuple") {
+        st.code = COPY;  // value unused; elements recorded below
+        st.a = i.operands.empty() ? -1 : i.operands[0];
+      } else { *why = "operator " + o + " in a reduction combiner"; return false; }
+      p->steps.push_back(st);
+    }
+    if (f.root < 0) { *why = "combiner without a root"; return false; }
+    const HloInstr& root = f.instrs[f.root];
+    if (root.opcode == "tuple") p->results = root.operands;
+    else p->results.push_back(f.root);
+    p->reg.assign(p->steps.size(), 0.f);
+    return true;
+  }
+  // args: accumulators then new elements (XLA's reducer signature); out: one per result
+  void run(const float* args, float* out) const {
+    float* r = reg.data();
+    for (size_t i = 0; i < steps.size(); ++i) {
+      const Step& s = steps[i];
+      switch (s.code) {
+        case PARAM: r[i] = args[s.a]; break;
+        case CONST: r[i] = s.k; break;
+        case ADD: r[i] = r[s.a] + r[s.b]; break;
+        case SUB: r[i] = r[s.a] - r[s.b]; break;
+        case MUL: r[i] = r[s.a] * r[s.b]; break;
+        case MAX: r[i] = std::max(r[s.a], r[s.b]); break;
+        case MIN: r[i] = std::min(r[s.a], r[s.b]); break;
+        case AND: r[i] = (r[s.a] != 0.f && r[s.b] != 0.f) ? 1.f : 0.f; break;
+        case OR: r[i] = (r[s.a] != 0.f || r[s.b] != 0.f) ? 1.f : 0.f; break;
+        case NOT: r[i] = r[s.a] != 0.f ? 0.f : 1.f; break;
+        case SELECT: r[i] = r[s.a] != 0.f ? r[s.b] : r[s.c]; break;
+        case EQ: r[i] = r[s.a] == r[s.b] ? 1.f : 0.f; break;
+        case NE: r[i] = r[s.a] != r[s.b] ? 1.f : 0.f; break;
+        case LT: r[i] = r[s.a] < r[s.b] ? 1.f : 0.f; break;
+        case LE: r[i] = r[s.a] <= r[s.b] ? 1.f : 0.f; break;
+        case GT: r[i] = r[s.a] > r[s.b] ? 1.f : 0.f; break;
+        case GE: r[i] = r[s.a] >= r[s.b] ? 1.f : 0.f; break;
+        case COPY: r[i] = s.a >= 0 ? r[s.a] : 0.f; break;
+      }
+    }
+    for (size_t k = 0; k < results.size(); ++k) out[k] = r[results[k]];
+  }
+};
+
 }  // namespace
 
 int eval_computation(const HloModule& m, const HloComputation& comp,
                      const std::vector<HTensor>& params, HTensor* out, std::string* err) {
   std::vector<HTensor> val(comp.instrs.size());
+  std::map<int, std::vector<HTensor>> tuples;  // results of variadic reduces
   // last use, to free intermediates of large fusions early
   std::vector<int> last_use(comp.instrs.size(), -1);
   for (size_t i = 0; i < comp.instrs.size(); ++i)
@@ -51,7 +131,57 @@ int eval_computation(const HloModule& m, const HloComputation& comp,
   for (size_t idx = 0; idx < comp.instrs.size(); ++idx) {
     const HloInstr& ins = comp.instrs[idx];
     const std::string& op = ins.opcode;
-    if (ins.shape.is_tuple()) return unsupported(err, ins, "tuple-shaped value inside a fusion");
+    if (ins.shape.is_tuple()) {
+      // Variadic reduce over one dimension: N inputs, N init values, N results.
+      if (op != "reduce" || ins.operands.size() < 4 || ins.operands.size() % 2 != 0)
+        return unsupported(err, ins, "tuple-shaped value inside a fusion");
+      const size_t N = ins.operands.size() / 2;
+      const std::vector<int64_t> rd = ins.int_list("dimensions");
+      const HloComputation* f = m.find(ins.attr("to_apply"));
+      if (rd.size() != 1 || !f || ins.shape.elems.size() != N)
+        return unsupported(err, ins, "variadic reduce must reduce one dimension with a known combiner");
+      ScalarProgram prog;
+      std::string why;
+      if (!ScalarProgram::compile(*f, &prog, &why)) return unsupported(err, ins, why);
+      if (f->params.size() != 2 * N || prog.results.size() != N)
+        return unsupported(err, ins, "combiner signature does not match the reduce");
+      const HTensor& a0 = val[ins.operands[0]];
+      const int64_t d = rd[0];
+      if (d < 0 || d >= static_cast<int64_t>(a0.dims.size())) return unsupported(err, ins, "bad dimension");
+      const auto as = strides_of(a0.dims);
+      const int64_t len = a0.dims[d], inner = as[d], outer = a0.size() / (len * inner);
+      std::vector<HTensor> res(N);
+      for (size_t k = 0; k < N; ++k) {
+        if (val[ins.operands[k]].size() != a0.size() || val[ins.operands[N + k]].size() != 1)
+          return unsupported(err, ins, "variadic reduce operand shapes differ");
+        res[k].dims = ins.shape.elems[k].dims;
+        if (res[k].size() != outer * inner) return unsupported(err, ins, "result shape mismatch");
+        res[k].v.resize(static_cast<size_t>(outer * inner));
+      }
+      std::vector<float> args(2 * N), acc(N);
+      for (int64_t o = 0; o < outer; ++o)
+        for (int64_t in = 0; in < inner; ++in) {
+          for (size_t k = 0; k < N; ++k) acc[k] = val[ins.operands[N + k]].v[0];
+          for (int64_t e = 0; e < len; ++e) {
+            for (size_t k = 0; k < N; ++k) {
+              args[k] = acc[k];
+              args[N + k] = val[ins.operands[k]].v[(o * len + e) * inner + in];
+            }
+            prog.run(args.data(), acc.data());
+          }
+          for (size_t k = 0; k < N; ++k) res[k].v[o * inner + in] = acc[k];
+        }
+      tuples[static_cast<int>(idx)] = std::move(res);
+      continue;
+    }
+    if (op == "get-tuple-element") {
+      const auto gi = ins.int_list("index");
+      auto it = ins.operands.size() == 1 ? tuples.find(ins.operands[0]) : tuples.end();
+      if (it == tuples.end() || gi.size() != 1 || gi[0] < 0 || gi[0] >= static_cast<int64_t>(it->second.size()))
+        return unsupported(err, ins, "get-tuple-element of something that is not a variadic reduce");
+      val[idx] = it->second[gi[0]];
+      continue;
+    }
     if (!default_layout(ins.shape))
       return unsupported(err, ins, "non-default (not row-major) layout");
     HTensor r;

@@ -82,6 +82,8 @@ struct Val {
   int mask_arg = -1;                  // MASK: the s32 argument it derives from
   int ids = -1, types = -1, word = -1, pos = -1, type = -1;  // EMBED_SUM (FGraph tensors)
   uint32_t vocab = 0;
+  uint32_t pos_off = 0;               // EMBED_SUM: first row of the position table that is used
+  bool causal = false;                // PROBS
 };
 
 class Lowering {
@@ -136,11 +138,13 @@ class Lowering {
       } else if (ins.opcode == "bitcast" || ins.opcode == "reshape" || ins.opcode == "copy") {
         if (ins.operands.size() != 1) return unsupported(ins, "expects one operand");
         const Val& s = vals_[ins.operands[0]];
-        if (s.kind != Val::ACT && s.kind != Val::ARG && s.kind != Val::CONST)
+        if (s.kind != Val::ACT && s.kind != Val::ARG && s.kind != Val::CONST &&
+            !(s.kind == Val::GEMM && uses_[ins.operands[0]] == 1))
           return unsupported(ins, "reshape of this kind of value at the top level");
         if (ins.shape.elements() != e_.instrs[ins.operands[0]].shape.elements())
           return unsupported(ins, "element count changes");
         vals_[idx] = s;  // same buffer, row-major in both shapes
+        if (s.kind == Val::GEMM) vals_[idx].instr = static_cast<int>(idx);  // consumers are counted on the alias
       } else if (ins.opcode == "get-tuple-element") {
         if (ins.operands.size() != 1) return unsupported(ins, "expects one operand");
         const Val& s = vals_[ins.operands[0]];
@@ -179,7 +183,8 @@ class Lowering {
   // ----------------------------------------------------------------- tensors
   int const_tensor(int instr, uint32_t rows, uint32_t cols, bool transposed = false) {
     const HloInstr& c = e_.instrs[instr];
-    auto it = const_tensors_.find(instr);
+    const std::pair<int, bool> key(instr, transposed);
+    auto it = const_tensors_.find(key);
     if (it != const_tensors_.end()) return it->second;
     FTensor t;
     t.name = c.name;
@@ -191,7 +196,7 @@ class Lowering {
     t.const_name = c.name;
     t.const_transposed = transposed;
     for (int64_t d : c.shape.dims) t.const_dims.push_back(static_cast<uint32_t>(d));
-    return const_tensors_[instr] = g_.add_tensor(t);
+    return const_tensors_[key] = g_.add_tensor(t);
   }
   int act_tensor(const std::string& name, uint32_t rows, uint32_t cols) {
     FTensor t;
@@ -322,6 +327,7 @@ class Lowering {
       o.batches = a.B;
       o.head_dim = a.D;
       o.alpha = a.alpha;
+      if (a.causal) o.flags |= F_CAUSAL;
       g_.ops.push_back(o);
       Val v;
       v.kind = Val::ATTN;
@@ -350,6 +356,7 @@ class Lowering {
     bool has_concat = false;
     for (const HloInstr& i : c->instrs) has_concat = has_concat || i.opcode == "concatenate";
     if (has_gather) return lower_embed_sum(idx, *c);
+    if (has_reduce && ins.shape.dtype == "s32" && ins.operands.size() == 1) return lower_argmax(idx, *c);
     if (has_concat) {  // token assembly: the result has more rows than the patch GEMM
       for (size_t k = 0; k < ins.operands.size(); ++k)
         if (vals_[ins.operands[k]].kind == Val::GEMM) return lower_tokens(idx, *c, static_cast<int>(k));
@@ -597,6 +604,7 @@ class Lowering {
       n.type = mv.type;
       n.seq = mv.S;
       n.vocab = mv.vocab;
+      n.q_col = mv.pos_off;
       n.alpha = -10000.f;
     } else {
       if (bias_k >= 0) return unsupported(ins, "bias vector on a LayerNorm that does not follow a GEMM");
@@ -639,29 +647,38 @@ class Lowering {
     int rc = probe(c, ps, &got);
     if (rc) return rc;
     std::vector<float> want(got.v.size());
-    for (uint32_t b = 0; b < B; ++b)
-      for (uint32_t h = 0; h < H; ++h)
-        for (uint32_t q = 0; q < S; ++q) {
-          const size_t base = ((static_cast<size_t>(b) * H + h) * S + q) * S;
-          float mx = -INFINITY;
-          for (uint32_t k = 0; k < S; ++k) {
-            const float z = ps[main_k].v[base + k] + (mask_k >= 0 ? ps[mask_k].v[static_cast<size_t>(b) * S + k] : 0.f);
-            want[base + k] = z;
-            mx = std::max(mx, z);
+    bool causal = false, ok = false;
+    for (int trial = 0; trial < 2 && !ok; ++trial) {
+      causal = (trial == 1);  // keys after the query position are excluded
+      for (uint32_t b = 0; b < B; ++b)
+        for (uint32_t h = 0; h < H; ++h)
+          for (uint32_t q = 0; q < S; ++q) {
+            const size_t base = ((static_cast<size_t>(b) * H + h) * S + q) * S;
+            const uint32_t n_keys = causal ? q + 1 : S;
+            float mx = -INFINITY;
+            for (uint32_t k = 0; k < n_keys; ++k) {
+              const float z = ps[main_k].v[base + k] + (mask_k >= 0 ? ps[mask_k].v[static_cast<size_t>(b) * S + k] : 0.f);
+              want[base + k] = z;
+              mx = std::max(mx, z);
+            }
+            double sum = 0;
+            for (uint32_t k = 0; k < n_keys; ++k) {
+              want[base + k] = std::exp(want[base + k] - mx);
+              sum += want[base + k];
+            }
+            for (uint32_t k = 0; k < n_keys; ++k) want[base + k] = static_cast<float>(want[base + k] / sum);
+            for (uint32_t k = n_keys; k < S; ++k) want[base + k] = 0.f;
           }
-          double sum = 0;
-          for (uint32_t k = 0; k < S; ++k) {
-            want[base + k] = std::exp(want[base + k] - mx);
-            sum += want[base + k];
-          }
-          for (uint32_t k = 0; k < S; ++k) want[base + k] = static_cast<float>(want[base + k] / sum);
-        }
-    if (!all_close(got.v, want, 1e-5f, 1e-4f))
-      return unsupported(ins, "fused computation " + c.name + " is not softmax(scores + mask) over the last dimension");
+      ok = all_close(got.v, want, 1e-5f, 1e-4f);
+    }
+    if (!ok)
+      return unsupported(ins, "fused computation " + c.name +
+                                  " is not softmax(scores + mask) over the last dimension, plain or causal");
     Val v = sv;
     v.kind = Val::PROBS;
     v.instr = idx;
     v.mask_tensor = mask_k >= 0 ? vals_[ins.operands[mask_k]].tensor : -1;
+    v.causal = causal;
     vals_[idx] = v;
     return MONONN_OK;
   }
@@ -951,10 +968,17 @@ class Lowering {
     };
     std::vector<std::pair<int, int>> gathers;  // (table param, index param)
     int pos_param = -1;
+    uint32_t pos_off = 0;
     for (const HloInstr& i : c.instrs) {
       if (i.opcode == "gather" && i.operands.size() == 2)
         gathers.push_back({param_of(i.operands[0]), param_of(i.operands[1])});
-      if (i.opcode == "slice" && i.operands.size() == 1) pos_param = param_of(i.operands[0]);
+      if (i.opcode == "slice" && i.operands.size() == 1) {
+        pos_param = param_of(i.operands[0]);
+        // first row taken from the position table: slice={[a:b], [0:H]}
+        const std::string sl = i.attr("slice");
+        const size_t lb = sl.find('[');
+        pos_off = lb == std::string::npos ? 0 : static_cast<uint32_t>(std::strtoul(sl.c_str() + lb + 1, nullptr, 10));
+      }
     }
     if (gathers.empty() || gathers.size() > 2 || pos_param < 0)
       return unsupported(ins, "embedding fusion must be word gather + position slice (+ type gather)");
@@ -984,14 +1008,15 @@ class Lowering {
     std::vector<float> want(static_cast<size_t>(T) * H);
     for (uint32_t t = 0; t < T; ++t)
       for (uint32_t j = 0; j < H; ++j) {
-        float y = ps[pos_param].v[static_cast<size_t>(t % S) * H + j];
+        float y = ps[pos_param].v[static_cast<size_t>(t % S + pos_off) * H + j];
         for (auto& gp : gathers)
           y += ps[gp.first].v[static_cast<size_t>(ps[gp.second].v[t]) * H + j];
         want[static_cast<size_t>(t) * H + j] = y;
       }
     if (!all_close(got.v, want, 1e-5f, 1e-5f))
-      return unsupported(ins, "fused computation " + c.name + " is not word[ids] + position[0:S] + type[type_ids]");
-    if (uses_[idx] != 1) return unsupported(ins, "embedding sum with more than one consumer");
+      return unsupported(ins, "fused computation " + c.name + " is not word[ids] + position[a:a+S] + type[type_ids]");
+    if (static_cast<int64_t>(pos_off) + S > c.instrs[c.params[pos_param]].shape.dims[0])
+      return unsupported(ins, "position slice runs past the table");
     auto table = [&](int param) {
       const int instr = vals_[ins.operands[param]].instr;
       const HloInstr& ti = e_.instrs[instr];
@@ -1015,6 +1040,105 @@ class Lowering {
       v.types = vals_[ins.operands[gathers[1].second]].tensor;
       v.type = table(gathers[1].first);
     }
+    v.pos_off = pos_off;
+    if (uses_[idx] != 1) {
+      // No LayerNorm follows directly (pre-LN decoder): the sum itself is the residual
+      // stream, materialised in f32 by an embedding stage without normalisation.
+      FTensor st;
+      st.name = canonical_node_name(ins.name);
+      st.kind = TKind::AccF32;
+      st.rows = T;
+      st.cols = H;
+      st.ld = H;
+      st.elem_bytes = 4;
+      FOp e;
+      e.kind = OP_EMBED;
+      e.name = canonical_node_name(ins.name);
+      e.ids = v.ids;
+      e.type_ids = v.types;
+      e.word = v.word;
+      e.pos = v.pos;
+      e.type = v.type;
+      e.seq = S;
+      e.vocab = v.vocab;
+      e.q_col = pos_off;
+      e.rows = T;
+      e.cols = H;
+      e.out2 = g_.add_tensor(st);
+      g_.ops.push_back(e);
+      Val sv;
+      sv.kind = Val::STREAM;
+      sv.instr = idx;
+      sv.tensor = e.out2;
+      sv.op = static_cast<int>(g_.ops.size()) - 1;
+      sv.rows = T;
+      sv.cols = H;
+      vals_[idx] = sv;
+      return MONONN_OK;
+    }
+    vals_[idx] = v;
+    return MONONN_OK;
+  }
+
+  // A GEMM whose result is used as it is (no epilogue fusion follows): give it an f16 output.
+  int materialise_gemm(int instr) {
+    Val& v = vals_[instr];
+    if (v.kind != Val::GEMM) return MONONN_OK;
+    FOp& gop = g_.ops[v.op];
+    if (gop.out < 0) gop.out = act_tensor(gop.name, gop.M, gop.N);
+    v.kind = Val::ACT;
+    v.tensor = gop.out;
+    v.rows = gop.M;
+    v.cols = gop.N;
+    return MONONN_OK;
+  }
+
+  // index of the row maximum (first index on ties): XLA's variadic (value, index) reduce
+  int lower_argmax(int idx, const HloComputation& c) {
+    const HloInstr& ins = e_.instrs[idx];
+    int rc = materialise_gemm(ins.operands[0]);
+    if (rc) return rc;
+    const Val sv = vals_[ins.operands[0]];
+    if (sv.kind != Val::ACT) return unsupported(ins, "arg-max over something that is not an activation");
+    const uint32_t rows = sv.rows, cols = sv.cols;
+    if (ins.shape.elements() != rows) return unsupported(ins, "arg-max must reduce the last dimension");
+    // few distinct values, so that every row has ties and the tie-break rule is checked
+    Rng rng;
+    std::vector<HTensor> ps = probe_inputs(c, [&](size_t, HTensor& t) {
+      for (float& x : t.v) x = std::floor(rng.uni(0.f, 7.999f)) - 4.f;
+    });
+    HTensor got;
+    rc = probe(c, ps, &got);
+    if (rc) return rc;
+    for (uint32_t r = 0; r < rows; ++r) {
+      uint32_t best = 0;
+      for (uint32_t j = 1; j < cols; ++j)
+        if (ps[0].v[static_cast<size_t>(r) * cols + j] > ps[0].v[static_cast<size_t>(r) * cols + best]) best = j;
+      if (got.v[r] != static_cast<float>(best))
+        return unsupported(ins, "fused computation " + c.name + " is not arg-max over the last dimension (first index on ties)");
+    }
+    FTensor t;
+    t.name = canonical_node_name(ins.name);
+    t.kind = TKind::ActF16;
+    t.rows = rows;
+    t.cols = 1;
+    t.ld = 2;  // one s32 per row, counted in 16-bit units
+    t.elem_bytes = 4;
+    FOp o;
+    o.kind = OP_ARGMAX;
+    o.name = canonical_node_name(ins.name);
+    o.src = sv.tensor;
+    o.rows = rows;
+    o.cols = cols;
+    o.out = g_.add_tensor(t);
+    g_.ops.push_back(o);
+    Val v;
+    v.kind = Val::ACT;
+    v.instr = idx;
+    v.tensor = o.out;
+    v.op = static_cast<int>(g_.ops.size()) - 1;
+    v.rows = rows;
+    v.cols = 1;
     vals_[idx] = v;
     return MONONN_OK;
   }
@@ -1028,6 +1152,7 @@ class Lowering {
     const int n_params = static_cast<int>(e_.params.size());
     int ordinal = 0;
     for (int o : outs) {
+      materialise_gemm(o);
       const Val& v = vals_[o];
       const HloInstr& oi = e_.instrs[o];
       if (v.kind != Val::ACT || v.op < 0)
@@ -1072,7 +1197,7 @@ class Lowering {
   std::string* err_;
   std::vector<Val> vals_;
   std::vector<int> uses_;
-  std::map<int, int> const_tensors_;
+  std::map<std::pair<int, bool>, int> const_tensors_;
   std::vector<Val> masks_;
 };
 

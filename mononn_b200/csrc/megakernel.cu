@@ -172,6 +172,8 @@ struct Ctrl {
   uint32_t abort_flag;
   float bias_tile[2][256];  // bias of the current GEMM tile, double buffered across items
   float mask_row[384];      // additive key mask of the current attention tile (log2 units)
+  float red_val[4];         // arg-max: per-warp partial results of the current row
+  uint32_t red_idx[4];
   // Shared-memory copies of the operator descriptor each role is working on: slot 0 weight
   // producer, 1 activation producer, 2 MMA issuer, 3..6 the four epilogue warps.
   uint4 desc[7][16];
@@ -966,6 +968,61 @@ __device__ __noinline__ void rowwise_item(const OpDesc& op, uint32_t local, uint
   if (mark) trace(P, stage, TR_MARK0 + 2);
 }
 
+// Arg-max item: one f16 row per 128-thread group. Each thread scans every 128th 16-byte
+// vector in ascending order (so "strictly greater" keeps its first maximum), then the
+// partial results are merged by (larger value, then smaller index): the first index of the
+// row maximum, which is what XLA's (value, index) reduce returns
+// (reduction functors: mononn_engine/codegen/reduction_functor_generator.cc:296-441).
+__device__ __noinline__ bool argmax_item(Ctx& c, const OpDesc& op, uint32_t row, uint32_t quarter,
+                                         uint32_t lane, uint32_t tid_in_group) {
+  const uint32_t nvec = op.cols >> 3;
+  const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(op.p[1]) +
+                                                    static_cast<size_t>(row) * op.lds);
+  float best = -INFINITY;
+  uint32_t best_i = 0;
+#pragma unroll 1
+  for (uint32_t v0 = tid_in_group; v0 < nvec; v0 += 512u) {
+    uint4 h[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __ldcg(src + ((v0 + i * 128u < nvec) ? v0 + i * 128u : v0));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t vi = v0 + i * 128u;
+      if (vi < nvec) {
+        const __half2* hp = reinterpret_cast<const __half2*>(&h[i]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __half22float2(hp[j]);
+          if (f.x > best) { best = f.x; best_i = vi * 8u + 2u * j; }
+          if (f.y > best) { best = f.y; best_i = vi * 8u + 2u * j + 1u; }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+    const uint32_t oi = __shfl_xor_sync(0xffffffffu, best_i, off);
+    if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+  }
+  if (lane == 0) {
+    c.ctrl->red_val[quarter] = best;
+    c.ctrl->red_idx[quarter] = best_i;
+  }
+  if (!group_sync(c, 0x420)) return false;
+  if (tid_in_group == 0) {
+#pragma unroll
+    for (int w = 1; w < 4; ++w) {
+      const float ov = c.ctrl->red_val[w];
+      const uint32_t oi = c.ctrl->red_idx[w];
+      if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+    }
+    reinterpret_cast<int32_t*>(op.p[0])[row] = static_cast<int32_t>(best_i);
+  }
+  // the partial-result slots are reused by the group's next row
+  return group_sync(c, 0x421);
+}
+
 // Patch extraction for a convolution whose stride equals its window (ViT / CLIP patch
 // embedding): row (b, py, px) of the f16 output holds the window's pixels in (ky, kx, c)
 // order, read from the NCHW f32 image. With that operand the convolution is a plain GEMM
@@ -1167,6 +1224,9 @@ __device__ void role_simt(Ctx c, uint32_t tmem_base, uint32_t tid_in_group) {
           break;
         case OP_PATCHIFY:
           patchify_item(op, it.local, quarter, lane);
+          break;
+        case OP_ARGMAX:
+          WAIT_OR_RETURN(argmax_item(c, op, it.local, quarter, lane, tid_in_group));
           break;
         default:
           break;

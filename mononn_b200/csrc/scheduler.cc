@@ -192,6 +192,11 @@ int validate_plan(const Plan& P, std::string* err) {
         if (op.p[6].space == SPACE_NONE && d.kind != OP_LAYERNORM) return bad(n + "no scale pointer");
         if (d.kind == OP_ASSEMBLE && (d.seq == 0 || d.k_col >= d.seq)) return bad(n + "token geometry");
         break;
+      case OP_ARGMAX:
+        if (d.cols == 0 || d.cols % 8 || d.lds % 8) return bad(n + "row length must be a multiple of 8");
+        if (d.n_items != d.rows) return bad(n + "item count");
+        if (op.p[0].space == SPACE_NONE || op.p[1].space == SPACE_NONE) return bad(n + "buffers");
+        break;
       case OP_PATCHIFY:
         if (d.cols != d.heads * d.head_dim * d.q_col || d.vocab == 0 || d.k_col == 0)
           return bad(n + "patch geometry");
@@ -628,6 +633,15 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
           po.p[1] = where[o.src];
           break;
         }
+        case OP_ARGMAX: {
+          d.rows = o.rows;
+          d.cols = o.cols;
+          d.lds = g.tensors[o.src].ld;
+          d.n_items = o.rows;  // one row per 128-thread group
+          po.p[0] = where[o.out];
+          po.p[1] = where[o.src];
+          break;
+        }
         case OP_ASSEMBLE: {
           d.rows = o.rows;
           d.cols = o.cols;
@@ -736,7 +750,7 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
     }
   std::set<std::string> counted;
   for (const ConstBinding& b : P.consts) {
-    if (gathered.count(b.const_name) || counted.count(b.const_name)) continue;
+    if ((b.kind == ConstBinding::RAW && gathered.count(b.const_name)) || counted.count(b.const_name)) continue;
     counted.insert(b.const_name);
     P.algorithmic_bytes += static_cast<double>(b.src_bytes);
   }

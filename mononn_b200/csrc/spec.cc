@@ -123,6 +123,7 @@ static const char* kind_name(uint32_t k) {
     case OP_EMBED: return "embed";
     case OP_ASSEMBLE: return "assemble";
     case OP_PATCHIFY: return "patchify";
+    case OP_ARGMAX: return "argmax";
     default: return "none";
   }
 }

@@ -20,6 +20,7 @@ enum OpKind : uint32_t {
   OP_L2NORM_LOGITS = 5,
   OP_ASSEMBLE = 6,   // token rows = [constant prefix rows | GEMM rows + bias] + position rows -> f32
   OP_PATCHIFY = 7,   // NCHW f32 image -> f16 patch rows (operand of the patch-embedding GEMM)
+  OP_ARGMAX = 8,     // s32 index of the maximum of every f16 row (first index on ties)
 };
 
 enum ActKind : uint32_t {

@@ -304,6 +304,121 @@ def bert_hlo(cfg: EncoderConfig) -> tuple[str, dict[str, str]]:
     return text, names
 
 
+def _preln_blocks(cfg: EncoderConfig, comps: list, entry: list, const, x: str, causal: bool) -> str:
+    """Appends the fused computations and the entry instructions of `cfg.layers` pre-LN
+    transformer blocks plus the final LayerNorm, reading the [tokens, hidden] f16 value `x`;
+    returns the name of the final LayerNorm fusion. With `causal` the softmax fusion masks
+    keys after the query position (iota/compare/select, as XLA prints a causal mask)."""
+    B, S, H, F, NH = cfg.batch, cfg.seq, cfg.hidden, cfg.ffn, cfg.heads
+    D, T = H // NH, cfg.batch * cfg.seq
+    h_TH, h_H, f_TH = _shape("f16", [T, H]), _shape("f16", [H]), _shape("f32", [T, H])
+    comps.append(f"%fused_ln (p0: {h_TH}, p1: {h_H}, p2: {h_H}) -> {h_TH} {{\n"
+                 f"  %x = {h_TH} parameter(0)\n  %gamma = {h_H} parameter(1)\n  %beta = {h_H} parameter(2)\n"
+                 f"  %x32 = {f_TH} convert({h_TH} %x)\n" + "\n".join(_ln_body(T, H, cfg.eps, "x32")) + "\n}\n")
+    h_heads, h_BShd = _shape("f16", [B, NH, S, D]), _shape("f16", [B, S, NH, D])
+    comps.append(f"""%fused_bias_split (p0: {h_TH}, p1: {h_H}) -> {h_heads} {{
+  %x = {h_TH} parameter(0)
+  %b = {h_H} parameter(1)
+  %bb = {h_TH} broadcast({h_H} %b), dimensions={{1}}
+  %y = {h_TH} add({h_TH} %x, {h_TH} %bb)
+  %r = {h_BShd} reshape({h_TH} %y)
+  ROOT %t = {h_heads} transpose({h_BShd} %r), dimensions={{0,2,1,3}}
+}}
+""")
+    h_sc, f_sc, f_row = _shape("f16", [B, NH, S, S]), _shape("f32", [B, NH, S, S]), _shape("f32", [B, NH, S])
+    i_sc, p_sc = _shape("s32", [B, NH, S, S]), _shape("pred", [B, NH, S, S])
+    if causal:
+        causal_lines = (f"  %qi = {i_sc} iota(), iota_dimension=2\n  %ki = {i_sc} iota(), iota_dimension=3\n"
+                        f"  %keep = {p_sc} compare({i_sc} %qi, {i_sc} %ki), direction=GE\n"
+                        f"  %ninf_b = {f_sc} broadcast(f32[] %ninf), dimensions={{}}\n"
+                        f"  %z = {f_sc} select({p_sc} %keep, {f_sc} %z0, {f_sc} %ninf_b)")
+    else:
+        causal_lines = f"  %z = {f_sc} copy({f_sc} %z0)"
+    comps.append(f"""%fused_softmax (p0: {h_sc}) -> {h_sc} {{
+  %s = {h_sc} parameter(0)
+  %z0 = {f_sc} convert({h_sc} %s)
+  %ninf = f32[] constant(-inf)
+{causal_lines}
+  %zmax = {f_row} reduce({f_sc} %z, f32[] %ninf), dimensions={{3}}, to_apply=%region_max
+  %zmax_b = {f_sc} broadcast({f_row} %zmax), dimensions={{0,1,2}}
+  %zc = {f_sc} subtract({f_sc} %z, {f_sc} %zmax_b)
+  %e = {f_sc} exponential({f_sc} %zc)
+  %zero = f32[] constant(0)
+  %esum = {f_row} reduce({f_sc} %e, f32[] %zero), dimensions={{3}}, to_apply=%region_add
+  %esum_b = {f_sc} broadcast({f_row} %esum), dimensions={{0,1,2}}
+  %p = {f_sc} divide({f_sc} %e, {f_sc} %esum_b)
+  ROOT %p16 = {h_sc} convert({f_sc} %p)
+}}
+""")
+    comps.append(f"""%fused_merge (p0: {h_heads}) -> {h_TH} {{
+  %x = {h_heads} parameter(0)
+  %t = {h_BShd} transpose({h_heads} %x), dimensions={{0,2,1,3}}
+  ROOT %r = {h_TH} reshape({h_BShd} %t)
+}}
+""")
+    comps.append(f"""%fused_bias_resid (p0: {h_TH}, p1: {h_H}, p2: {h_TH}) -> {h_TH} {{
+  %x = {h_TH} parameter(0)
+  %b = {h_H} parameter(1)
+  %res = {h_TH} parameter(2)
+  %bb = {h_TH} broadcast({h_H} %b), dimensions={{1}}
+  %y = {h_TH} add({h_TH} %x, {h_TH} %bb)
+  ROOT %yr = {h_TH} add({h_TH} %y, {h_TH} %res)
+}}
+""")
+    h_TF, h_F, f_TF = _shape("f16", [T, F]), _shape("f16", [F]), _shape("f32", [T, F])
+    act_lines, act_name = _activation_lines(cfg.act, "y32", f_TF)
+    comps.append(f"%fused_bias_act (p0: {h_TF}, p1: {h_F}) -> {h_TF} {{\n"
+                 f"  %x = {h_TF} parameter(0)\n  %b = {h_F} parameter(1)\n"
+                 f"  %bb = {h_TF} broadcast({h_F} %b), dimensions={{1}}\n"
+                 f"  %y = {h_TF} add({h_TF} %x, {h_TF} %bb)\n"
+                 f"  %y32 = {f_TF} convert({h_TF} %y)\n" + "\n".join(act_lines) + "\n"
+                 f"  ROOT %out = {h_TF} convert({f_TF} %{act_name})\n}}\n")
+
+    def gemm(name, a, a_shape, w, w_shape, out_shape, alpha=1.0, lhs_c=1, rhs_c=0, batch_dims=(), batch=1,
+             ls=0, rs=0):
+        entry.append(f"  %{name} = {_shape('f16', out_shape)} custom-call({_shape('f16', a_shape)} %{a}, "
+                     f"{_shape('f16', w_shape)} %{w}), custom_call_target=\"__cublas$gemm\", "
+                     f"backend_config={_gemm_config(alpha, lhs_c, rhs_c, batch_dims, batch, ls, rs)}")
+        return name
+
+    for l in range(cfg.layers):
+        p = f"layer{l}."
+        g1, b1 = const(p + "ln1.gamma", [H]), const(p + "ln1.beta", [H])
+        entry.append(f"  %fusion.ln1.{l} = {h_TH} fusion({h_TH} %{x}, {h_H} %{g1}, {h_H} %{b1}), kind=kInput, calls=%fused_ln")
+        heads = {}
+        for n in ("q", "k", "v"):
+            w = const(p + f"attn.{n}.w", [H, H])
+            b = const(p + f"attn.{n}.b", [H])
+            gname = gemm(f"gemm.{n}.{l}", f"fusion.ln1.{l}", [T, H], w, [H, H], [T, H], ls=T * H, rs=H * H)
+            entry.append(f"  %fusion.{n}.{l} = {h_heads} fusion({h_TH} %{gname}, {h_H} %{b}), kind=kLoop, "
+                         f"calls=%fused_bias_split")
+            heads[n] = f"fusion.{n}.{l}"
+        sc = gemm(f"gemm.scores.{l}", heads["q"], [B, NH, S, D], heads["k"], [B, NH, S, D], [B, NH, S, S],
+                  alpha=1.0 / (D ** 0.5), lhs_c=3, rhs_c=3, batch_dims=(0, 1), batch=B * NH, ls=S * D, rs=S * D)
+        entry.append(f"  %fusion.softmax.{l} = {h_sc} fusion({h_sc} %{sc}), kind=kInput, calls=%fused_softmax")
+        pv = gemm(f"gemm.pv.{l}", f"fusion.softmax.{l}", [B, NH, S, S], heads["v"], [B, NH, S, D], [B, NH, S, D],
+                  lhs_c=3, rhs_c=2, batch_dims=(0, 1), batch=B * NH, ls=S * S, rs=S * D)
+        entry.append(f"  %fusion.ctx.{l} = {h_TH} fusion({h_heads} %{pv}), kind=kLoop, calls=%fused_merge")
+        wo, bo = const(p + "attn.o.w", [H, H]), const(p + "attn.o.b", [H])
+        go = gemm(f"gemm.o.{l}", f"fusion.ctx.{l}", [T, H], wo, [H, H], [T, H], ls=T * H, rs=H * H)
+        entry.append(f"  %fusion.res1.{l} = {h_TH} fusion({h_TH} %{go}, {h_H} %{bo}, {h_TH} %{x}), kind=kLoop, "
+                     f"calls=%fused_bias_resid")
+        x = f"fusion.res1.{l}"
+        g2, b2 = const(p + "ln2.gamma", [H]), const(p + "ln2.beta", [H])
+        entry.append(f"  %fusion.ln2.{l} = {h_TH} fusion({h_TH} %{x}, {h_H} %{g2}, {h_H} %{b2}), kind=kInput, calls=%fused_ln")
+        w1, bb1 = const(p + "ffn.up.w", [H, F]), const(p + "ffn.up.b", [F])
+        gu = gemm(f"gemm.up.{l}", f"fusion.ln2.{l}", [T, H], w1, [H, F], [T, F], ls=T * H, rs=H * F)
+        entry.append(f"  %fusion.act.{l} = {h_TF} fusion({h_TF} %{gu}, {h_F} %{bb1}), kind=kLoop, calls=%fused_bias_act")
+        w2, bb2 = const(p + "ffn.down.w", [F, H]), const(p + "ffn.down.b", [H])
+        gd = gemm(f"gemm.down.{l}", f"fusion.act.{l}", [T, F], w2, [F, H], [T, H], ls=T * F, rs=F * H)
+        entry.append(f"  %fusion.res2.{l} = {h_TH} fusion({h_TH} %{gd}, {h_H} %{bb2}, {h_TH} %{x}), kind=kLoop, "
+                     f"calls=%fused_bias_resid")
+        x = f"fusion.res2.{l}"
+    gf, bf = const("ln.gamma", [H]), const("ln.beta", [H])
+    entry.append(f"  %fusion.lnf = {h_TH} fusion({h_TH} %{x}, {h_H} %{gf}, {h_H} %{bf}), kind=kInput, calls=%fused_ln")
+    return "fusion.lnf"
+
+
 def vit_hlo(cfg: EncoderConfig) -> tuple[str, dict[str, str]]:
     """HLO text of the pre-LN vision encoder (ViT) of `cfg`: NCHW f32 pixels, patch embedding as
     a ``__cudnn$convForward`` custom-call on the NHWC f16 image (window = stride = patch;
@@ -364,104 +479,84 @@ def vit_hlo(cfg: EncoderConfig) -> tuple[str, dict[str, str]]:
     entry.append(f"  %fusion.tokens = {h_TH} fusion({conv_s} %gte.patch, {h_H} %{bp}, {_shape('f16', [1, H])} %{cls}, "
                  f"{h_SH} %{pos}), kind=kLoop, calls=%fused_tokens")
 
-    comps.append(f"%fused_ln (p0: {h_TH}, p1: {h_H}, p2: {h_H}) -> {h_TH} {{\n"
-                 f"  %x = {h_TH} parameter(0)\n  %gamma = {h_H} parameter(1)\n  %beta = {h_H} parameter(2)\n"
-                 f"  %x32 = {f_TH} convert({h_TH} %x)\n" + "\n".join(_ln_body(T, H, cfg.eps, "x32")) + "\n}\n")
-    h_heads, h_BShd = _shape("f16", [B, NH, S, D]), _shape("f16", [B, S, NH, D])
-    comps.append(f"""%fused_bias_split (p0: {h_TH}, p1: {h_H}) -> {h_heads} {{
-  %x = {h_TH} parameter(0)
-  %b = {h_H} parameter(1)
-  %bb = {h_TH} broadcast({h_H} %b), dimensions={{1}}
-  %y = {h_TH} add({h_TH} %x, {h_TH} %bb)
-  %r = {h_BShd} reshape({h_TH} %y)
-  ROOT %t = {h_heads} transpose({h_BShd} %r), dimensions={{0,2,1,3}}
-}}
-""")
-    h_sc, f_sc, f_row = _shape("f16", [B, NH, S, S]), _shape("f32", [B, NH, S, S]), _shape("f32", [B, NH, S])
-    comps.append(f"""%fused_softmax (p0: {h_sc}) -> {h_sc} {{
-  %s = {h_sc} parameter(0)
-  %z = {f_sc} convert({h_sc} %s)
-  %ninf = f32[] constant(-inf)
-  %zmax = {f_row} reduce({f_sc} %z, f32[] %ninf), dimensions={{3}}, to_apply=%region_max
-  %zmax_b = {f_sc} broadcast({f_row} %zmax), dimensions={{0,1,2}}
-  %zc = {f_sc} subtract({f_sc} %z, {f_sc} %zmax_b)
-  %e = {f_sc} exponential({f_sc} %zc)
-  %zero = f32[] constant(0)
-  %esum = {f_row} reduce({f_sc} %e, f32[] %zero), dimensions={{3}}, to_apply=%region_add
-  %esum_b = {f_sc} broadcast({f_row} %esum), dimensions={{0,1,2}}
-  %p = {f_sc} divide({f_sc} %e, {f_sc} %esum_b)
-  ROOT %p16 = {h_sc} convert({f_sc} %p)
-}}
-""")
-    comps.append(f"""%fused_merge (p0: {h_heads}) -> {h_TH} {{
-  %x = {h_heads} parameter(0)
-  %t = {h_BShd} transpose({h_heads} %x), dimensions={{0,2,1,3}}
-  ROOT %r = {h_TH} reshape({h_BShd} %t)
-}}
-""")
-    comps.append(f"""%fused_bias_resid (p0: {h_TH}, p1: {h_H}, p2: {h_TH}) -> {h_TH} {{
-  %x = {h_TH} parameter(0)
-  %b = {h_H} parameter(1)
-  %res = {h_TH} parameter(2)
-  %bb = {h_TH} broadcast({h_H} %b), dimensions={{1}}
-  %y = {h_TH} add({h_TH} %x, {h_TH} %bb)
-  ROOT %yr = {h_TH} add({h_TH} %y, {h_TH} %res)
-}}
-""")
-    h_TF, h_F, f_TF = _shape("f16", [T, F]), _shape("f16", [F]), _shape("f32", [T, F])
-    act_lines, act_name = _activation_lines(cfg.act, "y32", f_TF)
-    comps.append(f"%fused_bias_act (p0: {h_TF}, p1: {h_F}) -> {h_TF} {{\n"
-                 f"  %x = {h_TF} parameter(0)\n  %b = {h_F} parameter(1)\n"
-                 f"  %bb = {h_TF} broadcast({h_F} %b), dimensions={{1}}\n"
-                 f"  %y = {h_TF} add({h_TF} %x, {h_TF} %bb)\n"
-                 f"  %y32 = {f_TF} convert({h_TF} %y)\n" + "\n".join(act_lines) + "\n"
-                 f"  ROOT %out = {h_TF} convert({f_TF} %{act_name})\n}}\n")
-
-    def gemm(name, a, a_shape, w, w_shape, out_shape, alpha=1.0, lhs_c=1, rhs_c=0, batch_dims=(), batch=1,
-             ls=0, rs=0):
-        entry.append(f"  %{name} = {_shape('f16', out_shape)} custom-call({_shape('f16', a_shape)} %{a}, "
-                     f"{_shape('f16', w_shape)} %{w}), custom_call_target=\"__cublas$gemm\", "
-                     f"backend_config={_gemm_config(alpha, lhs_c, rhs_c, batch_dims, batch, ls, rs)}")
-        return name
-
-    x = "fusion.tokens"
-    for l in range(cfg.layers):
-        p = f"layer{l}."
-        g1, b1 = const(p + "ln1.gamma", [H]), const(p + "ln1.beta", [H])
-        entry.append(f"  %fusion.ln1.{l} = {h_TH} fusion({h_TH} %{x}, {h_H} %{g1}, {h_H} %{b1}), kind=kInput, calls=%fused_ln")
-        heads = {}
-        for n in ("q", "k", "v"):
-            w = const(p + f"attn.{n}.w", [H, H])
-            b = const(p + f"attn.{n}.b", [H])
-            gname = gemm(f"gemm.{n}.{l}", f"fusion.ln1.{l}", [T, H], w, [H, H], [T, H], ls=T * H, rs=H * H)
-            entry.append(f"  %fusion.{n}.{l} = {h_heads} fusion({h_TH} %{gname}, {h_H} %{b}), kind=kLoop, "
-                         f"calls=%fused_bias_split")
-            heads[n] = f"fusion.{n}.{l}"
-        sc = gemm(f"gemm.scores.{l}", heads["q"], [B, NH, S, D], heads["k"], [B, NH, S, D], [B, NH, S, S],
-                  alpha=1.0 / (D ** 0.5), lhs_c=3, rhs_c=3, batch_dims=(0, 1), batch=B * NH, ls=S * D, rs=S * D)
-        entry.append(f"  %fusion.softmax.{l} = {h_sc} fusion({h_sc} %{sc}), kind=kInput, calls=%fused_softmax")
-        pv = gemm(f"gemm.pv.{l}", f"fusion.softmax.{l}", [B, NH, S, S], heads["v"], [B, NH, S, D], [B, NH, S, D],
-                  lhs_c=3, rhs_c=2, batch_dims=(0, 1), batch=B * NH, ls=S * S, rs=S * D)
-        entry.append(f"  %fusion.ctx.{l} = {h_TH} fusion({h_heads} %{pv}), kind=kLoop, calls=%fused_merge")
-        wo, bo = const(p + "attn.o.w", [H, H]), const(p + "attn.o.b", [H])
-        go = gemm(f"gemm.o.{l}", f"fusion.ctx.{l}", [T, H], wo, [H, H], [T, H], ls=T * H, rs=H * H)
-        entry.append(f"  %fusion.res1.{l} = {h_TH} fusion({h_TH} %{go}, {h_H} %{bo}, {h_TH} %{x}), kind=kLoop, "
-                     f"calls=%fused_bias_resid")
-        x = f"fusion.res1.{l}"
-        g2, b2 = const(p + "ln2.gamma", [H]), const(p + "ln2.beta", [H])
-        entry.append(f"  %fusion.ln2.{l} = {h_TH} fusion({h_TH} %{x}, {h_H} %{g2}, {h_H} %{b2}), kind=kInput, calls=%fused_ln")
-        w1, bb1 = const(p + "ffn.up.w", [H, F]), const(p + "ffn.up.b", [F])
-        gu = gemm(f"gemm.up.{l}", f"fusion.ln2.{l}", [T, H], w1, [H, F], [T, F], ls=T * H, rs=H * F)
-        entry.append(f"  %fusion.act.{l} = {h_TF} fusion({h_TF} %{gu}, {h_F} %{bb1}), kind=kLoop, calls=%fused_bias_act")
-        w2, bb2 = const(p + "ffn.down.w", [F, H]), const(p + "ffn.down.b", [H])
-        gd = gemm(f"gemm.down.{l}", f"fusion.act.{l}", [T, F], w2, [F, H], [T, H], ls=T * F, rs=F * H)
-        entry.append(f"  %fusion.res2.{l} = {h_TH} fusion({h_TH} %{gd}, {h_H} %{bb2}, {h_TH} %{x}), kind=kLoop, "
-                     f"calls=%fused_bias_resid")
-        x = f"fusion.res2.{l}"
-    gf, bf = const("ln.gamma", [H]), const("ln.beta", [H])
-    entry.append(f"  %fusion.lnf = {h_TH} fusion({h_TH} %{x}, {h_H} %{gf}, {h_H} %{bf}), kind=kInput, calls=%fused_ln")
+    lnf = _preln_blocks(cfg, comps, entry, const, "fusion.tokens", causal=False)
     out_shape = _shape("f16", [B, S, H])
-    entry.append(f"  ROOT %last_hidden_state = {out_shape} bitcast({h_TH} %fusion.lnf)")
+    entry.append(f"  ROOT %last_hidden_state = {out_shape} bitcast({h_TH} %{lnf})")
     text = (f"HloModule {cfg.name}, entry_computation_layout={{({px_s})->{out_shape}}}\n\n" + "\n".join(comps)
             + f"\nENTRY %{cfg.name}_main (pixel_values: {px_s}) -> {out_shape} {{\n" + "\n".join(entry) + "\n}\n")
+    return text, names
+
+
+def opt_hlo(cfg: EncoderConfig) -> tuple[str, dict[str, str]]:
+    """HLO text of the prefill of a pre-LN causal decoder (OPT) of `cfg`: token gather + learned
+    positions (table rows 2..2+S), causal pre-LN blocks with ReLU, final LayerNorm, LM head
+    against the transposed token table (tied weights) and the arg-max token per position as
+    XLA's (value, index) reduce. Outputs: (logits f16 [B*S, vocab], ids s32 [B*S]); the model of
+    examples/utils/save_model.py:55-64 returns the arg-max of the last position only."""
+    B, S, H, V = cfg.batch, cfg.seq, cfg.hidden, cfg.vocab
+    T = B * S
+    comps: list[str] = [_REGIONS]
+    entry: list[str] = []
+    names: dict[str, str] = {}
+
+    def const(name: str, dims) -> str:
+        names[name] = name
+        entry.append(f"  %{name} = {_shape('f16', dims)} constant({{...}})")
+        return name
+
+    i_BS = _shape("s32", [B, S])
+    h_TH, h_BSH, h_SH = _shape("f16", [T, H]), _shape("f16", [B, S, H]), _shape("f16", [S, H])
+    entry.append(f"  %input_ids = {i_BS} parameter(0)")
+    word = const("embeddings.word", [V, H])
+    pos = const("embeddings.position", [cfg.max_pos + 2, H])
+    w_s, p_s = _shape("f16", [V, H]), _shape("f16", [cfg.max_pos + 2, H])
+    comps.append(f"""%fused_embed (p0: {i_BS}, p1: {w_s}, p2: {p_s}) -> {h_TH} {{
+  %ids = {i_BS} parameter(0)
+  %word = {w_s} parameter(1)
+  %pos = {p_s} parameter(2)
+  %tok = {h_BSH} gather({w_s} %word, {i_BS} %ids), offset_dims={{2}}, collapsed_slice_dims={{0}}, start_index_map={{0}}, index_vector_dim=2, slice_sizes={{1,{H}}}
+  %pos_s = {h_SH} slice({p_s} %pos), slice={{[2:{2 + S}], [0:{H}]}}
+  %pos_b = {h_BSH} broadcast({h_SH} %pos_s), dimensions={{1,2}}
+  %sum = {h_BSH} add({h_BSH} %tok, {h_BSH} %pos_b)
+  ROOT %r = {h_TH} reshape({h_BSH} %sum)
+}}
+""")
+    entry.append(f"  %fusion.embed = {h_TH} fusion({i_BS} %input_ids, {w_s} %{word}, {p_s} %{pos}), kind=kLoop, "
+                 f"calls=%fused_embed")
+    lnf = _preln_blocks(cfg, comps, entry, const, "fusion.embed", causal=True)
+    h_TV, f_TV, i_TV = _shape("f16", [T, V]), _shape("f32", [T, V]), _shape("s32", [T, V])
+    f_T, i_T = _shape("f32", [T]), _shape("s32", [T])
+    entry.append(f"  %gemm.lm_head = {h_TV} custom-call({h_TH} %{lnf}, {w_s} %{word}), "
+                 f"custom_call_target=\"__cublas$gemm\", "
+                 f"backend_config={_gemm_config(1.0, 1, 1, (), 1, T * H, V * H)}")
+    comps.append(f"""%region_argmax (a_v: f32[], a_i: s32[], b_v: f32[], b_i: s32[]) -> (f32[], s32[]) {{
+  %a_v = f32[] parameter(0)
+  %a_i = s32[] parameter(1)
+  %b_v = f32[] parameter(2)
+  %b_i = s32[] parameter(3)
+  %gt = pred[] compare(f32[] %a_v, f32[] %b_v), direction=GT
+  %eq = pred[] compare(f32[] %a_v, f32[] %b_v), direction=EQ
+  %lt_i = pred[] compare(s32[] %a_i, s32[] %b_i), direction=LT
+  %tie = pred[] and(pred[] %eq, pred[] %lt_i)
+  %keep = pred[] or(pred[] %gt, pred[] %tie)
+  %v = f32[] select(pred[] %keep, f32[] %a_v, f32[] %b_v)
+  %i = s32[] select(pred[] %keep, s32[] %a_i, s32[] %b_i)
+  ROOT %t = (f32[], s32[]) tuple(f32[] %v, s32[] %i)
+}}
+
+%fused_argmax (p0: {h_TV}) -> {i_T} {{
+  %x = {h_TV} parameter(0)
+  %x32 = {f_TV} convert({h_TV} %x)
+  %idx = {i_TV} iota(), iota_dimension=1
+  %ninf = f32[] constant(-inf)
+  %zero = s32[] constant(0)
+  %r = ({f_T}, {i_T}) reduce({f_TV} %x32, {i_TV} %idx, f32[] %ninf, s32[] %zero), dimensions={{1}}, to_apply=%region_argmax
+  ROOT %ids = {i_T} get-tuple-element(({f_T}, {i_T}) %r), index=1
+}}
+""")
+    entry.append(f"  %fusion.argmax = {i_T} fusion({h_TV} %gemm.lm_head), kind=kInput, calls=%fused_argmax")
+    out_shape = f"({h_TV}, {i_T})"
+    entry.append(f"  ROOT %outputs = {out_shape} tuple({h_TV} %gemm.lm_head, {i_T} %fusion.argmax)")
+    text = (f"HloModule {cfg.name}, entry_computation_layout={{({i_BS})->{out_shape}}}\n\n" + "\n".join(comps)
+            + f"\nENTRY %{cfg.name}_main (input_ids: {i_BS}) -> {out_shape} {{\n" + "\n".join(entry) + "\n}\n")
     return text, names

@@ -84,7 +84,7 @@ def make_weights(cfg: EncoderConfig, seed: int = 1234, stress: bool = False) -> 
     copy and the fp32 CPU copy hold the same numbers.  Linear weights are [in, out]."""
     rng = np.random.default_rng(seed)
     out: dict[str, np.ndarray] = {}
-    shapes = vit_weight_shapes(cfg) if cfg.model == "vit" else bert_weight_shapes(cfg)
+    shapes = {"vit": vit_weight_shapes, "opt": opt_weight_shapes}.get(cfg.model, bert_weight_shapes)(cfg)
     for name, shape in shapes.items():
         if name.endswith(".gamma"):
             w = np.ones(shape, np.float32)
@@ -155,3 +155,40 @@ def make_vit_inputs(cfg: EncoderConfig, seed: int = 1234) -> dict[str, np.ndarra
     rng = np.random.default_rng(seed + 7919)
     px = rng.uniform(-1.0, 1.0, (cfg.batch, cfg.channels, cfg.image, cfg.image)).astype(np.float32)
     return {"pixel_values": px}
+
+
+def opt_1p3b(batch: int = 1, seq: int = 128) -> EncoderConfig:
+    """OPT-1.3B-shaped decoder prefill: 24 pre-LN layers, hidden 2048, 32 heads, FFN 8192 with
+    ReLU, causal attention, learned positions (offset 2), vocab 50272 with a tied LM head."""
+    return EncoderConfig(model="opt", layers=24, hidden=2048, heads=32, ffn=8192, vocab=50272,
+                         max_pos=2048, types=0, batch=batch, seq=seq, eps=1e-5, act="relu")
+
+
+def opt_tiny(batch: int = 1, seq: int = 16, layers: int = 1, hidden: int = 64, ffn: int = 256,
+             vocab: int = 128) -> EncoderConfig:
+    return EncoderConfig(model="opt", layers=layers, hidden=hidden, heads=hidden // 64, ffn=ffn, vocab=vocab,
+                         max_pos=max(64, seq), types=0, batch=batch, seq=seq, eps=1e-5, act="relu")
+
+
+def opt_weight_shapes(cfg: EncoderConfig) -> dict[str, tuple[int, ...]]:
+    h, f = cfg.hidden, cfg.ffn
+    shapes: dict[str, tuple[int, ...]] = {
+        "embeddings.word": (cfg.vocab, h),           # also the LM head (tied)
+        "embeddings.position": (cfg.max_pos + 2, h),  # learned positions, index = position + 2
+    }
+    for l in range(cfg.layers):
+        p = f"layer{l}."
+        shapes[p + "ln1.gamma"] = (h,)
+        shapes[p + "ln1.beta"] = (h,)
+        for n in ("q", "k", "v", "o"):
+            shapes[p + f"attn.{n}.w"] = (h, h)
+            shapes[p + f"attn.{n}.b"] = (h,)
+        shapes[p + "ln2.gamma"] = (h,)
+        shapes[p + "ln2.beta"] = (h,)
+        shapes[p + "ffn.up.w"] = (h, f)
+        shapes[p + "ffn.up.b"] = (f,)
+        shapes[p + "ffn.down.w"] = (f, h)
+        shapes[p + "ffn.down.b"] = (h,)
+    shapes["ln.gamma"] = (h,)
+    shapes["ln.beta"] = (h,)
+    return shapes

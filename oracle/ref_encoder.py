@@ -170,3 +170,23 @@ def vit_encoder(cfg, w, inputs, return_all=False):
         hidden.append(x)
     out = layer_norm(x, w["ln.gamma"], w["ln.beta"], cfg.eps).reshape(b * cfg.seq, h)
     return (out, hidden) if return_all else out
+
+
+def opt_decoder(cfg, w, inputs):
+    """fp32 prefill of the pre-LN causal decoder (OPT): token + learned position embeddings
+    (position index + 2, attention mask all ones), causal attention, ReLU FFN, final
+    LayerNorm, LM head tied to the token table. Returns (logits [B*S, vocab], argmax [B*S])."""
+    ids = inputs["input_ids"]
+    b, s_, h = cfg.batch, cfg.seq, cfg.hidden
+    x = (w["embeddings.word"][ids] + w["embeddings.position"][2:2 + s_][None]).astype(np.float32)
+    for l in range(cfg.layers):
+        p = f"layer{l}."
+        lin = lambda t, n: t @ w[p + n + ".w"] + w[p + n + ".b"]
+        y = layer_norm(x, w[p + "ln1.gamma"], w[p + "ln1.beta"], cfg.eps)
+        ctx = attention(lin(y, "attn.q"), lin(y, "attn.k"), lin(y, "attn.v"), None, cfg.heads, causal=True)
+        x = x + lin(ctx, "attn.o")
+        y = layer_norm(x, w[p + "ln2.gamma"], w[p + "ln2.beta"], cfg.eps)
+        x = x + lin(activation(lin(y, "ffn.up"), cfg.act), "ffn.down")
+    y = layer_norm(x, w["ln.gamma"], w["ln.beta"], cfg.eps).reshape(b * s_, h)
+    logits = (y @ w["embeddings.word"].T).astype(np.float32)
+    return logits, logits.argmax(-1).astype(np.int32)

@@ -91,6 +91,37 @@ def hf_vit_forward(cfg: EncoderConfig, w: dict, inputs: dict) -> np.ndarray:
     return out.reshape(cfg.batch * cfg.seq, cfg.hidden).numpy()
 
 
+def hf_opt_forward(cfg: EncoderConfig, w: dict, inputs: dict) -> np.ndarray:
+    from transformers import OPTConfig, OPTForCausalLM
+    hc = OPTConfig(vocab_size=cfg.vocab, hidden_size=cfg.hidden, ffn_dim=cfg.ffn, num_hidden_layers=cfg.layers,
+                   num_attention_heads=cfg.heads, max_position_embeddings=cfg.max_pos,
+                   word_embed_proj_dim=cfg.hidden, do_layer_norm_before=True, dropout=0.0,
+                   activation_function="relu", layer_norm_elementwise_affine=True)
+    model = OPTForCausalLM(hc).eval()
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a))
+    sd = {"model.decoder.embed_tokens.weight": t(w["embeddings.word"]),
+          "model.decoder.embed_positions.weight": t(w["embeddings.position"]),
+          "model.decoder.final_layer_norm.weight": t(w["ln.gamma"]),
+          "model.decoder.final_layer_norm.bias": t(w["ln.beta"]),
+          "lm_head.weight": t(w["embeddings.word"])}
+    for l in range(cfg.layers):
+        p, q = f"layer{l}.", f"model.decoder.layers.{l}."
+        for ours, theirs in (("attn.q", "self_attn.q_proj"), ("attn.k", "self_attn.k_proj"),
+                             ("attn.v", "self_attn.v_proj"), ("attn.o", "self_attn.out_proj"),
+                             ("ffn.up", "fc1"), ("ffn.down", "fc2")):
+            sd[q + theirs + ".weight"] = t(w[p + ours + ".w"].T)
+            sd[q + theirs + ".bias"] = t(w[p + ours + ".b"])
+        sd[q + "self_attn_layer_norm.weight"] = t(w[p + "ln1.gamma"])
+        sd[q + "self_attn_layer_norm.bias"] = t(w[p + "ln1.beta"])
+        sd[q + "final_layer_norm.weight"] = t(w[p + "ln2.gamma"])
+        sd[q + "final_layer_norm.bias"] = t(w[p + "ln2.beta"])
+    missing, unexpected = model.load_state_dict(sd, strict=False)
+    assert not missing and not unexpected, (missing, unexpected)
+    with torch.no_grad():
+        out = model(input_ids=torch.from_numpy(inputs["input_ids"]).long()).logits
+    return out.reshape(cfg.batch * cfg.seq, cfg.vocab).numpy()
+
+
 CASES = {
     # name: (config, weight seed, stress, pad_fraction)
     "bert_tiny_b1_s16": (EncoderConfig(layers=2, hidden=64, heads=1, ffn=256, vocab=100, max_pos=64,
@@ -100,6 +131,8 @@ CASES = {
     "vit_tiny_b2_img48": (EncoderConfig(model="vit", layers=2, hidden=128, heads=2, ffn=256, batch=2, seq=10,
                                         image=48, patch=16, channels=3, max_pos=10, vocab=0, types=0),
                           13, True, 0.0),
+    "opt_tiny_b2_s24": (EncoderConfig(model="opt", layers=2, hidden=128, heads=2, ffn=256, vocab=160, max_pos=64,
+                                      types=0, batch=2, seq=24, eps=1e-5, act="relu"), 14, True, 0.0),
 }
 
 
@@ -109,6 +142,9 @@ def main():
         if cfg.model == "vit":
             inp = make_vit_inputs(cfg, seed)
             out = hf_vit_forward(cfg, w, inp)
+        elif cfg.model == "opt":
+            inp = make_inputs(cfg, seed)
+            out = hf_opt_forward(cfg, w, inp)  # logits; stored under the common key
         else:
             inp = make_inputs(cfg, seed, pad_fraction=pad)
             out = hf_bert_forward(cfg, w, inp)

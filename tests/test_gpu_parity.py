@@ -3,8 +3,8 @@ import numpy as np
 import pytest
 
 from mononn_b200 import (bert_base, bert_tiny, compile_encoder, compile_hlo, make_inputs, make_vit_inputs,
-                         make_weights, vit_base, vit_tiny)
-from mononn_b200.hlo_builder import bert_hlo, vit_hlo
+                         make_weights, opt_tiny, vit_base, vit_tiny)
+from mononn_b200.hlo_builder import bert_hlo, opt_hlo, vit_hlo
 from mononn_b200.models import EncoderConfig
 from oracle import ref_encoder as R
 from tests.helpers import assert_parity, golden_cases, load_golden, reference_fixture_inputs
@@ -33,10 +33,13 @@ def build(cfg, w, frontend):
 def test_golden_vectors(name, frontend):
     cfg, seed, stress, pad = golden_cases()[name]
     w = make_weights(cfg, seed, stress=stress)
+    if cfg.model != "bert" and frontend == "builder":
+        pytest.skip("the config builder covers the BERT family only")
     if cfg.model == "vit":
-        if frontend == "builder":
-            pytest.skip("the config builder covers the BERT family only")
         got = run_vit(cfg, w, make_vit_inputs(cfg, seed))
+    elif cfg.model == "opt":
+        got, ids = run_opt(cfg, w, make_inputs(cfg, seed))
+        check_argmax(got, ids, load_golden(name)["last_hidden_state"])
     else:
         inp = make_inputs(cfg, seed, pad_fraction=pad)
         mod = build(cfg, w, frontend)
@@ -182,3 +185,56 @@ def test_layernorm_output_statistics(base):
     g, b = w[f"layer{cfg.layers - 1}.ffn.ln.gamma"], w[f"layer{cfg.layers - 1}.ffn.ln.beta"]
     z = (got - b) / g
     assert np.abs(z.mean(1)).max() < 2e-2 and np.abs(z.var(1) - 1).max() < 5e-2
+
+
+def run_opt(cfg, w, inp):
+    """(logits f32 [tokens, vocab], arg-max ids s32 [tokens]) of the decoder prefill."""
+    text, names = opt_hlo(cfg)
+    mod = compile_hlo(text, barrier_timeout_us=2000000)
+    mod.set_weights({names[k]: v for k, v in w.items()})
+    outs = mod.run([inp["input_ids"]])
+    mod.close()
+    logits = outs[0][: cfg.tokens * cfg.vocab].reshape(cfg.tokens, cfg.vocab)
+    ids = outs[1].view(np.int32)[: cfg.tokens]
+    return logits.astype(np.float32), ids
+
+
+def check_argmax(logits, ids, ref_logits):
+    """Token ids are bit-exact: equal to the first maximum of the device's own f16 logits on
+    every row, and equal to the fp32 oracle's arg-max wherever the oracle's top-2 margin is
+    larger than the f16 tolerance of the logits (a closer race is decided by rounding)."""
+    assert np.array_equal(ids, logits.argmax(-1).astype(np.int32))
+    top2 = np.sort(ref_logits, axis=-1)[:, -2:]
+    clear = (top2[:, 1] - top2[:, 0]) > 2 * 2e-2
+    assert clear.any()
+    assert np.array_equal(ids[clear], ref_logits.argmax(-1)[clear].astype(np.int32))
+
+
+@pytest.mark.parametrize("cfg", [
+    opt_tiny(),                                                     # one layer, one head
+    opt_tiny(batch=3, seq=40, layers=2, hidden=128, vocab=1008),    # ragged rows, vocab not a tile multiple
+    opt_tiny(batch=2, seq=128, layers=1, hidden=256, ffn=1024, vocab=4096),
+    opt_tiny(batch=1, seq=200, layers=1, hidden=128, vocab=512),    # causal mask across two key chunks
+], ids=lambda c: f"b{c.batch}s{c.seq}h{c.hidden}v{c.vocab}")
+def test_opt_shapes_against_oracle(cfg):
+    """Pre-LN causal decoder: embedding rows (position offset 2) into the f32 stream, causal
+    attention, LM head against the transposed token table, arg-max per position."""
+    w = make_weights(cfg, 77, stress=True)
+    inp = make_inputs(cfg, 77)
+    logits, ids = run_opt(cfg, w, inp)
+    ref, _ = R.opt_decoder(cfg, w, inp)
+    assert_parity(logits, ref, "OPT shape case")
+    check_argmax(logits, ids, ref)
+
+
+def test_opt_wide_reduced_depth():
+    """OPT-1.3B's widths (hidden 2048, 32 heads, FFN 8192, vocab 50272) on two layers: the
+    three-pass LayerNorm for 2048 columns, the 50272-column LM head and its arg-max."""
+    cfg = EncoderConfig(model="opt", layers=2, hidden=2048, heads=32, ffn=8192, vocab=50272, max_pos=2048,
+                        types=0, batch=1, seq=128, eps=1e-5, act="relu")
+    w = make_weights(cfg, 78)
+    inp = make_inputs(cfg, 78)
+    logits, ids = run_opt(cfg, w, inp)
+    ref, _ = R.opt_decoder(cfg, w, inp)
+    assert_parity(logits, ref, "OPT-1.3B widths, 2 layers")
+    check_argmax(logits, ids, ref)

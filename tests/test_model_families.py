@@ -1,0 +1,93 @@
+"""Device-free lowering of the pre-LN families (vision encoder, causal decoder): what the
+recogniser finds in their HLO and what the scheduler plans for it."""
+import pytest
+
+from mononn_b200 import capi
+from mononn_b200.hlo_builder import opt_hlo, vit_hlo
+from mononn_b200.models import opt_1p3b, opt_tiny, vit_tiny
+from mononn_b200.module import describe
+
+F_CAUSAL, F_SRC_F32, F_NO_NORM = 1 << 3, 1 << 5, 1 << 9
+
+
+def plan_of(text):
+    return describe("hlo", text)["plan"]
+
+
+def ops_of(plan, kind):
+    return [o for st in plan["stages"] for o in st["ops"] if o["kind"] == kind]
+
+
+def test_decoder_structure(lib_built):
+    cfg = opt_tiny(batch=2, seq=24, layers=2, hidden=128, vocab=160)
+    plan = plan_of(opt_hlo(cfg)[0])
+    # embed | per layer: LN, QKV, attention, out-proj, LN, up, down | final LN, LM head, arg-max
+    assert len(plan["stages"]) == 1 + 7 * cfg.layers + 3
+    embed = ops_of(plan, "embed")
+    assert len(embed) == 1 and embed[0]["flags"] & F_NO_NORM          # the sum is the residual stream
+    assert embed[0]["p"][0]["space"] == "none"                          # no f16 copy of it is written
+    att = ops_of(plan, "attention")
+    assert len(att) == cfg.layers and all(o["flags"] & F_CAUSAL for o in att)
+    assert all(o["flags"] & F_SRC_F32 for o in ops_of(plan, "layernorm"))
+    assert len(ops_of(plan, "argmax")) == 1 and ops_of(plan, "argmax")[0]["n_items"] == cfg.tokens
+    # residual updates accumulate into the stream: out-proj and FFN-down write f32 reductions
+    red = [o for o in ops_of(plan, "gemm") if o["out_mode"] == 2]
+    assert len(red) == 2 * cfg.layers
+    assert len({(o["p"][0]["space"], o["p"][0]["offset"]) for o in red}) == 1
+
+
+def test_decoder_arguments_and_tied_head(lib_built):
+    cfg = opt_tiny(batch=2, seq=24, layers=1, hidden=128, vocab=160)
+    plan = plan_of(opt_hlo(cfg)[0])
+    args = plan["args"]
+    assert [(a["name"], a["kind"]) for a in args] == [("input_ids", 0), ("gemm.lm_head", 1), ("fusion.argmax", 1),
+                                                     ("temp_buffer", 2)]
+    assert args[1]["bytes"] == cfg.tokens * cfg.vocab * 2 and args[2]["bytes"] == cfg.tokens * 4
+    # the token table is bound twice: raw rows for the gather, packed tiles for the LM head
+    kinds = sorted(c["kind"] for c in plan["constants"] if c["name"] == "embeddings.word")
+    assert len(kinds) == 2 and kinds[0] != kinds[1]
+    head = [o for o in ops_of(plan, "gemm") if o["name"] == "gemm_lm_head"][0]
+    assert (head["N"], head["K"]) == (cfg.vocab, cfg.hidden)
+
+
+def test_position_rows_start_at_the_slice_offset(lib_built):
+    cfg = opt_tiny(seq=16)
+    text, _ = opt_hlo(cfg)
+    # a slice that would run past the table is refused rather than read out of bounds
+    bad = text.replace(f"slice={{[2:{2 + cfg.seq}]", f"slice={{[{cfg.max_pos}:{cfg.max_pos + cfg.seq}]")
+    lib = capi.lib()
+    import ctypes as C
+    out = C.c_void_p()
+    rc = lib.mononn_describe(b"hlo", bad.encode(), len(bad.encode()), None, 148, C.byref(out))
+    assert rc != 0
+
+
+def test_non_causal_softmax_is_not_flagged_causal(lib_built):
+    plan = plan_of(vit_hlo(vit_tiny())[0])
+    assert all(not (o["flags"] & F_CAUSAL) for o in ops_of(plan, "attention"))
+    assert len(ops_of(plan, "patchify")) == 1 and len(ops_of(plan, "assemble")) == 1
+
+
+def test_argmax_with_another_tie_rule_is_rejected(lib_built):
+    text, _ = opt_hlo(opt_tiny())
+    # prefer the later index on ties: not the arg-max the kernel computes
+    bad = text.replace("%lt_i = pred[] compare(s32[] %a_i, s32[] %b_i), direction=LT",
+                       "%lt_i = pred[] compare(s32[] %a_i, s32[] %b_i), direction=GT")
+    assert bad != text
+    with pytest.raises(capi.MononnError) as e:
+        plan_of(bad)
+    assert "arg-max" in str(e.value)
+
+
+def test_full_size_decoder_cost(lib_built):
+    """OPT-1.3B prefill b1/s128: every weight once (token table: rows gathered + the whole
+    table for the tied head), 338.8 GFLOP."""
+    cfg = opt_1p3b()
+    plan = plan_of(opt_hlo(cfg)[0])
+    h, f, v = cfg.hidden, cfg.ffn, cfg.vocab
+    per_layer = 4 * h * h + 2 * h * f
+    flops = 2.0 * cfg.tokens * (cfg.layers * per_layer + h * v) + cfg.layers * 4.0 * cfg.seq * cfg.seq * h
+    assert abs(plan["algorithmic_flops"] - flops) / flops < 1e-6
+    weights = 2.0 * (cfg.layers * (per_layer + 9 * h + f) + 2 * h + h * v)
+    assert abs(plan["algorithmic_bytes"] - weights) / weights < 0.01
+    assert len(plan["stages"]) == 1 + 7 * cfg.layers + 3

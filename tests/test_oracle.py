@@ -14,6 +14,9 @@ def test_oracle_matches_golden_vectors(name):
     w = make_weights(cfg, seed, stress=stress)
     if cfg.model == "vit":
         out = R.vit_encoder(cfg, w, make_vit_inputs(cfg, seed))
+    elif cfg.model == "opt":
+        out, ids = R.opt_decoder(cfg, w, make_inputs(cfg, seed))
+        assert np.array_equal(ids, g["last_hidden_state"].argmax(-1))  # the stored array holds the logits
     else:
         out = R.bert_encoder(cfg, w, make_inputs(cfg, seed, pad_fraction=pad))
     ref = g["last_hidden_state"]
@@ -42,6 +45,19 @@ def test_mask_changes_only_through_masked_keys():
     other = R.bert_encoder(cfg, w, inp2)
     keep = inp["attention_mask"].reshape(-1) == 1
     assert np.abs(base[keep] - other[keep]).max() < 1e-5
+
+
+def test_causal_decoder_ignores_later_tokens():
+    from mononn_b200.models import opt_tiny
+    cfg = opt_tiny(batch=1, seq=12)
+    w = make_weights(cfg, 8, stress=True)
+    inp = make_inputs(cfg, 8)
+    base, _ = R.opt_decoder(cfg, w, inp)
+    inp2 = {k: v.copy() for k, v in inp.items()}
+    inp2["input_ids"][0, 7] = (inp2["input_ids"][0, 7] + 1) % cfg.vocab
+    other, _ = R.opt_decoder(cfg, w, inp2)
+    assert np.abs(base[:7] - other[:7]).max() == 0.0   # positions before the change are untouched
+    assert np.abs(base[7:] - other[7:]).max() > 1e-4
 
 
 def test_layer_norm_eps_and_biased_variance():
