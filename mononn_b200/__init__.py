@@ -3,5 +3,6 @@ one persistent kernel launch per inference out.  The work is done by libmononn_b
 (mononn_b200/csrc); this package is the thin host-side mirror of its C ABI."""
 from .capi import MononnError, Options  # noqa: F401
 from .module import Module, compile_encoder, compile_hlo  # noqa: F401
-from .models import (EncoderConfig, bert_base, bert_tiny, make_inputs, make_vit_inputs,  # noqa: F401
-                     make_weights, opt_1p3b, opt_tiny, vit_base, vit_tiny)
+from .models import (ClipConfig, EncoderConfig, bert_base, bert_tiny, clip_b32, clip_tiny,  # noqa: F401
+                     make_clip_inputs, make_inputs, make_vit_inputs, make_weights, opt_1p3b, opt_tiny,
+                     vit_base, vit_tiny)

@@ -264,6 +264,7 @@ class Lowering {
     if (lb.empty() && rb.empty()) {
       // ---- dense layer: activation [M,K] x constant weight
       if (a.kind != Val::ACT) return unsupported(ins, "left operand is not a materialised activation");
+      if (b.kind == Val::ACT) return lower_pairdot(idx, alpha, lc[0], rc_[0]);
       if (b.kind != Val::CONST) return unsupported(ins, "right operand is not a constant weight");
       if (lhs.shape.dims.size() != 2 || rhs.shape.dims.size() != 2 || lc[0] != 1)
         return unsupported(ins, "left operand must be [M,K] contracting its last dimension");
@@ -355,6 +356,7 @@ class Lowering {
     }
     bool has_concat = false;
     for (const HloInstr& i : c->instrs) has_concat = has_concat || i.opcode == "concatenate";
+    if (has_gather && has_reduce) return lower_rowsel(idx, *c);
     if (has_gather) return lower_embed_sum(idx, *c);
     if (has_reduce && ins.shape.dtype == "s32" && ins.operands.size() == 1) return lower_argmax(idx, *c);
     if (has_concat) {  // token assembly: the result has more rows than the patch GEMM
@@ -373,8 +375,19 @@ class Lowering {
     if (main_k < 0 && ins.operands.size() == 1 && vals_[ins.operands[0]].kind == Val::ARG &&
         e_.instrs[ins.operands[0]].shape.dims.size() == 4)
       return lower_image_layout(idx, *c);
+    if (main_k < 0 && has_reduce) {
+      // a row-wise reduction over selected rows of a larger tensor (class-token LayerNorm)
+      for (size_t k = 0; k < ins.operands.size(); ++k) {
+        const Val& v = vals_[ins.operands[k]];
+        const int64_t ne = e_.instrs[ins.operands[k]].shape.elements();
+        if ((v.kind == Val::ACT || v.kind == Val::STREAM) && ne > ins.shape.elements() && ne % ins.shape.elements() == 0)
+          return lower_layernorm(idx, *c, static_cast<int>(k));
+      }
+    }
     if (main_k < 0) return unsupported(ins, "fusion without a tensor operand of the result's size");
     const Val& mv = vals_[ins.operands[main_k]];
+    if (has_reduce && ins.operands.size() == 1 && (mv.kind == Val::GEMM || mv.kind == Val::ACT))
+      return lower_l2norm(idx, *c);
     switch (mv.kind) {
       case Val::GEMM:
         return has_reduce ? lower_layernorm(idx, *c, main_k) : lower_epilogue(idx, *c, main_k);
@@ -457,6 +470,41 @@ class Lowering {
     }
     if (!ok) return unsupported(ins, "fused computation " + c.name + " matches no epilogue form act(x + bias) + residual");
     if (bias_k >= 0) gop.bias = const_tensor(vals_[ins.operands[bias_k]].instr, 1, N);
+    if (resid_k >= 0 && vals_[ins.operands[resid_k]].kind == Val::ACT && found == ACT_NONE && !split) {
+      // x + (A W + b) where x is a LayerNorm output that starts a pre-LN residual stream (the
+      // LayerNorm before the blocks of a CLIP vision tower): that LayerNorm also writes an f32
+      // copy, and from here on the stream is the accumulator the GEMMs add into.
+      Val& rv = vals_[ins.operands[resid_k]];
+      if (rv.op >= 0 && g_.ops[rv.op].kind == OP_LAYERNORM && g_.ops[rv.op].out == rv.tensor &&
+          g_.ops[rv.op].out2 < 0 && g_.ops[rv.op].rows == M && g_.ops[rv.op].cols == N) {
+        FTensor st;
+        st.name = g_.ops[rv.op].name + "_stream";
+        st.kind = TKind::AccF32;
+        st.rows = M;
+        st.cols = N;
+        st.ld = N;
+        st.elem_bytes = 4;
+        g_.ops[rv.op].out2 = g_.add_tensor(st);
+        Val sv;
+        sv.kind = Val::STREAM;
+        sv.instr = rv.instr;
+        sv.tensor = g_.ops[rv.op].out2;
+        sv.op = rv.op;
+        sv.rows = M;
+        sv.cols = N;
+        stream_of_[rv.tensor] = sv;
+      }
+    }
+    if (resid_k >= 0 && vals_[ins.operands[resid_k]].kind == Val::ACT &&
+        stream_of_.count(vals_[ins.operands[resid_k]].tensor) && found == ACT_NONE && !split) {
+      Val sv = stream_of_[vals_[ins.operands[resid_k]].tensor];
+      gop.act = ACT_NONE;
+      gop.out = sv.tensor;
+      sv.instr = idx;
+      sv.op = gv.op;
+      vals_[idx] = sv;
+      return MONONN_OK;
+    }
     if (resid_k >= 0 && vals_[ins.operands[resid_k]].kind == Val::STREAM) {
       // pre-LN residual: x <- x + (A W + b). The stream is an f32 accumulator the GEMM adds
       // its (split-K) partial sums into; nothing is copied.
@@ -507,9 +555,25 @@ class Lowering {
       else if (v.kind == Val::ACT && v.rows == rows && v.cols == cols && resid_k < 0) resid_k = static_cast<int>(k);
       else return unsupported(ins, "operand %" + oi.name + " has no role in a LayerNorm fusion");
     }
-    if (mv.kind == Val::STREAM && (mv.rows != rows || mv.cols != cols)) {
-      return unsupported(ins, "LayerNorm shape differs from the residual stream");
+    // Row selection: the result has one row per `stride` source rows, taken at offset `off`
+    // (a slice inside the fusion: the class-token row of every image).
+    uint32_t stride = 1;
+    std::vector<uint32_t> off_cands{0};
+    if ((mv.kind == Val::STREAM || mv.kind == Val::ACT) && (mv.rows != rows || mv.cols != cols)) {
+      if (mv.cols != cols || rows == 0 || mv.rows % rows != 0 || resid_k >= 0)
+        return unsupported(ins, "LayerNorm shape differs from its source");
+      stride = mv.rows / rows;
+      for (const HloInstr& i : c.instrs)
+        if (i.opcode == "slice") {
+          const std::string sl = i.attr("slice");
+          for (size_t p = sl.find('['); p != std::string::npos; p = sl.find('[', p + 1)) {
+            const uint32_t st = static_cast<uint32_t>(std::strtoul(sl.c_str() + p + 1, nullptr, 10));
+            if (st < stride && std::find(off_cands.begin(), off_cands.end(), st) == off_cands.end())
+              off_cands.push_back(st);
+          }
+        }
     }
+    uint32_t off_found = 0;
     if (vec_k.size() < 2 || vec_k.size() > 3) return unsupported(ins, "expected scale, shift and at most one bias vector");
     std::vector<float> eps_cands;
     for (const HloInstr& i : c.instrs)
@@ -528,12 +592,13 @@ class Lowering {
     if (rc) return rc;
     // closed form for a given assignment of the vectors to (bias?, gamma, beta) and epsilon
     std::vector<float> want(static_cast<size_t>(rows) * cols), sum(cols);
+    uint32_t off = 0;
     auto max_error = [&](int bk, int gk, int ek, float eps, uint32_t n_rows) {
       float worst = 0.f;
       for (uint32_t r = 0; r < n_rows; ++r) {
         double mean = 0;
         for (uint32_t j = 0; j < cols; ++j) {
-          float y = ps[main_k].v[static_cast<size_t>(r) * cols + j];
+          float y = ps[main_k].v[(static_cast<size_t>(r) * stride + off) * cols + j];
           if (bk >= 0) y += ps[bk].v[j];
           if (resid_k >= 0) y += ps[resid_k].v[static_cast<size_t>(r) * cols + j];
           sum[j] = y;
@@ -558,15 +623,19 @@ class Lowering {
     do {
       const int bk = perm.size() == 3 ? perm[0] : -1;
       const int gk = perm[perm.size() - 2], ek = perm[perm.size() - 1];
-      for (float eps : eps_cands) {
-        const float e = max_error(bk, gk, ek, eps, std::min<uint32_t>(rows, 4));
-        if (e < best) {
-          best = e;
-          bias_k = bk; gamma_k = gk; beta_k = ek;
-          eps_found = eps;
+      for (float eps : eps_cands)
+        for (uint32_t oc : off_cands) {
+          off = oc;
+          const float e = max_error(bk, gk, ek, eps, std::min<uint32_t>(rows, 4));
+          if (e < best) {
+            best = e;
+            bias_k = bk; gamma_k = gk; beta_k = ek;
+            eps_found = eps;
+            off_found = oc;
+          }
         }
-      }
     } while (std::next_permutation(perm.begin(), perm.end()));
+    off = off_found;
     const bool ok = best < 1e-3f && max_error(bias_k, gamma_k, beta_k, eps_found, rows) < 1e-3f;
     if (!ok) return unsupported(ins, "fused computation " + c.name + " matches no LayerNorm(x + bias + residual) form");
 
@@ -610,6 +679,10 @@ class Lowering {
       if (bias_k >= 0) return unsupported(ins, "bias vector on a LayerNorm that does not follow a GEMM");
       n.src = mv.tensor;  // f16 activation, or the f32 residual stream (read, not cleared)
       if (resid_k >= 0) n.resid = vals_[ins.operands[resid_k]].tensor;
+      if (stride > 1) {
+        n.k_col = stride;
+        n.q_col = off_found;
+      }
     }
     n.out = act_tensor(n.name, rows, cols);
     g_.ops.push_back(n);
@@ -850,7 +923,10 @@ class Lowering {
       if (oi.shape.elements() == static_cast<int64_t>(S) * O && pos_k < 0) pos_k = static_cast<int>(k);
       else small.push_back(static_cast<int>(k));
     }
-    if (pos_k < 0 || small.size() != 2) return unsupported(ins, "expected bias, prefix rows and position rows");
+    if (pos_k < 0 || small.empty() || small.size() > 2)
+      return unsupported(ins, "expected prefix rows, position rows and at most one bias vector");
+    const bool with_bias = small.size() == 2;
+    if (!with_bias) small.push_back(-1);
     Rng rng;
     std::vector<HTensor> ps = probe_inputs(c, [&](size_t, HTensor& t) {
       for (float& x : t.v) x = rng.uni(-1.f, 1.f);
@@ -859,9 +935,10 @@ class Lowering {
     int rc = probe(c, ps, &got);
     if (rc) return rc;
     int bias_k = -1, cls_k = -1;
-    for (int trial = 0; trial < 2 && bias_k < 0; ++trial) {
+    for (int trial = 0; trial < 2; ++trial) {
       const int bk = small[trial], ck = small[1 - trial];
-      if (e_.instrs[ins.operands[bk]].shape.elements() != O ||
+      if (ck < 0 || (with_bias && bk < 0)) continue;
+      if ((bk >= 0 && e_.instrs[ins.operands[bk]].shape.elements() != O) ||
           e_.instrs[ins.operands[ck]].shape.elements() != static_cast<int64_t>(prefix) * O)
         continue;
       std::vector<float> want(static_cast<size_t>(T) * O);
@@ -870,15 +947,16 @@ class Lowering {
           for (uint32_t j = 0; j < O; ++j) {
             float y = ps[pos_k].v[static_cast<size_t>(t) * O + j];
             if (t < prefix) y += ps[ck].v[static_cast<size_t>(t) * O + j];
-            else y += ps[main_k].v[(static_cast<size_t>(b) * P + (t - prefix)) * O + j] + ps[bk].v[j];
+            else y += ps[main_k].v[(static_cast<size_t>(b) * P + (t - prefix)) * O + j] + (bk >= 0 ? ps[bk].v[j] : 0.f);
             want[(static_cast<size_t>(b) * S + t) * O + j] = y;
           }
       if (all_close(got.v, want, 1e-5f, 1e-5f)) {
         bias_k = bk;
         cls_k = ck;
+        break;
       }
     }
-    if (bias_k < 0)
+    if (cls_k < 0)
       return unsupported(ins, "fused computation " + c.name + " is not concat(prefix, patches + bias) + positions");
     gop.out = act_tensor(gop.name + "_out", M, O);
     FTensor st;
@@ -892,7 +970,7 @@ class Lowering {
     a.kind = OP_ASSEMBLE;
     a.name = canonical_node_name(ins.name);
     a.a = gop.out;
-    a.bias = const_tensor(vals_[ins.operands[bias_k]].instr, 1, O);
+    if (bias_k >= 0) a.bias = const_tensor(vals_[ins.operands[bias_k]].instr, 1, O);
     a.word = const_tensor(vals_[ins.operands[cls_k]].instr, prefix, O);
     a.pos = const_tensor(vals_[ins.operands[pos_k]].instr, S, O);
     a.out2 = g_.add_tensor(st);
@@ -1143,6 +1221,153 @@ class Lowering {
     return MONONN_OK;
   }
 
+  // x / sqrt(sum x^2) over the last dimension (embedding normalisation of a dual encoder)
+  int lower_l2norm(int idx, const HloComputation& c) {
+    const HloInstr& ins = e_.instrs[idx];
+    const Val mv = vals_[ins.operands[0]];
+    if (ins.shape.dims.empty()) return unsupported(ins, "scalar result");
+    const uint32_t cols = static_cast<uint32_t>(ins.shape.dims.back());
+    const uint32_t rows = static_cast<uint32_t>(ins.shape.elements() / cols);
+    if (mv.rows != rows || mv.cols != cols) return unsupported(ins, "shape differs from the operand");
+    Rng rng;
+    std::vector<HTensor> ps = probe_inputs(c, [&](size_t, HTensor& t) {
+      for (float& x : t.v) x = rng.uni(-1.f, 1.f);
+    });
+    HTensor got;
+    int rc = probe(c, ps, &got);
+    if (rc) return rc;
+    std::vector<float> want(got.v.size());
+    for (uint32_t r = 0; r < rows; ++r) {
+      double sq = 0;
+      for (uint32_t j = 0; j < cols; ++j) sq += static_cast<double>(ps[0].v[static_cast<size_t>(r) * cols + j]) * ps[0].v[static_cast<size_t>(r) * cols + j];
+      const double inv = 1.0 / std::sqrt(sq);
+      for (uint32_t j = 0; j < cols; ++j)
+        want[static_cast<size_t>(r) * cols + j] = static_cast<float>(ps[0].v[static_cast<size_t>(r) * cols + j] * inv);
+    }
+    if (!all_close(got.v, want, 1e-5f, 1e-4f))
+      return unsupported(ins, "fused computation " + c.name + " is not x / sqrt(sum x^2) over the last dimension");
+    FOp n;
+    n.kind = OP_LAYERNORM;
+    n.name = canonical_node_name(ins.name);
+    n.rows = rows;
+    n.cols = cols;
+    n.flags = F_L2NORM;
+    if (mv.kind == Val::GEMM) {
+      if (uses_[mv.instr] != 1) return unsupported(ins, "GEMM result with more than one consumer");
+      FOp& gop = g_.ops[mv.op];
+      FTensor acc;
+      acc.name = gop.name + "_sum";
+      acc.kind = TKind::AccF32;
+      acc.rows = rows;
+      acc.cols = cols;
+      acc.ld = cols;
+      acc.elem_bytes = 4;
+      gop.out = g_.add_tensor(acc);
+      n.src = gop.out;
+      n.flags |= F_ZERO_SRC;
+    } else {
+      n.src = mv.tensor;
+    }
+    n.out = act_tensor(n.name, rows, cols);
+    g_.ops.push_back(n);
+    Val v;
+    v.kind = Val::ACT;
+    v.instr = idx;
+    v.tensor = n.out;
+    v.op = static_cast<int>(g_.ops.size()) - 1;
+    v.rows = rows;
+    v.cols = cols;
+    vals_[idx] = v;
+    return MONONN_OK;
+  }
+
+  // out[b, :] = x[b * S + argmax(ids[b, :]), :]: pooling at the largest token id
+  int lower_rowsel(int idx, const HloComputation& c) {
+    const HloInstr& ins = e_.instrs[idx];
+    int x_k = -1, ids_k = -1;
+    for (size_t k = 0; k < ins.operands.size(); ++k) {
+      const Val& v = vals_[ins.operands[k]];
+      const HloInstr& oi = e_.instrs[ins.operands[k]];
+      if (v.kind == Val::ACT && x_k < 0) x_k = static_cast<int>(k);
+      else if (v.kind == Val::ARG && oi.shape.dtype == "s32" && oi.shape.dims.size() == 2 && ids_k < 0)
+        ids_k = static_cast<int>(k);
+      else return unsupported(ins, "operand %" + oi.name + " has no role in a pooling fusion");
+    }
+    if (x_k < 0 || ids_k < 0 || ins.shape.dims.size() != 2) return unsupported(ins, "expected an activation and s32 [B,S] ids");
+    const Val xv = vals_[ins.operands[x_k]];
+    const HloInstr& ids_i = e_.instrs[ins.operands[ids_k]];
+    const uint32_t B = static_cast<uint32_t>(ids_i.shape.dims[0]), S = static_cast<uint32_t>(ids_i.shape.dims[1]);
+    const uint32_t H = xv.cols;
+    if (xv.rows != B * S || ins.shape.dims[0] != B || ins.shape.dims[1] != H) return unsupported(ins, "shapes");
+    Rng rng;
+    std::vector<HTensor> ps = probe_inputs(c, [&](size_t k, HTensor& t) {
+      // few distinct ids, so that ties occur and the first-maximum rule is checked
+      for (float& x : t.v) x = (static_cast<int>(k) == ids_k) ? std::floor(rng.uni(0.f, 4.999f)) : rng.uni(-1.f, 1.f);
+    });
+    HTensor got;
+    int rc = probe(c, ps, &got);
+    if (rc) return rc;
+    std::vector<float> want(static_cast<size_t>(B) * H);
+    for (uint32_t b = 0; b < B; ++b) {
+      uint32_t best = 0;
+      for (uint32_t t = 1; t < S; ++t)
+        if (ps[ids_k].v[static_cast<size_t>(b) * S + t] > ps[ids_k].v[static_cast<size_t>(b) * S + best]) best = t;
+      for (uint32_t j = 0; j < H; ++j)
+        want[static_cast<size_t>(b) * H + j] = ps[x_k].v[(static_cast<size_t>(b) * S + best) * H + j];
+    }
+    if (!all_close(got.v, want, 0.f, 0.f))
+      return unsupported(ins, "fused computation " + c.name + " is not the row at the largest id of every sequence");
+    FOp o;
+    o.kind = OP_ROWSEL;
+    o.name = canonical_node_name(ins.name);
+    o.src = xv.tensor;
+    o.ids = vals_[ins.operands[ids_k]].tensor;
+    o.rows = B;
+    o.cols = H;
+    o.seq = S;
+    o.out = act_tensor(o.name, B, H);
+    g_.ops.push_back(o);
+    Val v;
+    v.kind = Val::ACT;
+    v.instr = idx;
+    v.tensor = o.out;
+    v.op = static_cast<int>(g_.ops.size()) - 1;
+    v.rows = B;
+    v.cols = H;
+    vals_[idx] = v;
+    return MONONN_OK;
+  }
+
+  // activation x activation^T (both operands contract their last dimension): small SIMT product
+  int lower_pairdot(int idx, float alpha, int lhs_c, int rhs_c) {
+    const HloInstr& ins = e_.instrs[idx];
+    const Val a = vals_[ins.operands[0]], b = vals_[ins.operands[1]];
+    if (lhs_c != 1 || rhs_c != 1 || a.cols != b.cols)
+      return unsupported(ins, "activation x activation GEMM must contract the last dimension of both");
+    if (a.rows > 1024 || b.rows > 1024)
+      return unsupported(ins, "activation x activation GEMM larger than 1024 rows a side");
+    FOp o;
+    o.kind = OP_PAIRDOT;
+    o.name = canonical_node_name(ins.name);
+    o.a = a.tensor;
+    o.src = b.tensor;
+    o.M = a.rows;
+    o.N = b.rows;
+    o.K = a.cols;
+    o.alpha = alpha;
+    o.out = act_tensor(o.name, a.rows, b.rows);
+    g_.ops.push_back(o);
+    Val v;
+    v.kind = Val::ACT;
+    v.instr = idx;
+    v.tensor = o.out;
+    v.op = static_cast<int>(g_.ops.size()) - 1;
+    v.rows = a.rows;
+    v.cols = b.rows;
+    vals_[idx] = v;
+    return MONONN_OK;
+  }
+
   // ------------------------------------------------------------------ outputs
   int finish_outputs() {
     const HloInstr& root = e_.instrs[e_.root];
@@ -1199,6 +1424,7 @@ class Lowering {
   std::vector<int> uses_;
   std::map<std::pair<int, bool>, int> const_tensors_;
   std::vector<Val> masks_;
+  std::map<int, Val> stream_of_;  // f16 LayerNorm output -> the f32 stream it was promoted to
 };
 
 }  // namespace

@@ -777,8 +777,12 @@ __device__ __forceinline__ float4 row_chunk(const RowSrc& s, uint32_t vi) {
 }
 __device__ __forceinline__ void row_emit(float4 a, float mean, float rstd, uint32_t vi,
                                          uint2 gv, uint2 bv, uint2 b2v, uint2* out, float4* out2,
-                                         bool add_bias2, bool no_norm) {
-  const float4 g = h4_to_f4(gv), b = h4_to_f4(bv);
+                                         bool add_bias2, bool no_norm, bool l2 = false) {
+  float4 g = h4_to_f4(gv), b = h4_to_f4(bv);
+  if (l2) {
+    g = make_float4(1.f, 1.f, 1.f, 1.f);
+    b = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   float4 y = a;
   if (!no_norm) {
     y.x = (a.x - mean) * rstd * g.x + b.x;
@@ -808,7 +812,7 @@ __device__ __noinline__ void rowwise_item(const OpDesc& op, uint32_t local, uint
   if (mark) trace(P, stage, TR_MARK0);
   const uint32_t cols = op.cols, nvec = cols >> 2, flags = op.flags;
   const bool embed = (op.kind == OP_EMBED), assemble = (op.kind == OP_ASSEMBLE);
-  const bool no_norm = (flags & F_NO_NORM) != 0u;
+  const bool no_norm = (flags & F_NO_NORM) != 0u, l2 = (flags & F_L2NORM) != 0u;
   RowSrc s{nullptr, nullptr, nullptr, nullptr, false};
   if (assemble) {
     // token row t of batch b: the first k_col rows come from a constant table (class token),
@@ -926,7 +930,7 @@ __device__ __noinline__ void rowwise_item(const OpDesc& op, uint32_t local, uint
       sum += x[i].x + x[i].y + x[i].z + x[i].w;
     }
     if (mark) trace(P, stage, TR_MARK0 + 1);
-    const float mean = warp_sum(sum) * inv_n;
+    const float mean = l2 ? 0.f : warp_sum(sum) * inv_n;
     float sq = 0.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i)
@@ -934,11 +938,11 @@ __device__ __noinline__ void rowwise_item(const OpDesc& op, uint32_t local, uint
         const float a = x[i].x - mean, b = x[i].y - mean, c = x[i].z - mean, d = x[i].w - mean;
         sq += a * a + b * b + c * c + d * d;
       }
-    const float rstd = rsqrtf(warp_sum(sq) * inv_n + eps);
+    const float rstd = l2 ? rsqrtf(warp_sum(sq)) : rsqrtf(warp_sum(sq) * inv_n + eps);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const uint32_t vi = i * 32u + lane;
-      if (vi < nvec) row_emit(x[i], mean, rstd, vi, gv[i], bv[i], b2v[i], out, out2, add_bias2, no_norm);
+      if (vi < nvec) row_emit(x[i], mean, rstd, vi, gv[i], bv[i], b2v[i], out, out2, add_bias2, no_norm, l2);
     }
   } else {
     // wide rows: three passes over the (L2-resident) sources
@@ -948,7 +952,7 @@ __device__ __noinline__ void rowwise_item(const OpDesc& op, uint32_t local, uint
       const float4 a = row_chunk(s, vi);
       sum += a.x + a.y + a.z + a.w;
     }
-    const float mean = warp_sum(sum) * inv_n;
+    const float mean = l2 ? 0.f : warp_sum(sum) * inv_n;
     float sq = 0.f;
 #pragma unroll 1
     for (uint32_t vi = lane; vi < nvec; vi += 32u) {
@@ -956,13 +960,13 @@ __device__ __noinline__ void rowwise_item(const OpDesc& op, uint32_t local, uint
       const float e = a.x - mean, f = a.y - mean, g = a.z - mean, h = a.w - mean;
       sq += e * e + f * f + g * g + h * h;
     }
-    const float rstd = rsqrtf(warp_sum(sq) * inv_n + eps);
+    const float rstd = l2 ? rsqrtf(warp_sum(sq)) : rsqrtf(warp_sum(sq) * inv_n + eps);
 #pragma unroll 1
     for (uint32_t vi = lane; vi < nvec; vi += 32u) {
       const float4 a = row_chunk(s, vi);
       if (s.zero) const_cast<float4*>(s.f32)[vi] = make_float4(0.f, 0.f, 0.f, 0.f);
       row_emit(a, mean, rstd, vi, __ldg(gamma + vi), __ldg(beta + vi),
-               add_bias2 ? __ldg(bias2 + vi) : make_uint2(0u, 0u), out, out2, add_bias2, no_norm);
+               add_bias2 ? __ldg(bias2 + vi) : make_uint2(0u, 0u), out, out2, add_bias2, no_norm, l2);
     }
   }
   if (mark) trace(P, stage, TR_MARK0 + 2);
@@ -1021,6 +1025,62 @@ __device__ __noinline__ bool argmax_item(Ctx& c, const OpDesc& op, uint32_t row,
   }
   // the partial-result slots are reused by the group's next row
   return group_sync(c, 0x421);
+}
+
+// Pooling at the largest token id: out[b, :] = src[b * seq + argmax(ids[b, :]), :], the first
+// maximum on ties (the end-of-text row of a CLIP text tower). One warp per output row.
+__device__ __noinline__ void rowsel_item(const OpDesc& op, uint32_t local, uint32_t warp_in_group,
+                                         uint32_t lane) {
+  const uint32_t b = local * 4u + warp_in_group;
+  if (b >= op.rows) return;
+  const int32_t* ids = reinterpret_cast<const int32_t*>(op.p[2]) + static_cast<size_t>(b) * op.seq;
+  int32_t best = INT32_MIN;
+  uint32_t best_i = 0;
+  for (uint32_t i = lane; i < op.seq; i += 32u) {
+    const int32_t v = __ldg(ids + i);
+    if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+  }
+  if (lane >= op.seq) best_i = 0xffffffffu;  // lanes without an element never win a tie
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) {
+    const int32_t ov = __shfl_xor_sync(0xffffffffu, best, off);
+    const uint32_t oi = __shfl_xor_sync(0xffffffffu, best_i, off);
+    if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+  }
+  const uint2* src = reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(op.p[1]) +
+                                                    (static_cast<size_t>(b) * op.seq + best_i) * op.lds);
+  uint2* out = reinterpret_cast<uint2*>(reinterpret_cast<__half*>(op.p[0]) + static_cast<size_t>(b) * op.ldo);
+  for (uint32_t vi = lane; vi < (op.cols >> 2); vi += 32u) out[vi] = __ldcg(src + vi);
+}
+
+// out[i, j] = alpha * <a[i, :], b[j, :]> for two small f16 activations (the image-text logits
+// of a dual encoder: a few dozen rows each). One warp per row i, lanes over j.
+__device__ __noinline__ void pairdot_item(const OpDesc& op, uint32_t local, uint32_t warp_in_group,
+                                          uint32_t lane) {
+  const uint32_t i = local * 4u + warp_in_group;
+  if (i >= op.M) return;
+  const uint4* a = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(op.p[1]) +
+                                                  static_cast<size_t>(i) * op.lds);
+  __half* out = reinterpret_cast<__half*>(op.p[0]) + static_cast<size_t>(i) * op.ldo;
+  const uint32_t kv = op.K >> 3;
+  for (uint32_t j = lane; j < op.N; j += 32u) {
+    const uint4* bj = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(op.p[2]) +
+                                                     static_cast<size_t>(j) * op.ldr);
+    float acc = 0.f;
+#pragma unroll 4
+    for (uint32_t k = 0; k < kv; ++k) {
+      const uint4 av = __ldcg(a + k), bv = __ldcg(bj + k);
+      const __half2* ah = reinterpret_cast<const __half2*>(&av);
+      const __half2* bh = reinterpret_cast<const __half2*>(&bv);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 x = __half22float2(ah[q]), y = __half22float2(bh[q]);
+        acc = fmaf(x.x, y.x, acc);
+        acc = fmaf(x.y, y.y, acc);
+      }
+    }
+    out[j] = __float2half_rn(acc * op.alpha);
+  }
 }
 
 // Patch extraction for a convolution whose stride equals its window (ViT / CLIP patch
@@ -1227,6 +1287,12 @@ __device__ void role_simt(Ctx c, uint32_t tmem_base, uint32_t tid_in_group) {
           break;
         case OP_ARGMAX:
           WAIT_OR_RETURN(argmax_item(c, op, it.local, quarter, lane, tid_in_group));
+          break;
+        case OP_ROWSEL:
+          rowsel_item(op, it.local, quarter, lane);
+          break;
+        case OP_PAIRDOT:
+          pairdot_item(op, it.local, quarter, lane);
           break;
         default:
           break;

@@ -192,6 +192,18 @@ int validate_plan(const Plan& P, std::string* err) {
         if (op.p[6].space == SPACE_NONE && d.kind != OP_LAYERNORM) return bad(n + "no scale pointer");
         if (d.kind == OP_ASSEMBLE && (d.seq == 0 || d.k_col >= d.seq)) return bad(n + "token geometry");
         break;
+      case OP_ROWSEL:
+        if (d.cols == 0 || d.cols % 4 || d.lds % 4 || d.ldo % 4 || d.seq == 0) return bad(n + "row geometry");
+        if (d.n_items != (d.rows + 3) / 4) return bad(n + "item count");
+        if (op.p[0].space == SPACE_NONE || op.p[1].space == SPACE_NONE || op.p[2].space == SPACE_NONE)
+          return bad(n + "buffers");
+        break;
+      case OP_PAIRDOT:
+        if (d.K == 0 || d.K % 8 || d.lds % 8 || d.ldr % 8) return bad(n + "K and row pitches must be multiples of 8");
+        if (d.n_items != (d.M + 3) / 4) return bad(n + "item count");
+        if (op.p[0].space == SPACE_NONE || op.p[1].space == SPACE_NONE || op.p[2].space == SPACE_NONE)
+          return bad(n + "buffers");
+        break;
       case OP_ARGMAX:
         if (d.cols == 0 || d.cols % 8 || d.lds % 8) return bad(n + "row length must be a multiple of 8");
         if (d.n_items != d.rows) return bad(n + "item count");
@@ -304,9 +316,13 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
 
   // ---- liveness
   std::vector<int> def_stage(n_t, -1), last_stage(n_t, -1);
+  std::vector<char> first_write_accumulates(n_t, 0);
   for (const FOp& o : ops) {
     for (int t : outputs_of(o)) {
-      if (def_stage[t] < 0) def_stage[t] = o.stage;
+      if (def_stage[t] < 0) {
+        def_stage[t] = o.stage;
+        first_write_accumulates[t] = (o.kind == OP_GEMM);
+      }
       last_stage[t] = std::max(last_stage[t], o.stage);
     }
     for (int t : inputs_of(o)) {
@@ -318,7 +334,12 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
   // ---- scratch layout: barrier counter, status, stamps, then f32 tensors
   uint64_t scratch = kScratchStampsOff + align_up(8ull * (n_stages + 2), 256);
 
-  std::vector<Interval> temp_iv, scratch_iv;
+  // f32 tensors come in two kinds that must not inherit each other's memory. A GEMM
+  // accumulator whose first write is a reduction needs zeros when its life starts and is
+  // cleared again by its reader (F_ZERO_SRC), so such tensors can follow one another. A tensor
+  // whose first write is a plain store (a residual stream, a pre-loaded accumulator, the mask
+  // bias) is left dirty when it dies; only other tensors of that kind may reuse its memory.
+  std::vector<Interval> temp_iv, scratch_iv, dirty_iv;
   for (int t = 0; t < n_t; ++t) {
     if (def_stage[t] < 0) continue;
     const FTensor& T = g.tensors[t];
@@ -334,12 +355,12 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
         break;
       case TKind::AccF32:
         iv.bytes = align_up(static_cast<uint64_t>(T.rows) * T.cols * 4, 256);
-        scratch_iv.push_back(iv);
+        (first_write_accumulates[t] ? scratch_iv : dirty_iv).push_back(iv);
         break;
       case TKind::VecF32:
         iv.bytes = align_up(static_cast<uint64_t>(T.rows) * 4, 256);
         // the mask bias is produced once and read by every layer
-        scratch_iv.push_back(iv);
+        dirty_iv.push_back(iv);
         break;
       default:
         break;
@@ -348,6 +369,7 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
   P.temp_bytes = assign_offsets(temp_iv, 0, 256);
   if (P.temp_bytes == 0) P.temp_bytes = 256;
   P.scratch_bytes = assign_offsets(scratch_iv, scratch, 256);
+  P.scratch_bytes = assign_offsets(dirty_iv, P.scratch_bytes, 256);
 
   std::vector<BufRef> where(n_t);
   const int temp_arg = static_cast<int>(P.args.size());
@@ -361,6 +383,7 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
   }
   for (const Interval& iv : temp_iv) where[iv.tensor] = BufRef{SPACE_ARG, temp_arg, iv.offset};
   for (const Interval& iv : scratch_iv) where[iv.tensor] = BufRef{SPACE_SCRATCH, 0, iv.offset};
+  for (const Interval& iv : dirty_iv) where[iv.tensor] = BufRef{SPACE_SCRATCH, 0, iv.offset};
   for (int t = 0; t < n_t; ++t)
     if (g.tensors[t].kind == TKind::Arg) where[t] = BufRef{SPACE_ARG, g.tensors[t].arg_index, 0};
 
@@ -598,14 +621,23 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
           po.p[0] = where[o.out];
           d.ldo = g.tensors[o.out].ld;
           po.p[1] = where[o.src];
+          // rows taken every `k_col`-th source row starting at row `q_col` (class-token pooling)
+          const uint32_t stride = o.k_col ? o.k_col : 1u;
           if (S.kind == TKind::AccF32) {
             d.flags |= F_SRC_F32;
-            d.lds = S.cols;
+            d.lds = S.cols * stride;
+            po.p[1].offset += static_cast<uint64_t>(o.q_col) * S.cols * 4;
           } else {
-            d.lds = S.ld;
+            d.lds = S.ld * stride;
+            po.p[1].offset += static_cast<uint64_t>(o.q_col) * S.ld * 2;
           }
-          po.p[2] = raw_const(o.gamma);
-          po.p[3] = raw_const(o.beta);
+          if (o.flags & F_L2NORM) {  // scale and shift are unused; any readable row will do
+            po.p[2] = po.p[1];
+            po.p[3] = po.p[1];
+          } else {
+            po.p[2] = raw_const(o.gamma);
+            po.p[3] = raw_const(o.beta);
+          }
           if (o.resid >= 0) {
             po.p[4] = where[o.resid];
             d.flags |= F_RESID;
@@ -631,6 +663,32 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
           po.p[0] = where[o.out];
           d.ldo = g.tensors[o.out].ld;
           po.p[1] = where[o.src];
+          break;
+        }
+        case OP_ROWSEL: {
+          d.rows = o.rows;
+          d.cols = o.cols;
+          d.seq = o.seq;
+          d.lds = g.tensors[o.src].ld;
+          d.ldo = g.tensors[o.out].ld;
+          d.n_items = (o.rows + 3) / 4;
+          po.p[0] = where[o.out];
+          po.p[1] = where[o.src];
+          po.p[2] = where[o.ids];
+          break;
+        }
+        case OP_PAIRDOT: {
+          d.M = o.M;
+          d.N = o.N;
+          d.K = o.K;
+          d.lds = g.tensors[o.a].ld;
+          d.ldr = g.tensors[o.src].ld;
+          d.ldo = g.tensors[o.out].ld;
+          d.n_items = (o.M + 3) / 4;
+          po.p[0] = where[o.out];
+          po.p[1] = where[o.a];
+          po.p[2] = where[o.src];
+          P.algorithmic_flops += 2.0 * o.M * o.N * o.K;
           break;
         }
         case OP_ARGMAX: {

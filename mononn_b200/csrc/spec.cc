@@ -124,6 +124,8 @@ static const char* kind_name(uint32_t k) {
     case OP_ASSEMBLE: return "assemble";
     case OP_PATCHIFY: return "patchify";
     case OP_ARGMAX: return "argmax";
+    case OP_ROWSEL: return "rowsel";
+    case OP_PAIRDOT: return "pairdot";
     default: return "none";
   }
 }
@@ -188,6 +190,9 @@ std::string plan_to_json(const Plan& plan) {
       Json ptrs = Json::array();
       for (int k = 0; k < 8; ++k) ptrs.arr.push_back(ref_json(op.p[k]));
       o.set("p", ptrs);
+      Json aux = Json::array();
+      for (int k = 0; k < 4; ++k) aux.arr.push_back(ref_json(op.q[k]));
+      o.set("q", aux);
       ops.arr.push_back(o);
     }
     st.set("ops", ops);

@@ -21,6 +21,8 @@ enum OpKind : uint32_t {
   OP_ASSEMBLE = 6,   // token rows = [constant prefix rows | GEMM rows + bias] + position rows -> f32
   OP_PATCHIFY = 7,   // NCHW f32 image -> f16 patch rows (operand of the patch-embedding GEMM)
   OP_ARGMAX = 8,     // s32 index of the maximum of every f16 row (first index on ties)
+  OP_ROWSEL = 9,     // out[b,:] = src[b*seq + argmax(ids[b,:]), :] (pooling at the largest token id)
+  OP_PAIRDOT = 10,   // out[i,j] = alpha * <a[i,:], b[j,:]> for two small f16 activations (SIMT)
 };
 
 enum ActKind : uint32_t {
@@ -49,6 +51,7 @@ enum OpFlags : uint32_t {
   F_OUT2_F16 = 1u << 7,    // LayerNorm: also write the un-normalised sum as f16
   F_RESID_F32 = 1u << 8,   // residual source is f32
   F_NO_NORM = 1u << 9,     // row op: no LayerNorm, the row sum is the result
+  F_L2NORM = 1u << 10,     // row op: x / sqrt(sum x^2) instead of LayerNorm (scale and shift unused)
 };
 
 // Pointer slots p[0..7]; meaning per kind:

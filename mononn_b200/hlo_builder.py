@@ -17,7 +17,7 @@ from __future__ import annotations
 
 import json
 
-from .models import EncoderConfig
+from .models import ClipConfig, EncoderConfig
 
 
 class _Emitter:
@@ -304,19 +304,22 @@ def bert_hlo(cfg: EncoderConfig) -> tuple[str, dict[str, str]]:
     return text, names
 
 
-def _preln_blocks(cfg: EncoderConfig, comps: list, entry: list, const, x: str, causal: bool) -> str:
+def _preln_blocks(cfg: EncoderConfig, comps: list, entry: list, const, x: str, causal: bool, tag: str = "",
+                  final_ln: bool = True) -> str:
     """Appends the fused computations and the entry instructions of `cfg.layers` pre-LN
     transformer blocks plus the final LayerNorm, reading the [tokens, hidden] f16 value `x`;
     returns the name of the final LayerNorm fusion. With `causal` the softmax fusion masks
-    keys after the query position (iota/compare/select, as XLA prints a causal mask)."""
+    keys after the query position (iota/compare/select, as XLA prints a causal mask). `tag`
+    prefixes every computation, instruction and constant name (models with two towers); without
+    `final_ln` the name of the last residual value is returned instead."""
     B, S, H, F, NH = cfg.batch, cfg.seq, cfg.hidden, cfg.ffn, cfg.heads
     D, T = H // NH, cfg.batch * cfg.seq
     h_TH, h_H, f_TH = _shape("f16", [T, H]), _shape("f16", [H]), _shape("f32", [T, H])
-    comps.append(f"%fused_ln (p0: {h_TH}, p1: {h_H}, p2: {h_H}) -> {h_TH} {{\n"
+    comps.append(f"%{tag}fused_ln (p0: {h_TH}, p1: {h_H}, p2: {h_H}) -> {h_TH} {{\n"
                  f"  %x = {h_TH} parameter(0)\n  %gamma = {h_H} parameter(1)\n  %beta = {h_H} parameter(2)\n"
                  f"  %x32 = {f_TH} convert({h_TH} %x)\n" + "\n".join(_ln_body(T, H, cfg.eps, "x32")) + "\n}\n")
     h_heads, h_BShd = _shape("f16", [B, NH, S, D]), _shape("f16", [B, S, NH, D])
-    comps.append(f"""%fused_bias_split (p0: {h_TH}, p1: {h_H}) -> {h_heads} {{
+    comps.append(f"""%{tag}fused_bias_split (p0: {h_TH}, p1: {h_H}) -> {h_heads} {{
   %x = {h_TH} parameter(0)
   %b = {h_H} parameter(1)
   %bb = {h_TH} broadcast({h_H} %b), dimensions={{1}}
@@ -334,7 +337,7 @@ def _preln_blocks(cfg: EncoderConfig, comps: list, entry: list, const, x: str, c
                         f"  %z = {f_sc} select({p_sc} %keep, {f_sc} %z0, {f_sc} %ninf_b)")
     else:
         causal_lines = f"  %z = {f_sc} copy({f_sc} %z0)"
-    comps.append(f"""%fused_softmax (p0: {h_sc}) -> {h_sc} {{
+    comps.append(f"""%{tag}fused_softmax (p0: {h_sc}) -> {h_sc} {{
   %s = {h_sc} parameter(0)
   %z0 = {f_sc} convert({h_sc} %s)
   %ninf = f32[] constant(-inf)
@@ -350,13 +353,13 @@ def _preln_blocks(cfg: EncoderConfig, comps: list, entry: list, const, x: str, c
   ROOT %p16 = {h_sc} convert({f_sc} %p)
 }}
 """)
-    comps.append(f"""%fused_merge (p0: {h_heads}) -> {h_TH} {{
+    comps.append(f"""%{tag}fused_merge (p0: {h_heads}) -> {h_TH} {{
   %x = {h_heads} parameter(0)
   %t = {h_BShd} transpose({h_heads} %x), dimensions={{0,2,1,3}}
   ROOT %r = {h_TH} reshape({h_BShd} %t)
 }}
 """)
-    comps.append(f"""%fused_bias_resid (p0: {h_TH}, p1: {h_H}, p2: {h_TH}) -> {h_TH} {{
+    comps.append(f"""%{tag}fused_bias_resid (p0: {h_TH}, p1: {h_H}, p2: {h_TH}) -> {h_TH} {{
   %x = {h_TH} parameter(0)
   %b = {h_H} parameter(1)
   %res = {h_TH} parameter(2)
@@ -367,7 +370,7 @@ def _preln_blocks(cfg: EncoderConfig, comps: list, entry: list, const, x: str, c
 """)
     h_TF, h_F, f_TF = _shape("f16", [T, F]), _shape("f16", [F]), _shape("f32", [T, F])
     act_lines, act_name = _activation_lines(cfg.act, "y32", f_TF)
-    comps.append(f"%fused_bias_act (p0: {h_TF}, p1: {h_F}) -> {h_TF} {{\n"
+    comps.append(f"%{tag}fused_bias_act (p0: {h_TF}, p1: {h_F}) -> {h_TF} {{\n"
                  f"  %x = {h_TF} parameter(0)\n  %b = {h_F} parameter(1)\n"
                  f"  %bb = {h_TF} broadcast({h_F} %b), dimensions={{1}}\n"
                  f"  %y = {h_TF} add({h_TF} %x, {h_TF} %bb)\n"
@@ -382,41 +385,43 @@ def _preln_blocks(cfg: EncoderConfig, comps: list, entry: list, const, x: str, c
         return name
 
     for l in range(cfg.layers):
-        p = f"layer{l}."
+        p = f"{tag}layer{l}."
         g1, b1 = const(p + "ln1.gamma", [H]), const(p + "ln1.beta", [H])
-        entry.append(f"  %fusion.ln1.{l} = {h_TH} fusion({h_TH} %{x}, {h_H} %{g1}, {h_H} %{b1}), kind=kInput, calls=%fused_ln")
+        entry.append(f"  %{tag}fusion.ln1.{l} = {h_TH} fusion({h_TH} %{x}, {h_H} %{g1}, {h_H} %{b1}), kind=kInput, calls=%{tag}fused_ln")
         heads = {}
         for n in ("q", "k", "v"):
             w = const(p + f"attn.{n}.w", [H, H])
             b = const(p + f"attn.{n}.b", [H])
-            gname = gemm(f"gemm.{n}.{l}", f"fusion.ln1.{l}", [T, H], w, [H, H], [T, H], ls=T * H, rs=H * H)
-            entry.append(f"  %fusion.{n}.{l} = {h_heads} fusion({h_TH} %{gname}, {h_H} %{b}), kind=kLoop, "
-                         f"calls=%fused_bias_split")
-            heads[n] = f"fusion.{n}.{l}"
-        sc = gemm(f"gemm.scores.{l}", heads["q"], [B, NH, S, D], heads["k"], [B, NH, S, D], [B, NH, S, S],
+            gname = gemm(f"{tag}gemm.{n}.{l}", f"{tag}fusion.ln1.{l}", [T, H], w, [H, H], [T, H], ls=T * H, rs=H * H)
+            entry.append(f"  %{tag}fusion.{n}.{l} = {h_heads} fusion({h_TH} %{gname}, {h_H} %{b}), kind=kLoop, "
+                         f"calls=%{tag}fused_bias_split")
+            heads[n] = f"{tag}fusion.{n}.{l}"
+        sc = gemm(f"{tag}gemm.scores.{l}", heads["q"], [B, NH, S, D], heads["k"], [B, NH, S, D], [B, NH, S, S],
                   alpha=1.0 / (D ** 0.5), lhs_c=3, rhs_c=3, batch_dims=(0, 1), batch=B * NH, ls=S * D, rs=S * D)
-        entry.append(f"  %fusion.softmax.{l} = {h_sc} fusion({h_sc} %{sc}), kind=kInput, calls=%fused_softmax")
-        pv = gemm(f"gemm.pv.{l}", f"fusion.softmax.{l}", [B, NH, S, S], heads["v"], [B, NH, S, D], [B, NH, S, D],
+        entry.append(f"  %{tag}fusion.softmax.{l} = {h_sc} fusion({h_sc} %{sc}), kind=kInput, calls=%{tag}fused_softmax")
+        pv = gemm(f"{tag}gemm.pv.{l}", f"{tag}fusion.softmax.{l}", [B, NH, S, S], heads["v"], [B, NH, S, D], [B, NH, S, D],
                   lhs_c=3, rhs_c=2, batch_dims=(0, 1), batch=B * NH, ls=S * S, rs=S * D)
-        entry.append(f"  %fusion.ctx.{l} = {h_TH} fusion({h_heads} %{pv}), kind=kLoop, calls=%fused_merge")
+        entry.append(f"  %{tag}fusion.ctx.{l} = {h_TH} fusion({h_heads} %{pv}), kind=kLoop, calls=%{tag}fused_merge")
         wo, bo = const(p + "attn.o.w", [H, H]), const(p + "attn.o.b", [H])
-        go = gemm(f"gemm.o.{l}", f"fusion.ctx.{l}", [T, H], wo, [H, H], [T, H], ls=T * H, rs=H * H)
-        entry.append(f"  %fusion.res1.{l} = {h_TH} fusion({h_TH} %{go}, {h_H} %{bo}, {h_TH} %{x}), kind=kLoop, "
-                     f"calls=%fused_bias_resid")
-        x = f"fusion.res1.{l}"
+        go = gemm(f"{tag}gemm.o.{l}", f"{tag}fusion.ctx.{l}", [T, H], wo, [H, H], [T, H], ls=T * H, rs=H * H)
+        entry.append(f"  %{tag}fusion.res1.{l} = {h_TH} fusion({h_TH} %{go}, {h_H} %{bo}, {h_TH} %{x}), kind=kLoop, "
+                     f"calls=%{tag}fused_bias_resid")
+        x = f"{tag}fusion.res1.{l}"
         g2, b2 = const(p + "ln2.gamma", [H]), const(p + "ln2.beta", [H])
-        entry.append(f"  %fusion.ln2.{l} = {h_TH} fusion({h_TH} %{x}, {h_H} %{g2}, {h_H} %{b2}), kind=kInput, calls=%fused_ln")
+        entry.append(f"  %{tag}fusion.ln2.{l} = {h_TH} fusion({h_TH} %{x}, {h_H} %{g2}, {h_H} %{b2}), kind=kInput, calls=%{tag}fused_ln")
         w1, bb1 = const(p + "ffn.up.w", [H, F]), const(p + "ffn.up.b", [F])
-        gu = gemm(f"gemm.up.{l}", f"fusion.ln2.{l}", [T, H], w1, [H, F], [T, F], ls=T * H, rs=H * F)
-        entry.append(f"  %fusion.act.{l} = {h_TF} fusion({h_TF} %{gu}, {h_F} %{bb1}), kind=kLoop, calls=%fused_bias_act")
+        gu = gemm(f"{tag}gemm.up.{l}", f"{tag}fusion.ln2.{l}", [T, H], w1, [H, F], [T, F], ls=T * H, rs=H * F)
+        entry.append(f"  %{tag}fusion.act.{l} = {h_TF} fusion({h_TF} %{gu}, {h_F} %{bb1}), kind=kLoop, calls=%{tag}fused_bias_act")
         w2, bb2 = const(p + "ffn.down.w", [F, H]), const(p + "ffn.down.b", [H])
-        gd = gemm(f"gemm.down.{l}", f"fusion.act.{l}", [T, F], w2, [F, H], [T, H], ls=T * F, rs=F * H)
-        entry.append(f"  %fusion.res2.{l} = {h_TH} fusion({h_TH} %{gd}, {h_H} %{bb2}, {h_TH} %{x}), kind=kLoop, "
-                     f"calls=%fused_bias_resid")
-        x = f"fusion.res2.{l}"
-    gf, bf = const("ln.gamma", [H]), const("ln.beta", [H])
-    entry.append(f"  %fusion.lnf = {h_TH} fusion({h_TH} %{x}, {h_H} %{gf}, {h_H} %{bf}), kind=kInput, calls=%fused_ln")
-    return "fusion.lnf"
+        gd = gemm(f"{tag}gemm.down.{l}", f"{tag}fusion.act.{l}", [T, F], w2, [F, H], [T, H], ls=T * F, rs=F * H)
+        entry.append(f"  %{tag}fusion.res2.{l} = {h_TH} fusion({h_TH} %{gd}, {h_H} %{bb2}, {h_TH} %{x}), kind=kLoop, "
+                     f"calls=%{tag}fused_bias_resid")
+        x = f"{tag}fusion.res2.{l}"
+    if not final_ln:
+        return x
+    gf, bf = const(tag + "ln.gamma", [H]), const(tag + "ln.beta", [H])
+    entry.append(f"  %{tag}fusion.lnf = {h_TH} fusion({h_TH} %{x}, {h_H} %{gf}, {h_H} %{bf}), kind=kInput, calls=%{tag}fused_ln")
+    return f"{tag}fusion.lnf"
 
 
 def vit_hlo(cfg: EncoderConfig) -> tuple[str, dict[str, str]]:
@@ -559,4 +564,202 @@ def opt_hlo(cfg: EncoderConfig) -> tuple[str, dict[str, str]]:
     entry.append(f"  ROOT %outputs = {out_shape} tuple({h_TV} %gemm.lm_head, {i_T} %fusion.argmax)")
     text = (f"HloModule {cfg.name}, entry_computation_layout={{({i_BS})->{out_shape}}}\n\n" + "\n".join(comps)
             + f"\nENTRY %{cfg.name}_main (input_ids: {i_BS}) -> {out_shape} {{\n" + "\n".join(entry) + "\n}\n")
+    return text, names
+
+
+def clip_hlo(cfg: ClipConfig, towers: str = "both") -> tuple[str, dict[str, str]]:
+    """HLO text of a CLIP-shaped dual encoder (model of examples/utils/save_model.py:66-74, which
+    returns logits_per_image). Vision tower: bias-free patch convolution, class token +
+    positions, LayerNorm, pre-LN blocks, LayerNorm of the class row (slice inside the fusion),
+    projection. Text tower: token + position rows, causal pre-LN blocks, final LayerNorm, the row
+    at the largest token id (arg-max reduce + gather), projection. Both embeddings are
+    L2-normalised; logits = logit_scale * image . text^T as one GEMM of two activations.
+    Outputs: (logits_per_image f16 [images, texts], image_embeds, text_embeds). With
+    `towers` = "vision" or "text" only that tower is emitted and its normalised embeddings are
+    the single output (the get_image_features / get_text_features use of the model)."""
+    assert towers in ("both", "vision", "text")
+    v, t, P = cfg.vision, cfg.text, cfg.proj
+    live = [True]  # False while the tower being written is not part of the module
+
+    class _Sink(list):
+        def append(self, item):
+            if live[0]:
+                super().append(item)
+
+    comps = _Sink([_REGIONS])
+    entry = _Sink()
+    names: dict[str, str] = {}
+
+    def const(name: str, dims) -> str:
+        if live[0]:
+            names[name] = name
+        entry.append(f"  %{name} = {_shape('f16', dims)} constant({{...}})")
+        return name
+
+    def gemm(name, a, a_shape, w, w_shape, out_shape, alpha=1.0, rhs_c=0):
+        entry.append(f"  %{name} = {_shape('f16', out_shape)} custom-call({_shape('f16', a_shape)} %{a}, "
+                     f"{_shape('f16', w_shape)} %{w}), custom_call_target=\"__cublas$gemm\", "
+                     f"backend_config={_gemm_config(alpha, 1, rhs_c, (), 1, 0, 0)}")
+        return name
+
+    # ---------------------------------------------------------------- vision tower
+    live[0] = towers != "text"
+    B, S, H, C, IMG, PS = v.batch, v.seq, v.hidden, v.channels, v.image, v.patch
+    G = IMG // PS
+    Pn, T = G * G, B * S
+    px_s, nhwc_s = _shape("f32", [B, C, IMG, IMG]), _shape("f16", [B, IMG, IMG, C])
+    h_TH, h_H, f_TH = _shape("f16", [T, H]), _shape("f16", [H]), _shape("f32", [T, H])
+    i_BS = _shape("s32", [t.batch, t.seq])
+    live[0] = True
+    if towers != "text":
+        entry.append(f"  %pixel_values = {px_s} parameter(0)")
+    if towers != "vision":
+        entry.append(f"  %input_ids = {i_BS} parameter({1 if towers == 'both' else 0})")
+    live[0] = towers != "text"
+    comps.append(f"""%fused_nhwc (p0: {px_s}) -> {nhwc_s} {{
+  %x = {px_s} parameter(0)
+  %t = {_shape('f32', [B, IMG, IMG, C])} transpose({px_s} %x), dimensions={{0,2,3,1}}
+  ROOT %c = {nhwc_s} convert({_shape('f32', [B, IMG, IMG, C])} %t)
+}}
+""")
+    entry.append(f"  %fusion.nhwc = {nhwc_s} fusion({px_s} %pixel_values), kind=kLoop, calls=%fused_nhwc")
+    wp = const("vision.embeddings.patch.w", [H, PS, PS, C])
+    cls = const("vision.embeddings.cls", [1, H])
+    pos = const("vision.embeddings.position", [S, H])
+    conv_s = _shape("f16", [B, G, G, H])
+    conv_cfg = json.dumps(json.dumps({"conv_result_scale": 1, "side_input_scale": 0, "activation_mode": "0",
+                                      "tensor_ops_enabled": True}, separators=(",", ":")))
+    entry.append(f"  %conv.patch = ({conv_s}, u8[0]{{0}}) custom-call({nhwc_s} %fusion.nhwc, "
+                 f"{_shape('f16', [H, PS, PS, C])} %{wp}), window={{size={PS}x{PS} stride={PS}x{PS}}}, "
+                 f"dim_labels=b01f_o01i->b01f, custom_call_target=\"__cudnn$convForward\", backend_config={conv_cfg}")
+    entry.append(f"  %gte.patch = {conv_s} get-tuple-element(({conv_s}, u8[0]{{0}}) %conv.patch), index=0")
+    h_BPH, h_BSH, h_B1H, h_SH, h_1H = (_shape("f16", [B, Pn, H]), _shape("f16", [B, S, H]), _shape("f16", [B, 1, H]),
+                                       _shape("f16", [S, H]), _shape("f16", [1, H]))
+    comps.append(f"""%fused_tokens (p0: {conv_s}, p1: {h_1H}, p2: {h_SH}) -> {h_TH} {{
+  %y = {conv_s} parameter(0)
+  %cls = {h_1H} parameter(1)
+  %pos = {h_SH} parameter(2)
+  %yr = {h_BPH} reshape({conv_s} %y)
+  %cls_b = {h_B1H} broadcast({h_1H} %cls), dimensions={{1,2}}
+  %cat = {h_BSH} concatenate({h_B1H} %cls_b, {h_BPH} %yr), dimensions={{1}}
+  %pos_b = {h_BSH} broadcast({h_SH} %pos), dimensions={{1,2}}
+  %tok = {h_BSH} add({h_BSH} %cat, {h_BSH} %pos_b)
+  ROOT %r = {h_TH} reshape({h_BSH} %tok)
+}}
+""")
+    entry.append(f"  %fusion.tokens = {h_TH} fusion({conv_s} %gte.patch, {h_1H} %{cls}, {h_SH} %{pos}), kind=kLoop, "
+                 f"calls=%fused_tokens")
+    g0, b0 = const("vision.pre_ln.gamma", [H]), const("vision.pre_ln.beta", [H])
+    entry.append(f"  %vision.fusion.pre_ln = {h_TH} fusion({h_TH} %fusion.tokens, {h_H} %{g0}, {h_H} %{b0}), "
+                 f"kind=kInput, calls=%vision.fused_ln")
+    x = _preln_blocks(v, comps, entry, const, "vision.fusion.pre_ln", causal=False, tag="vision.", final_ln=False)
+    h_BH, f_BH = _shape("f16", [B, H]), _shape("f32", [B, H])
+    comps.append(f"%fused_cls_ln (p0: {h_TH}, p1: {h_H}, p2: {h_H}) -> {h_BH} {{\n"
+                 f"  %xa = {h_TH} parameter(0)\n  %gamma = {h_H} parameter(1)\n  %beta = {h_H} parameter(2)\n"
+                 f"  %x3 = {h_BSH} reshape({h_TH} %xa)\n"
+                 f"  %xs = {h_B1H} slice({h_BSH} %x3), slice={{[0:{B}], [0:1], [0:{H}]}}\n"
+                 f"  %xc = {h_BH} reshape({h_B1H} %xs)\n"
+                 f"  %x32 = {f_BH} convert({h_BH} %xc)\n" + "\n".join(_ln_body(B, H, v.eps, "x32")) + "\n}\n")
+    g1, b1 = const("vision.ln.gamma", [H]), const("vision.ln.beta", [H])
+    entry.append(f"  %fusion.cls_ln = {h_BH} fusion({h_TH} %{x}, {h_H} %{g1}, {h_H} %{b1}), kind=kInput, "
+                 f"calls=%fused_cls_ln")
+    wv = const("vision.proj.w", [H, P])
+    gi = gemm("gemm.image_proj", "fusion.cls_ln", [B, H], wv, [H, P], [B, P])
+
+    def l2norm(tag, rows, src):
+        h_s, f_s, f_r = _shape("f16", [rows, P]), _shape("f32", [rows, P]), _shape("f32", [rows])
+        comps.append(f"""%fused_l2norm_{tag} (p0: {h_s}) -> {h_s} {{
+  %x = {h_s} parameter(0)
+  %x32 = {f_s} convert({h_s} %x)
+  %sq = {f_s} multiply({f_s} %x32, {f_s} %x32)
+  %zero = f32[] constant(0)
+  %ss = {f_r} reduce({f_s} %sq, f32[] %zero), dimensions={{1}}, to_apply=%region_add
+  %nrm = {f_r} sqrt({f_r} %ss)
+  %nrm_b = {f_s} broadcast({f_r} %nrm), dimensions={{0}}
+  %y = {f_s} divide({f_s} %x32, {f_s} %nrm_b)
+  ROOT %y16 = {h_s} convert({f_s} %y)
+}}
+""")
+        entry.append(f"  %{tag}_embeds = {h_s} fusion({h_s} %{src}), kind=kInput, calls=%fused_l2norm_{tag}")
+        return f"{tag}_embeds"
+
+    img = l2norm("image", B, gi)
+
+    # ------------------------------------------------------------------ text tower
+    live[0] = towers != "vision"
+    Bt, St, Ht, V = t.batch, t.seq, t.hidden, t.vocab
+    Tt = Bt * St
+    t_TH, t_BSH, t_SH, t_BH = (_shape("f16", [Tt, Ht]), _shape("f16", [Bt, St, Ht]), _shape("f16", [St, Ht]),
+                               _shape("f16", [Bt, Ht]))
+    word = const("text.embeddings.word", [V, Ht])
+    tpos = const("text.embeddings.position", [t.max_pos, Ht])
+    w_s, p_s = _shape("f16", [V, Ht]), _shape("f16", [t.max_pos, Ht])
+    comps.append(f"""%fused_embed (p0: {i_BS}, p1: {w_s}, p2: {p_s}) -> {t_TH} {{
+  %ids = {i_BS} parameter(0)
+  %word = {w_s} parameter(1)
+  %pos = {p_s} parameter(2)
+  %tok = {t_BSH} gather({w_s} %word, {i_BS} %ids), offset_dims={{2}}, collapsed_slice_dims={{0}}, start_index_map={{0}}, index_vector_dim=2, slice_sizes={{1,{Ht}}}
+  %pos_s = {t_SH} slice({p_s} %pos), slice={{[0:{St}], [0:{Ht}]}}
+  %pos_b = {t_BSH} broadcast({t_SH} %pos_s), dimensions={{1,2}}
+  %sum = {t_BSH} add({t_BSH} %tok, {t_BSH} %pos_b)
+  ROOT %r = {t_TH} reshape({t_BSH} %sum)
+}}
+""")
+    entry.append(f"  %fusion.embed = {t_TH} fusion({i_BS} %input_ids, {w_s} %{word}, {p_s} %{tpos}), kind=kLoop, "
+                 f"calls=%fused_embed")
+    lnf = _preln_blocks(t, comps, entry, const, "fusion.embed", causal=True, tag="text.")
+    i_B, f_B = _shape("s32", [Bt]), _shape("s32", [Bt])
+    comps.append(f"""%region_argmax_s32 (a_v: s32[], a_i: s32[], b_v: s32[], b_i: s32[]) -> (s32[], s32[]) {{
+  %a_v = s32[] parameter(0)
+  %a_i = s32[] parameter(1)
+  %b_v = s32[] parameter(2)
+  %b_i = s32[] parameter(3)
+  %gt = pred[] compare(s32[] %a_v, s32[] %b_v), direction=GT
+  %eq = pred[] compare(s32[] %a_v, s32[] %b_v), direction=EQ
+  %lt_i = pred[] compare(s32[] %a_i, s32[] %b_i), direction=LT
+  %tie = pred[] and(pred[] %eq, pred[] %lt_i)
+  %keep = pred[] or(pred[] %gt, pred[] %tie)
+  %v = s32[] select(pred[] %keep, s32[] %a_v, s32[] %b_v)
+  %i = s32[] select(pred[] %keep, s32[] %a_i, s32[] %b_i)
+  ROOT %t = (s32[], s32[]) tuple(s32[] %v, s32[] %i)
+}}
+
+%fused_eos_pool (p0: {t_TH}, p1: {i_BS}) -> {t_BH} {{
+  %x = {t_TH} parameter(0)
+  %ids = {i_BS} parameter(1)
+  %idx = {i_BS} iota(), iota_dimension=1
+  %imin = s32[] constant(-2147483648)
+  %zero = s32[] constant(0)
+  %r = ({i_B}, {i_B}) reduce({i_BS} %ids, {i_BS} %idx, s32[] %imin, s32[] %zero), dimensions={{1}}, to_apply=%region_argmax_s32
+  %eos = {i_B} get-tuple-element(({i_B}, {i_B}) %r), index=1
+  %b = {i_B} iota(), iota_dimension=0
+  %len = s32[] constant({St})
+  %len_b = {i_B} broadcast(s32[] %len), dimensions={{}}
+  %base = {i_B} multiply({i_B} %b, {i_B} %len_b)
+  %flat = {i_B} add({i_B} %base, {i_B} %eos)
+  ROOT %rows = {t_BH} gather({t_TH} %x, {i_B} %flat), offset_dims={{1}}, collapsed_slice_dims={{0}}, start_index_map={{0}}, index_vector_dim=1, slice_sizes={{1,{Ht}}}
+}}
+""")
+    entry.append(f"  %fusion.eos_pool = {t_BH} fusion({t_TH} %{lnf}, {i_BS} %input_ids), kind=kInput, "
+                 f"calls=%fused_eos_pool")
+    wt = const("text.proj.w", [Ht, P])
+    gt = gemm("gemm.text_proj", "fusion.eos_pool", [Bt, Ht], wt, [Ht, P], [Bt, P])
+    txt = l2norm("text", Bt, gt)
+    live[0] = True
+    lg_s = _shape("f16", [B, Bt])
+    i_s, t_s = _shape("f16", [B, P]), _shape("f16", [Bt, P])
+    if towers == "both":
+        gemm("logits_per_image", img, [B, P], txt, [Bt, P], [B, Bt], alpha=cfg.logit_scale, rhs_c=1)
+        out_shape = f"({lg_s}, {i_s}, {t_s})"
+        entry.append(f"  ROOT %outputs = {out_shape} tuple({lg_s} %logits_per_image, {i_s} %{img}, {t_s} %{txt})")
+        params, sig = f"{px_s}, {i_BS}", f"pixel_values: {px_s}, input_ids: {i_BS}"
+    elif towers == "vision":
+        out_shape, params, sig = i_s, px_s, f"pixel_values: {px_s}"
+        entry.append(f"  ROOT %outputs = {i_s} bitcast({i_s} %{img})")
+    else:
+        out_shape, params, sig = t_s, i_BS, f"input_ids: {i_BS}"
+        entry.append(f"  ROOT %outputs = {t_s} bitcast({t_s} %{txt})")
+    text = (f"HloModule {cfg.name}, entry_computation_layout={{({params})->{out_shape}}}\n\n"
+            + "\n".join(comps) + f"\nENTRY %{cfg.name}_main ({sig}) -> {out_shape} "
+            f"{{\n" + "\n".join(entry) + "\n}\n")
     return text, names

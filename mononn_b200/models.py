@@ -79,12 +79,15 @@ def bert_weight_shapes(cfg: EncoderConfig) -> dict[str, tuple[int, ...]]:
     return shapes
 
 
-def make_weights(cfg: EncoderConfig, seed: int = 1234, stress: bool = False) -> dict[str, np.ndarray]:
+def make_weights(cfg, seed: int = 1234, stress: bool = False) -> dict[str, np.ndarray]:
     """fp32 weights, already rounded to fp16-representable values so that the fp16 device
     copy and the fp32 CPU copy hold the same numbers.  Linear weights are [in, out]."""
     rng = np.random.default_rng(seed)
     out: dict[str, np.ndarray] = {}
-    shapes = {"vit": vit_weight_shapes, "opt": opt_weight_shapes}.get(cfg.model, bert_weight_shapes)(cfg)
+    if isinstance(cfg, ClipConfig):
+        shapes = clip_weight_shapes(cfg)
+    else:
+        shapes = {"vit": vit_weight_shapes, "opt": opt_weight_shapes}.get(cfg.model, bert_weight_shapes)(cfg)
     for name, shape in shapes.items():
         if name.endswith(".gamma"):
             w = np.ones(shape, np.float32)
@@ -192,3 +195,63 @@ def opt_weight_shapes(cfg: EncoderConfig) -> dict[str, tuple[int, ...]]:
     shapes["ln.gamma"] = (h,)
     shapes["ln.beta"] = (h,)
     return shapes
+
+
+@dataclasses.dataclass
+class ClipConfig:
+    """Dual encoder: a pre-LN vision tower (class token, LayerNorm before the blocks, LayerNorm
+    of the class row after them) and a pre-LN causal text tower (row of the largest token id
+    pooled after the final LayerNorm); both projected to `proj` columns, L2-normalised and
+    compared: logits[i, j] = logit_scale * <image_i, text_j>."""
+    vision: EncoderConfig
+    text: EncoderConfig
+    proj: int = 512
+    logit_scale: float = 1.0 / 0.07   # exp(2.6592), the initial value of the learned temperature
+    name: str = "cluster_0"
+    model: str = "clip"
+
+
+def _clip_towers(batch_img, batch_txt, image, patch, vh, vl, vf, th, tl, tf, seq, vocab):
+    n = (image // patch) ** 2 + 1
+    vision = EncoderConfig(model="vit", layers=vl, hidden=vh, heads=vh // 64, ffn=vf, batch=batch_img, seq=n,
+                           image=image, patch=patch, channels=3, max_pos=n, vocab=0, types=0, eps=1e-5,
+                           act="quick_gelu")
+    text = EncoderConfig(model="opt", layers=tl, hidden=th, heads=th // 64, ffn=tf, vocab=vocab, max_pos=seq,
+                         types=0, batch=batch_txt, seq=seq, eps=1e-5, act="quick_gelu")
+    return vision, text
+
+
+def clip_b32(images: int = 32, texts: int = 32) -> ClipConfig:
+    """CLIP ViT-B/32 shape: 224x224 image in 32x32 patches (50 tokens, width 768, 12 layers),
+    text width 512 / 8 heads / 12 layers / 77 tokens over 49408 ids, projection 512."""
+    v, t = _clip_towers(images, texts, 224, 32, 768, 12, 3072, 512, 12, 2048, 77, 49408)
+    return ClipConfig(vision=v, text=t, proj=512)
+
+
+def clip_tiny(images: int = 3, texts: int = 5, image: int = 64, patch: int = 32, layers: int = 1,
+              vh: int = 128, th: int = 64, seq: int = 12, vocab: int = 200, proj: int = 64) -> ClipConfig:
+    v, t = _clip_towers(images, texts, image, patch, vh, layers, 2 * vh, th, layers, 2 * th, seq, vocab)
+    return ClipConfig(vision=v, text=t, proj=proj)
+
+
+def clip_weight_shapes(cfg: ClipConfig) -> dict[str, tuple[int, ...]]:
+    v, t = cfg.vision, cfg.text
+    shapes: dict[str, tuple[int, ...]] = {}
+    for k, shp in vit_weight_shapes(v).items():
+        if k == "embeddings.patch.b":
+            continue  # the patch convolution has no bias
+        shapes["vision." + k] = shp
+    shapes["vision.pre_ln.gamma"] = (v.hidden,)
+    shapes["vision.pre_ln.beta"] = (v.hidden,)
+    shapes["vision.proj.w"] = (v.hidden, cfg.proj)
+    for k, shp in opt_weight_shapes(t).items():
+        shapes["text." + k] = (t.max_pos, t.hidden) if k == "embeddings.position" else shp
+    shapes["text.proj.w"] = (t.hidden, cfg.proj)
+    return shapes
+
+
+def make_clip_inputs(cfg: ClipConfig, seed: int = 1234) -> dict[str, np.ndarray]:
+    """Pixels uniform in [-1, 1], token ids uniform over the vocabulary."""
+    out = make_vit_inputs(cfg.vision, seed)
+    out["input_ids"] = make_inputs(cfg.text, seed)["input_ids"]
+    return out

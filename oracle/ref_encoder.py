@@ -190,3 +190,46 @@ def opt_decoder(cfg, w, inputs):
     y = layer_norm(x, w["ln.gamma"], w["ln.beta"], cfg.eps).reshape(b * s_, h)
     logits = (y @ w["embeddings.word"].T).astype(np.float32)
     return logits, logits.argmax(-1).astype(np.int32)
+
+
+def _preln_blocks(cfg, w, x, prefix="", causal=False):
+    """The pre-LN transformer blocks of `cfg` applied to the residual stream x [B, S, H]."""
+    for l in range(cfg.layers):
+        p = f"{prefix}layer{l}."
+        lin = lambda t, n: t @ w[p + n + ".w"] + w[p + n + ".b"]
+        y = layer_norm(x, w[p + "ln1.gamma"], w[p + "ln1.beta"], cfg.eps)
+        ctx = attention(lin(y, "attn.q"), lin(y, "attn.k"), lin(y, "attn.v"), None, cfg.heads, causal=causal)
+        x = x + lin(ctx, "attn.o")
+        y = layer_norm(x, w[p + "ln2.gamma"], w[p + "ln2.beta"], cfg.eps)
+        x = x + lin(activation(lin(y, "ffn.up"), cfg.act), "ffn.down")
+    return x
+
+
+def clip_dual(cfg, w, inputs):
+    """fp32 forward of the dual encoder (CLIP). Vision: bias-free patch convolution, class
+    token + positions, LayerNorm, pre-LN blocks (quick-GELU), LayerNorm of the class row,
+    projection. Text: token + position rows, causal pre-LN blocks, final LayerNorm, the row of
+    the largest token id (first on ties), projection. Returns (logits_per_image [images,
+    texts], image_embeds, text_embeds), the embeddings L2-normalised."""
+    v, t = cfg.vision, cfg.text
+    px = inputs["pixel_values"].astype(np.float32)
+    pat = vit_patches(v, px) @ w["vision.embeddings.patch.w"].reshape(v.hidden, -1).T
+    pat = pat.reshape(v.batch, v.seq - 1, v.hidden)
+    cls = np.broadcast_to(w["vision.embeddings.cls"].reshape(1, 1, v.hidden), (v.batch, 1, v.hidden))
+    x = (np.concatenate([cls, pat], 1) + w["vision.embeddings.position"][None]).astype(np.float32)
+    x = layer_norm(x, w["vision.pre_ln.gamma"], w["vision.pre_ln.beta"], v.eps)
+    x = _preln_blocks(v, w, x, "vision.")
+    pooled = layer_norm(x[:, 0, :], w["vision.ln.gamma"], w["vision.ln.beta"], v.eps)
+    img = pooled @ w["vision.proj.w"]
+
+    ids = inputs["input_ids"]
+    y = (w["text.embeddings.word"][ids] + w["text.embeddings.position"][: t.seq][None]).astype(np.float32)
+    y = _preln_blocks(t, w, y, "text.", causal=True)
+    y = layer_norm(y, w["text.ln.gamma"], w["text.ln.beta"], t.eps)
+    eos = ids.argmax(-1)  # first occurrence of the largest id
+    txt = y[np.arange(t.batch), eos] @ w["text.proj.w"]
+
+    img = img / np.linalg.norm(img, axis=-1, keepdims=True)
+    txt = txt / np.linalg.norm(txt, axis=-1, keepdims=True)
+    logits = (cfg.logit_scale * img @ txt.T).astype(np.float32)
+    return logits, img.astype(np.float32), txt.astype(np.float32)

@@ -16,7 +16,8 @@ import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 sys.path.insert(0, ROOT)
-from mononn_b200.models import EncoderConfig, make_inputs, make_vit_inputs, make_weights  # noqa: E402
+from mononn_b200.models import (ClipConfig, EncoderConfig, clip_tiny, make_clip_inputs, make_inputs,  # noqa: E402
+                                make_vit_inputs, make_weights)
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
@@ -122,6 +123,51 @@ def hf_opt_forward(cfg: EncoderConfig, w: dict, inputs: dict) -> np.ndarray:
     return out.reshape(cfg.batch * cfg.seq, cfg.vocab).numpy()
 
 
+def hf_clip_forward(cfg, w: dict, inputs: dict) -> np.ndarray:
+    from transformers import CLIPConfig, CLIPModel
+    v, t = cfg.vision, cfg.text
+    tc = dict(vocab_size=t.vocab, hidden_size=t.hidden, intermediate_size=t.ffn, num_hidden_layers=t.layers,
+              num_attention_heads=t.heads, max_position_embeddings=t.max_pos, hidden_act="quick_gelu",
+              layer_norm_eps=t.eps, eos_token_id=2, attention_dropout=0.0)
+    vc = dict(hidden_size=v.hidden, intermediate_size=v.ffn, num_hidden_layers=v.layers,
+              num_attention_heads=v.heads, image_size=v.image, patch_size=v.patch, hidden_act="quick_gelu",
+              layer_norm_eps=v.eps, attention_dropout=0.0)
+    model = CLIPModel(CLIPConfig(text_config=tc, vision_config=vc, projection_dim=cfg.proj)).eval()
+    tt = lambda a: torch.from_numpy(np.ascontiguousarray(a))
+    sd = {"logit_scale": torch.tensor(float(np.log(cfg.logit_scale))),
+          "text_model.embeddings.token_embedding.weight": tt(w["text.embeddings.word"]),
+          "text_model.embeddings.position_embedding.weight": tt(w["text.embeddings.position"]),
+          "text_model.final_layer_norm.weight": tt(w["text.ln.gamma"]),
+          "text_model.final_layer_norm.bias": tt(w["text.ln.beta"]),
+          "text_projection.weight": tt(w["text.proj.w"].T),
+          "vision_model.embeddings.class_embedding": tt(w["vision.embeddings.cls"].reshape(-1)),
+          "vision_model.embeddings.patch_embedding.weight": tt(w["vision.embeddings.patch.w"].transpose(0, 3, 1, 2)),
+          "vision_model.embeddings.position_embedding.weight": tt(w["vision.embeddings.position"]),
+          "vision_model.pre_layrnorm.weight": tt(w["vision.pre_ln.gamma"]),
+          "vision_model.pre_layrnorm.bias": tt(w["vision.pre_ln.beta"]),
+          "vision_model.post_layernorm.weight": tt(w["vision.ln.gamma"]),
+          "vision_model.post_layernorm.bias": tt(w["vision.ln.beta"]),
+          "visual_projection.weight": tt(w["vision.proj.w"].T)}
+    for tower, c, pre in (("vision.", v, "vision_model."), ("text.", t, "text_model.")):
+        for l in range(c.layers):
+            p, q = f"{tower}layer{l}.", f"{pre}encoder.layers.{l}."
+            for ours, theirs in (("attn.q", "self_attn.q_proj"), ("attn.k", "self_attn.k_proj"),
+                                 ("attn.v", "self_attn.v_proj"), ("attn.o", "self_attn.out_proj"),
+                                 ("ffn.up", "mlp.fc1"), ("ffn.down", "mlp.fc2")):
+                sd[q + theirs + ".weight"] = tt(w[p + ours + ".w"].T)
+                sd[q + theirs + ".bias"] = tt(w[p + ours + ".b"])
+            for ours, theirs in (("ln1", "layer_norm1"), ("ln2", "layer_norm2")):
+                sd[q + theirs + ".weight"] = tt(w[p + ours + ".gamma"])
+                sd[q + theirs + ".bias"] = tt(w[p + ours + ".beta"])
+    missing, unexpected = model.load_state_dict(sd, strict=False)
+    missing = [m for m in missing if "position_ids" not in m]
+    assert not missing and not unexpected, (missing, unexpected)
+    with torch.no_grad():
+        out = model(input_ids=torch.from_numpy(inputs["input_ids"]).long(),
+                    pixel_values=torch.from_numpy(inputs["pixel_values"]))
+    return out.logits_per_image.numpy()
+
+
 CASES = {
     # name: (config, weight seed, stress, pad_fraction)
     "bert_tiny_b1_s16": (EncoderConfig(layers=2, hidden=64, heads=1, ffn=256, vocab=100, max_pos=64,
@@ -133,6 +179,7 @@ CASES = {
                           13, True, 0.0),
     "opt_tiny_b2_s24": (EncoderConfig(model="opt", layers=2, hidden=128, heads=2, ffn=256, vocab=160, max_pos=64,
                                       types=0, batch=2, seq=24, eps=1e-5, act="relu"), 14, True, 0.0),
+    "clip_tiny_i3_t5": (clip_tiny(images=3, texts=5, layers=2), 15, True, 0.0),
 }
 
 
@@ -142,6 +189,9 @@ def main():
         if cfg.model == "vit":
             inp = make_vit_inputs(cfg, seed)
             out = hf_vit_forward(cfg, w, inp)
+        elif isinstance(cfg, ClipConfig):
+            inp = make_clip_inputs(cfg, seed)
+            out = hf_clip_forward(cfg, w, inp)  # logits_per_image; stored under the common key
         elif cfg.model == "opt":
             inp = make_inputs(cfg, seed)
             out = hf_opt_forward(cfg, w, inp)  # logits; stored under the common key

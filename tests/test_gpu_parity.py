@@ -2,9 +2,9 @@
 import numpy as np
 import pytest
 
-from mononn_b200 import (bert_base, bert_tiny, compile_encoder, compile_hlo, make_inputs, make_vit_inputs,
-                         make_weights, opt_tiny, vit_base, vit_tiny)
-from mononn_b200.hlo_builder import bert_hlo, opt_hlo, vit_hlo
+from mononn_b200 import (bert_base, bert_tiny, clip_b32, clip_tiny, compile_encoder, compile_hlo, make_clip_inputs,
+                         make_inputs, make_vit_inputs, make_weights, opt_tiny, vit_base, vit_tiny)
+from mononn_b200.hlo_builder import bert_hlo, clip_hlo, opt_hlo, vit_hlo
 from mononn_b200.models import EncoderConfig
 from oracle import ref_encoder as R
 from tests.helpers import assert_parity, golden_cases, load_golden, reference_fixture_inputs
@@ -37,6 +37,8 @@ def test_golden_vectors(name, frontend):
         pytest.skip("the config builder covers the BERT family only")
     if cfg.model == "vit":
         got = run_vit(cfg, w, make_vit_inputs(cfg, seed))
+    elif cfg.model == "clip":
+        got = run_clip(cfg, w, make_clip_inputs(cfg, seed))[0]
     elif cfg.model == "opt":
         got, ids = run_opt(cfg, w, make_inputs(cfg, seed))
         check_argmax(got, ids, load_golden(name)["last_hidden_state"])
@@ -238,3 +240,46 @@ def test_opt_wide_reduced_depth():
     ref, _ = R.opt_decoder(cfg, w, inp)
     assert_parity(logits, ref, "OPT-1.3B widths, 2 layers")
     check_argmax(logits, ids, ref)
+
+
+def run_clip(cfg, w, inp):
+    """(logits_per_image [images, texts], image_embeds, text_embeds) as f32."""
+    text, names = clip_hlo(cfg)
+    mod = compile_hlo(text, barrier_timeout_us=2000000)
+    mod.set_weights({names[k]: v for k, v in w.items()})
+    outs = mod.run([inp["pixel_values"], inp["input_ids"]])
+    mod.close()
+    ni, nt, p = cfg.vision.batch, cfg.text.batch, cfg.proj
+    return (outs[0][: ni * nt].reshape(ni, nt).astype(np.float32), outs[1][: ni * p].reshape(ni, p).astype(np.float32),
+            outs[2][: nt * p].reshape(nt, p).astype(np.float32))
+
+
+def check_clip(cfg, seed):
+    w = make_weights(cfg, seed, stress=True)
+    inp = make_clip_inputs(cfg, seed)
+    # repeat the largest id inside some sequences: the pooled row is the first occurrence
+    ids = inp["input_ids"]
+    for b in range(0, cfg.text.batch, 2):
+        ids[b, cfg.text.seq - 1] = ids[b].max()
+    logits, img, txt = run_clip(cfg, w, inp)
+    ref_logits, ref_img, ref_txt = R.clip_dual(cfg, w, inp)
+    assert_parity(img, ref_img, "image embeddings")
+    assert_parity(txt, ref_txt, "text embeddings")
+    assert_parity(logits, ref_logits, "image-text logits")
+
+
+@pytest.mark.parametrize("cfg", [
+    clip_tiny(),                                                    # 5 image tokens, 12 text tokens
+    clip_tiny(images=4, texts=7, image=96, layers=2, vh=128, th=128, seq=40, vocab=1000, proj=128),
+    clip_tiny(images=2, texts=3, image=224, layers=1, vh=192, th=64, seq=77, vocab=49408, proj=64),
+], ids=lambda c: f"i{c.vision.batch}t{c.text.batch}img{c.vision.image}s{c.text.seq}")
+def test_clip_shapes_against_oracle(cfg):
+    """Dual encoder: both towers scheduled into the same stages of one launch; LayerNorm that
+    starts a residual stream, class-row LayerNorm, pooling at the largest token id, L2
+    normalisation and the activation x activation logits product."""
+    check_clip(cfg, 91)
+
+
+def test_clip_b32_full_size():
+    """CLIP ViT-B/32 shape, 32 images x 32 texts."""
+    check_clip(clip_b32(), 1238)

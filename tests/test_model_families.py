@@ -3,8 +3,8 @@ recogniser finds in their HLO and what the scheduler plans for it."""
 import pytest
 
 from mononn_b200 import capi
-from mononn_b200.hlo_builder import opt_hlo, vit_hlo
-from mononn_b200.models import opt_1p3b, opt_tiny, vit_tiny
+from mononn_b200.hlo_builder import clip_hlo, opt_hlo, vit_hlo
+from mononn_b200.models import clip_b32, clip_tiny, opt_1p3b, opt_tiny, vit_tiny
 from mononn_b200.module import describe
 
 F_CAUSAL, F_SRC_F32, F_NO_NORM = 1 << 3, 1 << 5, 1 << 9
@@ -91,3 +91,58 @@ def test_full_size_decoder_cost(lib_built):
     weights = 2.0 * (cfg.layers * (per_layer + 9 * h + f) + 2 * h + h * v)
     assert abs(plan["algorithmic_bytes"] - weights) / weights < 0.01
     assert len(plan["stages"]) == 1 + 7 * cfg.layers + 3
+
+
+def _f32_regions(plan):
+    """(offset, bytes, first stage, last stage, first write accumulates) of every f32 scratch tensor."""
+    out = []
+    for t in plan["tensors"]:
+        if t["kind"] != "acc_f32":
+            continue
+        off = t["at"]["offset"]
+        first = None
+        for si, st in enumerate(plan["stages"]):
+            for o in st["ops"]:
+                writes_red = o["kind"] == "gemm" and o["out_mode"] == 2 and o["p"][0] == t["at"]
+                writes_plain = o["q"][2] == t["at"]
+                if first is None and (writes_red or writes_plain):
+                    first = "red" if writes_red else "plain"
+        out.append((off, t["rows"] * t["cols"] * 4, t["def_stage"], t["last_stage"], first == "red", t["name"]))
+    return out
+
+
+@pytest.mark.parametrize("towers", ["both", "vision", "text"])
+def test_accumulators_never_inherit_a_dirty_buffer(lib_built, towers):
+    """A GEMM accumulator whose first write is a reduction starts from zeros: it may reuse the
+    memory of an accumulator that its reader cleared, never that of a residual stream."""
+    plan = plan_of(clip_hlo(clip_tiny(layers=2), towers)[0])
+    regions = _f32_regions(plan)
+    assert any(r[4] for r in regions) and any(not r[4] for r in regions)
+    for a in regions:
+        for b in regions:
+            if a[4] and not b[4]:
+                overlap = not (a[0] + a[1] <= b[0] or b[0] + b[1] <= a[0])
+                assert not overlap, (a[5], b[5])
+
+
+def test_dual_encoder_structure(lib_built):
+    cfg = clip_tiny(layers=2)
+    plan = plan_of(clip_hlo(cfg)[0])
+    assert [a["name"] for a in plan["args"]] == ["pixel_values", "input_ids", "logits_per_image", "image_embeds",
+                                                 "text_embeds", "temp_buffer"]
+    att = ops_of(plan, "attention")
+    assert len(att) == 2 * cfg.vision.layers
+    assert sum(1 for o in att if o["flags"] & F_CAUSAL) == cfg.text.layers     # the text tower only
+    assert len(ops_of(plan, "rowsel")) == 1 and len(ops_of(plan, "pairdot")) == 1
+    l2 = [o for o in ops_of(plan, "layernorm") if o["flags"] & (1 << 10)]
+    assert len(l2) == 2
+    # both towers share stages: fewer stages than the two towers one after the other
+    alone = sum(len(plan_of(clip_hlo(cfg, t)[0])["stages"]) for t in ("vision", "text"))
+    assert len(plan["stages"]) < alone
+
+
+def test_full_size_dual_encoder_cost(lib_built):
+    plan = plan_of(clip_hlo(clip_b32())[0])
+    assert abs(plan["algorithmic_flops"] / 1e9 - 472.87) < 5.0
+    # every weight once, gathered token rows, the f32 pixels (19.27 MB) and the outputs
+    assert abs(plan["algorithmic_bytes"] / 1e6 - 273.8) < 1.0

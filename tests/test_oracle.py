@@ -2,7 +2,8 @@
 import numpy as np
 import pytest
 
-from mononn_b200.models import EncoderConfig, bert_tiny, make_inputs, make_vit_inputs, make_weights
+from mononn_b200.models import (EncoderConfig, bert_tiny, make_clip_inputs, make_inputs, make_vit_inputs,
+                                make_weights)
 from oracle import ref_encoder as R
 from tests.helpers import golden_cases, load_golden
 
@@ -14,6 +15,9 @@ def test_oracle_matches_golden_vectors(name):
     w = make_weights(cfg, seed, stress=stress)
     if cfg.model == "vit":
         out = R.vit_encoder(cfg, w, make_vit_inputs(cfg, seed))
+    elif cfg.model == "clip":
+        out, img, txt = R.clip_dual(cfg, w, make_clip_inputs(cfg, seed))
+        assert np.allclose(np.linalg.norm(img, axis=-1), 1.0, atol=1e-5)
     elif cfg.model == "opt":
         out, ids = R.opt_decoder(cfg, w, make_inputs(cfg, seed))
         assert np.array_equal(ids, g["last_hidden_state"].argmax(-1))  # the stored array holds the logits
@@ -58,6 +62,22 @@ def test_causal_decoder_ignores_later_tokens():
     other, _ = R.opt_decoder(cfg, w, inp2)
     assert np.abs(base[:7] - other[:7]).max() == 0.0   # positions before the change are untouched
     assert np.abs(base[7:] - other[7:]).max() > 1e-4
+
+
+def test_dual_encoder_pools_the_first_largest_id():
+    from mononn_b200.models import clip_tiny
+    cfg = clip_tiny()
+    w = make_weights(cfg, 4, stress=True)
+    inp = make_clip_inputs(cfg, 4)
+    ids = inp["input_ids"]
+    ids[:, :] = 5
+    ids[:, 3] = 150
+    base = R.clip_dual(cfg, w, inp)[2]
+    ids[:, 9] = 150                      # a later tie does not move the pooled row ...
+    causal_same = R.clip_dual(cfg, w, inp)[2]
+    assert np.abs(base - causal_same).max() < 1e-6   # ... and, being causal, row 3 does not see it
+    ids[:, 1] = 150                      # an earlier one does
+    assert np.abs(base - R.clip_dual(cfg, w, inp)[2]).max() > 1e-4
 
 
 def test_layer_norm_eps_and_biased_variance():
