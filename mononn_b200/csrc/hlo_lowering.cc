@@ -227,6 +227,25 @@ class Lowering {
     return ps;
   }
 
+  // Every layer of a model repeats the same fused computations; a computation that has been
+  // classified once (same instructions, shapes and attributes, same operand roles) is not
+  // evaluated again. Instruction names are not part of the key.
+  std::string memo_key(const char* what, const HloComputation& c, std::initializer_list<int> roles) const {
+    std::string k = what;
+    for (int r : roles) k += "," + std::to_string(r);
+    k += "|";
+    for (const HloInstr& i : c.instrs) {
+      k += i.opcode + ":" + i.shape.str() + "(";
+      for (int o : i.operands) k += std::to_string(o) + " ";
+      k += ")";
+      if (i.opcode == "parameter") k += std::to_string(i.param_number);
+      if (i.opcode == "constant") k += std::to_string(i.literal);
+      for (const auto& a : i.attrs) k += a.first + "=" + a.second + ";";
+      k += "\n";
+    }
+    return k;
+  }
+
   // ------------------------------------------------------------- custom-call
   int lower_custom_call(int idx) {
     const HloInstr& ins = e_.instrs[idx];
@@ -436,6 +455,14 @@ class Lowering {
     } else if (ins.shape.elements() != static_cast<int64_t>(M) * N) {
       return unsupported(ins, "result shape");
     }
+    ActKind found = ACT_NONE;
+    bool ok = false;
+    const std::string mkey = memo_key("epilogue", c, {main_k, bias_k, resid_k, split ? 1 : 0});
+    const auto hit = memo_.find(mkey);
+    if (hit != memo_.end()) {
+      found = static_cast<ActKind>(static_cast<int>(hit->second[0]));
+      ok = true;
+    } else {
     Rng rng;
     std::vector<HTensor> ps = probe_inputs(c, [&](size_t k, HTensor& t) {
       for (float& x : t.v) x = rng.uni(-2.f, 2.f);
@@ -445,8 +472,6 @@ class Lowering {
     int rc = probe(c, ps, &got);
     if (rc) return rc;
     const HTensor& x = ps[main_k];
-    ActKind found = ACT_NONE;
-    bool ok = false;
     for (ActKind act : {ACT_NONE, ACT_GELU_ERF, ACT_RELU, ACT_QUICK_GELU, ACT_GELU_TANH}) {
       std::vector<float> want(static_cast<size_t>(M) * N);
       for (uint32_t r = 0; r < M; ++r)
@@ -467,6 +492,8 @@ class Lowering {
         ok = true;
         break;
       }
+    }
+    if (ok) memo_[mkey] = {static_cast<double>(found)};
     }
     if (!ok) return unsupported(ins, "fused computation " + c.name + " matches no epilogue form act(x + bias) + residual");
     if (bias_k >= 0) gop.bias = const_tensor(vals_[ins.operands[bias_k]].instr, 1, N);
@@ -580,6 +607,20 @@ class Lowering {
       if (i.opcode == "constant" && i.literal_is_scalar && i.literal > 0 && i.literal < 0.1)
         eps_cands.push_back(static_cast<float>(i.literal));
     if (eps_cands.empty()) eps_cands.push_back(0.f);
+    int bias_k = -1, gamma_k = -1, beta_k = -1;
+    float eps_found = 0.f;
+    bool ok = false;
+    const std::string mkey = memo_key("layernorm", c, {main_k, resid_k, static_cast<int>(stride),
+                                                       static_cast<int>(mv.kind == Val::GEMM)});
+    const auto hit = memo_.find(mkey);
+    if (hit != memo_.end()) {
+      bias_k = static_cast<int>(hit->second[0]);
+      gamma_k = static_cast<int>(hit->second[1]);
+      beta_k = static_cast<int>(hit->second[2]);
+      eps_found = static_cast<float>(hit->second[3]);
+      off_found = static_cast<uint32_t>(hit->second[4]);
+      ok = true;
+    } else {
     // Probe with small-magnitude rows (variance ~1e-4) so that the epsilon under the square
     // root changes the result visibly; scale/shift stay O(1).
     Rng rng;
@@ -618,8 +659,7 @@ class Lowering {
     };
     std::vector<int> perm = vec_k;
     std::sort(perm.begin(), perm.end());
-    int bias_k = -1, gamma_k = -1, beta_k = -1;
-    float eps_found = 0.f, best = 1e30f;
+    float best = 1e30f;
     do {
       const int bk = perm.size() == 3 ? perm[0] : -1;
       const int gk = perm[perm.size() - 2], ek = perm[perm.size() - 1];
@@ -636,7 +676,10 @@ class Lowering {
         }
     } while (std::next_permutation(perm.begin(), perm.end()));
     off = off_found;
-    const bool ok = best < 1e-3f && max_error(bias_k, gamma_k, beta_k, eps_found, rows) < 1e-3f;
+    ok = best < 1e-3f && max_error(bias_k, gamma_k, beta_k, eps_found, rows) < 1e-3f;
+    if (ok) memo_[mkey] = {static_cast<double>(bias_k), static_cast<double>(gamma_k), static_cast<double>(beta_k),
+                           static_cast<double>(eps_found), static_cast<double>(off_found)};
+    }
     if (!ok) return unsupported(ins, "fused computation " + c.name + " matches no LayerNorm(x + bias + residual) form");
 
     FOp n;
@@ -710,7 +753,13 @@ class Lowering {
     }
     const uint32_t B = sv.B, H = sv.heads, S = sv.S;
     if (ins.shape.dims != std::vector<int64_t>{B, H, S, S}) return unsupported(ins, "result shape");
-    // probe on a reduced number of rows would need a different computation; scores are small
+    bool causal = false, ok = false;
+    const std::string mkey = memo_key("softmax", c, {main_k, mask_k});
+    const auto hit = memo_.find(mkey);
+    if (hit != memo_.end()) {
+      causal = hit->second[0] != 0.0;
+      ok = true;
+    } else {
     Rng rng;
     std::vector<HTensor> ps = probe_inputs(c, [&](size_t k, HTensor& t) {
       for (float& x : t.v) x = (static_cast<int>(k) == mask_k) ? (rng.uni(0.f, 1.f) < 0.25f ? -50.f : 0.f)
@@ -720,7 +769,6 @@ class Lowering {
     int rc = probe(c, ps, &got);
     if (rc) return rc;
     std::vector<float> want(got.v.size());
-    bool causal = false, ok = false;
     for (int trial = 0; trial < 2 && !ok; ++trial) {
       causal = (trial == 1);  // keys after the query position are excluded
       for (uint32_t b = 0; b < B; ++b)
@@ -744,6 +792,8 @@ class Lowering {
           }
       ok = all_close(got.v, want, 1e-5f, 1e-4f);
     }
+    if (ok) memo_[mkey] = {causal ? 1.0 : 0.0};
+    }
     if (!ok)
       return unsupported(ins, "fused computation " + c.name +
                                   " is not softmax(scores + mask) over the last dimension, plain or causal");
@@ -764,22 +814,26 @@ class Lowering {
     if (uses_[av.instr] != 1) return unsupported(ins, "attention output with more than one consumer");
     const uint32_t B = av.B, H = av.heads, S = av.S, D = av.D;
     if (ins.shape.elements() != static_cast<int64_t>(B) * H * S * D) return unsupported(ins, "result shape");
-    Rng rng;
-    std::vector<HTensor> ps = probe_inputs(c, [&](size_t, HTensor& t) {
-      for (float& x : t.v) x = rng.uni(-1.f, 1.f);
-    });
-    HTensor got;
-    int rc = probe(c, ps, &got);
-    if (rc) return rc;
-    std::vector<float> want(got.v.size());
-    for (uint32_t b = 0; b < B; ++b)
-      for (uint32_t h = 0; h < H; ++h)
-        for (uint32_t s = 0; s < S; ++s)
-          for (uint32_t d = 0; d < D; ++d)
-            want[(static_cast<size_t>(b) * S + s) * H * D + h * D + d] =
-                ps[0].v[((static_cast<size_t>(b) * H + h) * S + s) * D + d];
-    if (!all_close(got.v, want, 0.f, 0.f))
-      return unsupported(ins, "fused computation " + c.name + " is not the head merge [B,h,S,d] -> [B*S, h*d]");
+    const std::string mkey = memo_key("merge", c, {main_k});
+    if (!memo_.count(mkey)) {
+      Rng rng;
+      std::vector<HTensor> ps = probe_inputs(c, [&](size_t, HTensor& t) {
+        for (float& x : t.v) x = rng.uni(-1.f, 1.f);
+      });
+      HTensor got;
+      int rc = probe(c, ps, &got);
+      if (rc) return rc;
+      std::vector<float> want(got.v.size());
+      for (uint32_t b = 0; b < B; ++b)
+        for (uint32_t h = 0; h < H; ++h)
+          for (uint32_t s = 0; s < S; ++s)
+            for (uint32_t d = 0; d < D; ++d)
+              want[(static_cast<size_t>(b) * S + s) * H * D + h * D + d] =
+                  ps[0].v[((static_cast<size_t>(b) * H + h) * S + s) * D + d];
+      if (!all_close(got.v, want, 0.f, 0.f))
+        return unsupported(ins, "fused computation " + c.name + " is not the head merge [B,h,S,d] -> [B*S, h*d]");
+      memo_[mkey] = {1.0};
+    }
     FOp& aop = g_.ops[av.op];
     aop.out = act_tensor(canonical_node_name(ins.name), B * S, H * D);
     Val v;
@@ -1424,7 +1478,8 @@ class Lowering {
   std::vector<int> uses_;
   std::map<std::pair<int, bool>, int> const_tensors_;
   std::vector<Val> masks_;
-  std::map<int, Val> stream_of_;  // f16 LayerNorm output -> the f32 stream it was promoted to
+  std::map<int, Val> stream_of_;
+  std::map<std::string, std::vector<double>> memo_;  // classification results by memo_key  // f16 LayerNorm output -> the f32 stream it was promoted to
 };
 
 }  // namespace

@@ -125,8 +125,14 @@ enum StatusCode : uint32_t {
 
 // Shared-memory ring geometry (bytes).
 constexpr uint32_t kSlotBytes = 16384;  // one 128x64 f16 operand tile
-constexpr uint32_t kASlots = 6;
-constexpr uint32_t kBSlots = 7;
+#ifndef MONONN_A_SLOTS
+#define MONONN_A_SLOTS 6
+#endif
+#ifndef MONONN_B_SLOTS
+#define MONONN_B_SLOTS 7
+#endif
+constexpr uint32_t kASlots = MONONN_A_SLOTS;
+constexpr uint32_t kBSlots = MONONN_B_SLOTS;
 constexpr uint32_t kThreads = 256;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTraceEvents = 16;  // per (CTA, stage) slots of the optional event trace
