@@ -293,6 +293,77 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def stage_class(stage: dict) -> str:
+    """Operator class of a stage, e.g. 'gemm N2304 K768', 'attention', 'layernorm'."""
+    kinds = sorted({o["kind"] for o in stage["ops"]})
+    gemms = [o for o in stage["ops"] if o["kind"] == "gemm"]
+    if gemms:
+        n = sum(o["N"] for o in gemms)
+        return f"gemm N{n} K{gemms[0]['K']} split{gemms[0]['k_split']}" + ("" if kinds == ["gemm"] else " +" + "+".join(
+            k for k in kinds if k != "gemm"))
+    return "+".join(kinds)
+
+
+def run_diagnostics(args):
+    """Not a bench line. `--stages A:B` launches only stages [A, B) of the headline workload
+    `--steps` times (so that a profiler can capture one operator class alone) and prints their
+    time; `--stage-report` prints, per operator class, the time from the in-kernel event trace
+    and the share of the kernel spent between the last CTA finishing a stage's work and the
+    first CTA observing the barrier (release fence + arrive + propagation)."""
+    import numpy as np
+    import torch
+    from mononn_b200 import bert_base, compile_hlo, make_inputs, make_weights
+    from mononn_b200.hlo_builder import bert_hlo
+    torch.cuda.set_device(0)
+    cfg = bert_base()
+    w = make_weights(cfg, 1234)
+    inp = make_inputs(cfg, 1234)
+    text, names = bert_hlo(cfg)
+    mod = compile_hlo(text, device=0)
+    mod.set_weights({names[k]: v for k, v in w.items()})
+    mod.run([inp["input_ids"], inp["attention_mask"], inp["token_type_ids"]])
+    plan = mod.plan()
+    if args.stages:
+        a, b = (int(x) for x in args.stages.split(":"))
+        for _ in range(max(args.warmup, 1)):
+            mod.launch_stages(a, b)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            mod.launch_stages(a, b)
+        e1.record()
+        torch.cuda.synchronize()
+        mod.status()
+        print(json.dumps({"diagnostic": "stage_range", "stages": [a, b],
+                          "classes": [stage_class(st) for st in plan["stages"][a:b]],
+                          "us_per_launch": e0.elapsed_time(e1) * 1e3 / args.steps, "launches": args.steps}))
+    else:
+        for _ in range(5):
+            mod.launch()
+        mod.trace()
+        tr = mod.trace()
+        tr = np.where(tr == 0, np.nan, tr)
+        n_st = tr.shape[1]
+        ready = np.nanmin(tr[:, :, 0], axis=0)            # first CTA past the barrier
+        done = np.nanmax(tr[:, :, 1], axis=0)             # last CTA finished the stage's work
+        total = float(np.nanmax(tr[:, :, 2]) - ready[0])
+        per_class: dict[str, list[float]] = {}
+        sync = 0.0
+        for s_ in range(n_st):
+            end = ready[s_ + 1] if s_ + 1 < n_st else np.nanmax(tr[:, s_, 2])
+            sync += float(end - done[s_])
+            acc = per_class.setdefault(stage_class(plan["stages"][s_]), [0, 0.0, 0.0])
+            acc[0] += 1
+            acc[1] += float(end - ready[s_])
+            acc[2] += float(end - done[s_])
+        classes = {k: {"stages": v[0], "us_per_stage": v[1] / v[0] / 1e3, "share": v[1] / total,
+                       "barrier_us_per_stage": v[2] / v[0] / 1e3} for k, v in per_class.items()}
+        print(json.dumps({"diagnostic": "stage_report", "kernel_us": total / 1e3, "stages": n_st,
+                          "barrier_share": sync / total, "classes": classes}))
+    mod.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -304,8 +375,13 @@ def main():
     ap.add_argument("--tune", action="store_true", help="run the on-device tile search first")
     ap.add_argument("--no-flush", action="store_true", help="do not flush L2 between timed steps")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--stages", default="", help="diagnostic: launch only stages A:B of the workload")
+    ap.add_argument("--stage-report", action="store_true",
+                    help="diagnostic: per operator class time and the barrier's share, from the event trace")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.stages or args.stage_report:
+        run_diagnostics(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
