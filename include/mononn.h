@@ -96,6 +96,16 @@ int mononn_constant_info(const mononn_module* m, int i, const char** name, size_
  * argument pointers also uploads the re-bound stage table on the same stream. */
 int mononn_launch(mononn_module* m, void* const* device_args, int n, void* cuda_stream);
 
+/* One inference from and to HOST memory, the shape of the reference's user-facing call
+ * (`sess.run` on host tensors, examples/run_mononn.py:72-84): copies host_inputs[k] (one per
+ * parameter, by parameter number) into device_args, launches once, copies every live-out
+ * into host_outputs[j], reads the kernel's status word and waits for `cuda_stream`. Pinned
+ * host buffers make the copies asynchronous. Returns MONONN_ERR_BARRIER_TIMEOUT (and restores
+ * the module) when a bounded wait expired in the kernel. */
+int mononn_infer_host(mononn_module* m, const void* const* host_inputs, int n_inputs,
+                      void* const* host_outputs, int n_outputs, void* const* device_args, int n,
+                      void* cuda_stream);
+
 /* Synchronises the device, then reports the kernel's status word: 0, or
  * MONONN_ERR_BARRIER_TIMEOUT with the stage and CTA that gave up. */
 int mononn_last_status(mononn_module* m, int* stage, int* cta);

@@ -18,6 +18,7 @@ EXPORTS = [
     "mononn_save_spec", "mononn_spec_json", "mononn_profile_stages", "mononn_module_cost",
     "mononn_destroy", "mononn_strerror", "mononn_last_error", "mononn_enabled",
     "mononn_trace_stages", "mononn_plan_json", "mononn_describe", "mononn_free_string", "mononn_launch_stages", "mononn_debug_skew_barrier", "mononn_attention_noalloc",
+    "mononn_infer_host",
 ]
 
 
@@ -60,6 +61,7 @@ def lib() -> C.CDLL:
         l.mononn_constant_info.argtypes = [vp, C.c_int, C.POINTER(cp), C.POINTER(C.c_size_t)]
         l.mononn_launch.argtypes = [vp, C.POINTER(vp), C.c_int, vp]
         l.mononn_last_status.argtypes = [vp, ip, ip]
+        l.mononn_infer_host.argtypes = [vp, C.POINTER(vp), C.c_int, C.POINTER(vp), C.c_int, C.POINTER(vp), C.c_int, vp]
         l.mononn_tune.argtypes = [vp, C.POINTER(vp), C.c_int, vp]
         l.mononn_save_spec.argtypes = [vp, cp]
         l.mononn_spec_json.argtypes = [vp, C.POINTER(cp)]

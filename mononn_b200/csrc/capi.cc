@@ -169,6 +169,13 @@ int mononn_launch(mononn_module* m, void* const* device_args, int n, void* cuda_
   return m->rt.launch_all(device_args, n, cuda_stream);
 }
 
+int mononn_infer_host(mononn_module* m, const void* const* host_inputs, int n_inputs,
+                      void* const* host_outputs, int n_outputs, void* const* device_args, int n,
+                      void* cuda_stream) {
+  if (!m || !host_inputs || !host_outputs || !device_args) return fail(MONONN_ERR_INVALID_ARGUMENT, "null argument");
+  return m->rt.infer_host(host_inputs, n_inputs, host_outputs, n_outputs, device_args, n, cuda_stream);
+}
+
 int mononn_last_status(mononn_module* m, int* stage, int* cta) {
   if (!m) return fail(MONONN_ERR_INVALID_ARGUMENT, "null argument");
   return m->rt.check_status(stage, cta);

@@ -39,7 +39,8 @@ void Runtime::release() {
   if (d_scratch_) cudaFree(d_scratch_);
   if (d_table_) cudaFree(d_table_);
   if (d_trace_) cudaFree(d_trace_);
-  d_const_ = d_scratch_ = d_table_ = d_trace_ = nullptr;
+  if (h_status_) cudaFreeHost(h_status_);
+  d_const_ = d_scratch_ = d_table_ = d_trace_ = h_status_ = nullptr;
 }
 
 int Runtime::init(int device) {
@@ -303,6 +304,45 @@ int Runtime::launch(void* const* args, int n, void* stream, uint32_t stage_begin
   epoch_ += (stage_end - stage_begin) * plan_.grid;
   if (stamps) n_stamp_stages_ = stage_end - stage_begin;
   return MONONN_OK;
+}
+
+int Runtime::infer_host(const void* const* host_in, int n_in, void* const* host_out, int n_out,
+                        void* const* args, int n, void* stream) {
+  CUDA_TRY(cudaSetDevice(device_));
+  if (n != static_cast<int>(plan_.args.size())) {
+    set_last_error("argument count does not match the module");
+    return MONONN_ERR_INVALID_ARGUMENT;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int seen_in = 0, seen_out = 0;
+  for (const ArgDesc& a : plan_.args) seen_in += (a.kind == 0), seen_out += (a.kind == 1);
+  if (seen_in != n_in || seen_out != n_out) {
+    set_last_error("host buffer counts do not match the module's parameters / live-outs");
+    return MONONN_ERR_INVALID_ARGUMENT;
+  }
+  for (int i = 0; i < n; ++i) {
+    const ArgDesc& a = plan_.args[i];
+    if (a.kind == 0)
+      CUDA_TRY(cudaMemcpyAsync(args[i], host_in[a.param_number], a.bytes, cudaMemcpyHostToDevice, st));
+  }
+  int rc = launch_all(args, n, stream);
+  if (rc) return rc;
+  for (int i = 0; i < n; ++i) {
+    const ArgDesc& a = plan_.args[i];
+    if (a.kind == 1)
+      CUDA_TRY(cudaMemcpyAsync(host_out[a.param_number], args[i], a.bytes, cudaMemcpyDeviceToHost, st));
+  }
+  if (!h_status_) CUDA_TRY(cudaMallocHost(&h_status_, sizeof(KernelStatus)));
+  CUDA_TRY(cudaMemcpyAsync(h_status_, static_cast<uint8_t*>(d_scratch_) + kScratchStatusOff,
+                           sizeof(KernelStatus), cudaMemcpyDeviceToHost, st));
+  cudaError_t e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) {
+    set_last_error(std::string("kernel failed: ") + cudaGetErrorString(e));
+    return MONONN_ERR_CUDA;
+  }
+  if (static_cast<const KernelStatus*>(h_status_)->code == ST_OK) return MONONN_OK;
+  int stage = 0, cta = 0;
+  return check_status(&stage, &cta);  // formats the message and restores the module
 }
 
 int Runtime::check_status(int* stage, int* cta) {

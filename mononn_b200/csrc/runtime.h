@@ -48,6 +48,9 @@ class Runtime {
   int launch_all(void* const* args, int n, void* stream) {
     return launch(args, n, stream, 0, static_cast<uint32_t>(plan_.stages.size()), false);
   }
+  // Host buffers in, one launch, host buffers out, status word checked, stream synchronised.
+  int infer_host(const void* const* host_in, int n_in, void* const* host_out, int n_out,
+                 void* const* args, int n, void* stream);
   // cudaDeviceSynchronize + status word; resets barrier and accumulators after a failure.
   int check_status(int* stage, int* cta);
   int read_stamps(std::vector<double>* us);  // after a stamps launch + sync
@@ -77,6 +80,7 @@ class Runtime {
   void* d_scratch_ = nullptr;
   void* d_table_ = nullptr;
   void* d_trace_ = nullptr;
+  void* h_status_ = nullptr;  // pinned copy of the status word for infer_host
   bool trace_on_ = false;
   size_t table_bytes_ = 0, off_ops_ = 0, off_tmaps_ = 0;
   std::vector<uint8_t> h_table_;

@@ -35,15 +35,17 @@ static bool tile_legal(uint32_t N, uint32_t K, const GemmTileSpec& t, bool can_s
   return true;
 }
 
-// Bytes a CTA moves for one tile: the A slab (L2), the weight slab (HBM) and the
-// partial-sum reduction when K is split. A crude latency-free model; the tuner refines it.
+// Relative cost of one work item. On the device the main loop costs a fixed time per 64-wide
+// k-block (one MMA instruction takes about as long for a 16-column tile as for a 128-column
+// one) and the epilogue grows with the tile width; the byte count below is a proxy with the
+// same ordering (k-blocks weigh most, width a little, split-K adds its reduction). The tuner
+// measures the candidates on the device; at batch 1 it confirms these defaults.
 static double tile_cost(uint32_t M, uint32_t N, uint32_t K, const GemmTileSpec& t,
                         uint32_t cta_budget) {
   const uint32_t m_tiles = (M + 127) / 128, n_tiles = (N + t.n_tile - 1) / t.n_tile;
   const uint32_t items = m_tiles * n_tiles * t.k_split;
   const uint32_t waves = (items + cta_budget - 1) / cta_budget;
   const double kchunk = static_cast<double>(K) / t.k_split;
-  // A slab and weight slab both arrive through the SM's one memory port (~43 GB/s measured)
   double per_item = (128.0 + t.n_tile) * kchunk * 2.0;
   if (t.k_split > 1) per_item += 128.0 * t.n_tile * 4.0 * 2.0;  // f32 atomics
   per_item += 2000.0;                                            // fixed pipeline fill

@@ -170,6 +170,20 @@ class Module:
         self.status()
         return outs
 
+    def infer_host(self, host_inputs, host_outputs, stream=None) -> None:
+        """One inference between host buffers (torch CPU tensors, pinned for asynchronous
+        copies; inputs by parameter number, outputs by live-out order): H2D copies, one
+        launch, D2H copies, status check and stream synchronisation, all inside the library."""
+        if self._ptrs is None:
+            self.allocate()
+        key = tuple(t.data_ptr() for t in host_inputs) + tuple(t.data_ptr() for t in host_outputs)
+        if getattr(self, "_host_key", None) != key:  # pointer arrays are rebuilt only when the buffers change
+            self._host_key = key
+            self._host_in = (C.c_void_p * len(host_inputs))(*key[: len(host_inputs)])
+            self._host_out = (C.c_void_p * len(host_outputs))(*key[len(host_inputs):])
+        check(lib().mononn_infer_host(self._h, self._host_in, len(host_inputs), self._host_out, len(host_outputs),
+                                      self._ptrs, len(self._bufs), self._stream(stream)))
+
     def close(self) -> None:
         if self._h:
             lib().mononn_destroy(self._h)

@@ -136,3 +136,36 @@ def test_tuner_keeps_parity(tmp_path):
     assert_parity(run(mod, cfg, inp), R.bert_encoder(cfg, w, inp), "after tuning")
     assert (tmp_path / "cluster_0" / "tuning_log.log").exists()
     mod.close()
+
+
+def test_infer_host_matches_run_and_reports_timeouts():
+    """The host-buffer entry point (copies + launch + status in one call) gives the result of
+    the separate calls, twice in a row, and surfaces an expired wait as an error code."""
+    import torch
+    from mononn_b200 import capi
+    cfg = bert_tiny(batch=2, seq=24, layers=2, hidden=128, ffn=512)
+    w = make_weights(cfg, 21, stress=True)
+    inp = make_inputs(cfg, 21, pad_fraction=0.25)
+    mod = compile_encoder(cfg, barrier_timeout_us=20000)
+    mod.set_weights(w)
+    want = mod.run([inp["input_ids"], inp["attention_mask"], inp["token_type_ids"]])[0].copy()
+    hin = [torch.from_numpy(inp[k]).contiguous().view(torch.uint8).reshape(-1).pin_memory()
+           for k in ("input_ids", "attention_mask", "token_type_ids")]
+    out_bytes = [a["bytes"] for a in mod.args() if a["kind"] == 1][0]
+    hout = torch.zeros(out_bytes, dtype=torch.uint8).pin_memory()
+    for _ in range(2):
+        hout.zero_()
+        mod.infer_host(hin, [hout])
+        got = hout.numpy().view(np.float16)
+        # (split-K partial sums are added with atomics: two runs agree to rounding, not bit for bit)
+        assert np.abs(got[: want.size].astype(np.float32) - want[: got.size].astype(np.float32)).max() < 5e-3
+    with pytest.raises(capi.MononnError):
+        mod.infer_host(hin[:2], [hout])          # wrong number of host buffers
+    mod.debug_skew_barrier(1)
+    with pytest.raises(capi.MononnError) as e:
+        mod.infer_host(hin, [hout])
+    assert e.value.code == -6  # MONONN_ERR_BARRIER_TIMEOUT
+    mod.infer_host(hin, [hout])                   # usable again
+    got = hout.numpy().view(np.float16)
+    assert np.abs(got[: want.size].astype(np.float32) - want[: got.size].astype(np.float32)).max() < 5e-3
+    mod.close()
