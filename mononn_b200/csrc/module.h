@@ -42,6 +42,7 @@ int load_spec_dir(const std::string& dir, const std::string& module_name, Tuning
 int save_spec_dir(const std::string& dir, const std::string& module_name, const std::string& json,
                   const std::vector<PerfRow>& perf, const std::string& log, std::string* err);
 std::string cluster_dir_name(const std::string& module_name);
+bool make_dirs(const std::string& path);
 bool env_truthy(const char* name);
 // tuner.cc
 int tune_module(mononn_module* m, void* const* args, int n, void* stream);

@@ -315,7 +315,7 @@ int load_spec_dir(const std::string& dir, const std::string& module_name, Tuning
   return spec_from_json(text, spec, err);
 }
 
-static bool make_dirs(const std::string& path) {
+bool make_dirs(const std::string& path) {
   std::string cur;
   for (size_t i = 0; i <= path.size(); ++i) {
     if (i == path.size() || path[i] == '/') {

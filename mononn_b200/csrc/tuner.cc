@@ -9,6 +9,7 @@
 // by an nvcc subprocess, one candidate costs a re-pack of the affected weights plus a few
 // launches.
 #include <algorithm>
+#include <fstream>
 #include <sstream>
 #include <tuple>
 
@@ -24,19 +25,80 @@ struct ProblemKey {
            std::tie(o.M, o.N, o.K, o.flags, o.act, o.out_mode);
   }
 };
+
+// Per-measurement journal, <dump_dir>/<cluster_N>/tuning_progress.log: one line
+// "<label>\t<microseconds>" per timed spec, flushed as it is written. The search is
+// deterministic, so a tune that was interrupted (the reference cannot resume one:
+// its tuning_log.log is written at the end, mononn_module_tuner.cc:560-583) replays the
+// journal on its next run: measurements whose label matches, in order, are reused; from
+// the first difference on everything is measured again.
+struct Journal {
+  std::vector<std::pair<std::string, double>> old;
+  size_t next = 0;
+  int reused = 0;
+  std::ofstream out;
+
+  void open(const std::string& dump_dir, const std::string& module_name) {
+    if (dump_dir.empty()) return;
+    const std::string dir = dump_dir + "/" + cluster_dir_name(module_name);
+    if (!make_dirs(dir)) return;
+    const std::string path = dir + "/tuning_progress.log";
+    {
+      std::ifstream in(path);
+      std::string line;
+      while (std::getline(in, line)) {
+        const size_t tab = line.rfind('\t');
+        if (tab == std::string::npos) break;
+        char* end = nullptr;
+        const double us = std::strtod(line.c_str() + tab + 1, &end);
+        if (end == line.c_str() + tab + 1 || us <= 0) break;  // a torn last line ends the replay
+        old.push_back({line.substr(0, tab), us});
+      }
+    }
+    out.open(path, std::ios::trunc);
+  }
+  // Returns true and sets *us when the next journal entry is this measurement.
+  bool replay(const std::string& label, double* us) {
+    if (next < old.size() && old[next].first == label) {
+      *us = old[next++].second;
+      ++reused;
+      record(label, *us);
+      return true;
+    }
+    old.resize(next);  // diverged: nothing after this point can be trusted
+    return false;
+  }
+  void record(const std::string& label, double us) {
+    if (!out.is_open()) return;
+    out << label << '\t' << us << '\n';
+    out.flush();
+  }
+};
 }  // namespace
 
 int tune_module(mononn_module* m, void* const* args, int n, void* stream) {
   std::ostringstream log;
   const int warm = 3, iters = 20;
+  Journal journal;
+  journal.open(m->dump_dir, m->graph.module_name);
+  // one timed spec: replayed from the journal when possible, else lowered and measured
+  auto measure = [&](const std::string& label, const TuningSpec& spec, double* us) -> int {
+    if (journal.replay(label, us)) return MONONN_OK;
+    int r = m->lower(spec);
+    if (r) return r;
+    const uint32_t ns = static_cast<uint32_t>(m->rt.plan().stages.size());
+    r = m->rt.time_stages(args, n, stream, 0, ns, warm, iters, us);
+    if (r) return r;
+    journal.record(label, *us);
+    return MONONN_OK;
+  };
   TuningSpec best = m->rt.plan().spec;
   best.allow_list.clear();
   best.reject_list.clear();
   int rc = m->lower(best);
   if (rc) return rc;
-  const uint32_t n_stages = static_cast<uint32_t>(m->rt.plan().stages.size());
   double best_us = 0;
-  rc = m->rt.time_stages(args, n, stream, 0, n_stages, warm, iters, &best_us);
+  rc = measure("default", best, &best_us);
   if (rc) return rc;
   log << "default spec: " << best_us << " us\n";
   const double default_us = best_us;
@@ -70,10 +132,11 @@ int tune_module(mononn_module* m, void* const* args, int n, void* stream) {
         if (c.n_tile == cur.n_tile && c.k_split == cur.k_split) continue;
         TuningSpec trial = best;
         for (const std::string& node : kv.second) trial.gemm[node] = c;
-        rc = m->lower(trial);
-        if (rc) return rc;
         double us = 0;
-        rc = m->rt.time_stages(args, n, stream, 0, n_stages, warm, iters, &us);
+        std::ostringstream label;
+        label << "M" << k.M << " N" << k.N << " K" << k.K << " f" << k.flags << " a" << k.act << " o" << k.out_mode
+              << " n_tile " << c.n_tile << " k_split " << c.k_split;
+        rc = measure(label.str(), trial, &us);
         if (rc) return rc;
         log << "M" << k.M << " N" << k.N << " K" << k.K << " n_tile " << c.n_tile << " k_split "
             << c.k_split << ": " << us << " us\n";
@@ -89,8 +152,12 @@ int tune_module(mononn_module* m, void* const* args, int n, void* stream) {
   rc = m->lower(best);
   if (rc) return rc;
   double final_us = 0;
-  rc = m->rt.time_stages(args, n, stream, 0, n_stages, warm, iters, &final_us);
-  if (rc) return rc;
+  {
+    const uint32_t ns = static_cast<uint32_t>(m->rt.plan().stages.size());
+    rc = m->rt.time_stages(args, n, stream, 0, ns, warm, iters, &final_us);
+    if (rc) return rc;
+  }
+  if (journal.reused) log << "reused " << journal.reused << " measurements of an earlier run\n";
   log << "merged spec: " << final_us << " us (default " << default_us << " us)\n";
   if (final_us > default_us) {
     rc = m->lower(default_spec);

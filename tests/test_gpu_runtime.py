@@ -138,6 +138,33 @@ def test_tuner_keeps_parity(tmp_path):
     mod.close()
 
 
+def test_interrupted_tuning_resumes_from_its_journal(tmp_path):
+    """Every timed candidate is journalled as it is measured; a later tune of the same module
+    replays the journal (all of it, or the part an interrupted run got to) instead of
+    measuring again, and ends with the same spec."""
+    cfg, w, inp = small()
+    journal = tmp_path / "cluster_0" / "tuning_progress.log"
+
+    def tune_once():
+        mod = compile_encoder(cfg, tuning_level=1, dump_dir=str(tmp_path))
+        mod.set_weights(w)
+        mod.tune()
+        spec = mod.spec()["gemm_spec_list"]
+        log = (tmp_path / "cluster_0" / "tuning_log.log").read_text()
+        mod.close()
+        return spec, log
+
+    spec1, log1 = tune_once()
+    lines = journal.read_text().splitlines()
+    assert len(lines) > 3 and lines[0].startswith("default\t") and "reused" not in log1
+    spec2, log2 = tune_once()                                  # complete journal: nothing is timed twice
+    assert f"reused {len(lines)} measurements" in log2 and spec2 == spec1
+    journal.write_text("\n".join(lines[: len(lines) // 2]) + "\nM128 N1 K1 torn li")   # an interrupted run
+    spec3, log3 = tune_once()
+    assert f"reused {len(lines) // 2} measurements" in log3
+    assert len(journal.read_text().splitlines()) == len(lines)
+
+
 def test_infer_host_matches_run_and_reports_timeouts():
     """The host-buffer entry point (copies + launch + status in one call) gives the result of
     the separate calls, twice in a row, and surfaces an expired wait as an error code."""
