@@ -100,7 +100,9 @@ int mononn_launch(mononn_module* m, void* const* device_args, int n, void* cuda_
  * (`sess.run` on host tensors, examples/run_mononn.py:72-84): copies host_inputs[k] (one per
  * parameter, by parameter number) into device_args, launches once, copies every live-out
  * into host_outputs[j], reads the kernel's status word and waits for `cuda_stream`. Pinned
- * host buffers make the copies asynchronous. Returns MONONN_ERR_BARRIER_TIMEOUT (and restores
+ * host buffers make the copies asynchronous. Where device_args[i] IS the host buffer (pinned
+ * memory is device-addressable under unified addressing) no copy is issued: the kernel reads
+ * the parameter from, or writes the live-out to, host memory directly. Returns MONONN_ERR_BARRIER_TIMEOUT (and restores
  * the module) when a bounded wait expired in the kernel. */
 int mononn_infer_host(mononn_module* m, const void* const* host_inputs, int n_inputs,
                       void* const* host_outputs, int n_outputs, void* const* device_args, int n,

@@ -428,7 +428,7 @@ __device__ void role_weight_producer(Ctx c) {
         WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->b_empty[slot], (use & 1u) ^ 1u, 0x100));
         const uint32_t full = smem_u32(&c.ctrl->b_full[slot]);
         mbar_arrive_expect_tx(full, bytes);
-        tma_load_2d(c.b_ring + slot * kSlotBytes, tm, 0, static_cast<int32_t>(row0 + kb * op.n_tile),
+        tma_load_2d(c.b_ring + slot * kBSlotBytes, tm, 0, static_cast<int32_t>(row0 + kb * op.n_tile),
                     full);
         ++b_cnt;
       }
@@ -553,7 +553,7 @@ __device__ void role_mma(Ctx c, uint32_t tmem_base) {
           tc_fence_after();
           const uint64_t ad = umma_desc_sw128(c.a_ring + a_slot * kSlotBytes);
           const uint64_t bd =
-              umma_desc_sw128(c.b_ring + b_slot * kSlotBytes + sub * op.n_tile * 128u);
+              umma_desc_sw128(c.b_ring + b_slot * kBSlotBytes + sub * op.n_tile * 128u);
 #pragma unroll
           for (uint32_t k = 0; k < 4; ++k)
             tc_mma_f16(tmem_d, ad + 2u * k, bd + 2u * k, idesc, (kb | k) != 0u);
@@ -1326,7 +1326,7 @@ mononn_megakernel(const __grid_constant__ KernelParams P) {
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw & 1023u)) & 1023u;
   uint8_t* base = smem_raw + pad;
-  Ctrl* ctrl = reinterpret_cast<Ctrl*>(base + (kASlots + kBSlots) * kSlotBytes);
+  Ctrl* ctrl = reinterpret_cast<Ctrl*>(base + kASlots * kSlotBytes + kBSlots * kBSlotBytes);
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   if (threadIdx.x == 0) {

@@ -322,14 +322,15 @@ int Runtime::infer_host(const void* const* host_in, int n_in, void* const* host_
   }
   for (int i = 0; i < n; ++i) {
     const ArgDesc& a = plan_.args[i];
-    if (a.kind == 0)
+    // (a parameter bound to the host buffer itself -- mapped pinned memory -- is read in place)
+    if (a.kind == 0 && args[i] != host_in[a.param_number])
       CUDA_TRY(cudaMemcpyAsync(args[i], host_in[a.param_number], a.bytes, cudaMemcpyHostToDevice, st));
   }
   int rc = launch_all(args, n, stream);
   if (rc) return rc;
   for (int i = 0; i < n; ++i) {
     const ArgDesc& a = plan_.args[i];
-    if (a.kind == 1)
+    if (a.kind == 1 && args[i] != host_out[a.param_number])
       CUDA_TRY(cudaMemcpyAsync(host_out[a.param_number], args[i], a.bytes, cudaMemcpyDeviceToHost, st));
   }
   if (!h_status_) CUDA_TRY(cudaMallocHost(&h_status_, sizeof(KernelStatus)));

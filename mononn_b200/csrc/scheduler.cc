@@ -26,7 +26,7 @@ static bool tile_legal(uint32_t N, uint32_t K, const GemmTileSpec& t, bool can_s
   // UMMA N is a multiple of 16 up to 256, and one k-block of the tile (n_tile rows of 128
   // bytes) has to fit a weight-ring slot
   if (t.n_tile < 16 || t.n_tile > 256 || (t.n_tile % 16) != 0) return false;
-  if (t.n_tile * 128u > kSlotBytes) return false;
+  if (t.n_tile * 128u > kBSlotBytes) return false;
   if (t.k_split < 1) return false;
   const uint32_t kb = (K + 63) / 64;
   if (kb % t.k_split != 0) return false;
@@ -57,7 +57,7 @@ std::vector<GemmTileSpec> gemm_tile_candidates(uint32_t M, uint32_t N, uint32_t 
   std::vector<GemmTileSpec> out;
   const uint32_t kb = (K + 63) / 64;
   const uint32_t m_tiles = (M + 127) / 128;
-  for (uint32_t n_tile : {16u, 32u, 48u, 64u, 96u, 128u}) {
+  for (uint32_t n_tile : {16u, 32u, 48u, 64u, 96u, 128u, 192u, 256u}) {
     if (n_tile > std::max(16u, (N + 15) / 16 * 16)) continue;
     for (uint32_t ks = 1; ks <= kb; ++ks) {
       GemmTileSpec t;
@@ -157,7 +157,7 @@ int validate_plan(const Plan& P, std::string* err) {
       case OP_GEMM: {
         if (d.n_tile < 16 || d.n_tile > 256 || d.n_tile % 16) return bad(n + "n_tile");
         if (d.n_tile > kAccCols) return bad(n + "n_tile exceeds an accumulator buffer");
-        if (d.kb_per_bslot == 0 || d.n_tile * d.kb_per_bslot * 128u > kSlotBytes)
+        if (d.kb_per_bslot == 0 || d.n_tile * d.kb_per_bslot * 128u > kBSlotBytes)
           return bad(n + "weight tile exceeds a ring slot");
         if (d.n_tile * d.kb_per_bslot > 256) return bad(n + "TMA box taller than 256 rows");
         if (d.k_split == 0 || d.kb_per_split == 0 || d.k_split * d.kb_per_split * 64u != d.K)
@@ -503,7 +503,7 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
           d.n_tiles = (o.N + ts.n_tile - 1) / ts.n_tile;
           const uint32_t kb = o.K / 64;
           d.kb_per_split = kb / ts.k_split;
-          d.kb_per_bslot = std::max(1u, std::min(d.kb_per_split, kSlotBytes / (ts.n_tile * 128u)));
+          d.kb_per_bslot = std::max(1u, std::min(d.kb_per_split, kBSlotBytes / (ts.n_tile * 128u)));
           d.n_items = d.m_tiles * d.n_tiles * d.k_split;
           d.tmap_a = tmap_for_act(o.a);
           (void)A;

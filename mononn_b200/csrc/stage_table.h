@@ -124,12 +124,13 @@ enum StatusCode : uint32_t {
 };
 
 // Shared-memory ring geometry (bytes).
-constexpr uint32_t kSlotBytes = 16384;  // one 128x64 f16 operand tile
+constexpr uint32_t kSlotBytes = 16384;   // activation ring slot: one 128x64 f16 operand tile
+constexpr uint32_t kBSlotBytes = 32768;  // weight ring slot: up to 256 rows of 64 f16 (one TMA box)
 #ifndef MONONN_A_SLOTS
 #define MONONN_A_SLOTS 6
 #endif
 #ifndef MONONN_B_SLOTS
-#define MONONN_B_SLOTS 7
+#define MONONN_B_SLOTS 3
 #endif
 constexpr uint32_t kASlots = MONONN_A_SLOTS;
 constexpr uint32_t kBSlots = MONONN_B_SLOTS;

@@ -170,6 +170,19 @@ class Module:
         self.status()
         return outs
 
+    def bind_host_io(self, host_inputs, host_outputs) -> None:
+        """Zero-copy I/O: bind the parameters and live-outs to PINNED host tensors (inputs by
+        parameter number, outputs by live-out order), so that the kernel reads and writes host
+        memory itself and `infer_host` on the same tensors issues no copies."""
+        if self._ptrs is None:
+            self.allocate()
+        descs = self.args()
+        for d in descs:
+            if d["kind"] == 0:
+                self._ptrs[d["index"]] = host_inputs[d["param_number"]].data_ptr()
+            elif d["kind"] == 1:
+                self._ptrs[d["index"]] = host_outputs[d["param_number"]].data_ptr()
+
     def infer_host(self, host_inputs, host_outputs, stream=None) -> None:
         """One inference between host buffers (torch CPU tensors, pinned for asynchronous
         copies; inputs by parameter number, outputs by live-out order): H2D copies, one

@@ -110,16 +110,20 @@ def test_spec_controls_the_tiles_and_round_trips(lib_built, tmp_path):
 
 
 def test_tiles_wider_than_a_ring_slot_are_never_planned(lib_built):
-    # a 16-CTA grid once made the heuristic pick a 192-column tile (24 KB for a 16 KB slot)
+    # a 16-CTA grid once made the heuristic pick a tile whose weight slab overflowed its ring
+    # slot; a spec asking for one (320 columns = 40 KB for a 32 KB slot) is not honoured either
     cfg = bert_base()
     spec = describe("encoder", cfg.to_json())["spec"]
     spec["cuda_context"]["cuda_runtime_context"]["grid_dim"]["x"] = 16
-    spec["gemm_spec_list"] = {"layer0.ffn.up": {"sm100_config": {"mma_n": 192, "k_split": 1}}}
+    spec["gemm_spec_list"] = {"layer0.ffn.up": {"sm100_config": {"mma_n": 320, "k_split": 1}}}
     p = describe("encoder", cfg.to_json(), spec=spec)["plan"]
+    widest = 0
     for st in p["stages"]:
         for o in st["ops"]:
             if o["kind"] == "gemm":
-                assert o["n_tile"] * o["kb_per_bslot"] * 128 <= 16384
+                assert o["n_tile"] * o["kb_per_bslot"] * 128 <= 32768 and o["n_tile"] <= 256
+                widest = max(widest, o["n_tile"])
+    assert widest > 128   # with 16 CTAs the wide tiles are what the heuristic wants
 
 
 def test_long_sequences_and_large_batches_lower(lib_built):
