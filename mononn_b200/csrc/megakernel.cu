@@ -109,6 +109,25 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
+// Issue only: the registers are valid after the next tc_wait_ld(). Lets the following load be in
+// flight while the previous one is processed.
+__device__ __forceinline__ void tc_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
+  __syncwarp();
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
   uint32_t r[32];
   __syncwarp();
@@ -389,8 +408,16 @@ __device__ __forceinline__ AttnTile attn_tile(const OpDesc& op, uint32_t local) 
 // slots of an item, in allocation order: Q, K_0..K_{n-1}, then per chunk V^T_j, P_j (two
 // slots, written by the softmax warps).
 constexpr uint32_t kAttnOutCol = 448;
+// With F_FUSED_QKV (sequences up to 128) the item first computes [Q_h | K_h | V_h] = x_b W_h: the
+// K/64 k-block tiles of x come through the activation ring before the five attention slots, the
+// 192-column accumulator sits at columns kAttnQkvCol.., and the softmax warps turn it into the
+// Q, K and V^T operand tiles in the slots that the activation producer would have loaded.
+constexpr uint32_t kAttnQkvCol = 192;
+__device__ __forceinline__ bool attn_fused(const OpDesc& op) { return (op.flags & F_FUSED_QKV) != 0u; }
 __device__ __forceinline__ uint32_t attn_chunks(const OpDesc& op) { return (op.seq + 127u) / 128u; }
-__device__ __forceinline__ uint32_t attn_slots(const OpDesc& op) { return 1u + 4u * attn_chunks(op); }
+__device__ __forceinline__ uint32_t attn_slots(const OpDesc& op) {
+  return 1u + 4u * attn_chunks(op) + (attn_fused(op) ? op.kb_per_split : 0u);
+}
 
 // The CTAs of a GEMM stage all walk the same K range of the A operand. Starting each CTA at
 // a different k-block group (and wrapping around) spreads their simultaneous tile requests
@@ -411,9 +438,49 @@ __device__ void role_weight_producer(Ctx c) {
   for (uint32_t s = P.stage_begin; s < P.stage_end; ++s) {
     c.stage = s;
     const StageDesc st = load_stage(P, s);
+    if (blockIdx.x >= st.n_items) {
+      // This CTA has no work in the stage. If the stage holds attention items that compute their
+      // own projections, only a few SMs will pull those weights, each through a three-slot ring:
+      // bring the weights into L2 now (this role runs ahead of the barriers), shared out over
+      // the idle CTAs, so that the few stream them from L2 instead of HBM.
+      const uint32_t n_idle = gridDim.x - st.n_items, me = blockIdx.x - st.n_items;
+      for (uint32_t k = 0; k < st.op_count; ++k) {
+        const OpDesc* gop = P.ops + st.op_begin + k;
+        if (__ldg(&gop->kind) != OP_ATTENTION || !(__ldg(&gop->flags) & F_FUSED_QKV)) continue;
+        const uint32_t chunks = (__ldg(&gop->heads) * __ldg(&gop->K) * 128u) >> 14;  // 16 KB units per weight
+        for (uint32_t j = 0; j < 3; ++j) {
+          const uint8_t* wbase = reinterpret_cast<const uint8_t*>(__ldg(&gop->p[5 + j]));
+          for (uint32_t ch = me; ch < chunks; ch += n_idle)
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(wbase + (static_cast<size_t>(ch) << 14)),
+                         "r"(16384u)
+                         : "memory");
+        }
+      }
+    }
     for (uint32_t item = blockIdx.x; item < st.n_items; item += gridDim.x) {
       const Item it = fetch_item<false>(P, st, item, c.ctrl->desc[0], 0);
       const OpDesc& op = *it.op;
+      if (op.kind == OP_ATTENTION && attn_fused(op)) {
+        // per k-block one slot: the 64-row tiles of head h of the Q, K and V weights, stacked
+        const AttnTile t = attn_tile(op, it.local);
+        const uint32_t nkb = op.kb_per_split;
+        const void* tmw[3] = {tmaps + static_cast<size_t>(op.tmap_b) * 128u,
+                              tmaps + static_cast<size_t>(op.tmap_vt) * 128u,
+                              tmaps + static_cast<size_t>(op.vocab) * 128u};
+        for (uint32_t kb = 0; kb < nkb; ++kb) {
+          const uint32_t slot = b_cnt % kBSlots, use = b_cnt / kBSlots;
+          WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->b_empty[slot], (use & 1u) ^ 1u, 0x101));
+          const uint32_t full = smem_u32(&c.ctrl->b_full[slot]);
+          mbar_arrive_expect_tx(full, 3u * 8192u);
+#pragma unroll
+          for (uint32_t j = 0; j < 3; ++j)
+            tma_load_2d(c.b_ring + slot * kBSlotBytes + j * 8192u, tmw[j], 0,
+                        static_cast<int32_t>((t.h * nkb + kb) * 64u), full);
+          ++b_cnt;
+        }
+        trace(P, s, TR_W_ISSUED);
+        continue;
+      }
       if (op.kind != OP_GEMM) continue;
       const GemmTile t = gemm_tile(op, it.local);
       const uint32_t nkb = op.kb_per_split, kbps = op.kb_per_bslot;
@@ -492,6 +559,21 @@ __device__ void role_act_producer(Ctx c) {
         const void* tmk = tmaps + static_cast<size_t>(op.tmap_b) * 128u;
         const void* tmv = tmaps + static_cast<size_t>(op.tmap_vt) * 128u;
         const uint32_t nc = attn_chunks(op);
+        if (attn_fused(op)) {
+          // the k-block tiles of this batch's rows of x; Q, K, V^T and P are written on chip
+          for (uint32_t kb = 0; kb < op.kb_per_split; ++kb) {
+            const uint32_t slot = a_cnt % kASlots, use = a_cnt / kASlots;
+            WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->a_empty[slot], (use & 1u) ^ 1u, 0x203));
+            const uint32_t full = smem_u32(&c.ctrl->a_full[slot]);
+            mbar_arrive_expect_tx(full, kSlotBytes);
+            tma_load_2d(c.a_ring + slot * kSlotBytes, tm, static_cast<int32_t>(kb * 64u),
+                        static_cast<int32_t>(t.b * op.seq), full);
+            ++a_cnt;
+          }
+          a_cnt += 5;
+          trace(P, s, TR_ACT_ISSUED);
+          continue;
+        }
         // Q, K_0 .. K_{nc-1}, then V^T_j for every chunk (the P slots in between are skipped)
         for (uint32_t j = 0; j < 1u + 2u * nc; ++j) {
           if (j > nc) a_cnt += (j == nc + 1u) ? 0u : 2u;  // step over the previous chunk's P slots
@@ -568,12 +650,39 @@ __device__ void role_mma(Ctx c, uint32_t tmem_base) {
         ++acc_cnt;
         trace(P, s, TR_MMA_LAST);
       } else if (op.kind == OP_ATTENTION) {
-        const uint32_t nc = attn_chunks(op), base = a_cnt;
+        const uint32_t nc = attn_chunks(op);
+        uint32_t base = a_cnt, ph = acc_cnt;
         a_cnt += attn_slots(op);
         auto slot_of = [](uint32_t cnt) { return cnt % kASlots; };
         auto par_of = [](uint32_t cnt) { return (cnt / kASlots) & 1u; };
+        if (attn_fused(op)) {
+          // [Q_h | K_h | V_h] = x_b W_h into 192 columns; the accumulator overlaps both GEMM buffers
+          const uint32_t phQ = ph++, nkb = op.kb_per_split;
+          WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->acc_empty[phQ & 1u], ((phQ >> 1) & 1u) ^ 1u, 0x320));
+          WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->acc_empty[ph & 1u], ((ph >> 1) & 1u) ^ 1u, 0x321));
+          tc_fence_after();
+          const uint32_t idesc = umma_idesc_m128(192);
+          for (uint32_t kb = 0; kb < nkb; ++kb) {
+            const uint32_t b_slot = b_cnt % kBSlots, a_c = base + kb;
+            WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->b_full[b_slot], (b_cnt / kBSlots) & 1u, 0x322));
+            WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->a_full[slot_of(a_c)], par_of(a_c), 0x323));
+            if (kb == 0) trace(P, s, TR_MMA_FIRST);
+            tc_fence_after();
+            const uint64_t ad = umma_desc_sw128(c.a_ring + slot_of(a_c) * kSlotBytes);
+            const uint64_t bd = umma_desc_sw128(c.b_ring + b_slot * kBSlotBytes);
+#pragma unroll
+            for (uint32_t k = 0; k < 4; ++k)
+              tc_mma_f16(tmem_base + kAttnQkvCol, ad + 2u * k, bd + 2u * k, idesc, (kb | k) != 0u);
+            tc_commit(smem_u32(&c.ctrl->a_empty[slot_of(a_c)]));
+            tc_commit(smem_u32(&c.ctrl->b_empty[b_slot]));
+            ++b_cnt;
+          }
+          tc_commit(smem_u32(&c.ctrl->acc_full[phQ & 1u]));
+          trace(P, s, TR_MMA_LAST);
+          base += nkb;
+        }
         // the scores may span both accumulator buffers: both must have been drained
-        const uint32_t phS = acc_cnt, phO = acc_cnt + 1u;
+        const uint32_t phS = ph, phO = ph + 1u;
         WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->acc_empty[phS & 1u], ((phS >> 1) & 1u) ^ 1u, 0x310));
         WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->acc_empty[phO & 1u], ((phO >> 1) & 1u) ^ 1u, 0x313));
         // S_j = Q K_j^T  (128 x 128, K = 64) into columns j*128
@@ -611,7 +720,7 @@ __device__ void role_mma(Ctx c, uint32_t tmem_base) {
           for (uint32_t q = 0; q < 3; ++q) tc_commit(smem_u32(&c.ctrl->a_empty[slot_of(vc + q)]));
         }
         tc_commit(smem_u32(&c.ctrl->acc_full[phO & 1u]));
-        acc_cnt += 2;
+        acc_cnt = ph + 2u;
       }
     }
   }
@@ -1113,10 +1222,13 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
   const AttnTile t = attn_tile(op, local);
   const uint32_t row = quarter * 32u + lane;
   const uint32_t qrow = t.mt * 128u + row;  // query index inside the sequence
-  const uint32_t nc = attn_chunks(op), base = a_cnt;
+  const uint32_t nc = attn_chunks(op);
+  const bool fused = attn_fused(op);
+  uint32_t base = a_cnt;
   a_cnt += attn_slots(op);
-  const uint32_t phS = acc_cnt, phO = acc_cnt + 1u;
-  acc_cnt += 2;
+  const uint32_t phQ = acc_cnt;
+  const uint32_t phS = acc_cnt + (fused ? 1u : 0u), phO = phS + 1u;
+  acc_cnt = phO + 1u;
   const uint32_t seq = op.seq, n_cols = nc * 128u;
   const float alpha = op.alpha * 1.4426950408889634f;  // scores in log2 units: exp(x) = 2^(x log2 e)
   // Stage the additive key mask of this batch row while Q, K load and QK^T runs; keys past
@@ -1130,7 +1242,75 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
       if (i < seq) m = has_mask ? __ldcg(gm + i) : 0.f;
       mb[i] = m * 1.4426950408889634f;
     }
+    if (fused) {  // biases of this head's Q, K, V columns
+      float* bs = c.ctrl->bias_tile[0];
+      for (uint32_t i = tid_in_group; i < 192u; i += 128u) {
+        const __half* bp = reinterpret_cast<const __half*>(op.p[2u + (i >> 6)]);
+        bs[i] = bp ? __half2float(__ldg(bp + t.h * 64u + (i & 63u))) : 0.f;
+      }
+    }
     if (!group_sync(c, 0x415)) return false;
+  }
+  if (fused) {
+    // accumulator [tokens, Q | K | V] -> f16 operand tiles: Q and K row-major (token, d), V
+    // transposed (d, token) in two 64-key halves, all in the 128-byte-swizzled K-major layout
+    base += op.kb_per_split;
+    const uint32_t cQ = base, cK = base + 1u, cV = base + 2u;
+    // The accumulator is complete when every x tile has been consumed, and the commits that free
+    // the tiles' slots precede the accumulator's: after this wait the three slots written below
+    // (which x tiles occupied) are free. (Testing their empty barriers before it could be
+    // fooled: two uses of a slot may be pending at once, and a parity wait cannot tell 0 from 2.)
+    if (!mbar_wait_warp(c, &c.ctrl->acc_full[phQ & 1u], (phQ >> 1) & 1u, 0x419)) return false;
+    if (!mbar_wait_warp(c, &c.ctrl->a_empty[cQ % kASlots], ((cQ / kASlots) & 1u) ^ 1u, 0x416)) return false;
+    if (!mbar_wait_warp(c, &c.ctrl->a_empty[cK % kASlots], ((cK / kASlots) & 1u) ^ 1u, 0x417)) return false;
+    if (!mbar_wait_warp(c, &c.ctrl->a_empty[cV % kASlots], ((cV / kASlots) & 1u) ^ 1u, 0x418)) return false;
+    tc_fence_after();
+    const float* bs = c.ctrl->bias_tile[0];
+    const uint32_t tQ = tmem_base + kAttnQkvCol + ((quarter * 32u) << 16);
+    uint8_t* tileV = c.a_ring_ptr + (cV % kASlots) * kSlotBytes + (row >> 6) * 8192u;
+    // one 32-column load is in flight while the previous one is converted and stored
+    auto convert = [&](const uint32_t (&r)[32], uint32_t c0) {
+      float v[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) + bs[c0 + i];
+      if (c0 < 128u) {
+        uint8_t* tile = c.a_ring_ptr + (((c0 < 64u) ? cQ : cK) % kASlots) * kSlotBytes;
+        const uint32_t chunk = (c0 & 63u) >> 3;
+#pragma unroll
+        for (uint32_t q = 0; q < 4; ++q) {
+          uint4* d = reinterpret_cast<uint4*>(tile + row * 128u + (((chunk + q) ^ (row & 7u)) << 4));
+          *d = make_uint4(pack_h2(v[8 * q], v[8 * q + 1]), pack_h2(v[8 * q + 2], v[8 * q + 3]),
+                          pack_h2(v[8 * q + 4], v[8 * q + 5]), pack_h2(v[8 * q + 6], v[8 * q + 7]));
+        }
+      } else {
+        const uint32_t d0 = c0 - 128u, kc = (row & 63u) >> 3, kw = (row & 7u) << 1;
+#pragma unroll
+        for (uint32_t i = 0; i < 32; ++i) {
+          const uint32_t d = d0 + i;
+          *reinterpret_cast<__half*>(tileV + d * 128u + ((kc ^ (d & 7u)) << 4) + kw) = __float2half_rn(v[i]);
+        }
+      }
+    };
+    uint32_t ra[32], rb[32];
+    tc_ld32_issue(tQ, ra);
+#pragma unroll 1
+    for (uint32_t c0 = 0; c0 < 192u; c0 += 64) {
+      tc_wait_ld();
+      tc_ld32_issue(tQ + c0 + 32u, rb);
+      convert(ra, c0);
+      tc_wait_ld();
+      if (c0 + 64u < 192u) tc_ld32_issue(tQ + c0 + 64u, ra);
+      convert(rb, c0 + 32u);
+    }
+    fence_proxy_async_smem();
+    if (!group_sync(c, 0x41a)) return false;
+    if (tid_in_group == 0) {
+      mbar_arrive(smem_u32(&c.ctrl->a_full[cQ % kASlots]));
+      mbar_arrive(smem_u32(&c.ctrl->a_full[cK % kASlots]));
+      mbar_arrive(smem_u32(&c.ctrl->a_full[cV % kASlots]));
+    }
+    tc_fence_before();
+    mbar_arrive(smem_u32(&c.ctrl->acc_empty[phQ & 1u]));
   }
   // causal: keys after the query are masked
   const uint32_t key_limit = (op.flags & F_CAUSAL) ? qrow : 0xffffffffu;

@@ -33,6 +33,9 @@ struct TuningSpec {
   std::map<std::string, GemmTileSpec> gemm;  // per GEMM node
   std::vector<std::string> allow_list;       // run only these nodes (single-node profiling)
   std::vector<std::string> reject_list;
+  // 0: fuse the Q/K/V projections into an attention stage that cannot fill the GPU anyway
+  // (batches*heads <= CTAs, sequence <= 128); 1: never; 2: whenever the sequence allows it
+  uint32_t qkv_fusion = 0;
 };
 
 // ------------------------------------------------------------------- FGraph
@@ -68,6 +71,8 @@ struct FOp {
   uint32_t M = 0, N = 0, K = 0;
   // ATTENTION: q, k (ActF16 with column offsets), vt (ActF16T), mask (VecF32), out
   int q = -1, k = -1, vt = -1, mask = -1;
+  // ATTENTION fused with its projections: a = x, w / wk / wv and bias / bias_k / bias_v, K = width of x
+  int wk = -1, wv = -1, bias_k = -1, bias_v = -1;
   uint32_t q_col = 0, k_col = 0, heads = 0, seq = 0, batches = 0, head_dim = 64;
   // LAYERNORM: src (AccF32 | ActF16), resid, gamma, beta, out
   int src = -1, gamma = -1, beta = -1;

@@ -182,6 +182,13 @@ int validate_plan(const Plan& P, std::string* err) {
         if (d.tmap_a >= P.tmaps.size() || d.tmap_b >= P.tmaps.size() || d.tmap_vt >= P.tmaps.size())
           return bad(n + "tensor map index");
         if (P.tmaps[d.tmap_vt].box0 != 64 || P.tmaps[d.tmap_vt].box1 != 64) return bad(n + "V^T box");
+        if (d.flags & F_FUSED_QKV) {
+          if (d.seq > 128 || d.K == 0 || d.K % 64 || d.kb_per_split != d.K / 64) return bad(n + "fused projection geometry");
+          if (d.vocab >= P.tmaps.size()) return bad(n + "tensor map index");
+          for (uint32_t tmi : {d.tmap_b, d.vocab})
+            if (P.tmaps[tmi].box0 != 64 || P.tmaps[tmi].box1 != 64) return bad(n + "projection weight box");
+          if (P.tmaps[d.tmap_a].box0 != 64 || P.tmaps[d.tmap_a].box1 != 128) return bad(n + "activation box");
+        }
         if (d.n_items != d.batches * d.heads * ((d.seq + 127) / 128)) return bad(n + "item count");
         if (op.p[0].space == SPACE_NONE) return bad(n + "no output buffer");
         break;
@@ -252,7 +259,7 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
   auto inputs_of = [](const FOp& o) {
     std::vector<int> v;
     for (int t : {o.a, o.w, o.bias, o.resid, o.q, o.k, o.vt, o.mask, o.src, o.gamma, o.beta, o.ids,
-                  o.type_ids, o.mask_in, o.word, o.pos, o.type, o.bias2})
+                  o.type_ids, o.mask_in, o.word, o.pos, o.type, o.bias2, o.wk, o.wv, o.bias_k, o.bias_v})
       if (t >= 0) v.push_back(t);
     return v;
   };
@@ -272,6 +279,60 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
   if (ops.empty()) {
     if (err) *err = "no operators left after allow/reject lists";
     return MONONN_ERR_INVALID_ARGUMENT;
+  }
+
+  // ---- Q/K/V projections fused into the attention stage. With few (batch, head) pairs the
+  // attention stage leaves most CTAs idle and the projection stage before it costs a full
+  // barrier round trip; and an MMA instruction takes as long for a 16-column tile as for a
+  // 192-column one. So each (batch, head) item computes its own [Q_h | K_h | V_h] =
+  // x_b [W_q,h | W_k,h | W_v,h] + bias (one 192-column accumulator over K/64 k-blocks: as long
+  // as the projection stage's main loop took with 148 CTAs), turns it into the f16 operand
+  // tiles in shared memory and goes on with QK^T, softmax and PV. One stage and three
+  // round trips through global memory disappear.
+  {
+    const uint32_t ctas = spec_in.grid ? spec_in.grid : sm_count;
+    for (size_t ai = 0; ai < ops.size(); ++ai) {
+      FOp& att = ops[ai];
+      if (att.kind != OP_ATTENTION || att.a >= 0 || spec_in.qkv_fusion == 1) continue;
+      if (att.seq > 128 || att.head_dim != 64) continue;
+      if (spec_in.qkv_fusion == 0 && att.batches * att.heads > ctas) continue;
+      int gi[3] = {-1, -1, -1};
+      const int want[3] = {att.q, att.k, att.vt};
+      bool ok = true;
+      for (int j = 0; j < 3 && ok; ++j) {
+        int readers = 0;
+        for (size_t i = 0; i < ops.size(); ++i) {
+          if (ops[i].out == want[j] && ops[i].kind == OP_GEMM) gi[j] = static_cast<int>(i);
+          for (int in : inputs_of(ops[i]))
+            if (in == want[j]) ++readers;
+        }
+        ok = gi[j] >= 0 && readers == 1 && g.tensors[want[j]].kind != TKind::Arg;
+      }
+      if (!ok) continue;
+      const FOp &gq = ops[gi[0]], &gk = ops[gi[1]], &gv = ops[gi[2]];
+      const uint32_t width = att.heads * 64u;
+      for (const FOp* gp : {&gq, &gk, &gv})
+        ok = ok && gp->a == gq.a && gp->K == gq.K && gp->N == width && gp->act == ACT_NONE && gp->resid < 0 &&
+             gp->alpha == 1.f && gp->K % 64 == 0 && gp->M == att.batches * att.seq &&
+             g.tensors[gp->w].const_name != "" ;
+      if (!ok || att.q_col != 0 || att.k_col != 0) continue;
+      att.flags |= F_FUSED_QKV;
+      att.a = gq.a;
+      att.K = gq.K;
+      att.w = gq.w;
+      att.wk = gk.w;
+      att.wv = gv.w;
+      att.bias = gq.bias;
+      att.bias_k = gk.bias;
+      att.bias_v = gv.bias;
+      att.q = att.k = att.vt = -1;
+      std::vector<FOp> kept;
+      for (size_t i = 0; i < ops.size(); ++i)
+        if (static_cast<int>(i) != gi[0] && static_cast<int>(i) != gi[1] && static_cast<int>(i) != gi[2])
+          kept.push_back(ops[i]);
+      ops.swap(kept);
+      ai = 0;  // indices moved: rescan (fused ops are skipped by the att.a >= 0 test)
+    }
   }
 
   // ---- residual hoisting: a split-K GEMM that accumulates into an f32 buffer and adds a
@@ -430,7 +491,7 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
   // Small constants first, contiguously: biases and LayerNorm scale/shift of all layers share
   // a few pages, which the kernel prefetches to L2 when it starts.
   for (const FOp& o : ops)
-    for (int t : {o.bias, o.gamma, o.beta, o.bias2})
+    for (int t : {o.bias, o.gamma, o.beta, o.bias2, o.bias_k, o.bias_v})
       if (t >= 0 && static_cast<uint64_t>(g.tensors[t].rows) * g.tensors[t].cols *
                             g.tensors[t].elem_bytes <= 65536)
         raw_const(t);
@@ -451,6 +512,40 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
     s.box1 = 128;
     P.tmaps.push_back(s);
     return act_tmap[t] = static_cast<uint32_t>(P.tmaps.size() - 1);
+  };
+
+  // Packed copy of a weight ([n_tiles][K/64][n_tile][64], one binding per (constant, n_tile)) and
+  // a tensor map whose box is `kbps` k-blocks of one tile; returns the tensor-map index.
+  auto packed_weight = [&](int w, uint32_t K, uint32_t N, uint32_t n_tile, uint32_t kbps) -> uint32_t {
+    const FTensor& W = g.tensors[w];
+    const uint32_t n_tiles = (N + n_tile - 1) / n_tile, kb = K / 64;
+    auto key = std::make_pair(W.const_name, n_tile);
+    auto pit = packed_binding.find(key);
+    if (pit == packed_binding.end()) {
+      ConstBinding b;
+      b.const_name = W.const_name;
+      b.kind = ConstBinding::PACK_B;
+      b.K = K;
+      b.N = N;
+      b.n_tile = n_tile;
+      b.transposed = W.const_transposed;
+      b.src_bytes = static_cast<uint64_t>(K) * N * 2;
+      b.bytes = static_cast<uint64_t>(n_tiles) * n_tile * K * 2;
+      b.offset = const_top;
+      const_top = align_up(const_top + b.bytes, 1024);
+      P.consts.push_back(b);
+      pit = packed_binding.emplace(key, P.consts.size() - 1).first;
+    }
+    const ConstBinding& b = P.consts[pit->second];
+    TmapSpec tm;
+    tm.base = BufRef{SPACE_CONST, 0, b.offset};
+    tm.dim0 = 64;
+    tm.dim1 = static_cast<uint64_t>(n_tiles) * kb * n_tile;
+    tm.stride1_bytes = 128;
+    tm.box0 = 64;
+    tm.box1 = n_tile * kbps;
+    P.tmaps.push_back(tm);
+    return static_cast<uint32_t>(P.tmaps.size() - 1);
   };
 
   // ---- per stage: count GEMMs to share the CTA budget
@@ -507,36 +602,7 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
           d.n_items = d.m_tiles * d.n_tiles * d.k_split;
           d.tmap_a = tmap_for_act(o.a);
           (void)A;
-          // weights: packed per (constant, n_tile)
-          auto key = std::make_pair(W.const_name, ts.n_tile);
-          auto pit = packed_binding.find(key);
-          if (pit == packed_binding.end()) {
-            ConstBinding b;
-            b.const_name = W.const_name;
-            b.kind = ConstBinding::PACK_B;
-            b.K = o.K;
-            b.N = o.N;
-            b.n_tile = ts.n_tile;
-            b.transposed = W.const_transposed;
-            b.src_bytes = static_cast<uint64_t>(o.K) * o.N * 2;
-            b.bytes = static_cast<uint64_t>(d.n_tiles) * ts.n_tile * o.K * 2;
-            b.offset = const_top;
-            const_top = align_up(const_top + b.bytes, 1024);
-            P.consts.push_back(b);
-            pit = packed_binding.emplace(key, P.consts.size() - 1).first;
-          }
-          {
-            const ConstBinding& b = P.consts[pit->second];
-            TmapSpec tm;
-            tm.base = BufRef{SPACE_CONST, 0, b.offset};
-            tm.dim0 = 64;
-            tm.dim1 = static_cast<uint64_t>(d.n_tiles) * kb * ts.n_tile;
-            tm.stride1_bytes = 128;
-            tm.box0 = 64;
-            tm.box1 = ts.n_tile * d.kb_per_bslot;
-            P.tmaps.push_back(tm);
-            d.tmap_b = static_cast<uint32_t>(P.tmaps.size() - 1);
-          }
+          d.tmap_b = packed_weight(o.w, o.K, o.N, ts.n_tile, d.kb_per_bslot);
           po.p[0] = where[o.out];
           if (o.bias >= 0) {
             po.p[1] = raw_const(o.bias);
@@ -587,9 +653,25 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
           d.head_dim = o.head_dim;
           d.q_col = o.q_col;
           d.k_col = o.k_col;
-          d.tmap_a = tmap_for_act(o.q);
-          d.tmap_b = tmap_for_act(o.k);
-          {
+          if (o.flags & F_FUSED_QKV) {
+            const uint32_t width = o.heads * 64u;
+            d.K = o.K;
+            d.kb_per_split = o.K / 64;
+            d.tmap_a = tmap_for_act(o.a);
+            d.tmap_b = packed_weight(o.w, o.K, width, 64, 1);
+            d.tmap_vt = packed_weight(o.wk, o.K, width, 64, 1);
+            d.vocab = packed_weight(o.wv, o.K, width, 64, 1);
+            // bases of the three packed weights: CTAs without an item pre-fetch them into L2
+            po.p[5] = P.tmaps[d.tmap_b].base;
+            po.p[6] = P.tmaps[d.tmap_vt].base;
+            po.p[7] = P.tmaps[d.vocab].base;
+            if (o.bias >= 0) po.p[2] = raw_const(o.bias);
+            if (o.bias_k >= 0) po.p[3] = raw_const(o.bias_k);
+            if (o.bias_v >= 0) po.p[4] = raw_const(o.bias_v);
+            P.algorithmic_flops += 2.0 * o.batches * o.seq * 3.0 * width * o.K;
+          } else {
+            d.tmap_a = tmap_for_act(o.q);
+            d.tmap_b = tmap_for_act(o.k);
             const FTensor& VT = g.tensors[o.vt];
             TmapSpec tm;
             tm.base = where[o.vt];

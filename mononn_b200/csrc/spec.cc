@@ -72,6 +72,9 @@ std::string spec_to_json(const Plan& plan, uint32_t sm_count) {
   ctx.set("cuda_device_context", dev);
   root.set("cuda_context", ctx);
   root.set("hlo_module_name", Json::string(plan.module_name));
+  // "auto": Q/K/V projections are computed inside the attention items when the attention stage
+  // cannot fill the GPU (batches*heads <= CTAs, sequence <= 128); "off"; "on": whenever legal
+  root.set("qkv_fusion", Json::string(plan.spec.qkv_fusion == 1 ? "off" : plan.spec.qkv_fusion == 2 ? "on" : "auto"));
   root.set("cluster_elewise_spec", Json::object());
   root.set("cluster_reduce_spec", Json::object());
   Json gemms = Json::object();
@@ -269,6 +272,8 @@ int spec_from_json(const std::string& text, TuningSpec* spec, std::string* err) 
       if (const Json* g = rt->find("grid_dim")) spec->grid = static_cast<uint32_t>(g->get_number("x", 0));
       if (const Json* b = rt->find("block_dim")) spec->block = static_cast<uint32_t>(b->get_number("x", kThreads));
     }
+  if (const Json* qf = root.find("qkv_fusion"))
+    if (qf->type == Json::String) spec->qkv_fusion = qf->str == "off" ? 1u : qf->str == "on" ? 2u : 0u;
   if (const Json* gl = root.find("gemm_spec_list")) {
     if (!gl->is_object()) {
       if (err) *err = "gemm_spec_list must be an object";

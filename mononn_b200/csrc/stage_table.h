@@ -52,11 +52,14 @@ enum OpFlags : uint32_t {
   F_RESID_F32 = 1u << 8,   // residual source is f32
   F_NO_NORM = 1u << 9,     // row op: no LayerNorm, the row sum is the result
   F_L2NORM = 1u << 10,     // row op: x / sqrt(sum x^2) instead of LayerNorm (scale and shift unused)
+  F_FUSED_QKV = 1u << 11,  // attention: the item first computes its own Q, K, V = x W_h + b_h
 };
 
 // Pointer slots p[0..7]; meaning per kind:
 //  GEMM:      0 out, 1 bias(f16), 2 resid
-//  ATTENTION: 0 out ctx(f16), 1 mask bias(f32 [B,S])
+//  ATTENTION: 0 out ctx(f16), 1 mask bias(f32 [B,S]); with F_FUSED_QKV also 2/3/4 = bias of Q/K/V
+//             (f16 [heads*64]), tmap_a = x [tokens, K], tmap_b / tmap_vt / vocab = tensor maps of the
+//             Q / K / V weights packed in 64-row tiles, K = hidden size, kb_per_split = K/64
 //  LAYERNORM: 0 out(f16), 1 src, 2 gamma(f16), 3 beta(f16), 4 resid(f16, optional), 5 out2
 //  EMBED:     0 out(f16), 1 ids(i32), 2 type ids(i32), 3 word table(f16), 4 pos table(f16),
 //             5 type table(f16), 6 gamma, 7 beta ; mask(i32) -> q[0], mask bias out(f32) -> q[1]

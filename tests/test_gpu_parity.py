@@ -283,3 +283,30 @@ def test_clip_shapes_against_oracle(cfg):
 def test_clip_b32_full_size():
     """CLIP ViT-B/32 shape, 32 images x 32 texts."""
     check_clip(clip_b32(), 1238)
+
+
+@pytest.mark.parametrize("mode", ["off", "on"])
+@pytest.mark.parametrize("cfg", [
+    bert_tiny(batch=3, seq=40, layers=2, hidden=128, ffn=512),     # ragged rows, two heads, padded keys
+    bert_tiny(batch=2, seq=128, layers=1, hidden=192, ffn=256),    # full 128-row tiles, three heads
+], ids=lambda c: f"b{c.batch}s{c.seq}h{c.hidden}")
+def test_projection_fusion_modes_agree_with_the_oracle(cfg, mode, tmp_path):
+    """The Q/K/V projections as a stage of their own ("off") and computed inside the attention
+    items ("on": x W_h accumulated in TMEM, converted on chip into the Q, K and V^T operand
+    tiles) both meet the oracle."""
+    import json
+    from mononn_b200.module import describe
+    w = make_weights(cfg, 55, stress=True)
+    inp = make_inputs(cfg, 55, pad_fraction=0.25)
+    text, names = bert_hlo(cfg)
+    spec = describe("hlo", text)["spec"]
+    spec["qkv_fusion"] = mode
+    (tmp_path / "cluster_0").mkdir()
+    (tmp_path / "cluster_0" / "best_tuning_spec.json").write_text(json.dumps(spec))
+    mod = compile_hlo(text, spec_dir=str(tmp_path), barrier_timeout_us=500000)
+    mod.set_weights({names[k]: v for k, v in w.items()})
+    kinds = [[o["kind"] for o in st["ops"]] for st in mod.plan()["stages"]]
+    assert (["gemm", "gemm", "gemm"] in kinds) == (mode == "off")
+    got = run_module(mod, cfg, inp)
+    mod.close()
+    assert_parity(got, R.bert_encoder(cfg, w, inp), f"projection fusion {mode}")

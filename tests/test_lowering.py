@@ -19,12 +19,31 @@ def test_bert_base_stage_structure(base_plan):
     assert p["grid"] == 148 and p["block"] == 256
     assert p["smem_bytes"] <= 232448
     stages = p["stages"]
-    assert len(stages) == 1 + 12 * 7
-    kinds = [tuple(o["kind"] for o in s["ops"]) for s in stages[:8]]
-    assert kinds == [("embed",), ("gemm", "gemm", "gemm"), ("attention",), ("gemm",), ("layernorm",),
-                     ("gemm",), ("gemm",), ("layernorm",)]
+    # 12 (batch, head) pairs cannot fill 148 CTAs: the Q/K/V projections run inside the attention items
+    assert len(stages) == 1 + 12 * 6
+    kinds = [tuple(o["kind"] for o in s["ops"]) for s in stages[:7]]
+    assert kinds == [("embed",), ("attention",), ("gemm",), ("layernorm",), ("gemm",), ("gemm",), ("layernorm",)]
+    assert stages[1]["ops"][0]["flags"] & (1 << 11)
     # every stage fits one wave of the 148 CTAs at b1/s128
     assert all(s["n_items"] <= 148 for s in stages)
+
+
+def test_projections_stay_a_stage_of_their_own_when_attention_fills_the_gpu(lib_built, base_plan):
+    """Fusing costs every (batch, head) item a pass over its head's weights: it is done only
+    when the attention stage leaves CTAs idle (or on request), never for long sequences."""
+    off = dict(base_plan["spec"], qkv_fusion="off")
+    p = describe("encoder", bert_base().to_json(), spec=off)["plan"]
+    assert len(p["stages"]) == 1 + 12 * 7
+    assert [o["kind"] for o in p["stages"][1]["ops"]] == ["gemm", "gemm", "gemm"]
+    assert abs(p["algorithmic_flops"] - base_plan["plan"]["algorithmic_flops"]) < 1e6
+    many = describe("encoder", bert_tiny(batch=160, seq=16, layers=1).to_json())["plan"]   # 160 pairs > 148 CTAs
+    assert [o["kind"] for o in many["stages"][1]["ops"]] == ["gemm", "gemm", "gemm"]
+    forced = describe("encoder", bert_tiny(batch=160, seq=16, layers=1).to_json(),
+                      spec=dict(describe("encoder", bert_tiny(batch=160, seq=16, layers=1).to_json())["spec"],
+                                qkv_fusion="on"))["plan"]
+    assert [o["kind"] for o in forced["stages"][1]["ops"]] == ["attention"]
+    long_seq = describe("encoder", bert_tiny(batch=1, seq=200, layers=1).to_json())["plan"]
+    assert [o["kind"] for o in long_seq["stages"][1]["ops"]] == ["gemm", "gemm", "gemm"]
 
 
 def test_algorithmic_cost_matches_the_model(base_plan):

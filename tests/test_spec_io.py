@@ -21,6 +21,7 @@ def test_spec_json_is_plain_json_with_original_field_names(lib_built):
     text = json.dumps(d)
     back = json.loads(text)
     assert back["cuda_context"]["cuda_device_context"]["cuda_arch"] == "1000"
-    g = back["gemm_spec_list"]["layer0.attn.q"]
+    g = back["gemm_spec_list"]["layer0.attn.o"]
     assert set(g["sm100_config"]) >= {"mma_m", "mma_n", "k_split", "cluster_x", "cluster_y", "cta_group", "epilogue_fusion"}
     assert g["problem"] == {"m": 16, "n": 64, "k": 64}
+    assert back["qkv_fusion"] == "auto" and "layer0.attn.q" not in back["gemm_spec_list"]   # computed inside attention

@@ -17,15 +17,21 @@ def _tensor(plan, name):
     return next(t for t in plan["tensors"] if t["name"] == name)
 
 
-def test_noalloc_attention_matches_the_module_path_twice():
+def test_noalloc_attention_matches_the_module_path_twice(tmp_path):
+    import json
     import torch
     from mononn_b200 import bert_tiny, capi, compile_encoder, make_inputs, make_weights
-    from mononn_b200.module import attention_noalloc
+    from mononn_b200.module import attention_noalloc, describe
 
     cfg = bert_tiny(batch=3, seq=40, layers=1, hidden=128, ffn=256)
     w = make_weights(cfg, 31, stress=True)
     inp = make_inputs(cfg, 31, pad_fraction=0.25)
-    mod = compile_encoder(cfg)
+    # the regular module with the Q/K/V projections as a stage of their own, so that its Q, K
+    # and V^T tensors exist in the temp buffer for the stand-alone call to read
+    spec = dict(describe("encoder", cfg.to_json())["spec"], qkv_fusion="off")
+    (tmp_path / "cluster_0").mkdir()
+    (tmp_path / "cluster_0" / "best_tuning_spec.json").write_text(json.dumps(spec))
+    mod = compile_encoder(cfg, spec_dir=str(tmp_path))
     mod.set_weights(w)
     bufs = mod.allocate()
     descs = mod.args()
