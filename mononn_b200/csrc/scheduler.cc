@@ -316,6 +316,10 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
              gp->alpha == 1.f && gp->K % 64 == 0 && gp->M == att.batches * att.seq &&
              g.tensors[gp->w].const_name != "" ;
       if (!ok || att.q_col != 0 || att.k_col != 0) continue;
+      // wide models: a head's three weight slabs (3 * K * 128 bytes) no longer stream through the
+      // three-slot ring as fast as the MMAs consume them (measured: OPT-1.3B, K = 2048, is 2 %
+      // slower fused), so the automatic choice stops at K = 1024
+      if (spec_in.qkv_fusion == 0 && gq.K > 1024) continue;
       att.flags |= F_FUSED_QKV;
       att.a = gq.a;
       att.K = gq.K;
