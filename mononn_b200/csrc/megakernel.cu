@@ -208,6 +208,7 @@ struct Ctx {
   uint32_t a_ring;  // shared addresses
   uint32_t b_ring;
   uint8_t* a_ring_ptr;
+  uint8_t* store_stage;  // kStoreStageBytes after the control block: 4 KB per epilogue warp
   uint32_t stage;   // current stage (for status)
   uint32_t group_phase;  // parity of the next group_bar phase (epilogue warps only)
   uint64_t timeout_ns;
@@ -764,6 +765,17 @@ __device__ __forceinline__ void apply_act16(float (&v)[16], uint32_t act) {
   }
 }
 
+// 32 consecutive floats of a shared-memory table (16-byte aligned) as eight vector loads issued
+// back to back. Per-element scalar loads next to their uses left each multiply waiting for its
+// own load: with one warp per scheduler that was ~20 cycles per element.
+__device__ __forceinline__ void lds32(const float* p, float (&m)[32]) {
+  const float4* q = reinterpret_cast<const float4*>(p);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float4 t = q[i];
+    m[4 * i] = t.x; m[4 * i + 1] = t.y; m[4 * i + 2] = t.z; m[4 * i + 3] = t.w;
+  }
+}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -784,7 +796,8 @@ __device__ __forceinline__ void add4(float4& a, const float4 b) {
 
 // Thread `row` of the 128 epilogue threads owns accumulator row `row` (TMEM lane = row).
 __device__ __noinline__ void gemm_epilogue(const OpDesc& op, uint32_t local, uint32_t tmem_acc,
-                                           uint32_t quarter, uint32_t lane, const float* bias_s) {
+                                           uint32_t quarter, uint32_t lane, const float* bias_s,
+                                           uint8_t* stg) {
   const GemmTile t = gemm_tile(op, local);
   const uint32_t grow = t.mt * 128u + quarter * 32u + lane;
   const bool row_ok = grow < op.M;
@@ -800,14 +813,23 @@ __device__ __noinline__ void gemm_epilogue(const OpDesc& op, uint32_t local, uin
     float v[16];
     tc_ld16(tmem_acc + ((quarter * 32u) << 16) + c0, v);
     const uint32_t col = n0 + c0;
-    if (!row_ok || col >= N) continue;
+    // row-major f16 output: 64-column groups are collected in the warp's staging block and
+    // stored eight lanes to a row (whole lines) instead of one row per lane
+    const bool staged = (out_mode == OUT_F16);
+    const uint32_t g0 = c0 & ~63u;
+    const bool flush = staged && (c0 + 16u >= n_tile || ((c0 + 16u) & 63u) == 0u);
+    if (row_ok && col < N) {
     if (alpha != 1.0f) {
 #pragma unroll
       for (int i = 0; i < 16; ++i) v[i] *= alpha;
     }
     if (bias_on) {
+      const float4* bq = reinterpret_cast<const float4*>(bias_s + c0);
 #pragma unroll
-      for (int i = 0; i < 16; ++i) v[i] += bias_s[c0 + i];
+      for (int i = 0; i < 4; ++i) {
+        const float4 t = bq[i];
+        v[4 * i] += t.x; v[4 * i + 1] += t.y; v[4 * i + 2] += t.z; v[4 * i + 3] += t.w;
+      }
     }
     apply_act16(v, act);
     if (resid_on) {
@@ -830,12 +852,11 @@ __device__ __noinline__ void gemm_epilogue(const OpDesc& op, uint32_t local, uin
       }
     }
     if (out_mode == OUT_F16) {
-      uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(pout) +
-                                          static_cast<size_t>(grow) * ldo + col);
-      o[0] = make_uint4(pack_h2(v[0], v[1]), pack_h2(v[2], v[3]), pack_h2(v[4], v[5]),
-                        pack_h2(v[6], v[7]));
-      o[1] = make_uint4(pack_h2(v[8], v[9]), pack_h2(v[10], v[11]), pack_h2(v[12], v[13]),
-                        pack_h2(v[14], v[15]));
+      const uint32_t ch = (c0 - g0) >> 3;
+      *reinterpret_cast<uint4*>(stg + lane * 128u + ((ch ^ (lane & 7u)) << 4)) =
+          make_uint4(pack_h2(v[0], v[1]), pack_h2(v[2], v[3]), pack_h2(v[4], v[5]), pack_h2(v[6], v[7]));
+      *reinterpret_cast<uint4*>(stg + lane * 128u + (((ch + 1u) ^ (lane & 7u)) << 4)) =
+          make_uint4(pack_h2(v[8], v[9]), pack_h2(v[10], v[11]), pack_h2(v[12], v[13]), pack_h2(v[14], v[15]));
     } else if (out_mode == OUT_F32_RED) {
       float* o = reinterpret_cast<float*>(pout) + static_cast<size_t>(grow) * ldo + col;
 #pragma unroll
@@ -853,6 +874,20 @@ __device__ __noinline__ void gemm_epilogue(const OpDesc& op, uint32_t local, uin
 #pragma unroll
       for (int i = 0; i < 4; ++i)
         o[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    }
+    }  // row_ok && col < N
+    if (flush) {
+      __syncwarp();
+      const uint32_t chunks = (c0 + 16u - g0) >> 3;  // 16-byte chunks per row in this group (2..8)
+      const uint32_t row0 = t.mt * 128u + quarter * 32u;
+      for (uint32_t idx = lane; idx < 32u * chunks; idx += 32u) {
+        const uint32_t r = idx / chunks, q = idx - r * chunks;
+        const uint32_t gcol = n0 + g0 + q * 8u;
+        if (row0 + r < op.M && gcol < N)
+          *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(pout) + static_cast<size_t>(row0 + r) * ldo + gcol) =
+              *reinterpret_cast<const uint4*>(stg + r * 128u + ((q ^ (r & 7u)) << 4));
+      }
+      __syncwarp();
     }
   }
 }
@@ -1270,9 +1305,10 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
     uint8_t* tileV = c.a_ring_ptr + (cV % kASlots) * kSlotBytes + (row >> 6) * 8192u;
     // one 32-column load is in flight while the previous one is converted and stored
     auto convert = [&](const uint32_t (&r)[32], uint32_t c0) {
-      float v[32];
+      float v[32], bb[32];
+      lds32(bs + c0, bb);
 #pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) + bs[c0 + i];
+      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) + bb[i];
       if (c0 < 128u) {
         uint8_t* tile = c.a_ring_ptr + (((c0 < 64u) ? cQ : cK) % kASlots) * kSlotBytes;
         const uint32_t chunk = (c0 & 63u) >> 3;
@@ -1323,14 +1359,15 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
   float m0 = -3.0e38f, m1 = -3.0e38f, m2 = -3.0e38f, m3 = -3.0e38f;
 #pragma unroll 1
   for (uint32_t c0 = 0; c0 < n_cols; c0 += 32) {
-    float v[32];
+    float v[32], mk[32];
+    lds32(mb + c0, mk);
     tc_ld32(tS + c0, v);
 #pragma unroll
     for (int i = 0; i < 32; i += 4) {
-      m0 = fmaxf(m0, (c0 + i <= key_limit) ? fmaf(v[i], alpha, mb[c0 + i]) : -1.0e30f);
-      m1 = fmaxf(m1, (c0 + i + 1 <= key_limit) ? fmaf(v[i + 1], alpha, mb[c0 + i + 1]) : -1.0e30f);
-      m2 = fmaxf(m2, (c0 + i + 2 <= key_limit) ? fmaf(v[i + 2], alpha, mb[c0 + i + 2]) : -1.0e30f);
-      m3 = fmaxf(m3, (c0 + i + 3 <= key_limit) ? fmaf(v[i + 3], alpha, mb[c0 + i + 3]) : -1.0e30f);
+      m0 = fmaxf(m0, (c0 + i <= key_limit) ? fmaf(v[i], alpha, mk[i]) : -1.0e30f);
+      m1 = fmaxf(m1, (c0 + i + 1 <= key_limit) ? fmaf(v[i + 1], alpha, mk[i + 1]) : -1.0e30f);
+      m2 = fmaxf(m2, (c0 + i + 2 <= key_limit) ? fmaf(v[i + 2], alpha, mk[i + 2]) : -1.0e30f);
+      m3 = fmaxf(m3, (c0 + i + 3 <= key_limit) ? fmaf(v[i + 3], alpha, mk[i + 3]) : -1.0e30f);
     }
   }
   const float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
@@ -1348,12 +1385,13 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
 #pragma unroll 1
     for (uint32_t c0 = 0; c0 < 128u; c0 += 32) {
       const uint32_t cc = j * 128u + c0;
-      float v[32];
+      float v[32], mk[32];
+      lds32(mb + cc, mk);
       tc_ld32(tS + cc, v);
 #pragma unroll
       for (int i = 0; i < 32; i += 2) {
-        const float z0 = (cc + i <= key_limit) ? fmaf(v[i], alpha, mb[cc + i]) : -1.0e30f;
-        const float z1 = (cc + i + 1 <= key_limit) ? fmaf(v[i + 1], alpha, mb[cc + i + 1]) : -1.0e30f;
+        const float z0 = (cc + i <= key_limit) ? fmaf(v[i], alpha, mk[i]) : -1.0e30f;
+        const float z1 = (cc + i + 1 <= key_limit) ? fmaf(v[i + 1], alpha, mk[i + 1]) : -1.0e30f;
         v[i] = fast_exp2(z0 - mx);
         v[i + 1] = fast_exp2(z1 - mx);
         sum0 += v[i];
@@ -1386,22 +1424,35 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
   const uint32_t tO = tmem_base + kAttnOutCol + ((quarter * 32u) << 16);
   const float inv = 1.0f / (sum0 + sum1);
   const bool row_ok = qrow < seq;
-  __half* out = reinterpret_cast<__half*>(op.p[0]) +
-                (static_cast<size_t>(t.b) * seq + qrow) * op.ldo + t.h * 64u;
+  // A thread owns a row, but a store instruction whose 32 lanes hit 32 different rows costs 32
+  // memory transactions. The warp's 32 x 128-byte block goes through shared memory (swizzled, so
+  // neither side has bank conflicts) and is stored eight lanes to a row: four full lines per
+  // instruction.
+  uint8_t* stg = c.store_stage + quarter * 4096u;
+  (void)row_ok;
 #pragma unroll 1
   for (uint32_t c0 = 0; c0 < 64u; c0 += 32) {
     float v[32];
     tc_ld32(tO + c0, v);
-    if (row_ok) {
-      uint4* o = reinterpret_cast<uint4*>(out + c0);
 #pragma unroll
-      for (int q = 0; q < 4; ++q)
-        o[q] = make_uint4(pack_h2(v[8 * q] * inv, v[8 * q + 1] * inv),
-                          pack_h2(v[8 * q + 2] * inv, v[8 * q + 3] * inv),
-                          pack_h2(v[8 * q + 4] * inv, v[8 * q + 5] * inv),
-                          pack_h2(v[8 * q + 6] * inv, v[8 * q + 7] * inv));
+    for (uint32_t q = 0; q < 4; ++q)
+      *reinterpret_cast<uint4*>(stg + lane * 128u + ((((c0 >> 3) + q) ^ (lane & 7u)) << 4)) =
+          make_uint4(pack_h2(v[8 * q] * inv, v[8 * q + 1] * inv), pack_h2(v[8 * q + 2] * inv, v[8 * q + 3] * inv),
+                     pack_h2(v[8 * q + 4] * inv, v[8 * q + 5] * inv), pack_h2(v[8 * q + 6] * inv, v[8 * q + 7] * inv));
+  }
+  __syncwarp();
+  {
+    const uint32_t q = lane & 7u;
+    __half* obase = reinterpret_cast<__half*>(op.p[0]) + t.h * 64u + q * 8u;
+#pragma unroll
+    for (uint32_t j = 0; j < 8; ++j) {
+      const uint32_t r = 4u * j + (lane >> 3), qr = t.mt * 128u + quarter * 32u + r;
+      const uint4 val = *reinterpret_cast<const uint4*>(stg + r * 128u + ((q ^ (r & 7u)) << 4));
+      if (qr < seq)
+        *reinterpret_cast<uint4*>(obase + (static_cast<size_t>(t.b) * seq + qr) * op.ldo) = val;
     }
   }
+  __syncwarp();  // the staging block is reused by the warp's next item
   tc_fence_before();
   mbar_arrive(smem_u32(&c.ctrl->acc_empty[phO & 1u]));
   return true;
@@ -1446,7 +1497,8 @@ __device__ void role_simt(Ctx c, uint32_t tmem_base, uint32_t tid_in_group) {
           WAIT_OR_RETURN(mbar_wait_warp(c, &c.ctrl->acc_full[buf], (acc_cnt >> 1) & 1u, 0x401));
           if (tid_in_group == 0) trace(P, s, TR_MARK0 + 1);
           tc_fence_after();
-          gemm_epilogue(op, it.local, tmem_base + buf * kAccCols, quarter, lane, bias_s);
+          gemm_epilogue(op, it.local, tmem_base + buf * kAccCols, quarter, lane, bias_s,
+                        c.store_stage + quarter * 4096u);
           tc_fence_before();
           mbar_arrive(smem_u32(&c.ctrl->acc_empty[buf]));
           ++acc_cnt;
@@ -1550,6 +1602,7 @@ mononn_megakernel(const __grid_constant__ KernelParams P) {
   c.a_ring = smem_u32(base);
   c.b_ring = c.a_ring + kASlots * kSlotBytes;
   c.a_ring_ptr = base;
+  c.store_stage = base + kASlots * kSlotBytes + kBSlots * kBSlotBytes + 8192u;
   c.stage = P.stage_begin;
   c.group_phase = 0;
   c.timeout_ns = static_cast<uint64_t>(P.timeout_us) * 1000ull;

@@ -184,6 +184,7 @@ std::vector<GemmTileSpec> gemm_tile_candidates(uint32_t M, uint32_t N, uint32_t 
 // Fixed head of the module scratch: barrier counter, status word, per-stage time stamps.
 constexpr uint64_t kScratchBarrierOff = 0, kScratchStatusOff = 256, kScratchStampsOff = 512;
 
-constexpr uint32_t kSmemBytes = kASlots * kSlotBytes + kBSlots * kBSlotBytes + 8192 /*ctrl*/ + 1024 /*align*/;
+constexpr uint32_t kSmemBytes =
+    kASlots * kSlotBytes + kBSlots * kBSlotBytes + 8192 /*ctrl*/ + kStoreStageBytes + 1024 /*align*/;
 
 }  // namespace mononn

@@ -137,6 +137,7 @@ constexpr uint32_t kBSlotBytes = 32768;  // weight ring slot: up to 256 rows of 
 #endif
 constexpr uint32_t kASlots = MONONN_A_SLOTS;
 constexpr uint32_t kBSlots = MONONN_B_SLOTS;
+constexpr uint32_t kStoreStageBytes = 16384;  // per epilogue warp 32 rows x 128 B, to store whole lines
 constexpr uint32_t kThreads = 256;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTraceEvents = 16;  // per (CTA, stage) slots of the optional event trace
