@@ -1083,10 +1083,44 @@ __device__ __noinline__ void rowwise_item(const OpDesc& op, uint32_t local, uint
         sq += a * a + b * b + c * c + d * d;
       }
     const float rstd = l2 ? rsqrtf(warp_sum(sq)) : rsqrtf(warp_sum(sq) * inv_n + eps);
+    if (!no_norm && !l2 && out != nullptr) {
+      // the common LayerNorm: the per-item choices are made once here, not per 8-byte group (a
+      // branch costs a warp that is alone on its scheduler some twenty cycles)
+      const bool two = (out2 != nullptr);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const uint32_t vi = i * 32u + lane;
-      if (vi < nvec) row_emit(x[i], mean, rstd, vi, gv[i], bv[i], b2v[i], out, out2, add_bias2, no_norm, l2);
+      for (int i = 0; i < 8; ++i) {
+        const uint32_t vi = i * 32u + lane;
+        if (vi < nvec) {
+          const float4 g = h4_to_f4(gv[i]), b = h4_to_f4(bv[i]);
+          float4 y;
+          y.x = (x[i].x - mean) * rstd * g.x + b.x;
+          y.y = (x[i].y - mean) * rstd * g.y + b.y;
+          y.z = (x[i].z - mean) * rstd * g.z + b.z;
+          y.w = (x[i].w - mean) * rstd * g.w + b.w;
+          uint2 o;
+          o.x = pack_h2(y.x, y.y);
+          o.y = pack_h2(y.z, y.w);
+          out[vi] = o;
+          x[i] = y;
+        }
+      }
+      if (two) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint32_t vi = i * 32u + lane;
+          if (vi < nvec) {
+            float4 y = x[i];
+            add4(y, h4_to_f4(b2v[i]));  // zero when there is no bias to pre-load
+            out2[vi] = y;
+          }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const uint32_t vi = i * 32u + lane;
+        if (vi < nvec) row_emit(x[i], mean, rstd, vi, gv[i], bv[i], b2v[i], out, out2, add_bias2, no_norm, l2);
+      }
     }
   } else {
     // wide rows: three passes over the (L2-resident) sources
