@@ -1396,12 +1396,22 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
     float v[32], mk[32];
     lds32(mb + c0, mk);
     tc_ld32(tS + c0, v);
+    if (key_limit == 0xffffffffu) {  // not causal (warp-uniform): no per-element test
 #pragma unroll
-    for (int i = 0; i < 32; i += 4) {
-      m0 = fmaxf(m0, (c0 + i <= key_limit) ? fmaf(v[i], alpha, mk[i]) : -1.0e30f);
-      m1 = fmaxf(m1, (c0 + i + 1 <= key_limit) ? fmaf(v[i + 1], alpha, mk[i + 1]) : -1.0e30f);
-      m2 = fmaxf(m2, (c0 + i + 2 <= key_limit) ? fmaf(v[i + 2], alpha, mk[i + 2]) : -1.0e30f);
-      m3 = fmaxf(m3, (c0 + i + 3 <= key_limit) ? fmaf(v[i + 3], alpha, mk[i + 3]) : -1.0e30f);
+      for (int i = 0; i < 32; i += 4) {
+        m0 = fmaxf(m0, fmaf(v[i], alpha, mk[i]));
+        m1 = fmaxf(m1, fmaf(v[i + 1], alpha, mk[i + 1]));
+        m2 = fmaxf(m2, fmaf(v[i + 2], alpha, mk[i + 2]));
+        m3 = fmaxf(m3, fmaf(v[i + 3], alpha, mk[i + 3]));
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        m0 = fmaxf(m0, (c0 + i <= key_limit) ? fmaf(v[i], alpha, mk[i]) : -1.0e30f);
+        m1 = fmaxf(m1, (c0 + i + 1 <= key_limit) ? fmaf(v[i + 1], alpha, mk[i + 1]) : -1.0e30f);
+        m2 = fmaxf(m2, (c0 + i + 2 <= key_limit) ? fmaf(v[i + 2], alpha, mk[i + 2]) : -1.0e30f);
+        m3 = fmaxf(m3, (c0 + i + 3 <= key_limit) ? fmaf(v[i + 3], alpha, mk[i + 3]) : -1.0e30f);
+      }
     }
   }
   const float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
@@ -1422,14 +1432,27 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
       float v[32], mk[32];
       lds32(mb + cc, mk);
       tc_ld32(tS + cc, v);
+      if (key_limit == 0xffffffffu) {
+        // exp2(s*alpha + mask - max) with the subtraction folded into the multiply-add
 #pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        const float z0 = (cc + i <= key_limit) ? fmaf(v[i], alpha, mk[i]) : -1.0e30f;
-        const float z1 = (cc + i + 1 <= key_limit) ? fmaf(v[i + 1], alpha, mk[i + 1]) : -1.0e30f;
-        v[i] = fast_exp2(z0 - mx);
-        v[i + 1] = fast_exp2(z1 - mx);
-        sum0 += v[i];
-        sum1 += v[i + 1];
+        for (int i = 0; i < 32; ++i) mk[i] -= mx;
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          v[i] = fast_exp2(fmaf(v[i], alpha, mk[i]));
+          v[i + 1] = fast_exp2(fmaf(v[i + 1], alpha, mk[i + 1]));
+          sum0 += v[i];
+          sum1 += v[i + 1];
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float z0 = (cc + i <= key_limit) ? fmaf(v[i], alpha, mk[i]) : -1.0e30f;
+          const float z1 = (cc + i + 1 <= key_limit) ? fmaf(v[i + 1], alpha, mk[i + 1]) : -1.0e30f;
+          v[i] = fast_exp2(z0 - mx);
+          v[i + 1] = fast_exp2(z1 - mx);
+          sum0 += v[i];
+          sum1 += v[i + 1];
+        }
       }
       uint8_t* tile = c.a_ring_ptr + ((c0 < 64u) ? slotP0 : slotP1) * kSlotBytes;
       const uint32_t chunk = (c0 & 63u) >> 3;  // 16-byte chunk index inside the 128-byte row
