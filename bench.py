@@ -37,7 +37,7 @@ UNIT = "samples/s"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised
 # in profiles/ (None until a capture exists)
-NCU_TRAFFIC_BYTES = 175118592  # 170.87 MB read + 4.25 MB written
+NCU_TRAFFIC_BYTES = 175189504  # 170.90 MB read + 4.29 MB written
 
 
 def measured_hbm_peak():
