@@ -289,6 +289,7 @@ def test_clip_b32_full_size():
 @pytest.mark.parametrize("cfg", [
     bert_tiny(batch=3, seq=40, layers=2, hidden=128, ffn=512),     # ragged rows, two heads, padded keys
     bert_tiny(batch=2, seq=128, layers=1, hidden=192, ffn=256),    # full 128-row tiles, three heads
+    bert_tiny(batch=75, seq=16, layers=2, hidden=128, ffn=256),    # 150 items on 148 CTAs: two CTAs take a second item
 ], ids=lambda c: f"b{c.batch}s{c.seq}h{c.hidden}")
 def test_projection_fusion_modes_agree_with_the_oracle(cfg, mode, tmp_path):
     """The Q/K/V projections as a stage of their own ("off") and computed inside the attention
