@@ -166,6 +166,18 @@ int mononn_trace_stages(mononn_module* m, void* const* device_args, int n, void*
  * mononn_last_status reports MONONN_ERR_BARRIER_TIMEOUT and restores the module. */
 int mononn_debug_skew_barrier(mononn_module* m, unsigned missing_arrivals);
 
+/* Measurement aid: cycles per tcgen05.mma (128 x n x 16, f16 in, f32 accumulate) issued back to
+ * back by one thread per CTA from operands resident in shared memory, on `ctas` CTAs (one per
+ * SM) at once: `count` instructions cycling through `accumulators` TMEM buffers, one commit at
+ * the end. mode bit 0 adds a commit after every four instructions, bit 1 a satisfied mbarrier
+ * wait + tcgen05 fence before every four (the bookkeeping of the kernel's main loop).
+ * cycles_per_mma covers first issue .. commit observed, issue_cycles_per_mma the issuing
+ * thread alone. The GEMM tile menu of the tuner is sized from this table; the reference times
+ * whole CUTLASS tiles instead (mononn_engine/core/op_impl/gemm_impl.cc:505-566). */
+int mononn_debug_mma_issue(int device, unsigned n, unsigned count, unsigned accumulators,
+                           unsigned mode, unsigned ctas, double* cycles_per_mma,
+                           double* issue_cycles_per_mma, double* ns_per_mma);
+
 /* Algorithmic bytes and FLOPs of one inference (weights once + gathered rows + I/O). */
 int mononn_module_cost(const mononn_module* m, double* bytes, double* flops);
 
@@ -189,12 +201,21 @@ int mononn_module_cost(const mononn_module* m, double* bytes, double* flops);
  * The call is asynchronous on `cuda_stream` and allocates nothing. All calls on a device
  * share the static array and rewrite it: calls that overlap on the GPU (other streams or
  * threads) race, so serialise them. The first call on a device does the one-time set-up
- * (device address of the array, kernel attributes) and should come before any stream capture. */
+ * (device address of the array, kernel attributes) and should come before any stream capture.
+ * Every call stages a small table from host memory, so a stream that is being captured is
+ * refused with MONONN_ERR_INVALID_ARGUMENT. `out` and the row pitches must be 16-byte aligned;
+ * a misaligned one is refused on the host, nothing is launched. */
 #define MONONN_NOALLOC_MAX_TOKENS 16384
 int mononn_attention_noalloc(const void* q, const void* k, const void* v_t, const int32_t* mask,
                              void* out, unsigned batches, unsigned heads, unsigned seq,
                              unsigned ld_qk, unsigned ld_vt, unsigned ld_out, float scale,
                              float mask_scale, int causal, void* cuda_stream);
+/* Waits for `cuda_stream`, then reads the status word the kernel keeps in the same static array
+ * (no allocation): MONONN_OK, or MONONN_ERR_BARRIER_TIMEOUT when a bounded wait expired during
+ * the last mononn_attention_noalloc on this device, in which case `out` is incomplete. Like the
+ * entry point itself it has no counterpart in the reference, whose kernels spin without a bound
+ * (mononn_engine/core/gpu/synchronization.cc:45-97). */
+int mononn_attention_noalloc_status(void* cuda_stream);
 
 void mononn_destroy(mononn_module* m);
 const char* mononn_strerror(int code);

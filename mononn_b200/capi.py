@@ -18,7 +18,7 @@ EXPORTS = [
     "mononn_save_spec", "mononn_spec_json", "mononn_profile_stages", "mononn_module_cost",
     "mononn_destroy", "mononn_strerror", "mononn_last_error", "mononn_enabled",
     "mononn_trace_stages", "mononn_plan_json", "mononn_describe", "mononn_free_string", "mononn_launch_stages", "mononn_debug_skew_barrier", "mononn_attention_noalloc",
-    "mononn_infer_host",
+    "mononn_infer_host", "mononn_debug_mma_issue", "mononn_attention_noalloc_status",
 ]
 
 
@@ -77,6 +77,9 @@ def lib() -> C.CDLL:
         l.mononn_debug_skew_barrier.argtypes = [vp, C.c_uint]
         l.mononn_attention_noalloc.argtypes = [vp, vp, vp, vp, vp, C.c_uint, C.c_uint, C.c_uint, C.c_uint,
                                                C.c_uint, C.c_uint, C.c_float, C.c_float, C.c_int, vp]
+        l.mononn_attention_noalloc_status.argtypes = [vp]
+        dp = C.POINTER(C.c_double)
+        l.mononn_debug_mma_issue.argtypes = [C.c_int, C.c_uint, C.c_uint, C.c_uint, C.c_uint, C.c_uint, dp, dp, dp]
         l.mononn_destroy.argtypes = [vp]
         l.mononn_destroy.restype = None
         l.mononn_strerror.argtypes = [C.c_int]

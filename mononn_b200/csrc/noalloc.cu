@@ -143,9 +143,19 @@ extern "C" int mononn_attention_noalloc(const void* q, const void* k, const void
     return fail(MONONN_ERR_TOO_LARGE, "batches * seq = " + std::to_string(tokens) + " exceeds the " +
                                           std::to_string(MONONN_NOALLOC_MAX_TOKENS) +
                                           " tokens the static scratch is sized for");
-  const unsigned width = heads * 64u;
-  if (ld_qk < width || ld_out < width || ld_vt < seq || (ld_out % 8u) != 0u)
+  // geometry in 64 bits: heads * 64 and batches * heads must not wrap for absurd inputs
+  const uint64_t width64 = static_cast<uint64_t>(heads) * 64u;
+  const uint64_t items64 = static_cast<uint64_t>(batches) * heads * ((seq + 127u) / 128u);
+  if (width64 > 65536u || items64 > (1u << 24))
+    return fail(MONONN_ERR_TOO_LARGE, "heads * 64 exceeds 65536 columns or batches * heads exceeds 2^24 tiles");
+  const unsigned width = static_cast<unsigned>(width64);
+  if (ld_qk < width || ld_out < width || ld_vt < seq)
     return fail(MONONN_ERR_INVALID_ARGUMENT, "leading dimensions are smaller than the rows they hold");
+  if ((ld_out % 8u) != 0u || (reinterpret_cast<uintptr_t>(out) & 15u) != 0u)
+    return fail(MONONN_ERR_INVALID_ARGUMENT,
+                "out: base address and row pitch must be multiples of 16 bytes (the kernel stores 16-byte vectors)");
+  if (mask && (reinterpret_cast<uintptr_t>(mask) & 3u) != 0u)
+    return fail(MONONN_ERR_INVALID_ARGUMENT, "mask: int32 elements must be 4-byte aligned");
   int dev = 0;
   NA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return fail(MONONN_ERR_INVALID_ARGUMENT, "device ordinal out of range");
@@ -153,6 +163,15 @@ extern "C" int mononn_attention_noalloc(const void* q, const void* k, const void
   int rc = setup(dev, &st);
   if (rc) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  {
+    // Each call stages its table image from a stack buffer with cudaMemcpyAsync. A capturing
+    // stream would record that copy as a node that reads the buffer at replay time, long after
+    // this frame is gone, and would freeze this call's pointers into the tensor maps.
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    NA_TRY(cudaStreamIsCapturing(stream, &cap));
+    if (cap != cudaStreamCaptureStatusNone)
+      return fail(MONONN_ERR_INVALID_ARGUMENT, "the stream is being captured; this call stages host data per call");
+  }
   unsigned char* s = st->scratch;
 
   // host image of the table part of the scratch: stage, operator, three tensor maps
@@ -165,7 +184,7 @@ extern "C" int mononn_attention_noalloc(const void* q, const void* k, const void
   std::memset(&od, 0, sizeof(od));
   od.kind = OP_ATTENTION;
   od.flags = (mask ? F_MASK_BIAS : 0u) | (causal ? F_CAUSAL : 0u);
-  od.n_items = batches * heads * ((seq + 127u) / 128u);
+  od.n_items = static_cast<uint32_t>(items64);
   od.alpha = scale;
   od.heads = heads;
   od.seq = seq;
@@ -219,5 +238,30 @@ extern "C" int mononn_attention_noalloc(const void* q, const void* k, const void
   void* kargs[1] = {&kp};
   NA_TRY(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(mononn_megakernel), dim3(grid),
                                      dim3(kThreads), kargs, kSmemBytes, stream));
+  return MONONN_OK;
+}
+
+// Status of the allocation-free path: the kernel's status word lives in the static array, where a
+// bounded wait that expired leaves {code, stage, CTA, wait site}. Waits for `cuda_stream`, copies
+// the word out (no allocation) and reports it. The next mononn_attention_noalloc call clears it.
+extern "C" int mononn_attention_noalloc_status(void* cuda_stream) {
+  int dev = 0;
+  NA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(MONONN_ERR_INVALID_ARGUMENT, "device ordinal out of range");
+  DeviceState* st = nullptr;
+  int rc = setup(dev, &st);
+  if (rc) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  NA_TRY(cudaStreamSynchronize(stream));
+  KernelStatus ks;
+  NA_TRY(cudaMemcpy(&ks, st->scratch + kOffStatus, sizeof(ks), cudaMemcpyDeviceToHost));
+  if (ks.code != ST_OK)
+    return fail(MONONN_ERR_BARRIER_TIMEOUT, "a bounded wait expired in the attention kernel (code " +
+                                                std::to_string(ks.code) + ", CTA " + std::to_string(ks.cta) +
+                                                ", wait site 0x" + [&] {
+                                                  char b[16];
+                                                  std::snprintf(b, sizeof(b), "%x", ks.where);
+                                                  return std::string(b);
+                                                }() + "); `out` is incomplete");
   return MONONN_OK;
 }

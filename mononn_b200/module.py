@@ -254,6 +254,14 @@ def attention_noalloc(q_ptr: int, k_ptr: int, vt_ptr: int, mask_ptr: int | None,
                                          1 if causal else 0, C.c_void_p(st.cuda_stream)))
 
 
+def attention_noalloc_status(stream=None) -> None:
+    """Waits for the stream and raises MononnError(-6) when a bounded wait expired in the last
+    allocation-free attention call on this device (its output is then incomplete)."""
+    import torch
+    st = stream if stream is not None else torch.cuda.current_stream()
+    check(lib().mononn_attention_noalloc_status(C.c_void_p(st.cuda_stream)))
+
+
 def enabled() -> bool:
     """TF_MONONN_ENABLED truthiness (True / true / 1)."""
     return bool(lib().mononn_enabled())

@@ -137,6 +137,84 @@ def bert_encoder_torch(cfg, w, inputs, threads=0):
     return x.reshape(b * s, h).numpy()
 
 
+def _torch_weights(w):
+    import torch
+    return {k: torch.from_numpy(np.ascontiguousarray(v)) for k, v in w.items()}
+
+
+def _act_torch(x, kind):
+    import torch
+    import torch.nn.functional as F
+    if kind == "gelu_erf":
+        return F.gelu(x)
+    if kind == "relu":
+        return torch.relu(x)
+    if kind == "quick_gelu":
+        return x * torch.sigmoid(1.702 * x)
+    if kind == "gelu_tanh":
+        return F.gelu(x, approximate="tanh")
+    raise ValueError(kind)
+
+
+def preln_blocks_torch(cfg, tw, x, prefix="", causal=False):
+    """_preln_blocks through torch CPU ops (multi-threaded): the full-size parity cases need the
+    fp32 side in seconds. x: [B, S, H] torch tensor; tw: torch weights."""
+    import torch
+    import torch.nn.functional as F
+    b, s, h = x.shape
+    nh = cfg.heads
+    d = h // nh
+    tri = torch.triu(torch.full((s, s), -1e30), 1) if causal else None
+    for l in range(cfg.layers):
+        p = f"{prefix}layer{l}."
+        lin = lambda t, n: t @ tw[p + n + ".w"] + tw[p + n + ".b"]
+        split = lambda t: t.view(b, s, nh, d).transpose(1, 2)
+        y = F.layer_norm(x, (h,), tw[p + "ln1.gamma"], tw[p + "ln1.beta"], cfg.eps)
+        sc = split(lin(y, "attn.q")) @ split(lin(y, "attn.k")).transpose(-1, -2) / math.sqrt(d)
+        if tri is not None:
+            sc = sc + tri
+        ctx = (torch.softmax(sc, -1) @ split(lin(y, "attn.v"))).transpose(1, 2).reshape(b, s, h)
+        x = x + lin(ctx, "attn.o")
+        y = F.layer_norm(x, (h,), tw[p + "ln2.gamma"], tw[p + "ln2.beta"], cfg.eps)
+        x = x + lin(_act_torch(lin(y, "ffn.up"), cfg.act), "ffn.down")
+    return x
+
+
+def vit_encoder_torch(cfg, w, inputs, threads=0):
+    """vit_encoder through torch CPU ops. Returns [B*tokens, H] as numpy f32."""
+    import torch
+    import torch.nn.functional as F
+    if threads:
+        torch.set_num_threads(threads)
+    tw = _torch_weights(w)
+    b, h = cfg.batch, cfg.hidden
+    with torch.no_grad():
+        pat = torch.from_numpy(vit_patches(cfg, inputs["pixel_values"].astype(np.float32)))
+        pat = pat @ tw["embeddings.patch.w"].reshape(h, -1).T + tw["embeddings.patch.b"]
+        cls = tw["embeddings.cls"].reshape(1, 1, h).expand(b, 1, h)
+        x = torch.cat([cls, pat.reshape(b, cfg.seq - 1, h)], 1) + tw["embeddings.position"][None]
+        x = preln_blocks_torch(cfg, tw, x)
+        out = F.layer_norm(x, (h,), tw["ln.gamma"], tw["ln.beta"], cfg.eps)
+    return out.reshape(b * cfg.seq, h).numpy()
+
+
+def opt_decoder_torch(cfg, w, inputs, threads=0):
+    """opt_decoder through torch CPU ops. Returns (logits [B*S, vocab], argmax [B*S])."""
+    import torch
+    import torch.nn.functional as F
+    if threads:
+        torch.set_num_threads(threads)
+    tw = _torch_weights(w)
+    b, s_, h = cfg.batch, cfg.seq, cfg.hidden
+    with torch.no_grad():
+        ids = torch.from_numpy(inputs["input_ids"]).long()
+        x = tw["embeddings.word"][ids] + tw["embeddings.position"][2:2 + s_][None]
+        x = preln_blocks_torch(cfg, tw, x, causal=True)
+        y = F.layer_norm(x, (h,), tw["ln.gamma"], tw["ln.beta"], cfg.eps).reshape(b * s_, h)
+        logits = y @ tw["embeddings.word"].T
+    return logits.numpy(), logits.argmax(-1).to(torch.int32).numpy()
+
+
 def vit_patches(cfg, pixels):
     """[B, C, H, W] -> [B * patches, ky * kx * C]: the operand of the patch-embedding
     convolution (stride = window, cross-correlation, NHWC/KRSC as the reference's conv,

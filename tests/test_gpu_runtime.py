@@ -196,3 +196,24 @@ def test_infer_host_matches_run_and_reports_timeouts():
     got = hout.numpy().view(np.float16)
     assert np.abs(got[: want.size].astype(np.float32) - want[: got.size].astype(np.float32)).max() < 5e-3
     mod.close()
+
+
+def test_mma_issue_probe_reports_cycles_per_instruction():
+    """The tile menu rests on what one tcgen05.mma costs in isolation: the probe issues 256
+    instructions back to back from resident operands and reports cycles per instruction. A
+    wide instruction cannot beat the pipe (128 x 256 x 16 needs >= 100 cycles); a narrow one
+    must not cost more than a wide one."""
+    import ctypes as C
+    from mononn_b200 import capi
+    l = capi.lib()
+    table = {}
+    for n in (16, 64, 128, 256):
+        cyc, iss, ns = C.c_double(), C.c_double(), C.c_double()
+        capi.check(l.mononn_debug_mma_issue(0, n, 256, 1, 0, 148, C.byref(cyc), C.byref(iss), C.byref(ns)))
+        table[n] = cyc.value
+        assert 1.0 < cyc.value < 2000.0 and ns.value > 0
+    print("cycles per tcgen05.mma 128xNx16:", {n: round(v, 1) for n, v in table.items()})
+    assert table[256] >= 100.0
+    assert table[16] <= table[256] * 1.1
+    with pytest.raises(capi.MononnError):
+        capi.check(l.mononn_debug_mma_issue(0, 24, 256, 1, 0, 1, None, None, None))

@@ -38,6 +38,24 @@ def test_numpy_and_torch_restatements_agree():
     assert np.abs(a - b).max() < 2e-4
 
 
+def test_torch_variants_of_vit_and_opt_agree_with_the_numpy_ones():
+    """The full-size GPU parity cases use the torch-CPU variants (seconds instead of minutes);
+    here they are pinned to the numpy restatement, which the golden vectors pin in turn."""
+    from mononn_b200.models import opt_tiny, vit_tiny
+    cfg = vit_tiny(batch=2, image=48, layers=2, hidden=128, ffn=256)
+    w = make_weights(cfg, 6, stress=True)
+    inp = make_vit_inputs(cfg, 6)
+    assert np.abs(R.vit_encoder(cfg, w, inp) - R.vit_encoder_torch(cfg, w, inp, threads=1)).max() < 2e-4
+    cfg = opt_tiny(batch=2, seq=24, layers=2, hidden=128, vocab=1008)
+    w = make_weights(cfg, 7, stress=True)
+    inp = make_inputs(cfg, 7)
+    a, ia = R.opt_decoder(cfg, w, inp)
+    b, ib = R.opt_decoder_torch(cfg, w, inp, threads=1)
+    assert np.abs(a - b).max() < 2e-4
+    margin = np.sort(a, -1)[:, -1] - np.sort(a, -1)[:, -2]
+    assert np.array_equal(ia[margin > 1e-3], ib[margin > 1e-3])
+
+
 def test_mask_changes_only_through_masked_keys():
     cfg = bert_tiny(seq=16)
     w = make_weights(cfg, 3, stress=True)
