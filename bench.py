@@ -53,7 +53,7 @@ class ClockSampler:
     """nvidia-smi clock / throttle-reason samples while the timed region runs."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+              "clocks_event_reasons.sw_power_cap,utilization.gpu")
 
     def __init__(self, device_index: int):
         self.proc = None
@@ -63,7 +63,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
@@ -77,23 +77,26 @@ class ClockSampler:
         except Exception:
             self.proc.kill()
             out = ""
-        sm, mx, reasons = [], [], set()
+        sm, mx, busy, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in out.strip().splitlines():
             f = [x.strip() for x in line.split(",")]
-            if len(f) < 7:
+            if len(f) < 8:
                 continue
             try:
                 sm.append(float(f[0]))
                 mx.append(float(f[1]))
+                busy.append(float(f[7]) > 0.0)
             except ValueError:
                 continue
             for n, v in zip(names, f[3:7]):
                 if v.lower().startswith("active"):
                     reasons.add(n)
-        return {"sm_mhz": float(np.median(sm)) if sm else None,
+        loaded = [c for c, b in zip(sm, busy) if b]
+        return {"sm_mhz": float(np.median(loaded or sm)) if sm else None,
                 "sm_max_mhz": float(max(mx)) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "samples_under_load": len(loaded), "reasons": sorted(reasons),
+                "window": "from before the warm-up launches to after the end-to-end leg"}
 
 
 def dist_env():
@@ -108,12 +111,33 @@ def replica_throughput(n_gpus: int, steps: int, max_seconds: float) -> float:
     return n_gpus * steps / max_seconds if max_seconds > 0 else 0.0
 
 
+def physical_cores() -> int:
+    """Physical cores of the host (distinct (package, core) pairs), else the logical count."""
+    try:
+        pairs, phys, core = set(), None, None
+        for line in open("/proc/cpuinfo"):
+            if line.startswith("physical id"):
+                phys = line.split(":")[1].strip()
+            elif line.startswith("core id"):
+                core = line.split(":")[1].strip()
+            elif not line.strip():
+                if phys is not None and core is not None:
+                    pairs.add((phys, core))
+                phys = core = None
+        if pairs:
+            return len(pairs)
+    except OSError:
+        pass
+    return os.cpu_count() or 1
+
+
 def time_cpu_restatement(cfg, weights, inputs, budget_s: float = 15.0, max_iters: int = 100,
-                         warmup: int = 3):
-    """Bounded timing of the fp32 CPU restatement with all host threads."""
+                         warmup: int = 3, threads: int = 0):
+    """Bounded timing of the fp32 CPU restatement on `threads` host threads (0: one per
+    physical core)."""
     import torch
     from oracle import ref_encoder
-    cores = os.cpu_count() or 1
+    cores = threads or physical_cores()
     torch.set_num_threads(cores)
     for _ in range(warmup):
         ref_encoder.bert_encoder_torch(cfg, weights, inputs)
@@ -138,7 +162,7 @@ def run_reference(args):
     per_step = max(1, min(20, int(100 / max(1, args.steps))))  # inferences per step (bounded)
     import torch
     from oracle import ref_encoder
-    cores = os.cpu_count() or 1
+    cores = physical_cores()
     torch.set_num_threads(cores)
     for _ in range(args.warmup):
         ref_encoder.bert_encoder_torch(cfg, w, inp)
@@ -156,11 +180,40 @@ def run_reference(args):
                    "note": "TF-XLA CPU is not installable here; this is the fp32 CPU restatement "
                            "(torch CPU ops) of the same graph"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": f"{per_step} inferences per step x {args.steps} steps"},
+                         "logical_cpus": os.cpu_count(),
+                         "sample": f"{per_step} inferences per step x {args.steps} steps, "
+                                   f"one thread per physical core"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def spec_override_dir(overrides: str, text: str, kind: str):
+    """Diagnostic A/B switch: `--spec row_fusion=off,qkv_fusion=off` writes the heuristic spec
+    with those fields changed into a temporary spec directory and returns it (else None)."""
+    if not overrides:
+        return None
+    import tempfile
+    from mononn_b200.module import describe
+    d = describe(kind, text)
+    spec = d["spec"]
+    for kv in overrides.split(","):
+        k, v = kv.split("=")
+        if k == "grid":
+            spec["cuda_context"]["cuda_runtime_context"]["grid_dim"]["x"] = int(v)
+            spec["gemm_spec_list"] = {}
+        else:
+            spec[k] = v
+            if k in ("qkv_fusion", "row_fusion"):
+                spec["gemm_spec_list"] = {}
+    name = d["plan"]["module"]
+    root = tempfile.mkdtemp(prefix="mononn_spec_")
+    from mononn_b200.module import cluster_dir
+    os.makedirs(os.path.join(root, cluster_dir(name)), exist_ok=True)
+    with open(os.path.join(root, cluster_dir(name), "best_tuning_spec.json"), "w") as f:
+        json.dump(spec, f)
+    return root
 
 
 def run_ours(args):
@@ -181,12 +234,17 @@ def run_ours(args):
     cfg = bert_base()
     w = make_weights(cfg, 1234)
     inp = make_inputs(cfg, 1234 + rank)
+    opts = dict(device=local, tuning_level=args.tuning_level)
+    spec_dir = spec_override_dir(args.spec, bert_hlo(cfg)[0] if args.frontend == "hlo" else cfg.to_json(),
+                                 "hlo" if args.frontend == "hlo" else "encoder")
+    if spec_dir:
+        opts["spec_dir"] = spec_dir
     if args.frontend == "hlo":
         text, names = bert_hlo(cfg)
-        mod = compile_hlo(text, device=local)
+        mod = compile_hlo(text, **opts)
         mod.set_weights({names[k]: v for k, v in w.items()})
     else:
-        mod = compile_encoder(cfg, device=local)
+        mod = compile_encoder(cfg, **opts)
         mod.set_weights(w)
     if args.tune:
         mod.tune()
@@ -209,15 +267,15 @@ def run_ours(args):
 
     # ---- device-resident timing: K steps, each bracketed by its own event pair so that the
     # L2 flush between steps stays outside the measured time
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
     for _ in range(max(args.warmup, 3)):
         mod.launch()
     mod.status()
-    sampler = ClockSampler(local)
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
           for _ in range(args.steps)]
     barrier()
-    if rank == 0:
-        sampler.start()
     for e0, e1 in ev:
         if flush is not None:
             flush.zero_()
@@ -263,8 +321,11 @@ def run_ours(args):
         cpu = None
         if world == 1 and not args.no_cpu:
             v, cores, n, dt = time_cpu_restatement(cfg, w, inp)
+            v1, _, n1, dt1 = time_cpu_restatement(cfg, w, inp, budget_s=6.0, max_iters=20, warmup=1, threads=1)
             cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
-                   "sample": f"{n} inferences of the same workload in {dt:.1f} s (torch CPU fp32)"}
+                   "logical_cpus": os.cpu_count(), "single_thread": v1,
+                   "sample": f"{n} inferences of the same workload in {dt:.1f} s on {cores} threads (one per "
+                             f"physical core) and {n1} in {dt1:.1f} s on one thread (torch CPU fp32)"}
         h2d = sum(h.numel() for h in host_in)
         line = {
             "metric": METRIC, "value": replica_throughput(world, args.steps, dev_s), "unit": UNIT,
@@ -369,6 +430,133 @@ def run_diagnostics(args):
     mod.close()
 
 
+def run_config(args):
+    """Not a bench line: one launch per inference of another configuration at full size, device
+    time by CUDA events with an L2 flush between launches, against the slower of algorithmic
+    bytes at the measured HBM peak and FLOPs at the measured dense tensor peak."""
+    import torch
+    from mononn_b200 import (clip_b32, compile_hlo, make_clip_inputs, make_inputs, make_vit_inputs,
+                             make_weights, opt_1p3b, vit_base)
+    from mononn_b200.hlo_builder import bert_hlo, clip_hlo, opt_hlo, vit_hlo
+    from mononn_b200.models import EncoderConfig
+    torch.cuda.set_device(0)
+    name = args.config
+    large = lambda b: EncoderConfig(layers=24, hidden=1024, heads=16, ffn=4096, batch=b, seq=384)
+    table = {
+        "bert_large_b1": (large(1), bert_hlo, 1235, "bert"), "bert_large_b16": (large(16), bert_hlo, 1235, "bert"),
+        "vit_b1": (vit_base(1), vit_hlo, 1236, "vit"), "vit_b64": (vit_base(64), vit_hlo, 1236, "vit"),
+        "opt_b1": (opt_1p3b(1), opt_hlo, 1237, "opt"), "opt_b8": (opt_1p3b(8), opt_hlo, 1237, "opt"),
+        "clip": (clip_b32(), clip_hlo, 1238, "clip"),
+    }
+    cfg, hlo, seed, family = table[name]
+    w = make_weights(cfg, seed)
+    text, names = hlo(cfg)
+    mod = compile_hlo(text, device=0, barrier_timeout_us=2000000)
+    mod.set_weights({names[k]: v for k, v in w.items()})
+    if family == "bert":
+        inp = make_inputs(cfg, seed, pad_fraction=0.25)
+        ins = [inp["input_ids"], inp["attention_mask"], inp["token_type_ids"]]
+    elif family == "vit":
+        ins = [make_vit_inputs(cfg, seed)["pixel_values"]]
+    elif family == "opt":
+        ins = [make_inputs(cfg, seed)["input_ids"]]
+    else:
+        inp = make_clip_inputs(cfg, seed)
+        ins = [inp["pixel_values"], inp["input_ids"]]
+    mod.run(ins)
+    if args.tune:
+        mod.tune()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(max(args.warmup, 3)):
+        mod.launch()
+    steps = min(args.steps, 50)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for e0, e1 in ev:
+        flush.zero_()
+        e0.record()
+        mod.launch()
+        e1.record()
+    torch.cuda.synchronize()
+    mod.status()
+    us = sum(e0.elapsed_time(e1) for e0, e1 in ev) * 1e3 / steps
+    alg_bytes, alg_flops = mod.cost()
+    peak_gbs, kind = measured_hbm_peak()
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peak_tf = float(json.load(f)["bf16_tflops"])
+    except Exception:
+        peak_tf = 1590.0
+    t_hbm = alg_bytes / (peak_gbs * 1e9) * 1e6
+    t_tc = alg_flops / (peak_tf * 1e12) * 1e6
+    print(json.dumps({"diagnostic": "config", "config": name, "us_per_launch": us, "launches": steps,
+                      "stages": len(mod.plan()["stages"]), "algorithmic_bytes": alg_bytes,
+                      "algorithmic_flops": alg_flops, "roofline_us": max(t_hbm, t_tc),
+                      "bound": "hbm" if t_hbm >= t_tc else "tensor", "frac": max(t_hbm, t_tc) / us,
+                      "peaks": {"hbm_gbs": peak_gbs, "tensor_tflops": peak_tf, "source": kind}}))
+    mod.close()
+
+
+def run_torch_baseline(args):
+    """Not a bench line and not the product path: BERT-base b1/s128 forward written with plain
+    torch fp16 ops (library GEMMs, one kernel per operator) on the same GPU, eager and replayed
+    from a CUDA graph, so that the single persistent launch can be compared with the path every
+    user already has."""
+    import math
+    import torch
+    import torch.nn.functional as F
+    from mononn_b200 import bert_base, make_inputs, make_weights
+    torch.cuda.set_device(0)
+    cfg = bert_base()
+    w = {k: torch.from_numpy(v).cuda().half() for k, v in make_weights(cfg, 1234).items()}
+    inp = make_inputs(cfg, 1234)
+    ids = torch.from_numpy(inp["input_ids"]).long().cuda()
+    types = torch.from_numpy(inp["token_type_ids"]).long().cuda()
+    mask_bias = ((1.0 - torch.from_numpy(inp["attention_mask"]).float()) * -10000.0).cuda().half()
+    b, s_, h, nh = cfg.batch, cfg.seq, cfg.hidden, cfg.heads
+
+    def forward():
+        x = w["embeddings.word"][ids] + w["embeddings.position"][:s_][None] + w["embeddings.token_type"][types]
+        x = F.layer_norm(x, (h,), w["embeddings.ln.gamma"], w["embeddings.ln.beta"], cfg.eps)
+        for l in range(cfg.layers):
+            p = f"layer{l}."
+            lin = lambda t, n: torch.addmm(w[p + n + ".b"], t.reshape(-1, t.shape[-1]), w[p + n + ".w"]).view(b, s_, -1)
+            split = lambda t: t.view(b, s_, nh, h // nh).transpose(1, 2)
+            q, k, v = split(lin(x, "attn.q")), split(lin(x, "attn.k")), split(lin(x, "attn.v"))
+            sc = q @ k.transpose(-1, -2) / math.sqrt(h // nh) + mask_bias[:, None, None, :]
+            ctx = (torch.softmax(sc, -1) @ v).transpose(1, 2).reshape(b, s_, h)
+            x = F.layer_norm(lin(ctx, "attn.o") + x, (h,), w[p + "attn.ln.gamma"], w[p + "attn.ln.beta"], cfg.eps)
+            y = F.gelu(lin(x, "ffn.up"))
+            x = F.layer_norm(lin(y, "ffn.down") + x, (h,), w[p + "ffn.ln.gamma"], w[p + "ffn.ln.beta"], cfg.eps)
+        return x
+
+    def timed(fn, n):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / n
+
+    with torch.no_grad():
+        eager = timed(forward, args.steps)
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            forward()
+            with torch.cuda.graph(g, stream=side):
+                forward()
+        torch.cuda.synchronize()
+        replay = timed(g.replay, args.steps)
+    print(json.dumps({"diagnostic": "torch_fp16_baseline", "workload": "BERT-base b1 s128",
+                      "eager_us": eager, "cuda_graph_replay_us": replay, "launches": args.steps,
+                      "note": "plain torch fp16 ops with library GEMMs; weights stay L2/HBM resident between "
+                              "launches (no flush)"}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -377,7 +565,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--frontend", default="hlo", choices=["hlo", "builder"],
                     help="lower from authored HLO text (the hook path) or the config builder")
-    ap.add_argument("--tune", action="store_true", help="run the on-device tile search first")
+    ap.add_argument("--tune", action="store_true", help="run the on-device schedule search first")
+    ap.add_argument("--tuning-level", type=int, default=1, help="what --tune searches (see include/mononn.h)")
+    ap.add_argument("--spec", default="", help="diagnostic: spec fields to override, e.g. row_fusion=off,grid=128")
+    ap.add_argument("--config", default="", help="diagnostic: time another configuration (bert_large_b1, "
+                    "bert_large_b16, vit_b1, vit_b64, opt_b1, opt_b8, clip) and print its roofline fraction")
+    ap.add_argument("--torch-baseline", action="store_true",
+                    help="diagnostic: the same BERT-base forward in plain torch fp16 on this GPU (eager and graph replay)")
     ap.add_argument("--no-flush", action="store_true", help="do not flush L2 between timed steps")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--e2e-io", default="copy", choices=["copy", "zero_copy"],
@@ -386,7 +580,11 @@ def main():
     ap.add_argument("--stage-report", action="store_true",
                     help="diagnostic: per operator class time and the barrier's share, from the event trace")
     args = ap.parse_args()
-    if args.stages or args.stage_report:
+    if args.config:
+        run_config(args)
+    elif args.torch_baseline:
+        run_torch_baseline(args)
+    elif args.stages or args.stage_report:
         run_diagnostics(args)
     elif args.impl == "reference":
         run_reference(args)

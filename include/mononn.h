@@ -7,7 +7,9 @@
  *     no CPU fallback: without a usable sm_100 device the calls fail.
  *   - pointers are borrowed for the duration of the call unless the parameter is `out`.
  *   - different modules may be used from different threads; one module from one
- *     thread at a time.
+ *     thread at a time. Launches of one module must be ordered on the GPU (one stream, or
+ *     streams chained by events): a module owns one barrier counter and one stage table.
+ *   - every call runs on the module's device and restores the caller's current device.
  */
 #ifndef MONONN_B200_H_
 #define MONONN_B200_H_
@@ -43,8 +45,11 @@ typedef struct {
   int device;                   /* CUDA device ordinal (the reference hard-codes 0) */
   const char* dump_dir;         /* where tune() writes specs and reports */
   const char* spec_dir;         /* existing tuning spec to load instead of tuning */
-  int threadpool_size;          /* host threads for lowering candidates; 0 = all cores */
-  int tuning_level;             /* 0 heuristics only, 1 per-GEMM tile search, 2 + grid search */
+  int threadpool_size;          /* host threads that re-pack weights into tiles whenever a plan is
+                                   (re)loaded, i.e. per tuning candidate; 0 = all cores */
+  int tuning_level;             /* what mononn_tune searches: 0 nothing (times the heuristic spec),
+                                   1 stage structure (qkv_fusion, row_fusion) and per-GEMM-class
+                                   tiles timed on their own stage, 2 + the number of CTAs */
   unsigned barrier_timeout_us;  /* bound on every in-kernel wait; 0 = 2 000 000 */
 } mononn_options;
 

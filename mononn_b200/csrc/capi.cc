@@ -65,6 +65,7 @@ static int finish_compile(mononn_module* m, const mononn_options* opt, mononn_mo
     m->threadpool_size = v ? std::atoi(v) : 0;
   }
   m->tuning_level = opt ? opt->tuning_level : 0;
+  m->rt.pack_threads = m->threadpool_size;
   int rc = m->rt.init(opt ? opt->device : 0);
   if (rc) {
     delete m;

@@ -5,16 +5,17 @@
 // text per HLO module, the host fills a stage table (stage_table.h) and this
 // kernel interprets it in a single cooperative launch.
 //
-// Warp roles inside each 256-thread CTA (one CTA per SM):
+// Warp roles inside each 384-thread CTA (one CTA per SM):
 //   warp 0  weight producer : streams packed weight tiles HBM -> smem ring via TMA.
 //                             It never waits for the grid barrier (weights do not
 //                             depend on activations), so HBM stays busy across stages.
 //   warp 1  activation producer : after the previous stage's grid barrier, TMA-loads
 //                             128x64 activation tiles (L2 resident) into the A ring.
 //   warp 2  MMA issuer      : tcgen05.mma (kind::f16, fp32 accumulate in TMEM).
-//   warps 4-7 epilogue/SIMT : tcgen05.ld -> bias/activation/residual -> global;
+//   warps 4-11 epilogue/SIMT: tcgen05.ld -> bias/activation/residual -> global;
 //                             softmax of the attention stage; LayerNorm / embedding rows;
-//                             grid-barrier arrive.
+//                             grid-barrier arrive. Two warps share each 32-lane quarter of
+//                             TMEM (warp w reads lanes 32*(w%4)..) and split its columns.
 //
 // Grid barrier (replaces mononn_engine/core/gpu/synchronization.cc:45-97): one
 // monotonically increasing counter; each CTA adds 1 with release semantics after
@@ -186,19 +187,21 @@ struct Ctrl {
   uint64_t b_empty[kBSlots];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
-  uint64_t group_bar;  // the four epilogue warps (128 arrivals per phase)
+  uint64_t group_bar;  // the eight epilogue warps (256 arrivals per phase)
   uint32_t tmem_base;
   uint32_t abort_flag;
   float bias_tile[2][256];  // bias of the current GEMM tile, double buffered across items
   float mask_row[384];      // additive key mask of the current attention tile (log2 units)
-  float red_val[4];         // arg-max: per-warp partial results of the current row
-  uint32_t red_idx[4];
+  float row_max[2][128];    // attention: row maximum / row sum over each warp half's columns,
+  float row_sum[2][128];    // exchanged between the two threads that share a query row
+  float red_val[kSimtWarps];  // arg-max: per-warp partial results of the current row
+  uint32_t red_idx[kSimtWarps];
   // Shared-memory copies of the operator descriptor each role is working on: slot 0 weight
-  // producer, 1 activation producer, 2 MMA issuer, 3..6 the four epilogue warps.
-  uint4 desc[7][16];
+  // producer, 1 activation producer, 2 MMA issuer, 3.. the eight epilogue warps.
+  uint4 desc[3 + kSimtWarps][16];
 };
 
-static_assert(sizeof(Ctrl) <= 8192, "control block exceeds its shared-memory reserve");
+static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block exceeds its shared-memory reserve");
 static_assert(sizeof(OpDesc) % 16 == 0 && sizeof(OpDesc) <= 256, "descriptor slot size");
 static_assert(sizeof(StageDesc) == 48, "stage descriptor is read as three 16-byte words");
 
@@ -208,7 +211,7 @@ struct Ctx {
   uint32_t a_ring;  // shared addresses
   uint32_t b_ring;
   uint8_t* a_ring_ptr;
-  uint8_t* store_stage;  // kStoreStageBytes after the control block: 4 KB per epilogue warp
+  uint8_t* store_stage;  // kStoreStageBytes after the control block: 2 KB per epilogue warp
   uint32_t stage;   // current stage (for status)
   uint32_t group_phase;  // parity of the next group_bar phase (epilogue warps only)
   uint64_t timeout_ns;
@@ -317,7 +320,59 @@ __device__ __forceinline__ bool grid_wait_warp(const Ctx& c, uint32_t stage, uin
   if ((threadIdx.x & 31u) == 0u) ok = grid_wait(c, stage, where);
   return __all_sync(0xffffffffu, ok);
 }
-// Barrier across the 128 epilogue threads built on an mbarrier so that, unlike bar.sync,
+// A row op that shares a stage with the split-K GEMMs feeding it waits until all of their work
+// items have added themselves to the arrival counter (each after its reductions, with release).
+// Bounded like every wait; the waiting CTAs have no GEMM item left to do, so the GEMM items
+// never depend on a waiter.
+__device__ __noinline__ bool flag_wait_slow(const KernelParams* P, Ctrl* ctrl, const uint32_t* flag,
+                                            uint32_t target, uint32_t stage, uint32_t where) {
+  const uint64_t t0 = globaltimer_ns();
+  const uint64_t limit = static_cast<uint64_t>(P->timeout_us) * 1000ull;
+  uint32_t it = 0;
+  for (;;) {
+    if (ld_relaxed_gpu(flag) >= target) {
+      fence_acq_rel_gpu();
+      return true;
+    }
+    __nanosleep(32);
+    if ((++it & 31u) == 0u) {
+      if (*reinterpret_cast<volatile uint32_t*>(&ctrl->abort_flag)) return false;
+      if (*reinterpret_cast<volatile uint32_t*>(&P->status->code) != 0u) {
+        *reinterpret_cast<volatile uint32_t*>(&ctrl->abort_flag) = 1;
+        return false;
+      }
+      if (globaltimer_ns() - t0 > limit) {
+        report_failure(P, ctrl, stage, ST_GRID_BARRIER_TIMEOUT, where);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ bool flag_wait_warp(const Ctx& c, const OpDesc& op, uint32_t where) {
+  bool ok = true;
+  if ((threadIdx.x & 31u) == 0u) {
+    const uint32_t* flag = reinterpret_cast<const uint32_t*>(op.flag);
+    if (ld_relaxed_gpu(flag) >= op.flag_target) {
+      fence_acq_rel_gpu();
+    } else {
+      ok = flag_wait_slow(c.P, c.ctrl, flag, op.flag_target, c.stage, where);
+    }
+  }
+  return __all_sync(0xffffffffu, ok);
+}
+// After its row a waiting warp counts itself; the last one of the operator (every warp of every
+// item has then passed the wait, and no GEMM item adds any more) clears both counters for the
+// next launch.
+__device__ __forceinline__ void flag_done_warp(const OpDesc& op) {
+  if ((threadIdx.x & 31u) == 0u) {
+    uint32_t* flag = reinterpret_cast<uint32_t*>(op.flag);
+    if (atomicAdd(flag + 1, 1u) + 1u == op.n_items * kRowsPerItem) {
+      flag[0] = 0u;
+      flag[1] = 0u;
+    }
+  }
+}
+// Barrier across the 256 epilogue threads built on an mbarrier so that, unlike bar.sync,
 // the wait is bounded when a warp has already left on the abort path.
 __device__ __forceinline__ bool group_sync(Ctx& c, uint32_t where) {
   mbar_arrive(smem_u32(&c.ctrl->group_bar));
@@ -794,10 +849,12 @@ __device__ __forceinline__ void add4(float4& a, const float4 b) {
   a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
 }
 
-// Thread `row` of the 128 epilogue threads owns accumulator row `row` (TMEM lane = row).
+// Accumulator row `quarter * 32 + lane` (TMEM lane = row) is shared by the two warps of the
+// quarter: warp `half` takes every other column group of the tile (groups of 32 columns, of 16
+// for tiles up to 32 wide so that both warps have work).
 __device__ __noinline__ void gemm_epilogue(const OpDesc& op, uint32_t local, uint32_t tmem_acc,
-                                           uint32_t quarter, uint32_t lane, const float* bias_s,
-                                           uint8_t* stg) {
+                                           uint32_t quarter, uint32_t half, uint32_t lane,
+                                           const float* bias_s, uint8_t* stg) {
   const GemmTile t = gemm_tile(op, local);
   const uint32_t grow = t.mt * 128u + quarter * 32u + lane;
   const bool row_ok = grow < op.M;
@@ -808,84 +865,88 @@ __device__ __noinline__ void gemm_epilogue(const OpDesc& op, uint32_t local, uin
   const float alpha = op.alpha;
   const uint64_t pout = op.p[0], presid = op.p[2];
   const bool bias_on = (flags & F_BIAS) && lead, resid_on = (flags & F_RESID) && lead;
+  // row-major f16 output: a 32-column group is collected in the warp's staging block (32 rows x
+  // 64 bytes, swizzled) and stored four lanes to a row instead of one row per lane
+  const bool staged = (out_mode == OUT_F16);
+  const uint32_t sw = (lane >> 1) & 3u;
+  const uint32_t gstep = (n_tile <= 32u) ? 16u : 32u;
 #pragma unroll 1
-  for (uint32_t c0 = 0; c0 < n_tile; c0 += 16) {
-    float v[16];
-    tc_ld16(tmem_acc + ((quarter * 32u) << 16) + c0, v);
-    const uint32_t col = n0 + c0;
-    // row-major f16 output: 64-column groups are collected in the warp's staging block and
-    // stored eight lanes to a row (whole lines) instead of one row per lane
-    const bool staged = (out_mode == OUT_F16);
-    const uint32_t g0 = c0 & ~63u;
-    const bool flush = staged && (c0 + 16u >= n_tile || ((c0 + 16u) & 63u) == 0u);
-    if (row_ok && col < N) {
-    if (alpha != 1.0f) {
+  for (uint32_t g0 = half * gstep; g0 < n_tile; g0 += 2u * gstep) {
+    const uint32_t gw = (n_tile - g0 < gstep) ? n_tile - g0 : gstep;  // 16 or 32 columns
+#pragma unroll 1
+    for (uint32_t c0 = g0; c0 < g0 + gw; c0 += 16) {
+      float v[16];
+      tc_ld16(tmem_acc + ((quarter * 32u) << 16) + c0, v);
+      const uint32_t col = n0 + c0;
+      if (row_ok && col < N) {
+        if (alpha != 1.0f) {
 #pragma unroll
-      for (int i = 0; i < 16; ++i) v[i] *= alpha;
-    }
-    if (bias_on) {
-      const float4* bq = reinterpret_cast<const float4*>(bias_s + c0);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float4 t = bq[i];
-        v[4 * i] += t.x; v[4 * i + 1] += t.y; v[4 * i + 2] += t.z; v[4 * i + 3] += t.w;
-      }
-    }
-    apply_act16(v, act);
-    if (resid_on) {
-      if (flags & F_RESID_F32) {
-        const float4* r = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(presid) +
-                                                          static_cast<size_t>(grow) * ldr + col);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float4 x = __ldcg(r + i);
-          v[4 * i] += x.x; v[4 * i + 1] += x.y; v[4 * i + 2] += x.z; v[4 * i + 3] += x.w;
+          for (int i = 0; i < 16; ++i) v[i] *= alpha;
         }
-      } else {
-        const uint2* r = reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(presid) +
-                                                        static_cast<size_t>(grow) * ldr + col);
+        if (bias_on) {
+          const float4* bq = reinterpret_cast<const float4*>(bias_s + c0);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float4 x = h4_to_f4(__ldcg(r + i));
-          v[4 * i] += x.x; v[4 * i + 1] += x.y; v[4 * i + 2] += x.z; v[4 * i + 3] += x.w;
+          for (int i = 0; i < 4; ++i) {
+            const float4 t = bq[i];
+            v[4 * i] += t.x; v[4 * i + 1] += t.y; v[4 * i + 2] += t.z; v[4 * i + 3] += t.w;
+          }
         }
-      }
+        apply_act16(v, act);
+        if (resid_on) {
+          if (flags & F_RESID_F32) {
+            const float4* r = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(presid) +
+                                                              static_cast<size_t>(grow) * ldr + col);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float4 x = __ldcg(r + i);
+              v[4 * i] += x.x; v[4 * i + 1] += x.y; v[4 * i + 2] += x.z; v[4 * i + 3] += x.w;
+            }
+          } else {
+            const uint2* r = reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(presid) +
+                                                            static_cast<size_t>(grow) * ldr + col);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float4 x = h4_to_f4(__ldcg(r + i));
+              v[4 * i] += x.x; v[4 * i + 1] += x.y; v[4 * i + 2] += x.z; v[4 * i + 3] += x.w;
+            }
+          }
+        }
+        if (out_mode == OUT_F16) {
+          const uint32_t ch = (c0 - g0) >> 3;  // 0 or 2
+          *reinterpret_cast<uint4*>(stg + lane * 64u + ((ch ^ sw) << 4)) =
+              make_uint4(pack_h2(v[0], v[1]), pack_h2(v[2], v[3]), pack_h2(v[4], v[5]), pack_h2(v[6], v[7]));
+          *reinterpret_cast<uint4*>(stg + lane * 64u + (((ch + 1u) ^ sw) << 4)) =
+              make_uint4(pack_h2(v[8], v[9]), pack_h2(v[10], v[11]), pack_h2(v[12], v[13]), pack_h2(v[14], v[15]));
+        } else if (out_mode == OUT_F32_RED) {
+          float* o = reinterpret_cast<float*>(pout) + static_cast<size_t>(grow) * ldo + col;
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            red_add_f32x4(o + 4 * i, v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        } else if (out_mode == OUT_F16_T) {
+          const uint32_t b = grow / op.rows_per_batch, rib = grow % op.rows_per_batch;
+          const uint32_t ldt = op.ldt;
+          __half* o = reinterpret_cast<__half*>(pout) + (static_cast<size_t>(b) * N + col) * ldt + rib;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) o[static_cast<size_t>(i) * ldt] = __float2half_rn(v[i]);
+        } else {
+          float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(pout) +
+                                                static_cast<size_t>(grow) * ldo + col);
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            o[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        }
+      }  // row_ok && col < N
     }
-    if (out_mode == OUT_F16) {
-      const uint32_t ch = (c0 - g0) >> 3;
-      *reinterpret_cast<uint4*>(stg + lane * 128u + ((ch ^ (lane & 7u)) << 4)) =
-          make_uint4(pack_h2(v[0], v[1]), pack_h2(v[2], v[3]), pack_h2(v[4], v[5]), pack_h2(v[6], v[7]));
-      *reinterpret_cast<uint4*>(stg + lane * 128u + (((ch + 1u) ^ (lane & 7u)) << 4)) =
-          make_uint4(pack_h2(v[8], v[9]), pack_h2(v[10], v[11]), pack_h2(v[12], v[13]), pack_h2(v[14], v[15]));
-    } else if (out_mode == OUT_F32_RED) {
-      float* o = reinterpret_cast<float*>(pout) + static_cast<size_t>(grow) * ldo + col;
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-        red_add_f32x4(o + 4 * i, v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-    } else if (out_mode == OUT_F16_T) {
-      const uint32_t b = grow / op.rows_per_batch, rib = grow % op.rows_per_batch;
-      const uint32_t ldt = op.ldt;
-      __half* o = reinterpret_cast<__half*>(pout) + (static_cast<size_t>(b) * N + col) * ldt + rib;
-#pragma unroll
-      for (int i = 0; i < 16; ++i) o[static_cast<size_t>(i) * ldt] = __float2half_rn(v[i]);
-    } else {
-      float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(pout) +
-                                            static_cast<size_t>(grow) * ldo + col);
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-        o[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-    }
-    }  // row_ok && col < N
-    if (flush) {
+    if (staged) {
       __syncwarp();
-      const uint32_t chunks = (c0 + 16u - g0) >> 3;  // 16-byte chunks per row in this group (2..8)
+      const uint32_t chunks = gw >> 3;  // 16-byte chunks per row in this group (2 or 4)
       const uint32_t row0 = t.mt * 128u + quarter * 32u;
       for (uint32_t idx = lane; idx < 32u * chunks; idx += 32u) {
         const uint32_t r = idx / chunks, q = idx - r * chunks;
         const uint32_t gcol = n0 + g0 + q * 8u;
         if (row0 + r < op.M && gcol < N)
           *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(pout) + static_cast<size_t>(row0 + r) * ldo + gcol) =
-              *reinterpret_cast<const uint4*>(stg + r * 128u + ((q ^ (r & 7u)) << 4));
+              *reinterpret_cast<const uint4*>(stg + r * 64u + ((q ^ ((r >> 1) & 3u)) << 4));
       }
       __syncwarp();
     }
@@ -946,11 +1007,11 @@ __device__ __forceinline__ void row_emit(float4 a, float mean, float rstd, uint3
   }
 }
 
-// LayerNorm / embedding item: four rows, one warp each. Rows up to 1024 columns stay in
+// LayerNorm / embedding item: eight rows, one warp each. Rows up to 1024 columns stay in
 // registers between the statistics and the normalisation; wider rows are re-read.
 __device__ __noinline__ void rowwise_item(const OpDesc& op, uint32_t local, uint32_t warp_in_group,
                                           uint32_t lane, const KernelParams& P, uint32_t stage) {
-  const uint32_t row = local * 4u + warp_in_group;
+  const uint32_t row = local * kRowsPerItem + warp_in_group;
   if (row >= op.rows) return;
   const bool mark = (warp_in_group == 0 && lane == 0);
   if (mark) trace(P, stage, TR_MARK0);
@@ -1150,12 +1211,12 @@ __device__ __noinline__ void rowwise_item(const OpDesc& op, uint32_t local, uint
   if (mark) trace(P, stage, TR_MARK0 + 2);
 }
 
-// Arg-max item: one f16 row per 128-thread group. Each thread scans every 128th 16-byte
+// Arg-max item: one f16 row per 256-thread group. Each thread scans every 256th 16-byte
 // vector in ascending order (so "strictly greater" keeps its first maximum), then the
 // partial results are merged by (larger value, then smaller index): the first index of the
 // row maximum, which is what XLA's (value, index) reduce returns
 // (reduction functors: mononn_engine/codegen/reduction_functor_generator.cc:296-441).
-__device__ __noinline__ bool argmax_item(Ctx& c, const OpDesc& op, uint32_t row, uint32_t quarter,
+__device__ __noinline__ bool argmax_item(Ctx& c, const OpDesc& op, uint32_t row, uint32_t widx,
                                          uint32_t lane, uint32_t tid_in_group) {
   const uint32_t nvec = op.cols >> 3;
   const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(op.p[1]) +
@@ -1163,13 +1224,14 @@ __device__ __noinline__ bool argmax_item(Ctx& c, const OpDesc& op, uint32_t row,
   float best = -INFINITY;
   uint32_t best_i = 0;
 #pragma unroll 1
-  for (uint32_t v0 = tid_in_group; v0 < nvec; v0 += 512u) {
+  for (uint32_t v0 = tid_in_group; v0 < nvec; v0 += 4u * kSimtThreads) {
     uint4 h[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) h[i] = __ldcg(src + ((v0 + i * 128u < nvec) ? v0 + i * 128u : v0));
+    for (int i = 0; i < 4; ++i)
+      h[i] = __ldcg(src + ((v0 + i * kSimtThreads < nvec) ? v0 + i * kSimtThreads : v0));
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const uint32_t vi = v0 + i * 128u;
+      const uint32_t vi = v0 + i * kSimtThreads;
       if (vi < nvec) {
         const __half2* hp = reinterpret_cast<const __half2*>(&h[i]);
 #pragma unroll
@@ -1188,13 +1250,13 @@ __device__ __noinline__ bool argmax_item(Ctx& c, const OpDesc& op, uint32_t row,
     if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
   }
   if (lane == 0) {
-    c.ctrl->red_val[quarter] = best;
-    c.ctrl->red_idx[quarter] = best_i;
+    c.ctrl->red_val[widx] = best;
+    c.ctrl->red_idx[widx] = best_i;
   }
   if (!group_sync(c, 0x420)) return false;
   if (tid_in_group == 0) {
 #pragma unroll
-    for (int w = 1; w < 4; ++w) {
+    for (int w = 1; w < static_cast<int>(kSimtWarps); ++w) {
       const float ov = c.ctrl->red_val[w];
       const uint32_t oi = c.ctrl->red_idx[w];
       if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
@@ -1209,7 +1271,7 @@ __device__ __noinline__ bool argmax_item(Ctx& c, const OpDesc& op, uint32_t row,
 // maximum on ties (the end-of-text row of a CLIP text tower). One warp per output row.
 __device__ __noinline__ void rowsel_item(const OpDesc& op, uint32_t local, uint32_t warp_in_group,
                                          uint32_t lane) {
-  const uint32_t b = local * 4u + warp_in_group;
+  const uint32_t b = local * kRowsPerItem + warp_in_group;
   if (b >= op.rows) return;
   const int32_t* ids = reinterpret_cast<const int32_t*>(op.p[2]) + static_cast<size_t>(b) * op.seq;
   int32_t best = INT32_MIN;
@@ -1235,7 +1297,7 @@ __device__ __noinline__ void rowsel_item(const OpDesc& op, uint32_t local, uint3
 // of a dual encoder: a few dozen rows each). One warp per row i, lanes over j.
 __device__ __noinline__ void pairdot_item(const OpDesc& op, uint32_t local, uint32_t warp_in_group,
                                           uint32_t lane) {
-  const uint32_t i = local * 4u + warp_in_group;
+  const uint32_t i = local * kRowsPerItem + warp_in_group;
   if (i >= op.M) return;
   const uint4* a = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(op.p[1]) +
                                                   static_cast<size_t>(i) * op.lds);
@@ -1268,7 +1330,7 @@ __device__ __noinline__ void pairdot_item(const OpDesc& op, uint32_t local, uint
 // implicit-GEMM fprop (mononn_engine/core/op_impl/conv_impl.cc:36-106).
 __device__ __noinline__ void patchify_item(const OpDesc& op, uint32_t local, uint32_t warp_in_group,
                                            uint32_t lane) {
-  const uint32_t row = local * 4u + warp_in_group;
+  const uint32_t row = local * kRowsPerItem + warp_in_group;
   if (row >= op.rows) return;
   const uint32_t C = op.heads, Himg = op.seq, Wimg = op.batches, kh = op.head_dim, kw = op.q_col;
   const uint32_t gw = op.k_col, per_img = op.vocab;  // patches per image row / per image
@@ -1283,10 +1345,13 @@ __device__ __noinline__ void patchify_item(const OpDesc& op, uint32_t local, uin
   }
 }
 
-// Softmax + output of one attention tile; thread `row` owns query row `row`.
+// Softmax + output of one attention tile. Query row `row` belongs to two threads (the warps
+// `half` = 0, 1 of the row's TMEM quarter): each takes one 64-key half of every 128-key score
+// chunk (which is also one of the chunk's two P tiles) and 32 of the 64 output columns; the row
+// maximum and the row sum are combined through shared memory.
 __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t local,
                                             uint32_t tmem_base, uint32_t& a_cnt, uint32_t& acc_cnt,
-                                            uint32_t quarter, uint32_t lane,
+                                            uint32_t quarter, uint32_t half, uint32_t lane,
                                             uint32_t tid_in_group) {
   const AttnTile t = attn_tile(op, local);
   const uint32_t row = quarter * 32u + lane;
@@ -1306,17 +1371,16 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
   {
     const bool has_mask = (op.flags & F_MASK_BIAS) != 0u;
     const float* gm = reinterpret_cast<const float*>(op.p[1]) + static_cast<size_t>(t.b) * seq;
-    for (uint32_t i = tid_in_group; i < n_cols; i += 128u) {
+    for (uint32_t i = tid_in_group; i < n_cols; i += kSimtThreads) {
       float m = -1.0e30f;
       if (i < seq) m = has_mask ? __ldcg(gm + i) : 0.f;
       mb[i] = m * 1.4426950408889634f;
     }
-    if (fused) {  // biases of this head's Q, K, V columns
+    if (fused && tid_in_group < 192u) {  // biases of this head's Q, K, V columns
       float* bs = c.ctrl->bias_tile[0];
-      for (uint32_t i = tid_in_group; i < 192u; i += 128u) {
-        const __half* bp = reinterpret_cast<const __half*>(op.p[2u + (i >> 6)]);
-        bs[i] = bp ? __half2float(__ldg(bp + t.h * 64u + (i & 63u))) : 0.f;
-      }
+      const uint32_t i = tid_in_group;
+      const __half* bp = reinterpret_cast<const __half*>(op.p[2u + (i >> 6)]);
+      bs[i] = bp ? __half2float(__ldg(bp + t.h * 64u + (i & 63u))) : 0.f;
     }
     if (!group_sync(c, 0x415)) return false;
   }
@@ -1361,17 +1425,18 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
         }
       }
     };
+    // warp `half` converts columns [32*half, +32) of each of Q, K and V
     uint32_t ra[32], rb[32];
-    tc_ld32_issue(tQ, ra);
-#pragma unroll 1
-    for (uint32_t c0 = 0; c0 < 192u; c0 += 64) {
-      tc_wait_ld();
-      tc_ld32_issue(tQ + c0 + 32u, rb);
-      convert(ra, c0);
-      tc_wait_ld();
-      if (c0 + 64u < 192u) tc_ld32_issue(tQ + c0 + 64u, ra);
-      convert(rb, c0 + 32u);
-    }
+    const uint32_t h32 = half * 32u;
+    tc_ld32_issue(tQ + h32, ra);
+    tc_wait_ld();
+    tc_ld32_issue(tQ + 64u + h32, rb);
+    convert(ra, h32);
+    tc_wait_ld();
+    tc_ld32_issue(tQ + 128u + h32, ra);
+    convert(rb, 64u + h32);
+    tc_wait_ld();
+    convert(ra, 128u + h32);
     fence_proxy_async_smem();
     if (!group_sync(c, 0x41a)) return false;
     if (tid_in_group == 0) {
@@ -1388,11 +1453,11 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
   if (tid_in_group == 0) trace(*c.P, c.stage, TR_MARK0);
   tc_fence_after();
   const uint32_t tS = tmem_base + ((quarter * 32u) << 16);
-  // pass 1: row maximum of scale*s + mask (four independent chains: one warp per scheduler
-  // has nothing else to hide the dependent-issue latency with)
+  const uint32_t h64 = half * 64u;
+  // pass 1: row maximum of scale*s + mask over this warp's key halves (four independent chains)
   float m0 = -3.0e38f, m1 = -3.0e38f, m2 = -3.0e38f, m3 = -3.0e38f;
 #pragma unroll 1
-  for (uint32_t c0 = 0; c0 < n_cols; c0 += 32) {
+  for (uint32_t c0 = h64; c0 < n_cols; c0 += ((c0 & 32u) ? 96u : 32u)) {  // 64 of every 128 columns
     float v[32], mk[32];
     lds32(mb + c0, mk);
     tc_ld32(tS + c0, v);
@@ -1414,21 +1479,24 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
       }
     }
   }
-  const float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+  float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+  c.ctrl->row_max[half][row] = mx;
+  if (!group_sync(c, 0x41b)) return false;
+  mx = fmaxf(mx, c.ctrl->row_max[half ^ 1u][row]);
   if (tid_in_group == 0) trace(*c.P, c.stage, TR_MARK0 + 1);
-  // pass 2: p = exp(z - max), row sum, P tiles in the swizzled K-major operand layout
+  // pass 2: p = exp(z - max), row sum, this warp's P tile of every chunk in the swizzled
+  // K-major operand layout
   float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll 1
   for (uint32_t j = 0; j < nc; ++j) {
-    const uint32_t cP = base + 2u + nc + 3u * j;  // first of the chunk's two P slots
-    const uint32_t slotP0 = cP % kASlots, slotP1 = (cP + 1u) % kASlots;
-    // the P slots must be free before they are overwritten
-    if (!mbar_wait_warp(c, &c.ctrl->a_empty[slotP0], ((cP / kASlots) & 1u) ^ 1u, 0x411)) return false;
-    if (!mbar_wait_warp(c, &c.ctrl->a_empty[slotP1], (((cP + 1u) / kASlots) & 1u) ^ 1u, 0x412))
-      return false;
+    const uint32_t cP = base + 2u + nc + 3u * j + half;  // the chunk's two P slots: one per warp half
+    const uint32_t slotP = cP % kASlots;
+    // the P slot must be free before it is overwritten
+    if (!mbar_wait_warp(c, &c.ctrl->a_empty[slotP], ((cP / kASlots) & 1u) ^ 1u, 0x411)) return false;
+    uint8_t* tile = c.a_ring_ptr + slotP * kSlotBytes;
 #pragma unroll 1
-    for (uint32_t c0 = 0; c0 < 128u; c0 += 32) {
-      const uint32_t cc = j * 128u + c0;
+    for (uint32_t c0 = 0; c0 < 64u; c0 += 32) {
+      const uint32_t cc = j * 128u + h64 + c0;
       float v[32], mk[32];
       lds32(mb + cc, mk);
       tc_ld32(tS + cc, v);
@@ -1454,8 +1522,7 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
           sum1 += v[i + 1];
         }
       }
-      uint8_t* tile = c.a_ring_ptr + ((c0 < 64u) ? slotP0 : slotP1) * kSlotBytes;
-      const uint32_t chunk = (c0 & 63u) >> 3;  // 16-byte chunk index inside the 128-byte row
+      const uint32_t chunk = c0 >> 3;  // 16-byte chunk index inside the 128-byte row
 #pragma unroll
       for (uint32_t q = 0; q < 4; ++q) {
         uint4* d = reinterpret_cast<uint4*>(tile + row * 128u + (((chunk + q) ^ (row & 7u)) << 4));
@@ -1463,48 +1530,47 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
                         pack_h2(v[8 * q + 4], v[8 * q + 5]), pack_h2(v[8 * q + 6], v[8 * q + 7]));
       }
     }
+    if (j + 1u == nc) c.ctrl->row_sum[half][row] = sum0 + sum1;
     fence_proxy_async_smem();
     if (!group_sync(c, 0x414)) return false;
     if (tid_in_group == 0) {
-      mbar_arrive(smem_u32(&c.ctrl->a_full[slotP0]));
-      mbar_arrive(smem_u32(&c.ctrl->a_full[slotP1]));
+      const uint32_t cP0 = cP - half;
+      mbar_arrive(smem_u32(&c.ctrl->a_full[cP0 % kASlots]));
+      mbar_arrive(smem_u32(&c.ctrl->a_full[(cP0 + 1u) % kASlots]));
     }
   }
   if (tid_in_group == 0) trace(*c.P, c.stage, TR_MARK0 + 2);
+  const float inv = 1.0f / (sum0 + sum1 + c.ctrl->row_sum[half ^ 1u][row]);
   tc_fence_before();
   mbar_arrive(smem_u32(&c.ctrl->acc_empty[phS & 1u]));
 
-  // O = sum_j P_j V_j
+  // O = sum_j P_j V_j: this warp stores 32 of the head's 64 columns
   if (!mbar_wait_warp(c, &c.ctrl->acc_full[phO & 1u], (phO >> 1) & 1u, 0x413)) return false;
   if (tid_in_group == 0) trace(*c.P, c.stage, TR_MARK0 + 3);
   tc_fence_after();
-  const uint32_t tO = tmem_base + kAttnOutCol + ((quarter * 32u) << 16);
-  const float inv = 1.0f / (sum0 + sum1);
-  const bool row_ok = qrow < seq;
+  const uint32_t tO = tmem_base + kAttnOutCol + half * 32u + ((quarter * 32u) << 16);
   // A thread owns a row, but a store instruction whose 32 lanes hit 32 different rows costs 32
-  // memory transactions. The warp's 32 x 128-byte block goes through shared memory (swizzled, so
-  // neither side has bank conflicts) and is stored eight lanes to a row: four full lines per
-  // instruction.
-  uint8_t* stg = c.store_stage + quarter * 4096u;
-  (void)row_ok;
-#pragma unroll 1
-  for (uint32_t c0 = 0; c0 < 64u; c0 += 32) {
+  // memory transactions. The warp's 32 x 64-byte block goes through shared memory (swizzled, so
+  // neither side has bank conflicts) and is stored four lanes to a row.
+  uint8_t* stg = c.store_stage + (tid_in_group >> 5) * 2048u;
+  {
     float v[32];
-    tc_ld32(tO + c0, v);
+    tc_ld32(tO, v);
+    const uint32_t sw = (lane >> 1) & 3u;
 #pragma unroll
     for (uint32_t q = 0; q < 4; ++q)
-      *reinterpret_cast<uint4*>(stg + lane * 128u + ((((c0 >> 3) + q) ^ (lane & 7u)) << 4)) =
+      *reinterpret_cast<uint4*>(stg + lane * 64u + ((q ^ sw) << 4)) =
           make_uint4(pack_h2(v[8 * q] * inv, v[8 * q + 1] * inv), pack_h2(v[8 * q + 2] * inv, v[8 * q + 3] * inv),
                      pack_h2(v[8 * q + 4] * inv, v[8 * q + 5] * inv), pack_h2(v[8 * q + 6] * inv, v[8 * q + 7] * inv));
   }
   __syncwarp();
   {
-    const uint32_t q = lane & 7u;
-    __half* obase = reinterpret_cast<__half*>(op.p[0]) + t.h * 64u + q * 8u;
+    const uint32_t q = lane & 3u;
+    __half* obase = reinterpret_cast<__half*>(op.p[0]) + t.h * 64u + half * 32u + q * 8u;
 #pragma unroll
-    for (uint32_t j = 0; j < 8; ++j) {
-      const uint32_t r = 4u * j + (lane >> 3), qr = t.mt * 128u + quarter * 32u + r;
-      const uint4 val = *reinterpret_cast<const uint4*>(stg + r * 128u + ((q ^ (r & 7u)) << 4));
+    for (uint32_t j = 0; j < 4; ++j) {
+      const uint32_t r = 8u * j + (lane >> 2), qr = t.mt * 128u + quarter * 32u + r;
+      const uint4 val = *reinterpret_cast<const uint4*>(stg + r * 64u + ((q ^ ((r >> 1) & 3u)) << 4));
       if (qr < seq)
         *reinterpret_cast<uint4*>(obase + (static_cast<size_t>(t.b) * seq + qr) * op.ldo) = val;
     }
@@ -1516,16 +1582,17 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
 }
 
 // ----------------------------------------------------------------------------
-// Role: epilogue + SIMT stages + grid barrier (warps 4..7)
+// Role: epilogue + SIMT stages + grid barrier (warps 4..11)
 // ----------------------------------------------------------------------------
 __device__ void role_simt(Ctx c, uint32_t tmem_base, uint32_t tid_in_group) {
   const KernelParams& P = *c.P;
-  const uint32_t quarter = tid_in_group >> 5, lane = tid_in_group & 31u;
+  // warp w of the CTA reads TMEM lanes 32*(w%4)..: the SIMT warps 4..11 form two sets of quarters
+  const uint32_t widx = tid_in_group >> 5, quarter = widx & 3u, half = widx >> 2, lane = tid_in_group & 31u;
   uint32_t a_cnt = 0, acc_cnt = 0;
   for (uint32_t s = P.stage_begin; s < P.stage_end; ++s) {
     c.stage = s;
     const StageDesc st = load_stage(P, s);
-    uint4* slot = c.ctrl->desc[3 + quarter];
+    uint4* slot = c.ctrl->desc[3 + widx];
     Item first{nullptr, 0};
     if (blockIdx.x < st.n_items) first = fetch_item<true>(P, st, blockIdx.x, slot, lane);
     // All CTAs must have finished the previous stage before this CTA reads its
@@ -1544,44 +1611,53 @@ __device__ void role_simt(Ctx c, uint32_t tmem_base, uint32_t tid_in_group) {
           if (op.flags & F_BIAS) {
             // stage the tile's bias while the MMAs run
             const uint32_t n0 = ((it.local / op.k_split) % op.n_tiles) * op.n_tile;
-            for (uint32_t i = tid_in_group; i < op.n_tile; i += 128u)
-              bias_s[i] = (n0 + i < op.N)
-                              ? __half2float(__ldg(reinterpret_cast<const __half*>(op.p[1]) + n0 + i))
-                              : 0.f;
+            if (tid_in_group < op.n_tile)
+              bias_s[tid_in_group] =
+                  (n0 + tid_in_group < op.N)
+                      ? __half2float(__ldg(reinterpret_cast<const __half*>(op.p[1]) + n0 + tid_in_group))
+                      : 0.f;
             WAIT_OR_RETURN(group_sync(c, 0x403));
           }
           if (tid_in_group == 0) trace(P, s, TR_MARK0);
           WAIT_OR_RETURN(mbar_wait_warp(c, &c.ctrl->acc_full[buf], (acc_cnt >> 1) & 1u, 0x401));
           if (tid_in_group == 0) trace(P, s, TR_MARK0 + 1);
           tc_fence_after();
-          gemm_epilogue(op, it.local, tmem_base + buf * kAccCols, quarter, lane, bias_s,
-                        c.store_stage + quarter * 4096u);
+          gemm_epilogue(op, it.local, tmem_base + buf * kAccCols, quarter, half, lane, bias_s,
+                        c.store_stage + widx * 2048u);
           tc_fence_before();
           mbar_arrive(smem_u32(&c.ctrl->acc_empty[buf]));
           ++acc_cnt;
           a_cnt += op.kb_per_split;
+          if (op.flag != 0) {
+            // a row op of this stage waits for this item: publish the reductions of all eight
+            // warps (ordered by the group barrier), then count the item
+            WAIT_OR_RETURN(group_sync(c, 0x404));
+            if (tid_in_group == 0) red_release_gpu_add(reinterpret_cast<uint32_t*>(op.flag), 1u);
+          }
           break;
         }
         case OP_ATTENTION:
-          WAIT_OR_RETURN(
-              attention_simt(c, op, it.local, tmem_base, a_cnt, acc_cnt, quarter, lane, tid_in_group));
+          WAIT_OR_RETURN(attention_simt(c, op, it.local, tmem_base, a_cnt, acc_cnt, quarter, half, lane,
+                                        tid_in_group));
           break;
         case OP_LAYERNORM:
         case OP_EMBED:
         case OP_ASSEMBLE:
-          rowwise_item(op, it.local, quarter, lane, P, s);
+          if (op.flag_target != 0) WAIT_OR_RETURN(flag_wait_warp(c, op, 0x430));
+          rowwise_item(op, it.local, widx, lane, P, s);
+          if (op.flag_target != 0) flag_done_warp(op);
           break;
         case OP_PATCHIFY:
-          patchify_item(op, it.local, quarter, lane);
+          patchify_item(op, it.local, widx, lane);
           break;
         case OP_ARGMAX:
-          WAIT_OR_RETURN(argmax_item(c, op, it.local, quarter, lane, tid_in_group));
+          WAIT_OR_RETURN(argmax_item(c, op, it.local, widx, lane, tid_in_group));
           break;
         case OP_ROWSEL:
-          rowsel_item(op, it.local, quarter, lane);
+          rowsel_item(op, it.local, widx, lane);
           break;
         case OP_PAIRDOT:
-          pairdot_item(op, it.local, quarter, lane);
+          pairdot_item(op, it.local, widx, lane);
           break;
         default:
           break;
@@ -1593,7 +1669,7 @@ __device__ void role_simt(Ctx c, uint32_t tmem_base, uint32_t tid_in_group) {
       // Results that later stages read through TMA need a generic->async proxy fence somewhere
       // between the store and the load. It sits on the reader side (the activation producer
       // issues fence.proxy.async after it has acquired the barrier): a second fence here, on
-      // all 128 writers, cost about half a microsecond per stage.
+      // all the writers, cost about half a microsecond per stage.
       WAIT_OR_RETURN(group_sync(c, 0x402));
     }
     if (tid_in_group == 0) {
@@ -1629,9 +1705,9 @@ mononn_megakernel(const __grid_constant__ KernelParams P) {
     }
     for (uint32_t i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&ctrl->acc_full[i]), 1);
-      mbar_init(smem_u32(&ctrl->acc_empty[i]), 128);
+      mbar_init(smem_u32(&ctrl->acc_empty[i]), kSimtThreads);
     }
-    mbar_init(smem_u32(&ctrl->group_bar), 128);
+    mbar_init(smem_u32(&ctrl->group_bar), kSimtThreads);
     ctrl->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -1659,19 +1735,20 @@ mononn_megakernel(const __grid_constant__ KernelParams P) {
   c.a_ring = smem_u32(base);
   c.b_ring = c.a_ring + kASlots * kSlotBytes;
   c.a_ring_ptr = base;
-  c.store_stage = base + kASlots * kSlotBytes + kBSlots * kBSlotBytes + 8192u;
+  c.store_stage = base + kASlots * kSlotBytes + kBSlots * kBSlotBytes + kCtrlBytes;
   c.stage = P.stage_begin;
   c.group_phase = 0;
   c.timeout_ns = static_cast<uint64_t>(P.timeout_us) * 1000ull;
 
-  if (warp == 0) {
-    if (lane == 0) role_weight_producer(c);
-  } else if (warp == 1) {
-    if (lane == 0) role_act_producer(c);
-  } else if (warp == 2) {
-    if (lane == 0) role_mma(c, tmem_base);
-  } else if (warp >= 4) {
-    role_simt(c, tmem_base, threadIdx.x - 128u);
+  // 384 threads share the 64 K registers: 168 each, which every role fits without spilling.
+  if (warp < 4) {
+    if (lane == 0) {
+      if (warp == 0) role_weight_producer(c);
+      else if (warp == 1) role_act_producer(c);
+      else if (warp == 2) role_mma(c, tmem_base);
+    }
+  } else {
+    role_simt(c, tmem_base, threadIdx.x - kRoleThreads);
   }
   __syncwarp();
 

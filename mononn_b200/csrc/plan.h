@@ -36,6 +36,9 @@ struct TuningSpec {
   // 0: fuse the Q/K/V projections into an attention stage that cannot fill the GPU anyway
   // (batches*heads <= CTAs, sequence <= 128); 1: never; 2: whenever the sequence allows it
   uint32_t qkv_fusion = 0;
+  // 0 / 2: a LayerNorm that reads a split-K accumulator joins its GEMMs' stage and waits on an
+  // arrival counter instead of a grid barrier; 1: it keeps a stage of its own
+  uint32_t row_fusion = 0;
 };
 
 // ------------------------------------------------------------------- FGraph
@@ -123,6 +126,11 @@ struct PlanOp {
   OpDesc d{};
   BufRef p[8];
   BufRef q[4];
+  // arrival counter shared by a split-K GEMM (signals) and the row op of the same stage that
+  // reads its accumulator (waits); flag_index < 0: none
+  BufRef flag;
+  int flag_index = -1;
+  bool waits = false;
 };
 
 // How one HLO constant lands in the constant arena.
@@ -185,6 +193,6 @@ std::vector<GemmTileSpec> gemm_tile_candidates(uint32_t M, uint32_t N, uint32_t 
 constexpr uint64_t kScratchBarrierOff = 0, kScratchStatusOff = 256, kScratchStampsOff = 512;
 
 constexpr uint32_t kSmemBytes =
-    kASlots * kSlotBytes + kBSlots * kBSlotBytes + 8192 /*ctrl*/ + kStoreStageBytes + 1024 /*align*/;
+    kASlots * kSlotBytes + kBSlots * kBSlotBytes + kCtrlBytes + kStoreStageBytes + 1024 /*align*/;
 
 }  // namespace mononn

@@ -5,8 +5,11 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
+#include <atomic>
 #include <cstdio>
 #include <cstring>
+#include <thread>
 
 #include "../../include/mononn.h"
 
@@ -26,6 +29,29 @@ const char* get_last_error() { return g_last_error.c_str(); }
       return MONONN_ERR_CUDA;                                                            \
     }                                                                                    \
   } while (0)
+
+// Every entry point runs on the module's device and puts the caller's current device back
+// when it returns (the reference hard-codes device 0 and never switches).
+namespace {
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = false;
+  explicit DeviceGuard(int device) {
+    if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+    ok = (prev == device) || cudaSetDevice(device) == cudaSuccess;
+    if (prev == device) prev = -1;  // nothing to restore
+  }
+  ~DeviceGuard() {
+    if (prev >= 0) cudaSetDevice(prev);
+  }
+};
+}  // namespace
+#define ON_DEVICE()                                             \
+  DeviceGuard guard__(device_);                                  \
+  if (!guard__.ok) {                                            \
+    set_last_error("cannot select the module's CUDA device");   \
+    return MONONN_ERR_CUDA;                                     \
+  }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -53,7 +79,8 @@ int Runtime::init(int device) {
     set_last_error("device ordinal out of range");
     return MONONN_ERR_INVALID_ARGUMENT;
   }
-  CUDA_TRY(cudaSetDevice(device));
+  device_ = device;
+  ON_DEVICE();
   cudaDeviceProp prop;
   CUDA_TRY(cudaGetDeviceProperties(&prop, device));
   if (prop.major != 10) {
@@ -90,7 +117,7 @@ int Runtime::max_coresident_ctas() {
 }
 
 int Runtime::load_plan(const Plan& plan) {
-  CUDA_TRY(cudaSetDevice(device_));
+  ON_DEVICE();
   const int cap = max_coresident_ctas();
   if (static_cast<int>(plan.grid) > cap) {
     set_last_error("grid of " + std::to_string(plan.grid) + " CTAs exceeds the " +
@@ -122,13 +149,28 @@ int Runtime::load_plan(const Plan& plan) {
   bound_ = false;
   bound_args_.clear();
   epoch_ = 0;
-  for (const auto& kv : host_consts_)
-    for (const ConstBinding& b : plan_.consts)
-      if (b.const_name == kv.first) {
-        int rc = upload_constant(b, kv.second);
-        if (rc) return rc;
+  return upload_all_constants();
+}
+
+// PACK_B: [n_tiles][K/64][n_tile][64], zero padded in N (host side of a weight's tiled copy)
+static void pack_weight(const ConstBinding& b, const std::vector<uint8_t>& src, std::vector<uint16_t>* packed) {
+  const uint32_t K = b.K, N = b.N, nt = b.n_tile, kb = K / 64;
+  const uint32_t n_tiles = (N + nt - 1) / nt;
+  packed->assign(static_cast<size_t>(n_tiles) * nt * K, 0);
+  const uint16_t* w = reinterpret_cast<const uint16_t*>(src.data());
+  for (uint32_t t = 0; t < n_tiles; ++t)
+    for (uint32_t k = 0; k < kb; ++k)
+      for (uint32_t r = 0; r < nt; ++r) {
+        const uint32_t n = t * nt + r;
+        if (n >= N) continue;
+        uint16_t* d = &(*packed)[((static_cast<size_t>(t) * kb + k) * nt + r) * 64];
+        if (b.transposed) {
+          std::memcpy(d, w + static_cast<size_t>(n) * K + k * 64, 128);
+        } else {
+          const uint16_t* s = w + static_cast<size_t>(k) * 64 * N + n;
+          for (uint32_t c = 0; c < 64; ++c) d[c] = s[static_cast<size_t>(c) * N];
+        }
       }
-  return MONONN_OK;
 }
 
 int Runtime::upload_constant(const ConstBinding& b, const std::vector<uint8_t>& src) {
@@ -137,25 +179,47 @@ int Runtime::upload_constant(const ConstBinding& b, const std::vector<uint8_t>& 
     CUDA_TRY(cudaMemcpy(dst, src.data(), b.bytes, cudaMemcpyHostToDevice));
     return MONONN_OK;
   }
-  // PACK_B: [n_tiles][K/64][n_tile][64], zero padded in N
-  const uint32_t K = b.K, N = b.N, nt = b.n_tile, kb = K / 64;
-  const uint32_t n_tiles = (N + nt - 1) / nt;
-  std::vector<uint16_t> packed(static_cast<size_t>(n_tiles) * nt * K, 0);
-  const uint16_t* w = reinterpret_cast<const uint16_t*>(src.data());
-  for (uint32_t t = 0; t < n_tiles; ++t)
-    for (uint32_t k = 0; k < kb; ++k)
-      for (uint32_t r = 0; r < nt; ++r) {
-        const uint32_t n = t * nt + r;
-        if (n >= N) continue;
-        uint16_t* d = &packed[((static_cast<size_t>(t) * kb + k) * nt + r) * 64];
-        if (b.transposed) {
-          std::memcpy(d, w + static_cast<size_t>(n) * K + k * 64, 128);
-        } else {
-          const uint16_t* s = w + static_cast<size_t>(k) * 64 * N + n;
-          for (uint32_t c = 0; c < 64; ++c) d[c] = s[static_cast<size_t>(c) * N];
-        }
-      }
+  std::vector<uint16_t> packed;
+  pack_weight(b, src, &packed);
   CUDA_TRY(cudaMemcpy(dst, packed.data(), packed.size() * 2, cudaMemcpyHostToDevice));
+  return MONONN_OK;
+}
+
+// Re-packs every constant already given for the current plan. The tiled copies are made by a
+// pool of host threads (the reference's CompilationThreadpool compiles candidates in parallel,
+// mononn_engine/codegen/compilation_threadpool.cc:41-125; here a candidate costs a re-pack of
+// the weights whose tile changed, and that is what the pool shares out); uploads stay on the
+// calling thread.
+int Runtime::upload_all_constants() {
+  std::vector<const ConstBinding*> jobs;
+  for (const ConstBinding& b : plan_.consts)
+    if (host_consts_.count(b.const_name)) jobs.push_back(&b);
+  unsigned workers = pack_threads > 0 ? static_cast<unsigned>(pack_threads) : std::thread::hardware_concurrency();
+  workers = std::max(1u, std::min<unsigned>(workers, 64u));
+  const size_t kBatch = 32;  // bounds the host memory held by packed copies
+  for (size_t base = 0; base < jobs.size(); base += kBatch) {
+    const size_t end = std::min(jobs.size(), base + kBatch);
+    std::vector<std::vector<uint16_t>> packed(end - base);
+    std::atomic<size_t> next{base};
+    auto work = [&]() {
+      for (size_t i = next.fetch_add(1); i < end; i = next.fetch_add(1))
+        if (jobs[i]->kind == ConstBinding::PACK_B)
+          pack_weight(*jobs[i], host_consts_.at(jobs[i]->const_name), &packed[i - base]);
+    };
+    std::vector<std::thread> pool;
+    for (unsigned t = 1; t < workers && t < end - base; ++t) pool.emplace_back(work);
+    work();
+    for (std::thread& t : pool) t.join();
+    for (size_t i = base; i < end; ++i) {
+      const ConstBinding& b = *jobs[i];
+      uint8_t* dst = static_cast<uint8_t*>(d_const_) + b.offset;
+      if (b.kind == ConstBinding::RAW) {
+        CUDA_TRY(cudaMemcpy(dst, host_consts_.at(b.const_name).data(), b.bytes, cudaMemcpyHostToDevice));
+      } else {
+        CUDA_TRY(cudaMemcpy(dst, packed[i - base].data(), packed[i - base].size() * 2, cudaMemcpyHostToDevice));
+      }
+    }
+  }
   return MONONN_OK;
 }
 
@@ -169,7 +233,7 @@ static std::string canon(const std::string& n) {
 }
 
 int Runtime::set_constant(const std::string& given, const void* host, size_t bytes) {
-  CUDA_TRY(cudaSetDevice(device_));
+  ON_DEVICE();
   std::string name = given;
   for (const ConstBinding& b : plan_.consts)
     if (b.const_name != given && canon(b.const_name) == canon(given)) name = b.const_name;
@@ -233,6 +297,7 @@ int Runtime::bind(void* const* args, int n, void* stream) {
     ops[i] = plan_.ops[i].d;
     for (int k = 0; k < 8; ++k) ops[i].p[k] = resolve(plan_.ops[i].p[k]);
     for (int k = 0; k < 4; ++k) ops[i].q[k] = resolve(plan_.ops[i].q[k]);
+    ops[i].flag = resolve(plan_.ops[i].flag);
   }
   EncodeTiledFn encode = reinterpret_cast<EncodeTiledFn>(encode_fn_);
   for (size_t i = 0; i < plan_.tmaps.size(); ++i) {
@@ -268,7 +333,7 @@ int Runtime::bind(void* const* args, int n, void* stream) {
 
 int Runtime::launch(void* const* args, int n, void* stream, uint32_t stage_begin,
                     uint32_t stage_end, bool stamps) {
-  CUDA_TRY(cudaSetDevice(device_));
+  ON_DEVICE();
   if (stage_end > plan_.stages.size() || stage_begin >= stage_end) {
     set_last_error("stage range out of bounds");
     return MONONN_ERR_INVALID_ARGUMENT;
@@ -308,7 +373,7 @@ int Runtime::launch(void* const* args, int n, void* stream, uint32_t stage_begin
 
 int Runtime::infer_host(const void* const* host_in, int n_in, void* const* host_out, int n_out,
                         void* const* args, int n, void* stream) {
-  CUDA_TRY(cudaSetDevice(device_));
+  ON_DEVICE();
   if (n != static_cast<int>(plan_.args.size())) {
     set_last_error("argument count does not match the module");
     return MONONN_ERR_INVALID_ARGUMENT;
@@ -347,7 +412,7 @@ int Runtime::infer_host(const void* const* host_in, int n_in, void* const* host_
 }
 
 int Runtime::check_status(int* stage, int* cta) {
-  CUDA_TRY(cudaSetDevice(device_));
+  ON_DEVICE();
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) {
     set_last_error(std::string("kernel failed: ") + cudaGetErrorString(e));
@@ -371,6 +436,7 @@ int Runtime::check_status(int* stage, int* cta) {
 }
 
 int Runtime::read_stamps(std::vector<double>* us) {
+  ON_DEVICE();
   std::vector<uint64_t> t(n_stamp_stages_ + 1);
   CUDA_TRY(cudaMemcpy(t.data(), static_cast<uint8_t*>(d_scratch_) + kScratchStampsOff,
                       t.size() * 8, cudaMemcpyDeviceToHost));
@@ -381,7 +447,7 @@ int Runtime::read_stamps(std::vector<double>* us) {
 }
 
 int Runtime::trace_launch(void* const* args, int n, void* stream, std::vector<double>* out) {
-  CUDA_TRY(cudaSetDevice(device_));
+  ON_DEVICE();
   const size_t ns = plan_.stages.size();
   const size_t words = static_cast<size_t>(plan_.grid) * ns * kTraceEvents;
   if (!d_trace_) CUDA_TRY(cudaMalloc(&d_trace_, words * 8));
@@ -406,6 +472,7 @@ int Runtime::trace_launch(void* const* args, int n, void* stream, std::vector<do
 
 int Runtime::time_stages(void* const* args, int n, void* stream, uint32_t begin, uint32_t end,
                          int warmup, int iters, double* us) {
+  ON_DEVICE();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   for (int i = 0; i < warmup; ++i) {
     int rc = launch(args, n, stream, begin, end, false);

@@ -66,11 +66,13 @@ class Runtime {
   void skew_epoch(uint32_t n) { epoch_ += n; }
 
   unsigned timeout_us = 2000000;
+  int pack_threads = 0;  // host threads that re-pack weights when a plan is (re)loaded; 0 = all cores
   const std::map<std::string, std::vector<uint8_t>>& host_constants() const { return host_consts_; }
 
  private:
   int bind(void* const* args, int n, void* stream);
   int upload_constant(const ConstBinding& b, const std::vector<uint8_t>& src);
+  int upload_all_constants();
   void release();
 
   int device_ = 0;

@@ -196,20 +196,20 @@ int validate_plan(const Plan& P, std::string* err) {
       case OP_EMBED:
       case OP_ASSEMBLE:
         if (d.cols == 0 || d.cols % 4 || d.cols > 2048) return bad(n + "row length");
-        if (d.n_items != (d.rows + 3) / 4) return bad(n + "item count");
+        if (d.n_items != (d.rows + kRowsPerItem - 1) / kRowsPerItem) return bad(n + "item count");
         if (op.p[0].space == SPACE_NONE && op.q[2].space == SPACE_NONE) return bad(n + "no output buffer");
         if (op.p[6].space == SPACE_NONE && d.kind != OP_LAYERNORM) return bad(n + "no scale pointer");
         if (d.kind == OP_ASSEMBLE && (d.seq == 0 || d.k_col >= d.seq)) return bad(n + "token geometry");
         break;
       case OP_ROWSEL:
         if (d.cols == 0 || d.cols % 4 || d.lds % 4 || d.ldo % 4 || d.seq == 0) return bad(n + "row geometry");
-        if (d.n_items != (d.rows + 3) / 4) return bad(n + "item count");
+        if (d.n_items != (d.rows + kRowsPerItem - 1) / kRowsPerItem) return bad(n + "item count");
         if (op.p[0].space == SPACE_NONE || op.p[1].space == SPACE_NONE || op.p[2].space == SPACE_NONE)
           return bad(n + "buffers");
         break;
       case OP_PAIRDOT:
         if (d.K == 0 || d.K % 8 || d.lds % 8 || d.ldr % 8) return bad(n + "K and row pitches must be multiples of 8");
-        if (d.n_items != (d.M + 3) / 4) return bad(n + "item count");
+        if (d.n_items != (d.M + kRowsPerItem - 1) / kRowsPerItem) return bad(n + "item count");
         if (op.p[0].space == SPACE_NONE || op.p[1].space == SPACE_NONE || op.p[2].space == SPACE_NONE)
           return bad(n + "buffers");
         break;
@@ -221,11 +221,33 @@ int validate_plan(const Plan& P, std::string* err) {
       case OP_PATCHIFY:
         if (d.cols != d.heads * d.head_dim * d.q_col || d.vocab == 0 || d.k_col == 0)
           return bad(n + "patch geometry");
-        if (d.n_items != (d.rows + 3) / 4) return bad(n + "item count");
+        if (d.n_items != (d.rows + kRowsPerItem - 1) / kRowsPerItem) return bad(n + "item count");
         if (op.p[0].space == SPACE_NONE || op.p[1].space == SPACE_NONE) return bad(n + "buffers");
         break;
       default:
         return bad(n + "unknown operator kind");
+    }
+  }
+  for (const StageDesc& sd : P.stages) {
+    // a row op that waits on an arrival counter needs its signalling GEMMs earlier in the same
+    // stage's item order, their item counts adding up to its target
+    bool seen_wait = false;
+    for (uint32_t a = sd.op_begin; a < sd.op_begin + sd.op_count; ++a) {
+      const PlanOp& op = P.ops[a];
+      if (op.flag_index < 0) {
+        if (op.d.flag_target != 0) return bad(op.name + ": wait target without a counter");
+        continue;
+      }
+      if (op.flag.space != SPACE_SCRATCH) return bad(op.name + ": arrival counter outside the scratch");
+      if (!op.waits) {
+        if (op.d.kind != OP_GEMM || seen_wait) return bad(op.name + ": signalling operator after a waiting one");
+        continue;
+      }
+      seen_wait = true;
+      uint32_t target = 0;
+      for (uint32_t b = sd.op_begin; b < a; ++b)
+        if (!P.ops[b].waits && P.ops[b].flag_index == op.flag_index) target += P.ops[b].d.n_items;
+      if (target == 0 || target != op.d.flag_target) return bad(op.name + ": wait target does not match its GEMMs");
     }
   }
   for (const TmapSpec& t : P.tmaps) {
@@ -362,12 +384,37 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
   }
 
   // ---- stage = dependency depth
+  // A LayerNorm over an f32 accumulator whose last writers are split-K GEMMs normally sits one
+  // barrier after them. When nothing else holds it back it joins their stage instead: every GEMM
+  // item adds 1 to an arrival counter after its reductions and the row items, dealt to the CTAs
+  // after the GEMM items, wait for the full count (a wait for CTAs that never wait themselves,
+  // all co-resident: it cannot deadlock). One grid barrier per LayerNorm disappears. The
+  // reference splits the same pair into a GEMM node and a reduce cluster with a barrier between
+  // (mononn_engine/optimization/global_synchronization_elimination_pass.cc:98-147).
   std::vector<int> producer(n_t, -1), last_reader(n_t, -1);
+  std::vector<std::vector<int>> writers(n_t);
+  std::vector<int> flag_of(ops.size(), -1);   // arrival counter an op signals (GEMM) or waits on (row op)
+  std::vector<char> waits(ops.size(), 0);
+  int n_flags = 0;
   int n_stages = 0;
   for (size_t i = 0; i < ops.size(); ++i) {
+    int fuse_src = -1, fuse_stage = -1;
+    if (ops[i].kind == OP_LAYERNORM && spec_in.row_fusion != 1 && ops[i].src >= 0 &&
+        g.tensors[ops[i].src].kind == TKind::AccF32 && !writers[ops[i].src].empty()) {
+      const int T = ops[i].src;
+      int d = -1;
+      for (int w : writers[T]) d = std::max(d, ops[w].stage);
+      bool ok = true;
+      for (int w : writers[T])
+        if (ops[w].stage == d && (ops[w].kind != OP_GEMM || flag_of[w] >= 0)) ok = false;
+      if (ok) {
+        fuse_src = T;
+        fuse_stage = d;
+      }
+    }
     int depth = 0;
     for (int t : inputs_of(ops[i]))
-      if (producer[t] >= 0) depth = std::max(depth, ops[producer[t]].stage + 1);
+      if (producer[t] >= 0 && t != fuse_src) depth = std::max(depth, ops[producer[t]].stage + 1);
     // an op that adds into a live tensor (the f32 residual stream of pre-LN models) also
     // runs after every earlier reader of the old value
     for (int t : outputs_of(ops[i]))
@@ -375,10 +422,25 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
     // an op that accumulates into a tensor someone pre-loaded runs after that producer
     for (int t : outputs_of(ops[i]))
       if (producer[t] >= 0) depth = std::max(depth, ops[producer[t]].stage + 1);
+    if (fuse_src >= 0) {
+      if (depth <= fuse_stage) {
+        depth = fuse_stage;
+        flag_of[i] = n_flags;
+        waits[i] = 1;
+        for (int w : writers[fuse_src])
+          if (ops[w].stage == fuse_stage) flag_of[w] = n_flags;
+        ++n_flags;
+      } else {
+        depth = std::max(depth, fuse_stage + 1);
+      }
+    }
     ops[i].stage = depth;
     n_stages = std::max(n_stages, depth + 1);
     for (int t : inputs_of(ops[i])) last_reader[t] = std::max(last_reader[t], depth);
-    for (int t : outputs_of(ops[i])) producer[t] = static_cast<int>(i);
+    for (int t : outputs_of(ops[i])) {
+      producer[t] = static_cast<int>(i);
+      writers[t].push_back(static_cast<int>(i));
+    }
   }
 
   // ---- liveness
@@ -400,6 +462,9 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
 
   // ---- scratch layout: barrier counter, status, stamps, then f32 tensors
   uint64_t scratch = kScratchStampsOff + align_up(8ull * (n_stages + 2), 256);
+  // arrival counters of the row ops that share a stage with their GEMMs: {arrived, finished} each
+  const uint64_t flags_off = scratch;
+  scratch += align_up(8ull * n_flags, 256);
 
   // f32 tensors come in two kinds that must not inherit each other's memory. A GEMM
   // accumulator whose first write is a reduction needs zeros when its life starts and is
@@ -559,7 +624,12 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
 
   // ---- emit ops stage by stage
   std::vector<std::vector<size_t>> by_stage(n_stages);
-  for (size_t i = 0; i < ops.size(); ++i) by_stage[ops[i].stage].push_back(i);
+  for (size_t i = 0; i < ops.size(); ++i)
+    if (!waits[i]) by_stage[ops[i].stage].push_back(i);
+  // row ops that wait for GEMMs of their own stage come last, so that a CTA meets its GEMM
+  // items before any item that waits
+  for (size_t i = 0; i < ops.size(); ++i)
+    if (waits[i]) by_stage[ops[i].stage].push_back(i);
 
   for (int s = 0; s < n_stages; ++s) {
     StageDesc sd{};
@@ -705,7 +775,7 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
             if (err) *err = "layernorm " + o.name + ": row length must be <= 2048 and a multiple of 4";
             return MONONN_ERR_UNSUPPORTED;
           }
-          d.n_items = (o.rows + 3) / 4;
+          d.n_items = (o.rows + kRowsPerItem - 1) / kRowsPerItem;
           po.p[0] = where[o.out];
           d.ldo = g.tensors[o.out].ld;
           po.p[1] = where[o.src];
@@ -747,7 +817,7 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
           d.q_col = o.q_col;
           d.k_col = o.k_col;
           d.vocab = o.vocab;
-          d.n_items = (o.rows + 3) / 4;
+          d.n_items = (o.rows + kRowsPerItem - 1) / kRowsPerItem;
           po.p[0] = where[o.out];
           d.ldo = g.tensors[o.out].ld;
           po.p[1] = where[o.src];
@@ -759,7 +829,7 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
           d.seq = o.seq;
           d.lds = g.tensors[o.src].ld;
           d.ldo = g.tensors[o.out].ld;
-          d.n_items = (o.rows + 3) / 4;
+          d.n_items = (o.rows + kRowsPerItem - 1) / kRowsPerItem;
           po.p[0] = where[o.out];
           po.p[1] = where[o.src];
           po.p[2] = where[o.ids];
@@ -772,7 +842,7 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
           d.lds = g.tensors[o.a].ld;
           d.ldr = g.tensors[o.src].ld;
           d.ldo = g.tensors[o.out].ld;
-          d.n_items = (o.M + 3) / 4;
+          d.n_items = (o.M + kRowsPerItem - 1) / kRowsPerItem;
           po.p[0] = where[o.out];
           po.p[1] = where[o.a];
           po.p[2] = where[o.src];
@@ -797,7 +867,7 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
             if (err) *err = "assemble " + o.name + ": row length must be <= 2048 and a multiple of 4";
             return MONONN_ERR_UNSUPPORTED;
           }
-          d.n_items = (o.rows + 3) / 4;
+          d.n_items = (o.rows + kRowsPerItem - 1) / kRowsPerItem;
           d.flags |= F_NO_NORM;
           if (o.out >= 0) {
             po.p[0] = where[o.out];
@@ -825,7 +895,7 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
             if (err) *err = "embed " + o.name + ": row length must be <= 2048 and a multiple of 4";
             return MONONN_ERR_UNSUPPORTED;
           }
-          d.n_items = (o.rows + 3) / 4;
+          d.n_items = (o.rows + kRowsPerItem - 1) / kRowsPerItem;
           d.q_col = o.q_col;  // offset of the position index
           if (o.out >= 0) {
             po.p[0] = where[o.out];
@@ -862,12 +932,24 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
           if (err) *err = "operator " + o.name + ": unknown kind";
           return MONONN_ERR_UNSUPPORTED;
       }
+      if (flag_of[oi] >= 0) {
+        po.flag = BufRef{SPACE_SCRATCH, 0, flags_off + 8ull * flag_of[oi]};
+        po.flag_index = flag_of[oi];
+        po.waits = waits[oi] != 0;
+      }
       sd.n_items += d.n_items;
       if (!sname.empty()) sname += "+";
       sname += o.name;
       P.ops.push_back(po);
     }
     sd.op_count = static_cast<uint32_t>(P.ops.size()) - sd.op_begin;
+    for (size_t a = sd.op_begin; a < P.ops.size(); ++a) {
+      if (!P.ops[a].waits) continue;
+      uint32_t target = 0;
+      for (size_t b = sd.op_begin; b < P.ops.size(); ++b)
+        if (!P.ops[b].waits && P.ops[b].flag_index == P.ops[a].flag_index) target += P.ops[b].d.n_items;
+      P.ops[a].d.flag_target = target;
+    }
     if (sd.op_count > kMaxStageOps) {
       if (err) *err = "more than " + std::to_string(kMaxStageOps) + " independent operators at one depth";
       return MONONN_ERR_UNSUPPORTED;

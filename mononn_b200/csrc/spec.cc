@@ -75,6 +75,7 @@ std::string spec_to_json(const Plan& plan, uint32_t sm_count) {
   // "auto": Q/K/V projections are computed inside the attention items when the attention stage
   // cannot fill the GPU (batches*heads <= CTAs, sequence <= 128); "off"; "on": whenever legal
   root.set("qkv_fusion", Json::string(plan.spec.qkv_fusion == 1 ? "off" : plan.spec.qkv_fusion == 2 ? "on" : "auto"));
+  root.set("row_fusion", Json::string(plan.spec.row_fusion == 1 ? "off" : "on"));
   root.set("cluster_elewise_spec", Json::object());
   root.set("cluster_reduce_spec", Json::object());
   Json gemms = Json::object();
@@ -180,6 +181,11 @@ std::string plan_to_json(const Plan& plan) {
       o.set("n_items", Json::number(op.d.n_items));
       o.set("flags", Json::number(op.d.flags));
       o.set("act", Json::number(op.d.act));
+      if (op.flag_index >= 0) {
+        o.set("flag", Json::number(op.flag_index));
+        o.set("waits", Json::number(op.waits ? 1 : 0));
+        o.set("flag_target", Json::number(op.d.flag_target));
+      }
       if (op.d.kind == OP_GEMM) {
         o.set("M", Json::number(op.d.M));
         o.set("N", Json::number(op.d.N));
@@ -272,6 +278,8 @@ int spec_from_json(const std::string& text, TuningSpec* spec, std::string* err) 
       if (const Json* g = rt->find("grid_dim")) spec->grid = static_cast<uint32_t>(g->get_number("x", 0));
       if (const Json* b = rt->find("block_dim")) spec->block = static_cast<uint32_t>(b->get_number("x", kThreads));
     }
+  if (const Json* rf = root.find("row_fusion"))
+    if (rf->type == Json::String) spec->row_fusion = rf->str == "off" ? 1u : 0u;
   if (const Json* qf = root.find("qkv_fusion"))
     if (qf->type == Json::String) spec->qkv_fusion = qf->str == "off" ? 1u : qf->str == "on" ? 2u : 0u;
   if (const Json* gl = root.find("gemm_spec_list")) {

@@ -96,9 +96,16 @@ struct alignas(16) OpDesc {
   uint32_t lds;             // leading dim of row-wise source
   uint32_t vocab;           // embed: word-table rows (ids are not clamped, as in the reference)
   uint32_t pad0;
+  uint32_t flag_target;     // row op that follows its producer GEMM inside one stage: arrivals to wait for
+  uint32_t pad1;
   uint64_t p[8];
   uint64_t q[4];  // LAYERNORM / EMBED: q[2] second output (f32, + q[3] bias f16), see plan
+  // Arrival counter shared by a split-K GEMM and the row op that consumes its accumulator in the
+  // same stage: every GEMM item adds 1 after its reductions, the row items wait for flag_target.
+  uint64_t flag;
+  uint64_t pad2;
 };
+static_assert(sizeof(OpDesc) == 256, "operator descriptor is copied as sixteen 16-byte words");
 
 constexpr uint32_t kMaxStageOps = 8;
 
@@ -137,8 +144,13 @@ constexpr uint32_t kBSlotBytes = 32768;  // weight ring slot: up to 256 rows of 
 #endif
 constexpr uint32_t kASlots = MONONN_A_SLOTS;
 constexpr uint32_t kBSlots = MONONN_B_SLOTS;
-constexpr uint32_t kStoreStageBytes = 16384;  // per epilogue warp 32 rows x 128 B, to store whole lines
-constexpr uint32_t kThreads = 256;
+constexpr uint32_t kStoreStageBytes = 16384;  // per epilogue warp 32 rows x 64 B, to store rows in 64-byte runs
+constexpr uint32_t kCtrlBytes = 12288;        // shared-memory reserve of the control block
+constexpr uint32_t kRoleThreads = 128;        // warps 0..3: producers and the MMA issuer (one lane each)
+constexpr uint32_t kSimtThreads = 256;        // warps 4..11: epilogue / row-wise work
+constexpr uint32_t kSimtWarps = kSimtThreads / 32;
+constexpr uint32_t kThreads = kRoleThreads + kSimtThreads;
+constexpr uint32_t kRowsPerItem = kSimtWarps;  // row-wise operators: one row per SIMT warp per work item
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTraceEvents = 16;  // per (CTA, stage) slots of the optional event trace
 constexpr uint32_t kAccCols = 256;  // two accumulator buffers of 256 columns

@@ -1,13 +1,23 @@
 // On-device schedule search.
 //
 // Follows the shape of MonoNNModuleTuner::tune
-// (mononn_engine/module/mononn_module_tuner.cc:620-991): GEMM candidates are de-duplicated
-// by problem (the reference hashes the GEMM problem, :386-408, and copies the best
-// CutlassConfig to every node with that hash, :820-975), each candidate is timed on the
-// device, and the winners are merged into one spec that is timed end to end against the
-// heuristic default. Because a candidate here is a table, not a CUDA source to be compiled
-// by an nvcc subprocess, one candidate costs a re-pack of the affected weights plus a few
-// launches.
+// (mononn_engine/module/mononn_module_tuner.cc:620-991): candidates are enumerated per
+// dimension of the schedule space (TuningSpaceGenerator,
+// mononn_engine/tuning/tuning_space_generator.cc:52-309), GEMM candidates are de-duplicated by
+// problem (the reference hashes the GEMM problem, :386-408, and copies the best CutlassConfig to
+// every node with that hash, :820-975) and timed in isolation on the stage that holds one node
+// of the class (the reference isolates a node with its codegen allow-list, :647-722), and the
+// winners are merged into one spec that is timed end to end against the heuristic default.
+// Because a candidate here is a table, not a CUDA source to be compiled by an nvcc
+// subprocess, one candidate costs a re-pack of the affected weights plus a few launches.
+//
+// Dimensions searched, by tuning_level:
+//   0  none: the heuristic spec is timed and reported
+//   1  stage structure (Q/K/V projections inside the attention items or as a stage of their own;
+//      LayerNorm in the stage of its split-K GEMMs or behind a grid barrier of its own), then
+//      the tile width and K split of every GEMM problem class
+//   2  + the number of CTAs of the cooperative launch (the reference's (grid, block) contexts,
+//      mononn_engine/tuning/tuning_space_generator.cc:65-101)
 #include <algorithm>
 #include <fstream>
 #include <sstream>
@@ -74,6 +84,14 @@ struct Journal {
     out.flush();
   }
 };
+
+// Stage of the current plan that holds operator `node`, or -1.
+int stage_of(const Plan& p, const std::string& node) {
+  for (size_t s = 0; s < p.stages.size(); ++s)
+    for (uint32_t i = 0; i < p.stages[s].op_count; ++i)
+      if (p.ops[p.stages[s].op_begin + i].name == node) return static_cast<int>(s);
+  return -1;
+}
 }  // namespace
 
 int tune_module(mononn_module* m, void* const* args, int n, void* stream) {
@@ -81,13 +99,24 @@ int tune_module(mononn_module* m, void* const* args, int n, void* stream) {
   const int warm = 3, iters = 20;
   Journal journal;
   journal.open(m->dump_dir, m->graph.module_name);
-  // one timed spec: replayed from the journal when possible, else lowered and measured
-  auto measure = [&](const std::string& label, const TuningSpec& spec, double* us) -> int {
+  // One timed spec: replayed from the journal when possible, else lowered and measured. With a
+  // node name only the stage that holds the node is launched (isolation); otherwise all stages.
+  auto measure = [&](const std::string& label, const TuningSpec& spec, const std::string& node,
+                     double* us) -> int {
     if (journal.replay(label, us)) return MONONN_OK;
     int r = m->lower(spec);
     if (r) return r;
-    const uint32_t ns = static_cast<uint32_t>(m->rt.plan().stages.size());
-    r = m->rt.time_stages(args, n, stream, 0, ns, warm, iters, us);
+    uint32_t begin = 0, end = static_cast<uint32_t>(m->rt.plan().stages.size());
+    if (!node.empty()) {
+      const int s = stage_of(m->rt.plan(), node);
+      if (s < 0) {
+        set_last_error("tuner: operator " + node + " is not in the lowered plan");
+        return MONONN_ERR_INVALID_ARGUMENT;
+      }
+      begin = static_cast<uint32_t>(s);
+      end = begin + 1;
+    }
+    r = m->rt.time_stages(args, n, stream, begin, end, warm, iters, us);
     if (r) return r;
     journal.record(label, *us);
     return MONONN_OK;
@@ -98,14 +127,48 @@ int tune_module(mononn_module* m, void* const* args, int n, void* stream) {
   int rc = m->lower(best);
   if (rc) return rc;
   double best_us = 0;
-  rc = measure("default", best, &best_us);
+  rc = measure("default", best, "", &best_us);
   if (rc) return rc;
   log << "default spec: " << best_us << " us\n";
   const double default_us = best_us;
   const TuningSpec default_spec = best;
 
   if (m->tuning_level >= 1) {
-    // group GEMM nodes by problem
+    // ---- stage structure: whole-graph choices, timed end to end
+    struct Structural {
+      const char* name;
+      uint32_t TuningSpec::*field;
+      uint32_t value;
+    };
+    const Structural choices[] = {
+        {"qkv_fusion off", &TuningSpec::qkv_fusion, 1u},
+        {"qkv_fusion on", &TuningSpec::qkv_fusion, 2u},
+        {"row_fusion off", &TuningSpec::row_fusion, 1u},
+    };
+    for (const Structural& c : choices) {
+      if (best.*(c.field) == c.value) continue;
+      TuningSpec trial = best;
+      trial.*(c.field) = c.value;
+      trial.gemm.clear();  // the GEMM nodes and their CTA budgets change with the structure
+      double us = 0;
+      rc = measure(c.name, trial, "", &us);
+      if (rc == MONONN_ERR_UNSUPPORTED || rc == MONONN_ERR_INVALID_ARGUMENT) {
+        log << c.name << ": not applicable to this graph\n";
+        continue;
+      }
+      if (rc) return rc;
+      log << c.name << ": " << us << " us\n";
+      if (us < best_us) {
+        best_us = us;
+        rc = m->lower(trial);
+        if (rc) return rc;
+        best = m->rt.plan().spec;  // with the heuristic tiles of the new structure filled in
+      }
+    }
+    rc = m->lower(best);
+    if (rc) return rc;
+
+    // ---- GEMM tiles: group the nodes by problem, time candidates on one node's stage alone
     std::map<ProblemKey, std::vector<std::string>> classes;
     std::map<ProblemKey, std::pair<bool, uint32_t>> meta;  // can_split, budget
     {
@@ -126,25 +189,56 @@ int tune_module(mononn_module* m, void* const* args, int n, void* stream) {
     }
     for (const auto& kv : classes) {
       const ProblemKey& k = kv.first;
+      // a node from the middle of the graph: its inputs are what a steady-state layer sees
+      const std::string probe = kv.second[kv.second.size() / 2];
       const auto cands = gemm_tile_candidates(k.M, k.N, k.K, meta[k].first, meta[k].second);
-      GemmTileSpec cur = best.gemm[kv.second.front()];
+      GemmTileSpec cur = best.gemm[probe];
+      std::ostringstream cls;
+      cls << "M" << k.M << " N" << k.N << " K" << k.K << " f" << k.flags << " a" << k.act << " o" << k.out_mode;
+      double cur_us = 0;
+      rc = measure(cls.str() + " stage of " + probe + " as is", best, probe, &cur_us);
+      if (rc) return rc;
+      log << cls.str() << " n_tile " << cur.n_tile << " k_split " << cur.k_split << " (current): " << cur_us
+          << " us for its stage\n";
       for (const GemmTileSpec& c : cands) {
         if (c.n_tile == cur.n_tile && c.k_split == cur.k_split) continue;
         TuningSpec trial = best;
         for (const std::string& node : kv.second) trial.gemm[node] = c;
         double us = 0;
         std::ostringstream label;
-        label << "M" << k.M << " N" << k.N << " K" << k.K << " f" << k.flags << " a" << k.act << " o" << k.out_mode
-              << " n_tile " << c.n_tile << " k_split " << c.k_split;
-        rc = measure(label.str(), trial, &us);
+        label << cls.str() << " n_tile " << c.n_tile << " k_split " << c.k_split;
+        rc = measure(label.str(), trial, probe, &us);
         if (rc) return rc;
-        log << "M" << k.M << " N" << k.N << " K" << k.K << " n_tile " << c.n_tile << " k_split "
-            << c.k_split << ": " << us << " us\n";
-        if (us < best_us) {
-          best_us = us;
+        log << label.str() << ": " << us << " us for its stage\n";
+        if (us < cur_us) {
+          cur_us = us;
           best = trial;
           cur = c;
         }
+      }
+    }
+  }
+  if (m->tuning_level >= 2) {
+    // ---- CTAs of the launch: fewer CTAs make the grid barrier cheaper and the tiles wider
+    const uint32_t sms = m->rt.sm_count();
+    rc = measure("merged tiles", best, "", &best_us);
+    if (rc) return rc;
+    for (uint32_t grid : {sms - sms / 8, sms - sms / 4, sms / 2}) {
+      if (grid == 0 || grid == best.grid) continue;
+      TuningSpec trial = best;
+      trial.grid = grid;
+      trial.gemm.clear();  // tiles are chosen for the CTA budget
+      double us = 0;
+      std::ostringstream label;
+      label << "grid " << grid;
+      rc = measure(label.str(), trial, "", &us);
+      if (rc) return rc;
+      log << label.str() << ": " << us << " us\n";
+      if (us < best_us) {
+        best_us = us;
+        rc = m->lower(trial);
+        if (rc) return rc;
+        best = m->rt.plan().spec;
       }
     }
   }

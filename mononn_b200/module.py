@@ -240,6 +240,16 @@ def describe(kind: str, text: str, spec: dict | None = None, sm_count: int = 148
         lib().mononn_free_string(out)
 
 
+def cluster_dir(module_name: str) -> str:
+    """Directory name of a module inside a spec / dump directory: "cluster_<digits>" taken from the
+    module name (mononn_engine/helpers/string_helpers.cc:34-46), else the sanitised name."""
+    import re
+    m = re.match(r"cluster_(\d+)", module_name)
+    if m:
+        return f"cluster_{m.group(1)}"
+    return re.sub(r"[^0-9A-Za-z]", "_", module_name) or "cluster_0"
+
+
 def attention_noalloc(q_ptr: int, k_ptr: int, vt_ptr: int, mask_ptr: int | None, out_ptr: int, batches: int,
                       heads: int, seq: int, ld_qk: int, ld_vt: int, ld_out: int, scale: float,
                       mask_scale: float = -10000.0, causal: bool = False, stream=None) -> None:

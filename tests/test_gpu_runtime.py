@@ -32,7 +32,7 @@ def test_launch_configuration_and_arguments():
     lc = mod.launch_config()
     import torch
     assert lc["grid"][0] == torch.cuda.get_device_properties(0).multi_processor_count
-    assert lc["block"] == (256, 1, 1) and lc["smem_bytes"] <= 232448
+    assert lc["block"] == (384, 1, 1) and lc["smem_bytes"] <= 232448
     kinds = [a["kind"] for a in mod.args()]
     assert kinds == [0, 0, 0, 1, 2]
     mod.close()
@@ -113,9 +113,9 @@ def test_spec_dump_and_reload(tmp_path):
     assert (cdir / "best_tuning_spec.json").exists() and (cdir / "performance_report.csv").exists()
     spec = json.loads((cdir / "best_tuning_spec.json").read_text())
     grid = spec["cuda_context"]["cuda_runtime_context"]["grid_dim"]["x"]
-    assert (cdir / f"{grid}_1_1__256_1_1.json").exists()
+    assert (cdir / f"{grid}_1_1__384_1_1.json").exists()
     rows = (cdir / "performance_report.csv").read_text().strip().splitlines()
-    assert len(rows) == len(mod.plan()["stages"]) and rows[0].split(",")[0] == f"{grid}_1_1__256_1_1"
+    assert len(rows) == len(mod.plan()["stages"]) and rows[0].split(",")[0] == f"{grid}_1_1__384_1_1"
     # change a tile in the saved spec, reload through TF_MONONN_EXISTING_TUNING_SPEC_DIR semantics
     spec["gemm_spec_list"]["gemm_down_0"]["sm100_config"].update(mma_n=32, k_split=2)
     (cdir / "best_tuning_spec.json").write_text(json.dumps(spec))

@@ -16,16 +16,30 @@ def base_plan(lib_built):
 
 def test_bert_base_stage_structure(base_plan):
     p = base_plan["plan"]
-    assert p["grid"] == 148 and p["block"] == 256
+    assert p["grid"] == 148 and p["block"] == 384
     assert p["smem_bytes"] <= 232448
     stages = p["stages"]
     # 12 (batch, head) pairs cannot fill 148 CTAs: the Q/K/V projections run inside the attention items
-    assert len(stages) == 1 + 12 * 6
-    kinds = [tuple(o["kind"] for o in s["ops"]) for s in stages[:7]]
-    assert kinds == [("embed",), ("attention",), ("gemm",), ("layernorm",), ("gemm",), ("gemm",), ("layernorm",)]
+    # and each LayerNorm shares the stage of the split-K GEMM that feeds it: four stages a layer
+    assert len(stages) == 1 + 12 * 4
+    kinds = [tuple(o["kind"] for o in s["ops"]) for s in stages[:5]]
+    assert kinds == [("embed",), ("attention",), ("gemm", "layernorm"), ("gemm",), ("gemm", "layernorm")]
     assert stages[1]["ops"][0]["flags"] & (1 << 11)
-    # every stage fits one wave of the 148 CTAs at b1/s128
-    assert all(s["n_items"] <= 148 for s in stages)
+    # the row items wait for exactly the GEMM items dealt before them
+    for s in stages:
+        if len(s["ops"]) == 2:
+            g, ln = s["ops"]
+            assert g["flag"] == ln["flag"] and not g["waits"] and ln["waits"] and ln["flag_target"] == g["n_items"]
+    # every GEMM / attention operator fits one wave of the 148 CTAs at b1/s128
+    assert all(o["n_items"] <= 148 for s in stages for o in s["ops"])
+
+
+def test_row_fusion_off_keeps_layernorm_stages(base_plan):
+    off = dict(base_plan["spec"], row_fusion="off")
+    p = describe("encoder", bert_base().to_json(), spec=off)["plan"]
+    assert len(p["stages"]) == 1 + 12 * 6
+    assert all("flag" not in o for s in p["stages"] for o in s["ops"])
+    assert p["spec_echo"]["row_fusion"] == "off" if "spec_echo" in p else True
 
 
 def test_projections_stay_a_stage_of_their_own_when_attention_fills_the_gpu(lib_built, base_plan):
@@ -33,7 +47,7 @@ def test_projections_stay_a_stage_of_their_own_when_attention_fills_the_gpu(lib_
     when the attention stage leaves CTAs idle (or on request), never for long sequences."""
     off = dict(base_plan["spec"], qkv_fusion="off")
     p = describe("encoder", bert_base().to_json(), spec=off)["plan"]
-    assert len(p["stages"]) == 1 + 12 * 7
+    assert len(p["stages"]) == 1 + 12 * 5
     assert [o["kind"] for o in p["stages"][1]["ops"]] == ["gemm", "gemm", "gemm"]
     assert abs(p["algorithmic_flops"] - base_plan["plan"]["algorithmic_flops"]) < 1e6
     many = describe("encoder", bert_tiny(batch=160, seq=16, layers=1).to_json())["plan"]   # 160 pairs > 148 CTAs
@@ -112,7 +126,7 @@ def test_spec_controls_the_tiles_and_round_trips(lib_built, tmp_path):
     assert set(spec) >= {"cuda_context", "gemm_spec_list", "cluster_elewise_spec", "cluster_reduce_spec",
                          "conv_spec_list", "codegen_allow_list", "codegen_reject_list"}
     rt = spec["cuda_context"]["cuda_runtime_context"]
-    assert rt["grid_dim"] == {"x": 148, "y": 1, "z": 1} and rt["block_dim"]["x"] == 256
+    assert rt["grid_dim"] == {"x": 148, "y": 1, "z": 1} and rt["block_dim"]["x"] == 384
     spec["gemm_spec_list"]["layer0.ffn.down"]["sm100_config"].update(mma_n=64, k_split=2)
     d2 = describe("encoder", cfg.to_json(), spec=spec)
     ops = {o["name"]: o for s in d2["plan"]["stages"] for o in s["ops"]}
