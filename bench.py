@@ -203,6 +203,8 @@ def spec_override_dir(overrides: str, text: str, kind: str):
         if k == "grid":
             spec["cuda_context"]["cuda_runtime_context"]["grid_dim"]["x"] = int(v)
             spec["gemm_spec_list"] = {}
+        elif k == "cluster":
+            spec["cuda_context"]["cuda_runtime_context"]["cluster_dim"] = {"x": int(v), "y": 1, "z": 1}
         else:
             spec[k] = v
             if k in ("qkv_fusion", "row_fusion"):

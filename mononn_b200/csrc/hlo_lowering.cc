@@ -78,6 +78,7 @@ struct Val {
   int q_tensor = -1, k_tensor = -1;   // SCORES / PROBS
   float alpha = 1.f;
   int mask_tensor = -1;               // PROBS
+  int pbias_tensor = -1;              // PROBS: constant bias per (head, query, key)
   float mask_scale = 0.f;             // MASK
   int mask_arg = -1;                  // MASK: the s32 argument it derives from
   int ids = -1, types = -1, word = -1, pos = -1, type = -1;  // EMBED_SUM (FGraph tensors)
@@ -342,6 +343,7 @@ class Lowering {
       o.k = a.k_tensor;
       o.vt = b.tensor;
       o.mask = a.mask_tensor;
+      o.pos_bias = a.pbias_tensor;
       o.heads = a.heads;
       o.seq = a.S;
       o.batches = a.B;
@@ -601,6 +603,7 @@ class Lowering {
         }
     }
     uint32_t off_found = 0;
+    if (vec_k.size() == 1) return lower_rmsnorm(idx, c, main_k, vec_k[0], resid_k, stride);
     if (vec_k.size() < 2 || vec_k.size() > 3) return unsupported(ins, "expected scale, shift and at most one bias vector");
     std::vector<float> eps_cands;
     for (const HloInstr& i : c.instrs)
@@ -740,21 +743,100 @@ class Lowering {
     return MONONN_OK;
   }
 
+  // x * rsqrt(mean(x^2) + eps) * scale over the last dimension: the LayerNorm of T5 (no mean
+  // subtraction, no shift), reading an activation or the f32 residual stream.
+  int lower_rmsnorm(int idx, const HloComputation& c, int main_k, int gamma_k, int resid_k, uint32_t stride) {
+    const HloInstr& ins = e_.instrs[idx];
+    const Val mv = vals_[ins.operands[main_k]];
+    const uint32_t cols = static_cast<uint32_t>(ins.shape.dims.back());
+    const uint32_t rows = static_cast<uint32_t>(ins.shape.elements() / cols);
+    if (resid_k >= 0 || stride != 1 || (mv.kind != Val::ACT && mv.kind != Val::STREAM))
+      return unsupported(ins, "RMS normalisation of anything but a plain activation");
+    std::vector<float> eps_cands;
+    for (const HloInstr& i : c.instrs)
+      if (i.opcode == "constant" && i.literal_is_scalar && i.literal > 0 && i.literal < 0.1)
+        eps_cands.push_back(static_cast<float>(i.literal));
+    if (eps_cands.empty()) eps_cands.push_back(0.f);
+    float eps_found = 0.f;
+    bool ok = false;
+    const std::string mkey = memo_key("rmsnorm", c, {main_k, gamma_k});
+    const auto hit = memo_.find(mkey);
+    if (hit != memo_.end()) {
+      eps_found = static_cast<float>(hit->second[0]);
+      ok = true;
+    } else {
+      Rng rng;  // small rows, so that the epsilon under the root is visible in the result
+      std::vector<HTensor> ps = probe_inputs(c, [&](size_t k, HTensor& t) {
+        for (float& x : t.v) x = static_cast<int>(k) == gamma_k ? rng.uni(0.5f, 1.5f) : rng.uni(-0.02f, 0.02f);
+      });
+      HTensor got;
+      int rc = probe(c, ps, &got);
+      if (rc) return rc;
+      float best = 1e30f;
+      for (float eps : eps_cands) {
+        float worst = 0.f;
+        for (uint32_t r = 0; r < rows; ++r) {
+          double sq = 0;
+          for (uint32_t j = 0; j < cols; ++j) {
+            const double y = ps[main_k].v[static_cast<size_t>(r) * cols + j];
+            sq += y * y;
+          }
+          const double rstd = 1.0 / std::sqrt(sq / cols + eps);
+          for (uint32_t j = 0; j < cols; ++j) {
+            const float w = static_cast<float>(ps[main_k].v[static_cast<size_t>(r) * cols + j] * rstd) * ps[gamma_k].v[j];
+            worst = std::max(worst, std::fabs(w - got.v[static_cast<size_t>(r) * cols + j]));
+          }
+        }
+        if (worst < best) {
+          best = worst;
+          eps_found = eps;
+        }
+      }
+      ok = best < 1e-3f;
+      if (ok) memo_[mkey] = {static_cast<double>(eps_found)};
+    }
+    if (!ok) return unsupported(ins, "fused computation " + c.name + " is neither LayerNorm nor x * rsqrt(mean(x^2) + eps) * scale");
+    FOp n;
+    n.kind = OP_LAYERNORM;
+    n.name = canonical_node_name(ins.name);
+    n.flags = F_RMSNORM;
+    n.rows = rows;
+    n.cols = cols;
+    n.eps = eps_found;
+    n.gamma = const_tensor(vals_[ins.operands[gamma_k]].instr, 1, cols);
+    n.src = mv.tensor;
+    n.out = act_tensor(n.name, rows, cols);
+    g_.ops.push_back(n);
+    Val v;
+    v.kind = Val::ACT;
+    v.instr = idx;
+    v.tensor = n.out;
+    v.op = static_cast<int>(g_.ops.size()) - 1;
+    v.rows = rows;
+    v.cols = cols;
+    vals_[idx] = v;
+    return MONONN_OK;
+  }
+
   // softmax(scores + mask) over the keys
   int lower_softmax(int idx, const HloComputation& c, int main_k) {
     const HloInstr& ins = e_.instrs[idx];
     const Val sv = vals_[ins.operands[main_k]];
     if (uses_[sv.instr] != 1) return unsupported(ins, "attention scores with more than one consumer");
-    int mask_k = -1;
+    int mask_k = -1, pbias_k = -1;
     for (size_t k = 0; k < ins.operands.size(); ++k) {
       if (static_cast<int>(k) == main_k) continue;
-      if (vals_[ins.operands[k]].kind == Val::MASK && mask_k < 0) mask_k = static_cast<int>(k);
+      const Val& ov = vals_[ins.operands[k]];
+      if (ov.kind == Val::MASK && mask_k < 0) mask_k = static_cast<int>(k);
+      else if (ov.kind == Val::CONST && pbias_k < 0 &&
+               e_.instrs[ins.operands[k]].shape.elements() == static_cast<int64_t>(sv.heads) * sv.S * sv.S)
+        pbias_k = static_cast<int>(k);  // additive bias per (head, query, key)
       else return unsupported(ins, "operand %" + e_.instrs[ins.operands[k]].name + " has no role in a softmax fusion");
     }
     const uint32_t B = sv.B, H = sv.heads, S = sv.S;
     if (ins.shape.dims != std::vector<int64_t>{B, H, S, S}) return unsupported(ins, "result shape");
     bool causal = false, ok = false;
-    const std::string mkey = memo_key("softmax", c, {main_k, mask_k});
+    const std::string mkey = memo_key("softmax", c, {main_k, mask_k, pbias_k});
     const auto hit = memo_.find(mkey);
     if (hit != memo_.end()) {
       causal = hit->second[0] != 0.0;
@@ -778,7 +860,8 @@ class Lowering {
             const uint32_t n_keys = causal ? q + 1 : S;
             float mx = -INFINITY;
             for (uint32_t k = 0; k < n_keys; ++k) {
-              const float z = ps[main_k].v[base + k] + (mask_k >= 0 ? ps[mask_k].v[static_cast<size_t>(b) * S + k] : 0.f);
+              const float z = ps[main_k].v[base + k] + (mask_k >= 0 ? ps[mask_k].v[static_cast<size_t>(b) * S + k] : 0.f) +
+                              (pbias_k >= 0 ? ps[pbias_k].v[(static_cast<size_t>(h) * S + q) * S + k] : 0.f);
               want[base + k] = z;
               mx = std::max(mx, z);
             }
@@ -801,6 +884,7 @@ class Lowering {
     v.kind = Val::PROBS;
     v.instr = idx;
     v.mask_tensor = mask_k >= 0 ? vals_[ins.operands[mask_k]].tensor : -1;
+    v.pbias_tensor = pbias_k >= 0 ? const_tensor(vals_[ins.operands[pbias_k]].instr, H * S, S) : -1;
     v.causal = causal;
     vals_[idx] = v;
     return MONONN_OK;
@@ -1112,8 +1196,9 @@ class Lowering {
         pos_off = lb == std::string::npos ? 0 : static_cast<uint32_t>(std::strtoul(sl.c_str() + lb + 1, nullptr, 10));
       }
     }
-    if (gathers.empty() || gathers.size() > 2 || pos_param < 0)
-      return unsupported(ins, "embedding fusion must be word gather + position slice (+ type gather)");
+    // (no position slice: a model with relative positions, e.g. T5, gathers token rows only)
+    if (gathers.empty() || gathers.size() > 2 || (pos_param < 0 && gathers.size() != 1))
+      return unsupported(ins, "embedding fusion must be word gather (+ position slice) (+ type gather)");
     for (auto& gp : gathers)
       if (gp.first < 0 || gp.second < 0) return unsupported(ins, "gather operands must come from fusion parameters");
     if (ins.shape.dims.size() != 2) return unsupported(ins, "embedding sum must be [tokens, hidden]");
@@ -1140,14 +1225,14 @@ class Lowering {
     std::vector<float> want(static_cast<size_t>(T) * H);
     for (uint32_t t = 0; t < T; ++t)
       for (uint32_t j = 0; j < H; ++j) {
-        float y = ps[pos_param].v[static_cast<size_t>(t % S + pos_off) * H + j];
+        float y = pos_param >= 0 ? ps[pos_param].v[static_cast<size_t>(t % S + pos_off) * H + j] : 0.f;
         for (auto& gp : gathers)
           y += ps[gp.first].v[static_cast<size_t>(ps[gp.second].v[t]) * H + j];
         want[static_cast<size_t>(t) * H + j] = y;
       }
     if (!all_close(got.v, want, 1e-5f, 1e-5f))
       return unsupported(ins, "fused computation " + c.name + " is not word[ids] + position[a:a+S] + type[type_ids]");
-    if (static_cast<int64_t>(pos_off) + S > c.instrs[c.params[pos_param]].shape.dims[0])
+    if (pos_param >= 0 && static_cast<int64_t>(pos_off) + S > c.instrs[c.params[pos_param]].shape.dims[0])
       return unsupported(ins, "position slice runs past the table");
     auto table = [&](int param) {
       const int instr = vals_[ins.operands[param]].instr;
@@ -1155,7 +1240,7 @@ class Lowering {
       return const_tensor(instr, static_cast<uint32_t>(ti.shape.dims[0]), static_cast<uint32_t>(ti.shape.dims[1]));
     };
     for (int p : {gathers[0].first, pos_param})
-      if (vals_[ins.operands[p]].kind != Val::CONST) return unsupported(ins, "embedding tables must be constants");
+      if (p >= 0 && vals_[ins.operands[p]].kind != Val::CONST) return unsupported(ins, "embedding tables must be constants");
     Val v;
     v.kind = Val::EMBED_SUM;
     v.instr = idx;
@@ -1166,7 +1251,7 @@ class Lowering {
     v.ids = vals_[ins.operands[gathers[0].second]].tensor;
     v.word = table(gathers[0].first);
     v.vocab = g_.tensors[v.word].rows;
-    v.pos = table(pos_param);
+    v.pos = pos_param >= 0 ? table(pos_param) : -1;
     if (gathers.size() == 2) {
       if (vals_[ins.operands[gathers[1].first]].kind != Val::CONST) return unsupported(ins, "type table must be a constant");
       v.types = vals_[ins.operands[gathers[1].second]].tensor;

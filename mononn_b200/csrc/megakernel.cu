@@ -24,6 +24,7 @@
 // up in KernelStatus and all roles drain and return.
 #include <cuda.h>
 #include <cuda_fp16.h>
+#include <stddef.h>
 #include <stdint.h>
 
 #include "stage_table.h"
@@ -69,6 +70,28 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int3
       "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
       "l"(tmap), "r"(x), "r"(y), "r"(bar)
       : "memory");
+}
+// The same copy with an L2 eviction-priority hint (replaces the evict-last / streaming loads the
+// reference selects per access pattern, mononn_engine/core/gpu/memory.cc:172-235): weights are
+// read once per inference (evict first), activation tiles are re-read by every CTA of a stage
+// (evict last).
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const void* tmap, int32_t x, int32_t y,
+                                                 uint32_t bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%2, %3}], [%4], %5;" ::"r"(dst),
+      "l"(tmap), "r"(x), "r"(y), "r"(bar), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
 }
 __device__ __forceinline__ void fence_proxy_async_all() {
   asm volatile("fence.proxy.async;" ::: "memory");
@@ -155,6 +178,44 @@ __device__ __forceinline__ uint32_t ld_relaxed_gpu(const uint32_t* p) {
   asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+// Thread-block cluster helpers: rank of this CTA, the shared::cluster address of a peer's copy of
+// a shared-memory object, a remote mbarrier arrival with release at cluster scope, the matching
+// acquire-side test, and the whole-cluster barrier used around set-up and teardown.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t mapa_smem(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_remote_release_cluster(uint32_t remote_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait_acquire_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ void st_release_cta_smem(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_cta_smem(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
+  return v;
+}
 __device__ __forceinline__ void fence_acq_rel_gpu() {
   asm volatile("fence.acq_rel.gpu;" ::: "memory");
 }
@@ -188,9 +249,12 @@ struct Ctrl {
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
   uint64_t group_bar;  // the eight epilogue warps (256 arrivals per phase)
+  uint64_t cl_bar;     // first CTA of a cluster: one arrival per CTA of the cluster per stage
   uint32_t tmem_base;
   uint32_t abort_flag;
-  float bias_tile[2][256];  // bias of the current GEMM tile, double buffered across items
+  uint32_t barriers_seen;  // grid barriers of this launch the CTA's poller has observed (monotonic)
+  uint32_t pad_;
+  alignas(16) float bias_tile[2][256];  // bias of the current GEMM tile, double buffered across items
   float mask_row[384];      // additive key mask of the current attention tile (log2 units)
   float row_max[2][128];    // attention: row maximum / row sum over each warp half's columns,
   float row_sum[2][128];    // exchanged between the two threads that share a query row
@@ -202,6 +266,10 @@ struct Ctrl {
 };
 
 static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block exceeds its shared-memory reserve");
+// these members are read with 16-byte vector loads
+static_assert(offsetof(Ctrl, bias_tile) % 16 == 0 && offsetof(Ctrl, mask_row) % 16 == 0 &&
+                  offsetof(Ctrl, desc) % 16 == 0,
+              "vector-loaded members of the control block must be 16-byte aligned");
 static_assert(sizeof(OpDesc) % 16 == 0 && sizeof(OpDesc) <= 256, "descriptor slot size");
 static_assert(sizeof(StageDesc) == 48, "stage descriptor is read as three 16-byte words");
 
@@ -272,7 +340,15 @@ __device__ __forceinline__ bool mbar_wait(const Ctx& c, uint64_t* bar, uint32_t 
   return mbar_wait_slow(c.P, c.ctrl, b, parity, c.stage, where);
 }
 
-// Bounded wait until every CTA has arrived for all stages before `stage`.
+#ifndef MONONN_POLL_SLEEP
+#define MONONN_POLL_SLEEP 32
+#endif
+// Bounded wait until every CTA has arrived for all stages before `stage`. Two threads per CTA
+// poll the global counter: the activation producer (its first tile load is the critical path of
+// a GEMM stage; routing it through a second hop measured 20 us slower over a whole inference)
+// and the first epilogue warp's lane 0, which then publishes the number of barriers seen in
+// shared memory for the other seven epilogue warps: some 300 pollers on the counter's L2 line
+// instead of 1300.
 __device__ __noinline__ bool grid_wait_slow(const KernelParams* P, Ctrl* ctrl, uint32_t target,
                                             uint32_t stage, uint32_t where) {
   const uint64_t t0 = globaltimer_ns();
@@ -283,7 +359,9 @@ __device__ __noinline__ bool grid_wait_slow(const KernelParams* P, Ctrl* ctrl, u
       fence_acq_rel_gpu();
       return true;
     }
-    __nanosleep(32);
+#if MONONN_POLL_SLEEP > 0
+    __nanosleep(MONONN_POLL_SLEEP);
+#endif
     if ((++it & 31u) == 0u) {
       if (*reinterpret_cast<volatile uint32_t*>(&ctrl->abort_flag)) return false;
       if (*reinterpret_cast<volatile uint32_t*>(&P->status->code) != 0u) {
@@ -297,15 +375,45 @@ __device__ __noinline__ bool grid_wait_slow(const KernelParams* P, Ctrl* ctrl, u
     }
   }
 }
-__device__ __forceinline__ bool grid_wait(const Ctx& c, uint32_t stage, uint32_t where) {
+// A global poller; with `announce` it also makes the shared-memory announcement.
+__device__ __forceinline__ bool grid_wait(const Ctx& c, uint32_t stage, uint32_t where, bool announce) {
   const KernelParams& P = *c.P;
   if (stage == P.stage_begin) return true;
-  const uint32_t target = P.epoch_base + (stage - P.stage_begin) * gridDim.x;
+  const uint32_t target =
+      P.epoch_base + (stage - P.stage_begin) * (gridDim.x / P.cluster) * (P.warp_arrive ? kSimtWarps : 1u);
+  bool ok = true;
   if (static_cast<int32_t>(ld_relaxed_gpu(P.barrier) - target) >= 0) {
     fence_acq_rel_gpu();
-    return true;
+  } else {
+    ok = grid_wait_slow(c.P, c.ctrl, target, stage, where);
   }
-  return grid_wait_slow(c.P, c.ctrl, target, stage, where);
+  if (ok && announce) st_release_cta_smem(&c.ctrl->barriers_seen, stage - P.stage_begin);
+  return ok;
+}
+// Everybody else in the CTA: wait for the poller's announcement (acquire at CTA scope after the
+// poller's acquire at GPU scope orders the other CTAs' stores before this thread's loads).
+__device__ __noinline__ bool local_wait_slow(const KernelParams* P, Ctrl* ctrl, uint32_t need,
+                                             uint32_t stage, uint32_t where) {
+  const uint64_t t0 = globaltimer_ns();
+  const uint64_t limit = static_cast<uint64_t>(P->timeout_us) * 1000ull;
+  uint32_t it = 0;
+  for (;;) {
+    if (ld_acquire_cta_smem(&ctrl->barriers_seen) >= need) return true;
+    if ((++it & 63u) == 0u) {
+      if (*reinterpret_cast<volatile uint32_t*>(&ctrl->abort_flag)) return false;
+      if (globaltimer_ns() - t0 > limit) {
+        report_failure(P, ctrl, stage, ST_GRID_BARRIER_TIMEOUT, where);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ bool grid_wait_local(const Ctx& c, uint32_t stage, uint32_t where) {
+  const KernelParams& P = *c.P;
+  if (stage == P.stage_begin) return true;
+  const uint32_t need = stage - P.stage_begin;
+  if (ld_acquire_cta_smem(&c.ctrl->barriers_seen) >= need) return true;
+  return local_wait_slow(c.P, c.ctrl, need, stage, where);
 }
 
 // Warp-collective variants for the epilogue warps: every lane gets the same answer, so a
@@ -317,7 +425,8 @@ __device__ __forceinline__ bool mbar_wait_warp(const Ctx& c, uint64_t* bar, uint
 }
 __device__ __forceinline__ bool grid_wait_warp(const Ctx& c, uint32_t stage, uint32_t where) {
   bool ok = true;
-  if ((threadIdx.x & 31u) == 0u) ok = grid_wait(c, stage, where);
+  if ((threadIdx.x & 31u) == 0u)
+    ok = (threadIdx.x == kRoleThreads) ? grid_wait(c, stage, where, true) : grid_wait_local(c, stage, where);
   return __all_sync(0xffffffffu, ok);
 }
 // A row op that shares a stage with the split-K GEMMs feeding it waits until all of their work
@@ -490,6 +599,8 @@ __device__ __forceinline__ uint32_t k_rotation(uint32_t nkb, uint32_t kbps) {
 __device__ void role_weight_producer(Ctx c) {
   const KernelParams& P = *c.P;
   const uint8_t* tmaps = static_cast<const uint8_t*>(P.tmaps);
+  const bool hint = P.l2_hints != 0u;
+  const uint64_t pol = l2_policy_evict_first();
   uint32_t b_cnt = 0;
   for (uint32_t s = P.stage_begin; s < P.stage_end; ++s) {
     c.stage = s;
@@ -529,9 +640,14 @@ __device__ void role_weight_producer(Ctx c) {
           const uint32_t full = smem_u32(&c.ctrl->b_full[slot]);
           mbar_arrive_expect_tx(full, 3u * 8192u);
 #pragma unroll
-          for (uint32_t j = 0; j < 3; ++j)
-            tma_load_2d(c.b_ring + slot * kBSlotBytes + j * 8192u, tmw[j], 0,
-                        static_cast<int32_t>((t.h * nkb + kb) * 64u), full);
+          for (uint32_t j = 0; j < 3; ++j) {
+            if (hint)
+              tma_load_2d_hint(c.b_ring + slot * kBSlotBytes + j * 8192u, tmw[j], 0,
+                               static_cast<int32_t>((t.h * nkb + kb) * 64u), full, pol);
+            else
+              tma_load_2d(c.b_ring + slot * kBSlotBytes + j * 8192u, tmw[j], 0,
+                          static_cast<int32_t>((t.h * nkb + kb) * 64u), full);
+          }
           ++b_cnt;
         }
         trace(P, s, TR_W_ISSUED);
@@ -551,8 +667,12 @@ __device__ void role_weight_producer(Ctx c) {
         WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->b_empty[slot], (use & 1u) ^ 1u, 0x100));
         const uint32_t full = smem_u32(&c.ctrl->b_full[slot]);
         mbar_arrive_expect_tx(full, bytes);
-        tma_load_2d(c.b_ring + slot * kBSlotBytes, tm, 0, static_cast<int32_t>(row0 + kb * op.n_tile),
-                    full);
+        if (hint)
+          tma_load_2d_hint(c.b_ring + slot * kBSlotBytes, tm, 0, static_cast<int32_t>(row0 + kb * op.n_tile),
+                           full, pol);
+        else
+          tma_load_2d(c.b_ring + slot * kBSlotBytes, tm, 0, static_cast<int32_t>(row0 + kb * op.n_tile),
+                      full);
         ++b_cnt;
       }
       trace(P, s, TR_W_ISSUED);
@@ -566,6 +686,8 @@ __device__ void role_weight_producer(Ctx c) {
 __device__ void role_act_producer(Ctx c) {
   const KernelParams& P = *c.P;
   const uint8_t* tmaps = static_cast<const uint8_t*>(P.tmaps);
+  const bool hint = P.l2_hints != 0u;
+  const uint64_t pol = l2_policy_evict_last();
   uint32_t a_cnt = 0;
   for (uint32_t s = P.stage_begin; s < P.stage_end; ++s) {
     c.stage = s;
@@ -588,7 +710,7 @@ __device__ void role_act_producer(Ctx c) {
       const OpDesc& op = *it.op;
       if (op.kind != OP_GEMM && op.kind != OP_ATTENTION) continue;
       if (!waited) {
-        WAIT_OR_RETURN(grid_wait(c, s, 0x200));
+        WAIT_OR_RETURN(grid_wait(c, s, 0x200, false));
         fence_proxy_async_all();
         waited = true;
         trace(P, s, TR_ACT_READY);
@@ -604,9 +726,12 @@ __device__ void role_act_producer(Ctx c) {
           WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->a_empty[slot], (use & 1u) ^ 1u, 0x201));
           const uint32_t full = smem_u32(&c.ctrl->a_full[slot]);
           mbar_arrive_expect_tx(full, kSlotBytes);
-          tma_load_2d(c.a_ring + slot * kSlotBytes, tm,
-                      static_cast<int32_t>((t.ks * nkb + kb) * 64u),
-                      static_cast<int32_t>(t.mt * 128u), full);
+          if (hint)
+            tma_load_2d_hint(c.a_ring + slot * kSlotBytes, tm, static_cast<int32_t>((t.ks * nkb + kb) * 64u),
+                             static_cast<int32_t>(t.mt * 128u), full, pol);
+          else
+            tma_load_2d(c.a_ring + slot * kSlotBytes, tm, static_cast<int32_t>((t.ks * nkb + kb) * 64u),
+                        static_cast<int32_t>(t.mt * 128u), full);
           ++a_cnt;
         }
       } else {
@@ -831,6 +956,23 @@ __device__ __forceinline__ void lds32(const float* p, float (&m)[32]) {
     m[4 * i] = t.x; m[4 * i + 1] = t.y; m[4 * i + 2] = t.z; m[4 * i + 3] = t.w;
   }
 }
+// mk[i] += log2(e) * bias[i] for 32 consecutive f16 values (64-byte aligned: four vector loads)
+__device__ __forceinline__ void add_bias32(const __half* p, float (&mk)[32]) {
+  const uint4* q = reinterpret_cast<const uint4*>(p);
+  uint4 r[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) r[i] = __ldg(q + i);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __half2* h = reinterpret_cast<const __half2*>(&r[i]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __half22float2(h[j]);
+      mk[8 * i + 2 * j] = fmaf(f.x, 1.4426950408889634f, mk[8 * i + 2 * j]);
+      mk[8 * i + 2 * j + 1] = fmaf(f.y, 1.4426950408889634f, mk[8 * i + 2 * j + 1]);
+    }
+  }
+}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -1017,7 +1159,7 @@ __device__ __noinline__ void rowwise_item(const OpDesc& op, uint32_t local, uint
   if (mark) trace(P, stage, TR_MARK0);
   const uint32_t cols = op.cols, nvec = cols >> 2, flags = op.flags;
   const bool embed = (op.kind == OP_EMBED), assemble = (op.kind == OP_ASSEMBLE);
-  const bool no_norm = (flags & F_NO_NORM) != 0u, l2 = (flags & F_L2NORM) != 0u;
+  const bool no_norm = (flags & F_NO_NORM) != 0u, l2 = (flags & F_L2NORM) != 0u, rms = (flags & F_RMSNORM) != 0u;
   RowSrc s{nullptr, nullptr, nullptr, nullptr, false};
   if (assemble) {
     // token row t of batch b: the first k_col rows come from a constant table (class token),
@@ -1038,8 +1180,9 @@ __device__ __noinline__ void rowwise_item(const OpDesc& op, uint32_t local, uint
     const int32_t id = reinterpret_cast<const int32_t*>(op.p[1])[row];
     s.h0 = reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(op.p[3]) +
                                           static_cast<int64_t>(id) * cols);
-    s.h1 = reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(op.p[4]) +
-                                          static_cast<size_t>(row % op.seq + op.q_col) * cols);
+    if (op.p[4] != 0)  // (a model without learned positions has no table: T5)
+      s.h1 = reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(op.p[4]) +
+                                            static_cast<size_t>(row % op.seq + op.q_col) * cols);
     if (flags & F_TYPE_IDS) {
       const int32_t ty = reinterpret_cast<const int32_t*>(op.p[2])[row];
       s.h2 = reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(op.p[5]) +
@@ -1135,7 +1278,7 @@ __device__ __noinline__ void rowwise_item(const OpDesc& op, uint32_t local, uint
       sum += x[i].x + x[i].y + x[i].z + x[i].w;
     }
     if (mark) trace(P, stage, TR_MARK0 + 1);
-    const float mean = l2 ? 0.f : warp_sum(sum) * inv_n;
+    const float mean = (l2 || rms) ? 0.f : warp_sum(sum) * inv_n;
     float sq = 0.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i)
@@ -1144,6 +1287,10 @@ __device__ __noinline__ void rowwise_item(const OpDesc& op, uint32_t local, uint
         sq += a * a + b * b + c * c + d * d;
       }
     const float rstd = l2 ? rsqrtf(warp_sum(sq)) : rsqrtf(warp_sum(sq) * inv_n + eps);
+    if (rms) {  // no shift: the host binds the scale vector as the shift pointer too
+#pragma unroll
+      for (int i = 0; i < 8; ++i) bv[i] = make_uint2(0u, 0u);
+    }
     if (!no_norm && !l2 && out != nullptr) {
       // the common LayerNorm: the per-item choices are made once here, not per 8-byte group (a
       // branch costs a warp that is alone on its scheduler some twenty cycles)
@@ -1191,7 +1338,7 @@ __device__ __noinline__ void rowwise_item(const OpDesc& op, uint32_t local, uint
       const float4 a = row_chunk(s, vi);
       sum += a.x + a.y + a.z + a.w;
     }
-    const float mean = l2 ? 0.f : warp_sum(sum) * inv_n;
+    const float mean = (l2 || rms) ? 0.f : warp_sum(sum) * inv_n;
     float sq = 0.f;
 #pragma unroll 1
     for (uint32_t vi = lane; vi < nvec; vi += 32u) {
@@ -1204,7 +1351,7 @@ __device__ __noinline__ void rowwise_item(const OpDesc& op, uint32_t local, uint
     for (uint32_t vi = lane; vi < nvec; vi += 32u) {
       const float4 a = row_chunk(s, vi);
       if (s.zero) const_cast<float4*>(s.f32)[vi] = make_float4(0.f, 0.f, 0.f, 0.f);
-      row_emit(a, mean, rstd, vi, __ldg(gamma + vi), __ldg(beta + vi),
+      row_emit(a, mean, rstd, vi, __ldg(gamma + vi), rms ? make_uint2(0u, 0u) : __ldg(beta + vi),
                add_bias2 ? __ldg(bias2 + vi) : make_uint2(0u, 0u), out, out2, add_bias2, no_norm, l2);
     }
   }
@@ -1454,12 +1601,19 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
   tc_fence_after();
   const uint32_t tS = tmem_base + ((quarter * 32u) << 16);
   const uint32_t h64 = half * 64u;
+  // additive bias per (head, query, key): this thread's row of the head's [seq, seq] table
+  // (rows past the sequence end read the last row; their results are never stored)
+  const __half* pb = nullptr;
+  if (op.flags & F_POS_BIAS)
+    pb = reinterpret_cast<const __half*>(op.q[0]) +
+         (static_cast<size_t>(t.h) * seq + (qrow < seq ? qrow : seq - 1u)) * seq;
   // pass 1: row maximum of scale*s + mask over this warp's key halves (four independent chains)
   float m0 = -3.0e38f, m1 = -3.0e38f, m2 = -3.0e38f, m3 = -3.0e38f;
 #pragma unroll 1
   for (uint32_t c0 = h64; c0 < n_cols; c0 += ((c0 & 32u) ? 96u : 32u)) {  // 64 of every 128 columns
     float v[32], mk[32];
     lds32(mb + c0, mk);
+    if (pb != nullptr) add_bias32(pb + c0, mk);
     tc_ld32(tS + c0, v);
     if (key_limit == 0xffffffffu) {  // not causal (warp-uniform): no per-element test
 #pragma unroll
@@ -1499,6 +1653,7 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
       const uint32_t cc = j * 128u + h64 + c0;
       float v[32], mk[32];
       lds32(mb + cc, mk);
+      if (pb != nullptr) add_bias32(pb + cc, mk);
       tc_ld32(tS + cc, v);
       if (key_limit == 0xffffffffu) {
         // exp2(s*alpha + mask - max) with the subtraction folded into the multiply-add
@@ -1665,16 +1820,48 @@ __device__ void role_simt(Ctx c, uint32_t tmem_base, uint32_t tid_in_group) {
     }
     // publish this CTA's stores of the stage, then arrive
     if (tid_in_group == 0) trace(P, s, TR_SIMT_DONE);
-    if (blockIdx.x < st.n_items) {
-      // Results that later stages read through TMA need a generic->async proxy fence somewhere
-      // between the store and the load. It sits on the reader side (the activation producer
-      // issues fence.proxy.async after it has acquired the barrier): a second fence here, on
-      // all the writers, cost about half a microsecond per stage.
-      WAIT_OR_RETURN(group_sync(c, 0x402));
+    // Results that later stages read through TMA need a generic->async proxy fence somewhere
+    // between the store and the load. It sits on the reader side (the activation producer
+    // issues fence.proxy.async after it has acquired the barrier): a second fence here, on
+    // all the writers, cost about half a microsecond per stage.
+    if (P.warp_arrive) {
+      // every warp publishes its own stores (a warp stores whole rows or its own reductions) and
+      // arrives for itself: no CTA-wide sync in front of the release
+      __syncwarp();
+      if (lane == 0) red_release_gpu_add(P.barrier, 1u);
+      if (tid_in_group == 0) trace(P, s, TR_SIMT_ARRIVED);
+      continue;
     }
+    if (blockIdx.x < st.n_items) WAIT_OR_RETURN(group_sync(c, 0x402));
     if (tid_in_group == 0) {
-      // release at gpu scope is cumulative over the group's stores ordered by group_sync
-      red_release_gpu_add(P.barrier, 1u);
+      if (P.cluster > 1u) {
+        // Cluster-scoped arrival: every CTA of the cluster arrives (release at cluster scope) on
+        // an mbarrier in the first CTA's shared memory; that CTA acquires the phase and adds one
+        // arrival for the whole cluster to the global counter (release at GPU scope, cumulative
+        // over what it acquired).
+        mbar_arrive_remote_release_cluster(mapa_smem(smem_u32(&c.ctrl->cl_bar), 0u));
+        if (cluster_ctarank() == 0u) {
+          const uint32_t bar = smem_u32(&c.ctrl->cl_bar), parity = (s - P.stage_begin) & 1u;
+          bool ok = mbar_try_wait_acquire_cluster(bar, parity) != 0u;
+          if (!ok) {
+            const uint64_t t0 = globaltimer_ns();
+            for (uint32_t it = 1; !ok; ++it) {
+              ok = mbar_try_wait_acquire_cluster(bar, parity) != 0u;
+              if (!ok && (it & 63u) == 0u) {
+                if (*reinterpret_cast<volatile uint32_t*>(&c.ctrl->abort_flag)) break;
+                if (globaltimer_ns() - t0 > c.timeout_ns) {
+                  report_failure(c.P, c.ctrl, s, ST_GRID_BARRIER_TIMEOUT, 0x440);
+                  break;
+                }
+              }
+            }
+          }
+          if (ok) red_release_gpu_add(P.barrier, 1u);
+        }
+      } else {
+        // release at gpu scope is cumulative over the group's stores ordered by group_sync
+        red_release_gpu_add(P.barrier, 1u);
+      }
       trace(P, s, TR_SIMT_ARRIVED);
     }
   }
@@ -1708,7 +1895,9 @@ mononn_megakernel(const __grid_constant__ KernelParams P) {
       mbar_init(smem_u32(&ctrl->acc_empty[i]), kSimtThreads);
     }
     mbar_init(smem_u32(&ctrl->group_bar), kSimtThreads);
+    mbar_init(smem_u32(&ctrl->cl_bar), P.cluster);
     ctrl->abort_flag = 0;
+    ctrl->barriers_seen = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {
@@ -1721,6 +1910,8 @@ mononn_megakernel(const __grid_constant__ KernelParams P) {
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  // no CTA may arrive on a peer's mbarrier before that peer has initialised it
+  if (P.cluster > 1u) cluster_sync_all();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
 
   // Biases and LayerNorm scale/shift of every layer sit in one small region; touching it now
@@ -1764,6 +1955,8 @@ mononn_megakernel(const __grid_constant__ KernelParams P) {
                  "r"(kTmemCols)
                  : "memory");
   }
+  // a CTA's shared memory must outlive the last remote arrival aimed at it
+  if (P.cluster > 1u) cluster_sync_all();
 }
 
 }  // namespace mononn

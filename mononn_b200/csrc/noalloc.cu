@@ -233,6 +233,9 @@ extern "C" int mononn_attention_noalloc(const void* q, const void* k, const void
   kp.timeout_us = 2000000u;
   kp.stage_begin = 0;
   kp.stage_end = 1;
+  kp.cluster = 1;
+  kp.l2_hints = 0;
+  kp.warp_arrive = 0;
   const unsigned grid = od.n_items < static_cast<unsigned>(st->sm_count) ? od.n_items
                                                                         : static_cast<unsigned>(st->sm_count);
   void* kargs[1] = {&kp};

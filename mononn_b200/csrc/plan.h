@@ -39,6 +39,16 @@ struct TuningSpec {
   // 0 / 2: a LayerNorm that reads a split-K accumulator joins its GEMMs' stage and waits on an
   // arrival counter instead of a grid barrier; 1: it keeps a stage of its own
   uint32_t row_fusion = 0;
+  // CTAs per thread-block cluster (1, 2 or 4; 0 = 1). With more than one, the CTAs of a cluster
+  // arrive at the grid barrier through an mbarrier in the first CTA's shared memory and that
+  // CTA alone adds to the global counter.
+  uint32_t cluster = 0;
+  // L2 eviction-priority hints on the TMA loads: 0 / 1 none, 2 weights evict-first and GEMM
+  // activation tiles evict-last
+  uint32_t l2_hints = 0;
+  // grid-barrier arrival: 0 / 2 one per epilogue warp (each releases its own stores), 1 one per
+  // CTA after a CTA-wide sync (always the case inside a cluster launch)
+  uint32_t barrier_arrive = 0;
 };
 
 // ------------------------------------------------------------------- FGraph
@@ -76,6 +86,9 @@ struct FOp {
   int q = -1, k = -1, vt = -1, mask = -1;
   // ATTENTION fused with its projections: a = x, w / wk / wv and bias / bias_k / bias_v, K = width of x
   int wk = -1, wv = -1, bias_k = -1, bias_v = -1;
+  // ATTENTION: optional additive bias per (head, query, key), a constant [heads*seq, seq] (the
+  // relative position bias of T5, folded to a tensor by the compiler that wrote the HLO)
+  int pos_bias = -1;
   uint32_t q_col = 0, k_col = 0, heads = 0, seq = 0, batches = 0, head_dim = 64;
   // LAYERNORM: src (AccF32 | ActF16), resid, gamma, beta, out
   int src = -1, gamma = -1, beta = -1;
@@ -169,6 +182,7 @@ struct Plan {
   uint64_t scratch_bytes = 0;  // module-owned, zero-initialised
   uint64_t temp_bytes = 0;
   uint32_t grid = 0, block = kThreads, smem_bytes = 0;
+  uint32_t cluster = 1;  // CTAs per cluster of the launch
   TuningSpec spec;             // the spec this plan realises (with heuristics filled in)
   double algorithmic_bytes = 0, algorithmic_flops = 0;
 };

@@ -108,6 +108,23 @@ int Runtime::init(int device) {
   return MONONN_OK;
 }
 
+// Cooperative launch of clusters: both attributes on one launch (the grid barrier needs every
+// CTA resident, the cluster-scoped arrival needs the cluster shape).
+void Runtime::fill_cluster_launch(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attrs, cudaStream_t stream) const {
+  cfg->gridDim = dim3(plan_.grid);
+  cfg->blockDim = dim3(plan_.block);
+  cfg->dynamicSmemBytes = plan_.smem_bytes;
+  cfg->stream = stream;
+  attrs[0].id = cudaLaunchAttributeCooperative;
+  attrs[0].val.cooperative = 1;
+  attrs[1].id = cudaLaunchAttributeClusterDimension;
+  attrs[1].val.clusterDim.x = plan_.cluster;
+  attrs[1].val.clusterDim.y = 1;
+  attrs[1].val.clusterDim.z = 1;
+  cfg->attrs = attrs;
+  cfg->numAttrs = 2;
+}
+
 int Runtime::max_coresident_ctas() {
   int per_sm = 0;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, mononn_megakernel, kThreads,
@@ -135,6 +152,21 @@ int Runtime::load_plan(const Plan& plan) {
   CUDA_TRY(cudaDeviceSynchronize());
   release();
   plan_ = plan;
+  if (plan_.cluster > 1) {
+    // every cluster of the grid must be resident at once, or the grid barrier cannot complete
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attrs[2];
+    fill_cluster_launch(&cfg, attrs, nullptr);
+    cfg.numAttrs = 2;
+    int clusters = 0;
+    cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, reinterpret_cast<const void*>(mononn_megakernel), &cfg);
+    if (e != cudaSuccess || clusters * static_cast<int>(plan_.cluster) < static_cast<int>(plan_.grid)) {
+      cudaGetLastError();
+      set_last_error("clusters of " + std::to_string(plan_.cluster) + " CTAs: only " + std::to_string(clusters) +
+                     " can be co-resident, the grid needs " + std::to_string(plan_.grid / plan_.cluster));
+      return MONONN_ERR_INVALID_ARGUMENT;
+    }
+  }
   CUDA_TRY(cudaMalloc(&d_const_, plan_.const_bytes));
   CUDA_TRY(cudaMemset(d_const_, 0, plan_.const_bytes));
   CUDA_TRY(cudaMalloc(&d_scratch_, plan_.scratch_bytes));
@@ -362,11 +394,22 @@ int Runtime::launch(void* const* args, int n, void* stream, uint32_t stage_begin
   kp.timeout_us = timeout_us ? timeout_us : 2000000u;
   kp.stage_begin = stage_begin;
   kp.stage_end = stage_end;
+  kp.cluster = plan_.cluster;
+  kp.l2_hints = plan_.spec.l2_hints == 2 ? 1u : 0u;
+  kp.warp_arrive = warp_arrive() ? 1u : 0u;
+  kp.pad = 0;
   void* kargs[1] = {&kp};
-  CUDA_TRY(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(mononn_megakernel),
-                                       dim3(plan_.grid), dim3(plan_.block), kargs, plan_.smem_bytes,
-                                       static_cast<cudaStream_t>(stream)));
-  epoch_ += (stage_end - stage_begin) * plan_.grid;
+  if (plan_.cluster <= 1) {
+    CUDA_TRY(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(mononn_megakernel),
+                                         dim3(plan_.grid), dim3(plan_.block), kargs, plan_.smem_bytes,
+                                         static_cast<cudaStream_t>(stream)));
+  } else {
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attrs[2];
+    fill_cluster_launch(&cfg, attrs, static_cast<cudaStream_t>(stream));
+    CUDA_TRY(cudaLaunchKernelExC(&cfg, reinterpret_cast<const void*>(mononn_megakernel), kargs));
+  }
+  epoch_ += (stage_end - stage_begin) * (plan_.grid / plan_.cluster) * (warp_arrive() ? kSimtWarps : 1u);
   if (stamps) n_stamp_stages_ = stage_end - stage_begin;
   return MONONN_OK;
 }

@@ -11,6 +11,8 @@
 #include <string>
 #include <vector>
 
+#include <cuda_runtime.h>
+
 #include "plan.h"
 
 namespace mononn {
@@ -65,6 +67,8 @@ class Runtime {
   // so its first grid-barrier wait runs into the timeout and the kernel reports it.
   void skew_epoch(uint32_t n) { epoch_ += n; }
 
+  // Per-warp barrier arrival is the default; a cluster launch arrives per CTA through the cluster.
+  bool warp_arrive() const { return plan_.cluster <= 1 && plan_.spec.barrier_arrive != 1; }
   unsigned timeout_us = 2000000;
   int pack_threads = 0;  // host threads that re-pack weights when a plan is (re)loaded; 0 = all cores
   const std::map<std::string, std::vector<uint8_t>>& host_constants() const { return host_consts_; }
@@ -73,6 +77,7 @@ class Runtime {
   int bind(void* const* args, int n, void* stream);
   int upload_constant(const ConstBinding& b, const std::vector<uint8_t>& src);
   int upload_all_constants();
+  void fill_cluster_launch(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attrs, cudaStream_t stream) const;
   void release();
 
   int device_ = 0;

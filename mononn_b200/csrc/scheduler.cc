@@ -134,6 +134,7 @@ int validate_plan(const Plan& P, std::string* err) {
     return MONONN_ERR_INVALID_ARGUMENT;
   };
   if (P.block != kThreads) return bad("block size");
+  if ((P.cluster != 1 && P.cluster != 2 && P.cluster != 4) || P.grid % P.cluster != 0) return bad("cluster shape");
   if (P.smem_bytes != kSmemBytes) return bad("shared memory size");
   for (size_t s = 0; s < P.stages.size(); ++s) {
     const StageDesc& sd = P.stages[s];
@@ -190,6 +191,7 @@ int validate_plan(const Plan& P, std::string* err) {
           if (P.tmaps[d.tmap_a].box0 != 64 || P.tmaps[d.tmap_a].box1 != 128) return bad(n + "activation box");
         }
         if (d.n_items != d.batches * d.heads * ((d.seq + 127) / 128)) return bad(n + "item count");
+        if ((d.flags & F_POS_BIAS) && (op.q[0].space == SPACE_NONE || d.seq % 32 != 0)) return bad(n + "position bias");
         if (op.p[0].space == SPACE_NONE) return bad(n + "no output buffer");
         break;
       case OP_LAYERNORM:
@@ -271,6 +273,12 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
   P.grid = spec_in.grid ? spec_in.grid : sm_count;
   P.block = kThreads;
   P.smem_bytes = kSmemBytes;
+  P.cluster = spec_in.cluster ? spec_in.cluster : 1u;
+  if ((P.cluster != 1 && P.cluster != 2 && P.cluster != 4) || P.grid % P.cluster != 0) {
+    if (err) *err = "cluster of " + std::to_string(P.cluster) + " CTAs: must be 1, 2 or 4 and divide the grid";
+    return MONONN_ERR_INVALID_ARGUMENT;
+  }
+  P.spec.cluster = P.cluster;
   P.spec.grid = P.grid;
   P.spec.block = P.block;
   P.spec.smem_bytes = P.smem_bytes;
@@ -281,7 +289,7 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
   auto inputs_of = [](const FOp& o) {
     std::vector<int> v;
     for (int t : {o.a, o.w, o.bias, o.resid, o.q, o.k, o.vt, o.mask, o.src, o.gamma, o.beta, o.ids,
-                  o.type_ids, o.mask_in, o.word, o.pos, o.type, o.bias2, o.wk, o.wv, o.bias_k, o.bias_v})
+                  o.type_ids, o.mask_in, o.word, o.pos, o.type, o.bias2, o.wk, o.wv, o.bias_k, o.bias_v, o.pos_bias})
       if (t >= 0) v.push_back(t);
     return v;
   };
@@ -440,6 +448,41 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
     for (int t : outputs_of(ops[i])) {
       producer[t] = static_cast<int>(i);
       writers[t].push_back(static_cast<int>(i));
+    }
+  }
+
+  // ---- a stage holds at most kMaxStageOps operators (its descriptor has that many item
+  // ranges). Many independent operators can share a depth (the cross-attention K / V projections
+  // of every decoder layer depend on the encoder output alone); those whose results are not
+  // needed in the next stage move one stage later, which no dependent operator can notice.
+  {
+    auto depends = [&](size_t j, size_t i) {  // does op j (later in program order) depend on op i?
+      for (int t : inputs_of(ops[j]))
+        for (int o : outputs_of(ops[i]))
+          if (t == o) return true;
+      for (int t : outputs_of(ops[j])) {
+        for (int o : outputs_of(ops[i]))
+          if (t == o) return true;
+        for (int r : inputs_of(ops[i]))
+          if (t == r && g.tensors[t].kind != TKind::Const) return true;
+      }
+      return false;
+    };
+    for (int st = 0; st < n_stages; ++st) {
+      std::vector<size_t> here;
+      for (size_t i = 0; i < ops.size(); ++i)
+        if (ops[i].stage == st) here.push_back(i);
+      for (size_t k = here.size(); here.size() > kMaxStageOps && k-- > 0;) {
+        const size_t i = here[k];
+        if (flag_of[i] >= 0) continue;  // tied to its partner's stage
+        bool free_to_move = true;
+        for (size_t j = i + 1; j < ops.size() && free_to_move; ++j)
+          if (ops[j].stage <= st + 1 && depends(j, i)) free_to_move = false;
+        if (!free_to_move) continue;
+        ops[i].stage = st + 1;
+        n_stages = std::max(n_stages, st + 2);
+        here.erase(here.begin() + static_cast<long>(k));
+      }
     }
   }
 
@@ -764,6 +807,14 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
             po.p[1] = where[o.mask];
             d.flags |= F_MASK_BIAS;
           }
+          if (o.pos_bias >= 0) {
+            if (o.seq % 32 != 0) {
+              if (err) *err = "attention " + o.name + ": a position bias needs a sequence length that is a multiple of 32";
+              return MONONN_ERR_UNSUPPORTED;
+            }
+            po.q[0] = raw_const(o.pos_bias);
+            d.flags |= F_POS_BIAS;
+          }
           P.algorithmic_flops += 2.0 * 2.0 * o.seq * o.seq * o.head_dim * o.heads * o.batches;
           break;
         }
@@ -794,7 +845,7 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
             po.p[3] = po.p[1];
           } else {
             po.p[2] = raw_const(o.gamma);
-            po.p[3] = raw_const(o.beta);
+            po.p[3] = raw_const(o.beta >= 0 ? o.beta : o.gamma);  // RMS norm: no shift, any valid row
           }
           if (o.resid >= 0) {
             po.p[4] = where[o.resid];
@@ -903,7 +954,7 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
           }
           po.p[1] = where[o.ids];
           po.p[3] = raw_const(o.word);
-          po.p[4] = raw_const(o.pos);
+          if (o.pos >= 0) po.p[4] = raw_const(o.pos);
           if (o.type_ids >= 0 && o.type >= 0) {
             po.p[2] = where[o.type_ids];
             po.p[5] = raw_const(o.type);
@@ -914,8 +965,8 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
             po.p[7] = raw_const(o.beta);
           } else {  // no embedding LayerNorm: the row sum is the result
             d.flags |= F_NO_NORM;
-            po.p[6] = po.p[4];
-            po.p[7] = po.p[4];
+            po.p[6] = po.p[3];
+            po.p[7] = po.p[3];
           }
           if (o.mask_in >= 0 && o.mask_out >= 0) {
             po.q[0] = where[o.mask_in];

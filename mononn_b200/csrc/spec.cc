@@ -57,6 +57,7 @@ std::string spec_to_json(const Plan& plan, uint32_t sm_count) {
   Json rt = Json::object();
   rt.set("grid_dim", dim3_json(plan.grid));
   rt.set("block_dim", dim3_json(plan.block));
+  rt.set("cluster_dim", dim3_json(plan.cluster));
   rt.set("smem_size", Json::number(plan.smem_bytes));
   rt.set("stream", Json::string("stream"));
   ctx.set("cuda_runtime_context", rt);
@@ -76,6 +77,8 @@ std::string spec_to_json(const Plan& plan, uint32_t sm_count) {
   // cannot fill the GPU (batches*heads <= CTAs, sequence <= 128); "off"; "on": whenever legal
   root.set("qkv_fusion", Json::string(plan.spec.qkv_fusion == 1 ? "off" : plan.spec.qkv_fusion == 2 ? "on" : "auto"));
   root.set("row_fusion", Json::string(plan.spec.row_fusion == 1 ? "off" : "on"));
+  root.set("l2_hints", Json::string(plan.spec.l2_hints == 2 ? "on" : "off"));
+  root.set("barrier_arrive", Json::string(plan.spec.barrier_arrive == 1 || plan.cluster > 1 ? "cta" : "warp"));
   root.set("cluster_elewise_spec", Json::object());
   root.set("cluster_reduce_spec", Json::object());
   Json gemms = Json::object();
@@ -89,7 +92,7 @@ std::string spec_to_json(const Plan& plan, uint32_t sm_count) {
     cfg.set("k_block", Json::number(64));
     cfg.set("a_stages", Json::number(kASlots));
     cfg.set("b_stages", Json::number(kBSlots));
-    cfg.set("cluster_x", Json::number(1));
+    cfg.set("cluster_x", Json::number(plan.cluster));
     cfg.set("cluster_y", Json::number(1));
     cfg.set("cta_group", Json::number(1));
     Json fus = Json::array();
@@ -161,6 +164,7 @@ std::string plan_to_json(const Plan& plan) {
   root.set("module", Json::string(plan.module_name));
   root.set("grid", Json::number(plan.grid));
   root.set("block", Json::number(plan.block));
+  root.set("cluster", Json::number(plan.cluster));
   root.set("smem_bytes", Json::number(plan.smem_bytes));
   root.set("temp_bytes", Json::number(static_cast<double>(plan.temp_bytes)));
   root.set("scratch_bytes", Json::number(static_cast<double>(plan.scratch_bytes)));
@@ -276,8 +280,13 @@ int spec_from_json(const std::string& text, TuningSpec* spec, std::string* err) 
   if (const Json* ctx = root.find("cuda_context"))
     if (const Json* rt = ctx->find("cuda_runtime_context")) {
       if (const Json* g = rt->find("grid_dim")) spec->grid = static_cast<uint32_t>(g->get_number("x", 0));
+      if (const Json* cl = rt->find("cluster_dim")) spec->cluster = static_cast<uint32_t>(cl->get_number("x", 1));
       if (const Json* b = rt->find("block_dim")) spec->block = static_cast<uint32_t>(b->get_number("x", kThreads));
     }
+  if (const Json* ba = root.find("barrier_arrive"))
+    if (ba->type == Json::String) spec->barrier_arrive = ba->str == "cta" ? 1u : 2u;
+  if (const Json* lh = root.find("l2_hints"))
+    if (lh->type == Json::String) spec->l2_hints = lh->str == "on" ? 2u : 1u;
   if (const Json* rf = root.find("row_fusion"))
     if (rf->type == Json::String) spec->row_fusion = rf->str == "off" ? 1u : 0u;
   if (const Json* qf = root.find("qkv_fusion"))

@@ -53,6 +53,8 @@ enum OpFlags : uint32_t {
   F_NO_NORM = 1u << 9,     // row op: no LayerNorm, the row sum is the result
   F_L2NORM = 1u << 10,     // row op: x / sqrt(sum x^2) instead of LayerNorm (scale and shift unused)
   F_FUSED_QKV = 1u << 11,  // attention: the item first computes its own Q, K, V = x W_h + b_h
+  F_POS_BIAS = 1u << 12,   // attention: additive f16 bias per (head, query, key), q[0] = [heads, seq, seq]
+  F_RMSNORM = 1u << 13,    // row op: x * rsqrt(mean(x^2) + eps) * scale (no mean subtraction, no shift)
 };
 
 // Pointer slots p[0..7]; meaning per kind:
@@ -67,7 +69,8 @@ enum OpFlags : uint32_t {
 //             5 bias(f16), 6/7 valid dummies; seq = tokens per batch, k_col = prefix rows
 //  PATCHIFY:  0 out(f16 [rows, cols]), 1 image(f32 NCHW); heads = C, seq = H, batches = W,
 //             head_dim = kh, q_col = kw, k_col = patches per image row, vocab = patches per image
-//  EMBED: q_col = offset added to the position index
+//  EMBED: q_col = offset added to the position index; p[4] = 0: no position table
+//  ATTENTION with F_POS_BIAS: q[0] = f16 [heads, seq, seq] added to the scaled scores (seq % 32 == 0)
 //  LAYERNORM and EMBED may also write q[2] = f32 copy of the result plus the f16 bias q[3]
 //  (residual + bias pre-loaded into the accumulator of the next split-K GEMM)
 struct alignas(16) OpDesc {
@@ -170,6 +173,11 @@ struct KernelParams {
   uint32_t timeout_us;   // bound on every wait
   uint32_t stage_begin;  // run stages [stage_begin, stage_end)
   uint32_t stage_end;
+  uint32_t cluster;      // CTAs per cluster of this launch (1: no cluster-scoped arrival)
+  uint32_t l2_hints;     // 1: weight tiles are loaded evict-first, GEMM activation tiles evict-last
+  uint32_t warp_arrive;  // 1: every epilogue warp arrives at the grid barrier for itself (8 arrivals per
+                         // CTA and stage, no CTA-wide sync before the arrival); 0: one arrival per CTA
+  uint32_t pad;
 };
 
 }  // namespace mononn

@@ -14,9 +14,11 @@
 // Dimensions searched, by tuning_level:
 //   0  none: the heuristic spec is timed and reported
 //   1  stage structure (Q/K/V projections inside the attention items or as a stage of their own;
-//      LayerNorm in the stage of its split-K GEMMs or behind a grid barrier of its own), then
+//      LayerNorm in the stage of its split-K GEMMs or behind a grid barrier of its own), L2
+//      eviction hints on the weight and activation streams, then
 //      the tile width and K split of every GEMM problem class
-//   2  + the number of CTAs of the cooperative launch (the reference's (grid, block) contexts,
+//   2  + the cluster shape (CTAs that arrive at the grid barrier through one of them) and the
+//      number of CTAs of the cooperative launch (the reference's (grid, block) contexts,
 //      mononn_engine/tuning/tuning_space_generator.cc:65-101)
 #include <algorithm>
 #include <fstream>
@@ -144,12 +146,15 @@ int tune_module(mononn_module* m, void* const* args, int n, void* stream) {
         {"qkv_fusion off", &TuningSpec::qkv_fusion, 1u},
         {"qkv_fusion on", &TuningSpec::qkv_fusion, 2u},
         {"row_fusion off", &TuningSpec::row_fusion, 1u},
+        {"l2_hints on", &TuningSpec::l2_hints, 2u},
+        {"barrier_arrive cta", &TuningSpec::barrier_arrive, 1u},
     };
     for (const Structural& c : choices) {
       if (best.*(c.field) == c.value) continue;
       TuningSpec trial = best;
       trial.*(c.field) = c.value;
-      trial.gemm.clear();  // the GEMM nodes and their CTA budgets change with the structure
+      if (c.field != &TuningSpec::l2_hints && c.field != &TuningSpec::barrier_arrive)
+        trial.gemm.clear();  // the GEMM nodes and their CTA budgets change with the structure
       double us = 0;
       rc = measure(c.name, trial, "", &us);
       if (rc == MONONN_ERR_UNSUPPORTED || rc == MONONN_ERR_INVALID_ARGUMENT) {
@@ -223,7 +228,27 @@ int tune_module(mononn_module* m, void* const* args, int n, void* stream) {
     const uint32_t sms = m->rt.sm_count();
     rc = measure("merged tiles", best, "", &best_us);
     if (rc) return rc;
+    for (uint32_t cluster : {2u, 4u}) {
+      if (best.grid % cluster != 0 || cluster == best.cluster) continue;
+      TuningSpec trial = best;
+      trial.cluster = cluster;
+      double us = 0;
+      std::ostringstream label;
+      label << "cluster " << cluster;
+      rc = measure(label.str(), trial, "", &us);
+      if (rc == MONONN_ERR_INVALID_ARGUMENT) {  // not co-resident in this shape
+        log << label.str() << ": " << get_last_error() << "\n";
+        continue;
+      }
+      if (rc) return rc;
+      log << label.str() << ": " << us << " us\n";
+      if (us < best_us) {
+        best_us = us;
+        best = trial;
+      }
+    }
     for (uint32_t grid : {sms - sms / 8, sms - sms / 4, sms / 2}) {
+      grid -= grid % std::max(1u, best.cluster);
       if (grid == 0 || grid == best.grid) continue;
       TuningSpec trial = best;
       trial.grid = grid;

@@ -763,3 +763,186 @@ def clip_hlo(cfg: ClipConfig, towers: str = "both") -> tuple[str, dict[str, str]
             + "\n".join(comps) + f"\nENTRY %{cfg.name}_main ({sig}) -> {out_shape} "
             f"{{\n" + "\n".join(entry) + "\n}\n")
     return text, names
+
+
+def t5_hlo(cfg: EncoderConfig) -> tuple[str, dict[str, str]]:
+    """HLO text of a T5-shaped encoder-decoder (model of examples/utils/save_model.py:84-92, which
+    returns the decoder's last hidden state): token gather from the shared table (no position
+    table), pre-norm blocks with RMS LayerNorm (x * rsqrt(mean(x^2) + eps) * scale), bias-free
+    projections, un-scaled attention scores plus a constant per-(head, query, key) bias -- the
+    stack's relative position bias as the compiler folds it, since the bucket arithmetic has no
+    run-time input -- causal self-attention and bias-free cross-attention over the encoder output
+    in the decoder, ReLU FFN. Inputs: input_ids, decoder_input_ids s32 [B, S]; output f16
+    [B, S, H]. The constants named *.pos_bias are [heads * S, S]
+    (mononn_b200.models.t5_device_weights makes them from the learned tables)."""
+    B, S, H, F, NH = cfg.batch, cfg.seq, cfg.hidden, cfg.ffn, cfg.heads
+    D, T, V = H // NH, cfg.batch * cfg.seq, cfg.vocab
+    comps: list[str] = [_REGIONS]
+    entry: list[str] = []
+    names: dict[str, str] = {}
+
+    def const(name: str, dims) -> str:
+        names[name] = name
+        entry.append(f"  %{name} = {_shape('f16', dims)} constant({{...}})")
+        return name
+
+    def gemm(name, a, a_shape, w, w_shape, out_shape, alpha=1.0, lhs_c=1, rhs_c=0, batch_dims=(), batch=1, ls=0, rs=0):
+        entry.append(f"  %{name} = {_shape('f16', out_shape)} custom-call({_shape('f16', a_shape)} %{a}, "
+                     f"{_shape('f16', w_shape)} %{w}), custom_call_target=\"__cublas$gemm\", "
+                     f"backend_config={_gemm_config(alpha, lhs_c, rhs_c, batch_dims, batch, ls, rs)}")
+        return name
+
+    i_BS = _shape("s32", [B, S])
+    h_TH, h_BSH, h_H, f_TH, f_T = (_shape("f16", [T, H]), _shape("f16", [B, S, H]), _shape("f16", [H]),
+                                   _shape("f32", [T, H]), _shape("f32", [T]))
+    w_s = _shape("f16", [V, H])
+    entry.append(f"  %input_ids = {i_BS} parameter(0)")
+    entry.append(f"  %decoder_input_ids = {i_BS} parameter(1)")
+    shared = const("shared", [V, H])
+    comps.append(f"""%fused_embed (p0: {i_BS}, p1: {w_s}) -> {h_TH} {{
+  %ids = {i_BS} parameter(0)
+  %word = {w_s} parameter(1)
+  %tok = {h_BSH} gather({w_s} %word, {i_BS} %ids), offset_dims={{2}}, collapsed_slice_dims={{0}}, start_index_map={{0}}, index_vector_dim=2, slice_sizes={{1,{H}}}
+  ROOT %r = {h_TH} reshape({h_BSH} %tok)
+}}
+""")
+    f_H = _shape("f32", [H])
+    comps.append(f"""%fused_rms (p0: {h_TH}, p1: {h_H}) -> {h_TH} {{
+  %x = {h_TH} parameter(0)
+  %gamma = {h_H} parameter(1)
+  %x32 = {f_TH} convert({h_TH} %x)
+  %zero = f32[] constant(0)
+  %inv_n_s = f32[] constant({1.0 / H!r})
+  %inv_n = {f_T} broadcast(f32[] %inv_n_s), dimensions={{}}
+  %eps_s = f32[] constant({cfg.eps!r})
+  %eps = {f_T} broadcast(f32[] %eps_s), dimensions={{}}
+  %sq = {f_TH} multiply({f_TH} %x32, {f_TH} %x32)
+  %sqsum = {f_T} reduce({f_TH} %sq, f32[] %zero), dimensions={{1}}, to_apply=%region_add
+  %ms = {f_T} multiply({f_T} %sqsum, {f_T} %inv_n)
+  %ms_eps = {f_T} add({f_T} %ms, {f_T} %eps)
+  %rstd = {f_T} rsqrt({f_T} %ms_eps)
+  %rstd_b = {f_TH} broadcast({f_T} %rstd), dimensions={{0}}
+  %norm = {f_TH} multiply({f_TH} %x32, {f_TH} %rstd_b)
+  %gamma32 = {f_H} convert({h_H} %gamma)
+  %gamma_b = {f_TH} broadcast({f_H} %gamma32), dimensions={{1}}
+  %scaled = {f_TH} multiply({f_TH} %norm, {f_TH} %gamma_b)
+  ROOT %out = {h_TH} convert({f_TH} %scaled)
+}}
+""")
+    h_heads, h_BShd = _shape("f16", [B, NH, S, D]), _shape("f16", [B, S, NH, D])
+    comps.append(f"""%fused_split (p0: {h_TH}) -> {h_heads} {{
+  %x = {h_TH} parameter(0)
+  %r = {h_BShd} reshape({h_TH} %x)
+  ROOT %t = {h_heads} transpose({h_BShd} %r), dimensions={{0,2,1,3}}
+}}
+""")
+    h_sc, f_sc, f_row = _shape("f16", [B, NH, S, S]), _shape("f32", [B, NH, S, S]), _shape("f32", [B, NH, S])
+    i_sc, p_sc = _shape("s32", [B, NH, S, S]), _shape("pred", [B, NH, S, S])
+    h_pb, f_pb = _shape("f16", [NH * S, S]), _shape("f32", [NH, S, S])
+    tail = f"""  %zmax = {f_row} reduce({f_sc} %z, f32[] %ninf), dimensions={{3}}, to_apply=%region_max
+  %zmax_b = {f_sc} broadcast({f_row} %zmax), dimensions={{0,1,2}}
+  %zc = {f_sc} subtract({f_sc} %z, {f_sc} %zmax_b)
+  %e = {f_sc} exponential({f_sc} %zc)
+  %zero = f32[] constant(0)
+  %esum = {f_row} reduce({f_sc} %e, f32[] %zero), dimensions={{3}}, to_apply=%region_add
+  %esum_b = {f_sc} broadcast({f_row} %esum), dimensions={{0,1,2}}
+  %p = {f_sc} divide({f_sc} %e, {f_sc} %esum_b)
+  ROOT %p16 = {h_sc} convert({f_sc} %p)
+}}
+"""
+    bias_lines = (f"  %pb = {h_pb} parameter(1)\n  %pb3 = {_shape('f16', [NH, S, S])} reshape({h_pb} %pb)\n"
+                  f"  %pb32 = {f_pb} convert({_shape('f16', [NH, S, S])} %pb3)\n"
+                  f"  %pb_b = {f_sc} broadcast({f_pb} %pb32), dimensions={{1,2,3}}\n"
+                  f"  %zb = {f_sc} add({f_sc} %z0, {f_sc} %pb_b)\n")
+    head = f"  %s = {h_sc} parameter(0)\n  %z0 = {f_sc} convert({h_sc} %s)\n  %ninf = f32[] constant(-inf)\n"
+    comps.append(f"%fused_softmax_enc (p0: {h_sc}, p1: {h_pb}) -> {h_sc} {{\n" + head + bias_lines +
+                 f"  %z = {f_sc} copy({f_sc} %zb)\n" + tail)
+    comps.append(f"%fused_softmax_dec (p0: {h_sc}, p1: {h_pb}) -> {h_sc} {{\n" + head + bias_lines +
+                 f"  %qi = {i_sc} iota(), iota_dimension=2\n  %ki = {i_sc} iota(), iota_dimension=3\n"
+                 f"  %keep = {p_sc} compare({i_sc} %qi, {i_sc} %ki), direction=GE\n"
+                 f"  %ninf_b = {f_sc} broadcast(f32[] %ninf), dimensions={{}}\n"
+                 f"  %z = {f_sc} select({p_sc} %keep, {f_sc} %zb, {f_sc} %ninf_b)\n" + tail)
+    comps.append(f"%fused_softmax_x (p0: {h_sc}) -> {h_sc} {{\n" + head + f"  %z = {f_sc} copy({f_sc} %z0)\n" + tail)
+    comps.append(f"""%fused_merge (p0: {h_heads}) -> {h_TH} {{
+  %x = {h_heads} parameter(0)
+  %t = {h_BShd} transpose({h_heads} %x), dimensions={{0,2,1,3}}
+  ROOT %r = {h_TH} reshape({h_BShd} %t)
+}}
+""")
+    comps.append(f"""%fused_resid (p0: {h_TH}, p1: {h_TH}) -> {h_TH} {{
+  %x = {h_TH} parameter(0)
+  %res = {h_TH} parameter(1)
+  ROOT %y = {h_TH} add({h_TH} %x, {h_TH} %res)
+}}
+""")
+    h_TF, f_TF = _shape("f16", [T, F]), _shape("f32", [T, F])
+    act_lines, act_name = _activation_lines(cfg.act, "y32", f_TF)
+    comps.append(f"%fused_act (p0: {h_TF}) -> {h_TF} {{\n  %x = {h_TF} parameter(0)\n"
+                 f"  %y32 = {f_TF} convert({h_TF} %x)\n" + "\n".join(act_lines) + "\n"
+                 f"  ROOT %out = {h_TF} convert({f_TF} %{act_name})\n}}\n")
+
+    def rms(tag, x, gamma_name):
+        g = const(gamma_name, [H])
+        entry.append(f"  %{tag} = {h_TH} fusion({h_TH} %{x}, {h_H} %{g}), kind=kInput, calls=%fused_rms")
+        return tag
+
+    def heads_of(tag, src, wname):
+        w = const(wname, [H, H])
+        g = gemm(f"gemm.{tag}", src, [T, H], w, [H, H], [T, H], ls=T * H, rs=H * H)
+        entry.append(f"  %fusion.{tag} = {h_heads} fusion({h_TH} %{g}), kind=kLoop, calls=%fused_split")
+        return f"fusion.{tag}"
+
+    def attention(tag, q_src, kv_src, prefix, softmax, bias):
+        q, k, v = (heads_of(f"{tag}.q", q_src, prefix + "q.w"), heads_of(f"{tag}.k", kv_src, prefix + "k.w"),
+                   heads_of(f"{tag}.v", kv_src, prefix + "v.w"))
+        sc = gemm(f"gemm.{tag}.scores", q, [B, NH, S, D], k, [B, NH, S, D], [B, NH, S, S], alpha=1.0, lhs_c=3,
+                  rhs_c=3, batch_dims=(0, 1), batch=B * NH, ls=S * D, rs=S * D)
+        ops = f"{h_sc} %{sc}" + (f", {h_pb} %{bias}" if bias else "")
+        entry.append(f"  %fusion.{tag}.softmax = {h_sc} fusion({ops}), kind=kInput, calls=%{softmax}")
+        pv = gemm(f"gemm.{tag}.pv", f"fusion.{tag}.softmax", [B, NH, S, S], v, [B, NH, S, D], [B, NH, S, D],
+                  lhs_c=3, rhs_c=2, batch_dims=(0, 1), batch=B * NH, ls=S * S, rs=S * D)
+        entry.append(f"  %fusion.{tag}.ctx = {h_TH} fusion({h_heads} %{pv}), kind=kLoop, calls=%fused_merge")
+        wo = const(prefix + "o.w", [H, H])
+        return gemm(f"gemm.{tag}.o", f"fusion.{tag}.ctx", [T, H], wo, [H, H], [T, H], ls=T * H, rs=H * H)
+
+    def resid(tag, g, x):
+        entry.append(f"  %{tag} = {h_TH} fusion({h_TH} %{g}, {h_TH} %{x}), kind=kLoop, calls=%fused_resid")
+        return tag
+
+    def ffn(tag, y, x, prefix):
+        w1, w2 = const(prefix + "ffn.up.w", [H, F]), const(prefix + "ffn.down.w", [F, H])
+        gu = gemm(f"gemm.{tag}.up", y, [T, H], w1, [H, F], [T, F], ls=T * H, rs=H * F)
+        entry.append(f"  %fusion.{tag}.act = {h_TF} fusion({h_TF} %{gu}), kind=kLoop, calls=%fused_act")
+        gd = gemm(f"gemm.{tag}.down", f"fusion.{tag}.act", [T, F], w2, [F, H], [T, H], ls=T * F, rs=F * H)
+        return resid(f"fusion.{tag}.res2", gd, x)
+
+    # ---- encoder
+    entry.append(f"  %fusion.enc.embed = {h_TH} fusion({i_BS} %input_ids, {w_s} %{shared}), kind=kLoop, calls=%fused_embed")
+    enc_pb = const("encoder.pos_bias", [NH * S, S])
+    x = "fusion.enc.embed"
+    for l in range(cfg.layers):
+        p = f"encoder.layer{l}."
+        y = rms(f"fusion.enc.ln1.{l}", x, p + "ln1.gamma")
+        x = resid(f"fusion.enc.res1.{l}", attention(f"enc.{l}", y, y, p + "attn.", "fused_softmax_enc", enc_pb), x)
+        y = rms(f"fusion.enc.ln2.{l}", x, p + "ln2.gamma")
+        x = ffn(f"enc.{l}", y, x, p)
+    enc_out = rms("fusion.enc.lnf", x, "encoder.ln.gamma")
+    # ---- decoder
+    entry.append(f"  %fusion.dec.embed = {h_TH} fusion({i_BS} %decoder_input_ids, {w_s} %{shared}), kind=kLoop, calls=%fused_embed")
+    dec_pb = const("decoder.pos_bias", [NH * S, S])
+    x = "fusion.dec.embed"
+    for l in range(cfg.layers):
+        p = f"decoder.layer{l}."
+        y = rms(f"fusion.dec.ln1.{l}", x, p + "ln1.gamma")
+        x = resid(f"fusion.dec.res1.{l}", attention(f"dec.{l}", y, y, p + "attn.", "fused_softmax_dec", dec_pb), x)
+        y = rms(f"fusion.dec.lnx.{l}", x, p + "lnx.gamma")
+        x = resid(f"fusion.dec.resx.{l}", attention(f"decx.{l}", y, enc_out, p + "xattn.", "fused_softmax_x", None), x)
+        y = rms(f"fusion.dec.ln2.{l}", x, p + "ln2.gamma")
+        x = ffn(f"dec.{l}", y, x, p)
+    dec_out = rms("fusion.dec.lnf", x, "decoder.ln.gamma")
+    out_shape = _shape("f16", [B, S, H])
+    entry.append(f"  ROOT %last_hidden_state = {out_shape} bitcast({h_TH} %{dec_out})")
+    text = (f"HloModule {cfg.name}, entry_computation_layout={{({i_BS}, {i_BS})->{out_shape}}}\n\n" + "\n".join(comps)
+            + f"\nENTRY %{cfg.name}_main (input_ids: {i_BS}, decoder_input_ids: {i_BS}) -> {out_shape} {{\n"
+            + "\n".join(entry) + "\n}\n")
+    return text, names

@@ -87,7 +87,8 @@ def make_weights(cfg, seed: int = 1234, stress: bool = False) -> dict[str, np.nd
     if isinstance(cfg, ClipConfig):
         shapes = clip_weight_shapes(cfg)
     else:
-        shapes = {"vit": vit_weight_shapes, "opt": opt_weight_shapes}.get(cfg.model, bert_weight_shapes)(cfg)
+        shapes = {"vit": vit_weight_shapes, "opt": opt_weight_shapes, "t5": t5_weight_shapes}.get(
+            cfg.model, bert_weight_shapes)(cfg)
     for name, shape in shapes.items():
         if name.endswith(".gamma"):
             w = np.ones(shape, np.float32)
@@ -195,6 +196,88 @@ def opt_weight_shapes(cfg: EncoderConfig) -> dict[str, tuple[int, ...]]:
     shapes["ln.gamma"] = (h,)
     shapes["ln.beta"] = (h,)
     return shapes
+
+
+# ---------------------------------------------------------------------------- T5
+T5_BUCKETS, T5_MAX_DISTANCE = 32, 128
+
+
+def t5_small(batch: int = 1, seq: int = 128) -> EncoderConfig:
+    """T5-small-shaped encoder-decoder (examples/utils/save_model.py:84-92, 107-110): 6 + 6
+    layers, width 512, 8 heads of 64, ReLU FFN 2048, no biases, RMS LayerNorm, relative position
+    bias shared by the layers of a stack; `seq` is both the encoder and the decoder length."""
+    return EncoderConfig(model="t5", layers=6, hidden=512, heads=8, ffn=2048, vocab=32128, max_pos=0, types=0,
+                         batch=batch, seq=seq, eps=1e-6, act="relu")
+
+
+def t5_tiny(batch: int = 1, seq: int = 32, layers: int = 1, hidden: int = 64, ffn: int = 128,
+            vocab: int = 96) -> EncoderConfig:
+    return EncoderConfig(model="t5", layers=layers, hidden=hidden, heads=hidden // 64, ffn=ffn, vocab=vocab,
+                         max_pos=0, types=0, batch=batch, seq=seq, eps=1e-6, act="relu")
+
+
+def t5_weight_shapes(cfg: EncoderConfig) -> dict[str, tuple[int, ...]]:
+    h, f = cfg.hidden, cfg.ffn
+    shapes: dict[str, tuple[int, ...]] = {"shared": (cfg.vocab, h)}
+    for stack in ("encoder", "decoder"):
+        shapes[f"{stack}.rel_bias"] = (T5_BUCKETS, cfg.heads)   # the learned table; not a device constant
+        for l in range(cfg.layers):
+            p = f"{stack}.layer{l}."
+            shapes[p + "ln1.gamma"] = (h,)
+            for n in ("q", "k", "v", "o"):
+                shapes[p + f"attn.{n}.w"] = (h, h)
+            if stack == "decoder":
+                shapes[p + "lnx.gamma"] = (h,)
+                for n in ("q", "k", "v", "o"):
+                    shapes[p + f"xattn.{n}.w"] = (h, h)
+            shapes[p + "ln2.gamma"] = (h,)
+            shapes[p + "ffn.up.w"] = (h, f)
+            shapes[p + "ffn.down.w"] = (f, h)
+        shapes[f"{stack}.ln.gamma"] = (h,)
+    return shapes
+
+
+def t5_relative_buckets(seq_q: int, seq_k: int, bidirectional: bool) -> np.ndarray:
+    """Bucket index [seq_q, seq_k] of the relative position key - query, as T5 defines it: half
+    of the buckets (of each sign when bidirectional) hold exact distances, the other half
+    logarithmically growing ranges up to T5_MAX_DISTANCE, beyond which everything shares the
+    last bucket; a causal stack only distinguishes keys at or before the query."""
+    rel = np.arange(seq_k)[None, :] - np.arange(seq_q)[:, None]
+    n = T5_BUCKETS
+    out = np.zeros_like(rel)
+    if bidirectional:
+        n //= 2
+        out += (rel > 0).astype(rel.dtype) * n
+        dist = np.abs(rel)
+    else:
+        dist = -np.minimum(rel, 0)
+    exact = n // 2
+    big = exact + (np.log(np.maximum(dist, 1).astype(np.float32) / exact) / np.log(T5_MAX_DISTANCE / exact)
+                   * (n - exact)).astype(rel.dtype)
+    big = np.minimum(big, n - 1)
+    return out + np.where(dist < exact, dist, big)
+
+
+def t5_position_bias(table: np.ndarray, seq_q: int, seq_k: int, bidirectional: bool) -> np.ndarray:
+    """[heads, seq_q, seq_k] additive attention bias gathered from the [buckets, heads] table."""
+    return np.ascontiguousarray(table[t5_relative_buckets(seq_q, seq_k, bidirectional)].transpose(2, 0, 1))
+
+
+def t5_device_weights(cfg: EncoderConfig, w: dict[str, np.ndarray]) -> dict[str, np.ndarray]:
+    """The constants of the T5 HLO module: every weight, with each stack's relative-position
+    table replaced by the [heads * seq, seq] bias tensor a compiler folds it into (the table,
+    the bucket arithmetic and the gather involve no run-time input)."""
+    out = {k: v for k, v in w.items() if not k.endswith(".rel_bias")}
+    s = cfg.seq
+    out["encoder.pos_bias"] = t5_position_bias(w["encoder.rel_bias"], s, s, True).reshape(cfg.heads * s, s)
+    out["decoder.pos_bias"] = t5_position_bias(w["decoder.rel_bias"], s, s, False).reshape(cfg.heads * s, s)
+    return out
+
+
+def make_t5_inputs(cfg: EncoderConfig, seed: int = 1234) -> dict[str, np.ndarray]:
+    rng = np.random.default_rng(seed + 7919)
+    return {"input_ids": rng.integers(0, cfg.vocab, (cfg.batch, cfg.seq), dtype=np.int32),
+            "decoder_input_ids": rng.integers(0, cfg.vocab, (cfg.batch, cfg.seq), dtype=np.int32)}
 
 
 @dataclasses.dataclass

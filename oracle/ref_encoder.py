@@ -311,3 +311,58 @@ def clip_dual(cfg, w, inputs):
     txt = txt / np.linalg.norm(txt, axis=-1, keepdims=True)
     logits = (cfg.logit_scale * img @ txt.T).astype(np.float32)
     return logits, img.astype(np.float32), txt.astype(np.float32)
+
+
+# ------------------------------------------------------------------------------------ T5
+def rms_norm(x: np.ndarray, gamma: np.ndarray, eps: float) -> np.ndarray:
+    """T5's LayerNorm: x / sqrt(mean(x^2) + eps) * scale, no mean subtraction and no shift."""
+    return (x / np.sqrt((x * x).mean(-1, keepdims=True) + eps) * gamma).astype(np.float32)
+
+
+def _t5_attention(q, k, v, heads, bias, causal):
+    """Un-scaled scores + per-(head, query, key) bias; q [B, Sq, H], k / v [B, Sk, H]."""
+    b, sq, h = q.shape
+    sk, d = k.shape[1], h // heads
+    qh = q.reshape(b, sq, heads, d).transpose(0, 2, 1, 3)
+    kh = k.reshape(b, sk, heads, d).transpose(0, 2, 1, 3)
+    vh = v.reshape(b, sk, heads, d).transpose(0, 2, 1, 3)
+    scores = np.matmul(qh, kh.transpose(0, 1, 3, 2))
+    if bias is not None:
+        scores = scores + bias[None]
+    if causal:
+        scores = scores + np.triu(np.full((sq, sk), -1e30, np.float32), 1)
+    return np.matmul(softmax_rows(scores), vh).transpose(0, 2, 1, 3).reshape(b, sq, h)
+
+
+def t5_model(cfg, w, inputs):
+    """fp32 forward of the T5 encoder-decoder (the model of examples/utils/save_model.py:84-92,
+    which returns the decoder's last hidden state): shared token table, pre-norm blocks with RMS
+    LayerNorm, bias-free projections, un-scaled attention scores plus the relative position bias
+    of the stack (bidirectional buckets in the encoder, causal ones in the decoder, none in
+    cross-attention), ReLU FFN. Returns [B * S, H]."""
+    from mononn_b200.models import t5_position_bias
+    b, s_, h = cfg.batch, cfg.seq, cfg.hidden
+    lin = lambda t, name: t @ w[name + ".w"]
+    enc_bias = t5_position_bias(w["encoder.rel_bias"], s_, s_, True)
+    dec_bias = t5_position_bias(w["decoder.rel_bias"], s_, s_, False)
+    x = w["shared"][inputs["input_ids"]].astype(np.float32)
+    for l in range(cfg.layers):
+        p = f"encoder.layer{l}."
+        y = rms_norm(x, w[p + "ln1.gamma"], cfg.eps)
+        ctx = _t5_attention(lin(y, p + "attn.q"), lin(y, p + "attn.k"), lin(y, p + "attn.v"), cfg.heads, enc_bias, False)
+        x = x + lin(ctx, p + "attn.o")
+        y = rms_norm(x, w[p + "ln2.gamma"], cfg.eps)
+        x = x + lin(activation(lin(y, p + "ffn.up"), cfg.act), p + "ffn.down")
+    enc = rms_norm(x, w["encoder.ln.gamma"], cfg.eps)
+    x = w["shared"][inputs["decoder_input_ids"]].astype(np.float32)
+    for l in range(cfg.layers):
+        p = f"decoder.layer{l}."
+        y = rms_norm(x, w[p + "ln1.gamma"], cfg.eps)
+        ctx = _t5_attention(lin(y, p + "attn.q"), lin(y, p + "attn.k"), lin(y, p + "attn.v"), cfg.heads, dec_bias, True)
+        x = x + lin(ctx, p + "attn.o")
+        y = rms_norm(x, w[p + "lnx.gamma"], cfg.eps)
+        ctx = _t5_attention(lin(y, p + "xattn.q"), lin(enc, p + "xattn.k"), lin(enc, p + "xattn.v"), cfg.heads, None, False)
+        x = x + lin(ctx, p + "xattn.o")
+        y = rms_norm(x, w[p + "ln2.gamma"], cfg.eps)
+        x = x + lin(activation(lin(y, p + "ffn.up"), cfg.act), p + "ffn.down")
+    return rms_norm(x, w["decoder.ln.gamma"], cfg.eps).reshape(b * s_, h)

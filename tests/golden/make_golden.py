@@ -17,7 +17,7 @@ import torch
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 sys.path.insert(0, ROOT)
 from mononn_b200.models import (ClipConfig, EncoderConfig, clip_tiny, make_clip_inputs, make_inputs,  # noqa: E402
-                                make_vit_inputs, make_weights)
+                                make_t5_inputs, make_vit_inputs, make_weights)
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
@@ -168,6 +168,40 @@ def hf_clip_forward(cfg, w: dict, inputs: dict) -> np.ndarray:
     return out.logits_per_image.numpy()
 
 
+def hf_t5_forward(cfg: EncoderConfig, w: dict, inputs: dict) -> np.ndarray:
+    from transformers import T5Config, T5Model
+    hc = T5Config(vocab_size=cfg.vocab, d_model=cfg.hidden, d_kv=cfg.hidden // cfg.heads, d_ff=cfg.ffn,
+                  num_layers=cfg.layers, num_decoder_layers=cfg.layers, num_heads=cfg.heads,
+                  relative_attention_num_buckets=32, relative_attention_max_distance=128, dropout_rate=0.0,
+                  layer_norm_epsilon=cfg.eps, feed_forward_proj="relu", tie_word_embeddings=True)
+    model = T5Model(hc).eval()
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a))
+    sd = {"shared.weight": t(w["shared"]), "encoder.embed_tokens.weight": t(w["shared"]),
+          "decoder.embed_tokens.weight": t(w["shared"])}
+    for stack in ("encoder", "decoder"):
+        sd[f"{stack}.block.0.layer.0.SelfAttention.relative_attention_bias.weight"] = t(w[f"{stack}.rel_bias"])
+        sd[f"{stack}.final_layer_norm.weight"] = t(w[f"{stack}.ln.gamma"])
+        for l in range(cfg.layers):
+            p, q = f"{stack}.layer{l}.", f"{stack}.block.{l}.layer."
+            ff = 1 if stack == "encoder" else 2
+            for n in ("q", "k", "v", "o"):
+                sd[f"{q}0.SelfAttention.{n}.weight"] = t(w[p + f"attn.{n}.w"].T)
+                if stack == "decoder":
+                    sd[f"{q}1.EncDecAttention.{n}.weight"] = t(w[p + f"xattn.{n}.w"].T)
+            sd[f"{q}0.layer_norm.weight"] = t(w[p + "ln1.gamma"])
+            if stack == "decoder":
+                sd[f"{q}1.layer_norm.weight"] = t(w[p + "lnx.gamma"])
+            sd[f"{q}{ff}.layer_norm.weight"] = t(w[p + "ln2.gamma"])
+            sd[f"{q}{ff}.DenseReluDense.wi.weight"] = t(w[p + "ffn.up.w"].T)
+            sd[f"{q}{ff}.DenseReluDense.wo.weight"] = t(w[p + "ffn.down.w"].T)
+    missing, unexpected = model.load_state_dict(sd, strict=False)
+    assert not missing and not unexpected, (missing, unexpected)
+    with torch.no_grad():
+        out = model(input_ids=torch.from_numpy(inputs["input_ids"]).long(),
+                    decoder_input_ids=torch.from_numpy(inputs["decoder_input_ids"]).long()).last_hidden_state
+    return out.reshape(cfg.batch * cfg.seq, cfg.hidden).numpy()
+
+
 CASES = {
     # name: (config, weight seed, stress, pad_fraction)
     "bert_tiny_b1_s16": (EncoderConfig(layers=2, hidden=64, heads=1, ffn=256, vocab=100, max_pos=64,
@@ -180,6 +214,8 @@ CASES = {
     "opt_tiny_b2_s24": (EncoderConfig(model="opt", layers=2, hidden=128, heads=2, ffn=256, vocab=160, max_pos=64,
                                       types=0, batch=2, seq=24, eps=1e-5, act="relu"), 14, True, 0.0),
     "clip_tiny_i3_t5": (clip_tiny(images=3, texts=5, layers=2), 15, True, 0.0),
+    "t5_tiny_b2_s32": (EncoderConfig(model="t5", layers=2, hidden=128, heads=2, ffn=256, vocab=96, max_pos=0,
+                                     types=0, batch=2, seq=32, eps=1e-6, act="relu"), 16, True, 0.0),
 }
 
 
@@ -192,6 +228,9 @@ def main():
         elif isinstance(cfg, ClipConfig):
             inp = make_clip_inputs(cfg, seed)
             out = hf_clip_forward(cfg, w, inp)  # logits_per_image; stored under the common key
+        elif cfg.model == "t5":
+            inp = make_t5_inputs(cfg, seed)
+            out = hf_t5_forward(cfg, w, inp)  # the decoder's last hidden state
         elif cfg.model == "opt":
             inp = make_inputs(cfg, seed)
             out = hf_opt_forward(cfg, w, inp)  # logits; stored under the common key

@@ -4,7 +4,8 @@ import pytest
 
 from mononn_b200 import (bert_base, bert_tiny, clip_b32, clip_tiny, compile_encoder, compile_hlo, make_clip_inputs,
                          make_inputs, make_vit_inputs, make_weights, opt_tiny, vit_base, vit_tiny)
-from mononn_b200.hlo_builder import bert_hlo, clip_hlo, opt_hlo, vit_hlo
+from mononn_b200 import make_t5_inputs, t5_device_weights, t5_small, t5_tiny
+from mononn_b200.hlo_builder import bert_hlo, clip_hlo, opt_hlo, t5_hlo, vit_hlo
 from mononn_b200.models import EncoderConfig
 from oracle import ref_encoder as R
 from tests.helpers import assert_parity, golden_cases, load_golden, reference_fixture_inputs
@@ -39,6 +40,8 @@ def test_golden_vectors(name, frontend):
         got = run_vit(cfg, w, make_vit_inputs(cfg, seed))
     elif cfg.model == "clip":
         got = run_clip(cfg, w, make_clip_inputs(cfg, seed))[0]
+    elif cfg.model == "t5":
+        got = run_t5(cfg, w, make_t5_inputs(cfg, seed))
     elif cfg.model == "opt":
         got, ids = run_opt(cfg, w, make_inputs(cfg, seed))
         check_argmax(got, ids, load_golden(name)["last_hidden_state"])
@@ -48,6 +51,39 @@ def test_golden_vectors(name, frontend):
         got = run_module(mod, cfg, inp)
         mod.close()
     assert_parity(got, load_golden(name)["last_hidden_state"], name)
+
+
+def run_t5(cfg, w, inp):
+    """Decoder last hidden state [tokens, hidden] of the encoder-decoder, one launch."""
+    text, names = t5_hlo(cfg)
+    mod = compile_hlo(text, barrier_timeout_us=1000000)
+    dw = t5_device_weights(cfg, w)
+    mod.set_weights({names[k]: v for k, v in dw.items()})
+    out = mod.run([inp["input_ids"], inp["decoder_input_ids"]])[0]
+    mod.close()
+    return out[: cfg.tokens * cfg.hidden].reshape(cfg.tokens, cfg.hidden).astype(np.float32)
+
+
+@pytest.mark.parametrize("cfg", [
+    t5_tiny(),                                                 # one layer per stack, one head, 32 tokens
+    t5_tiny(batch=3, seq=64, layers=2, hidden=128, ffn=256),   # ragged rows (192), two heads
+    t5_tiny(batch=1, seq=128, layers=1, hidden=192, ffn=384),  # a full 128-row tile, three heads
+], ids=lambda c: f"b{c.batch}s{c.seq}h{c.hidden}l{c.layers}")
+def test_t5_shapes_against_oracle(cfg):
+    """Encoder-decoder: RMS LayerNorm, un-scaled scores with a per-(head, query, key) position
+    bias (bidirectional in the encoder, causal in the decoder), cross-attention over the encoder
+    output, bias-free projections; both stacks share stages until the decoder needs the encoder."""
+    w = make_weights(cfg, 61, stress=True)
+    inp = make_t5_inputs(cfg, 61)
+    assert_parity(run_t5(cfg, w, inp), R.t5_model(cfg, w, inp), "T5 shape case")
+
+
+def test_t5_small_full_size():
+    """T5-small shape (6 + 6 layers, width 512, 8 heads, FFN 2048, vocab 32128), batch 1, 128 tokens."""
+    cfg = t5_small()
+    w = make_weights(cfg, 1239, stress=True)
+    inp = make_t5_inputs(cfg, 1239)
+    assert_parity(run_t5(cfg, w, inp), R.t5_model(cfg, w, inp), "T5-small b1 s128")
 
 
 def run_vit(cfg, w, inp):

@@ -217,3 +217,30 @@ def test_mma_issue_probe_reports_cycles_per_instruction():
     assert table[16] <= table[256] * 1.1
     with pytest.raises(capi.MononnError):
         capi.check(l.mononn_debug_mma_issue(0, 24, 256, 1, 0, 1, None, None, None))
+
+
+@pytest.mark.parametrize("cluster", [2, 4])
+def test_cluster_scoped_barrier_arrival_keeps_parity(cluster, tmp_path):
+    """Launched as thread-block clusters, the CTAs of a cluster arrive at the grid barrier through
+    an mbarrier in the first CTA's shared memory and only that CTA touches the global counter.
+    Same results; a shape that cannot be co-resident is refused when the plan is loaded."""
+    from mononn_b200.module import describe
+    cfg, w, inp = small()
+    text, names = bert_hlo(cfg)
+    spec = describe("hlo", text)["spec"]
+    spec["cuda_context"]["cuda_runtime_context"]["cluster_dim"] = {"x": cluster, "y": 1, "z": 1}
+    (tmp_path / "cluster_0").mkdir()
+    (tmp_path / "cluster_0" / "best_tuning_spec.json").write_text(json.dumps(spec))
+    try:
+        mod = compile_hlo(text, spec_dir=str(tmp_path), barrier_timeout_us=500000)
+    except capi.MononnError as e:
+        assert e.code == -1 and "co-resident" in str(e)
+        pytest.skip(str(e))
+    assert mod.plan()["cluster"] == cluster
+    mod.set_weights({names[k]: v for k, v in w.items()})
+    assert_parity(run(mod, cfg, inp), R.bert_encoder(cfg, w, inp), f"clusters of {cluster}")
+    for _ in range(3):
+        mod.launch()
+    mod.status()
+    assert_parity(run(mod, cfg, inp), R.bert_encoder(cfg, w, inp), f"clusters of {cluster}, relaunched")
+    mod.close()

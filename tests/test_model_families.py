@@ -148,3 +148,31 @@ def test_full_size_dual_encoder_cost(lib_built):
     assert abs(plan["algorithmic_flops"] / 1e9 - 472.87) < 5.0
     # every weight once, gathered token rows, the f32 pixels (19.27 MB) and the outputs
     assert abs(plan["algorithmic_bytes"] / 1e6 - 273.8) < 1.0
+
+
+def test_encoder_decoder_structure(lib_built):
+    """T5: two token gathers without a position table, RMS LayerNorm everywhere, a position bias
+    on self-attention only, decoder self-attention causal; the cross-attention K / V projections
+    of all layers depend on the encoder output alone and are spread over stages of at most
+    eight operators."""
+    from mononn_b200.hlo_builder import t5_hlo
+    from mononn_b200.models import t5_small, t5_tiny
+    cfg = t5_tiny(batch=2, seq=32, layers=2, hidden=128, ffn=256)
+    plan = plan_of(t5_hlo(cfg)[0])
+    assert [a["name"] for a in plan["args"]] == ["input_ids", "decoder_input_ids", "last_hidden_state", "temp_buffer"]
+    embed = ops_of(plan, "embed")
+    assert len(embed) == 2 and all(o["p"][4]["space"] == "none" for o in embed)      # no position table
+    F_POS_BIAS, F_RMSNORM = 1 << 12, 1 << 13
+    ln = ops_of(plan, "layernorm")
+    assert len(ln) == 2 * cfg.layers + 1 + 3 * cfg.layers + 1 and all(o["flags"] & F_RMSNORM for o in ln)
+    att = ops_of(plan, "attention")
+    assert len(att) == 3 * cfg.layers
+    assert sum(1 for o in att if o["flags"] & F_POS_BIAS) == 2 * cfg.layers            # not on cross-attention
+    assert sum(1 for o in att if o["flags"] & F_CAUSAL) == cfg.layers                  # decoder self-attention
+    assert all(bool(o["flags"] & F_CAUSAL) <= bool(o["flags"] & F_POS_BIAS) for o in att)
+    full = plan_of(t5_hlo(t5_small())[0])
+    assert all(len(st["ops"]) <= 8 for st in full["stages"])
+    kv = [i for i, st in enumerate(full["stages"]) for o in st["ops"] if o["name"].startswith("gemm_decx_") and
+          o["name"].endswith(("_k", "_v"))]
+    assert len(kv) == 12 and len(set(kv)) >= 2     # twelve projections, more than one stage
+    assert abs(full["algorithmic_flops"] / 1e9 - 11.88) < 0.1

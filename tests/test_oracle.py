@@ -18,6 +18,9 @@ def test_oracle_matches_golden_vectors(name):
     elif cfg.model == "clip":
         out, img, txt = R.clip_dual(cfg, w, make_clip_inputs(cfg, seed))
         assert np.allclose(np.linalg.norm(img, axis=-1), 1.0, atol=1e-5)
+    elif cfg.model == "t5":
+        from mononn_b200.models import make_t5_inputs
+        out = R.t5_model(cfg, w, make_t5_inputs(cfg, seed))
     elif cfg.model == "opt":
         out, ids = R.opt_decoder(cfg, w, make_inputs(cfg, seed))
         assert np.array_equal(ids, g["last_hidden_state"].argmax(-1))  # the stored array holds the logits
