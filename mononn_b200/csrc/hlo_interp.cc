@@ -258,6 +258,58 @@ int eval_computation(const HloModule& m, const HloComputation& comp,
         for (size_t k = 0; k < start.size(); ++k) src += ((i / os[k]) % r.dims[k] + start[k]) * as[k];
         r.v[i] = a.v[src];
       }
+    } else if (op == "pad") {
+      // padding=lo_hi[_interior] per dimension joined by 'x'; no interior padding and no negative
+      // edges (mononn_engine/parser/ir_parser_fused.cc:1143-1151); out-of-range reads give the
+      // pad value (index_tracer.cc:368-401)
+      if (!need(2) || A(1).size() != 1) return unsupported(err, ins, "expects an operand and a scalar pad value");
+      const std::string ps = ins.attr("padding");
+      std::vector<int64_t> lo;
+      size_t p = 0;
+      while (p < ps.size()) {
+        const size_t e = ps.find('x', p);
+        const std::string part = ps.substr(p, e == std::string::npos ? std::string::npos : e - p);
+        char* q = nullptr;
+        const long long l = std::strtoll(part.c_str(), &q, 10);
+        const long long h = (q && *q == '_') ? std::strtoll(q + 1, &q, 10) : 0;
+        const long long in = (q && *q == '_') ? std::strtoll(q + 1, &q, 10) : 0;
+        if (l < 0 || h < 0 || in != 0) return unsupported(err, ins, "interior or negative padding");
+        lo.push_back(l);
+        if (e == std::string::npos) break;
+        p = e + 1;
+      }
+      const HTensor& a = A(0);
+      if (lo.size() != a.dims.size() || r.dims.size() != a.dims.size()) return unsupported(err, ins, "pad rank mismatch");
+      const auto os = strides_of(r.dims), as = strides_of(a.dims);
+      r.v.assign(static_cast<size_t>(n), A(1).v[0]);
+      for (int64_t i = 0; i < a.size(); ++i) {
+        int64_t dst = 0;
+        for (size_t k = 0; k < a.dims.size(); ++k) dst += ((i / as[k]) % a.dims[k] + lo[k]) * os[k];
+        if (dst >= n) return unsupported(err, ins, "padded extent smaller than the operand");
+        r.v[dst] = a.v[i];
+      }
+    } else if (op == "dynamic-slice") {
+      // operand, then one scalar start index per dimension, clamped to [0, dim - size]
+      // (mononn_engine/core/context/index_tracer.cc:142-148)
+      if (ins.operands.empty()) return unsupported(err, ins, "expects operands");
+      const HTensor& a = A(0);
+      const auto sizes = ins.int_list("dynamic_slice_sizes");
+      if (ins.operands.size() != 1 + a.dims.size() || sizes.size() != a.dims.size() || r.dims.size() != a.dims.size())
+        return unsupported(err, ins, "one start index per dimension is expected");
+      std::vector<int64_t> start(a.dims.size());
+      for (size_t k = 0; k < a.dims.size(); ++k) {
+        if (A(static_cast<int>(k) + 1).size() != 1 || sizes[k] != r.dims[k] || sizes[k] > a.dims[k])
+          return unsupported(err, ins, "start indices must be scalars and sizes must match the result");
+        const int64_t st = static_cast<int64_t>(A(static_cast<int>(k) + 1).v[0]);
+        start[k] = std::min(std::max<int64_t>(st, 0), a.dims[k] - sizes[k]);
+      }
+      const auto os = strides_of(r.dims), as = strides_of(a.dims);
+      r.v.resize(static_cast<size_t>(n));
+      for (int64_t i = 0; i < n; ++i) {
+        int64_t src = 0;
+        for (size_t k = 0; k < start.size(); ++k) src += ((i / os[k]) % r.dims[k] + start[k]) * as[k];
+        r.v[i] = a.v[src];
+      }
     } else if (op == "gather") {
       // Row lookup only (embedding): operand [V, H], indices [...] ->  [..., H]; the gathered
       // index is not clamped (mononn_engine/core/context/index_tracer.cc:235-280).

@@ -126,7 +126,7 @@ class Lowering {
     for (size_t idx = 0; idx < e_.instrs.size(); ++idx) {
       const HloInstr& ins = e_.instrs[idx];
       int rc = MONONN_OK;
-      if (ins.opcode == "parameter") continue;
+      if (ins.opcode == "parameter" || ins.opcode == "split-fusion") continue;
       if (ins.opcode == "constant") {
         Val v;
         v.kind = Val::CONST;
@@ -369,7 +369,7 @@ class Lowering {
     if (!c) return fail(MONONN_ERR_PARSE, "%" + ins.name + ": fused computation " + ins.attr("calls") + " not found");
     if (c->params.size() != ins.operands.size())
       return fail(MONONN_ERR_PARSE, "%" + ins.name + ": operand count does not match " + c->name);
-    if (ins.shape.is_tuple()) return unsupported(ins, "multi-output fusion");
+    if (ins.shape.is_tuple()) return unsupported(ins, "multi-output fusion that is not read through get-tuple-element");
     bool has_reduce = false, has_gather = false;
     for (const HloInstr& i : c->instrs) {
       has_reduce = has_reduce || i.opcode == "reduce";
@@ -1569,9 +1569,102 @@ class Lowering {
 
 }  // namespace
 
+// A multi-output fusion returns a tuple that the entry computation takes apart with
+// get-tuple-element (the reference names those pointers get_tuple_element_<cluster>_<i>,
+// mononn_engine/parser/ir_parser_fused.cc:447-455, codegen/graph_codegen.cc:491-543). Each
+// element is a function of some of the fusion's operands: the fusion is split into one
+// single-output fusion per element (the instructions its root reaches, parameters renumbered),
+// every get-tuple-element becomes that fusion, and the tuple-valued instruction is left without
+// operands or users. What shares work between the elements in the original is recomputed, which
+// is free here: the pieces end up as epilogues of different GEMMs or as separate row ops anyway.
+static int split_multi_output_fusions(HloModule* m, std::string* err) {
+  HloComputation& entry = m->comps[m->entry];
+  const size_t n_entry = entry.instrs.size();
+  for (size_t fi = 0; fi < n_entry; ++fi) {
+    if (entry.instrs[fi].opcode != "fusion" || !entry.instrs[fi].shape.is_tuple()) continue;
+    const HloComputation* cp = m->find(entry.instrs[fi].attr("calls"));
+    if (!cp || cp->root < 0 || cp->instrs[cp->root].opcode != "tuple") {
+      if (err) *err = "%" + entry.instrs[fi].name + ": a tuple-shaped fusion must end in a tuple instruction";
+      return MONONN_ERR_UNSUPPORTED;
+    }
+    const HloComputation base = *cp;  // (m->comps grows below)
+    const std::vector<int> elems = base.instrs[base.root].operands;
+    bool used_whole = false;
+    for (size_t gi = 0; gi < n_entry; ++gi) {
+      HloInstr& g = entry.instrs[gi];
+      bool reads = false;
+      for (int o : g.operands) reads = reads || o == static_cast<int>(fi);
+      if (!reads) continue;
+      const auto idx = g.int_list("index");
+      if (g.opcode != "get-tuple-element" || g.operands.size() != 1 || idx.size() != 1 || idx[0] < 0 ||
+          idx[0] >= static_cast<int64_t>(elems.size())) {
+        used_whole = true;
+        continue;
+      }
+      const int root = elems[idx[0]];
+      std::vector<char> keep(base.instrs.size(), 0);
+      std::vector<int> stack{root};
+      while (!stack.empty()) {
+        const int i = stack.back();
+        stack.pop_back();
+        if (keep[i]) continue;
+        keep[i] = 1;
+        for (int o : base.instrs[i].operands) stack.push_back(o);
+      }
+      HloComputation sub;
+      sub.name = base.name + "_out" + std::to_string(idx[0]);
+      std::vector<int> remap(base.instrs.size(), -1);
+      std::vector<int> new_operands;
+      for (size_t pn = 0; pn < base.params.size(); ++pn) {  // parameters in ascending number, renumbered
+        const int pi = base.params[pn];
+        if (pi < 0 || !keep[pi]) continue;
+        new_operands.push_back(entry.instrs[fi].operands[pn]);
+      }
+      int next_param = 0;
+      std::map<int64_t, int64_t> renum;
+      for (size_t pn = 0; pn < base.params.size(); ++pn)
+        if (base.params[pn] >= 0 && keep[base.params[pn]]) renum[static_cast<int64_t>(pn)] = next_param++;
+      for (size_t i = 0; i < base.instrs.size(); ++i) {
+        if (!keep[i]) continue;
+        HloInstr c = base.instrs[i];
+        for (int& o : c.operands) o = remap[o];
+        c.is_root = static_cast<int>(i) == root;
+        if (c.opcode == "parameter") c.param_number = renum[c.param_number];
+        remap[i] = static_cast<int>(sub.instrs.size());
+        sub.index[c.name] = remap[i];
+        sub.instrs.push_back(c);
+      }
+      sub.root = remap[root];
+      sub.params.assign(static_cast<size_t>(next_param), -1);
+      for (size_t i = 0; i < sub.instrs.size(); ++i)
+        if (sub.instrs[i].opcode == "parameter") sub.params[static_cast<size_t>(sub.instrs[i].param_number)] = static_cast<int>(i);
+      m->comp_index[sub.name] = static_cast<int>(m->comps.size());
+      m->comps.push_back(sub);
+      HloComputation& e2 = m->comps[m->entry];  // (the vector may have moved)
+      HloInstr& g2 = e2.instrs[gi];
+      g2.opcode = "fusion";
+      g2.operands = new_operands;
+      g2.attrs.erase("index");
+      g2.attrs["calls"] = "%" + sub.name;
+      g2.attrs["kind"] = e2.instrs[fi].attr("kind");
+    }
+    HloComputation& e2 = m->comps[m->entry];
+    if (used_whole) {
+      if (err) *err = "%" + e2.instrs[fi].name + ": a multi-output fusion may only be read through get-tuple-element";
+      return MONONN_ERR_UNSUPPORTED;
+    }
+    e2.instrs[fi].opcode = "split-fusion";  // no operands, no users: skipped by the lowering
+    e2.instrs[fi].operands.clear();
+    return split_multi_output_fusions(m, err);  // references were invalidated: start over for the next one
+  }
+  return MONONN_OK;
+}
+
 int hlo_text_to_fgraph(const std::string& text, FGraph* graph, std::string* err) {
   HloModule m;
   int rc = parse_hlo_text(text, &m, err);
+  if (rc) return rc;
+  rc = split_multi_output_fusions(&m, err);
   if (rc) return rc;
   Lowering l(m, graph, err);
   return l.run();
