@@ -437,9 +437,9 @@ def run_config(args):
     time by CUDA events with an L2 flush between launches, against the slower of algorithmic
     bytes at the measured HBM peak and FLOPs at the measured dense tensor peak."""
     import torch
-    from mononn_b200 import (clip_b32, compile_hlo, make_clip_inputs, make_inputs, make_vit_inputs,
-                             make_weights, opt_1p3b, vit_base)
-    from mononn_b200.hlo_builder import bert_hlo, clip_hlo, opt_hlo, vit_hlo
+    from mononn_b200 import (clip_b32, compile_hlo, make_clip_inputs, make_inputs, make_t5_inputs, make_vit_inputs,
+                             make_weights, opt_1p3b, t5_device_weights, t5_small, vit_base)
+    from mononn_b200.hlo_builder import bert_hlo, clip_hlo, opt_hlo, t5_hlo, vit_hlo
     from mononn_b200.models import EncoderConfig
     torch.cuda.set_device(0)
     name = args.config
@@ -449,9 +449,12 @@ def run_config(args):
         "vit_b1": (vit_base(1), vit_hlo, 1236, "vit"), "vit_b64": (vit_base(64), vit_hlo, 1236, "vit"),
         "opt_b1": (opt_1p3b(1), opt_hlo, 1237, "opt"), "opt_b8": (opt_1p3b(8), opt_hlo, 1237, "opt"),
         "clip": (clip_b32(), clip_hlo, 1238, "clip"),
+        "t5_small": (t5_small(1), t5_hlo, 1239, "t5"),
     }
     cfg, hlo, seed, family = table[name]
     w = make_weights(cfg, seed)
+    if family == "t5":
+        w = t5_device_weights(cfg, w)
     text, names = hlo(cfg)
     mod = compile_hlo(text, device=0, barrier_timeout_us=2000000)
     mod.set_weights({names[k]: v for k, v in w.items()})
@@ -462,6 +465,9 @@ def run_config(args):
         ins = [make_vit_inputs(cfg, seed)["pixel_values"]]
     elif family == "opt":
         ins = [make_inputs(cfg, seed)["input_ids"]]
+    elif family == "t5":
+        inp = make_t5_inputs(cfg, seed)
+        ins = [inp["input_ids"], inp["decoder_input_ids"]]
     else:
         inp = make_clip_inputs(cfg, seed)
         ins = [inp["pixel_values"], inp["input_ids"]]
@@ -496,6 +502,24 @@ def run_config(args):
                       "bound": "hbm" if t_hbm >= t_tc else "tensor", "frac": max(t_hbm, t_tc) / us,
                       "peaks": {"hbm_gbs": peak_gbs, "tensor_tflops": peak_tf, "source": kind}}))
     mod.close()
+
+
+def run_mma_probe(args):
+    """Not a bench line: the issue-cost table of tcgen05.mma (128 x N x 16, f16 in, f32 accumulate)
+    from operands resident in shared memory, one issuing thread per CTA on every SM."""
+    import ctypes as C
+    import torch
+    from mononn_b200 import capi
+    l = capi.lib()
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    rows = []
+    for mode, what in ((0, "back to back"), (1, "+ a commit per four"), (3, "+ commit, satisfied wait and fence per four")):
+        for n in (16, 32, 64, 128, 192, 256):
+            cyc, iss, ns = C.c_double(), C.c_double(), C.c_double()
+            capi.check(l.mononn_debug_mma_issue(0, n, 1024, 1, mode, sms, C.byref(cyc), C.byref(iss), C.byref(ns)))
+            rows.append({"n": n, "mode": what, "cycles_per_mma": round(cyc.value, 1),
+                         "issue_cycles_per_mma": round(iss.value, 1), "ns_per_mma": round(ns.value, 1)})
+    print(json.dumps({"diagnostic": "mma_issue_probe", "ctas": sms, "instructions": 1024, "table": rows}))
 
 
 def run_torch_baseline(args):
@@ -571,7 +595,9 @@ def main():
     ap.add_argument("--tuning-level", type=int, default=1, help="what --tune searches (see include/mononn.h)")
     ap.add_argument("--spec", default="", help="diagnostic: spec fields to override, e.g. row_fusion=off,grid=128")
     ap.add_argument("--config", default="", help="diagnostic: time another configuration (bert_large_b1, "
-                    "bert_large_b16, vit_b1, vit_b64, opt_b1, opt_b8, clip) and print its roofline fraction")
+                    "bert_large_b16, vit_b1, vit_b64, opt_b1, opt_b8, clip, t5_small) and print its roofline fraction")
+    ap.add_argument("--mma-probe", action="store_true",
+                    help="diagnostic: cycles per tcgen05.mma by tile width (mononn_debug_mma_issue)")
     ap.add_argument("--torch-baseline", action="store_true",
                     help="diagnostic: the same BERT-base forward in plain torch fp16 on this GPU (eager and graph replay)")
     ap.add_argument("--no-flush", action="store_true", help="do not flush L2 between timed steps")
@@ -582,7 +608,9 @@ def main():
     ap.add_argument("--stage-report", action="store_true",
                     help="diagnostic: per operator class time and the barrier's share, from the event trace")
     args = ap.parse_args()
-    if args.config:
+    if args.mma_probe:
+        run_mma_probe(args)
+    elif args.config:
         run_config(args)
     elif args.torch_baseline:
         run_torch_baseline(args)

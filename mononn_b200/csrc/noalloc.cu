@@ -236,6 +236,7 @@ extern "C" int mononn_attention_noalloc(const void* q, const void* k, const void
   kp.cluster = 1;
   kp.l2_hints = 0;
   kp.warp_arrive = 0;
+  kp.flag_epoch = 0;
   const unsigned grid = od.n_items < static_cast<unsigned>(st->sm_count) ? od.n_items
                                                                         : static_cast<unsigned>(st->sm_count);
   void* kargs[1] = {&kp};

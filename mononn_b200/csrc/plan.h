@@ -180,6 +180,7 @@ struct Plan {
   uint64_t const_bytes = 0;
   uint64_t hot_const_bytes = 0;  // leading part of the constant arena holding the small constants
   uint64_t scratch_bytes = 0;  // module-owned, zero-initialised
+  uint64_t flag_offset = 0, flag_bytes = 0;  // arrival counters of row ops fused into GEMM stages
   uint64_t temp_bytes = 0;
   uint32_t grid = 0, block = kThreads, smem_bytes = 0;
   uint32_t cluster = 1;  // CTAs per cluster of the launch

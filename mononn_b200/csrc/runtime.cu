@@ -181,6 +181,8 @@ int Runtime::load_plan(const Plan& plan) {
   bound_ = false;
   bound_args_.clear();
   epoch_ = 0;
+  flag_epoch_ = 0;
+  flags_uneven_ = false;
   return upload_all_constants();
 }
 
@@ -394,10 +396,19 @@ int Runtime::launch(void* const* args, int n, void* stream, uint32_t stage_begin
   kp.timeout_us = timeout_us ? timeout_us : 2000000u;
   kp.stage_begin = stage_begin;
   kp.stage_end = stage_end;
+  // Arrival counters of row ops that share a stage with their GEMMs grow by the same amount on
+  // every launch of all stages. A launch of a stage sub-range (tuning, profiling) would leave
+  // them uneven, so it starts from cleared counters and the launch after it clears them again.
+  const bool full = (stage_begin == 0 && stage_end == plan_.stages.size());
+  if (plan_.flag_bytes != 0 && (!full || flags_uneven_)) {
+    CUDA_TRY(cudaMemsetAsync(scr + plan_.flag_offset, 0, plan_.flag_bytes, static_cast<cudaStream_t>(stream)));
+    flag_epoch_ = 0;
+  }
+  flags_uneven_ = !full;
+  kp.flag_epoch = ++flag_epoch_;
   kp.cluster = plan_.cluster;
   kp.l2_hints = plan_.spec.l2_hints == 2 ? 1u : 0u;
   kp.warp_arrive = warp_arrive() ? 1u : 0u;
-  kp.pad = 0;
   void* kargs[1] = {&kp};
   if (plan_.cluster <= 1) {
     CUDA_TRY(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(mononn_megakernel),
@@ -475,6 +486,8 @@ int Runtime::check_status(int* stage, int* cta) {
   // restore the invariants the next launch relies on: counter, status, zeroed accumulators
   CUDA_TRY(cudaMemset(d_scratch_, 0, plan_.scratch_bytes));
   epoch_ = 0;
+  flag_epoch_ = 0;
+  flags_uneven_ = false;
   return MONONN_ERR_BARRIER_TIMEOUT;
 }
 

@@ -94,6 +94,8 @@ class Runtime {
   std::vector<void*> bound_args_;
   bool bound_ = false;
   uint32_t epoch_ = 0;
+  uint32_t flag_epoch_ = 0;    // launches since the row ops' arrival counters were cleared
+  bool flags_uneven_ = false;  // the last launch ran a stage sub-range
   uint32_t n_stamp_stages_ = 0;
   std::map<std::string, std::vector<uint8_t>> host_consts_;
   void* encode_fn_ = nullptr;

@@ -505,9 +505,11 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
 
   // ---- scratch layout: barrier counter, status, stamps, then f32 tensors
   uint64_t scratch = kScratchStampsOff + align_up(8ull * (n_stages + 2), 256);
-  // arrival counters of the row ops that share a stage with their GEMMs: {arrived, finished} each
+  // arrival counters of the row ops that share a stage with their GEMMs (one per pair, 8 bytes apart)
   const uint64_t flags_off = scratch;
   scratch += align_up(8ull * n_flags, 256);
+  P.flag_offset = flags_off;
+  P.flag_bytes = n_flags ? align_up(8ull * n_flags, 256) : 0;
 
   // f32 tensors come in two kinds that must not inherit each other's memory. A GEMM
   // accumulator whose first write is a reduction needs zeros when its life starts and is
