@@ -175,7 +175,7 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
 }
 // Polling uses relaxed loads: an acquire load in a spin loop would invalidate the SM's L1 on
 // every iteration, under the feet of the warps that are doing the stage's work. One acquire
-// fence after the poll succeeds gives the ordering.
+// load after the poll succeeds gives the ordering.
 __device__ __forceinline__ uint32_t ld_relaxed_gpu(const uint32_t* p) {
   uint32_t v;
   asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -251,7 +251,7 @@ struct Ctrl {
   uint64_t b_empty[kBSlots];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
-  uint64_t group_bar;  // the eight epilogue warps (256 arrivals per phase)
+  uint64_t group_bar;  // the eight epilogue warps (one arrival per warp and phase)
   uint64_t cl_bar;     // first CTA of a cluster: one arrival per CTA of the cluster per stage
   uint32_t tmem_base;
   uint32_t abort_flag;
@@ -343,6 +343,18 @@ __device__ __forceinline__ bool mbar_wait(const Ctx& c, uint64_t* bar, uint32_t 
   return mbar_wait_slow(c.P, c.ctrl, b, parity, c.stage, where);
 }
 
+// After a relaxed poll has seen the count, one acquire load of the same counter gives the
+// ordering: it observes the last arrival (a release atomic) and through the chain of atomics
+// all earlier ones. A full fence.acq_rel.gpu in its place measured 32 us slower per inference
+// (it also waits for this thread's own outstanding stores).
+__device__ __forceinline__ void acquire_after_poll(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  (void)v;
+}
+#ifndef MONONN_ALL_POLL
+#define MONONN_ALL_POLL 0  // 1: every epilogue warp polls the global counter itself
+#endif
 #ifndef MONONN_POLL_SLEEP
 #define MONONN_POLL_SLEEP 32
 #endif
@@ -359,7 +371,7 @@ __device__ __noinline__ bool grid_wait_slow(const KernelParams* P, Ctrl* ctrl, u
   uint32_t it = 0;
   for (;;) {
     if (static_cast<int32_t>(ld_relaxed_gpu(P->barrier) - target) >= 0) {
-      fence_acq_rel_gpu();
+      acquire_after_poll(P->barrier);
       return true;
     }
 #if MONONN_POLL_SLEEP > 0
@@ -386,7 +398,7 @@ __device__ __forceinline__ bool grid_wait(const Ctx& c, uint32_t stage, uint32_t
       P.epoch_base + (stage - P.stage_begin) * (gridDim.x / P.cluster) * (P.warp_arrive ? kSimtWarps : 1u);
   bool ok = true;
   if (static_cast<int32_t>(ld_relaxed_gpu(P.barrier) - target) >= 0) {
-    fence_acq_rel_gpu();
+    acquire_after_poll(P.barrier);
   } else {
     ok = grid_wait_slow(c.P, c.ctrl, target, stage, where);
   }
@@ -429,7 +441,11 @@ __device__ __forceinline__ bool mbar_wait_warp(const Ctx& c, uint64_t* bar, uint
 __device__ __forceinline__ bool grid_wait_warp(const Ctx& c, uint32_t stage, uint32_t where) {
   bool ok = true;
   if ((threadIdx.x & 31u) == 0u)
+#if MONONN_ALL_POLL
+    ok = grid_wait(c, stage, where, threadIdx.x == kRoleThreads);
+#else
     ok = (threadIdx.x == kRoleThreads) ? grid_wait(c, stage, where, true) : grid_wait_local(c, stage, where);
+#endif
   return __all_sync(0xffffffffu, ok);
 }
 // A row op that shares a stage with the split-K GEMMs feeding it waits until all of their work
@@ -444,7 +460,7 @@ __device__ __noinline__ bool flag_wait_slow(const KernelParams* P, Ctrl* ctrl, c
   uint32_t it = 0;
   for (;;) {
     if (static_cast<int32_t>(ld_relaxed_gpu(flag) - target) >= 0) {
-      fence_acq_rel_gpu();
+      acquire_after_poll(flag);
       return true;
     }
     __nanosleep(32);
@@ -471,17 +487,25 @@ __device__ __forceinline__ bool flag_wait_warp(const Ctx& c, const OpDesc& op, u
     const uint32_t* flag = reinterpret_cast<const uint32_t*>(op.flag);
     const uint32_t target = c.P->flag_epoch * op.flag_target;
     if (static_cast<int32_t>(ld_relaxed_gpu(flag) - target) >= 0) {
-      fence_acq_rel_gpu();
+      acquire_after_poll(flag);
     } else {
       ok = flag_wait_slow(c.P, c.ctrl, flag, target, c.stage, where);
     }
   }
   return __all_sync(0xffffffffu, ok);
 }
+// One arrival for the whole warp on an mbarrier that counts the eight epilogue warps.
+__device__ __forceinline__ void warp_arrive(uint64_t* bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31u) == 0u) mbar_arrive(smem_u32(bar));
+}
 // Barrier across the 256 epilogue threads built on an mbarrier so that, unlike bar.sync,
 // the wait is bounded when a warp has already left on the abort path.
 __device__ __forceinline__ bool group_sync(Ctx& c, uint32_t where) {
-  mbar_arrive(smem_u32(&c.ctrl->group_bar));
+  // one arrival per warp (the warp barrier orders the other lanes' accesses before it): 256
+  // arrivals on one shared-memory word would serialise for a quarter of a microsecond
+  __syncwarp();
+  if ((threadIdx.x & 31u) == 0u) mbar_arrive(smem_u32(&c.ctrl->group_bar));
   const bool ok = mbar_wait(c, &c.ctrl->group_bar, c.group_phase, where);
   c.group_phase ^= 1u;
   return __all_sync(0xffffffffu, ok);
@@ -1355,6 +1379,21 @@ __device__ __noinline__ void rowwise_item(const OpDesc& op, uint32_t local, uint
   if (mark) trace(P, stage, TR_MARK0 + 2);
 }
 
+// Scale, shift and pre-load bias of a row op are small constants that every layer reads once.
+// The weight stream (larger than L2) evicts them between their uses, so a row op asks for them
+// again while it waits for its inputs (grid barrier or arrival counter): the loads in
+// rowwise_item then hit L2 instead of paying an HBM round trip on the critical path.
+__device__ __forceinline__ void prefetch_row_consts(const OpDesc& op, uint32_t lane) {
+  const bool alt = (op.kind == OP_EMBED || op.kind == OP_ASSEMBLE);
+  const uint64_t g = alt ? op.p[6] : op.p[2], b = alt ? op.p[7] : op.p[3], b2 = op.q[3];
+  const uint32_t off = lane * 128u;
+  if (off < op.cols * 2u) {
+    if (g != 0) asm volatile("prefetch.global.L2 [%0];" ::"l"(g + off));
+    if (b != 0) asm volatile("prefetch.global.L2 [%0];" ::"l"(b + off));
+    if (b2 != 0) asm volatile("prefetch.global.L2 [%0];" ::"l"(b2 + off));
+  }
+}
+
 // Arg-max item: one f16 row per 256-thread group. Each thread scans every 256th 16-byte
 // vector in ascending order (so "strictly greater" keeps its first maximum), then the
 // partial results are merged by (larger value, then smaller index): the first index of the
@@ -1589,7 +1628,7 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
       mbar_arrive(smem_u32(&c.ctrl->a_full[cV % kASlots]));
     }
     tc_fence_before();
-    mbar_arrive(smem_u32(&c.ctrl->acc_empty[phQ & 1u]));
+    warp_arrive(&c.ctrl->acc_empty[phQ & 1u]);
   }
   // causal: keys after the query are masked
   const uint32_t key_limit = (op.flags & F_CAUSAL) ? qrow : 0xffffffffu;
@@ -1694,7 +1733,7 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
   if (tid_in_group == 0) trace(*c.P, c.stage, TR_MARK0 + 2);
   const float inv = 1.0f / (sum0 + sum1 + c.ctrl->row_sum[half ^ 1u][row]);
   tc_fence_before();
-  mbar_arrive(smem_u32(&c.ctrl->acc_empty[phS & 1u]));
+  warp_arrive(&c.ctrl->acc_empty[phS & 1u]);
 
   // O = sum_j P_j V_j: this warp stores 32 of the head's 64 columns
   if (!mbar_wait_warp(c, &c.ctrl->acc_full[phO & 1u], (phO >> 1) & 1u, 0x413)) return false;
@@ -1729,7 +1768,7 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
   }
   __syncwarp();  // the staging block is reused by the warp's next item
   tc_fence_before();
-  mbar_arrive(smem_u32(&c.ctrl->acc_empty[phO & 1u]));
+  warp_arrive(&c.ctrl->acc_empty[phO & 1u]);
   return true;
 }
 
@@ -1746,7 +1785,11 @@ __device__ void role_simt(Ctx c, uint32_t tmem_base, uint32_t tid_in_group) {
     const StageDesc st = load_stage(P, s);
     uint4* slot = c.ctrl->desc[3 + widx];
     Item first{nullptr, 0};
-    if (blockIdx.x < st.n_items) first = fetch_item<true>(P, st, blockIdx.x, slot, lane);
+    if (blockIdx.x < st.n_items) {
+      first = fetch_item<true>(P, st, blockIdx.x, slot, lane);
+      const uint32_t k0 = first.op->kind;
+      if (k0 == OP_LAYERNORM || k0 == OP_EMBED || k0 == OP_ASSEMBLE) prefetch_row_consts(*first.op, lane);
+    }
     // All CTAs must have finished the previous stage before this CTA reads its
     // results or arrives for this stage.
     WAIT_OR_RETURN(grid_wait_warp(c, s, 0x400));
@@ -1777,7 +1820,7 @@ __device__ void role_simt(Ctx c, uint32_t tmem_base, uint32_t tid_in_group) {
           gemm_epilogue(op, it.local, tmem_base + buf * kAccCols, quarter, half, lane, bias_s,
                         c.store_stage + widx * 2048u);
           tc_fence_before();
-          mbar_arrive(smem_u32(&c.ctrl->acc_empty[buf]));
+          warp_arrive(&c.ctrl->acc_empty[buf]);
           ++acc_cnt;
           a_cnt += op.kb_per_split;
           if (op.flag != 0) {
@@ -1796,7 +1839,10 @@ __device__ void role_simt(Ctx c, uint32_t tmem_base, uint32_t tid_in_group) {
         case OP_LAYERNORM:
         case OP_EMBED:
         case OP_ASSEMBLE:
-          if (op.flag_target != 0) WAIT_OR_RETURN(flag_wait_warp(c, op, 0x430));
+          if (op.flag_target != 0) {
+            prefetch_row_consts(op, lane);
+            WAIT_OR_RETURN(flag_wait_warp(c, op, 0x430));
+          }
           rowwise_item(op, it.local, widx, lane, P, s);
           break;
         case OP_PATCHIFY:
@@ -1889,9 +1935,9 @@ mononn_megakernel(const __grid_constant__ KernelParams P) {
     }
     for (uint32_t i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&ctrl->acc_full[i]), 1);
-      mbar_init(smem_u32(&ctrl->acc_empty[i]), kSimtThreads);
+      mbar_init(smem_u32(&ctrl->acc_empty[i]), kSimtWarps);
     }
-    mbar_init(smem_u32(&ctrl->group_bar), kSimtThreads);
+    mbar_init(smem_u32(&ctrl->group_bar), kSimtWarps);
     mbar_init(smem_u32(&ctrl->cl_bar), P.cluster);
     ctrl->abort_flag = 0;
     ctrl->barriers_seen = 0;

@@ -43,8 +43,8 @@ struct TuningSpec {
   // arrive at the grid barrier through an mbarrier in the first CTA's shared memory and that
   // CTA alone adds to the global counter.
   uint32_t cluster = 0;
-  // L2 eviction-priority hints on the TMA loads: 0 / 1 none, 2 weights evict-first and GEMM
-  // activation tiles evict-last
+  // L2 eviction-priority hints on the TMA loads: 0 / 2 weights evict-first and GEMM activation
+  // tiles evict-last, 1 none
   uint32_t l2_hints = 0;
   // grid-barrier arrival: 0 / 2 one per epilogue warp (each releases its own stores), 1 one per
   // CTA after a CTA-wide sync (always the case inside a cluster launch)

@@ -407,7 +407,7 @@ int Runtime::launch(void* const* args, int n, void* stream, uint32_t stage_begin
   flags_uneven_ = !full;
   kp.flag_epoch = ++flag_epoch_;
   kp.cluster = plan_.cluster;
-  kp.l2_hints = plan_.spec.l2_hints == 2 ? 1u : 0u;
+  kp.l2_hints = plan_.spec.l2_hints == 1 ? 0u : 1u;
   kp.warp_arrive = warp_arrive() ? 1u : 0u;
   void* kargs[1] = {&kp};
   if (plan_.cluster <= 1) {

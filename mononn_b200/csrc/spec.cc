@@ -77,7 +77,7 @@ std::string spec_to_json(const Plan& plan, uint32_t sm_count) {
   // cannot fill the GPU (batches*heads <= CTAs, sequence <= 128); "off"; "on": whenever legal
   root.set("qkv_fusion", Json::string(plan.spec.qkv_fusion == 1 ? "off" : plan.spec.qkv_fusion == 2 ? "on" : "auto"));
   root.set("row_fusion", Json::string(plan.spec.row_fusion == 1 ? "off" : "on"));
-  root.set("l2_hints", Json::string(plan.spec.l2_hints == 2 ? "on" : "off"));
+  root.set("l2_hints", Json::string(plan.spec.l2_hints == 1 ? "off" : "on"));
   root.set("barrier_arrive", Json::string(plan.spec.barrier_arrive == 1 || plan.cluster > 1 ? "cta" : "warp"));
   root.set("cluster_elewise_spec", Json::object());
   root.set("cluster_reduce_spec", Json::object());

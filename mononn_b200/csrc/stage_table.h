@@ -174,7 +174,7 @@ struct KernelParams {
   uint32_t stage_begin;  // run stages [stage_begin, stage_end)
   uint32_t stage_end;
   uint32_t cluster;      // CTAs per cluster of this launch (1: no cluster-scoped arrival)
-  uint32_t l2_hints;     // 1: weight tiles are loaded evict-first, GEMM activation tiles evict-last
+  uint32_t l2_hints;     // 1: weight tiles are loaded evict-first, GEMM activation tiles evict-last (default)
   uint32_t warp_arrive;  // 1: every epilogue warp arrives at the grid barrier for itself (8 arrivals per
                          // CTA and stage, no CTA-wide sync before the arrival); 0: one arrival per CTA
   uint32_t flag_epoch;   // launches that have added to the arrival counters since they were cleared,
