@@ -1,5 +1,6 @@
-"""The N>1 path of bench.py is 'replicas only': each rank runs its own inferences and the
-ranks only agree on the slowest time.  Checked here with two gloo ranks on CPU."""
+"""The N>1 path of bench.py is 'replicas only': each rank lowers its own module, runs its own
+inferences on its own inputs, and the ranks only agree on the slowest time.  Checked here with
+two gloo ranks on CPU (lowering needs no device; the launches are covered on the GPU box)."""
 import os
 import subprocess
 import sys
@@ -15,12 +16,27 @@ WORKER = textwrap.dedent("""
     dist.init_process_group("gloo")
     rank, world, local = bench.dist_env()
     assert world == 2 and rank == int(os.environ["RANK"])
+    # every replica lowers the module on its own (no device is needed to lower) and draws its own
+    # inputs; the stage tables must be identical, the inputs must not
+    import hashlib
+    from mononn_b200 import bert_tiny, make_inputs
+    from mononn_b200.hlo_builder import bert_hlo
+    from mononn_b200.module import describe
+    cfg = bert_tiny(batch=2, seq=24, layers=2, hidden=128, ffn=512)
+    plan = describe("hlo", bert_hlo(cfg)[0])["plan"]
+    digest = hashlib.sha256(json.dumps(plan, sort_keys=True).encode()).digest()[:8]
+    ids = make_inputs(cfg, 1234 + rank)["input_ids"]
+    mine = torch.tensor(list(digest) + [int(ids.sum())], dtype=torch.int64)
+    both = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(both, mine)
+    assert torch.equal(both[0][:8], both[1][:8]), "replicas lowered different plans"
+    assert both[0][8] != both[1][8], "replicas drew the same inputs"
     # every rank 'measures' its own time; the job time is the maximum over ranks
     t = torch.tensor([0.5 if rank == 0 else 0.8], dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     value = bench.replica_throughput(world, 100, float(t))
     if rank == 0:
-        print(json.dumps({{"value": value, "max_s": float(t)}}))
+        print(json.dumps({{"value": value, "max_s": float(t), "stages": len(plan["stages"])}}))
     dist.barrier()
     dist.destroy_process_group()
 """)
@@ -37,7 +53,7 @@ def test_two_replicas_report_whole_job_throughput(tmp_path):
     line = [l for l in out.stdout.splitlines() if l.startswith("{")][-1]
     import json
     r = json.loads(line)
-    assert r["max_s"] == 0.8
+    assert r["max_s"] == 0.8 and r["stages"] == 1 + 2 * 4
     assert abs(r["value"] - 2 * 100 / 0.8) < 1e-9
 
 
