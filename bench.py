@@ -37,7 +37,7 @@ UNIT = "samples/s"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised
 # in profiles/ (None until a capture exists)
-NCU_TRAFFIC_BYTES = 175189504  # 170.90 MB read + 4.29 MB written
+NCU_TRAFFIC_BYTES = 175312640  # 170.77 MB read + 4.55 MB written
 
 
 def measured_hbm_peak():
@@ -63,8 +63,11 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "50"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            # nvidia-smi needs about a second before its first sample: wait for that line, so that
+            # the samples that follow fall into the timed region and not behind it
+            self.first = self.proc.stdout.readline()
         except Exception:
             self.proc = None
 
@@ -77,6 +80,7 @@ class ClockSampler:
         except Exception:
             self.proc.kill()
             out = ""
+        out = getattr(self, "first", "") + out
         sm, mx, busy, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in out.strip().splitlines():
