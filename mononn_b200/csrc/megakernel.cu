@@ -261,6 +261,7 @@ struct Ctrl {
   float mask_row[384];      // additive key mask of the current attention tile (log2 units)
   float row_max[2][128];    // attention: row maximum / row sum over each warp half's columns,
   float row_sum[2][128];    // exchanged between the two threads that share a query row
+  float ln_part[2][kSplitRowsPerItem][4];  // split LayerNorm: per-warp partial sum / squared deviation
   float red_val[kSimtWarps];  // arg-max: per-warp partial results of the current row
   uint32_t red_idx[kSimtWarps];
   // Shared-memory copies of the operator descriptor each role is working on: slot 0 weight
@@ -1394,6 +1395,117 @@ __device__ __forceinline__ void prefetch_row_consts(const OpDesc& op, uint32_t l
   }
 }
 
+// LayerNorm / RMS norm of few rows: four warps share a row (two rows per work item), each
+// taking a quarter of the columns; the partial sums meet in shared memory. With 128 rows this
+// puts 512 warps on 64 SMs instead of 128 warps on 16, and cuts the per-warp chain of loads,
+// reductions, conversions and stores (about 2 us for a 768-column row on one warp) to a quarter.
+__device__ __noinline__ bool rowwise_split_item(Ctx& c, const OpDesc& op, uint32_t local, uint32_t widx,
+                                                uint32_t lane) {
+  const uint32_t r_in = widx >> 2, part = widx & 3u;
+  const uint32_t row = local * kSplitRowsPerItem + r_in;
+  const bool live = row < op.rows;
+  const uint32_t safe_row = live ? row : 0u;
+  const uint32_t cols = op.cols, per = cols >> 4;  // 16-byte f32 vectors per warp (<= 64)
+  const uint32_t flags = op.flags;
+  const bool rms = (flags & F_RMSNORM) != 0u, src32 = (flags & F_SRC_F32) != 0u;
+  const uint32_t v0 = part * per;
+  uint32_t vi[2];
+  bool on[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    on[i] = lane + 32u * i < per;
+    vi[i] = v0 + (on[i] ? lane + 32u * i : 0u);
+  }
+  const uint2* gamma = reinterpret_cast<const uint2*>(op.p[2]);
+  const uint2* beta = reinterpret_cast<const uint2*>(op.p[3]);
+  const bool two = op.q[2] != 0, add_b2 = two && op.q[3] != 0;
+  const uint2* b2p = add_b2 ? reinterpret_cast<const uint2*>(op.q[3]) : gamma;
+  uint2 gv[2], bv[2], b2v[2];
+  float4 x[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    gv[i] = __ldg(gamma + vi[i]);
+    bv[i] = __ldg(beta + vi[i]);
+    b2v[i] = __ldg(b2p + vi[i]);
+  }
+  if (src32) {
+    const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(op.p[1]) +
+                                                        static_cast<size_t>(safe_row) * op.lds);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) x[i] = __ldcg(src + vi[i]);
+    if ((flags & F_ZERO_SRC) && live) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+        if (on[i]) const_cast<float4*>(src)[vi[i]] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  } else {
+    const uint2* src = reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(op.p[1]) +
+                                                      static_cast<size_t>(safe_row) * op.lds);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) x[i] = h4_to_f4(__ldcg(src + vi[i]));
+  }
+  if (flags & F_RESID) {
+    const uint2* res = reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(op.p[4]) +
+                                                      static_cast<size_t>(safe_row) * op.ldr);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) add4(x[i], h4_to_f4(__ldcg(res + vi[i])));
+  }
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    if (!on[i]) x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    sum += x[i].x + x[i].y + x[i].z + x[i].w;
+  }
+  const float inv_n = 1.0f / static_cast<float>(cols);
+  sum = warp_sum(sum);
+  if (lane == 0) c.ctrl->ln_part[0][r_in][part] = sum;
+  if (!group_sync(c, 0x431)) return false;
+  const float* p0 = c.ctrl->ln_part[0][r_in];
+  const float mean = rms ? 0.f : (p0[0] + p0[1] + p0[2] + p0[3]) * inv_n;
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+    if (on[i]) {
+      const float a = x[i].x - mean, b = x[i].y - mean, d = x[i].z - mean, e = x[i].w - mean;
+      sq += a * a + b * b + d * d + e * e;
+    }
+  sq = warp_sum(sq);
+  if (lane == 0) c.ctrl->ln_part[1][r_in][part] = sq;
+  if (!group_sync(c, 0x432)) return false;
+  const float* p1 = c.ctrl->ln_part[1][r_in];
+  const float rstd = rsqrtf((p1[0] + p1[1] + p1[2] + p1[3]) * inv_n + op.eps);
+  if (live) {
+    uint2* out = op.p[0] ? reinterpret_cast<uint2*>(reinterpret_cast<__half*>(op.p[0]) +
+                                                    static_cast<size_t>(row) * op.ldo)
+                         : nullptr;
+    float4* out2 = two ? reinterpret_cast<float4*>(reinterpret_cast<float*>(op.q[2]) +
+                                                   static_cast<size_t>(row) * cols)
+                       : nullptr;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      if (!on[i]) continue;
+      const float4 g = h4_to_f4(gv[i]);
+      const float4 b = rms ? make_float4(0.f, 0.f, 0.f, 0.f) : h4_to_f4(bv[i]);
+      float4 y;
+      y.x = (x[i].x - mean) * rstd * g.x + b.x;
+      y.y = (x[i].y - mean) * rstd * g.y + b.y;
+      y.z = (x[i].z - mean) * rstd * g.z + b.z;
+      y.w = (x[i].w - mean) * rstd * g.w + b.w;
+      if (out != nullptr) {
+        uint2 o;
+        o.x = pack_h2(y.x, y.y);
+        o.y = pack_h2(y.z, y.w);
+        out[vi[i]] = o;
+      }
+      if (out2 != nullptr) {
+        if (add_b2) add4(y, h4_to_f4(b2v[i]));
+        out2[vi[i]] = y;
+      }
+    }
+  }
+  return true;
+}
+
 // Arg-max item: one f16 row per 256-thread group. Each thread scans every 256th 16-byte
 // vector in ascending order (so "strictly greater" keeps its first maximum), then the
 // partial results are merged by (larger value, then smaller index): the first index of the
@@ -1506,25 +1618,32 @@ __device__ __noinline__ void pairdot_item(const OpDesc& op, uint32_t local, uint
   }
 }
 
-// Patch extraction for a convolution whose stride equals its window (ViT / CLIP patch
-// embedding): row (b, py, px) of the f16 output holds the window's pixels in (ky, kx, c)
-// order, read from the NCHW f32 image. With that operand the convolution is a plain GEMM
-// against the [out_channels, ky*kx*c] filter. The reference runs these through CUTLASS
-// implicit-GEMM fprop (mononn_engine/core/op_impl/conv_impl.cc:36-106).
+// Window extraction for a forward convolution over the image (the ViT / CLIP patch embedding
+// with stride = window, or an overlapping, zero-padded stem): row (b, py, px) of the f16 output
+// holds the window's pixels in (ky, kx, c) order, read from the NCHW f32 image, zero where the
+// window hangs over the edge and in the columns that pad the row to a multiple of 64. With
+// that operand the convolution is a plain GEMM against the [out_channels, ky*kx*c] filter. The
+// reference runs these through CUTLASS implicit-GEMM fprop
+// (mononn_engine/core/op_impl/conv_impl.cc:36-106, 252-345).
 __device__ __noinline__ void patchify_item(const OpDesc& op, uint32_t local, uint32_t warp_in_group,
                                            uint32_t lane) {
   const uint32_t row = local * kRowsPerItem + warp_in_group;
   if (row >= op.rows) return;
   const uint32_t C = op.heads, Himg = op.seq, Wimg = op.batches, kh = op.head_dim, kw = op.q_col;
-  const uint32_t gw = op.k_col, per_img = op.vocab;  // patches per image row / per image
+  const uint32_t gw = op.k_col, per_img = op.vocab;  // windows per image row / per image
   const uint32_t b = row / per_img, pr = row % per_img, py = pr / gw, px = pr % gw;
+  const uint32_t y0 = py * op.M - op.rows_per_batch, x0 = px * op.N - op.ldt;  // may wrap below 0
+  const uint32_t valid = op.K;
+  (void)kh;
   const float* src = reinterpret_cast<const float*>(op.p[1]);
   __half* dst = reinterpret_cast<__half*>(op.p[0]) + static_cast<size_t>(row) * op.ldo;
 #pragma unroll 4
   for (uint32_t j = lane; j < op.cols; j += 32u) {
     const uint32_t c = j % C, kx = (j / C) % kw, ky = j / (C * kw);
-    dst[j] = __float2half_rn(
-        src[((static_cast<size_t>(b) * C + c) * Himg + py * kh + ky) * Wimg + px * kw + kx]);
+    const uint32_t y = y0 + ky, x = x0 + kx;  // a wrapped (negative) coordinate fails the bound test
+    float v = 0.f;
+    if (j < valid && y < Himg && x < Wimg) v = src[((static_cast<size_t>(b) * C + c) * Himg + y) * Wimg + x];
+    dst[j] = __float2half_rn(v);
   }
 }
 
@@ -1843,7 +1962,11 @@ __device__ void role_simt(Ctx c, uint32_t tmem_base, uint32_t tid_in_group) {
             prefetch_row_consts(op, lane);
             WAIT_OR_RETURN(flag_wait_warp(c, op, 0x430));
           }
-          rowwise_item(op, it.local, widx, lane, P, s);
+          if (op.flags & F_ROW_SPLIT) {
+            WAIT_OR_RETURN(rowwise_split_item(c, op, it.local, widx, lane));
+          } else {
+            rowwise_item(op, it.local, widx, lane, P, s);
+          }
           break;
         case OP_PATCHIFY:
           patchify_item(op, it.local, widx, lane);

@@ -19,7 +19,7 @@ enum OpKind : uint32_t {
   OP_EMBED = 4,      // row gather + position + type + LayerNorm, mask bias
   OP_L2NORM_LOGITS = 5,
   OP_ASSEMBLE = 6,   // token rows = [constant prefix rows | GEMM rows + bias] + position rows -> f32
-  OP_PATCHIFY = 7,   // NCHW f32 image -> f16 patch rows (operand of the patch-embedding GEMM)
+  OP_PATCHIFY = 7,   // NCHW f32 image -> f16 window rows (operand of the convolution's GEMM)
   OP_ARGMAX = 8,     // s32 index of the maximum of every f16 row (first index on ties)
   OP_ROWSEL = 9,     // out[b,:] = src[b*seq + argmax(ids[b,:]), :] (pooling at the largest token id)
   OP_PAIRDOT = 10,   // out[i,j] = alpha * <a[i,:], b[j,:]> for two small f16 activations (SIMT)
@@ -55,6 +55,7 @@ enum OpFlags : uint32_t {
   F_FUSED_QKV = 1u << 11,  // attention: the item first computes its own Q, K, V = x W_h + b_h
   F_POS_BIAS = 1u << 12,   // attention: additive f16 bias per (head, query, key), q[0] = [heads, seq, seq]
   F_RMSNORM = 1u << 13,    // row op: x * rsqrt(mean(x^2) + eps) * scale (no mean subtraction, no shift)
+  F_ROW_SPLIT = 1u << 14,  // LayerNorm: a row is shared by four warps (two rows per work item), for few rows
 };
 
 // Pointer slots p[0..7]; meaning per kind:
@@ -68,7 +69,9 @@ enum OpFlags : uint32_t {
 //  ASSEMBLE:  0 out(f16, optional), 1 GEMM rows(f16), 3 prefix rows(f16), 4 position rows(f16),
 //             5 bias(f16), 6/7 valid dummies; seq = tokens per batch, k_col = prefix rows
 //  PATCHIFY:  0 out(f16 [rows, cols]), 1 image(f32 NCHW); heads = C, seq = H, batches = W,
-//             head_dim = kh, q_col = kw, k_col = patches per image row, vocab = patches per image
+//             head_dim = kh, q_col = kw, k_col = windows per image row, vocab = windows per image,
+//             M / N = vertical / horizontal stride, rows_per_batch / ldt = rows / columns of zero
+//             padding above / left of the image, K = kh*kw*C (columns K..cols-1 are written as 0)
 //  EMBED: q_col = offset added to the position index; p[4] = 0: no position table
 //  ATTENTION with F_POS_BIAS: q[0] = f16 [heads, seq, seq] added to the scaled scores (seq % 32 == 0)
 //  LAYERNORM and EMBED may also write q[2] = f32 copy of the result plus the f16 bias q[3]
@@ -154,6 +157,7 @@ constexpr uint32_t kSimtThreads = 256;        // warps 4..11: epilogue / row-wis
 constexpr uint32_t kSimtWarps = kSimtThreads / 32;
 constexpr uint32_t kThreads = kRoleThreads + kSimtThreads;
 constexpr uint32_t kRowsPerItem = kSimtWarps;  // row-wise operators: one row per SIMT warp per work item
+constexpr uint32_t kSplitRowsPerItem = 2;      // LayerNorm with F_ROW_SPLIT: four warps per row
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTraceEvents = 16;  // per (CTA, stage) slots of the optional event trace
 constexpr uint32_t kAccCols = 256;  // two accumulator buffers of 256 columns

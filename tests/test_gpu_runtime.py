@@ -244,3 +244,22 @@ def test_cluster_scoped_barrier_arrival_keeps_parity(cluster, tmp_path):
     mod.status()
     assert_parity(run(mod, cfg, inp), R.bert_encoder(cfg, w, inp), f"clusters of {cluster}, relaunched")
     mod.close()
+
+
+def test_row_per_warp_layernorm_keeps_parity_when_the_split_is_switched_off(tmp_path):
+    """Few rows are normalised by four warps each (the default here); `row_split: off` in the
+    spec deals whole rows to single warps, the form large batches always use. Same results."""
+    from mononn_b200.module import describe
+    cfg, w, inp = small()
+    text, names = bert_hlo(cfg)
+    spec = describe("hlo", text)["spec"]
+    assert spec["row_split"] == "on"
+    spec["row_split"] = "off"
+    (tmp_path / "cluster_0").mkdir()
+    (tmp_path / "cluster_0" / "best_tuning_spec.json").write_text(json.dumps(spec))
+    mod = compile_hlo(text, spec_dir=str(tmp_path), barrier_timeout_us=500000)
+    lns = [o for s in mod.plan()["stages"] for o in s["ops"] if o["kind"] == "layernorm"]
+    assert lns and all(not (o["flags"] & (1 << 14)) for o in lns)
+    mod.set_weights({names[k]: v for k, v in w.items()})
+    assert_parity(run(mod, cfg, inp), R.bert_encoder(cfg, w, inp), "row per warp")
+    mod.close()

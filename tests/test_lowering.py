@@ -42,6 +42,20 @@ def test_row_fusion_off_keeps_layernorm_stages(base_plan):
     assert p["spec_echo"]["row_fusion"] == "off" if "spec_echo" in p else True
 
 
+def test_layernorm_rows_are_shared_by_four_warps_when_there_are_few_rows(base_plan):
+    """128 rows dealt eight to an item occupy 16 CTAs with one row per warp; two rows per item,
+    four warps each, spread the same rows over 64 CTAs. Many rows keep the row-per-warp form."""
+    lns = [o for s in base_plan["plan"]["stages"] for o in s["ops"] if o["kind"] == "layernorm"]
+    assert lns and all(o["flags"] & (1 << 14) and o["n_items"] == 64 for o in lns)
+    off = describe("encoder", bert_base().to_json(), spec=dict(base_plan["spec"], row_split="off"))
+    assert off["spec"]["row_split"] == "off"
+    lns = [o for s in off["plan"]["stages"] for o in s["ops"] if o["kind"] == "layernorm"]
+    assert all(not (o["flags"] & (1 << 14)) and o["n_items"] == 16 for o in lns)
+    big = describe("encoder", bert_base(batch=16).to_json())["plan"]
+    lns = [o for s in big["stages"] for o in s["ops"] if o["kind"] == "layernorm"]
+    assert all(not (o["flags"] & (1 << 14)) and o["n_items"] == 16 * 128 // 8 for o in lns)
+
+
 def test_projections_stay_a_stage_of_their_own_when_attention_fills_the_gpu(lib_built, base_plan):
     """Fusing costs every (batch, head) item a pass over its head's weights: it is done only
     when the attention stage leaves CTAs idle (or on request), never for long sequences."""
