@@ -967,9 +967,10 @@ class Lowering {
     return MONONN_OK;
   }
 
-  // __cudnn$convForward whose stride equals its window and that has no padding: every output
-  // position sees its own patch, so the convolution is a GEMM over patch rows
-  // (NHWC input, KRSC filter, cross-correlation: ir_parser_fused.cc:749-800).
+  // __cudnn$convForward over the image: a window-extraction stage (stride, zero padding) writes
+  // one row per output position and the convolution is a GEMM over those rows. With stride =
+  // window and no padding every position sees its own patch (the ViT / CLIP embedding)
+  // (NHWC input, KRSC filter, cross-correlation: ir_parser_fused.cc:749-800, conv_impl.cc:252-345).
   int lower_conv(int idx) {
     const HloInstr& ins = e_.instrs[idx];
     if (ins.operands.size() != 2) return unsupported(ins, "convolution with a side input");
@@ -991,20 +992,37 @@ class Lowering {
     int64_t kh = 0, kw = 0, sh = 1, sw = 1;
     if (!pair_after("size", &kh, &kw)) return unsupported(ins, "window without a size");
     pair_after("stride", &sh, &sw);
-    if (win.find("pad") != std::string::npos || win.find("dilation") != std::string::npos)
-      return unsupported(ins, "padded or dilated convolution");
-    if (sh != kh || sw != kw) return unsupported(ins, "convolution whose stride differs from its window");
+    if (win.find("dilat") != std::string::npos || win.find("rhs_reversal") != std::string::npos)
+      return unsupported(ins, "dilated or reversed convolution");
+    // pad=<top>_<bottom>x<left>_<right>
+    int64_t pad[4] = {0, 0, 0, 0};
+    const size_t pp = win.find("pad=");
+    if (pp != std::string::npos) {
+      const char* s = win.c_str() + pp + 4;
+      for (int i = 0; i < 4; ++i) {
+        char* e = nullptr;
+        pad[i] = std::strtoll(s, &e, 10);
+        const char want = i == 1 ? 'x' : '_';
+        if (e == s || (i < 3 && *e != want)) return unsupported(ins, "window padding is not lo_hixlo_hi");
+        s = e + 1;
+      }
+    }
+    if (kh <= 0 || kw <= 0 || sh <= 0 || sw <= 0 || pad[0] < 0 || pad[1] < 0 || pad[2] < 0 || pad[3] < 0 ||
+        pad[0] >= kh || pad[1] >= kh || pad[2] >= kw || pad[3] >= kw)
+      return unsupported(ins, "window geometry (padding must be smaller than the window)");
     const HloInstr& wi = e_.instrs[ins.operands[1]];
     if (!ins.shape.is_tuple() || ins.shape.elems.empty() || ins.shape.elems[0].dims.size() != 4 ||
         wi.shape.dims.size() != 4)
       return unsupported(ins, "convolution result must be a tuple whose element 0 is [B,P,Q,K]");
     const auto& od = ins.shape.elems[0].dims;
     const uint32_t O = static_cast<uint32_t>(wi.shape.dims[0]);
-    if (wi.shape.dims[1] != kh || wi.shape.dims[2] != kw || wi.shape.dims[3] != img.heads ||
-        od[0] != img.B || od[1] * kh != img.S || od[2] * kw != img.D || od[3] != O)
+    const int64_t span_h = img.S + pad[0] + pad[1] - kh, span_w = img.D + pad[2] + pad[3] - kw;
+    if (wi.shape.dims[1] != kh || wi.shape.dims[2] != kw || wi.shape.dims[3] != img.heads || span_h < 0 ||
+        span_w < 0 || od[0] != img.B || od[1] != span_h / sh + 1 || od[2] != span_w / sw + 1 || od[3] != O)
       return unsupported(ins, "convolution shapes are inconsistent");
     const uint32_t gh = static_cast<uint32_t>(od[1]), gw = static_cast<uint32_t>(od[2]);
-    const uint32_t M = img.B * gh * gw, K = static_cast<uint32_t>(kh * kw) * img.heads;
+    const uint32_t Kw = static_cast<uint32_t>(kh * kw) * img.heads;  // elements of one window
+    const uint32_t M = img.B * gh * gw, K = (Kw + 63u) / 64u * 64u;   // GEMM rows are whole 64-element k blocks
     FOp pt;
     pt.kind = OP_PATCHIFY;
     pt.name = canonical_node_name(ins.name) + "_patches";
@@ -1019,12 +1037,17 @@ class Lowering {
     pt.q_col = static_cast<uint32_t>(kw);
     pt.k_col = gw;
     pt.vocab = gh * gw;
+    pt.M = static_cast<uint32_t>(sh);
+    pt.N = static_cast<uint32_t>(sw);
+    pt.K = Kw;
+    pt.pad_top = static_cast<uint32_t>(pad[0]);
+    pt.pad_left = static_cast<uint32_t>(pad[2]);
     g_.ops.push_back(pt);
     FOp o;
     o.kind = OP_GEMM;
     o.name = canonical_node_name(ins.name);
     o.a = pt.out;
-    o.w = const_tensor(wv.instr, K, O, /*transposed=*/true);  // filter [O, kh*kw*C] is [N, K]
+    o.w = const_tensor(wv.instr, Kw, O, /*transposed=*/true);  // filter [O, kh*kw*C] is [N, K], zero-extended to K
     o.M = M;
     o.N = O;
     o.K = K;

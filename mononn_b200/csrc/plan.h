@@ -49,6 +49,8 @@ struct TuningSpec {
   // grid-barrier arrival: 0 / 2 one per epilogue warp (each releases its own stores), 1 one per
   // CTA after a CTA-wide sync (always the case inside a cluster launch)
   uint32_t barrier_arrive = 0;
+  // 0 / 2: a LayerNorm with few rows shares each row among four warps; 1: always one warp per row
+  uint32_t row_split = 0;
 };
 
 // ------------------------------------------------------------------- FGraph
@@ -97,6 +99,8 @@ struct FOp {
   // EMBED: ids, type_ids, mask_in (Arg), word/pos/type tables (Const), mask_out (VecF32)
   int ids = -1, type_ids = -1, mask_in = -1, word = -1, pos = -1, type = -1, mask_out = -1;
   uint32_t rows = 0, cols = 0, vocab = 0;
+  // PATCHIFY: M / N = strides, K = window elements, zero padding above / left of the image
+  uint32_t pad_top = 0, pad_left = 0;
   int stage = -1;  // filled by the scheduler
 };
 
@@ -155,6 +159,7 @@ struct ConstBinding {
   // destination is [n_tiles][K/64][n_tile][64] so every (n tile, k block) is one
   // contiguous 128-byte-row tile a single TMA box can fetch.
   uint32_t K = 0, N = 0, n_tile = 0;
+  uint32_t K_src = 0;  // rows of the source when it has fewer than K (the rest packs as zeros)
   bool transposed = false;
   size_t src_bytes = 0;
 };

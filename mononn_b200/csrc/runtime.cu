@@ -188,7 +188,7 @@ int Runtime::load_plan(const Plan& plan) {
 
 // PACK_B: [n_tiles][K/64][n_tile][64], zero padded in N (host side of a weight's tiled copy)
 static void pack_weight(const ConstBinding& b, const std::vector<uint8_t>& src, std::vector<uint16_t>* packed) {
-  const uint32_t K = b.K, N = b.N, nt = b.n_tile, kb = K / 64;
+  const uint32_t K = b.K, N = b.N, nt = b.n_tile, kb = K / 64, Ks = b.K_src ? b.K_src : b.K;
   const uint32_t n_tiles = (N + nt - 1) / nt;
   packed->assign(static_cast<size_t>(n_tiles) * nt * K, 0);
   const uint16_t* w = reinterpret_cast<const uint16_t*>(src.data());
@@ -198,11 +198,13 @@ static void pack_weight(const ConstBinding& b, const std::vector<uint8_t>& src, 
         const uint32_t n = t * nt + r;
         if (n >= N) continue;
         uint16_t* d = &(*packed)[((static_cast<size_t>(t) * kb + k) * nt + r) * 64];
+        if (k * 64 >= Ks) continue;
+        const uint32_t take = std::min(64u, Ks - k * 64);  // source rows past Ks pack as zeros
         if (b.transposed) {
-          std::memcpy(d, w + static_cast<size_t>(n) * K + k * 64, 128);
+          std::memcpy(d, w + static_cast<size_t>(n) * Ks + k * 64, take * 2);
         } else {
           const uint16_t* s = w + static_cast<size_t>(k) * 64 * N + n;
-          for (uint32_t c = 0; c < 64; ++c) d[c] = s[static_cast<size_t>(c) * N];
+          for (uint32_t c = 0; c < take; ++c) d[c] = s[static_cast<size_t>(c) * N];
         }
       }
 }

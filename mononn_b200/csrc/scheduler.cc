@@ -198,7 +198,11 @@ int validate_plan(const Plan& P, std::string* err) {
       case OP_EMBED:
       case OP_ASSEMBLE:
         if (d.cols == 0 || d.cols % 4 || d.cols > 2048) return bad(n + "row length");
-        if (d.n_items != (d.rows + kRowsPerItem - 1) / kRowsPerItem) return bad(n + "item count");
+        if (d.flags & F_ROW_SPLIT) {
+          if (d.kind != OP_LAYERNORM || d.cols % 16 || d.cols > 1024 || (d.flags & (F_L2NORM | F_NO_NORM)))
+            return bad(n + "row split geometry");
+          if (d.n_items != (d.rows + kSplitRowsPerItem - 1) / kSplitRowsPerItem) return bad(n + "item count");
+        } else if (d.n_items != (d.rows + kRowsPerItem - 1) / kRowsPerItem) return bad(n + "item count");
         if (op.p[0].space == SPACE_NONE && op.q[2].space == SPACE_NONE) return bad(n + "no output buffer");
         if (op.p[6].space == SPACE_NONE && d.kind != OP_LAYERNORM) return bad(n + "no scale pointer");
         if (d.kind == OP_ASSEMBLE && (d.seq == 0 || d.k_col >= d.seq)) return bad(n + "token geometry");
@@ -221,8 +225,12 @@ int validate_plan(const Plan& P, std::string* err) {
         if (op.p[0].space == SPACE_NONE || op.p[1].space == SPACE_NONE) return bad(n + "buffers");
         break;
       case OP_PATCHIFY:
-        if (d.cols != d.heads * d.head_dim * d.q_col || d.vocab == 0 || d.k_col == 0)
-          return bad(n + "patch geometry");
+        if (d.K != d.heads * d.head_dim * d.q_col || d.cols < d.K || d.vocab == 0 || d.k_col == 0 ||
+            d.vocab % d.k_col || d.M == 0 || d.N == 0 || d.rows_per_batch >= d.head_dim || d.ldt >= d.q_col)
+          return bad(n + "window geometry");
+        // the last window may hang over the bottom / right edge (padding), never start beyond it
+        if ((d.vocab / d.k_col - 1) * d.M >= d.seq + d.rows_per_batch || (d.k_col - 1) * d.N >= d.batches + d.ldt)
+          return bad(n + "windows start outside the image");
         if (d.n_items != (d.rows + kRowsPerItem - 1) / kRowsPerItem) return bad(n + "item count");
         if (op.p[0].space == SPACE_NONE || op.p[1].space == SPACE_NONE) return bad(n + "buffers");
         break;
@@ -643,7 +651,8 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
       b.N = N;
       b.n_tile = n_tile;
       b.transposed = W.const_transposed;
-      b.src_bytes = static_cast<uint64_t>(K) * N * 2;
+      b.K_src = (W.rows && W.rows < K) ? W.rows : K;
+      b.src_bytes = static_cast<uint64_t>(b.K_src) * N * 2;
       b.bytes = static_cast<uint64_t>(n_tiles) * n_tile * K * 2;
       b.offset = const_top;
       const_top = align_up(const_top + b.bytes, 1024);
@@ -829,6 +838,14 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
             return MONONN_ERR_UNSUPPORTED;
           }
           d.n_items = (o.rows + kRowsPerItem - 1) / kRowsPerItem;
+          // Few rows (batch 1): one warp per row leaves most CTAs idle while each row's load ->
+          // reduce -> normalise -> store chain runs on a single warp. Four warps per row, two rows
+          // per item, when all items still fit one wave of the CTAs.
+          if (spec_in.row_split != 1 && !(o.flags & (F_L2NORM | F_NO_NORM)) && o.cols % 16 == 0 && o.cols <= 1024 &&
+              (o.rows + kSplitRowsPerItem - 1) / kSplitRowsPerItem <= P.grid) {
+            d.flags |= F_ROW_SPLIT;
+            d.n_items = (o.rows + kSplitRowsPerItem - 1) / kSplitRowsPerItem;
+          }
           po.p[0] = where[o.out];
           d.ldo = g.tensors[o.out].ld;
           po.p[1] = where[o.src];
@@ -870,6 +887,11 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
           d.q_col = o.q_col;
           d.k_col = o.k_col;
           d.vocab = o.vocab;
+          d.M = o.M;
+          d.N = o.N;
+          d.K = o.K;
+          d.rows_per_batch = o.pad_top;
+          d.ldt = o.pad_left;
           d.n_items = (o.rows + kRowsPerItem - 1) / kRowsPerItem;
           po.p[0] = where[o.out];
           d.ldo = g.tensors[o.out].ld;

@@ -78,6 +78,7 @@ std::string spec_to_json(const Plan& plan, uint32_t sm_count) {
   root.set("qkv_fusion", Json::string(plan.spec.qkv_fusion == 1 ? "off" : plan.spec.qkv_fusion == 2 ? "on" : "auto"));
   root.set("row_fusion", Json::string(plan.spec.row_fusion == 1 ? "off" : "on"));
   root.set("l2_hints", Json::string(plan.spec.l2_hints == 1 ? "off" : "on"));
+  root.set("row_split", Json::string(plan.spec.row_split == 1 ? "off" : "on"));
   root.set("barrier_arrive", Json::string(plan.spec.barrier_arrive == 1 || plan.cluster > 1 ? "cta" : "warp"));
   root.set("cluster_elewise_spec", Json::object());
   root.set("cluster_reduce_spec", Json::object());
@@ -200,6 +201,14 @@ std::string plan_to_json(const Plan& plan) {
         o.set("kb_per_bslot", Json::number(op.d.kb_per_bslot));
         o.set("out_mode", Json::number(op.d.out_mode));
       }
+      if (op.d.kind == OP_PATCHIFY) {
+        o.set("rows", Json::number(op.d.rows));
+        o.set("cols", Json::number(op.d.cols));
+        o.set("window_elements", Json::number(op.d.K));
+        o.set("window", Json::number(op.d.head_dim));
+        o.set("stride", Json::number(op.d.M));
+        o.set("pad", Json::number(op.d.rows_per_batch));
+      }
       Json ptrs = Json::array();
       for (int k = 0; k < 8; ++k) ptrs.arr.push_back(ref_json(op.p[k]));
       o.set("p", ptrs);
@@ -283,6 +292,8 @@ int spec_from_json(const std::string& text, TuningSpec* spec, std::string* err) 
       if (const Json* cl = rt->find("cluster_dim")) spec->cluster = static_cast<uint32_t>(cl->get_number("x", 1));
       if (const Json* b = rt->find("block_dim")) spec->block = static_cast<uint32_t>(b->get_number("x", kThreads));
     }
+  if (const Json* rs = root.find("row_split"))
+    if (rs->type == Json::String) spec->row_split = rs->str == "off" ? 1u : 0u;
   if (const Json* ba = root.find("barrier_arrive"))
     if (ba->type == Json::String) spec->barrier_arrive = ba->str == "cta" ? 1u : 2u;
   if (const Json* lh = root.find("l2_hints"))

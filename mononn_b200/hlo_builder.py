@@ -426,14 +426,17 @@ def _preln_blocks(cfg: EncoderConfig, comps: list, entry: list, const, x: str, c
 
 def vit_hlo(cfg: EncoderConfig) -> tuple[str, dict[str, str]]:
     """HLO text of the pre-LN vision encoder (ViT) of `cfg`: NCHW f32 pixels, patch embedding as
-    a ``__cudnn$convForward`` custom-call on the NHWC f16 image (window = stride = patch;
+    a ``__cudnn$convForward`` custom-call on the NHWC f16 image (window = stride = patch, or an
+    overlapping zero-padded window when the configuration sets ``patch_stride`` / ``patch_pad``;
     mononn_engine/parser/ir_parser_fused.cc:749-823), class token + learned positions, pre-LN
     blocks, final LayerNorm (model of examples/utils/save_model.py:76-82)."""
     B, S, H, F, NH = cfg.batch, cfg.seq, cfg.hidden, cfg.ffn, cfg.heads
     D, T, C, IMG, PS = H // NH, cfg.batch * cfg.seq, cfg.channels, cfg.image, cfg.patch
-    G = IMG // PS
+    G = cfg.patch_grid
     P = G * G
     assert S == P + 1
+    ST, PAD = cfg.patch_stride or PS, cfg.patch_pad
+    window = f"size={PS}x{PS} stride={ST}x{ST}" + (f" pad={PAD}_{PAD}x{PAD}_{PAD}" if PAD else "")
     comps: list[str] = [_REGIONS]
     entry: list[str] = []
     names: dict[str, str] = {}
@@ -461,7 +464,7 @@ def vit_hlo(cfg: EncoderConfig) -> tuple[str, dict[str, str]]:
     conv_cfg = json.dumps(json.dumps({"conv_result_scale": 1, "side_input_scale": 0, "activation_mode": "0",
                                       "tensor_ops_enabled": True}, separators=(",", ":")))
     entry.append(f"  %conv.patch = ({conv_s}, u8[0]{{0}}) custom-call({nhwc_s} %fusion.nhwc, "
-                 f"{_shape('f16', [H, PS, PS, C])} %{wp}), window={{size={PS}x{PS} stride={PS}x{PS}}}, "
+                 f"{_shape('f16', [H, PS, PS, C])} %{wp}), window={{{window}}}, "
                  f"dim_labels=b01f_o01i->b01f, custom_call_target=\"__cudnn$convForward\", backend_config={conv_cfg}")
     entry.append(f"  %gte.patch = {conv_s} get-tuple-element(({conv_s}, u8[0]{{0}}) %conv.patch), index=0")
     h_BPH, h_BSH, h_B1H, h_SH = (_shape("f16", [B, P, H]), _shape("f16", [B, S, H]), _shape("f16", [B, 1, H]),

@@ -33,6 +33,9 @@ class EncoderConfig:
     image: int = 0
     patch: int = 0
     channels: int = 3
+    # patch convolution with overlapping windows: stride (0 = the patch size) and zero padding on every side
+    patch_stride: int = 0
+    patch_pad: int = 0
 
     def to_json(self) -> str:
         return json.dumps(dataclasses.asdict(self))
@@ -40,6 +43,11 @@ class EncoderConfig:
     @property
     def tokens(self) -> int:
         return self.batch * self.seq
+
+    @property
+    def patch_grid(self) -> int:
+        """Output positions of the patch convolution along one image side."""
+        return (self.image + 2 * self.patch_pad - self.patch) // (self.patch_stride or self.patch) + 1
 
 
 def bert_base(batch: int = 1, seq: int = 128) -> EncoderConfig:
@@ -121,10 +129,14 @@ def vit_base(batch: int = 1) -> EncoderConfig:
 
 
 def vit_tiny(batch: int = 1, image: int = 32, patch: int = 16, layers: int = 1, hidden: int = 64,
-             ffn: int = 256) -> EncoderConfig:
-    n = (image // patch) ** 2 + 1
+             ffn: int = 256, patch_stride: int = 0, patch_pad: int = 0) -> EncoderConfig:
+    """Small vision encoder. `patch_stride` / `patch_pad` turn the patch embedding into an
+    overlapping, zero-padded convolution (a strided NHWC fprop as the reference's
+    mononn_engine/core/op_impl/conv_impl.cc:252-345 accepts)."""
+    n = ((image + 2 * patch_pad - patch) // (patch_stride or patch) + 1) ** 2 + 1
     return EncoderConfig(model="vit", layers=layers, hidden=hidden, heads=hidden // 64, ffn=ffn, batch=batch,
-                         seq=n, image=image, patch=patch, channels=3, max_pos=n, vocab=0, types=0)
+                         seq=n, image=image, patch=patch, channels=3, max_pos=n, vocab=0, types=0,
+                         patch_stride=patch_stride, patch_pad=patch_pad)
 
 
 def vit_weight_shapes(cfg: EncoderConfig) -> dict[str, tuple[int, ...]]:

@@ -217,13 +217,24 @@ def opt_decoder_torch(cfg, w, inputs, threads=0):
 
 def vit_patches(cfg, pixels):
     """[B, C, H, W] -> [B * patches, ky * kx * C]: the operand of the patch-embedding
-    convolution (stride = window, cross-correlation, NHWC/KRSC as the reference's conv,
+    convolution (any stride, symmetric zero padding, cross-correlation, NHWC/KRSC as the reference's conv,
     mononn_engine/core/op_impl/conv_impl.cc:252-345) written as a matrix product."""
     b, c, hh, ww = pixels.shape
     p = cfg.patch
-    g = hh // p
-    x = pixels.reshape(b, c, g, p, g, p).transpose(0, 2, 4, 3, 5, 1)  # b, gy, gx, ky, kx, c
-    return x.reshape(b * g * g, p * p * c)
+    st, pad = getattr(cfg, "patch_stride", 0) or p, getattr(cfg, "patch_pad", 0)
+    if st == p and pad == 0:
+        g = hh // p
+        x = pixels.reshape(b, c, g, p, g, p).transpose(0, 2, 4, 3, 5, 1)  # b, gy, gx, ky, kx, c
+        return x.reshape(b * g * g, p * p * c)
+    # overlapping / zero-padded windows: one output position at a time
+    xp = np.zeros((b, c, hh + 2 * pad, ww + 2 * pad), pixels.dtype)
+    xp[:, :, pad:pad + hh, pad:pad + ww] = pixels
+    gy, gx = (hh + 2 * pad - p) // st + 1, (ww + 2 * pad - p) // st + 1
+    out = np.empty((b, gy, gx, p, p, c), pixels.dtype)
+    for y in range(gy):
+        for x in range(gx):
+            out[:, y, x] = xp[:, :, y * st:y * st + p, x * st:x * st + p].transpose(0, 2, 3, 1)
+    return out.reshape(b * gy * gx, p * p * c)
 
 
 def vit_encoder(cfg, w, inputs, return_all=False):

@@ -108,6 +108,20 @@ def test_vit_shapes_against_oracle(cfg):
     assert_parity(run_vit(cfg, w, inp), R.vit_encoder(cfg, w, inp), "ViT shape case")
 
 
+@pytest.mark.parametrize("cfg", [
+    vit_tiny(batch=2, image=32, patch=7, patch_stride=4, patch_pad=3, hidden=128),  # 147-element windows -> 192
+    vit_tiny(batch=1, image=48, patch=16, patch_stride=8),                          # overlap, no padding
+    vit_tiny(batch=3, image=30, patch=8, patch_stride=8, patch_pad=1),              # padding only, 4x4 windows
+], ids=lambda c: f"b{c.batch}img{c.image}k{c.patch}s{c.patch_stride}p{c.patch_pad}")
+def test_strided_padded_patch_convolution_against_oracle(cfg):
+    """The convolution in general form (stride != window, zero padding, a window that is not a
+    whole number of 64-element blocks): window rows gathered with zeros at the edges, GEMM
+    against the zero-extended filter."""
+    w = make_weights(cfg, 43, stress=True)
+    inp = make_vit_inputs(cfg, 43)
+    assert_parity(run_vit(cfg, w, inp), R.vit_encoder(cfg, w, inp), "overlapping patch convolution")
+
+
 def test_vit_base_full_size():
     cfg = vit_base()
     w = make_weights(cfg, 1236, stress=True)

@@ -176,3 +176,23 @@ def test_encoder_decoder_structure(lib_built):
           o["name"].endswith(("_k", "_v"))]
     assert len(kv) == 12 and len(set(kv)) >= 2     # twelve projections, more than one stage
     assert abs(full["algorithmic_flops"] / 1e9 - 11.88) < 0.1
+
+
+def test_overlapping_padded_patch_convolution_lowers_to_windows_and_a_gemm(lib_built):
+    """A 7x7 window moved by 4 with 3 pixels of zero padding (an overlapping patch stem): the
+    window rows are 147 elements, written as 192 (whole 64-element k blocks) with zeros behind
+    them, and the filter constant keeps its own 147-element rows (zero-extended when packed)."""
+    cfg = vit_tiny(batch=2, image=32, patch=7, patch_stride=4, patch_pad=3, hidden=128)
+    assert cfg.patch_grid == 8 and cfg.seq == 65
+    text = vit_hlo(cfg)[0]
+    assert "window={size=7x7 stride=4x4 pad=3_3x3_3}" in text
+    plan = plan_of(text)
+    (win,) = ops_of(plan, "patchify")
+    assert (win["rows"], win["cols"], win["window_elements"]) == (2 * 64, 192, 147)
+    assert (win["window"], win["stride"], win["pad"]) == (7, 4, 3)
+    gemm = [o for o in ops_of(plan, "gemm") if o["name"] == "conv_patch"][0]
+    assert (gemm["M"], gemm["N"], gemm["K"]) == (128, 128, 192)
+    with pytest.raises(capi.MononnError, match="dilated"):
+        describe("hlo", text.replace("pad=3_3x3_3", "pad=3_3x3_3 rhs_dilate=2x2"))
+    with pytest.raises(capi.MononnError, match="inconsistent"):
+        describe("hlo", text.replace("stride=4x4", "stride=3x3"))

@@ -122,3 +122,21 @@ def test_weights_are_f16_representable_and_seeded():
         assert np.array_equal(a[k], b[k])
         assert np.array_equal(a[k].astype(np.float16).astype(np.float32), a[k])
     assert not np.array_equal(make_weights(cfg, 10)["embeddings.word"], a["embeddings.word"])
+
+
+@pytest.mark.parametrize("patch,stride,pad,image", [(7, 4, 3, 32), (16, 8, 0, 48), (8, 8, 1, 30), (16, 16, 0, 32)])
+def test_window_rows_times_filter_is_the_convolution(patch, stride, pad, image):
+    """The oracle writes the patch convolution as window rows times the [out, ky*kx*c] filter;
+    pinned here against torch's conv2d (cross-correlation, zero padding) on the same numbers."""
+    import torch
+    from mononn_b200.models import vit_tiny
+    cfg = vit_tiny(batch=2, image=image, patch=patch, patch_stride=stride, patch_pad=pad)
+    rng = np.random.default_rng(5)
+    px = rng.uniform(-1, 1, (2, 3, image, image)).astype(np.float32)
+    wt = rng.normal(0, 0.1, (cfg.hidden, patch, patch, 3)).astype(np.float32)     # [out, ky, kx, in]
+    got = R.vit_patches(cfg, px) @ wt.reshape(cfg.hidden, -1).T
+    want = torch.nn.functional.conv2d(torch.from_numpy(px), torch.from_numpy(wt).permute(0, 3, 1, 2).contiguous(),
+                                      stride=stride, padding=pad)               # [B, out, gy, gx]
+    g = cfg.patch_grid
+    assert want.shape == (2, cfg.hidden, g, g)
+    np.testing.assert_allclose(got, want.permute(0, 2, 3, 1).reshape(-1, cfg.hidden).numpy(), rtol=1e-4, atol=1e-4)
