@@ -222,6 +222,11 @@ __device__ __forceinline__ uint32_t ld_acquire_cta_smem(const uint32_t* p) {
 __device__ __forceinline__ void fence_acq_rel_gpu() {
   asm volatile("fence.acq_rel.gpu;" ::: "memory");
 }
+__device__ __forceinline__ uint32_t atom_add_acq_rel_cta_smem(uint32_t* p, uint32_t v) {
+  uint32_t old;
+  asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(smem_u32(p)), "r"(v) : "memory");
+  return old;
+}
 __device__ __forceinline__ void red_release_gpu_add(uint32_t* p, uint32_t v) {
   asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -256,6 +261,8 @@ struct Ctrl {
   uint32_t tmem_base;
   uint32_t abort_flag;
   uint32_t barriers_seen;  // grid barriers of this launch the CTA's poller has observed (monotonic)
+  uint32_t warps_done;     // epilogue warps that finished a stage (monotonic; every eighth arrives for the CTA)
+  uint32_t items_done[2];  // per accumulator buffer: epilogue warps that finished a GEMM item a row op waits for
   uint32_t pad_;
   alignas(16) float bias_tile[2][256];  // bias of the current GEMM tile, double buffered across items
   float mask_row[384];      // additive key mask of the current attention tile (log2 units)
@@ -396,7 +403,7 @@ __device__ __forceinline__ bool grid_wait(const Ctx& c, uint32_t stage, uint32_t
   const KernelParams& P = *c.P;
   if (stage == P.stage_begin) return true;
   const uint32_t target =
-      P.epoch_base + (stage - P.stage_begin) * (gridDim.x / P.cluster) * (P.warp_arrive ? kSimtWarps : 1u);
+      P.epoch_base + (stage - P.stage_begin) * (gridDim.x / P.cluster) * (P.warp_arrive == 1u ? kSimtWarps : 1u);
   bool ok = true;
   if (static_cast<int32_t>(ld_relaxed_gpu(P.barrier) - target) >= 0) {
     acquire_after_poll(P.barrier);
@@ -1939,16 +1946,23 @@ __device__ void role_simt(Ctx c, uint32_t tmem_base, uint32_t tid_in_group) {
           gemm_epilogue(op, it.local, tmem_base + buf * kAccCols, quarter, half, lane, bias_s,
                         c.store_stage + widx * 2048u);
           tc_fence_before();
+          // A row op of this stage may wait for this item. The warps count themselves per
+          // accumulator buffer in shared memory before they free the buffer (so the counts of two
+          // items never mix: the buffer is not filled again until all eight have counted), and the
+          // warp that counts last publishes the item: its release at GPU scope is cumulative over
+          // the reductions of the other seven, observed through the counter. (Eight global arrivals
+          // per item, one per warp, measured 6 us slower per inference.)
+          bool last_of_item = false;
+          if (op.flag != 0) {
+            __syncwarp();
+            if (lane == 0)
+              last_of_item = (atom_add_acq_rel_cta_smem(&c.ctrl->items_done[buf], 1u) & (kSimtWarps - 1u)) ==
+                             kSimtWarps - 1u;
+          }
           warp_arrive(&c.ctrl->acc_empty[buf]);
           ++acc_cnt;
           a_cnt += op.kb_per_split;
-          if (op.flag != 0) {
-            // a row op of this stage waits for this item: publish the reductions of all eight
-            // warps (ordered by the group barrier), then count the item. (Eight arrivals per item,
-            // one per warp without the group barrier, measured 6 us slower per inference.)
-            WAIT_OR_RETURN(group_sync(c, 0x404));
-            if (tid_in_group == 0) red_release_gpu_add(reinterpret_cast<uint32_t*>(op.flag), 1u);
-          }
+          if (last_of_item) red_release_gpu_add(reinterpret_cast<uint32_t*>(op.flag), 1u);
           break;
         }
         case OP_ATTENTION:
@@ -1990,11 +2004,24 @@ __device__ void role_simt(Ctx c, uint32_t tmem_base, uint32_t tid_in_group) {
     // between the store and the load. It sits on the reader side (the activation producer
     // issues fence.proxy.async after it has acquired the barrier): a second fence here, on
     // all the writers, cost about half a microsecond per stage.
-    if (P.warp_arrive) {
+    if (P.warp_arrive == 1u) {
       // every warp publishes its own stores (a warp stores whole rows or its own reductions) and
       // arrives for itself: no CTA-wide sync in front of the release
       __syncwarp();
       if (lane == 0) red_release_gpu_add(P.barrier, 1u);
+      if (tid_in_group == 0) trace(P, s, TR_SIMT_ARRIVED);
+      continue;
+    }
+    if (P.warp_arrive == 2u) {
+      // every warp counts itself in shared memory (acquire + release at CTA scope) and moves on;
+      // the warp that counts last arrives for the CTA. Its release at GPU scope is cumulative over
+      // the other warps' stores, which it observed through the counter. One global arrival per
+      // CTA and still no CTA-wide sync in front of it.
+      __syncwarp();
+      if (lane == 0) {
+        const uint32_t seen = atom_add_acq_rel_cta_smem(&c.ctrl->warps_done, 1u);
+        if ((seen & (kSimtWarps - 1u)) == kSimtWarps - 1u) red_release_gpu_add(P.barrier, 1u);
+      }
       if (tid_in_group == 0) trace(P, s, TR_SIMT_ARRIVED);
       continue;
     }
@@ -2064,6 +2091,8 @@ mononn_megakernel(const __grid_constant__ KernelParams P) {
     mbar_init(smem_u32(&ctrl->cl_bar), P.cluster);
     ctrl->abort_flag = 0;
     ctrl->barriers_seen = 0;
+    ctrl->warps_done = 0;
+    ctrl->items_done[0] = ctrl->items_done[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {

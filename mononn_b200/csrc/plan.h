@@ -46,8 +46,9 @@ struct TuningSpec {
   // L2 eviction-priority hints on the TMA loads: 0 / 2 weights evict-first and GEMM activation
   // tiles evict-last, 1 none
   uint32_t l2_hints = 0;
-  // grid-barrier arrival: 0 / 2 one per epilogue warp (each releases its own stores), 1 one per
-  // CTA after a CTA-wide sync (always the case inside a cluster launch)
+  // grid-barrier arrival: 0 / 3 one per CTA by the epilogue warp that finishes the stage last (the
+  // warps count themselves in shared memory), 2 one per epilogue warp (each releases its own
+  // stores), 1 one per CTA after a CTA-wide sync (always the case inside a cluster launch)
   uint32_t barrier_arrive = 0;
   // 0 / 2: a LayerNorm with few rows shares each row among four warps; 1: always one warp per row
   uint32_t row_split = 0;

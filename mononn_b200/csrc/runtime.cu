@@ -410,7 +410,7 @@ int Runtime::launch(void* const* args, int n, void* stream, uint32_t stage_begin
   kp.flag_epoch = ++flag_epoch_;
   kp.cluster = plan_.cluster;
   kp.l2_hints = plan_.spec.l2_hints == 1 ? 0u : 1u;
-  kp.warp_arrive = warp_arrive() ? 1u : 0u;
+  kp.warp_arrive = arrive_mode();
   void* kargs[1] = {&kp};
   if (plan_.cluster <= 1) {
     CUDA_TRY(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(mononn_megakernel),
@@ -422,7 +422,7 @@ int Runtime::launch(void* const* args, int n, void* stream, uint32_t stage_begin
     fill_cluster_launch(&cfg, attrs, static_cast<cudaStream_t>(stream));
     CUDA_TRY(cudaLaunchKernelExC(&cfg, reinterpret_cast<const void*>(mononn_megakernel), kargs));
   }
-  epoch_ += (stage_end - stage_begin) * (plan_.grid / plan_.cluster) * (warp_arrive() ? kSimtWarps : 1u);
+  epoch_ += (stage_end - stage_begin) * (plan_.grid / plan_.cluster) * (arrive_mode() == 1u ? kSimtWarps : 1u);
   if (stamps) n_stamp_stages_ = stage_end - stage_begin;
   return MONONN_OK;
 }

@@ -68,7 +68,12 @@ class Runtime {
   void skew_epoch(uint32_t n) { epoch_ += n; }
 
   // Per-warp barrier arrival is the default; a cluster launch arrives per CTA through the cluster.
-  bool warp_arrive() const { return plan_.cluster <= 1 && plan_.spec.barrier_arrive != 1; }
+  // 0: one arrival per CTA after a CTA-wide sync (always with clusters), 1: one per epilogue warp,
+  // 2: one per CTA by the warp that finishes last
+  uint32_t arrive_mode() const {
+    if (plan_.cluster > 1 || plan_.spec.barrier_arrive == 1) return 0;
+    return plan_.spec.barrier_arrive == 2 ? 1u : 2u;
+  }
   unsigned timeout_us = 2000000;
   int pack_threads = 0;  // host threads that re-pack weights when a plan is (re)loaded; 0 = all cores
   const std::map<std::string, std::vector<uint8_t>>& host_constants() const { return host_consts_; }

@@ -79,7 +79,9 @@ std::string spec_to_json(const Plan& plan, uint32_t sm_count) {
   root.set("row_fusion", Json::string(plan.spec.row_fusion == 1 ? "off" : "on"));
   root.set("l2_hints", Json::string(plan.spec.l2_hints == 1 ? "off" : "on"));
   root.set("row_split", Json::string(plan.spec.row_split == 1 ? "off" : "on"));
-  root.set("barrier_arrive", Json::string(plan.spec.barrier_arrive == 1 || plan.cluster > 1 ? "cta" : "warp"));
+  root.set("barrier_arrive", Json::string(plan.spec.barrier_arrive == 1 || plan.cluster > 1
+                                              ? "cta"
+                                              : (plan.spec.barrier_arrive == 2 ? "warp" : "last")));
   root.set("cluster_elewise_spec", Json::object());
   root.set("cluster_reduce_spec", Json::object());
   Json gemms = Json::object();
@@ -295,7 +297,7 @@ int spec_from_json(const std::string& text, TuningSpec* spec, std::string* err) 
   if (const Json* rs = root.find("row_split"))
     if (rs->type == Json::String) spec->row_split = rs->str == "off" ? 1u : 0u;
   if (const Json* ba = root.find("barrier_arrive"))
-    if (ba->type == Json::String) spec->barrier_arrive = ba->str == "cta" ? 1u : 2u;
+    if (ba->type == Json::String) spec->barrier_arrive = ba->str == "cta" ? 1u : (ba->str == "warp" ? 2u : 3u);
   if (const Json* lh = root.find("l2_hints"))
     if (lh->type == Json::String) spec->l2_hints = lh->str == "on" ? 2u : 1u;
   if (const Json* rf = root.find("row_fusion"))

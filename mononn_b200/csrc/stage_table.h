@@ -180,7 +180,9 @@ struct KernelParams {
   uint32_t cluster;      // CTAs per cluster of this launch (1: no cluster-scoped arrival)
   uint32_t l2_hints;     // 1: weight tiles are loaded evict-first, GEMM activation tiles evict-last (default)
   uint32_t warp_arrive;  // 1: every epilogue warp arrives at the grid barrier for itself (8 arrivals per
-                         // CTA and stage, no CTA-wide sync before the arrival); 0: one arrival per CTA
+                         // CTA and stage, no CTA-wide sync before the arrival); 2: the warps count themselves
+                         // in shared memory and the last one arrives for the CTA; 0: one arrival per CTA
+                         // after a CTA-wide sync
   uint32_t flag_epoch;   // launches that have added to the arrival counters since they were cleared,
                          // this one included (row ops wait for flag_epoch * their GEMM items)
 };

@@ -148,6 +148,7 @@ int tune_module(mononn_module* m, void* const* args, int n, void* stream) {
         {"row_fusion off", &TuningSpec::row_fusion, 1u},
         {"l2_hints off", &TuningSpec::l2_hints, 1u},
         {"barrier_arrive cta", &TuningSpec::barrier_arrive, 1u},
+        {"barrier_arrive warp", &TuningSpec::barrier_arrive, 2u},
         {"row_split off", &TuningSpec::row_split, 1u},
     };
     for (const Structural& c : choices) {
