@@ -376,6 +376,35 @@ def stage_class(stage: dict) -> str:
     return "+".join(kinds)
 
 
+def stage_report(mod):
+    """Per operator class, the time from the in-kernel event trace of one launch, and the share of
+    the kernel between the last CTA finishing a stage's work and the first CTA past the barrier."""
+    import numpy as np
+    plan = mod.plan()
+    for _ in range(5):
+        mod.launch()
+    mod.trace()
+    tr = mod.trace()
+    tr = np.where(tr == 0, np.nan, tr)
+    n_st = tr.shape[1]
+    ready = np.nanmin(tr[:, :, 0], axis=0)            # first CTA past the barrier
+    done = np.nanmax(tr[:, :, 1], axis=0)             # last CTA finished the stage's work
+    total = float(np.nanmax(tr[:, :, 2]) - ready[0])
+    per_class: dict[str, list[float]] = {}
+    sync = 0.0
+    for s_ in range(n_st):
+        end = ready[s_ + 1] if s_ + 1 < n_st else np.nanmax(tr[:, s_, 2])
+        sync += float(end - done[s_])
+        acc = per_class.setdefault(stage_class(plan["stages"][s_]), [0, 0.0, 0.0])
+        acc[0] += 1
+        acc[1] += float(end - ready[s_])
+        acc[2] += float(end - done[s_])
+    classes = {k: {"stages": v[0], "us_per_stage": v[1] / v[0] / 1e3, "share": v[1] / total,
+                   "barrier_us_per_stage": v[2] / v[0] / 1e3} for k, v in per_class.items()}
+    return {"diagnostic": "stage_report", "kernel_us": total / 1e3, "stages": n_st,
+            "barrier_share": sync / total, "classes": classes}
+
+
 def run_diagnostics(args):
     """Not a bench line. `--stages A:B` launches only stages [A, B) of the headline workload
     `--steps` times (so that a profiler can capture one operator class alone) and prints their
@@ -411,28 +440,7 @@ def run_diagnostics(args):
                           "classes": [stage_class(st) for st in plan["stages"][a:b]],
                           "us_per_launch": e0.elapsed_time(e1) * 1e3 / args.steps, "launches": args.steps}))
     else:
-        for _ in range(5):
-            mod.launch()
-        mod.trace()
-        tr = mod.trace()
-        tr = np.where(tr == 0, np.nan, tr)
-        n_st = tr.shape[1]
-        ready = np.nanmin(tr[:, :, 0], axis=0)            # first CTA past the barrier
-        done = np.nanmax(tr[:, :, 1], axis=0)             # last CTA finished the stage's work
-        total = float(np.nanmax(tr[:, :, 2]) - ready[0])
-        per_class: dict[str, list[float]] = {}
-        sync = 0.0
-        for s_ in range(n_st):
-            end = ready[s_ + 1] if s_ + 1 < n_st else np.nanmax(tr[:, s_, 2])
-            sync += float(end - done[s_])
-            acc = per_class.setdefault(stage_class(plan["stages"][s_]), [0, 0.0, 0.0])
-            acc[0] += 1
-            acc[1] += float(end - ready[s_])
-            acc[2] += float(end - done[s_])
-        classes = {k: {"stages": v[0], "us_per_stage": v[1] / v[0] / 1e3, "share": v[1] / total,
-                       "barrier_us_per_stage": v[2] / v[0] / 1e3} for k, v in per_class.items()}
-        print(json.dumps({"diagnostic": "stage_report", "kernel_us": total / 1e3, "stages": n_st,
-                          "barrier_share": sync / total, "classes": classes}))
+        print(json.dumps(stage_report(mod)))
     mod.close()
 
 
@@ -491,6 +499,8 @@ def run_config(args):
     torch.cuda.synchronize()
     mod.status()
     us = sum(e0.elapsed_time(e1) for e0, e1 in ev) * 1e3 / steps
+    if args.stage_report:
+        print(json.dumps(dict(stage_report(mod), config=name)))
     alg_bytes, alg_flops = mod.cost()
     peak_gbs, kind = measured_hbm_peak()
     try:

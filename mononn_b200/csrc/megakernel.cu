@@ -351,20 +351,38 @@ __device__ __forceinline__ bool mbar_wait(const Ctx& c, uint64_t* bar, uint32_t 
   return mbar_wait_slow(c.P, c.ctrl, b, parity, c.stage, where);
 }
 
-// After a relaxed poll has seen the count, one acquire load of the same counter gives the
-// ordering: it observes the last arrival (a release atomic) and through the chain of atomics
-// all earlier ones. A full fence.acq_rel.gpu in its place measured 32 us slower per inference
-// (it also waits for this thread's own outstanding stores).
+// The counters are polled with acquire loads: the load that sees the count observes the last
+// arrival (a release atomic) and through the chain of atomics all earlier ones, so nothing else
+// is needed before the data is read. Measured per inference against this: relaxed polls plus one
+// acquire load at the end +7 us (one more L2 round trip per wait), a fence.acq_rel.gpu after a
+// relaxed poll +39 us (it also waits for this thread's own outstanding stores). A pause between
+// polls (__nanosleep) only delays the detection (+2 us at 32 ns).
+#ifndef MONONN_POLL_ACQUIRE
+#define MONONN_POLL_ACQUIRE 1  // 0: relaxed polls, then one acquire load
+#endif
+__device__ __forceinline__ uint32_t poll_load(const uint32_t* p) {
+#if MONONN_POLL_ACQUIRE
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+#else
+  return ld_relaxed_gpu(p);
+#endif
+}
 __device__ __forceinline__ void acquire_after_poll(const uint32_t* p) {
+#if MONONN_POLL_ACQUIRE
+  (void)p;
+#else
   uint32_t v;
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   (void)v;
+#endif
 }
 #ifndef MONONN_ALL_POLL
 #define MONONN_ALL_POLL 0  // 1: every epilogue warp polls the global counter itself
 #endif
 #ifndef MONONN_POLL_SLEEP
-#define MONONN_POLL_SLEEP 32
+#define MONONN_POLL_SLEEP 0
 #endif
 // Bounded wait until every CTA has arrived for all stages before `stage`. Two threads per CTA
 // poll the global counter: the activation producer (its first tile load is the critical path of
@@ -378,7 +396,7 @@ __device__ __noinline__ bool grid_wait_slow(const KernelParams* P, Ctrl* ctrl, u
   const uint64_t limit = static_cast<uint64_t>(P->timeout_us) * 1000ull;
   uint32_t it = 0;
   for (;;) {
-    if (static_cast<int32_t>(ld_relaxed_gpu(P->barrier) - target) >= 0) {
+    if (static_cast<int32_t>(poll_load(P->barrier) - target) >= 0) {
       acquire_after_poll(P->barrier);
       return true;
     }
@@ -405,7 +423,7 @@ __device__ __forceinline__ bool grid_wait(const Ctx& c, uint32_t stage, uint32_t
   const uint32_t target =
       P.epoch_base + (stage - P.stage_begin) * (gridDim.x / P.cluster) * (P.warp_arrive == 1u ? kSimtWarps : 1u);
   bool ok = true;
-  if (static_cast<int32_t>(ld_relaxed_gpu(P.barrier) - target) >= 0) {
+  if (static_cast<int32_t>(poll_load(P.barrier) - target) >= 0) {
     acquire_after_poll(P.barrier);
   } else {
     ok = grid_wait_slow(c.P, c.ctrl, target, stage, where);
@@ -467,7 +485,7 @@ __device__ __noinline__ bool flag_wait_slow(const KernelParams* P, Ctrl* ctrl, c
   const uint64_t limit = static_cast<uint64_t>(P->timeout_us) * 1000ull;
   uint32_t it = 0;
   for (;;) {
-    if (static_cast<int32_t>(ld_relaxed_gpu(flag) - target) >= 0) {
+    if (static_cast<int32_t>(poll_load(flag) - target) >= 0) {
       acquire_after_poll(flag);
       return true;
     }
@@ -494,7 +512,7 @@ __device__ __forceinline__ bool flag_wait_warp(const Ctx& c, const OpDesc& op, u
   if ((threadIdx.x & 31u) == 0u) {
     const uint32_t* flag = reinterpret_cast<const uint32_t*>(op.flag);
     const uint32_t target = c.P->flag_epoch * op.flag_target;
-    if (static_cast<int32_t>(ld_relaxed_gpu(flag) - target) >= 0) {
+    if (static_cast<int32_t>(poll_load(flag) - target) >= 0) {
       acquire_after_poll(flag);
     } else {
       ok = flag_wait_slow(c.P, c.ctrl, flag, target, c.stage, where);

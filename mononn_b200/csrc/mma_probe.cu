@@ -17,6 +17,7 @@
 #include <stdint.h>
 
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "../../include/mononn.h"
@@ -47,6 +48,28 @@ __device__ __forceinline__ void mma(uint32_t d, uint64_t a, uint64_t b, uint32_t
       "l"(a), "l"(b), "r"(idesc), "r"(acc), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
       : "memory");
 }
+// A operand read from tensor memory (128 lanes x 8 columns hold one 128 x 16 f16 slice)
+__device__ __forceinline__ void mma_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n\t}" ::"r"(d),
+      "r"(a_tmem), "l"(b), "r"(idesc), "r"(acc), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+// The same instruction without the optional disable-output-lane vector
+__device__ __forceinline__ void mma_plain(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d),
+      "l"(a), "l"(b), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ uint32_t elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred)::"memory");
+  return pred;
+}
 __device__ __forceinline__ void commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                : "memory");
@@ -64,8 +87,18 @@ __device__ __forceinline__ uint32_t try_wait(uint32_t bar, uint32_t parity) {
 
 // mode bit 0: a commit (to a barrier nobody waits on) after every four instructions
 // mode bit 1: a try_wait on an already completed barrier + tcgen05.fence before every four
+// mode bit 2: M = 64 instead of 128 (half of the A rows per instruction)
+// mode bit 3: the A operand is read from tensor memory (columns 448..479) instead of shared memory
+// mode bit 4: the instruction is written without the disable-output-lane vector
+// mode bit 5: the whole first warp runs the loop converged and one elected lane issues (operands
+//             can then live in uniform registers)
+// mode bit 6: the operand descriptors are rebuilt for every group of four from a ring-slot index
+//             (slot stride `slot_stride` bytes, 0 from the host: same data, but nothing the compiler
+//             can hoist), as a main loop over a ring of tiles has to
+// The mode is a template parameter: a run-time test inside the loop would be part of what is timed.
+template <uint32_t mode>
 __global__ void __launch_bounds__(128, 1)
-mma_probe_kernel(ProbeOut* out, uint32_t n, uint32_t count, uint32_t accumulators, uint32_t mode) {
+mma_probe_kernel(ProbeOut* out, uint32_t n, uint32_t count, uint32_t accumulators, uint32_t slot_stride) {
   extern __shared__ uint8_t raw[];
   __shared__ uint64_t bar_done, bar_side, bar_ready;
   __shared__ uint32_t tmem_slot;
@@ -90,9 +123,11 @@ mma_probe_kernel(ProbeOut* out, uint32_t n, uint32_t count, uint32_t accumulator
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&tmem_slot);
-  if (threadIdx.x == 0) {
-    const uint32_t idesc = (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24);
-    const uint64_t ad = desc_sw128(s_u32(base)), bd = desc_sw128(s_u32(base) + 16384u);
+  if ((mode & 32u) ? (threadIdx.x < 32) : (threadIdx.x == 0)) {
+    const bool issuer = (mode & 32u) ? (elect_one() != 0u) : true;
+    const uint32_t m = (mode & 4u) ? 64u : 128u;
+    const uint32_t idesc = (1u << 4) | ((n >> 3) << 17) | ((m >> 4) << 24);
+    uint64_t ad = desc_sw128(s_u32(base)), bd = desc_sw128(s_u32(base) + 16384u);
     const uint32_t acc_stride = 512u / accumulators;
     const unsigned long long t0 = clock64();
     uint64_t g0;
@@ -104,12 +139,26 @@ mma_probe_kernel(ProbeOut* out, uint32_t n, uint32_t count, uint32_t accumulator
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       }
       const uint32_t d = tmem + ((i >> 2) % accumulators) * acc_stride;
+      if (mode & 64u) {
+        ad = desc_sw128(s_u32(base) + ((i >> 2) % 6u) * slot_stride);
+        bd = desc_sw128(s_u32(base) + 16384u + ((i >> 2) % 3u) * slot_stride);
+      }
 #pragma unroll
-      for (uint32_t k = 0; k < 4; ++k) mma(d, ad + 2u * k, bd + 2u * k, idesc, (i | k) != 0u);
-      if (mode & 1u) commit(s_u32(&bar_side));
+      for (uint32_t k = 0; k < 4; ++k) {
+        if (issuer) {
+          if (mode & 8u) {
+            mma_ts(d, tmem + 448u + 8u * k, bd + 2u * k, idesc, (i | k) != 0u);
+          } else if (mode & 16u) {
+            mma_plain(d, ad + 2u * k, bd + 2u * k, idesc, (i | k) != 0u);
+          } else {
+            mma(d, ad + 2u * k, bd + 2u * k, idesc, (i | k) != 0u);
+          }
+        }
+      }
+      if ((mode & 1u) && issuer) commit(s_u32(&bar_side));
     }
     const unsigned long long t1 = clock64();
-    commit(s_u32(&bar_done));
+    if (issuer) commit(s_u32(&bar_done));
     uint32_t ok = 0;
     for (uint32_t it = 0; it < 20000000u && !ok; ++it) ok = try_wait(s_u32(&bar_done), 0);
     const unsigned long long t2 = clock64();
@@ -121,7 +170,7 @@ mma_probe_kernel(ProbeOut* out, uint32_t n, uint32_t count, uint32_t accumulator
     o.ns_done = g1 - g0;
     o.ok = ok;
     o.pad = 0;
-    out[blockIdx.x] = o;
+    if (threadIdx.x == 0) out[blockIdx.x] = o;
     if (!ok) __nanosleep(2000000);  // give the pipe time to drain before TMEM is released
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -130,6 +179,15 @@ mma_probe_kernel(ProbeOut* out, uint32_t n, uint32_t count, uint32_t accumulator
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
   }
+}
+
+template <uint32_t... kModes>
+auto probe_kernel_table(std::integer_sequence<uint32_t, kModes...>) {
+  static void (*const table[])(ProbeOut*, uint32_t, uint32_t, uint32_t, uint32_t) = {mma_probe_kernel<kModes>...};
+  return table;
+}
+void (*probe_kernel_for(uint32_t mode))(ProbeOut*, uint32_t, uint32_t, uint32_t, uint32_t) {
+  return probe_kernel_table(std::make_integer_sequence<uint32_t, 128>{})[mode];
 }
 
 int probe_fail(int code, const std::string& msg) {
@@ -150,6 +208,10 @@ extern "C" int mononn_debug_mma_issue(int device, unsigned n, unsigned count, un
     return probe_fail(MONONN_ERR_INVALID_ARGUMENT, "count must be a multiple of 4 in 4..1048576");
   if (accumulators < 1 || accumulators > 4 || accumulators * n > 512u || (512u % accumulators) != 0u)
     return probe_fail(MONONN_ERR_INVALID_ARGUMENT, "accumulators x n must fit 512 TMEM columns");
+  if (mode > 127u) return probe_fail(MONONN_ERR_INVALID_ARGUMENT, "mode has seven bits");
+  if ((mode & 8u) && (mode & 16u)) return probe_fail(MONONN_ERR_INVALID_ARGUMENT, "mode bits 3 and 4 exclude each other");
+  if ((mode & 8u) && (accumulators != 1u || n > 256u))
+    return probe_fail(MONONN_ERR_INVALID_ARGUMENT, "with A in tensor memory one accumulator of at most 256 columns");
   if (ctas < 1 || ctas > 1024) return probe_fail(MONONN_ERR_INVALID_ARGUMENT, "ctas out of range");
   int prev = 0;
   if (cudaGetDevice(&prev) != cudaSuccess) return probe_fail(MONONN_ERR_NO_DEVICE, "no CUDA device");
@@ -170,11 +232,13 @@ extern "C" int mononn_debug_mma_issue(int device, unsigned n, unsigned count, un
     return bail(MONONN_ERR_INVALID_ARGUMENT, "more CTAs than SMs: TMEM allocation would serialise them");
   if (cudaMalloc(&d, ctas * sizeof(ProbeOut)) != cudaSuccess) return bail(MONONN_ERR_CUDA, "cudaMalloc failed");
   if (cudaMemset(d, 0, ctas * sizeof(ProbeOut)) != cudaSuccess) return bail(MONONN_ERR_CUDA, "cudaMemset failed");
-  if (cudaFuncSetAttribute(mma_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
+  using Kernel = void (*)(ProbeOut*, uint32_t, uint32_t, uint32_t, uint32_t);
+  Kernel kernel = probe_kernel_for(mode);
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
       cudaSuccess)
     return bail(MONONN_ERR_CUDA, "cannot raise the shared-memory limit");
   for (int rep = 0; rep < 2; ++rep) {  // the second launch is the warm one
-    mma_probe_kernel<<<ctas, 128, smem>>>(d, n, count, accumulators, mode);
+    kernel<<<ctas, 128, smem>>>(d, n, count, accumulators, 0u);
     cudaError_t e = cudaDeviceSynchronize();
     if (e != cudaSuccess) return bail(MONONN_ERR_CUDA, std::string("probe launch: ") + cudaGetErrorString(e));
   }
