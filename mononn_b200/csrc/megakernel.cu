@@ -121,6 +121,13 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t adesc, uint
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
       : "memory");
 }
+// One lane of a converged warp (the same one every time for a full mask).
+__device__ __forceinline__ bool elect_one_sync() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred)::"memory");
+  return pred != 0u;
+}
 __device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
   uint32_t r[16];
   __syncwarp();
@@ -832,16 +839,20 @@ __device__ void role_act_producer(Ctx c) {
 }
 
 // ----------------------------------------------------------------------------
-// Role: MMA issuer (warp 2, one lane)
+// Role: MMA issuer (warp 2). All 32 lanes run the loop converged and one elected lane issues the
+// tcgen05 instructions: the operands of a converged warp can be kept in uniform registers, and
+// a loop of four instructions, a commit and a wait per k block measured 88 cycles per
+// instruction this way against 121 when a single lane ran it (probe: mononn_debug_mma_issue).
 // ----------------------------------------------------------------------------
-__device__ void role_mma(Ctx c, uint32_t tmem_base) {
+__device__ void role_mma(Ctx c, uint32_t tmem_base, uint32_t lane) {
   const KernelParams& P = *c.P;
+  const bool issuer = elect_one_sync();
   uint32_t a_cnt = 0, b_cnt = 0, acc_cnt = 0;
   for (uint32_t s = P.stage_begin; s < P.stage_end; ++s) {
     c.stage = s;
     const StageDesc st = load_stage(P, s);
     for (uint32_t item = blockIdx.x; item < st.n_items; item += gridDim.x) {
-      const Item it = fetch_item<false>(P, st, item, c.ctrl->desc[2], 0);
+      const Item it = fetch_item<true>(P, st, item, c.ctrl->desc[2], lane);
       const OpDesc& op = *it.op;
       if (op.kind == OP_GEMM) {
         const uint32_t nkb = op.kb_per_split, kbps = op.kb_per_bslot;
@@ -859,24 +870,24 @@ __device__ void role_mma(Ctx c, uint32_t tmem_base) {
           }
           const uint32_t a_slot = a_cnt % kASlots;
           WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->a_full[a_slot], (a_cnt / kASlots) & 1u, 0x302));
-          if (kb == 0) trace(P, s, TR_MMA_FIRST);
+          if (kb == 0) if (issuer) trace(P, s, TR_MMA_FIRST);
           tc_fence_after();
           const uint64_t ad = umma_desc_sw128(c.a_ring + a_slot * kSlotBytes);
           const uint64_t bd =
               umma_desc_sw128(c.b_ring + b_slot * kBSlotBytes + sub * op.n_tile * 128u);
 #pragma unroll
           for (uint32_t k = 0; k < 4; ++k)
-            tc_mma_f16(tmem_d, ad + 2u * k, bd + 2u * k, idesc, (kb | k) != 0u);
-          tc_commit(smem_u32(&c.ctrl->a_empty[a_slot]));
+            if (issuer) tc_mma_f16(tmem_d, ad + 2u * k, bd + 2u * k, idesc, (kb | k) != 0u);
+          if (issuer) tc_commit(smem_u32(&c.ctrl->a_empty[a_slot]));
           ++a_cnt;
           if (sub + 1 == kbps || kb + 1 == nkb) {
-            tc_commit(smem_u32(&c.ctrl->b_empty[b_slot]));
+            if (issuer) tc_commit(smem_u32(&c.ctrl->b_empty[b_slot]));
             ++b_cnt;
           }
         }
-        tc_commit(smem_u32(&c.ctrl->acc_full[buf]));
+        if (issuer) tc_commit(smem_u32(&c.ctrl->acc_full[buf]));
         ++acc_cnt;
-        trace(P, s, TR_MMA_LAST);
+        if (issuer) trace(P, s, TR_MMA_LAST);
       } else if (op.kind == OP_ATTENTION) {
         const uint32_t nc = attn_chunks(op);
         uint32_t base = a_cnt, ph = acc_cnt;
@@ -894,19 +905,19 @@ __device__ void role_mma(Ctx c, uint32_t tmem_base) {
             const uint32_t b_slot = b_cnt % kBSlots, a_c = base + kb;
             WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->b_full[b_slot], (b_cnt / kBSlots) & 1u, 0x322));
             WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->a_full[slot_of(a_c)], par_of(a_c), 0x323));
-            if (kb == 0) trace(P, s, TR_MMA_FIRST);
+            if (kb == 0) if (issuer) trace(P, s, TR_MMA_FIRST);
             tc_fence_after();
             const uint64_t ad = umma_desc_sw128(c.a_ring + slot_of(a_c) * kSlotBytes);
             const uint64_t bd = umma_desc_sw128(c.b_ring + b_slot * kBSlotBytes);
 #pragma unroll
             for (uint32_t k = 0; k < 4; ++k)
-              tc_mma_f16(tmem_base + kAttnQkvCol, ad + 2u * k, bd + 2u * k, idesc, (kb | k) != 0u);
-            tc_commit(smem_u32(&c.ctrl->a_empty[slot_of(a_c)]));
-            tc_commit(smem_u32(&c.ctrl->b_empty[b_slot]));
+              if (issuer) tc_mma_f16(tmem_base + kAttnQkvCol, ad + 2u * k, bd + 2u * k, idesc, (kb | k) != 0u);
+            if (issuer) tc_commit(smem_u32(&c.ctrl->a_empty[slot_of(a_c)]));
+            if (issuer) tc_commit(smem_u32(&c.ctrl->b_empty[b_slot]));
             ++b_cnt;
           }
-          tc_commit(smem_u32(&c.ctrl->acc_full[phQ & 1u]));
-          trace(P, s, TR_MMA_LAST);
+          if (issuer) tc_commit(smem_u32(&c.ctrl->acc_full[phQ & 1u]));
+          if (issuer) trace(P, s, TR_MMA_LAST);
           base += nkb;
         }
         // the scores may span both accumulator buffers: both must have been drained
@@ -924,11 +935,11 @@ __device__ void role_mma(Ctx c, uint32_t tmem_base) {
           const uint32_t idesc = umma_idesc_m128(128);
 #pragma unroll
           for (uint32_t k = 0; k < 4; ++k)
-            tc_mma_f16(tmem_base + j * 128u, ad + 2u * k, bd + 2u * k, idesc, k != 0u);
-          tc_commit(smem_u32(&c.ctrl->a_empty[slot_of(kc)]));
+            if (issuer) tc_mma_f16(tmem_base + j * 128u, ad + 2u * k, bd + 2u * k, idesc, k != 0u);
+          if (issuer) tc_commit(smem_u32(&c.ctrl->a_empty[slot_of(kc)]));
         }
-        tc_commit(smem_u32(&c.ctrl->a_empty[slot_of(base)]));
-        tc_commit(smem_u32(&c.ctrl->acc_full[phS & 1u]));
+        if (issuer) tc_commit(smem_u32(&c.ctrl->a_empty[slot_of(base)]));
+        if (issuer) tc_commit(smem_u32(&c.ctrl->acc_full[phS & 1u]));
         // O += P_j V_j  (128 x 64, K = 128 per chunk) into columns kAttnOutCol..
         for (uint32_t j = 0; j < nc; ++j) {
           const uint32_t vc = base + 1u + nc + 3u * j;
@@ -943,11 +954,11 @@ __device__ void role_mma(Ctx c, uint32_t tmem_base) {
             const uint64_t bd = umma_desc_sw128(c.a_ring + slot_of(vc) * kSlotBytes + kb * 8192u);
 #pragma unroll
             for (uint32_t k = 0; k < 4; ++k)
-              tc_mma_f16(tmem_base + kAttnOutCol, ad + 2u * k, bd + 2u * k, idesc, (j | kb | k) != 0u);
+              if (issuer) tc_mma_f16(tmem_base + kAttnOutCol, ad + 2u * k, bd + 2u * k, idesc, (j | kb | k) != 0u);
           }
-          for (uint32_t q = 0; q < 3; ++q) tc_commit(smem_u32(&c.ctrl->a_empty[slot_of(vc + q)]));
+          for (uint32_t q = 0; q < 3; ++q) if (issuer) tc_commit(smem_u32(&c.ctrl->a_empty[slot_of(vc + q)]));
         }
-        tc_commit(smem_u32(&c.ctrl->acc_full[phO & 1u]));
+        if (issuer) tc_commit(smem_u32(&c.ctrl->acc_full[phO & 1u]));
         acc_cnt = ph + 2u;
       }
     }
@@ -2146,10 +2157,11 @@ mononn_megakernel(const __grid_constant__ KernelParams P) {
 
   // 384 threads share the 64 K registers: 168 each, which every role fits without spilling.
   if (warp < 4) {
-    if (lane == 0) {
+    if (warp == 2) {
+      role_mma(c, tmem_base, lane);
+    } else if (lane == 0) {
       if (warp == 0) role_weight_producer(c);
       else if (warp == 1) role_act_producer(c);
-      else if (warp == 2) role_mma(c, tmem_base);
     }
   } else {
     role_simt(c, tmem_base, threadIdx.x - kRoleThreads);
