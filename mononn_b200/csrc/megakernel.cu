@@ -647,11 +647,23 @@ __device__ __forceinline__ uint32_t k_rotation(uint32_t nkb, uint32_t kbps) {
   return (nkb % kbps == 0u) ? blockIdx.x % (nkb / kbps) : 0u;
 }
 
+// One elected lane of a converged producer warp issues the copy (with or without an L2 hint).
+__device__ __forceinline__ void tma_issue(bool issuer, bool hint, uint32_t dst, const void* tmap, int32_t x,
+                                          int32_t y, uint32_t bar, uint64_t policy) {
+  if (!issuer) return;
+  if (hint)
+    tma_load_2d_hint(dst, tmap, x, y, bar, policy);
+  else
+    tma_load_2d(dst, tmap, x, y, bar);
+}
+
 // ----------------------------------------------------------------------------
-// Role: weight producer (warp 0, one lane)
+// Role: weight producer (warp 0). Like the MMA role, the producers run all 32 lanes converged
+// and one elected lane issues the copies and the barrier arrivals.
 // ----------------------------------------------------------------------------
-__device__ void role_weight_producer(Ctx c) {
+__device__ void role_weight_producer(Ctx c, uint32_t lane) {
   const KernelParams& P = *c.P;
+  const bool issuer = elect_one_sync();
   const uint8_t* tmaps = static_cast<const uint8_t*>(P.tmaps);
   const bool hint = P.l2_hints != 0u;
   const uint64_t pol = l2_policy_evict_first();
@@ -671,7 +683,7 @@ __device__ void role_weight_producer(Ctx c) {
         const uint32_t chunks = (__ldg(&gop->heads) * __ldg(&gop->K) * 128u) >> 14;  // 16 KB units per weight
         for (uint32_t j = 0; j < 3; ++j) {
           const uint8_t* wbase = reinterpret_cast<const uint8_t*>(__ldg(&gop->p[5 + j]));
-          for (uint32_t ch = me; ch < chunks; ch += n_idle)
+          for (uint32_t ch = me + lane * n_idle; ch < chunks; ch += 32u * n_idle)  // shared out over the lanes too
             asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(wbase + (static_cast<size_t>(ch) << 14)),
                          "r"(16384u)
                          : "memory");
@@ -679,7 +691,7 @@ __device__ void role_weight_producer(Ctx c) {
       }
     }
     for (uint32_t item = blockIdx.x; item < st.n_items; item += gridDim.x) {
-      const Item it = fetch_item<false>(P, st, item, c.ctrl->desc[0], 0);
+      const Item it = fetch_item<true>(P, st, item, c.ctrl->desc[0], lane);
       const OpDesc& op = *it.op;
       if (op.kind == OP_ATTENTION && attn_fused(op)) {
         // per k-block one slot: the 64-row tiles of head h of the Q, K and V weights, stacked
@@ -692,19 +704,15 @@ __device__ void role_weight_producer(Ctx c) {
           const uint32_t slot = b_cnt % kBSlots, use = b_cnt / kBSlots;
           WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->b_empty[slot], (use & 1u) ^ 1u, 0x101));
           const uint32_t full = smem_u32(&c.ctrl->b_full[slot]);
-          mbar_arrive_expect_tx(full, 3u * 8192u);
+          if (issuer) mbar_arrive_expect_tx(full, 3u * 8192u);
 #pragma unroll
           for (uint32_t j = 0; j < 3; ++j) {
-            if (hint)
-              tma_load_2d_hint(c.b_ring + slot * kBSlotBytes + j * 8192u, tmw[j], 0,
+            tma_issue(issuer, hint, c.b_ring + slot * kBSlotBytes + j * 8192u, tmw[j], 0,
                                static_cast<int32_t>((t.h * nkb + kb) * 64u), full, pol);
-            else
-              tma_load_2d(c.b_ring + slot * kBSlotBytes + j * 8192u, tmw[j], 0,
-                          static_cast<int32_t>((t.h * nkb + kb) * 64u), full);
           }
           ++b_cnt;
         }
-        trace(P, s, TR_W_ISSUED);
+        if (issuer) trace(P, s, TR_W_ISSUED);
         continue;
       }
       if (op.kind != OP_GEMM) continue;
@@ -720,25 +728,22 @@ __device__ void role_weight_producer(Ctx c) {
         const uint32_t slot = b_cnt % kBSlots, use = b_cnt / kBSlots;
         WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->b_empty[slot], (use & 1u) ^ 1u, 0x100));
         const uint32_t full = smem_u32(&c.ctrl->b_full[slot]);
-        mbar_arrive_expect_tx(full, bytes);
-        if (hint)
-          tma_load_2d_hint(c.b_ring + slot * kBSlotBytes, tm, 0, static_cast<int32_t>(row0 + kb * op.n_tile),
+        if (issuer) mbar_arrive_expect_tx(full, bytes);
+        tma_issue(issuer, hint, c.b_ring + slot * kBSlotBytes, tm, 0, static_cast<int32_t>(row0 + kb * op.n_tile),
                            full, pol);
-        else
-          tma_load_2d(c.b_ring + slot * kBSlotBytes, tm, 0, static_cast<int32_t>(row0 + kb * op.n_tile),
-                      full);
         ++b_cnt;
       }
-      trace(P, s, TR_W_ISSUED);
+      if (issuer) trace(P, s, TR_W_ISSUED);
     }
   }
 }
 
 // ----------------------------------------------------------------------------
-// Role: activation producer (warp 1, one lane)
+// Role: activation producer (warp 1)
 // ----------------------------------------------------------------------------
-__device__ void role_act_producer(Ctx c) {
+__device__ void role_act_producer(Ctx c, uint32_t lane) {
   const KernelParams& P = *c.P;
+  const bool issuer = elect_one_sync();
   const uint8_t* tmaps = static_cast<const uint8_t*>(P.tmaps);
   const bool hint = P.l2_hints != 0u;
   const uint64_t pol = l2_policy_evict_last();
@@ -748,9 +753,9 @@ __device__ void role_act_producer(Ctx c) {
     const StageDesc st = load_stage(P, s);
     Item first{nullptr, 0};
     if (blockIdx.x < st.n_items) {
-      first = fetch_item<false>(P, st, blockIdx.x, c.ctrl->desc[1], 0);
+      first = fetch_item<true>(P, st, blockIdx.x, c.ctrl->desc[1], lane);
       const OpDesc& op0 = *first.op;
-      if (op0.kind == OP_GEMM || op0.kind == OP_ATTENTION) {
+      if (issuer && (op0.kind == OP_GEMM || op0.kind == OP_ATTENTION)) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(tmaps + static_cast<size_t>(op0.tmap_a) * 128u));
         if (op0.kind == OP_ATTENTION) {
           asm volatile("prefetch.tensormap [%0];" ::"l"(tmaps + static_cast<size_t>(op0.tmap_b) * 128u));
@@ -760,14 +765,16 @@ __device__ void role_act_producer(Ctx c) {
     }
     bool waited = false;
     for (uint32_t item = blockIdx.x; item < st.n_items; item += gridDim.x) {
-      const Item it = (item == blockIdx.x) ? first : fetch_item<false>(P, st, item, c.ctrl->desc[1], 0);
+      const Item it = (item == blockIdx.x) ? first : fetch_item<true>(P, st, item, c.ctrl->desc[1], lane);
       const OpDesc& op = *it.op;
       if (op.kind != OP_GEMM && op.kind != OP_ATTENTION) continue;
       if (!waited) {
-        WAIT_OR_RETURN(grid_wait(c, s, 0x200, false));
+        bool ok = true;  // one lane polls the global counter; the acquire, the proxy fence and the copies are its
+        if (issuer) ok = grid_wait(c, s, 0x200, false);
+        WAIT_OR_RETURN(__all_sync(0xffffffffu, ok));
         fence_proxy_async_global();
         waited = true;
-        trace(P, s, TR_ACT_READY);
+        if (issuer) trace(P, s, TR_ACT_READY);
       }
       if (op.kind == OP_GEMM) {
         const GemmTile t = gemm_tile(op, it.local);
@@ -779,13 +786,9 @@ __device__ void role_act_producer(Ctx c) {
           const uint32_t slot = a_cnt % kASlots, use = a_cnt / kASlots;
           WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->a_empty[slot], (use & 1u) ^ 1u, 0x201));
           const uint32_t full = smem_u32(&c.ctrl->a_full[slot]);
-          mbar_arrive_expect_tx(full, kSlotBytes);
-          if (hint)
-            tma_load_2d_hint(c.a_ring + slot * kSlotBytes, tm, static_cast<int32_t>((t.ks * nkb + kb) * 64u),
+          if (issuer) mbar_arrive_expect_tx(full, kSlotBytes);
+          tma_issue(issuer, hint, c.a_ring + slot * kSlotBytes, tm, static_cast<int32_t>((t.ks * nkb + kb) * 64u),
                              static_cast<int32_t>(t.mt * 128u), full, pol);
-          else
-            tma_load_2d(c.a_ring + slot * kSlotBytes, tm, static_cast<int32_t>((t.ks * nkb + kb) * 64u),
-                        static_cast<int32_t>(t.mt * 128u), full);
           ++a_cnt;
         }
       } else {
@@ -800,13 +803,13 @@ __device__ void role_act_producer(Ctx c) {
             const uint32_t slot = a_cnt % kASlots, use = a_cnt / kASlots;
             WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->a_empty[slot], (use & 1u) ^ 1u, 0x203));
             const uint32_t full = smem_u32(&c.ctrl->a_full[slot]);
-            mbar_arrive_expect_tx(full, kSlotBytes);
-            tma_load_2d(c.a_ring + slot * kSlotBytes, tm, static_cast<int32_t>(kb * 64u),
-                        static_cast<int32_t>(t.b * op.seq), full);
+            if (issuer) mbar_arrive_expect_tx(full, kSlotBytes);
+            tma_issue(issuer, false, c.a_ring + slot * kSlotBytes, tm, static_cast<int32_t>(kb * 64u),
+                        static_cast<int32_t>(t.b * op.seq), full, 0ull);
             ++a_cnt;
           }
           a_cnt += 5;
-          trace(P, s, TR_ACT_ISSUED);
+          if (issuer) trace(P, s, TR_ACT_ISSUED);
           continue;
         }
         // Q, K_0 .. K_{nc-1}, then V^T_j for every chunk (the P slots in between are skipped)
@@ -816,24 +819,24 @@ __device__ void role_act_producer(Ctx c) {
           WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->a_empty[slot], (use & 1u) ^ 1u, 0x202));
           const uint32_t full = smem_u32(&c.ctrl->a_full[slot]);
           const uint32_t dst = c.a_ring + slot * kSlotBytes;
-          mbar_arrive_expect_tx(full, kSlotBytes);
+          if (issuer) mbar_arrive_expect_tx(full, kSlotBytes);
           if (j == 0) {
-            tma_load_2d(dst, tm, static_cast<int32_t>(op.q_col + t.h * 64u),
-                        static_cast<int32_t>(t.b * op.seq + t.mt * 128u), full);
+            tma_issue(issuer, false, dst, tm, static_cast<int32_t>(op.q_col + t.h * 64u),
+                        static_cast<int32_t>(t.b * op.seq + t.mt * 128u), full, 0ull);
           } else if (j <= nc) {
-            tma_load_2d(dst, tmk, static_cast<int32_t>(op.k_col + t.h * 64u),
-                        static_cast<int32_t>(t.b * op.seq + (j - 1u) * 128u), full);
+            tma_issue(issuer, false, dst, tmk, static_cast<int32_t>(op.k_col + t.h * 64u),
+                        static_cast<int32_t>(t.b * op.seq + (j - 1u) * 128u), full, 0ull);
           } else {
             const int32_t x = static_cast<int32_t>((j - nc - 1u) * 128u);
             const int32_t y = static_cast<int32_t>((t.b * op.heads + t.h) * 64u);
-            tma_load_2d(dst, tmv, x, y, full);
-            tma_load_2d(dst + 8192u, tmv, x + 64, y, full);
+            tma_issue(issuer, false, dst, tmv, x, y, full, 0ull);
+            tma_issue(issuer, false, dst + 8192u, tmv, x + 64, y, full, 0ull);
           }
           ++a_cnt;
         }
         a_cnt += 2;  // the last chunk's P slots
       }
-      trace(P, s, TR_ACT_ISSUED);
+      if (issuer) trace(P, s, TR_ACT_ISSUED);
     }
   }
 }
@@ -2157,12 +2160,9 @@ mononn_megakernel(const __grid_constant__ KernelParams P) {
 
   // 384 threads share the 64 K registers: 168 each, which every role fits without spilling.
   if (warp < 4) {
-    if (warp == 2) {
-      role_mma(c, tmem_base, lane);
-    } else if (lane == 0) {
-      if (warp == 0) role_weight_producer(c);
-      else if (warp == 1) role_act_producer(c);
-    }
+    if (warp == 0) role_weight_producer(c, lane);
+    else if (warp == 1) role_act_producer(c, lane);
+    else if (warp == 2) role_mma(c, tmem_base, lane);
   } else {
     role_simt(c, tmem_base, threadIdx.x - kRoleThreads);
   }
