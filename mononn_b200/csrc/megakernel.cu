@@ -234,6 +234,14 @@ __device__ __forceinline__ uint32_t atom_add_acq_rel_cta_smem(uint32_t* p, uint3
   asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(smem_u32(p)), "r"(v) : "memory");
   return old;
 }
+// Counts the calling warp on a shared-memory counter (acquire + release at CTA scope, after a warp
+// barrier that orders the other lanes' accesses) and tells lane 0 of the warp that counted
+// eighth: whatever that lane releases next is cumulative over the eight warps' earlier stores.
+__device__ __forceinline__ bool last_warp_of(uint32_t* counter, uint32_t lane) {
+  __syncwarp();
+  if (lane != 0u) return false;
+  return (atom_add_acq_rel_cta_smem(counter, 1u) & (kSimtWarps - 1u)) == kSimtWarps - 1u;
+}
 __device__ __forceinline__ void red_release_gpu_add(uint32_t* p, uint32_t v) {
   asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -270,6 +278,8 @@ struct Ctrl {
   uint32_t barriers_seen;  // grid barriers of this launch the CTA's poller has observed (monotonic)
   uint32_t warps_done;     // epilogue warps that finished a stage (monotonic; every eighth arrives for the CTA)
   uint32_t items_done[2];  // per accumulator buffer: epilogue warps that finished a GEMM item a row op waits for
+  uint32_t tiles_done[4];  // attention: epilogue warps that finished writing the Q/K/V tiles ([0]) or the P
+                           // tiles of key chunk j ([1 + j]); every eighth count hands the tiles to the MMA issuer
   uint32_t pad_;
   alignas(16) float bias_tile[2][256];  // bias of the current GEMM tile, double buffered across items
   float mask_row[384];      // additive key mask of the current attention tile (log2 units)
@@ -1495,24 +1505,39 @@ __device__ __noinline__ bool rowwise_split_item(Ctx& c, const OpDesc& op, uint32
     if (!on[i]) x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     sum += x[i].x + x[i].y + x[i].z + x[i].w;
   }
+  // Each warp reduces its quarter to (sum, sum of squared deviations from its own mean); the
+  // four pairs are combined after ONE meeting in shared memory:
+  //   M2 = sum_w [ M2_w + n_w (mean_w - mean)^2 ]       (pairwise variance combination)
+  // which is as accurate as the two-pass form and saves its second group barrier.
   const float inv_n = 1.0f / static_cast<float>(cols);
+  const float n_w = static_cast<float>(cols >> 2), inv_nw = 1.0f / n_w;
   sum = warp_sum(sum);
-  if (lane == 0) c.ctrl->ln_part[0][r_in][part] = sum;
-  if (!group_sync(c, 0x431)) return false;
-  const float* p0 = c.ctrl->ln_part[0][r_in];
-  const float mean = rms ? 0.f : (p0[0] + p0[1] + p0[2] + p0[3]) * inv_n;
+  const float mean_w = rms ? 0.f : sum * inv_nw;
   float sq = 0.f;
 #pragma unroll
   for (int i = 0; i < 2; ++i)
     if (on[i]) {
-      const float a = x[i].x - mean, b = x[i].y - mean, d = x[i].z - mean, e = x[i].w - mean;
+      const float a = x[i].x - mean_w, b = x[i].y - mean_w, d = x[i].z - mean_w, e = x[i].w - mean_w;
       sq += a * a + b * b + d * d + e * e;
     }
   sq = warp_sum(sq);
-  if (lane == 0) c.ctrl->ln_part[1][r_in][part] = sq;
-  if (!group_sync(c, 0x432)) return false;
+  if (lane == 0) {
+    c.ctrl->ln_part[0][r_in][part] = sum;
+    c.ctrl->ln_part[1][r_in][part] = sq;
+  }
+  if (!group_sync(c, 0x431)) return false;
+  const float* p0 = c.ctrl->ln_part[0][r_in];
   const float* p1 = c.ctrl->ln_part[1][r_in];
-  const float rstd = rsqrtf((p1[0] + p1[1] + p1[2] + p1[3]) * inv_n + op.eps);
+  const float mean = rms ? 0.f : (p0[0] + p0[1] + p0[2] + p0[3]) * inv_n;
+  float m2 = p1[0] + p1[1] + p1[2] + p1[3];
+  if (!rms) {
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float dm = p0[w] * inv_nw - mean;
+      m2 = fmaf(n_w * dm, dm, m2);
+    }
+  }
+  const float rstd = rsqrtf(m2 * inv_n + op.eps);
   if (live) {
     uint2* out = op.p[0] ? reinterpret_cast<uint2*>(reinterpret_cast<__half*>(op.p[0]) +
                                                     static_cast<size_t>(row) * op.ldo)
@@ -1738,6 +1763,7 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
     if (!mbar_wait_warp(c, &c.ctrl->a_empty[cQ % kASlots], ((cQ / kASlots) & 1u) ^ 1u, 0x416)) return false;
     if (!mbar_wait_warp(c, &c.ctrl->a_empty[cK % kASlots], ((cK / kASlots) & 1u) ^ 1u, 0x417)) return false;
     if (!mbar_wait_warp(c, &c.ctrl->a_empty[cV % kASlots], ((cV / kASlots) & 1u) ^ 1u, 0x418)) return false;
+    if (tid_in_group == 0) trace(*c.P, c.stage, TR_MARK0 + 4);
     tc_fence_after();
     const float* bs = c.ctrl->bias_tile[0];
     const uint32_t tQ = tmem_base + kAttnQkvCol + ((quarter * 32u) << 16);
@@ -1778,12 +1804,17 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
     convert(rb, 64u + h32);
     tc_wait_ld();
     convert(ra, 128u + h32);
+    if (tid_in_group == 0) trace(*c.P, c.stage, TR_MARK0 + 5);
+    // Every warp makes its part of the tiles visible to the tensor core (proxy fence) and counts
+    // itself; the warp that counts last hands the three tiles to the MMA issuer. Nobody waits
+    // for anybody here (a barrier over the eight warps plus an arrival by its first thread put
+    // one more wake-up on the critical chain).
     fence_proxy_async_smem();
-    if (!group_sync(c, 0x41a)) return false;
-    if (tid_in_group == 0) {
+    if (last_warp_of(&c.ctrl->tiles_done[0], lane)) {
       mbar_arrive(smem_u32(&c.ctrl->a_full[cQ % kASlots]));
       mbar_arrive(smem_u32(&c.ctrl->a_full[cK % kASlots]));
       mbar_arrive(smem_u32(&c.ctrl->a_full[cV % kASlots]));
+      trace(*c.P, c.stage, TR_MARK0 + 6);
     }
     tc_fence_before();
     warp_arrive(&c.ctrl->acc_empty[phQ & 1u]);
@@ -1880,16 +1911,16 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
       }
     }
     if (j + 1u == nc) c.ctrl->row_sum[half][row] = sum0 + sum1;
+    // as above: the last warp to finish the chunk's two P tiles hands them over (one counter per
+    // chunk: a warp may be a chunk ahead of another)
     fence_proxy_async_smem();
-    if (!group_sync(c, 0x414)) return false;
-    if (tid_in_group == 0) {
+    if (last_warp_of(&c.ctrl->tiles_done[1u + j], lane)) {
       const uint32_t cP0 = cP - half;
       mbar_arrive(smem_u32(&c.ctrl->a_full[cP0 % kASlots]));
       mbar_arrive(smem_u32(&c.ctrl->a_full[(cP0 + 1u) % kASlots]));
     }
   }
   if (tid_in_group == 0) trace(*c.P, c.stage, TR_MARK0 + 2);
-  const float inv = 1.0f / (sum0 + sum1 + c.ctrl->row_sum[half ^ 1u][row]);
   tc_fence_before();
   warp_arrive(&c.ctrl->acc_empty[phS & 1u]);
 
@@ -1897,6 +1928,9 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
   if (!mbar_wait_warp(c, &c.ctrl->acc_full[phO & 1u], (phO >> 1) & 1u, 0x413)) return false;
   if (tid_in_group == 0) trace(*c.P, c.stage, TR_MARK0 + 3);
   tc_fence_after();
+  // the other half's row sum: its warp counted itself after writing it, the MMAs whose completion
+  // was just observed were issued after the last count, so the value is visible here
+  const float inv = 1.0f / (sum0 + sum1 + c.ctrl->row_sum[half ^ 1u][row]);
   const uint32_t tO = tmem_base + kAttnOutCol + half * 32u + ((quarter * 32u) << 16);
   // A thread owns a row, but a store instruction whose 32 lanes hit 32 different rows costs 32
   // memory transactions. The warp's 32 x 64-byte block goes through shared memory (swizzled, so
@@ -2125,6 +2159,7 @@ mononn_megakernel(const __grid_constant__ KernelParams P) {
     ctrl->barriers_seen = 0;
     ctrl->warps_done = 0;
     ctrl->items_done[0] = ctrl->items_done[1] = 0;
+    ctrl->tiles_done[0] = ctrl->tiles_done[1] = ctrl->tiles_done[2] = ctrl->tiles_done[3] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {
