@@ -37,7 +37,7 @@ UNIT = "samples/s"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised
 # in profiles/ (None until a capture exists)
-NCU_TRAFFIC_BYTES = 175312640  # 170.77 MB read + 4.55 MB written
+NCU_TRAFFIC_BYTES = 175656960  # 170.76 MB read + 4.89 MB written
 
 
 def measured_hbm_peak():
@@ -58,8 +58,52 @@ class ClockSampler:
     def __init__(self, device_index: int):
         self.proc = None
         self.index = device_index
+        self.thread = None
+        self.rows = []
+
+    def _nvml_loop(self, nv, handle):
+        # read-only NVML queries every 2 ms: a timed region of ten milliseconds still gets samples
+        # (one nvidia-smi query takes longer than that region)
+        bits = {"hw_slowdown": nv.nvmlClocksThrottleReasonHwSlowdown,
+                "hw_thermal_slowdown": nv.nvmlClocksThrottleReasonHwThermalSlowdown,
+                "sw_thermal_slowdown": nv.nvmlClocksThrottleReasonSwThermalSlowdown,
+                "sw_power_cap": nv.nvmlClocksThrottleReasonSwPowerCap}
+        while not self.stop_flag:
+            try:
+                sm = nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                util = nv.nvmlDeviceGetUtilizationRates(handle).gpu
+                self.rows.append((float(sm), [n for n, b in bits.items() if mask & b], util > 0))
+            except Exception:
+                pass
+            time.sleep(0.002)
 
     def start(self):
+        try:
+            import threading
+            import pynvml as nv
+            nv.nvmlInit()
+            uuid = None
+            try:
+                import torch
+                uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+            except Exception:
+                pass
+            handle = None
+            if uuid:
+                try:
+                    handle = nv.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+                except Exception:
+                    handle = None
+            if handle is None:
+                handle = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM))
+            self.stop_flag = False
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, handle), daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
@@ -72,6 +116,15 @@ class ClockSampler:
             self.proc = None
 
     def stop(self) -> dict:
+        if self.thread is not None:
+            self.stop_flag = True
+            self.thread.join(timeout=2)
+            sm = [r[0] for r in self.rows]
+            loaded = [r[0] for r in self.rows if r[2]]
+            reasons = sorted({n for r in self.rows for n in r[1]})
+            return {"sm_mhz": float(np.median(loaded or sm)) if sm else None, "sm_max_mhz": self.max_mhz,
+                    "samples": len(sm), "samples_under_load": len(loaded), "reasons": reasons, "source": "nvml",
+                    "window": "from before the warm-up launches to after the end-to-end leg"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -527,7 +580,12 @@ def run_mma_probe(args):
     l = capi.lib()
     sms = torch.cuda.get_device_properties(0).multi_processor_count
     rows = []
-    for mode, what in ((0, "back to back"), (1, "+ a commit per four"), (3, "+ commit, satisfied wait and fence per four")):
+    for mode, what in ((16, "back to back, one lane"),
+                       (16 + 64, "+ descriptors rebuilt per four from a ring slot"),
+                       (16 + 64 + 3, "+ commit, satisfied wait and fence per four (a main loop), one lane"),
+                       (16 + 64 + 3 + 32, "the same main loop, warp converged with an elected issuer"),
+                       (16 + 32 + 4, "back to back, M = 64"),
+                       (32 + 8, "back to back, A from tensor memory")):
         for n in (16, 32, 64, 128, 192, 256):
             cyc, iss, ns = C.c_double(), C.c_double(), C.c_double()
             capi.check(l.mononn_debug_mma_issue(0, n, 1024, 1, mode, sms, C.byref(cyc), C.byref(iss), C.byref(ns)))

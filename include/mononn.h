@@ -171,14 +171,23 @@ int mononn_trace_stages(mononn_module* m, void* const* device_args, int n, void*
  * mononn_last_status reports MONONN_ERR_BARRIER_TIMEOUT and restores the module. */
 int mononn_debug_skew_barrier(mononn_module* m, unsigned missing_arrivals);
 
-/* Measurement aid: cycles per tcgen05.mma (128 x n x 16, f16 in, f32 accumulate) issued back to
- * back by one thread per CTA from operands resident in shared memory, on `ctas` CTAs (one per
- * SM) at once: `count` instructions cycling through `accumulators` TMEM buffers, one commit at
- * the end. mode bit 0 adds a commit after every four instructions, bit 1 a satisfied mbarrier
- * wait + tcgen05 fence before every four (the bookkeeping of the kernel's main loop).
+/* Measurement aid: cycles per tcgen05.mma (128 x n x 16, f16 in, f32 accumulate) issued from
+ * operands resident in shared memory, on `ctas` CTAs (one per SM) at once: `count` instructions
+ * cycling through `accumulators` TMEM buffers, one commit at the end. mode bits (each mode is a
+ * separately compiled kernel, so that no run-time test sits in the timed loop):
+ *   0  a commit after every four instructions
+ *   1  a satisfied mbarrier wait + tcgen05 fence before every four (bits 0 and 1 together are the
+ *      bookkeeping of the kernel's main loop)
+ *   2  M = 64 instead of 128
+ *   3  the A operand is read from tensor memory instead of shared memory
+ *   4  the instruction is written without the optional disable-output-lane vector
+ *   5  the whole warp runs the loop converged and one elected lane issues (otherwise one lane
+ *      runs it alone, diverged from the other 31)
+ *   6  the operand descriptors are rebuilt for every group of four from a ring-slot index
  * cycles_per_mma covers first issue .. commit observed, issue_cycles_per_mma the issuing
- * thread alone. The GEMM tile menu of the tuner is sized from this table; the reference times
- * whole CUTLASS tiles instead (mononn_engine/core/op_impl/gemm_impl.cc:505-566). */
+ * thread alone. The issue loop of the kernel's MMA role and the GEMM tile menu of the tuner are
+ * designed from this table; the reference times whole CUTLASS tiles instead
+ * (mononn_engine/core/op_impl/gemm_impl.cc:505-566). */
 int mononn_debug_mma_issue(int device, unsigned n, unsigned count, unsigned accumulators,
                            unsigned mode, unsigned ctas, double* cycles_per_mma,
                            double* issue_cycles_per_mma, double* ns_per_mma);
