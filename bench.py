@@ -521,7 +521,8 @@ def run_config(args):
     if family == "t5":
         w = t5_device_weights(cfg, w)
     text, names = hlo(cfg)
-    mod = compile_hlo(text, device=0, barrier_timeout_us=2000000)
+    mod = compile_hlo(text, device=0, barrier_timeout_us=2000000, tuning_level=args.tuning_level,
+                      dump_dir=os.path.join(ROOT, "gpurun_out", "tune_" + name) if args.tune else None)
     mod.set_weights({names[k]: v for k, v in w.items()})
     if family == "bert":
         inp = make_inputs(cfg, seed, pad_fraction=0.25)

@@ -36,15 +36,18 @@ struct TuningSpec {
   // 0: fuse the Q/K/V projections into an attention stage that cannot fill the GPU anyway
   // (batches*heads <= CTAs, sequence <= 128); 1: never; 2: whenever the sequence allows it
   uint32_t qkv_fusion = 0;
-  // 0 / 2: a LayerNorm that reads a split-K accumulator joins its GEMMs' stage and waits on an
-  // arrival counter instead of a grid barrier; 1: it keeps a stage of its own
+  // 2: a LayerNorm that reads a split-K accumulator joins its GEMMs' stage and waits on an
+  // arrival counter instead of a grid barrier; 1: it keeps a stage of its own; 0: the scheduler
+  // decides (joined when the LayerNorm's rows are at most one wave of work items) and writes
+  // its choice back
   uint32_t row_fusion = 0;
   // CTAs per thread-block cluster (1, 2 or 4; 0 = 1). With more than one, the CTAs of a cluster
   // arrive at the grid barrier through an mbarrier in the first CTA's shared memory and that
   // CTA alone adds to the global counter.
   uint32_t cluster = 0;
-  // L2 eviction-priority hints on the TMA loads: 0 / 2 weights evict-first and GEMM activation
-  // tiles evict-last, 1 none
+  // L2 eviction-priority hints on the TMA loads: 2 weights evict-first and GEMM activation
+  // tiles evict-last, 1 none, 0 the scheduler decides (hints when no GEMM has more than four row
+  // tiles, i.e. when a weight tile is read by few CTAs) and writes its choice back
   uint32_t l2_hints = 0;
   // grid-barrier arrival: 0 / 3 one per CTA by the epilogue warp that finishes the stage last (the
   // warps count themselves in shared memory), 2 one per epilogue warp (each releases its own

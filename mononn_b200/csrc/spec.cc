@@ -299,9 +299,9 @@ int spec_from_json(const std::string& text, TuningSpec* spec, std::string* err) 
   if (const Json* ba = root.find("barrier_arrive"))
     if (ba->type == Json::String) spec->barrier_arrive = ba->str == "cta" ? 1u : (ba->str == "warp" ? 2u : 3u);
   if (const Json* lh = root.find("l2_hints"))
-    if (lh->type == Json::String) spec->l2_hints = lh->str == "on" ? 2u : 1u;
+    if (lh->type == Json::String) spec->l2_hints = lh->str == "on" ? 2u : (lh->str == "off" ? 1u : 0u);
   if (const Json* rf = root.find("row_fusion"))
-    if (rf->type == Json::String) spec->row_fusion = rf->str == "off" ? 1u : 0u;
+    if (rf->type == Json::String) spec->row_fusion = rf->str == "off" ? 1u : (rf->str == "on" ? 2u : 0u);
   if (const Json* qf = root.find("qkv_fusion"))
     if (qf->type == Json::String) spec->qkv_fusion = qf->str == "off" ? 1u : qf->str == "on" ? 2u : 0u;
   if (const Json* gl = root.find("gemm_spec_list")) {

@@ -146,7 +146,9 @@ int tune_module(mononn_module* m, void* const* args, int n, void* stream) {
         {"qkv_fusion off", &TuningSpec::qkv_fusion, 1u},
         {"qkv_fusion on", &TuningSpec::qkv_fusion, 2u},
         {"row_fusion off", &TuningSpec::row_fusion, 1u},
+        {"row_fusion on", &TuningSpec::row_fusion, 2u},
         {"l2_hints off", &TuningSpec::l2_hints, 1u},
+        {"l2_hints on", &TuningSpec::l2_hints, 2u},
         {"barrier_arrive cta", &TuningSpec::barrier_arrive, 1u},
         {"barrier_arrive warp", &TuningSpec::barrier_arrive, 2u},
         {"row_split off", &TuningSpec::row_split, 1u},

@@ -218,3 +218,16 @@ def test_hlo_and_builder_paths_agree(lib_built):
             assert ka == kb
         assert a["temp_bytes"] == b["temp_bytes"] and a["algorithmic_bytes"] == b["algorithmic_bytes"]
         assert [x["kind"] for x in a["args"]] == [0, 0, 0, 1, 2]
+
+
+def test_structure_choices_left_to_the_scheduler_follow_the_row_count(base_plan):
+    """With few rows the LayerNorms join their GEMMs' stage and the weight stream is marked
+    evict-first; with thousands of rows (48 row tiles re-reading every weight tile, 768 row items
+    that would wait for a whole GEMM) both are off. An explicit spec wins either way."""
+    assert (base_plan["spec"]["row_fusion"], base_plan["spec"]["l2_hints"]) == ("on", "on")
+    big = describe("encoder", bert_base(batch=16).to_json())
+    assert (big["spec"]["row_fusion"], big["spec"]["l2_hints"]) == ("off", "off")
+    assert all(len(s["ops"]) == 1 for s in big["plan"]["stages"] if s["ops"][0]["kind"] == "layernorm")
+    forced = describe("encoder", bert_base(batch=16).to_json(), spec=dict(big["spec"], row_fusion="on", l2_hints="on"))
+    assert (forced["spec"]["row_fusion"], forced["spec"]["l2_hints"]) == ("on", "on")
+    assert len(forced["plan"]["stages"]) < len(big["plan"]["stages"])
