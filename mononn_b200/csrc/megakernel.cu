@@ -1832,92 +1832,144 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
   if (op.flags & F_POS_BIAS)
     pb = reinterpret_cast<const __half*>(op.q[0]) +
          (static_cast<size_t>(t.h) * seq + (qrow < seq ? qrow : seq - 1u)) * seq;
-  // pass 1: row maximum of scale*s + mask over this warp's key halves (four independent chains)
-  float m0 = -3.0e38f, m1 = -3.0e38f, m2 = -3.0e38f, m3 = -3.0e38f;
-#pragma unroll 1
-  for (uint32_t c0 = h64; c0 < n_cols; c0 += ((c0 & 32u) ? 96u : 32u)) {  // 64 of every 128 columns
-    float v[32], mk[32];
-    lds32(mb + c0, mk);
-    if (pb != nullptr) add_bias32(pb + c0, mk);
-    tc_ld32(tS + c0, v);
-    if (key_limit == 0xffffffffu) {  // not causal (warp-uniform): no per-element test
-#pragma unroll
-      for (int i = 0; i < 32; i += 4) {
-        m0 = fmaxf(m0, fmaf(v[i], alpha, mk[i]));
-        m1 = fmaxf(m1, fmaf(v[i + 1], alpha, mk[i + 1]));
-        m2 = fmaxf(m2, fmaf(v[i + 2], alpha, mk[i + 2]));
-        m3 = fmaxf(m3, fmaf(v[i + 3], alpha, mk[i + 3]));
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 32; i += 4) {
-        m0 = fmaxf(m0, (c0 + i <= key_limit) ? fmaf(v[i], alpha, mk[i]) : -1.0e30f);
-        m1 = fmaxf(m1, (c0 + i + 1 <= key_limit) ? fmaf(v[i + 1], alpha, mk[i + 1]) : -1.0e30f);
-        m2 = fmaxf(m2, (c0 + i + 2 <= key_limit) ? fmaf(v[i + 2], alpha, mk[i + 2]) : -1.0e30f);
-        m3 = fmaxf(m3, (c0 + i + 3 <= key_limit) ? fmaf(v[i + 3], alpha, mk[i + 3]) : -1.0e30f);
-      }
-    }
-  }
-  float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-  c.ctrl->row_max[half][row] = mx;
-  if (!group_sync(c, 0x41b)) return false;
-  mx = fmaxf(mx, c.ctrl->row_max[half ^ 1u][row]);
-  if (tid_in_group == 0) trace(*c.P, c.stage, TR_MARK0 + 1);
-  // pass 2: p = exp(z - max), row sum, this warp's P tile of every chunk in the swizzled
-  // K-major operand layout
   float sum0 = 0.f, sum1 = 0.f;
-#pragma unroll 1
-  for (uint32_t j = 0; j < nc; ++j) {
-    const uint32_t cP = base + 2u + nc + 3u * j + half;  // the chunk's two P slots: one per warp half
+  if (nc == 1u && key_limit == 0xffffffffu && pb == nullptr) {
+    // One key chunk, no causal mask, no position bias (the encoder case): the 64 scaled and masked
+    // scores of this thread stay in registers between the maximum and the exponentials, so the
+    // accumulator and the mask row are read once.
+    float z[64];
+#pragma unroll
+    for (uint32_t c0 = 0; c0 < 64u; c0 += 32u) {
+      float v[32], mk[32];
+      lds32(mb + h64 + c0, mk);
+      tc_ld32(tS + h64 + c0, v);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) z[c0 + i] = fmaf(v[i], alpha, mk[i]);
+    }
+    float m0 = z[0], m1 = z[1], m2 = z[2], m3 = z[3];
+#pragma unroll
+    for (int i = 4; i < 64; i += 4) {
+      m0 = fmaxf(m0, z[i]);
+      m1 = fmaxf(m1, z[i + 1]);
+      m2 = fmaxf(m2, z[i + 2]);
+      m3 = fmaxf(m3, z[i + 3]);
+    }
+    float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+    c.ctrl->row_max[half][row] = mx;
+    if (!group_sync(c, 0x41b)) return false;
+    mx = fmaxf(mx, c.ctrl->row_max[half ^ 1u][row]);
+    if (tid_in_group == 0) trace(*c.P, c.stage, TR_MARK0 + 1);
+    const uint32_t cP = base + 2u + nc + half;
     const uint32_t slotP = cP % kASlots;
-    // the P slot must be free before it is overwritten
     if (!mbar_wait_warp(c, &c.ctrl->a_empty[slotP], ((cP / kASlots) & 1u) ^ 1u, 0x411)) return false;
     uint8_t* tile = c.a_ring_ptr + slotP * kSlotBytes;
-#pragma unroll 1
-    for (uint32_t c0 = 0; c0 < 64u; c0 += 32) {
-      const uint32_t cc = j * 128u + h64 + c0;
-      float v[32], mk[32];
-      lds32(mb + cc, mk);
-      if (pb != nullptr) add_bias32(pb + cc, mk);
-      tc_ld32(tS + cc, v);
-      if (key_limit == 0xffffffffu) {
-        // exp2(s*alpha + mask - max) with the subtraction folded into the multiply-add
 #pragma unroll
-        for (int i = 0; i < 32; ++i) mk[i] -= mx;
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          v[i] = fast_exp2(fmaf(v[i], alpha, mk[i]));
-          v[i + 1] = fast_exp2(fmaf(v[i + 1], alpha, mk[i + 1]));
-          sum0 += v[i];
-          sum1 += v[i + 1];
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float z0 = (cc + i <= key_limit) ? fmaf(v[i], alpha, mk[i]) : -1.0e30f;
-          const float z1 = (cc + i + 1 <= key_limit) ? fmaf(v[i + 1], alpha, mk[i + 1]) : -1.0e30f;
-          v[i] = fast_exp2(z0 - mx);
-          v[i + 1] = fast_exp2(z1 - mx);
-          sum0 += v[i];
-          sum1 += v[i + 1];
-        }
-      }
-      const uint32_t chunk = c0 >> 3;  // 16-byte chunk index inside the 128-byte row
-#pragma unroll
-      for (uint32_t q = 0; q < 4; ++q) {
-        uint4* d = reinterpret_cast<uint4*>(tile + row * 128u + (((chunk + q) ^ (row & 7u)) << 4));
-        *d = make_uint4(pack_h2(v[8 * q], v[8 * q + 1]), pack_h2(v[8 * q + 2], v[8 * q + 3]),
-                        pack_h2(v[8 * q + 4], v[8 * q + 5]), pack_h2(v[8 * q + 6], v[8 * q + 7]));
-      }
+    for (int i = 0; i < 64; i += 2) {
+      z[i] = fast_exp2(z[i] - mx);
+      z[i + 1] = fast_exp2(z[i + 1] - mx);
+      sum0 += z[i];
+      sum1 += z[i + 1];
     }
-    if (j + 1u == nc) c.ctrl->row_sum[half][row] = sum0 + sum1;
-    // as above: the last warp to finish the chunk's two P tiles hands them over (one counter per
-    // chunk: a warp may be a chunk ahead of another)
+#pragma unroll
+    for (uint32_t q = 0; q < 8; ++q) {
+      uint4* d = reinterpret_cast<uint4*>(tile + row * 128u + ((q ^ (row & 7u)) << 4));
+      *d = make_uint4(pack_h2(z[8 * q], z[8 * q + 1]), pack_h2(z[8 * q + 2], z[8 * q + 3]),
+                      pack_h2(z[8 * q + 4], z[8 * q + 5]), pack_h2(z[8 * q + 6], z[8 * q + 7]));
+    }
+    c.ctrl->row_sum[half][row] = sum0 + sum1;
     fence_proxy_async_smem();
-    if (last_warp_of(&c.ctrl->tiles_done[1u + j], lane)) {
+    if (last_warp_of(&c.ctrl->tiles_done[1], lane)) {
       const uint32_t cP0 = cP - half;
       mbar_arrive(smem_u32(&c.ctrl->a_full[cP0 % kASlots]));
       mbar_arrive(smem_u32(&c.ctrl->a_full[(cP0 + 1u) % kASlots]));
+    }
+  } else {
+    // pass 1: row maximum of scale*s + mask over this warp's key halves (four independent chains)
+    float m0 = -3.0e38f, m1 = -3.0e38f, m2 = -3.0e38f, m3 = -3.0e38f;
+  #pragma unroll 1
+    for (uint32_t c0 = h64; c0 < n_cols; c0 += ((c0 & 32u) ? 96u : 32u)) {  // 64 of every 128 columns
+      float v[32], mk[32];
+      lds32(mb + c0, mk);
+      if (pb != nullptr) add_bias32(pb + c0, mk);
+      tc_ld32(tS + c0, v);
+      if (key_limit == 0xffffffffu) {  // not causal (warp-uniform): no per-element test
+  #pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          m0 = fmaxf(m0, fmaf(v[i], alpha, mk[i]));
+          m1 = fmaxf(m1, fmaf(v[i + 1], alpha, mk[i + 1]));
+          m2 = fmaxf(m2, fmaf(v[i + 2], alpha, mk[i + 2]));
+          m3 = fmaxf(m3, fmaf(v[i + 3], alpha, mk[i + 3]));
+        }
+      } else {
+  #pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          m0 = fmaxf(m0, (c0 + i <= key_limit) ? fmaf(v[i], alpha, mk[i]) : -1.0e30f);
+          m1 = fmaxf(m1, (c0 + i + 1 <= key_limit) ? fmaf(v[i + 1], alpha, mk[i + 1]) : -1.0e30f);
+          m2 = fmaxf(m2, (c0 + i + 2 <= key_limit) ? fmaf(v[i + 2], alpha, mk[i + 2]) : -1.0e30f);
+          m3 = fmaxf(m3, (c0 + i + 3 <= key_limit) ? fmaf(v[i + 3], alpha, mk[i + 3]) : -1.0e30f);
+        }
+      }
+    }
+    float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+    c.ctrl->row_max[half][row] = mx;
+    if (!group_sync(c, 0x41b)) return false;
+    mx = fmaxf(mx, c.ctrl->row_max[half ^ 1u][row]);
+    if (tid_in_group == 0) trace(*c.P, c.stage, TR_MARK0 + 1);
+    // pass 2: p = exp(z - max), row sum, this warp's P tile of every chunk in the swizzled
+    // K-major operand layout
+  #pragma unroll 1
+    for (uint32_t j = 0; j < nc; ++j) {
+      const uint32_t cP = base + 2u + nc + 3u * j + half;  // the chunk's two P slots: one per warp half
+      const uint32_t slotP = cP % kASlots;
+      // the P slot must be free before it is overwritten
+      if (!mbar_wait_warp(c, &c.ctrl->a_empty[slotP], ((cP / kASlots) & 1u) ^ 1u, 0x411)) return false;
+      uint8_t* tile = c.a_ring_ptr + slotP * kSlotBytes;
+  #pragma unroll 1
+      for (uint32_t c0 = 0; c0 < 64u; c0 += 32) {
+        const uint32_t cc = j * 128u + h64 + c0;
+        float v[32], mk[32];
+        lds32(mb + cc, mk);
+        if (pb != nullptr) add_bias32(pb + cc, mk);
+        tc_ld32(tS + cc, v);
+        if (key_limit == 0xffffffffu) {
+          // exp2(s*alpha + mask - max) with the subtraction folded into the multiply-add
+  #pragma unroll
+          for (int i = 0; i < 32; ++i) mk[i] -= mx;
+  #pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            v[i] = fast_exp2(fmaf(v[i], alpha, mk[i]));
+            v[i + 1] = fast_exp2(fmaf(v[i + 1], alpha, mk[i + 1]));
+            sum0 += v[i];
+            sum1 += v[i + 1];
+          }
+        } else {
+  #pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float z0 = (cc + i <= key_limit) ? fmaf(v[i], alpha, mk[i]) : -1.0e30f;
+            const float z1 = (cc + i + 1 <= key_limit) ? fmaf(v[i + 1], alpha, mk[i + 1]) : -1.0e30f;
+            v[i] = fast_exp2(z0 - mx);
+            v[i + 1] = fast_exp2(z1 - mx);
+            sum0 += v[i];
+            sum1 += v[i + 1];
+          }
+        }
+        const uint32_t chunk = c0 >> 3;  // 16-byte chunk index inside the 128-byte row
+  #pragma unroll
+        for (uint32_t q = 0; q < 4; ++q) {
+          uint4* d = reinterpret_cast<uint4*>(tile + row * 128u + (((chunk + q) ^ (row & 7u)) << 4));
+          *d = make_uint4(pack_h2(v[8 * q], v[8 * q + 1]), pack_h2(v[8 * q + 2], v[8 * q + 3]),
+                          pack_h2(v[8 * q + 4], v[8 * q + 5]), pack_h2(v[8 * q + 6], v[8 * q + 7]));
+        }
+      }
+      if (j + 1u == nc) c.ctrl->row_sum[half][row] = sum0 + sum1;
+      // as above: the last warp to finish the chunk's two P tiles hands them over (one counter per
+      // chunk: a warp may be a chunk ahead of another)
+      fence_proxy_async_smem();
+      if (last_warp_of(&c.ctrl->tiles_done[1u + j], lane)) {
+        const uint32_t cP0 = cP - half;
+        mbar_arrive(smem_u32(&c.ctrl->a_full[cP0 % kASlots]));
+        mbar_arrive(smem_u32(&c.ctrl->a_full[(cP0 + 1u) % kASlots]));
+      }
     }
   }
   if (tid_in_group == 0) trace(*c.P, c.stage, TR_MARK0 + 2);
