@@ -278,8 +278,9 @@ struct Ctrl {
   uint32_t barriers_seen;  // grid barriers of this launch the CTA's poller has observed (monotonic)
   uint32_t warps_done;     // epilogue warps that finished a stage (monotonic; every eighth arrives for the CTA)
   uint32_t items_done[2];  // per accumulator buffer: epilogue warps that finished a GEMM item a row op waits for
-  uint32_t tiles_done[4];  // attention: epilogue warps that finished writing the Q/K/V tiles ([0]) or the P
-                           // tiles of key chunk j ([1 + j]); every eighth count hands the tiles to the MMA issuer
+  uint32_t tiles_done[5];  // attention: epilogue warps that finished writing the Q/K/V tiles ([0]) or the P
+                           // tiles of key chunk j ([1 + j]); every eighth count hands the tiles to the MMA issuer;
+                           // [4]: warps that stored their part of an item's output (every eighth counts the item)
   uint32_t pad_;
   alignas(16) float bias_tile[2][256];  // bias of the current GEMM tile, double buffered across items
   float mask_row[384];      // additive key mask of the current attention tile (log2 units)
@@ -506,7 +507,6 @@ __device__ __noinline__ bool flag_wait_slow(const KernelParams* P, Ctrl* ctrl, c
       acquire_after_poll(flag);
       return true;
     }
-    __nanosleep(32);
     if ((++it & 31u) == 0u) {
       if (*reinterpret_cast<volatile uint32_t*>(&ctrl->abort_flag)) return false;
       if (*reinterpret_cast<volatile uint32_t*>(&P->status->code) != 0u) {
@@ -524,11 +524,11 @@ __device__ __noinline__ bool flag_wait_slow(const KernelParams* P, Ctrl* ctrl, c
 // same amount every launch, and the host passes the number of launches since it was last
 // cleared (flag_epoch), so the target is flag_epoch * arrivals-per-launch. No atomic with a
 // return value, and so no extra L2 round trip, sits in the row op's critical path.
-__device__ __forceinline__ bool flag_wait_warp(const Ctx& c, const OpDesc& op, uint32_t where) {
+__device__ __forceinline__ bool flag_wait_warp(const Ctx& c, uint64_t counter, uint32_t per_launch, uint32_t where) {
   bool ok = true;
   if ((threadIdx.x & 31u) == 0u) {
-    const uint32_t* flag = reinterpret_cast<const uint32_t*>(op.flag);
-    const uint32_t target = c.P->flag_epoch * op.flag_target;
+    const uint32_t* flag = reinterpret_cast<const uint32_t*>(counter);
+    const uint32_t target = c.P->flag_epoch * per_launch;
     if (static_cast<int32_t>(poll_load(flag) - target) >= 0) {
       acquire_after_poll(flag);
     } else {
@@ -681,22 +681,30 @@ __device__ void role_weight_producer(Ctx c, uint32_t lane) {
   for (uint32_t s = P.stage_begin; s < P.stage_end; ++s) {
     c.stage = s;
     const StageDesc st = load_stage(P, s);
-    if (blockIdx.x >= st.n_items) {
-      // This CTA has no work in the stage. If the stage holds attention items that compute their
-      // own projections, only a few SMs will pull those weights, each through a three-slot ring:
-      // bring the weights into L2 now (this role runs ahead of the barriers), shared out over
-      // the idle CTAs, so that the few stream them from L2 instead of HBM.
-      const uint32_t n_idle = gridDim.x - st.n_items, me = blockIdx.x - st.n_items;
+    {
+      // If the stage holds attention items that compute their own projections, only a few SMs will
+      // pull those weights, each through a three-slot ring. The CTAs that got none of those items
+      // (idle in this stage, or holding items of operators that wait for the attention) bring the
+      // weights into L2 now (this role runs ahead of the barriers), shared out among them, so that
+      // the few stream them from L2 instead of HBM.
+      uint32_t busy = 0;  // work items up to and including the last such attention operator
       for (uint32_t k = 0; k < st.op_count; ++k) {
         const OpDesc* gop = P.ops + st.op_begin + k;
-        if (__ldg(&gop->kind) != OP_ATTENTION || !(__ldg(&gop->flags) & F_FUSED_QKV)) continue;
-        const uint32_t chunks = (__ldg(&gop->heads) * __ldg(&gop->K) * 128u) >> 14;  // 16 KB units per weight
-        for (uint32_t j = 0; j < 3; ++j) {
-          const uint8_t* wbase = reinterpret_cast<const uint8_t*>(__ldg(&gop->p[5 + j]));
-          for (uint32_t ch = me + lane * n_idle; ch < chunks; ch += 32u * n_idle)  // shared out over the lanes too
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(wbase + (static_cast<size_t>(ch) << 14)),
-                         "r"(16384u)
-                         : "memory");
+        if (__ldg(&gop->kind) == OP_ATTENTION && (__ldg(&gop->flags) & F_FUSED_QKV)) busy = st.item_end[k];
+      }
+      if (busy != 0u && blockIdx.x >= busy) {
+        const uint32_t n_idle = gridDim.x - busy, me = blockIdx.x - busy;
+        for (uint32_t k = 0; k < st.op_count; ++k) {
+          const OpDesc* gop = P.ops + st.op_begin + k;
+          if (__ldg(&gop->kind) != OP_ATTENTION || !(__ldg(&gop->flags) & F_FUSED_QKV)) continue;
+          const uint32_t chunks = (__ldg(&gop->heads) * __ldg(&gop->K) * 128u) >> 14;  // 16 KB units per weight
+          for (uint32_t j = 0; j < 3; ++j) {
+            const uint8_t* wbase = reinterpret_cast<const uint8_t*>(__ldg(&gop->p[5 + j]));
+            for (uint32_t ch = me + lane * n_idle; ch < chunks; ch += 32u * n_idle)  // shared out over the lanes too
+              asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(wbase + (static_cast<size_t>(ch) << 14)),
+                           "r"(16384u)
+                           : "memory");
+          }
         }
       }
     }
@@ -787,6 +795,14 @@ __device__ void role_act_producer(Ctx c, uint32_t lane) {
         if (issuer) trace(P, s, TR_ACT_READY);
       }
       if (op.kind == OP_GEMM) {
+        if (op.wait_target != 0u) {
+          // the A operand is the output of an attention operator of this stage: wait until all of
+          // its items have counted themselves (each after its stores, with release), then make
+          // those stores visible to the copies as after a grid barrier
+          WAIT_OR_RETURN(flag_wait_warp(c, op.wait_flag, op.wait_target, 0x204));
+          fence_proxy_async_global();
+          if (issuer) trace(P, s, TR_MARK0 + 7);
+        }
         const GemmTile t = gemm_tile(op, it.local);
         const void* tm = tmaps + static_cast<size_t>(op.tmap_a) * 128u;
         const uint32_t nkb = op.kb_per_split, kbps = op.kb_per_bslot;
@@ -2010,6 +2026,9 @@ __device__ __noinline__ bool attention_simt(Ctx& c, const OpDesc& op, uint32_t l
         *reinterpret_cast<uint4*>(obase + (static_cast<size_t>(t.b) * seq + qr) * op.ldo) = val;
     }
   }
+  // a GEMM of this stage may wait for this item's output: the warp that stores last counts the item
+  if (op.flag != 0 && last_warp_of(&c.ctrl->tiles_done[4], lane))
+    red_release_gpu_add(reinterpret_cast<uint32_t*>(op.flag), 1u);
   __syncwarp();  // the staging block is reused by the warp's next item
   tc_fence_before();
   warp_arrive(&c.ctrl->acc_empty[phO & 1u]);
@@ -2092,7 +2111,7 @@ __device__ void role_simt(Ctx c, uint32_t tmem_base, uint32_t tid_in_group) {
         case OP_ASSEMBLE:
           if (op.flag_target != 0) {
             prefetch_row_consts(op, lane);
-            WAIT_OR_RETURN(flag_wait_warp(c, op, 0x430));
+            WAIT_OR_RETURN(flag_wait_warp(c, op.flag, op.flag_target, 0x430));
           }
           if (op.flags & F_ROW_SPLIT) {
             WAIT_OR_RETURN(rowwise_split_item(c, op, it.local, widx, lane));
@@ -2211,7 +2230,7 @@ mononn_megakernel(const __grid_constant__ KernelParams P) {
     ctrl->barriers_seen = 0;
     ctrl->warps_done = 0;
     ctrl->items_done[0] = ctrl->items_done[1] = 0;
-    ctrl->tiles_done[0] = ctrl->tiles_done[1] = ctrl->tiles_done[2] = ctrl->tiles_done[3] = 0;
+    for (uint32_t i = 0; i < 5; ++i) ctrl->tiles_done[i] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {

@@ -55,6 +55,10 @@ struct TuningSpec {
   uint32_t barrier_arrive = 0;
   // 0 / 2: a LayerNorm with few rows shares each row among four warps; 1: always one warp per row
   uint32_t row_split = 0;
+  // 2: the GEMM that reads an attention's output shares its stage and waits on its arrival counter;
+  // 1: it keeps a stage of its own; 0: the scheduler decides (shared when the attention's work
+  // items occupy at most half of the CTAs and the LayerNorms are joined too) and writes it back
+  uint32_t out_fusion = 0;
 };
 
 // ------------------------------------------------------------------- FGraph
@@ -152,6 +156,10 @@ struct PlanOp {
   BufRef flag;
   int flag_index = -1;
   bool waits = false;
+  // arrival counter of an attention operator of the same stage that a GEMM reading its output
+  // waits for before it loads its A operand; wflag_index < 0: none
+  BufRef wflag;
+  int wflag_index = -1;
 };
 
 // How one HLO constant lands in the constant arena.

@@ -334,6 +334,7 @@ int Runtime::bind(void* const* args, int n, void* stream) {
     for (int k = 0; k < 8; ++k) ops[i].p[k] = resolve(plan_.ops[i].p[k]);
     for (int k = 0; k < 4; ++k) ops[i].q[k] = resolve(plan_.ops[i].q[k]);
     ops[i].flag = resolve(plan_.ops[i].flag);
+    ops[i].wait_flag = resolve(plan_.ops[i].wflag);
   }
   EncodeTiledFn encode = reinterpret_cast<EncodeTiledFn>(encode_fn_);
   for (size_t i = 0; i < plan_.tmaps.size(); ++i) {

@@ -244,13 +244,24 @@ int validate_plan(const Plan& P, std::string* err) {
     bool seen_wait = false;
     for (uint32_t a = sd.op_begin; a < sd.op_begin + sd.op_count; ++a) {
       const PlanOp& op = P.ops[a];
+      if (op.wflag_index >= 0) {
+        // a GEMM behind an attention of the same stage: the attention items come first and add up
+        uint32_t target = 0;
+        for (uint32_t b = sd.op_begin; b < a; ++b)
+          if (P.ops[b].d.kind == OP_ATTENTION && P.ops[b].flag_index == op.wflag_index) target += P.ops[b].d.n_items;
+        if (op.d.kind != OP_GEMM || op.wflag.space != SPACE_SCRATCH || target == 0 || target != op.d.wait_target)
+          return bad(op.name + ": wait target does not match its attention");
+      } else if (op.d.wait_target != 0) {
+        return bad(op.name + ": wait target without a counter");
+      }
       if (op.flag_index < 0) {
         if (op.d.flag_target != 0) return bad(op.name + ": wait target without a counter");
         continue;
       }
       if (op.flag.space != SPACE_SCRATCH) return bad(op.name + ": arrival counter outside the scratch");
       if (!op.waits) {
-        if (op.d.kind != OP_GEMM || seen_wait) return bad(op.name + ": signalling operator after a waiting one");
+        if ((op.d.kind != OP_GEMM && op.d.kind != OP_ATTENTION) || seen_wait)
+          return bad(op.name + ": signalling operator after a waiting one");
         continue;
       }
       seen_wait = true;
@@ -411,6 +422,9 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
   std::vector<std::vector<int>> writers(n_t);
   std::vector<int> flag_of(ops.size(), -1);   // arrival counter an op signals (GEMM) or waits on (row op)
   std::vector<char> waits(ops.size(), 0);
+  // a GEMM that shares the stage of the attention whose output it reads waits on that attention's
+  // counter (its own flag_of stays free for the row op that may follow it in the same stage)
+  std::vector<int> wflag_of(ops.size(), -1);
   int n_flags = 0;
   int n_stages = 0;
   // Left to the scheduler (0), a LayerNorm joins its GEMMs' stage when its rows are one wave of
@@ -425,8 +439,25 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
   }
   if (P.spec.row_fusion == 0) P.spec.row_fusion = (max_ln_rows <= kRowsPerItem * P.grid) ? 2u : 1u;
   if (P.spec.l2_hints == 0) P.spec.l2_hints = (max_m_tiles <= 4u) ? 2u : 1u;
+  // An attention stage that leaves most CTAs idle takes the GEMM that consumes its output (the
+  // out-projection) into the same stage: the GEMM's items wait for the attention's arrival counter
+  // instead of a grid barrier, and their weights are already on chip when the counter fills.
+  uint32_t max_attn_items = 0;
+  for (const FOp& o : ops)
+    if (o.kind == OP_ATTENTION)
+      max_attn_items = std::max(max_attn_items, o.batches * o.heads * ((o.seq + 127u) / 128u));
+  if (P.spec.out_fusion == 0)
+    P.spec.out_fusion = (P.spec.row_fusion == 2 && max_attn_items != 0 && max_attn_items * 2u <= P.grid) ? 2u : 1u;
   for (size_t i = 0; i < ops.size(); ++i) {
     int fuse_src = -1, fuse_stage = -1;
+    bool gemm_after_attention = false;
+    if (ops[i].kind == OP_GEMM && P.spec.out_fusion == 2 && ops[i].a >= 0 && producer[ops[i].a] >= 0 &&
+        ops[producer[ops[i].a]].kind == OP_ATTENTION && writers[ops[i].a].size() == 1 &&
+        wflag_of[producer[ops[i].a]] < 0) {
+      fuse_src = ops[i].a;
+      fuse_stage = ops[producer[ops[i].a]].stage;
+      gemm_after_attention = true;
+    }
     if (ops[i].kind == OP_LAYERNORM && P.spec.row_fusion != 1 && ops[i].src >= 0 &&
         g.tensors[ops[i].src].kind == TKind::AccF32 && !writers[ops[i].src].empty()) {
       const int T = ops[i].src;
@@ -451,7 +482,12 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
     for (int t : outputs_of(ops[i]))
       if (producer[t] >= 0) depth = std::max(depth, ops[producer[t]].stage + 1);
     if (fuse_src >= 0) {
-      if (depth <= fuse_stage) {
+      if (depth <= fuse_stage && gemm_after_attention) {
+        const int att = producer[fuse_src];
+        depth = fuse_stage;
+        if (flag_of[att] < 0) flag_of[att] = n_flags++;  // several GEMMs may read one attention's output
+        wflag_of[i] = flag_of[att];
+      } else if (depth <= fuse_stage) {
         depth = fuse_stage;
         flag_of[i] = n_flags;
         waits[i] = 1;
@@ -494,7 +530,7 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
         if (ops[i].stage == st) here.push_back(i);
       for (size_t k = here.size(); here.size() > kMaxStageOps && k-- > 0;) {
         const size_t i = here[k];
-        if (flag_of[i] >= 0) continue;  // tied to its partner's stage
+        if (flag_of[i] >= 0 || wflag_of[i] >= 0) continue;  // tied to its partner's stage
         bool free_to_move = true;
         for (size_t j = i + 1; j < ops.size() && free_to_move; ++j)
           if (ops[j].stage <= st + 1 && depends(j, i)) free_to_move = false;
@@ -684,16 +720,21 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
   };
 
   // ---- per stage: count GEMMs to share the CTA budget
-  std::vector<uint32_t> gemms_in_stage(n_stages, 0);
+  std::vector<uint32_t> gemms_in_stage(n_stages, 0), attn_items_in_stage(n_stages, 0);
+  for (const FOp& o : ops)
+    if (o.kind == OP_ATTENTION) attn_items_in_stage[o.stage] += o.batches * o.heads * ((o.seq + 127u) / 128u);
   for (const FOp& o : ops)
     if (o.kind == OP_GEMM) gemms_in_stage[o.stage]++;
 
   // ---- emit ops stage by stage
   std::vector<std::vector<size_t>> by_stage(n_stages);
   for (size_t i = 0; i < ops.size(); ++i)
-    if (!waits[i]) by_stage[ops[i].stage].push_back(i);
-  // row ops that wait for GEMMs of their own stage come last, so that a CTA meets its GEMM
-  // items before any item that waits
+    if (!waits[i] && wflag_of[i] < 0) by_stage[ops[i].stage].push_back(i);
+  // Operators that wait for others of their own stage come after them, so that a CTA meets the
+  // items that never wait before any item that does: first the GEMMs behind an attention, then
+  // the row ops behind GEMMs (which may be those same GEMMs).
+  for (size_t i = 0; i < ops.size(); ++i)
+    if (wflag_of[i] >= 0) by_stage[ops[i].stage].push_back(i);
   for (size_t i = 0; i < ops.size(); ++i)
     if (waits[i]) by_stage[ops[i].stage].push_back(i);
 
@@ -722,7 +763,9 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
             return MONONN_ERR_UNSUPPORTED;
           }
           const bool can_split = (O.kind == TKind::AccF32) && o.act == ACT_NONE;
-          const uint32_t budget = std::max(1u, P.grid / std::max(1u, gemms_in_stage[s]));
+          // CTAs busy with attention items of the same stage are not available to its GEMMs
+          const uint32_t free_ctas = P.grid > attn_items_in_stage[s] ? P.grid - attn_items_in_stage[s] : 1u;
+          const uint32_t budget = std::max(1u, free_ctas / std::max(1u, gemms_in_stage[s]));
           GemmTileSpec ts;
           auto it = spec_in.gemm.find(o.name);
           if (it != spec_in.gemm.end()) ts = it->second;
@@ -1024,6 +1067,10 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
         po.flag_index = flag_of[oi];
         po.waits = waits[oi] != 0;
       }
+      if (wflag_of[oi] >= 0) {
+        po.wflag = BufRef{SPACE_SCRATCH, 0, flags_off + 8ull * wflag_of[oi]};
+        po.wflag_index = wflag_of[oi];
+      }
       sd.n_items += d.n_items;
       if (!sname.empty()) sname += "+";
       sname += o.name;
@@ -1036,6 +1083,13 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
       for (size_t b = sd.op_begin; b < P.ops.size(); ++b)
         if (!P.ops[b].waits && P.ops[b].flag_index == P.ops[a].flag_index) target += P.ops[b].d.n_items;
       P.ops[a].d.flag_target = target;
+    }
+    for (size_t a = sd.op_begin; a < P.ops.size(); ++a) {
+      if (P.ops[a].wflag_index < 0) continue;
+      uint32_t target = 0;
+      for (size_t b = sd.op_begin; b < a; ++b)
+        if (!P.ops[b].waits && P.ops[b].flag_index == P.ops[a].wflag_index) target += P.ops[b].d.n_items;
+      P.ops[a].d.wait_target = target;
     }
     if (sd.op_count > kMaxStageOps) {
       if (err) *err = "more than " + std::to_string(kMaxStageOps) + " independent operators at one depth";

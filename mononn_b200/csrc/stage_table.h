@@ -103,13 +103,15 @@ struct alignas(16) OpDesc {
   uint32_t vocab;           // embed: word-table rows (ids are not clamped, as in the reference)
   uint32_t pad0;
   uint32_t flag_target;     // row op that follows its producer GEMM inside one stage: arrivals to wait for
-  uint32_t pad1;
+  uint32_t wait_target;     // GEMM that follows the attention it reads inside one stage: arrivals to wait for
   uint64_t p[8];
   uint64_t q[4];  // LAYERNORM / EMBED: q[2] second output (f32, + q[3] bias f16), see plan
   // Arrival counter shared by a split-K GEMM and the row op that consumes its accumulator in the
   // same stage: every GEMM item adds 1 after its reductions, the row items wait for flag_target.
   uint64_t flag;
-  uint64_t pad2;
+  // Arrival counter of the attention operator whose output this GEMM reads in the same stage: every
+  // attention item adds 1 after its stores, the GEMM's activation producer waits for wait_target.
+  uint64_t wait_flag;
 };
 static_assert(sizeof(OpDesc) == 256, "operator descriptor is copied as sixteen 16-byte words");
 

@@ -152,6 +152,8 @@ int tune_module(mononn_module* m, void* const* args, int n, void* stream) {
         {"barrier_arrive cta", &TuningSpec::barrier_arrive, 1u},
         {"barrier_arrive warp", &TuningSpec::barrier_arrive, 2u},
         {"row_split off", &TuningSpec::row_split, 1u},
+        {"out_fusion off", &TuningSpec::out_fusion, 1u},
+        {"out_fusion on", &TuningSpec::out_fusion, 2u},
     };
     for (const Structural& c : choices) {
       if (best.*(c.field) == c.value) continue;

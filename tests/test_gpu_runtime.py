@@ -263,3 +263,21 @@ def test_row_per_warp_layernorm_keeps_parity_when_the_split_is_switched_off(tmp_
     mod.set_weights({names[k]: v for k, v in w.items()})
     assert_parity(run(mod, cfg, inp), R.bert_encoder(cfg, w, inp), "row per warp")
     mod.close()
+
+
+def test_out_projection_in_a_stage_of_its_own_keeps_parity(tmp_path):
+    """By default the out-projection shares the attention's stage and waits on its arrival
+    counter; `out_fusion: off` gives it a stage behind a grid barrier. Same results."""
+    from mononn_b200.module import describe
+    cfg, w, inp = small()
+    text, names = bert_hlo(cfg)
+    spec = describe("hlo", text)["spec"]
+    assert spec["out_fusion"] == "on"
+    spec["out_fusion"] = "off"
+    (tmp_path / "cluster_0").mkdir()
+    (tmp_path / "cluster_0" / "best_tuning_spec.json").write_text(json.dumps(spec))
+    mod = compile_hlo(text, spec_dir=str(tmp_path), barrier_timeout_us=500000)
+    assert all("wait_flag" not in o for s in mod.plan()["stages"] for o in s["ops"])
+    mod.set_weights({names[k]: v for k, v in w.items()})
+    assert_parity(run(mod, cfg, inp), R.bert_encoder(cfg, w, inp), "out-projection behind a grid barrier")
+    mod.close()

@@ -19,26 +19,39 @@ def test_bert_base_stage_structure(base_plan):
     assert p["grid"] == 148 and p["block"] == 384
     assert p["smem_bytes"] <= 232448
     stages = p["stages"]
-    # 12 (batch, head) pairs cannot fill 148 CTAs: the Q/K/V projections run inside the attention items
-    # and each LayerNorm shares the stage of the split-K GEMM that feeds it: four stages a layer
-    assert len(stages) == 1 + 12 * 4
-    kinds = [tuple(o["kind"] for o in s["ops"]) for s in stages[:5]]
-    assert kinds == [("embed",), ("attention",), ("gemm", "layernorm"), ("gemm",), ("gemm", "layernorm")]
+    # 12 (batch, head) pairs cannot fill 148 CTAs: the Q/K/V projections run inside the attention items,
+    # the out-projection shares their stage behind the attention's arrival counter, and each
+    # LayerNorm shares the stage of the split-K GEMM that feeds it: three stages a layer
+    assert len(stages) == 1 + 12 * 3
+    kinds = [tuple(o["kind"] for o in s["ops"]) for s in stages[:4]]
+    assert kinds == [("embed",), ("attention", "gemm", "layernorm"), ("gemm",), ("gemm", "layernorm")]
     assert stages[1]["ops"][0]["flags"] & (1 << 11)
+    # the out-projection waits for exactly the attention items, on a counter of its own
+    att, o, ln = stages[1]["ops"]
+    assert o["wait_flag"] == att["flag"] and o["wait_target"] == att["n_items"] == 12 and not att["waits"]
+    assert o["flag"] == ln["flag"] != att["flag"] and o["n_items"] + att["n_items"] <= 148
     # the row items wait for exactly the GEMM items dealt before them
     for s in stages:
-        if len(s["ops"]) == 2:
-            g, ln = s["ops"]
+        if [x["kind"] for x in s["ops"]][-2:] == ["gemm", "layernorm"]:
+            g, ln = s["ops"][-2:]
             assert g["flag"] == ln["flag"] and not g["waits"] and ln["waits"] and ln["flag_target"] == g["n_items"]
+    # with out_fusion off the out-projection keeps a stage of its own: four stages a layer
+    four = describe("encoder", bert_base().to_json(), spec=dict(base_plan["spec"], out_fusion="off"))["plan"]
+    assert len(four["stages"]) == 1 + 12 * 4 and base_plan["spec"]["out_fusion"] == "on"
+    assert [tuple(o["kind"] for o in s["ops"]) for s in four["stages"][1:3]] == [("attention",), ("gemm", "layernorm")]
     # every GEMM / attention operator fits one wave of the 148 CTAs at b1/s128
     assert all(o["n_items"] <= 148 for s in stages for o in s["ops"])
 
 
 def test_row_fusion_off_keeps_layernorm_stages(base_plan):
-    off = dict(base_plan["spec"], row_fusion="off")
+    off = dict(base_plan["spec"], row_fusion="off", out_fusion="off")
     p = describe("encoder", bert_base().to_json(), spec=off)["plan"]
     assert len(p["stages"]) == 1 + 12 * 6
-    assert all("flag" not in o for s in p["stages"] for o in s["ops"])
+    assert all("flag" not in o and "wait_flag" not in o for s in p["stages"] for o in s["ops"])
+    # the two choices are independent: the out-projection can still share the attention's stage
+    p = describe("encoder", bert_base().to_json(), spec=dict(off, out_fusion="on"))["plan"]
+    assert len(p["stages"]) == 1 + 12 * 5
+    assert [o["kind"] for o in p["stages"][1]["ops"]] == ["attention", "gemm"]
     assert p["spec_echo"]["row_fusion"] == "off" if "spec_echo" in p else True
 
 
@@ -61,15 +74,16 @@ def test_projections_stay_a_stage_of_their_own_when_attention_fills_the_gpu(lib_
     when the attention stage leaves CTAs idle (or on request), never for long sequences."""
     off = dict(base_plan["spec"], qkv_fusion="off")
     p = describe("encoder", bert_base().to_json(), spec=off)["plan"]
-    assert len(p["stages"]) == 1 + 12 * 5
+    assert len(p["stages"]) == 1 + 12 * 4
     assert [o["kind"] for o in p["stages"][1]["ops"]] == ["gemm", "gemm", "gemm"]
+    assert [o["kind"] for o in p["stages"][2]["ops"]] == ["attention", "gemm", "layernorm"]
     assert abs(p["algorithmic_flops"] - base_plan["plan"]["algorithmic_flops"]) < 1e6
     many = describe("encoder", bert_tiny(batch=160, seq=16, layers=1).to_json())["plan"]   # 160 pairs > 148 CTAs
     assert [o["kind"] for o in many["stages"][1]["ops"]] == ["gemm", "gemm", "gemm"]
     forced = describe("encoder", bert_tiny(batch=160, seq=16, layers=1).to_json(),
                       spec=dict(describe("encoder", bert_tiny(batch=160, seq=16, layers=1).to_json())["spec"],
                                 qkv_fusion="on"))["plan"]
-    assert [o["kind"] for o in forced["stages"][1]["ops"]] == ["attention"]
+    assert [o["kind"] for o in forced["stages"][1]["ops"]][0] == "attention"
     long_seq = describe("encoder", bert_tiny(batch=1, seq=200, layers=1).to_json())["plan"]
     assert [o["kind"] for o in long_seq["stages"][1]["ops"]] == ["gemm", "gemm", "gemm"]
 

@@ -53,7 +53,7 @@ def test_two_replicas_report_whole_job_throughput(tmp_path):
     line = [l for l in out.stdout.splitlines() if l.startswith("{")][-1]
     import json
     r = json.loads(line)
-    assert r["max_s"] == 0.8 and r["stages"] == 1 + 2 * 4
+    assert r["max_s"] == 0.8 and r["stages"] == 1 + 2 * 3
     assert abs(r["value"] - 2 * 100 / 0.8) < 1e-9
 
 

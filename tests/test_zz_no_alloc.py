@@ -28,7 +28,7 @@ def test_noalloc_attention_matches_the_module_path_twice(tmp_path):
     inp = make_inputs(cfg, 31, pad_fraction=0.25)
     # the regular module with the Q/K/V projections as a stage of their own, so that its Q, K
     # and V^T tensors exist in the temp buffer for the stand-alone call to read
-    spec = dict(describe("encoder", cfg.to_json())["spec"], qkv_fusion="off")
+    spec = dict(describe("encoder", cfg.to_json())["spec"], qkv_fusion="off", out_fusion="off")
     (tmp_path / "cluster_0").mkdir()
     (tmp_path / "cluster_0" / "best_tuning_spec.json").write_text(json.dumps(spec))
     mod = compile_encoder(cfg, spec_dir=str(tmp_path))
