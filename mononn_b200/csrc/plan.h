@@ -59,6 +59,11 @@ struct TuningSpec {
   // 1: it keeps a stage of its own; 0: the scheduler decides (shared when the attention's work
   // items occupy at most half of the CTAs and the LayerNorms are joined too) and writes it back
   uint32_t out_fusion = 0;
+  // 2: a GEMM that reads the output of a LayerNorm or of another GEMM shares that operator's stage
+  // too and waits on its arrival counter (with out_fusion a whole transformer layer becomes one
+  // stage); 1: no; 0: the scheduler decides (no: it measured no faster than the barriers) and
+  // writes it back
+  uint32_t chain_fusion = 0;
 };
 
 // ------------------------------------------------------------------- FGraph
@@ -160,6 +165,9 @@ struct PlanOp {
   // waits for before it loads its A operand; wflag_index < 0: none
   BufRef wflag;
   int wflag_index = -1;
+  // arrival counter a LayerNorm adds to after each item because a GEMM of the stage waits for it
+  // (the counter's address travels in q[1]); sflag_index < 0: none
+  int sflag_index = -1;
 };
 
 // How one HLO constant lands in the constant arena.

@@ -10,6 +10,7 @@
 //   buffers           BufferAssignmentPass + XLA's BufferAssignment offsets
 //                     (mononn_engine/codegen/graph_codegen.cc:113-257); XLA is absent, so a
 //                     liveness-based first-fit allocator decides the temp-arena offsets
+#include <functional>
 #include <algorithm>
 #include <cstring>
 #include <set>
@@ -239,35 +240,39 @@ int validate_plan(const Plan& P, std::string* err) {
     }
   }
   for (const StageDesc& sd : P.stages) {
-    // a row op that waits on an arrival counter needs its signalling GEMMs earlier in the same
-    // stage's item order, their item counts adding up to its target
-    bool seen_wait = false;
+    // An operator that waits on an arrival counter needs the operators that add to that counter
+    // earlier in the same stage's item order (so that no CTA meets a waiting item before an item it
+    // waits for), their item counts adding up to its target.
+    auto signalled_before = [&](uint32_t a, int counter) {
+      uint32_t target = 0;
+      for (uint32_t b = sd.op_begin; b < a; ++b) {
+        const PlanOp& s = P.ops[b];
+        if ((!s.waits && s.flag_index == counter) || s.sflag_index == counter) target += s.d.n_items;
+      }
+      return target;
+    };
     for (uint32_t a = sd.op_begin; a < sd.op_begin + sd.op_count; ++a) {
       const PlanOp& op = P.ops[a];
       if (op.wflag_index >= 0) {
-        // a GEMM behind an attention of the same stage: the attention items come first and add up
-        uint32_t target = 0;
-        for (uint32_t b = sd.op_begin; b < a; ++b)
-          if (P.ops[b].d.kind == OP_ATTENTION && P.ops[b].flag_index == op.wflag_index) target += P.ops[b].d.n_items;
+        // a GEMM behind the operator of the same stage that writes its A operand
+        const uint32_t target = signalled_before(a, op.wflag_index);
         if (op.d.kind != OP_GEMM || op.wflag.space != SPACE_SCRATCH || target == 0 || target != op.d.wait_target)
-          return bad(op.name + ": wait target does not match its attention");
+          return bad(op.name + ": wait target does not match the operator it waits for");
       } else if (op.d.wait_target != 0) {
         return bad(op.name + ": wait target without a counter");
       }
+      if (op.sflag_index >= 0 && (op.d.kind != OP_LAYERNORM || op.q[1].space != SPACE_SCRATCH))
+        return bad(op.name + ": only a LayerNorm signals through q[1]");
       if (op.flag_index < 0) {
         if (op.d.flag_target != 0) return bad(op.name + ": wait target without a counter");
         continue;
       }
       if (op.flag.space != SPACE_SCRATCH) return bad(op.name + ": arrival counter outside the scratch");
       if (!op.waits) {
-        if ((op.d.kind != OP_GEMM && op.d.kind != OP_ATTENTION) || seen_wait)
-          return bad(op.name + ": signalling operator after a waiting one");
+        if (op.d.kind != OP_GEMM && op.d.kind != OP_ATTENTION) return bad(op.name + ": operator cannot signal");
         continue;
       }
-      seen_wait = true;
-      uint32_t target = 0;
-      for (uint32_t b = sd.op_begin; b < a; ++b)
-        if (!P.ops[b].waits && P.ops[b].flag_index == op.flag_index) target += P.ops[b].d.n_items;
+      const uint32_t target = signalled_before(a, op.flag_index);
       if (target == 0 || target != op.d.flag_target) return bad(op.name + ": wait target does not match its GEMMs");
     }
   }
@@ -425,6 +430,24 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
   // a GEMM that shares the stage of the attention whose output it reads waits on that attention's
   // counter (its own flag_of stays free for the row op that may follow it in the same stage)
   std::vector<int> wflag_of(ops.size(), -1);
+  // ... or, with chain fusion, of the LayerNorm or GEMM whose output it reads: a LayerNorm that is
+  // waited for signals a counter of its own (sflag_of; its flag_of is the one it waits on)
+  std::vector<int> sflag_of(ops.size(), -1);
+  std::vector<int> wprod(ops.size(), -1);     // the operator a GEMM with wflag_of waits for
+  std::vector<uint32_t> ops_at;               // operators per depth so far (a stage holds kMaxStageOps)
+  // does the chain of waits that starts at operator `from` pass through operator `target`?
+  std::function<bool(int, int)> chain_reaches = [&](int from, int target) -> bool {
+    if (from < 0) return false;
+    if (from == target) return true;
+    if (wflag_of[from] >= 0) return chain_reaches(wprod[from], target);
+    if (waits[from]) {
+      for (size_t w = 0; w < ops.size(); ++w)
+        if (!waits[w] && flag_of[w] == flag_of[from] && ops[w].stage == ops[from].stage &&
+            chain_reaches(static_cast<int>(w), target))
+          return true;
+    }
+    return false;
+  };
   int n_flags = 0;
   int n_stages = 0;
   // Left to the scheduler (0), a LayerNorm joins its GEMMs' stage when its rows are one wave of
@@ -448,25 +471,48 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
       max_attn_items = std::max(max_attn_items, o.batches * o.heads * ((o.seq + 127u) / 128u));
   if (P.spec.out_fusion == 0)
     P.spec.out_fusion = (P.spec.row_fusion == 2 && max_attn_items != 0 && max_attn_items * 2u <= P.grid) ? 2u : 1u;
+  // Chain fusion goes on from there: a GEMM whose A operand is written by a LayerNorm or by
+  // another GEMM of the stage joins it too and waits for that operator's counter, so that a whole
+  // layer (attention, out-projection, LayerNorm, FFN-up, FFN-down, LayerNorm) is one stage of
+  // operators chained by counters and only the attention still waits for a grid barrier.
+  // Measured on BERT-base b1: a chain of counters costs what the grid barriers it replaces cost
+  // (512 us either way: release, observation and first tile make the hop, not the barrier), so
+  // left to the scheduler it stays off; the tuner tries it.
+  if (P.spec.chain_fusion == 0) P.spec.chain_fusion = 1u;
   for (size_t i = 0; i < ops.size(); ++i) {
     int fuse_src = -1, fuse_stage = -1;
-    bool gemm_after_attention = false;
-    if (ops[i].kind == OP_GEMM && P.spec.out_fusion == 2 && ops[i].a >= 0 && producer[ops[i].a] >= 0 &&
-        ops[producer[ops[i].a]].kind == OP_ATTENTION && writers[ops[i].a].size() == 1 &&
-        wflag_of[producer[ops[i].a]] < 0) {
-      fuse_src = ops[i].a;
-      fuse_stage = ops[producer[ops[i].a]].stage;
-      gemm_after_attention = true;
+    bool gemm_after_producer = false;
+    if (ops[i].kind == OP_GEMM && ops[i].a >= 0 && producer[ops[i].a] >= 0 && writers[ops[i].a].size() == 1) {
+      const int pr = producer[ops[i].a];
+      const OpKind pk = ops[pr].kind;
+      const bool allowed = (pk == OP_ATTENTION && P.spec.out_fusion == 2) ||
+                           ((pk == OP_LAYERNORM || pk == OP_GEMM) && P.spec.chain_fusion == 2 &&
+                            g.tensors[ops[i].a].kind == TKind::ActF16);
+      if (allowed && ops_at.size() > static_cast<size_t>(ops[pr].stage) &&
+          ops_at[ops[pr].stage] < kMaxStageOps) {
+        fuse_src = ops[i].a;
+        fuse_stage = ops[pr].stage;
+        gemm_after_producer = true;
+      }
     }
     if (ops[i].kind == OP_LAYERNORM && P.spec.row_fusion != 1 && ops[i].src >= 0 &&
         g.tensors[ops[i].src].kind == TKind::AccF32 && !writers[ops[i].src].empty()) {
       const int T = ops[i].src;
       int d = -1;
       for (int w : writers[T]) d = std::max(d, ops[w].stage);
+      // the writers at that depth must be GEMMs free to signal, or operators those GEMMs already
+      // wait for through their chain of counters (a LayerNorm that pre-loaded the accumulator)
       bool ok = true;
-      for (int w : writers[T])
-        if (ops[w].stage == d && (ops[w].kind != OP_GEMM || flag_of[w] >= 0)) ok = false;
-      if (ok) {
+      for (int w : writers[T]) {
+        if (ops[w].stage != d) continue;
+        if (ops[w].kind == OP_GEMM && flag_of[w] < 0) continue;
+        bool ordered = false;
+        for (int v : writers[T])
+          if (v != w && ops[v].stage == d && ops[v].kind == OP_GEMM && flag_of[v] < 0 && chain_reaches(v, w))
+            ordered = true;
+        if (!ordered) ok = false;
+      }
+      if (ok && d >= 0 && ops_at[d] < kMaxStageOps) {
         fuse_src = T;
         fuse_stage = d;
       }
@@ -478,21 +524,29 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
     // runs after every earlier reader of the old value
     for (int t : outputs_of(ops[i]))
       if (producer[t] >= 0) depth = std::max(depth, last_reader[t] + 1);
-    // an op that accumulates into a tensor someone pre-loaded runs after that producer
+    // an op that accumulates into a tensor someone pre-loaded runs after that producer (which it
+    // does inside one stage too when the chain of counters it waits on passes through that producer)
     for (int t : outputs_of(ops[i]))
-      if (producer[t] >= 0) depth = std::max(depth, ops[producer[t]].stage + 1);
+      if (producer[t] >= 0 && !(gemm_after_producer && ops[producer[t]].stage == fuse_stage &&
+                                chain_reaches(producer[fuse_src], producer[t])))
+        depth = std::max(depth, ops[producer[t]].stage + 1);
     if (fuse_src >= 0) {
-      if (depth <= fuse_stage && gemm_after_attention) {
-        const int att = producer[fuse_src];
+      if (depth <= fuse_stage && gemm_after_producer) {
+        const int pr = producer[fuse_src];
         depth = fuse_stage;
-        if (flag_of[att] < 0) flag_of[att] = n_flags++;  // several GEMMs may read one attention's output
-        wflag_of[i] = flag_of[att];
+        // several GEMMs may read one operator's output: they share its counter
+        int& sig = (ops[pr].kind == OP_LAYERNORM) ? sflag_of[pr] : flag_of[pr];
+        if (sig < 0) sig = n_flags++;
+        wflag_of[i] = sig;
+        wprod[i] = pr;
+      } else if (gemm_after_producer) {
+        depth = std::max(depth, fuse_stage + 1);  // stays a stage behind its producer
       } else if (depth <= fuse_stage) {
         depth = fuse_stage;
         flag_of[i] = n_flags;
         waits[i] = 1;
         for (int w : writers[fuse_src])
-          if (ops[w].stage == fuse_stage) flag_of[w] = n_flags;
+          if (ops[w].stage == fuse_stage && ops[w].kind == OP_GEMM && flag_of[w] < 0) flag_of[w] = n_flags;
         ++n_flags;
       } else {
         depth = std::max(depth, fuse_stage + 1);
@@ -500,6 +554,8 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
     }
     ops[i].stage = depth;
     n_stages = std::max(n_stages, depth + 1);
+    if (ops_at.size() <= static_cast<size_t>(depth)) ops_at.resize(depth + 1, 0);
+    ++ops_at[depth];
     for (int t : inputs_of(ops[i])) last_reader[t] = std::max(last_reader[t], depth);
     for (int t : outputs_of(ops[i])) {
       producer[t] = static_cast<int>(i);
@@ -719,24 +775,32 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
     return static_cast<uint32_t>(P.tmaps.size() - 1);
   };
 
-  // ---- per stage: count GEMMs to share the CTA budget
-  std::vector<uint32_t> gemms_in_stage(n_stages, 0), attn_items_in_stage(n_stages, 0);
-  for (const FOp& o : ops)
-    if (o.kind == OP_ATTENTION) attn_items_in_stage[o.stage] += o.batches * o.heads * ((o.seq + 127u) / 128u);
-  for (const FOp& o : ops)
-    if (o.kind == OP_GEMM) gemms_in_stage[o.stage]++;
-
+  // Operators that wait for others of their own stage come after them, so that a CTA meets the
+  // items that never wait before any item that does, and every waiting item only items it does
+  // not wait for: ordered by the length of the chain of counters behind them.
+  std::vector<int> level(ops.size(), 0);
+  for (size_t i = 0; i < ops.size(); ++i) {
+    if (wflag_of[i] >= 0) level[i] = level[wprod[i]] + 1;
+    if (waits[i])
+      for (size_t w = 0; w < i; ++w)
+        if (!waits[w] && flag_of[w] == flag_of[i] && ops[w].stage == ops[i].stage)
+          level[i] = std::max(level[i], level[w] + 1);
+  }
   // ---- emit ops stage by stage
   std::vector<std::vector<size_t>> by_stage(n_stages);
-  for (size_t i = 0; i < ops.size(); ++i)
-    if (!waits[i] && wflag_of[i] < 0) by_stage[ops[i].stage].push_back(i);
-  // Operators that wait for others of their own stage come after them, so that a CTA meets the
-  // items that never wait before any item that does: first the GEMMs behind an attention, then
-  // the row ops behind GEMMs (which may be those same GEMMs).
-  for (size_t i = 0; i < ops.size(); ++i)
-    if (wflag_of[i] >= 0) by_stage[ops[i].stage].push_back(i);
-  for (size_t i = 0; i < ops.size(); ++i)
-    if (waits[i]) by_stage[ops[i].stage].push_back(i);
+  for (int lv = 0; lv <= static_cast<int>(kMaxStageOps); ++lv)
+    for (size_t i = 0; i < ops.size(); ++i)
+      if (level[i] == lv) by_stage[ops[i].stage].push_back(i);
+
+  // ---- the GEMMs that run side by side (same stage, same place in the chains of counters) share
+  // the CTAs that the stage's attention items leave free
+  std::vector<std::vector<uint32_t>> gemms_side_by_side(n_stages, std::vector<uint32_t>(kMaxStageOps + 1, 0));
+  std::vector<uint32_t> attn_items_in_stage(n_stages, 0);
+  for (size_t i = 0; i < ops.size(); ++i) {
+    const FOp& o = ops[i];
+    if (o.kind == OP_ATTENTION) attn_items_in_stage[o.stage] += o.batches * o.heads * ((o.seq + 127u) / 128u);
+    if (o.kind == OP_GEMM) gemms_side_by_side[o.stage][std::min<int>(level[i], kMaxStageOps)]++;
+  }
 
   for (int s = 0; s < n_stages; ++s) {
     StageDesc sd{};
@@ -765,7 +829,8 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
           const bool can_split = (O.kind == TKind::AccF32) && o.act == ACT_NONE;
           // CTAs busy with attention items of the same stage are not available to its GEMMs
           const uint32_t free_ctas = P.grid > attn_items_in_stage[s] ? P.grid - attn_items_in_stage[s] : 1u;
-          const uint32_t budget = std::max(1u, free_ctas / std::max(1u, gemms_in_stage[s]));
+          const uint32_t budget =
+              std::max(1u, free_ctas / std::max(1u, gemms_side_by_side[s][std::min<int>(level[oi], kMaxStageOps)]));
           GemmTileSpec ts;
           auto it = spec_in.gemm.find(o.name);
           if (it != spec_in.gemm.end()) ts = it->second;
@@ -1071,6 +1136,10 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
         po.wflag = BufRef{SPACE_SCRATCH, 0, flags_off + 8ull * wflag_of[oi]};
         po.wflag_index = wflag_of[oi];
       }
+      if (sflag_of[oi] >= 0) {  // a LayerNorm that a GEMM of the stage waits for: its counter goes in q[1]
+        po.q[1] = BufRef{SPACE_SCRATCH, 0, flags_off + 8ull * sflag_of[oi]};
+        po.sflag_index = sflag_of[oi];
+      }
       sd.n_items += d.n_items;
       if (!sname.empty()) sname += "+";
       sname += o.name;
@@ -1088,7 +1157,9 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
       if (P.ops[a].wflag_index < 0) continue;
       uint32_t target = 0;
       for (size_t b = sd.op_begin; b < a; ++b)
-        if (!P.ops[b].waits && P.ops[b].flag_index == P.ops[a].wflag_index) target += P.ops[b].d.n_items;
+        if ((!P.ops[b].waits && P.ops[b].flag_index == P.ops[a].wflag_index) ||
+            P.ops[b].sflag_index == P.ops[a].wflag_index)
+          target += P.ops[b].d.n_items;
       P.ops[a].d.wait_target = target;
     }
     if (sd.op_count > kMaxStageOps) {

@@ -80,6 +80,7 @@ std::string spec_to_json(const Plan& plan, uint32_t sm_count) {
   root.set("l2_hints", Json::string(plan.spec.l2_hints == 1 ? "off" : "on"));
   root.set("row_split", Json::string(plan.spec.row_split == 1 ? "off" : "on"));
   root.set("out_fusion", Json::string(plan.spec.out_fusion == 2 ? "on" : "off"));
+  root.set("chain_fusion", Json::string(plan.spec.chain_fusion == 2 ? "on" : "off"));
   root.set("barrier_arrive", Json::string(plan.spec.barrier_arrive == 1 || plan.cluster > 1
                                               ? "cta"
                                               : (plan.spec.barrier_arrive == 2 ? "warp" : "last")));
@@ -194,6 +195,7 @@ std::string plan_to_json(const Plan& plan) {
         o.set("waits", Json::number(op.waits ? 1 : 0));
         o.set("flag_target", Json::number(op.d.flag_target));
       }
+      if (op.sflag_index >= 0) o.set("signal_flag", Json::number(op.sflag_index));
       if (op.wflag_index >= 0) {
         o.set("wait_flag", Json::number(op.wflag_index));
         o.set("wait_target", Json::number(op.d.wait_target));
@@ -299,6 +301,8 @@ int spec_from_json(const std::string& text, TuningSpec* spec, std::string* err) 
       if (const Json* cl = rt->find("cluster_dim")) spec->cluster = static_cast<uint32_t>(cl->get_number("x", 1));
       if (const Json* b = rt->find("block_dim")) spec->block = static_cast<uint32_t>(b->get_number("x", kThreads));
     }
+  if (const Json* cf = root.find("chain_fusion"))
+    if (cf->type == Json::String) spec->chain_fusion = cf->str == "on" ? 2u : (cf->str == "off" ? 1u : 0u);
   if (const Json* of = root.find("out_fusion"))
     if (of->type == Json::String) spec->out_fusion = of->str == "on" ? 2u : (of->str == "off" ? 1u : 0u);
   if (const Json* rs = root.find("row_split"))

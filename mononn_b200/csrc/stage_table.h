@@ -74,6 +74,7 @@ enum OpFlags : uint32_t {
 //             padding above / left of the image, K = kh*kw*C (columns K..cols-1 are written as 0)
 //  EMBED: q_col = offset added to the position index; p[4] = 0: no position table
 //  ATTENTION with F_POS_BIAS: q[0] = f16 [heads, seq, seq] added to the scaled scores (seq % 32 == 0)
+//  LAYERNORM: q[1] = arrival counter the operator adds to after every item (0: nobody waits for it)
 //  LAYERNORM and EMBED may also write q[2] = f32 copy of the result plus the f16 bias q[3]
 //  (residual + bias pre-loaded into the accumulator of the next split-K GEMM)
 struct alignas(16) OpDesc {

@@ -154,6 +154,8 @@ int tune_module(mononn_module* m, void* const* args, int n, void* stream) {
         {"row_split off", &TuningSpec::row_split, 1u},
         {"out_fusion off", &TuningSpec::out_fusion, 1u},
         {"out_fusion on", &TuningSpec::out_fusion, 2u},
+        {"chain_fusion off", &TuningSpec::chain_fusion, 1u},
+        {"chain_fusion on", &TuningSpec::chain_fusion, 2u},
     };
     for (const Structural& c : choices) {
       if (best.*(c.field) == c.value) continue;

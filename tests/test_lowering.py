@@ -245,3 +245,27 @@ def test_structure_choices_left_to_the_scheduler_follow_the_row_count(base_plan)
     forced = describe("encoder", bert_base(batch=16).to_json(), spec=dict(big["spec"], row_fusion="on", l2_hints="on"))
     assert (forced["spec"]["row_fusion"], forced["spec"]["l2_hints"]) == ("on", "on")
     assert len(forced["plan"]["stages"]) < len(big["plan"]["stages"])
+
+
+def test_chain_fusion_makes_a_layer_one_stage_of_operators_chained_by_counters(base_plan):
+    """With chain_fusion a GEMM whose A operand is written by a LayerNorm or by another GEMM of
+    the stage joins it and waits for that operator's counter: attention -> out-projection ->
+    LayerNorm -> FFN-up -> FFN-down -> LayerNorm in one stage, every operator behind the ones it
+    waits for, every target the item count of what it waits for. Off by default."""
+    assert base_plan["spec"]["chain_fusion"] == "off"
+    spec = dict(base_plan["spec"], chain_fusion="on")
+    spec.pop("gemm_spec_list")          # tiles are chosen anew for the new structure
+    d = describe("encoder", bert_base().to_json(), spec=spec)
+    stages = d["plan"]["stages"]
+    assert len(stages) == 1 + 12
+    att, o, ln1, up, down, ln2 = stages[1]["ops"]
+    assert [x["kind"] for x in stages[1]["ops"]] == ["attention", "gemm", "layernorm", "gemm", "gemm", "layernorm"]
+    assert o["wait_flag"] == att["flag"] and o["wait_target"] == att["n_items"]
+    assert ln1["waits"] and ln1["flag"] == o["flag"] and ln1["flag_target"] == o["n_items"]
+    assert up["wait_flag"] == ln1["signal_flag"] and up["wait_target"] == ln1["n_items"]
+    assert down["wait_flag"] == up["flag"] and down["wait_target"] == up["n_items"]
+    assert ln2["waits"] and ln2["flag"] == down["flag"] and ln2["flag_target"] == down["n_items"]
+    # chained GEMMs run one after another: each may use all the CTAs the attention leaves free
+    assert all(x["n_items"] <= 148 - att["n_items"] for x in (o, up, down))
+    counters = {att["flag"], o["flag"], ln1["signal_flag"], up["flag"], down["flag"]}
+    assert len(counters) == 5
