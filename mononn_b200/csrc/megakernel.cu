@@ -278,7 +278,6 @@ struct Ctrl {
   uint32_t barriers_seen;  // grid barriers of this launch the CTA's poller has observed (monotonic)
   uint32_t warps_done;     // epilogue warps that finished a stage (monotonic; every eighth arrives for the CTA)
   uint32_t items_done[2];  // per accumulator buffer: epilogue warps that finished a GEMM item a row op waits for
-  uint32_t rows_done[4];   // epilogue warps that finished a row item some GEMM of the stage waits for
   uint32_t tiles_done[5];  // attention: epilogue warps that finished writing the Q/K/V tiles ([0]) or the P
                            // tiles of key chunk j ([1 + j]); every eighth count hands the tiles to the MMA issuer;
                            // [4]: warps that stored their part of an item's output (every eighth counts the item)
@@ -688,11 +687,7 @@ __device__ void role_weight_producer(Ctx c, uint32_t lane) {
       // (idle in this stage, or holding items of operators that wait for the attention) bring the
       // weights into L2 now (this role runs ahead of the barriers), shared out among them, so that
       // the few stream them from L2 instead of HBM.
-      uint32_t busy = 0;  // work items up to and including the last such attention operator
-      for (uint32_t k = 0; k < st.op_count; ++k) {
-        const OpDesc* gop = P.ops + st.op_begin + k;
-        if (__ldg(&gop->kind) == OP_ATTENTION && (__ldg(&gop->flags) & F_FUSED_QKV)) busy = st.item_end[k];
-      }
+      const uint32_t busy = st.attn_prefetch_from;  // (found by the scheduler: no descriptor is read to learn it)
       if (busy != 0u && blockIdx.x >= busy) {
         const uint32_t n_idle = gridDim.x - busy, me = blockIdx.x - busy;
         for (uint32_t k = 0; k < st.op_count; ++k) {
@@ -2043,7 +2038,7 @@ __device__ void role_simt(Ctx c, uint32_t tmem_base, uint32_t tid_in_group) {
   const KernelParams& P = *c.P;
   // warp w of the CTA reads TMEM lanes 32*(w%4)..: the SIMT warps 4..11 form two sets of quarters
   const uint32_t widx = tid_in_group >> 5, quarter = widx & 3u, half = widx >> 2, lane = tid_in_group & 31u;
-  uint32_t a_cnt = 0, acc_cnt = 0, row_items = 0;
+  uint32_t a_cnt = 0, acc_cnt = 0;
   for (uint32_t s = P.stage_begin; s < P.stage_end; ++s) {
     c.stage = s;
     const StageDesc st = load_stage(P, s);
@@ -2118,13 +2113,6 @@ __device__ void role_simt(Ctx c, uint32_t tmem_base, uint32_t tid_in_group) {
             WAIT_OR_RETURN(rowwise_split_item(c, op, it.local, widx, lane));
           } else {
             rowwise_item(op, it.local, widx, lane, P, s);
-          }
-          if (op.kind == OP_LAYERNORM && op.q[1] != 0) {
-            // a GEMM of this stage waits for this operator: the warp that finishes the item last
-            // counts it (four counters in turn, so that a warp that is an item ahead counts elsewhere)
-            if (last_warp_of(&c.ctrl->rows_done[row_items & 3u], lane))
-              red_release_gpu_add(reinterpret_cast<uint32_t*>(op.q[1]), 1u);
-            ++row_items;
           }
           break;
         case OP_PATCHIFY:
@@ -2239,7 +2227,6 @@ mononn_megakernel(const __grid_constant__ KernelParams P) {
     ctrl->warps_done = 0;
     ctrl->items_done[0] = ctrl->items_done[1] = 0;
     for (uint32_t i = 0; i < 5; ++i) ctrl->tiles_done[i] = 0;
-    for (uint32_t i = 0; i < 4; ++i) ctrl->rows_done[i] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {

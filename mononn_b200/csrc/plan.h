@@ -56,13 +56,13 @@ struct TuningSpec {
   // 0 / 2: a LayerNorm with few rows shares each row among four warps; 1: always one warp per row
   uint32_t row_split = 0;
   // 2: the GEMM that reads an attention's output shares its stage and waits on its arrival counter;
-  // 1: it keeps a stage of its own; 0: the scheduler decides (shared when the attention's work
-  // items occupy at most half of the CTAs and the LayerNorms are joined too) and writes it back
+  // 3: only behind an attention that computes its own projections; 1: it keeps a stage of its own;
+  // 0: the scheduler decides (3 when the attention's work items occupy at most half of the CTAs
+  // and the LayerNorms are joined too, else 1) and writes it back
   uint32_t out_fusion = 0;
-  // 2: a GEMM that reads the output of a LayerNorm or of another GEMM shares that operator's stage
-  // too and waits on its arrival counter (with out_fusion a whole transformer layer becomes one
-  // stage); 1: no; 0: the scheduler decides (no: it measured no faster than the barriers) and
-  // writes it back
+  // 2: a GEMM that reads the output of another GEMM shares that GEMM's stage too and waits on its
+  // arrival counter (FFN-up and FFN-down in one stage); 1: no; 0: the scheduler decides (no: it
+  // measured no faster than the barrier) and writes it back
   uint32_t chain_fusion = 0;
 };
 
@@ -165,9 +165,6 @@ struct PlanOp {
   // waits for before it loads its A operand; wflag_index < 0: none
   BufRef wflag;
   int wflag_index = -1;
-  // arrival counter a LayerNorm adds to after each item because a GEMM of the stage waits for it
-  // (the counter's address travels in q[1]); sflag_index < 0: none
-  int sflag_index = -1;
 };
 
 // How one HLO constant lands in the constant arena.

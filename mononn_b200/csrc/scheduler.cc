@@ -247,7 +247,7 @@ int validate_plan(const Plan& P, std::string* err) {
       uint32_t target = 0;
       for (uint32_t b = sd.op_begin; b < a; ++b) {
         const PlanOp& s = P.ops[b];
-        if ((!s.waits && s.flag_index == counter) || s.sflag_index == counter) target += s.d.n_items;
+        if (!s.waits && s.flag_index == counter) target += s.d.n_items;
       }
       return target;
     };
@@ -261,8 +261,6 @@ int validate_plan(const Plan& P, std::string* err) {
       } else if (op.d.wait_target != 0) {
         return bad(op.name + ": wait target without a counter");
       }
-      if (op.sflag_index >= 0 && (op.d.kind != OP_LAYERNORM || op.q[1].space != SPACE_SCRATCH))
-        return bad(op.name + ": only a LayerNorm signals through q[1]");
       if (op.flag_index < 0) {
         if (op.d.flag_target != 0) return bad(op.name + ": wait target without a counter");
         continue;
@@ -430,9 +428,7 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
   // a GEMM that shares the stage of the attention whose output it reads waits on that attention's
   // counter (its own flag_of stays free for the row op that may follow it in the same stage)
   std::vector<int> wflag_of(ops.size(), -1);
-  // ... or, with chain fusion, of the LayerNorm or GEMM whose output it reads: a LayerNorm that is
-  // waited for signals a counter of its own (sflag_of; its flag_of is the one it waits on)
-  std::vector<int> sflag_of(ops.size(), -1);
+  // ... or, with chain fusion, of the GEMM whose output it reads
   std::vector<int> wprod(ops.size(), -1);     // the operator a GEMM with wflag_of waits for
   std::vector<uint32_t> ops_at;               // operators per depth so far (a stage holds kMaxStageOps)
   // does the chain of waits that starts at operator `from` pass through operator `target`?
@@ -469,14 +465,17 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
   for (const FOp& o : ops)
     if (o.kind == OP_ATTENTION)
       max_attn_items = std::max(max_attn_items, o.batches * o.heads * ((o.seq + 127u) / 128u));
+  // Left to the scheduler this is done only behind an attention that computes its own projections
+  // (a long stage on few CTAs, the others idle: BERT-base b1 -5 us); behind a short attention
+  // stage it measured slower (BERT-large b1 s384 +46 us, OPT-1.3B b1 +50 us, CLIP +94 us).
   if (P.spec.out_fusion == 0)
-    P.spec.out_fusion = (P.spec.row_fusion == 2 && max_attn_items != 0 && max_attn_items * 2u <= P.grid) ? 2u : 1u;
-  // Chain fusion goes on from there: a GEMM whose A operand is written by a LayerNorm or by
-  // another GEMM of the stage joins it too and waits for that operator's counter, so that a whole
-  // layer (attention, out-projection, LayerNorm, FFN-up, FFN-down, LayerNorm) is one stage of
-  // operators chained by counters and only the attention still waits for a grid barrier.
-  // Measured on BERT-base b1: a chain of counters costs what the grid barriers it replaces cost
-  // (512 us either way: release, observation and first tile make the hop, not the barrier), so
+    P.spec.out_fusion = (P.spec.row_fusion == 2 && max_attn_items != 0 && max_attn_items * 2u <= P.grid) ? 3u : 1u;
+  // Chain fusion goes on from there: a GEMM whose A operand is written by another GEMM joins that
+  // GEMM's stage too and waits for its counter (FFN-up, FFN-down and the LayerNorm behind it in
+  // one stage). With LayerNorms signalling as well a whole layer was one stage of operators chained
+  // by counters; measured on BERT-base b1 that chain cost what the grid barriers it replaced cost
+  // (512 us either way: release, observation and first tile make the hop, not the barrier), and
+  // the signalling code cost the other configurations half a per cent, so it was taken out again;
   // left to the scheduler it stays off; the tuner tries it.
   if (P.spec.chain_fusion == 0) P.spec.chain_fusion = 1u;
   for (size_t i = 0; i < ops.size(); ++i) {
@@ -485,8 +484,9 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
     if (ops[i].kind == OP_GEMM && ops[i].a >= 0 && producer[ops[i].a] >= 0 && writers[ops[i].a].size() == 1) {
       const int pr = producer[ops[i].a];
       const OpKind pk = ops[pr].kind;
-      const bool allowed = (pk == OP_ATTENTION && P.spec.out_fusion == 2) ||
-                           ((pk == OP_LAYERNORM || pk == OP_GEMM) && P.spec.chain_fusion == 2 &&
+      const bool allowed = (pk == OP_ATTENTION && (P.spec.out_fusion == 2 ||
+                                                   (P.spec.out_fusion == 3 && (ops[pr].flags & F_FUSED_QKV)))) ||
+                           (pk == OP_GEMM && P.spec.chain_fusion == 2 &&
                             g.tensors[ops[i].a].kind == TKind::ActF16);
       if (allowed && ops_at.size() > static_cast<size_t>(ops[pr].stage) &&
           ops_at[ops[pr].stage] < kMaxStageOps) {
@@ -535,9 +535,8 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
         const int pr = producer[fuse_src];
         depth = fuse_stage;
         // several GEMMs may read one operator's output: they share its counter
-        int& sig = (ops[pr].kind == OP_LAYERNORM) ? sflag_of[pr] : flag_of[pr];
-        if (sig < 0) sig = n_flags++;
-        wflag_of[i] = sig;
+        if (flag_of[pr] < 0) flag_of[pr] = n_flags++;
+        wflag_of[i] = flag_of[pr];
         wprod[i] = pr;
       } else if (gemm_after_producer) {
         depth = std::max(depth, fuse_stage + 1);  // stays a stage behind its producer
@@ -827,8 +826,10 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
             return MONONN_ERR_UNSUPPORTED;
           }
           const bool can_split = (O.kind == TKind::AccF32) && o.act == ACT_NONE;
-          // CTAs busy with attention items of the same stage are not available to its GEMMs
-          const uint32_t free_ctas = P.grid > attn_items_in_stage[s] ? P.grid - attn_items_in_stage[s] : 1u;
+          // CTAs busy with a few attention items of the same stage are not available to its GEMMs
+          // (attention items that fill the grid take whole waves and then leave all of it)
+          const uint32_t reserved = attn_items_in_stage[s] * 2u <= P.grid ? attn_items_in_stage[s] : 0u;
+          const uint32_t free_ctas = P.grid - reserved;
           const uint32_t budget =
               std::max(1u, free_ctas / std::max(1u, gemms_side_by_side[s][std::min<int>(level[oi], kMaxStageOps)]));
           GemmTileSpec ts;
@@ -1136,10 +1137,6 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
         po.wflag = BufRef{SPACE_SCRATCH, 0, flags_off + 8ull * wflag_of[oi]};
         po.wflag_index = wflag_of[oi];
       }
-      if (sflag_of[oi] >= 0) {  // a LayerNorm that a GEMM of the stage waits for: its counter goes in q[1]
-        po.q[1] = BufRef{SPACE_SCRATCH, 0, flags_off + 8ull * sflag_of[oi]};
-        po.sflag_index = sflag_of[oi];
-      }
       sd.n_items += d.n_items;
       if (!sname.empty()) sname += "+";
       sname += o.name;
@@ -1157,9 +1154,7 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
       if (P.ops[a].wflag_index < 0) continue;
       uint32_t target = 0;
       for (size_t b = sd.op_begin; b < a; ++b)
-        if ((!P.ops[b].waits && P.ops[b].flag_index == P.ops[a].wflag_index) ||
-            P.ops[b].sflag_index == P.ops[a].wflag_index)
-          target += P.ops[b].d.n_items;
+        if (!P.ops[b].waits && P.ops[b].flag_index == P.ops[a].wflag_index) target += P.ops[b].d.n_items;
       P.ops[a].d.wait_target = target;
     }
     if (sd.op_count > kMaxStageOps) {
@@ -1171,6 +1166,9 @@ int schedule(const FGraph& g, const TuningSpec& spec_in, uint32_t sm_count, Plan
       for (uint32_t k = 0; k < kMaxStageOps; ++k) {
         if (k < sd.op_count) run += P.ops[sd.op_begin + k].d.n_items;
         sd.item_end[k] = (k < sd.op_count) ? run : 0xffffffffu;
+        if (k < sd.op_count && P.ops[sd.op_begin + k].d.kind == OP_ATTENTION &&
+            (P.ops[sd.op_begin + k].d.flags & F_FUSED_QKV))
+          sd.attn_prefetch_from = run;
       }
     }
     P.stages.push_back(sd);

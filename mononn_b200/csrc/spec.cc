@@ -79,7 +79,7 @@ std::string spec_to_json(const Plan& plan, uint32_t sm_count) {
   root.set("row_fusion", Json::string(plan.spec.row_fusion == 1 ? "off" : "on"));
   root.set("l2_hints", Json::string(plan.spec.l2_hints == 1 ? "off" : "on"));
   root.set("row_split", Json::string(plan.spec.row_split == 1 ? "off" : "on"));
-  root.set("out_fusion", Json::string(plan.spec.out_fusion == 2 ? "on" : "off"));
+  root.set("out_fusion", Json::string(plan.spec.out_fusion == 2 ? "on" : (plan.spec.out_fusion == 3 ? "fused_qkv" : "off")));
   root.set("chain_fusion", Json::string(plan.spec.chain_fusion == 2 ? "on" : "off"));
   root.set("barrier_arrive", Json::string(plan.spec.barrier_arrive == 1 || plan.cluster > 1
                                               ? "cta"
@@ -195,7 +195,6 @@ std::string plan_to_json(const Plan& plan) {
         o.set("waits", Json::number(op.waits ? 1 : 0));
         o.set("flag_target", Json::number(op.d.flag_target));
       }
-      if (op.sflag_index >= 0) o.set("signal_flag", Json::number(op.sflag_index));
       if (op.wflag_index >= 0) {
         o.set("wait_flag", Json::number(op.wflag_index));
         o.set("wait_target", Json::number(op.d.wait_target));
@@ -304,7 +303,7 @@ int spec_from_json(const std::string& text, TuningSpec* spec, std::string* err) 
   if (const Json* cf = root.find("chain_fusion"))
     if (cf->type == Json::String) spec->chain_fusion = cf->str == "on" ? 2u : (cf->str == "off" ? 1u : 0u);
   if (const Json* of = root.find("out_fusion"))
-    if (of->type == Json::String) spec->out_fusion = of->str == "on" ? 2u : (of->str == "off" ? 1u : 0u);
+    if (of->type == Json::String) spec->out_fusion = of->str == "on" ? 2u : (of->str == "fused_qkv" ? 3u : (of->str == "off" ? 1u : 0u));
   if (const Json* rs = root.find("row_split"))
     if (rs->type == Json::String) spec->row_split = rs->str == "off" ? 1u : 0u;
   if (const Json* ba = root.find("barrier_arrive"))

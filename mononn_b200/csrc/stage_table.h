@@ -74,7 +74,6 @@ enum OpFlags : uint32_t {
 //             padding above / left of the image, K = kh*kw*C (columns K..cols-1 are written as 0)
 //  EMBED: q_col = offset added to the position index; p[4] = 0: no position table
 //  ATTENTION with F_POS_BIAS: q[0] = f16 [heads, seq, seq] added to the scaled scores (seq % 32 == 0)
-//  LAYERNORM: q[1] = arrival counter the operator adds to after every item (0: nobody waits for it)
 //  LAYERNORM and EMBED may also write q[2] = f32 copy of the result plus the f16 bias q[3]
 //  (residual + bias pre-loaded into the accumulator of the next split-K GEMM)
 struct alignas(16) OpDesc {
@@ -122,7 +121,9 @@ struct alignas(16) StageDesc {
   uint32_t op_begin;
   uint32_t op_count;  // at most kMaxStageOps
   uint32_t n_items;   // sum over the ops
-  uint32_t flags;
+  // Work items up to and including the last attention operator that computes its own projections
+  // (0: the stage has none): the CTAs from this index on prefetch those projections' weights to L2.
+  uint32_t attn_prefetch_from;
   // item_end[k] = work items of ops 0..k; entries past the last op are 0xffffffff, so the
   // owner of an item is found by comparisons alone
   uint32_t item_end[kMaxStageOps];

@@ -272,7 +272,7 @@ def test_out_projection_in_a_stage_of_its_own_keeps_parity(tmp_path):
     cfg, w, inp = small()
     text, names = bert_hlo(cfg)
     spec = describe("hlo", text)["spec"]
-    assert spec["out_fusion"] == "on"
+    assert spec["out_fusion"] == "fused_qkv"
     spec["out_fusion"] = "off"
     (tmp_path / "cluster_0").mkdir()
     (tmp_path / "cluster_0" / "best_tuning_spec.json").write_text(json.dumps(spec))
@@ -283,10 +283,10 @@ def test_out_projection_in_a_stage_of_its_own_keeps_parity(tmp_path):
     mod.close()
 
 
-def test_a_layer_as_one_stage_of_chained_operators_keeps_parity(tmp_path):
-    """`chain_fusion: on`: every operator of a layer waits on the arrival counter of the operator
-    it reads instead of a grid barrier; launched repeatedly (the counters grow from launch to
-    launch) and after a launch of a stage sub-range (which clears them)."""
+def test_ffn_gemms_chained_in_one_stage_keep_parity(tmp_path):
+    """`chain_fusion: on`: FFN-down waits on FFN-up's arrival counter instead of a grid barrier;
+    launched repeatedly (the counters grow from launch to launch) and after a launch of a stage
+    sub-range (which clears them)."""
     from mononn_b200.module import describe
     cfg, w, inp = small()
     text, names = bert_hlo(cfg)
@@ -294,13 +294,13 @@ def test_a_layer_as_one_stage_of_chained_operators_keeps_parity(tmp_path):
     (tmp_path / "cluster_0").mkdir()
     (tmp_path / "cluster_0" / "best_tuning_spec.json").write_text(json.dumps(spec))
     mod = compile_hlo(text, spec_dir=str(tmp_path), barrier_timeout_us=500000)
-    assert len(mod.plan()["stages"]) == 1 + cfg.layers
+    assert len(mod.plan()["stages"]) == 1 + 2 * cfg.layers
     mod.set_weights({names[k]: v for k, v in w.items()})
     ref = R.bert_encoder(cfg, w, inp)
-    assert_parity(run(mod, cfg, inp), ref, "one stage a layer")
+    assert_parity(run(mod, cfg, inp), ref, "FFN in one stage")
     for _ in range(3):
         mod.launch()
     mod.launch_stages(0, 1)
     mod.status()
-    assert_parity(run(mod, cfg, inp), ref, "one stage a layer, relaunched")
+    assert_parity(run(mod, cfg, inp), ref, "FFN in one stage, relaunched")
     mod.close()

@@ -93,7 +93,7 @@ def test_full_size_decoder_cost(lib_built):
     weights = 2.0 * (cfg.layers * (per_layer + 9 * h + f) + 2 * h + h * v)
     assert abs(plan["algorithmic_bytes"] - weights) / weights < 0.01
     # (hidden 2048: the projections stay a stage of their own, see the fusion rule)
-    assert len(plan["stages"]) == 2 + 4 * cfg.layers + 2
+    assert len(plan["stages"]) == 2 + 5 * cfg.layers + 2
 
 
 def _f32_regions(plan):
