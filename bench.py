@@ -522,7 +522,7 @@ def run_config(args):
         w = t5_device_weights(cfg, w)
     text, names = hlo(cfg)
     mod = compile_hlo(text, device=0, barrier_timeout_us=2000000, tuning_level=args.tuning_level,
-                      dump_dir=os.path.join(ROOT, "gpurun_out", "tune_" + name) if args.tune else None)
+                      dump_dir=(args.dump_dir or None) if args.tune else None)
     mod.set_weights({names[k]: v for k, v in w.items()})
     if family == "bert":
         inp = make_inputs(cfg, seed, pad_fraction=0.25)
@@ -665,6 +665,7 @@ def main():
     ap.add_argument("--frontend", default="hlo", choices=["hlo", "builder"],
                     help="lower from authored HLO text (the hook path) or the config builder")
     ap.add_argument("--tune", action="store_true", help="run the on-device schedule search first")
+    ap.add_argument("--dump-dir", default="", help="with --config --tune: where the tuner writes its spec and logs")
     ap.add_argument("--tuning-level", type=int, default=1, help="what --tune searches (see include/mononn.h)")
     ap.add_argument("--spec", default="", help="diagnostic: spec fields to override, e.g. row_fusion=off,grid=128")
     ap.add_argument("--config", default="", help="diagnostic: time another configuration (bert_large_b1, "
