@@ -86,6 +86,17 @@ static int finish_compile(mononn_module* m, const mononn_options* opt, mononn_mo
     delete m;
     return rc;
   }
+  // constants whose values the HLO text carried need not be set by the caller
+  for (const auto& kv : m->graph.literals) {
+    bool wanted = false;
+    for (const ConstBinding& b : m->rt.plan().consts) wanted = wanted || b.const_name == kv.first;
+    if (!wanted) continue;
+    rc = m->rt.set_constant(kv.first, kv.second.data(), kv.second.size());
+    if (rc) {
+      delete m;
+      return rc;
+    }
+  }
   *out = m;
   return MONONN_OK;
 }
@@ -271,6 +282,18 @@ int mononn_describe(const char* kind, const char* text, size_t len, const char* 
   Json::parse(spec_to_json(plan, sm_count ? sm_count : 148), &spec_j, &e2);
   root.set("plan", plan_j);
   root.set("spec", spec_j);
+  // constants whose values the HLO text carried: name -> their bytes in the element type, as hex
+  Json lits = Json::object();
+  for (const auto& kv : g.literals) {
+    static const char* digits = "0123456789abcdef";
+    std::string hex;
+    for (uint8_t b : kv.second) {
+      hex.push_back(digits[b >> 4]);
+      hex.push_back(digits[b & 15]);
+    }
+    lits.set(kv.first, Json::string(hex));
+  }
+  root.set("literals", lits);
   const std::string s = root.dump(1);
   char* buf = static_cast<char*>(std::malloc(s.size() + 1));
   if (!buf) return fail(MONONN_ERR_INVALID_ARGUMENT, "out of memory");

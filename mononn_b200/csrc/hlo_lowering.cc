@@ -17,6 +17,7 @@
 // e.g. ir_parser_fused.cc:95,311; here the caller gets MONONN_ERR_UNSUPPORTED).
 #include "hlo_lowering.h"
 
+#include <cstring>
 #include <algorithm>
 #include <cmath>
 #include <functional>
@@ -29,6 +30,57 @@
 namespace mononn {
 
 namespace {
+
+// IEEE binary16 bits of a float, round to nearest even (the device type of every weight).
+uint16_t half_bits(float f) {
+  uint32_t x;
+  std::memcpy(&x, &f, 4);
+  const uint32_t sign = (x >> 16) & 0x8000u;
+  const uint32_t mant = x & 0x007fffffu;
+  const int32_t exp = static_cast<int32_t>((x >> 23) & 0xffu);
+  if (exp == 0xff) return static_cast<uint16_t>(sign | 0x7c00u | (mant ? 0x200u : 0u));  // inf / nan
+  const int32_t e = exp - 127 + 15;
+  if (e >= 31) return static_cast<uint16_t>(sign | 0x7c00u);  // overflow
+  if (e <= 0) {                                                // subnormal or zero
+    if (e < -10) return static_cast<uint16_t>(sign);
+    const uint32_t m = mant | 0x00800000u;
+    const uint32_t shift = static_cast<uint32_t>(14 - e);
+    uint32_t h = m >> shift;
+    const uint32_t rem = m & ((1u << shift) - 1u), halfway = 1u << (shift - 1);
+    if (rem > halfway || (rem == halfway && (h & 1u))) ++h;
+    return static_cast<uint16_t>(sign | h);
+  }
+  uint32_t h = (static_cast<uint32_t>(e) << 10) | (mant >> 13);
+  const uint32_t rem = mant & 0x1fffu;
+  if (rem > 0x1000u || (rem == 0x1000u && (h & 1u))) ++h;      // may carry into the exponent: still right
+  return static_cast<uint16_t>(sign | h);
+}
+
+// The printed values of a constant in its element type; false for a type no operand can have.
+bool encode_literal(const std::string& dtype, const std::vector<double>& v, std::vector<uint8_t>* raw) {
+  if (dtype == "f16") {
+    raw->resize(v.size() * 2);
+    for (size_t i = 0; i < v.size(); ++i) {
+      const uint16_t h = half_bits(static_cast<float>(v[i]));
+      std::memcpy(raw->data() + 2 * i, &h, 2);
+    }
+  } else if (dtype == "f32") {
+    raw->resize(v.size() * 4);
+    for (size_t i = 0; i < v.size(); ++i) {
+      const float f = static_cast<float>(v[i]);
+      std::memcpy(raw->data() + 4 * i, &f, 4);
+    }
+  } else if (dtype == "s32" || dtype == "u32") {
+    raw->resize(v.size() * 4);
+    for (size_t i = 0; i < v.size(); ++i) {
+      const int32_t k = static_cast<int32_t>(v[i]);
+      std::memcpy(raw->data() + 4 * i, &k, 4);
+    }
+  } else {
+    return false;
+  }
+  return true;
+}
 
 struct Rng {
   uint64_t s = 0x9E3779B97F4A7C15ull;
@@ -197,6 +249,11 @@ class Lowering {
     t.const_name = c.name;
     t.const_transposed = transposed;
     for (int64_t d : c.shape.dims) t.const_dims.push_back(static_cast<uint32_t>(d));
+    if (!c.payload.empty() && static_cast<int64_t>(c.payload.size()) == c.shape.elements() &&
+        !g_.literals.count(c.name)) {
+      std::vector<uint8_t> raw;
+      if (encode_literal(c.shape.dtype, c.payload, &raw)) g_.literals[c.name] = std::move(raw);
+    }
     return const_tensors_[key] = g_.add_tensor(t);
   }
   int act_tensor(const std::string& name, uint32_t rows, uint32_t cols) {

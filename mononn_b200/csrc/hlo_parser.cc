@@ -225,6 +225,35 @@ bool parse_scalar_literal(const std::string& text, double* v) {
   return true;
 }
 
+// "{ {1, 2}, /*i0=1*/ {3, inf} }" -> 1 2 3 inf. false for "{...}" (values elided) or anything
+// that is not a brace list of numbers.
+bool parse_array_literal(const std::string& text, std::vector<double>* out) {
+  const std::string t = trim(text);
+  if (t.size() < 2 || t[0] != '{' || t.find("...") != std::string::npos) return false;
+  out->clear();
+  size_t i = 0;
+  while (i < t.size()) {
+    const char ch = t[i];
+    if (ch == '/' && i + 1 < t.size() && t[i + 1] == '*') {  // index comments of long literals
+      const size_t e = t.find("*/", i + 2);
+      if (e == std::string::npos) return false;
+      i = e + 2;
+      continue;
+    }
+    if (ch == '{' || ch == '}' || ch == ',' || ch == ' ' || ch == '\t') {
+      ++i;
+      continue;
+    }
+    size_t j = i;
+    while (j < t.size() && t[j] != ',' && t[j] != '}' && t[j] != ' ' && t[j] != '{') ++j;
+    double v = 0;
+    if (!parse_scalar_literal(t.substr(i, j - i), &v)) return false;
+    out->push_back(v);
+    i = j;
+  }
+  return !out->empty();
+}
+
 }  // namespace
 
 int parse_hlo_text(const std::string& text, HloModule* module, std::string* err) {
@@ -374,6 +403,7 @@ int parse_hlo_text(const std::string& text, HloModule* module, std::string* err)
       ins.param_number = std::strtoll(args.c_str(), nullptr, 10);
     } else if (ins.opcode == "constant") {
       ins.literal_is_scalar = parse_scalar_literal(args, &ins.literal);
+      if (!ins.literal_is_scalar) parse_array_literal(args, &ins.payload);
     } else {
       for (const std::string& a : split_top(args)) {
         // "f16[128,768]{1,0} %x" or "%x" or "x"

@@ -38,6 +38,9 @@ struct HloInstr {
   int64_t param_number = -1;
   bool literal_is_scalar = false;  // constant with a parsed scalar literal
   double literal = 0;
+  // constant printed with its values ("constant({{1, 2}, {3, 4}})" instead of "constant({...})"):
+  // the values in the printed (row-major, logical dimension) order
+  std::vector<double> payload;
   int line = 0;
 
   std::vector<int64_t> int_list(const std::string& key) const;  // "{1,0}" -> {1,0}

@@ -129,6 +129,9 @@ struct FGraph {
   std::vector<FTensor> tensors;
   std::vector<FOp> ops;
   std::vector<ArgDesc> args;  // parameters.., live-outs.. ; the scheduler appends temp
+  // constants whose values were printed in the HLO text, in their element type, by constant name:
+  // given to the runtime when the module is compiled, so that nobody has to set them
+  std::map<std::string, std::vector<uint8_t>> literals;
   int add_tensor(const FTensor& t) {
     tensors.push_back(t);
     return static_cast<int>(tensors.size()) - 1;

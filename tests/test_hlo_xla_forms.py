@@ -14,6 +14,7 @@ import pytest
 from hypothesis import HealthCheck, given, settings, strategies as st
 
 from mononn_b200 import bert_tiny, make_inputs, make_weights
+from mononn_b200.hlo_builder import bert_hlo
 from mononn_b200.module import describe
 from tests.helpers import ROOT, assert_parity
 
@@ -129,3 +130,50 @@ def test_xla_style_text_runs_against_the_oracle():
     mod.close()
     got = out[: cfg.tokens * cfg.hidden].reshape(cfg.tokens, cfg.hidden).astype(np.float32)
     assert_parity(got, R.bert_encoder(cfg, w, inp), "XLA-style HLO text")
+
+
+def test_constants_printed_with_their_values_are_taken_from_the_text(lib_built):
+    """XLA prints small constants with their values; `constant({...})` is only the elided form.
+    Values are converted to the constant's element type exactly as numpy rounds them (ties to
+    even, subnormals, infinities), and the module then needs no set_constant for that name."""
+    cfg = bert_tiny(batch=2, seq=16, layers=1, hidden=64, ffn=128)
+    text, names = bert_hlo(cfg)
+    rng = np.random.default_rng(9)
+    vals = np.concatenate([rng.normal(0, 1, 40), [0.0, -0.0, 65504.0, 1e6, -1e6, 6e-8, 3e-8, 2.98e-8, 6.1e-5, 1.0009765625,
+                                                  1.00048828125, 1.00146484375, float("inf"), -float("inf")]]).astype(np.float64)
+    vals = np.concatenate([vals, rng.normal(0, 1e-3, 64 - len(vals))])
+    key = names["layer0.attn.q.b"]
+    line = [l for l in text.splitlines() if f"%{key} =" in l][0]
+    body = ", ".join("inf" if v == np.inf else "-inf" if v == -np.inf else repr(float(v)) for v in vals)
+    d = describe("hlo", text.replace(line, line.replace("constant({...})", "constant({ /*i0=0*/ " + body + " })")))
+    assert list(d["literals"]) == [key]
+    got = np.frombuffer(bytes.fromhex(d["literals"][key]), dtype=np.float16)
+    with np.errstate(over="ignore"):
+        want = vals.astype(np.float32).astype(np.float16)
+    assert got.tobytes() == want.tobytes()
+    # a literal of the wrong length is not taken (the constant stays to be set by the caller)
+    short = line.replace("constant({...})", "constant({1, 2, 3})")
+    assert describe("hlo", text.replace(line, short))["literals"] == {}
+
+
+@pytest.mark.gpu
+def test_a_module_runs_with_constants_taken_from_the_text():
+    """Every bias and LayerNorm vector is printed with its values; only the matrices are set."""
+    from mononn_b200 import compile_hlo
+    from oracle import ref_encoder as R
+    cfg = bert_tiny(batch=2, seq=24, layers=1, hidden=128, ffn=256)
+    w = make_weights(cfg, 35, stress=True)
+    inp = make_inputs(cfg, 35, pad_fraction=0.25)
+    text, names = bert_hlo(cfg)
+    printed = [k for k, v in w.items() if v.ndim == 1]
+    assert len(printed) >= 10
+    for k in printed:
+        line = [l for l in text.splitlines() if f"%{names[k]} =" in l][0]
+        body = ", ".join(repr(float(x)) for x in w[k].astype(np.float32))
+        text = text.replace(line, line.replace("constant({...})", "constant({" + body + "})"))
+    mod = compile_hlo(text, barrier_timeout_us=500000)
+    mod.set_weights({names[k]: v for k, v in w.items() if k not in printed})
+    out = mod.run([inp["input_ids"], inp["attention_mask"], inp["token_type_ids"]])[0]
+    mod.close()
+    got = out[: cfg.tokens * cfg.hidden].reshape(cfg.tokens, cfg.hidden).astype(np.float32)
+    assert_parity(got, R.bert_encoder(cfg, w, inp), "constants from the text")
