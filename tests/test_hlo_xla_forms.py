@@ -172,7 +172,9 @@ def test_a_module_runs_with_constants_taken_from_the_text():
         body = ", ".join(repr(float(x)) for x in w[k].astype(np.float32))
         text = text.replace(line, line.replace("constant({...})", "constant({" + body + "})"))
     mod = compile_hlo(text, barrier_timeout_us=500000)
-    mod.set_weights({names[k]: v for k, v in w.items() if k not in printed})
+    for k, v in w.items():
+        if k not in printed:
+            mod.set_constant(names[k], np.asarray(v).astype(np.float16))
     out = mod.run([inp["input_ids"], inp["attention_mask"], inp["token_type_ids"]])[0]
     mod.close()
     got = out[: cfg.tokens * cfg.hidden].reshape(cfg.tokens, cfg.hidden).astype(np.float32)
