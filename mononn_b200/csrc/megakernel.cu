@@ -324,6 +324,10 @@ __device__ __noinline__ void report_failure(const KernelParams* P, Ctrl* ctrl, u
     st->cta = blockIdx.x;
     st->where = where;
     __threadfence();
+    if (P->host_flag != nullptr) {
+      *reinterpret_cast<volatile uint32_t*>(P->host_flag) = code;
+      __threadfence_system();
+    }
   }
 }
 

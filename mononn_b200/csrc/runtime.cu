@@ -383,6 +383,7 @@ int Runtime::launch(void* const* args, int n, void* stream, uint32_t stage_begin
   int rc = bind(args, n, stream);
   if (rc) return rc;
   KernelParams kp;
+  std::memset(&kp, 0, sizeof(kp));
   uint8_t* tab = static_cast<uint8_t*>(d_table_);
   uint8_t* scr = static_cast<uint8_t*>(d_scratch_);
   kp.stages = reinterpret_cast<const StageDesc*>(tab);
@@ -412,6 +413,7 @@ int Runtime::launch(void* const* args, int n, void* stream, uint32_t stage_begin
   kp.cluster = plan_.cluster;
   kp.l2_hints = plan_.spec.l2_hints == 1 ? 0u : 1u;
   kp.warp_arrive = arrive_mode();
+  kp.host_flag = static_cast<uint32_t*>(h_status_);  // null until infer_host has been used
   void* kargs[1] = {&kp};
   if (plan_.cluster <= 1) {
     CUDA_TRY(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(mononn_megakernel),
@@ -448,6 +450,10 @@ int Runtime::infer_host(const void* const* host_in, int n_in, void* const* host_
     if (a.kind == 0 && args[i] != host_in[a.param_number])
       CUDA_TRY(cudaMemcpyAsync(args[i], host_in[a.param_number], a.bytes, cudaMemcpyHostToDevice, st));
   }
+  // A word in pinned host memory (device-accessible under unified addressing) that the kernel
+  // sets when a bounded wait expires: no status copy sits behind the outputs' copies.
+  if (!h_status_) CUDA_TRY(cudaHostAlloc(&h_status_, sizeof(KernelStatus), cudaHostAllocMapped));
+  *static_cast<volatile uint32_t*>(h_status_) = ST_OK;
   int rc = launch_all(args, n, stream);
   if (rc) return rc;
   for (int i = 0; i < n; ++i) {
@@ -455,15 +461,12 @@ int Runtime::infer_host(const void* const* host_in, int n_in, void* const* host_
     if (a.kind == 1 && args[i] != host_out[a.param_number])
       CUDA_TRY(cudaMemcpyAsync(host_out[a.param_number], args[i], a.bytes, cudaMemcpyDeviceToHost, st));
   }
-  if (!h_status_) CUDA_TRY(cudaMallocHost(&h_status_, sizeof(KernelStatus)));
-  CUDA_TRY(cudaMemcpyAsync(h_status_, static_cast<uint8_t*>(d_scratch_) + kScratchStatusOff,
-                           sizeof(KernelStatus), cudaMemcpyDeviceToHost, st));
   cudaError_t e = cudaStreamSynchronize(st);
   if (e != cudaSuccess) {
     set_last_error(std::string("kernel failed: ") + cudaGetErrorString(e));
     return MONONN_ERR_CUDA;
   }
-  if (static_cast<const KernelStatus*>(h_status_)->code == ST_OK) return MONONN_OK;
+  if (*static_cast<volatile uint32_t*>(h_status_) == ST_OK) return MONONN_OK;
   int stage = 0, cta = 0;
   return check_status(&stage, &cta);  // formats the message and restores the module
 }
