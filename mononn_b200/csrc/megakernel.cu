@@ -2252,6 +2252,12 @@ mononn_megakernel(const __grid_constant__ KernelParams P) {
   for (uint64_t off = (static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x) * 128ull;
        off < P.hot_const_bytes; off += static_cast<uint64_t>(gridDim.x) * kThreads * 128ull)
     asm volatile("prefetch.global.L2 [%0];" ::"l"(P.hot_consts + off));
+  // The same for the stage table, the operator descriptors and the tensor maps (one image): every
+  // role of every CTA reads its descriptor at each stage, from L2 instead of HBM when the launch
+  // starts with a cold cache.
+  for (uint64_t off = (static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x) * 128ull;
+       off < P.table_bytes; off += static_cast<uint64_t>(gridDim.x) * kThreads * 128ull)
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const uint8_t*>(P.stages) + off));
 
   Ctx c;
   c.P = &P;

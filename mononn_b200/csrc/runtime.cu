@@ -413,6 +413,7 @@ int Runtime::launch(void* const* args, int n, void* stream, uint32_t stage_begin
   kp.cluster = plan_.cluster;
   kp.l2_hints = plan_.spec.l2_hints == 1 ? 0u : 1u;
   kp.warp_arrive = arrive_mode();
+  kp.table_bytes = static_cast<uint32_t>(table_bytes_);
   kp.host_flag = static_cast<uint32_t*>(h_status_);  // null until infer_host has been used
   void* kargs[1] = {&kp};
   if (plan_.cluster <= 1) {

@@ -189,6 +189,8 @@ struct KernelParams {
                          // after a CTA-wide sync
   uint32_t flag_epoch;   // launches that have added to the arrival counters since they were cleared,
                          // this one included (row ops wait for flag_epoch * their GEMM items)
+  uint32_t table_bytes;  // size of the stage / operator / tensor-map image that starts at `stages`
+                         // (prefetched to L2 at kernel start; 0: not prefetched)
   uint32_t* host_flag;   // optional word in pinned host memory, set to the status code when a bounded
                          // wait expires: the host learns of a failure without copying the status back
 };
