@@ -353,8 +353,8 @@ def run_ours(args):
         # kernel pulls the ids over PCIe and writes the hidden states to host memory
         mod.bind_host_io(host_in, [host_out])
 
-    def e2e_step():
-        mod.infer_host(host_in, [host_out])
+    # (a prepared call: same library entry point, pointer arrays and stream handle built once)
+    e2e_step = mod.host_runner(host_in, [host_out])
 
     for _ in range(3):
         e2e_step()

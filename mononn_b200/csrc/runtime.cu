@@ -445,6 +445,8 @@ int Runtime::infer_host(const void* const* host_in, int n_in, void* const* host_
     set_last_error("host buffer counts do not match the module's parameters / live-outs");
     return MONONN_ERR_INVALID_ARGUMENT;
   }
+  // One copy per parameter: two host buffers that happen to be neighbours in the address space
+  // may still be separate pinned allocations, and a copy across their boundary is refused.
   for (int i = 0; i < n; ++i) {
     const ArgDesc& a = plan_.args[i];
     // (a parameter bound to the host buffer itself -- mapped pinned memory -- is read in place)

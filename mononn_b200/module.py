@@ -197,6 +197,25 @@ class Module:
         check(lib().mononn_infer_host(self._h, self._host_in, len(host_inputs), self._host_out, len(host_outputs),
                                       self._ptrs, len(self._bufs), self._stream(stream)))
 
+    def host_runner(self, host_inputs, host_outputs, stream=None):
+        """A prepared `infer_host`: the pointer arrays and the stream handle are built once, and the
+        returned zero-argument callable does nothing but the library call (for serving loops that
+        reuse their pinned buffers; the Python bookkeeping of `infer_host` is several microseconds
+        per call). The stream is the one given, or torch's current stream at preparation time."""
+        if self._ptrs is None:
+            self.allocate()
+        keep = (list(host_inputs), list(host_outputs))   # the buffers must outlive the runner
+        h_in = (C.c_void_p * len(host_inputs))(*[t.data_ptr() for t in host_inputs])
+        h_out = (C.c_void_p * len(host_outputs))(*[t.data_ptr() for t in host_outputs])
+        fn, args = lib().mononn_infer_host, (self._h, h_in, len(host_inputs), h_out, len(host_outputs),
+                                             self._ptrs, len(self._bufs), self._stream(stream))
+
+        def run(_keep=keep):
+            rc = fn(*args)
+            if rc:
+                check(rc)
+        return run
+
     def close(self) -> None:
         if self._h:
             lib().mononn_destroy(self._h)

@@ -195,6 +195,18 @@ def test_infer_host_matches_run_and_reports_timeouts():
     mod.infer_host(hin, [hout])                   # usable again
     got = hout.numpy().view(np.float16)
     assert np.abs(got[: want.size].astype(np.float32) - want[: got.size].astype(np.float32)).max() < 5e-3
+    # the prepared form of the same call (pointer arrays and stream handle built once)
+    step = mod.host_runner(hin, [hout])
+    for _ in range(2):
+        hout.zero_()
+        step()
+        got = hout.numpy().view(np.float16)
+        assert np.abs(got[: want.size].astype(np.float32) - want[: got.size].astype(np.float32)).max() < 5e-3
+    mod.debug_skew_barrier(1)
+    with pytest.raises(capi.MononnError) as e:
+        step()
+    assert e.value.code == -6
+    step()
     mod.close()
 
 
