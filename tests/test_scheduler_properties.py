@@ -66,7 +66,7 @@ def check_counters(plan):
         assert grid >= 1
 
 
-@settings(max_examples=60, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+@settings(max_examples=60, deadline=None, derandomize=True, suppress_health_check=[HealthCheck.too_slow])
 @given(family=st.sampled_from(["bert", "opt", "t5", "vit"]), batch=st.integers(1, 12),
        seq=st.sampled_from([8, 16, 24, 40, 64, 128, 160]), layers=st.integers(1, 3), heads=st.integers(1, 3),
        picks=st.fixed_dictionaries({k: st.sampled_from(v) for k, v in CHOICES.items()}), sms=st.sampled_from([16, 148]))
