@@ -741,8 +741,9 @@ __device__ void role_weight_producer(Ctx c, uint32_t lane) {
       const uint32_t bytes = op.n_tile * kbps * 128u;
       const void* tm = tmaps + static_cast<size_t>(op.tmap_b) * 128u;
       const uint32_t groups = (nkb + kbps - 1) / kbps, rot = k_rotation(nkb, kbps);
-      for (uint32_t gi = 0; gi < groups; ++gi) {
-        const uint32_t kb = ((gi + rot) % groups) * kbps;
+      for (uint32_t gi = 0, grp = rot; gi < groups; ++gi) {
+        const uint32_t kb = grp * kbps;  // ((gi + rot) % groups) * kbps
+        if (++grp == groups) grp = 0;
         const uint32_t slot = b_cnt % kBSlots, use = b_cnt / kBSlots;
         WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->b_empty[slot], (use & 1u) ^ 1u, 0x100));
         const uint32_t full = smem_u32(&c.ctrl->b_full[slot]);
@@ -786,6 +787,13 @@ __device__ void role_act_producer(Ctx c, uint32_t lane) {
       const Item it = (item == blockIdx.x) ? first : fetch_item<true>(P, st, item, c.ctrl->desc[1], lane);
       const OpDesc& op = *it.op;
       if (op.kind != OP_GEMM && op.kind != OP_ATTENTION) continue;
+      // everything the first copy needs is worked out before the wait (descriptor fields, tile
+      // coordinates with their divisions), so that the copy is issued as soon as the barrier opens
+      const bool is_gemm = op.kind == OP_GEMM;
+      const GemmTile gt = is_gemm ? gemm_tile(op, it.local) : GemmTile{0u, 0u, 0u};
+      const void* tm_a = tmaps + static_cast<size_t>(op.tmap_a) * 128u;
+      const uint32_t g_nkb = op.kb_per_split, g_kbps = is_gemm ? op.kb_per_bslot : 1u;
+      const uint32_t g_groups = (g_nkb + g_kbps - 1) / g_kbps, g_rot = is_gemm ? k_rotation(g_nkb, g_kbps) : 0u;
       if (!waited) {
         bool ok = true;  // one lane polls the global counter; the acquire, the proxy fence and the copies are its
         if (issuer) ok = grid_wait(c, s, 0x200, false);
@@ -803,12 +811,17 @@ __device__ void role_act_producer(Ctx c, uint32_t lane) {
           fence_proxy_async_global();
           if (issuer) trace(P, s, TR_MARK0 + 7);
         }
-        const GemmTile t = gemm_tile(op, it.local);
-        const void* tm = tmaps + static_cast<size_t>(op.tmap_a) * 128u;
-        const uint32_t nkb = op.kb_per_split, kbps = op.kb_per_bslot;
-        const uint32_t groups = (nkb + kbps - 1) / kbps, rot = k_rotation(nkb, kbps);
+        const GemmTile t = gt;
+        const void* tm = tm_a;
+        const uint32_t nkb = g_nkb, kbps = g_kbps, groups = g_groups, rot = g_rot;
+        // k block of step j: ((j / kbps + rot) % groups) * kbps + j % kbps, kept in two counters
+        uint32_t grp = rot, in_grp = 0;
         for (uint32_t j = 0; j < nkb; ++j) {
-          const uint32_t kb = ((j / kbps + rot) % groups) * kbps + j % kbps;
+          const uint32_t kb = grp * kbps + in_grp;
+          if (++in_grp == kbps) {
+            in_grp = 0;
+            if (++grp == groups) grp = 0;
+          }
           const uint32_t slot = a_cnt % kASlots, use = a_cnt / kASlots;
           WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->a_empty[slot], (use & 1u) ^ 1u, 0x201));
           const uint32_t full = smem_u32(&c.ctrl->a_full[slot]);
@@ -891,8 +904,9 @@ __device__ void role_mma(Ctx c, uint32_t tmem_base, uint32_t lane) {
         const uint32_t tmem_d = tmem_base + buf * kAccCols;
         const uint32_t idesc = umma_idesc_m128(op.n_tile);
         uint32_t b_slot = 0;
-        for (uint32_t kb = 0; kb < nkb; ++kb) {
-          const uint32_t sub = kb % kbps;
+        for (uint32_t kb = 0, next_sub = 0; kb < nkb; ++kb) {
+          const uint32_t sub = next_sub;  // kb % kbps without the division (this loop is bound by its issue path)
+          next_sub = (sub + 1u == kbps) ? 0u : sub + 1u;
           if (sub == 0) {
             b_slot = b_cnt % kBSlots;
             WAIT_OR_RETURN(mbar_wait(c, &c.ctrl->b_full[b_slot], (b_cnt / kBSlots) & 1u, 0x301));
@@ -1081,10 +1095,9 @@ __device__ __forceinline__ void add4(float4& a, const float4 b) {
 // Accumulator row `quarter * 32 + lane` (TMEM lane = row) is shared by the two warps of the
 // quarter: warp `half` takes every other column group of the tile (groups of 32 columns, of 16
 // for tiles up to 32 wide so that both warps have work).
-__device__ __noinline__ void gemm_epilogue(const OpDesc& op, uint32_t local, uint32_t tmem_acc,
+__device__ __noinline__ void gemm_epilogue(const OpDesc& op, const GemmTile t, uint32_t tmem_acc,
                                            uint32_t quarter, uint32_t half, uint32_t lane,
                                            const float* bias_s, uint8_t* stg) {
-  const GemmTile t = gemm_tile(op, local);
   const uint32_t grow = t.mt * 128u + quarter * 32u + lane;
   const bool row_ok = grow < op.M;
   const bool lead = (t.ks == 0);
@@ -2076,11 +2089,12 @@ __device__ void role_simt(Ctx c, uint32_t tmem_base, uint32_t tid_in_group) {
                       : 0.f;
             WAIT_OR_RETURN(group_sync(c, 0x403));
           }
+          const GemmTile tile = gemm_tile(op, it.local);  // (its divisions are done while the MMAs run)
           if (tid_in_group == 0) trace(P, s, TR_MARK0);
           WAIT_OR_RETURN(mbar_wait_warp(c, &c.ctrl->acc_full[buf], (acc_cnt >> 1) & 1u, 0x401));
           if (tid_in_group == 0) trace(P, s, TR_MARK0 + 1);
           tc_fence_after();
-          gemm_epilogue(op, it.local, tmem_base + buf * kAccCols, quarter, half, lane, bias_s,
+          gemm_epilogue(op, tile, tmem_base + buf * kAccCols, quarter, half, lane, bias_s,
                         c.store_stage + widx * 2048u);
           tc_fence_before();
           // A row op of this stage may wait for this item. The warps count themselves per
