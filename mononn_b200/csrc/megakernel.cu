@@ -794,6 +794,7 @@ __device__ void role_act_producer(Ctx c, uint32_t lane) {
       const void* tm_a = tmaps + static_cast<size_t>(op.tmap_a) * 128u;
       const uint32_t g_nkb = op.kb_per_split, g_kbps = is_gemm ? op.kb_per_bslot : 1u;
       const uint32_t g_groups = (g_nkb + g_kbps - 1) / g_kbps, g_rot = is_gemm ? k_rotation(g_nkb, g_kbps) : 0u;
+      const AttnTile at = is_gemm ? AttnTile{0u, 0u, 0u} : attn_tile(op, it.local);
       if (!waited) {
         bool ok = true;  // one lane polls the global counter; the acquire, the proxy fence and the copies are its
         if (issuer) ok = grid_wait(c, s, 0x200, false);
@@ -831,8 +832,8 @@ __device__ void role_act_producer(Ctx c, uint32_t lane) {
           ++a_cnt;
         }
       } else {
-        const AttnTile t = attn_tile(op, it.local);
-        const void* tm = tmaps + static_cast<size_t>(op.tmap_a) * 128u;
+        const AttnTile t = at;
+        const void* tm = tm_a;
         const void* tmk = tmaps + static_cast<size_t>(op.tmap_b) * 128u;
         const void* tmv = tmaps + static_cast<size_t>(op.tmap_vt) * 128u;
         const uint32_t nc = attn_chunks(op);
@@ -1182,9 +1183,10 @@ __device__ __noinline__ void gemm_epilogue(const OpDesc& op, const GemmTile t, u
     if (staged) {
       __syncwarp();
       const uint32_t chunks = gw >> 3;  // 16-byte chunks per row in this group (2 or 4)
+      const uint32_t chunk_shift = chunks >> 1;  // log2(chunks): no division in the store loop
       const uint32_t row0 = t.mt * 128u + quarter * 32u;
       for (uint32_t idx = lane; idx < 32u * chunks; idx += 32u) {
-        const uint32_t r = idx / chunks, q = idx - r * chunks;
+        const uint32_t r = idx >> chunk_shift, q = idx & (chunks - 1u);
         const uint32_t gcol = n0 + g0 + q * 8u;
         if (row0 + r < op.M && gcol < N)
           *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(pout) + static_cast<size_t>(row0 + r) * ldo + gcol) =
