@@ -37,7 +37,7 @@ UNIT = "samples/s"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised
 # in profiles/ (None until a capture exists)
-NCU_TRAFFIC_BYTES = 175662848  # 170.76 MB read + 4.90 MB written
+NCU_TRAFFIC_BYTES = 175083520  # 170.77 MB read + 4.32 MB written
 
 
 def measured_hbm_peak():
