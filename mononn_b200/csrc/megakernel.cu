@@ -1111,6 +1111,9 @@ __device__ __noinline__ void gemm_epilogue(const OpDesc& op, const GemmTile t, u
   // row-major f16 output: a 32-column group is collected in the warp's staging block (32 rows x
   // 64 bytes, swizzled) and stored four lanes to a row instead of one row per lane
   const bool staged = (out_mode == OUT_F16);
+  // transposed output: batch and row inside the batch of this thread's row, once per item
+  const uint32_t t_batch = (out_mode == OUT_F16_T) ? grow / op.rows_per_batch : 0u;
+  const uint32_t t_row = (out_mode == OUT_F16_T) ? grow - t_batch * op.rows_per_batch : 0u;
   const uint32_t sw = (lane >> 1) & 3u;
   const uint32_t gstep = (n_tile <= 32u) ? 16u : 32u;
 #pragma unroll 1
@@ -1166,7 +1169,7 @@ __device__ __noinline__ void gemm_epilogue(const OpDesc& op, const GemmTile t, u
           for (int i = 0; i < 4; ++i)
             red_add_f32x4(o + 4 * i, v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
         } else if (out_mode == OUT_F16_T) {
-          const uint32_t b = grow / op.rows_per_batch, rib = grow % op.rows_per_batch;
+          const uint32_t b = t_batch, rib = t_row;
           const uint32_t ldt = op.ldt;
           __half* o = reinterpret_cast<__half*>(pout) + (static_cast<size_t>(b) * N + col) * ldt + rib;
 #pragma unroll
@@ -1732,13 +1735,30 @@ __device__ __noinline__ void patchify_item(const OpDesc& op, uint32_t local, uin
   (void)kh;
   const float* src = reinterpret_cast<const float*>(op.p[1]);
   __half* dst = reinterpret_cast<__half*>(op.p[0]) + static_cast<size_t>(row) * op.ldo;
+  // (ky, kx, c) of column j = lane, then of every 32nd column after it: the step of 32 columns is
+  // split once into whole window rows, whole pixels and channels, and added with carries (three
+  // divisions per element made this stage 16 % longer at batch 64; the scattered pixel reads are
+  // the rest)
+  const uint32_t per_row = C * kw;
+  const uint32_t step_ky = 32u / per_row, step_kx = (32u % per_row) / C, step_c = 32u % C;
+  uint32_t ky = lane / per_row, kx = (lane % per_row) / C, ch = lane % C;
 #pragma unroll 4
   for (uint32_t j = lane; j < op.cols; j += 32u) {
-    const uint32_t c = j % C, kx = (j / C) % kw, ky = j / (C * kw);
     const uint32_t y = y0 + ky, x = x0 + kx;  // a wrapped (negative) coordinate fails the bound test
     float v = 0.f;
-    if (j < valid && y < Himg && x < Wimg) v = src[((static_cast<size_t>(b) * C + c) * Himg + y) * Wimg + x];
+    if (j < valid && y < Himg && x < Wimg) v = src[((static_cast<size_t>(b) * C + ch) * Himg + y) * Wimg + x];
     dst[j] = __float2half_rn(v);
+    ch += step_c;
+    if (ch >= C) {
+      ch -= C;
+      ++kx;
+    }
+    kx += step_kx;
+    if (kx >= kw) {
+      kx -= kw;
+      ++ky;
+    }
+    ky += step_ky;
   }
 }
 
